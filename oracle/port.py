@@ -1,0 +1,326 @@
+"""CPU restatement of browsergrad-jit's NumPy realizer for the forward hot path.
+
+TEST INFRASTRUCTURE.  Only ``tests/``, ``__graft_entry__.smoke()`` and the ``cpu_baseline`` /
+``--impl reference`` legs of ``bench.py`` may import this module; the product package
+``browsergrad_b200`` never does.
+
+Every handler restates one handler of packages/browsergrad-jit/src/python/_realize.py with the
+same NumPy calls in the same order, so on one NumPy build the results are bit-identical to the
+reference's (pinned by ``tests/golden/*.npz``, generated from the unmodified reference by
+``tests/golden/make_golden.py``).  NumPy itself (ufunc loops, pairwise ``np.sum``, OpenBLAS
+``sgemm`` behind ``@``) is the third-party arithmetic underneath; the reference pins it only
+indirectly through Pyodide ^0.26.4 (packages/browsergrad-jit/package.json peerDependencies),
+this oracle is pinned to the NumPy of the image the golden vectors were generated with
+(version stored in each fixture).
+
+``realize(root, store)`` walks any graph of nodes carrying ``op, inputs, shape, dtype, arg``.
+``prepare`` of the product package is *not* used here: callers pass the graph they want
+realized (the tests pass the post-pass graph, as ``_realize.realize`` would see it,
+_realize.py:1890-1902).
+"""
+from __future__ import annotations
+
+from typing import Any, Callable, Dict, List
+
+import numpy as np
+
+
+class OracleError(RuntimeError):
+    pass
+
+
+def toposort(root: Any) -> List[Any]:
+    """_ir.py:403-430."""
+    order: List[Any] = []
+    seen: set = set()
+    stack = [(root, 0)]
+    while stack:
+        node, i = stack[-1]
+        if id(node) in seen:
+            stack.pop()
+            continue
+        if i < len(node.inputs):
+            stack[-1] = (node, i + 1)
+            child = node.inputs[i]
+            if id(child) not in seen:
+                stack.append((child, 0))
+            continue
+        seen.add(id(node))
+        order.append(node)
+        stack.pop()
+    return order
+
+
+def _in(node: Any, vt: Dict[int, np.ndarray], i: int) -> np.ndarray:
+    return vt[id(node.inputs[i])]
+
+
+def _h_buffer(node, vt, store):  # _realize.py:170-179
+    arr = store.get(node.arg)
+    if tuple(arr.shape) != tuple(node.shape):
+        raise OracleError(f"BUFFER {node.arg!r} shape {arr.shape} != IR {node.shape}")
+    return arr
+
+
+def _h_load(node, vt, store):  # _realize.py:182-185
+    return _in(node, vt, 0)
+
+
+def _h_const(node, vt, store):  # _realize.py:187-189
+    return np.asarray(node.arg["value"], dtype=np.dtype(node.dtype))
+
+
+def _h_cast(node, vt, store):  # _realize.py:210-212
+    dt = node.arg["dtype"]
+    if dt == "bfloat16":
+        return to_bfloat16(_in(node, vt, 0))
+    return _in(node, vt, 0).astype(np.dtype(dt), copy=False)
+
+
+def _h_div(node, vt, store):  # _realize.py:227-234
+    out = _in(node, vt, 0) / _in(node, vt, 1)
+    return out.astype(np.dtype(node.dtype), copy=False)
+
+
+_CMP = {"eq": np.equal, "ne": np.not_equal, "lt": np.less, "le": np.less_equal,
+        "gt": np.greater, "ge": np.greater_equal}
+
+
+def _h_cmp(node, vt, store):  # _realize.py:386-392
+    return _CMP[node.arg["op"]](_in(node, vt, 0), _in(node, vt, 1))
+
+
+def to_bfloat16(x: np.ndarray) -> np.ndarray:
+    """Round float32 to bfloat16 (nearest even), returned as float32 holding bf16 values.
+
+    Extension of this build: the reference IR has no bfloat16 (_ir.py:348-353).  NumPy has no
+    bf16 dtype, so a "bfloat16" tensor is carried as float32 whose low 16 bits are zero.
+    """
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    u = x.view(np.uint32)
+    rounded = (u + (np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1)))) & np.uint32(0xFFFF0000)
+    out = rounded.view(np.float32).copy()
+    nan = np.isnan(x)
+    if nan.any():
+        out[nan] = np.nan
+    return out
+
+
+def _h_matmul(node, vt, store):  # _realize.py:395-410
+    a, b = _in(node, vt, 0), _in(node, vt, 1)
+    if node.dtype == "bfloat16":
+        return to_bfloat16(a.astype(np.float32) @ b.astype(np.float32))
+    if a.dtype == np.float16 or b.dtype == np.float16:
+        out = a.astype(np.float32) @ b.astype(np.float32)
+        return out.astype(np.dtype(node.dtype), copy=False)
+    return a @ b
+
+
+def _h_layer_norm(node, vt, store):  # _realize.py:1008-1034
+    x, weight, bias = _in(node, vt, 0), _in(node, vt, 1), _in(node, vt, 2)
+    rows, cols = int(node.arg["rows"]), int(node.arg["cols"])
+    eps = float(node.arg.get("eps", 1e-5))
+    x2 = x.reshape(rows, cols).astype(np.float32, copy=False)
+    w = weight.reshape(cols).astype(np.float32, copy=False)
+    mean = x2.mean(axis=1, keepdims=True)
+    centered = x2 - mean
+    var = (centered * centered).mean(axis=1, keepdims=True)
+    inv_std = 1.0 / np.sqrt(var + eps)
+    x_hat = centered * inv_std
+    b = bias.reshape(cols).astype(np.float32, copy=False)
+    out = x_hat * w.reshape(1, cols) + b.reshape(1, cols)
+    return out.reshape(x.shape).astype(np.dtype(node.dtype), copy=False)
+
+
+_REDUCE = {"sum": np.sum, "max": np.max, "min": np.min, "mean": np.mean,
+           "argmax": np.argmax, "argmin": np.argmin, "any": np.any, "all": np.all}
+
+
+def _h_reduce(node, vt, store):  # _realize.py:1094-1111
+    x = _in(node, vt, 0)
+    op = node.arg["op"]
+    axis = node.arg.get("axis", None)
+    keepdims = node.arg.get("keepdims", False)
+    fn = _REDUCE[op]
+    if op in ("argmax", "argmin"):
+        out = fn(x, axis=axis)
+        if keepdims and axis is not None:
+            out = np.expand_dims(out, axis=axis)
+    else:
+        out = fn(x, axis=axis, keepdims=keepdims)
+    return np.asarray(out, dtype=np.dtype(node.dtype))
+
+
+def _h_where(node, vt, store):  # _realize.py:1453-1459
+    sel = np.where(_in(node, vt, 0), _in(node, vt, 1), _in(node, vt, 2))
+    return np.array(sel, dtype=np.dtype(node.dtype), copy=True).reshape(node.shape)
+
+
+def _h_index(node, vt, store):  # _realize.py:1462-1485
+    x, idx = _in(node, vt, 0), _in(node, vt, 1)
+    dim = int(node.arg["dim"])
+    if idx.size and (bool(np.any(idx < 0)) or bool(np.any(idx >= x.shape[dim]))):
+        raise OracleError(f"gather: index values must be in [0, {x.shape[dim]})")
+    coords = []
+    for d in range(idx.ndim):
+        if d == dim:
+            coords.append(idx)
+        else:
+            shape = [1] * idx.ndim
+            shape[d] = idx.shape[d]
+            coords.append(np.broadcast_to(np.arange(idx.shape[d]).reshape(shape), idx.shape))
+    return np.array(x[tuple(coords)], dtype=np.dtype(node.dtype), copy=True)
+
+
+def _h_fused_elementwise(node, vt, store):  # _realize.py:1557-1600
+    ext = [vt[id(i)] for i in node.inputs]
+    steps: List[np.ndarray] = []
+
+    def res(ref: int) -> np.ndarray:
+        return ext[-ref - 1] if ref < 0 else steps[ref]
+
+    for opcode, lhs, rhs in node.arg["ops"]:
+        a = res(lhs)
+        if opcode == "ADD":
+            steps.append(a + res(rhs))
+        elif opcode == "MUL":
+            steps.append(a * res(rhs))
+        elif opcode == "DIV":
+            steps.append(a / res(rhs))
+        elif opcode == "NEG":
+            steps.append(-a)
+        elif opcode == "EXP":
+            steps.append(np.exp(a))
+        elif opcode == "LOG":
+            steps.append(np.log(a))
+        else:
+            raise OracleError(f"FUSED_ELEMENTWISE: unsupported inner opcode {opcode!r}")
+    return steps[-1]
+
+
+def _h_fused_softmax(node, vt, store):  # _realize.py:1603-1614
+    x = _in(node, vt, 0)
+    axis = node.arg["axis"]
+    m = x.max(axis=axis, keepdims=True)
+    e = np.exp(x - m)
+    return e / e.sum(axis=axis, keepdims=True)
+
+
+def _h_cross_entropy(node, vt, store):
+    """Index-target branch of ``execute_cross_entropy_arrays``
+    (_framework_contracts.py:3644-3664 log-probabilities, :3667-3702 selection,
+    :3725-3753 reduction, :3756-3835 driver), without class weights or label smoothing."""
+    arg = node.arg
+    if arg.get("target_mode") != "indices" or arg.get("has_weight") or arg.get("label_smoothing"):
+        raise OracleError("cross_entropy: only unweighted class-index targets are restated")
+    logits_in, targets = _in(node, vt, 0), _in(node, vt, 1)
+    batch_rank = int(arg.get("batch_rank", 0))
+    class_axis = batch_rank + 1 if logits_in.ndim > batch_rank + 1 else batch_rank
+    dtype = np.dtype("float32" if node.dtype == "float16" else node.dtype)  # :3613-3616
+    logits = logits_in.astype(dtype, copy=False)
+    maximum = np.max(logits, axis=class_axis, keepdims=True)
+    shifted = np.empty(logits.shape, dtype=dtype)
+    np.subtract(logits, maximum, out=shifted)
+    exps = np.empty(logits.shape, dtype=dtype)
+    with np.errstate(over="ignore", invalid="ignore"):
+        np.exp(shifted, out=exps)
+    norm = exps.sum(axis=class_axis, keepdims=True, dtype=dtype)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        np.log(norm, out=norm)
+    np.subtract(shifted, norm, out=shifted)
+    ignore = int(arg["ignore_index"])
+    valid = targets != ignore
+    n_class = logits.shape[class_axis]
+    if bool(valid.any()):
+        lo = int(np.min(targets, where=valid, initial=0))
+        hi = int(np.max(targets, where=valid, initial=0))
+        if lo < 0 or hi >= n_class:
+            raise OracleError(f"cross_entropy: target values must be in [0, {n_class})")
+    safe = np.where(valid, targets, 0)
+    sel_w = valid.astype(dtype, copy=False)
+    class_last = np.moveaxis(shifted, class_axis, -1)
+    per = np.take_along_axis(class_last, safe[..., None], axis=-1)[..., 0]
+    np.negative(per, out=per)
+    np.copyto(per, 0.0, where=~valid)
+    red = arg["reduction"]
+    if red == "none":
+        result = per
+    else:
+        axes = tuple(range(batch_rank, per.ndim))
+        num = per.sum(axis=axes, dtype=dtype) if axes else np.asarray(per)
+        if red == "sum":
+            result = num
+        else:
+            den = valid.sum(axis=axes) if axes else np.asarray(valid)
+            with np.errstate(divide="ignore", invalid="ignore"):
+                result = np.divide(num, den)
+    return np.array(result, dtype=np.dtype(node.dtype), copy=True)
+
+
+def _h_attention_forward(node, vt, store):  # _framework_contracts.py:2881-2932
+    q, k, v = (_in(node, vt, i) for i in range(3))
+    for a in (q, k, v):
+        if a.dtype != np.float32 or not bool(np.isfinite(a).all()):
+            raise OracleError("attention_forward inputs must be finite float32")
+    scale = float(node.arg["scale"])
+    with np.errstate(over="ignore", invalid="ignore", divide="ignore"):
+        scores = np.matmul(q, np.swapaxes(k, -1, -2))
+        scores = np.asarray(scores * np.float32(scale), dtype=np.float32)
+        mx = scores.max(axis=-1, keepdims=True)
+        e = np.exp(scores - mx)
+        den = e.sum(axis=-1, keepdims=True, dtype=np.float32)
+        out = np.matmul(e / den, v)
+    return np.array(out, dtype=np.float32, copy=True)
+
+
+def _h_broadcast_to(node, vt, store):  # _realize.py:1515-1529
+    return np.broadcast_to(_in(node, vt, 0), tuple(node.arg["shape"])).copy()
+
+
+_DISPATCH: Dict[str, Callable] = {
+    "BUFFER": _h_buffer,
+    "LOAD": _h_load,
+    "CONST": _h_const,
+    "CAST": _h_cast,
+    "ADD": lambda n, vt, s: _in(n, vt, 0) + _in(n, vt, 1),      # _realize.py:215-218
+    "MUL": lambda n, vt, s: _in(n, vt, 0) * _in(n, vt, 1),      # :221-224
+    "DIV": _h_div,
+    "NEG": lambda n, vt, s: -_in(n, vt, 0),                     # :237-238
+    "EXP": lambda n, vt, s: np.exp(_in(n, vt, 0)),              # :241-242
+    "LOG": lambda n, vt, s: np.log(_in(n, vt, 0)),              # :245-246
+    "ABS": lambda n, vt, s: np.abs(_in(n, vt, 0)),
+    "SIN": lambda n, vt, s: np.sin(_in(n, vt, 0)),
+    "COS": lambda n, vt, s: np.cos(_in(n, vt, 0)),
+    "SIGN": lambda n, vt, s: np.sign(_in(n, vt, 0)),
+    "ISNAN": lambda n, vt, s: np.isnan(_in(n, vt, 0)),          # :1076-1080
+    "CMP": _h_cmp,
+    "MATMUL": _h_matmul,
+    "LAYER_NORM": _h_layer_norm,
+    "REDUCE": _h_reduce,
+    "RESHAPE": lambda n, vt, s: _in(n, vt, 0).reshape(n.arg["new_shape"]),         # :1114-1116
+    "PERMUTE": lambda n, vt, s: np.transpose(_in(n, vt, 0), axes=n.arg["axes"]),   # :1119-1121
+    "WHERE": _h_where,
+    "INDEX": _h_index,
+    "BROADCAST_TO": _h_broadcast_to,
+    "FUSED_ELEMENTWISE": _h_fused_elementwise,
+    "FUSED_SOFTMAX": _h_fused_softmax,
+    "CROSS_ENTROPY": _h_cross_entropy,
+    "ATTENTION_FORWARD": _h_attention_forward,
+}
+
+
+def supported_ops() -> frozenset:
+    return frozenset(_DISPATCH)
+
+
+def realize(root: Any, store: Any) -> np.ndarray:
+    """Dispatch loop of ``_realize.realize`` (_realize.py:1902-1920) without the passes."""
+    vt: Dict[int, np.ndarray] = {}
+    with np.errstate(all="ignore"):
+        for node in toposort(root):
+            h = _DISPATCH.get(node.op)
+            if h is None:
+                raise OracleError(f"oracle: opcode {node.op!r} is not restated")
+            vt[id(node)] = h(node, vt, store)
+    out = vt[id(root)]
+    return np.asarray(out)

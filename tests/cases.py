@@ -1,0 +1,210 @@
+"""Parity cases shared by the golden generator, the CPU tests and the GPU tests.
+
+A case = seeded inputs + a builder that takes an ``api`` namespace, so the same definition
+produces the reference's graph (``RefApi`` over ``browsergrad_jit``), this build's graph
+(``browsergrad_b200.graph``) and the oracle's input.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List
+
+import numpy as np
+
+from browsergrad_b200 import configs
+
+
+class RefApi:
+    """Adapter exposing the reference's ``browsergrad_jit`` module with the builder names
+    ``browsergrad_b200.graph`` uses."""
+
+    def __init__(self, bg: Any) -> None:
+        F = bg.F
+        self.relu, self.gelu, self.softmax, self.linear = F.relu, F.gelu, F.softmax, F.linear
+        self.layer_norm, self.cross_entropy = F.layer_norm, F.cross_entropy
+        self.scaled_dot_product_attention = F.scaled_dot_product_attention
+        self.exp, self.where, self.tanh = bg.exp, bg.where, bg.tanh
+        self.attention_forward = bg.kernels.attention_forward
+        self.autocast = lambda dtype="float16": bg.amp.autocast(dtype=dtype)
+        self.from_numpy = bg.from_numpy
+
+
+def canonical_arg(op: str, arg: Any) -> Any:
+    if op == "BUFFER":
+        return "buffer"
+    if isinstance(arg, dict):
+        return {k: canonical_arg("", v) for k, v in sorted(arg.items()) if k != "vjp_of"}
+    if isinstance(arg, (tuple, list)):
+        return [canonical_arg("", v) for v in arg]
+    if isinstance(arg, float):
+        return repr(arg)
+    if isinstance(arg, (np.integer,)):
+        return int(arg)
+    if isinstance(arg, (np.floating,)):
+        return repr(float(arg))
+    return arg
+
+
+def signature(order: List[Any]) -> List[Any]:
+    pos = {id(n): i for i, n in enumerate(order)}
+    return [[n.op, [pos[id(i)] for i in n.inputs], list(n.shape), n.dtype,
+             canonical_arg(n.op, n.arg)] for n in order]
+
+
+@dataclass
+class Case:
+    inputs: Callable[[], Dict[str, np.ndarray]]
+    build: Callable[[Any, Dict[str, Any], Dict[str, np.ndarray]], Any]
+    kind: str = "float"          # "float" (tolerance) or "exact" (bit-exact)
+    rtol: float = 1e-5
+    reference_has_it: bool = True
+
+
+def _rng(seed: int) -> np.random.Generator:
+    return np.random.default_rng(seed)
+
+
+def _misc_inputs() -> Dict[str, np.ndarray]:
+    r = _rng(100)
+    return {
+        "x": r.standard_normal((6, 5, 33), dtype=np.float32),
+        "p": (r.standard_normal((6, 5, 33), dtype=np.float32) ** 2 + np.float32(0.1)),
+        "row": r.standard_normal((33,), dtype=np.float32),
+        "col": r.standard_normal((5, 1), dtype=np.float32),
+        "i": r.integers(-1000, 1000, (6, 5, 33), dtype=np.int64),
+        "j": r.integers(-50, 50, (5, 33), dtype=np.int64),
+        "i32": r.integers(-2 ** 30, 2 ** 30, (6, 5, 33), dtype=np.int32),
+        "big": r.integers(-2 ** 62, 2 ** 62, (6, 5, 33), dtype=np.int64),
+        "d": r.standard_normal((6, 5, 33)),
+        "h": r.standard_normal((6, 5, 33)).astype(np.float16),
+        "g": np.linspace(0.5, 1.5, 33, dtype=np.float32),
+        "be": np.linspace(-0.2, 0.2, 33, dtype=np.float32),
+        "table": r.standard_normal((17, 33), dtype=np.float32),
+        "tidx": np.ascontiguousarray(np.broadcast_to(r.integers(0, 17, (9, 1), dtype=np.int64), (9, 33))),
+        "cidx": r.integers(0, 33, (17, 4), dtype=np.int64),
+        "bm": r.standard_normal((2, 1, 7, 9), dtype=np.float32),
+        "bn": r.standard_normal((3, 9, 4), dtype=np.float32),
+        "v9": r.standard_normal((9,), dtype=np.float32),
+        "m79": r.standard_normal((7, 9), dtype=np.float32),
+        "logits": r.standard_normal((12, 7), dtype=np.float32) * np.float32(3),
+        "tgt": np.array([0, 6, 3, -100, 2, 2, 5, -100, 1, 0, 4, 6], dtype=np.int64),
+        "logits3": r.standard_normal((4, 7, 5), dtype=np.float32),
+        "tgt3": r.integers(0, 7, (4, 5), dtype=np.int64),
+    }
+
+
+def _attn_small(b: int, h: int, s: int, d: int) -> Callable[[], Dict[str, np.ndarray]]:
+    def make() -> Dict[str, np.ndarray]:
+        t = configs.attention_inputs(b, h, s, d)
+        t["mask"] = configs.causal_mask(s)
+        return t
+    return make
+
+
+def _gpt_tiny() -> Dict[str, np.ndarray]:
+    return configs.gpt_inputs(layers=2, d_model=64, heads=4, d_mlp=128, vocab=211, seq=32, batch=2)
+
+
+CASES: Dict[str, Case] = {
+    # -- the five configurations at sizes the CPU oracle finishes in well under a second ----
+    "c1_mlp_ce": Case(lambda: configs.mlp_inputs(), lambda api, t, raw: configs.mlp_loss(api, t)),
+    "c2_y": Case(lambda: configs.chain_inputs(64, 512), lambda api, t, raw: configs.chain_y(api, t)),
+    "c2_rowsum": Case(lambda: configs.chain_inputs(64, 512),
+                      lambda api, t, raw: configs.chain_rowsum(api, t)),
+    "c2_rowsoftmax": Case(lambda: configs.chain_inputs(64, 512),
+                          lambda api, t, raw: configs.chain_rowsoftmax(api, t)),
+    "c2_y_ragged": Case(lambda: configs.chain_inputs(7, 37),
+                        lambda api, t, raw: configs.chain_y(api, t)),
+    "c2_rowsum_ragged": Case(lambda: configs.chain_inputs(7, 37),
+                             lambda api, t, raw: configs.chain_rowsum(api, t)),
+    "c2_rowsoftmax_ragged": Case(lambda: configs.chain_inputs(7, 37),
+                                 lambda api, t, raw: configs.chain_rowsoftmax(api, t)),
+    "c2_rowsoftmax_long": Case(lambda: configs.chain_inputs(3, 9001),
+                               lambda api, t, raw: configs.chain_rowsoftmax(api, t)),
+    "c3_linear_gelu": Case(lambda: configs.linear_inputs(96, 80, 72),
+                           lambda api, t, raw: configs.linear_gelu(api, t)),
+    "c3_linear_gelu_128": Case(lambda: configs.linear_inputs(256, 128, 192),
+                               lambda api, t, raw: configs.linear_gelu(api, t)),
+    "c3_linear_gelu_f16": Case(lambda: configs.linear_inputs(96, 80, 72),
+                               lambda api, t, raw: configs.linear_gelu(api, t, "float16"), rtol=2e-2),
+    "c3_linear_gelu_f16_128": Case(lambda: configs.linear_inputs(256, 128, 192),
+                                   lambda api, t, raw: configs.linear_gelu(api, t, "float16"),
+                                   rtol=2e-2),
+    "c3_linear_gelu_bf16": Case(lambda: configs.linear_inputs(256, 128, 192),
+                                lambda api, t, raw: configs.linear_gelu(api, t, "bfloat16"),
+                                rtol=2e-2, reference_has_it=False),
+    "c4_attn_mask": Case(_attn_small(2, 3, 64, 16),
+                         lambda api, t, raw: configs.attention(api, t, "mask")),
+    "c4_attn_causal": Case(_attn_small(2, 3, 64, 16),
+                           lambda api, t, raw: configs.attention(api, t, "causal")),
+    "c4_attn_mask_d64": Case(_attn_small(1, 2, 160, 64),
+                             lambda api, t, raw: configs.attention(api, t, "mask")),
+    "c4_attn_causal_d64": Case(_attn_small(1, 2, 160, 64),
+                               lambda api, t, raw: configs.attention(api, t, "causal")),
+    "c4_attn_full": Case(_attn_small(1, 2, 96, 32),
+                         lambda api, t, raw: configs.attention(api, t, "none")),
+    "c5_gpt_tiny": Case(_gpt_tiny, lambda api, t, raw: configs.gpt_forward(api, t, raw["_meta"]),
+                        rtol=1e-4),
+    # -- single ops and edge cases -----------------------------------------------------
+    "typed_attention": Case(_attn_small(2, 2, 40, 24),
+                            lambda api, t, raw: api.attention_forward(t["q"], t["k"], t["v"])),
+    "layer_norm": Case(_misc_inputs, lambda api, t, raw: api.layer_norm(t["x"], (33,), t["g"], t["be"])),
+    "layer_norm_2axes": Case(_misc_inputs, lambda api, t, raw: api.layer_norm(t["x"], (5, 33))),
+    "gather_rows": Case(_misc_inputs, lambda api, t, raw: t["table"].gather(0, t["tidx"]), kind="exact"),
+    "gather_cols": Case(_misc_inputs, lambda api, t, raw: t["table"].gather(1, t["cidx"]), kind="exact"),
+    "int_arith": Case(_misc_inputs, lambda api, t, raw: (t["i"] * t["j"] + t["i"]) * 3 + (-t["j"]),
+                      kind="exact"),
+    "int_wrap64": Case(_misc_inputs, lambda api, t, raw: t["big"] * t["i"] + t["big"], kind="exact"),
+    "int32_arith": Case(_misc_inputs, lambda api, t, raw: t["i32"] * t["i32"] + t["i32"], kind="exact"),
+    "int_cmp_where": Case(_misc_inputs,
+                          lambda api, t, raw: api.where(t["i"] > t["j"], t["i"], t["j"] * 2),
+                          kind="exact"),
+    "bool_cmp": Case(_misc_inputs, lambda api, t, raw: t["x"] >= t["row"], kind="exact"),
+    "argmax_last": Case(_misc_inputs, lambda api, t, raw: t["x"].argmax(axis=-1), kind="exact"),
+    "argmax_mid": Case(_misc_inputs, lambda api, t, raw: t["x"].argmax(axis=1), kind="exact"),
+    "argmax_all": Case(_misc_inputs, lambda api, t, raw: t["x"].argmax(), kind="exact"),
+    "int_sum": Case(_misc_inputs, lambda api, t, raw: t["i"].sum(axis=0), kind="exact"),
+    "int_max_last": Case(_misc_inputs, lambda api, t, raw: t["i"].max(axis=-1), kind="exact"),
+    "reduce_max_keep": Case(_misc_inputs, lambda api, t, raw: t["x"].max(axis=-1, keepdims=True),
+                            kind="exact"),
+    "reduce_min_axis0": Case(_misc_inputs, lambda api, t, raw: t["x"].min(axis=0), kind="exact"),
+    "reduce_mean_mid": Case(_misc_inputs, lambda api, t, raw: t["x"].mean(axis=1)),
+    "reduce_sum_all": Case(_misc_inputs, lambda api, t, raw: t["p"].sum()),
+    "reduce_sum_two_axes": Case(_misc_inputs, lambda api, t, raw: t["p"].sum(axis=(0, 2))),
+    "broadcast_chain": Case(_misc_inputs,
+                            lambda api, t, raw: (t["x"] * t["row"] + t["col"]) / t["p"]),
+    "log_exp": Case(_misc_inputs, lambda api, t, raw: (t["p"].log() * 0.5).exp()),
+    "f64_chain": Case(_misc_inputs, lambda api, t, raw: (t["d"] * t["d"] + t["x"]).exp() / 3.0),
+    "f16_chain": Case(_misc_inputs, lambda api, t, raw: t["h"] * t["h"] + t["h"], rtol=2e-3),
+    "cast_chain": Case(_misc_inputs,
+                       lambda api, t, raw: (t["x"] * 100.0).cast("int32").cast("float32") + t["row"]),
+    "cast_f16": Case(_misc_inputs, lambda api, t, raw: t["x"].cast("float16"), kind="exact"),
+    "cast_bool": Case(_misc_inputs, lambda api, t, raw: t["j"].cast("bool"), kind="exact"),
+    "softmax_mid_axis": Case(_misc_inputs, lambda api, t, raw: api.softmax(t["x"], dim=1)),
+    "softmax_axis0": Case(_misc_inputs, lambda api, t, raw: api.softmax(t["x"], dim=0)),
+    "permute_copy": Case(_misc_inputs, lambda api, t, raw: t["x"].permute(2, 0, 1), kind="exact"),
+    "permute_add": Case(_misc_inputs, lambda api, t, raw: t["x"].permute(1, 0, 2) + t["row"]),
+    "reshape_reduce": Case(_misc_inputs, lambda api, t, raw: t["x"].reshape(30, 33).sum(axis=0)),
+    "matmul_batched_bcast": Case(_misc_inputs, lambda api, t, raw: t["bm"] @ t["bn"]),
+    "matmul_vec_rhs": Case(_misc_inputs, lambda api, t, raw: t["m79"] @ t["v9"]),
+    "matmul_vec_lhs": Case(_misc_inputs, lambda api, t, raw: t["v9"] @ t["bn"]),
+    "matmul_dot": Case(_misc_inputs, lambda api, t, raw: t["v9"] @ t["v9"]),
+    "matmul_f64": Case(_misc_inputs, lambda api, t, raw: t["d"] @ t["d"].permute(0, 2, 1), rtol=1e-12),
+    "matmul_int": Case(_misc_inputs, lambda api, t, raw: t["i"] @ t["i"].permute(0, 2, 1), kind="exact"),
+    "relu_linear_relu": Case(lambda: configs.linear_inputs(33, 17, 129),
+                             lambda api, t, raw: api.relu(api.linear(t["x"], t["w"], t["bias"]))),
+    "linear_nobias_odd": Case(lambda: configs.linear_inputs(130, 70, 250),
+                              lambda api, t, raw: api.linear(t["x"], t["w"])),
+    "ce_mean_ignore": Case(_misc_inputs, lambda api, t, raw: api.cross_entropy(t["logits"], t["tgt"])),
+    "ce_sum": Case(_misc_inputs,
+                   lambda api, t, raw: api.cross_entropy(t["logits"], t["tgt"], reduction="sum")),
+    "ce_none": Case(_misc_inputs,
+                    lambda api, t, raw: api.cross_entropy(t["logits"], t["tgt"], reduction="none")),
+    "ce_spatial": Case(_misc_inputs, lambda api, t, raw: api.cross_entropy(t["logits3"], t["tgt3"])),
+    "tanh": Case(_misc_inputs, lambda api, t, raw: api.tanh(t["x"])),
+    "scalar_only": Case(_misc_inputs, lambda api, t, raw: t["row"].sum() * 2.0 + 1.0),
+    "empty_rows": Case(lambda: {"a": np.zeros((0, 8), np.float32), "b": np.ones((0, 8), np.float32)},
+                       lambda api, t, raw: api.relu(t["a"] * t["b"])),
+    "single_element": Case(lambda: {"a": np.array([[2.5]], np.float32)},
+                           lambda api, t, raw: api.softmax(t["a"] * t["a"], dim=-1)),
+}
