@@ -1,0 +1,166 @@
+// Internal declarations shared by the translation units of libbgcuda.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <functional>
+#include <map>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/bgcuda.h"
+
+namespace bg {
+
+constexpr int kMaxRank = BG_MAX_RANK;
+
+inline int dtype_size(int dt) {
+  switch (dt) {
+    case BG_F16: case BG_BF16: case BG_I16: case BG_U16: return 2;
+    case BG_F32: case BG_I32: case BG_U32: return 4;
+    case BG_F64: case BG_I64: case BG_U64: return 8;
+    case BG_I8: case BG_U8: case BG_BOOL: return 1;
+  }
+  return 0;
+}
+inline bool dtype_is_float(int dt) { return dt == BG_F16 || dt == BG_F32 || dt == BG_F64 || dt == BG_BF16; }
+inline bool dtype_is_int(int dt) { return dt >= BG_I8 && dt <= BG_U64; }
+const char* dtype_name(int dt);
+const char* op_name(int op);
+
+// ---------------------------------------------------------------------------------------
+// Elementwise program: the descriptor the generic kernel interprets.  It is passed as a
+// __grid_constant__ kernel parameter, i.e. it lives in the constant bank.
+// ---------------------------------------------------------------------------------------
+enum EwType : uint8_t { T_F32 = 0, T_F64 = 1, T_I64 = 2, T_B = 3 };
+
+enum EwOp : uint8_t {
+  E_LOAD = 0,   // dst <- inputs[aux], converted to `type`
+  E_CONST,      // dst <- consts[aux] (double bits for floats, int64 bits for T_I64/T_B)
+  E_ADD, E_MUL, E_DIV, E_NEG, E_EXP, E_LOG, E_ABS, E_SIGN, E_SIN, E_COS,
+  E_ISNAN,      // dst(T_B) <- isnan(a) ; type = class of a
+  E_CMP,        // dst(T_B) <- a (aux = bg_cmp) b ; type = class of a, b
+  E_WHERE,      // dst <- a(T_B) ? b : c
+  E_CVT,        // dst(type) <- a (aux low 4 bits = source class); applies narrowing
+  E_NARROW,     // dst <- round/wrap a to the storage dtype in aux (f16, bf16, i8..u32, bool)
+  E_AND, E_OR,  // bool arithmetic (NumPy: bool*bool = and, bool+bool = or)
+  E_STORE,      // outputs[aux] <- a
+  E_OPCOUNT
+};
+
+struct EwInstr {
+  uint8_t op, type, dst, a, b, c;
+  uint16_t aux;
+};
+
+constexpr int kEwMaxInstr = 160;
+constexpr int kEwMaxInputs = 12;
+constexpr int kEwMaxOutputs = 4;
+constexpr int kEwMaxConsts = 24;
+constexpr int kEwMaxDims = 5;
+
+enum EwAddr : int32_t { A_CONTIG = 0, A_SCALAR = 1, A_STRIDED = 2 };
+
+struct EwOperand {
+  const void* ptr;
+  int32_t dtype;
+  int32_t mode;                 // EwAddr
+  int32_t vec_ok;               // 16-byte (or natural 4-element) vector access allowed
+  int32_t pad;
+  int64_t stride[kEwMaxDims];   // element strides per collapsed iteration dim (A_STRIDED)
+};
+
+struct EwOutput {
+  void* ptr;
+  int32_t dtype;
+  int32_t vec_ok;
+};
+
+enum RowTail : int32_t {
+  TAIL_NONE = 0,
+  TAIL_REDUCE = 1,     // tail_arg = bg_reduce; result per row -> outputs[tail_out]
+  TAIL_SOFTMAX = 2,    // softmax over the row of register tail_reg -> outputs[tail_out]
+  TAIL_LAYERNORM = 3,  // (x-mean)*rsqrt(var+eps)*w+b; w = inputs[tail_w], b = inputs[tail_b]
+  TAIL_LOGSOFTMAX_PICK = 4  // cross entropy per row: -(log_softmax(x)[target]); target = inputs[tail_w]
+};
+
+struct EwProgram {
+  int32_t n_instr;
+  int32_t n_regs;
+  int32_t wide;                 // any 8-byte register class in use
+  int32_t ndim;                 // collapsed iteration rank (>= 1)
+  int64_t shape[kEwMaxDims];    // collapsed iteration shape, row-major
+  int64_t numel;
+  int32_t n_inputs, n_outputs, n_consts;
+  // row mode
+  int32_t tail;                 // RowTail
+  int32_t tail_arg;
+  int32_t tail_reg;             // register holding the row values
+  int32_t tail_type;            // EwType of tail_reg
+  int32_t tail_out;             // output index of the tail result
+  int32_t tail_w, tail_b;       // operand indices (layer norm weight/bias, CE target)
+  int32_t tail_out_dtype;
+  float tail_eps;
+  int64_t rows, cols;           // row mode: numel = rows * cols
+  int64_t tail_aux;             // CE: ignore_index
+  EwInstr instr[kEwMaxInstr];
+  EwOperand inputs[kEwMaxInputs];
+  EwOutput outputs[kEwMaxOutputs];
+  int64_t consts[kEwMaxConsts];  // raw 64-bit patterns
+};
+
+// Kernel launchers (defined in the .cu files).  All return cudaError_t of the launch.
+cudaError_t launch_elementwise(const EwProgram& p, cudaStream_t s, int sm_count);
+cudaError_t launch_rowwise(const EwProgram& p, cudaStream_t s, int sm_count, int* status_flag);
+// Row-mode capacity: how many 1024-element chunks per row the shared-memory register file holds.
+int rowwise_max_chunks(int n_regs, int wide);
+
+struct StridedView {
+  const void* ptr;
+  int32_t dtype;
+  int32_t rank;
+  int64_t shape[kMaxRank];
+  int64_t stride[kMaxRank];   // elements
+};
+
+// out[...] = in[view] : dense copy of a strided view (permute / broadcast materialisation).
+cudaError_t launch_strided_copy(const StridedView& in, void* out, int64_t numel, cudaStream_t s);
+// Generic [outer, R, inner] reductions / softmax on dense data (any inner), fp32/fp64/int64.
+cudaError_t launch_reduce_generic(const void* in, void* out, int in_dtype, int out_dtype, int red_op,
+                                  int64_t outer, int64_t R, int64_t inner, cudaStream_t s);
+cudaError_t launch_softmax_generic(const void* in, void* out, int dtype, int64_t outer, int64_t R,
+                                   int64_t inner, cudaStream_t s);
+// gather along `dim` (torch.gather semantics); out-of-range indices set *status = BG_ERR_INDEX_RANGE.
+cudaError_t launch_gather(const void* x, const int64_t* idx, void* out, int esize, int rank,
+                          const int64_t* x_shape, const int64_t* idx_shape, int dim, int* status,
+                          cudaStream_t s);
+// Cross entropy epilogue: per-position losses (fp32/fp64) -> none/mean/sum over valid targets.
+cudaError_t launch_ce_reduce(const void* per_pos, const int64_t* targets, void* out, int dtype,
+                             int64_t n, int reduction, int64_t ignore_index, cudaStream_t s);
+// Cross entropy per-position term for logits [outer, C, inner] (class axis strided by inner).
+cudaError_t launch_ce_rows(const void* logits, const int64_t* targets, void* per_pos, int dtype,
+                           int64_t outer, int64_t C, int64_t inner, int64_t ignore_index, int* status,
+                           cudaStream_t s);
+
+struct GemmOperand {
+  const void* ptr;
+  int32_t dtype;
+  int64_t row_stride, col_stride;   // elements
+  int64_t batch_stride[4];          // per broadcast batch dim (0 where broadcast)
+};
+struct GemmProblem {
+  int64_t m, n, k;
+  int32_t n_batch_dims;
+  int64_t batch_shape[4];
+  GemmOperand a, b;
+  void* c;            // dense [batch..., m, n]
+  int32_t c_dtype;
+};
+// Reference-order SIMT GEMM for every dtype (fp32 FMA, fp64 FMA, exact int64).
+cudaError_t launch_gemm_simt(const GemmProblem& p, cudaStream_t s);
+
+}  // namespace bg

@@ -1,0 +1,950 @@
+// Generic fused elementwise / row-reduction kernel for sm_100a.
+//
+// A fusion group arrives as an EwProgram: a short register program (LOAD, arithmetic, CMP,
+// WHERE, CVT, STORE ...) passed as a __grid_constant__ parameter, so every thread fetches the
+// same instruction from the constant bank and the opcode switch is warp-uniform.  The virtual
+// registers live in shared memory, one 16-byte slot per thread per plane
+// (plane = register x chunk [x half for 64-bit classes]); consecutive threads own consecutive
+// slots, so every LDS.128/STS.128 is conflict free and dynamic register numbers cost nothing.
+// Each thread handles 4 consecutive elements per chunk: contiguous operands move with one
+// 128-bit coalesced load/store per thread (512 B per warp), strided/broadcast operands fall
+// back to per-lane addressing.
+//
+// Two kernels share the interpreter:
+//   ew_kernel   - flat iteration space, grid-stride over tiles of U chunks;
+//   row_kernel  - one CTA per row of [rows, cols]; after the program has produced the row in a
+//                 register, a tail (reduce / softmax / layer norm) finishes it on chip with
+//                 warp shuffles, so the row is read from HBM once and written once.
+#include "common.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math_constants.h>
+
+namespace bg {
+
+constexpr int kBlock = 256;
+constexpr int kVec = 4;
+constexpr int kChunk = kBlock * kVec;  // 1024 elements
+
+// ------------------------------------------------------------------------------------
+// Register file access
+// ------------------------------------------------------------------------------------
+struct RegFile {
+  char* base;
+  int U;       // chunks per pass
+  int planes;  // 1 (4-byte classes only) or 2
+  __device__ __forceinline__ char* slot(int r, int u, int h) const {
+    return base + ((size_t)((r * U + u) * planes + h) * kBlock + threadIdx.x) * 16;
+  }
+};
+
+template <typename T> struct V4 { T v[4]; };
+
+template <typename T> __device__ __forceinline__ V4<T> rget(const RegFile& rf, int r, int u);
+template <typename T> __device__ __forceinline__ void rput(const RegFile& rf, int r, int u, const V4<T>& x);
+
+template <> __device__ __forceinline__ V4<float> rget<float>(const RegFile& rf, int r, int u) {
+  float4 t = *reinterpret_cast<const float4*>(rf.slot(r, u, 0));
+  return {{t.x, t.y, t.z, t.w}};
+}
+template <> __device__ __forceinline__ void rput<float>(const RegFile& rf, int r, int u, const V4<float>& x) {
+  *reinterpret_cast<float4*>(rf.slot(r, u, 0)) = make_float4(x.v[0], x.v[1], x.v[2], x.v[3]);
+}
+template <> __device__ __forceinline__ V4<uint32_t> rget<uint32_t>(const RegFile& rf, int r, int u) {
+  uint4 t = *reinterpret_cast<const uint4*>(rf.slot(r, u, 0));
+  return {{t.x, t.y, t.z, t.w}};
+}
+template <> __device__ __forceinline__ void rput<uint32_t>(const RegFile& rf, int r, int u, const V4<uint32_t>& x) {
+  *reinterpret_cast<uint4*>(rf.slot(r, u, 0)) = make_uint4(x.v[0], x.v[1], x.v[2], x.v[3]);
+}
+template <> __device__ __forceinline__ V4<double> rget<double>(const RegFile& rf, int r, int u) {
+  double2 a = *reinterpret_cast<const double2*>(rf.slot(r, u, 0));
+  double2 b = *reinterpret_cast<const double2*>(rf.slot(r, u, 1));
+  return {{a.x, a.y, b.x, b.y}};
+}
+template <> __device__ __forceinline__ void rput<double>(const RegFile& rf, int r, int u, const V4<double>& x) {
+  *reinterpret_cast<double2*>(rf.slot(r, u, 0)) = make_double2(x.v[0], x.v[1]);
+  *reinterpret_cast<double2*>(rf.slot(r, u, 1)) = make_double2(x.v[2], x.v[3]);
+}
+template <> __device__ __forceinline__ V4<long long> rget<long long>(const RegFile& rf, int r, int u) {
+  longlong2 a = *reinterpret_cast<const longlong2*>(rf.slot(r, u, 0));
+  longlong2 b = *reinterpret_cast<const longlong2*>(rf.slot(r, u, 1));
+  return {{a.x, a.y, b.x, b.y}};
+}
+template <> __device__ __forceinline__ void rput<long long>(const RegFile& rf, int r, int u, const V4<long long>& x) {
+  *reinterpret_cast<longlong2*>(rf.slot(r, u, 0)) = make_longlong2(x.v[0], x.v[1]);
+  *reinterpret_cast<longlong2*>(rf.slot(r, u, 1)) = make_longlong2(x.v[2], x.v[3]);
+}
+
+// ------------------------------------------------------------------------------------
+// Scalar element access with dtype conversion to the natural register class
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ float ld_f32class(const void* p, int dt, int64_t i) {
+  switch (dt) {
+    case BG_F32: return reinterpret_cast<const float*>(p)[i];
+    case BG_F16: return __half2float(reinterpret_cast<const __half*>(p)[i]);
+    default: return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  }
+}
+__device__ __forceinline__ long long ld_i64class(const void* p, int dt, int64_t i) {
+  switch (dt) {
+    case BG_I64: case BG_U64: return reinterpret_cast<const long long*>(p)[i];
+    case BG_I32: return reinterpret_cast<const int*>(p)[i];
+    case BG_U32: return reinterpret_cast<const unsigned*>(p)[i];
+    case BG_I16: return reinterpret_cast<const short*>(p)[i];
+    case BG_U16: return reinterpret_cast<const unsigned short*>(p)[i];
+    case BG_I8: return reinterpret_cast<const signed char*>(p)[i];
+    default: return reinterpret_cast<const unsigned char*>(p)[i];
+  }
+}
+__device__ __forceinline__ void st_f32class(void* p, int dt, int64_t i, float x) {
+  switch (dt) {
+    case BG_F32: reinterpret_cast<float*>(p)[i] = x; break;
+    case BG_F16: reinterpret_cast<__half*>(p)[i] = __float2half_rn(x); break;
+    default: reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(x); break;
+  }
+}
+__device__ __forceinline__ void st_i64class(void* p, int dt, int64_t i, long long x) {
+  switch (dt) {
+    case BG_I64: case BG_U64: reinterpret_cast<long long*>(p)[i] = x; break;
+    case BG_I32: case BG_U32: reinterpret_cast<int*>(p)[i] = (int)x; break;
+    case BG_I16: case BG_U16: reinterpret_cast<short*>(p)[i] = (short)x; break;
+    default: reinterpret_cast<signed char*>(p)[i] = (signed char)x; break;
+  }
+}
+
+__device__ __forceinline__ float narrow_f32(float x, int dt) {
+  if (dt == BG_F16) return __half2float(__float2half_rn(x));
+  if (dt == BG_BF16) return __bfloat162float(__float2bfloat16_rn(x));
+  return x;
+}
+__device__ __forceinline__ long long narrow_i64(long long x, int dt) {
+  switch (dt) {
+    case BG_I32: return (int)x;
+    case BG_U32: return (unsigned)x;
+    case BG_I16: return (short)x;
+    case BG_U16: return (unsigned short)x;
+    case BG_I8: return (signed char)x;
+    case BG_U8: return (unsigned char)x;
+    case BG_BOOL: return x != 0;
+    default: return x;
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// Per-chunk iteration state
+// ------------------------------------------------------------------------------------
+struct ChunkPos {
+  int64_t idx;   // linear index of lane 0 in the iteration space
+  int nvalid;    // 0..4 lanes inside the tensor (row mode: inside the row)
+};
+
+// Offsets of the 4 lanes of a strided operand.
+__device__ __forceinline__ void strided_offsets(const EwProgram& p, const EwOperand& o, int64_t idx, int nvalid,
+                                                int64_t off[4]) {
+  const int nd = p.ndim;
+  const int64_t last = p.shape[nd - 1];
+  if ((last & 3) == 0) {
+    int64_t rem = idx, base = 0;
+#pragma unroll 1
+    for (int d = nd - 1; d >= 0; --d) {
+      int64_t s = p.shape[d];
+      int64_t q = rem / s;
+      base += (rem - q * s) * o.stride[d];
+      rem = q;
+    }
+    const int64_t si = o.stride[nd - 1];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) off[e] = base + e * si;
+  } else {
+#pragma unroll 1
+    for (int e = 0; e < 4; ++e) {
+      int64_t rem = idx + (e < nvalid ? e : 0), base = 0;
+#pragma unroll 1
+      for (int d = nd - 1; d >= 0; --d) {
+        int64_t s = p.shape[d];
+        int64_t q = rem / s;
+        base += (rem - q * s) * o.stride[d];
+        rem = q;
+      }
+      off[e] = base;
+    }
+  }
+}
+
+__device__ __forceinline__ void do_load(const EwProgram& p, const EwInstr& ins, const RegFile& rf, int u,
+                                        const ChunkPos& cp) {
+  const EwOperand& o = p.inputs[ins.aux];
+  int64_t off[4];
+  bool vec = false;
+  if (o.mode == A_CONTIG) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) off[e] = cp.idx + (e < cp.nvalid ? e : 0);
+    vec = o.vec_ok && cp.nvalid == 4;
+  } else if (o.mode == A_SCALAR) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) off[e] = 0;
+  } else {
+    strided_offsets(p, o, cp.idx, cp.nvalid, off);
+    vec = o.vec_ok && cp.nvalid == 4 && o.stride[p.ndim - 1] == 1 && (p.shape[p.ndim - 1] & 3) == 0;
+  }
+  const int dt = o.dtype;
+  if (dt == BG_F32 || dt == BG_F16 || dt == BG_BF16) {
+    V4<float> r;
+    if (vec && dt == BG_F32) {
+      float4 t = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(o.ptr) + off[0]));
+      r = {{t.x, t.y, t.z, t.w}};
+    } else if (vec && dt == BG_F16) {
+      uint2 t = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(o.ptr) + off[0]));
+      __half2 h0 = *reinterpret_cast<__half2*>(&t.x), h1 = *reinterpret_cast<__half2*>(&t.y);
+      float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+      r = {{f0.x, f0.y, f1.x, f1.y}};
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = ld_f32class(o.ptr, dt, off[e]);
+    }
+    rput<float>(rf, ins.dst, u, r);
+  } else if (dt == BG_F64) {
+    V4<double> r;
+    const double* q = reinterpret_cast<const double*>(o.ptr);
+    if (vec) {
+      double2 a = __ldg(reinterpret_cast<const double2*>(q + off[0]));
+      double2 b = __ldg(reinterpret_cast<const double2*>(q + off[0] + 2));
+      r = {{a.x, a.y, b.x, b.y}};
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = q[off[e]];
+    }
+    rput<double>(rf, ins.dst, u, r);
+  } else if (dt == BG_BOOL) {
+    V4<uint32_t> r;
+    const unsigned char* q = reinterpret_cast<const unsigned char*>(o.ptr);
+    if (vec) {
+      uint32_t t = __ldg(reinterpret_cast<const uint32_t*>(q + off[0]));
+      r = {{(t & 0xffu) != 0, ((t >> 8) & 0xffu) != 0, ((t >> 16) & 0xffu) != 0, (t >> 24) != 0}};
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = q[off[e]] != 0;
+    }
+    rput<uint32_t>(rf, ins.dst, u, r);
+  } else {
+    V4<long long> r;
+    if (vec && (dt == BG_I64 || dt == BG_U64)) {
+      const long long* q = reinterpret_cast<const long long*>(o.ptr);
+      longlong2 a = __ldg(reinterpret_cast<const longlong2*>(q + off[0]));
+      longlong2 b = __ldg(reinterpret_cast<const longlong2*>(q + off[0] + 2));
+      r = {{a.x, a.y, b.x, b.y}};
+    } else if (vec && dt == BG_I32) {
+      int4 t = __ldg(reinterpret_cast<const int4*>(reinterpret_cast<const int*>(o.ptr) + off[0]));
+      r = {{t.x, t.y, t.z, t.w}};
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = ld_i64class(o.ptr, dt, off[e]);
+    }
+    rput<long long>(rf, ins.dst, u, r);
+  }
+}
+
+__device__ __forceinline__ void do_store(const EwProgram& p, const EwInstr& ins, const RegFile& rf, int u,
+                                         const ChunkPos& cp) {
+  if (cp.nvalid <= 0) return;
+  const EwOutput& o = p.outputs[ins.aux];
+  const int dt = o.dtype;
+  const bool vec = o.vec_ok && cp.nvalid == 4;
+  const int64_t i0 = cp.idx;
+  if (ins.type == T_F32) {
+    V4<float> r = rget<float>(rf, ins.a, u);
+    if (vec && dt == BG_F32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(o.ptr) + i0) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+    } else if (vec && dt == BG_F16) {
+      __half2 h0 = __floats2half2_rn(r.v[0], r.v[1]), h1 = __floats2half2_rn(r.v[2], r.v[3]);
+      uint2 t;
+      t.x = *reinterpret_cast<uint32_t*>(&h0);
+      t.y = *reinterpret_cast<uint32_t*>(&h1);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(o.ptr) + i0) = t;
+    } else if (vec && dt == BG_BF16) {
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(r.v[0], r.v[1]), h1 = __floats2bfloat162_rn(r.v[2], r.v[3]);
+      uint2 t;
+      t.x = *reinterpret_cast<uint32_t*>(&h0);
+      t.y = *reinterpret_cast<uint32_t*>(&h1);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(o.ptr) + i0) = t;
+    } else {
+      for (int e = 0; e < cp.nvalid; ++e) st_f32class(o.ptr, dt, i0 + e, r.v[e]);
+    }
+  } else if (ins.type == T_F64) {
+    V4<double> r = rget<double>(rf, ins.a, u);
+    double* q = reinterpret_cast<double*>(o.ptr);
+    if (vec) {
+      *reinterpret_cast<double2*>(q + i0) = make_double2(r.v[0], r.v[1]);
+      *reinterpret_cast<double2*>(q + i0 + 2) = make_double2(r.v[2], r.v[3]);
+    } else {
+      for (int e = 0; e < cp.nvalid; ++e) q[i0 + e] = r.v[e];
+    }
+  } else if (ins.type == T_B) {
+    V4<uint32_t> r = rget<uint32_t>(rf, ins.a, u);
+    unsigned char* q = reinterpret_cast<unsigned char*>(o.ptr);
+    if (vec) {
+      *reinterpret_cast<uint32_t*>(q + i0) = (r.v[0] & 1u) | ((r.v[1] & 1u) << 8) | ((r.v[2] & 1u) << 16) | ((r.v[3] & 1u) << 24);
+    } else {
+      for (int e = 0; e < cp.nvalid; ++e) q[i0 + e] = (unsigned char)(r.v[e] != 0);
+    }
+  } else {
+    V4<long long> r = rget<long long>(rf, ins.a, u);
+    if (vec && (dt == BG_I64 || dt == BG_U64)) {
+      long long* q = reinterpret_cast<long long*>(o.ptr);
+      *reinterpret_cast<longlong2*>(q + i0) = make_longlong2(r.v[0], r.v[1]);
+      *reinterpret_cast<longlong2*>(q + i0 + 2) = make_longlong2(r.v[2], r.v[3]);
+    } else if (vec && (dt == BG_I32 || dt == BG_U32)) {
+      *reinterpret_cast<int4*>(reinterpret_cast<int*>(o.ptr) + i0) = make_int4((int)r.v[0], (int)r.v[1], (int)r.v[2], (int)r.v[3]);
+    } else {
+      for (int e = 0; e < cp.nvalid; ++e) st_i64class(o.ptr, dt, i0 + e, r.v[e]);
+    }
+  }
+}
+
+template <typename T> __device__ __forceinline__ bool cmp_op(T a, T b, int op) {
+  switch (op) {
+    case BG_CMP_EQ: return a == b;
+    case BG_CMP_NE: return a != b;
+    case BG_CMP_LT: return a < b;
+    case BG_CMP_LE: return a <= b;
+    case BG_CMP_GT: return a > b;
+    default: return a >= b;
+  }
+}
+
+template <typename T> __device__ __forceinline__ T f_exp(T x);
+template <> __device__ __forceinline__ float f_exp<float>(float x) { return expf(x); }
+template <> __device__ __forceinline__ double f_exp<double>(double x) { return exp(x); }
+template <typename T> __device__ __forceinline__ T f_log(T x);
+template <> __device__ __forceinline__ float f_log<float>(float x) { return logf(x); }
+template <> __device__ __forceinline__ double f_log<double>(double x) { return log(x); }
+template <typename T> __device__ __forceinline__ T f_sin(T x);
+template <> __device__ __forceinline__ float f_sin<float>(float x) { return sinf(x); }
+template <> __device__ __forceinline__ double f_sin<double>(double x) { return sin(x); }
+template <typename T> __device__ __forceinline__ T f_cos(T x);
+template <> __device__ __forceinline__ float f_cos<float>(float x) { return cosf(x); }
+template <> __device__ __forceinline__ double f_cos<double>(double x) { return cos(x); }
+
+// Arithmetic on floating classes.  Explicit __f*_rn / __d*_rn keep the compiler from contracting
+// a MUL followed by an ADD into an FMA: NumPy rounds after each ufunc.
+__device__ __forceinline__ float fadd(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float fmul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float fdiv(float a, float b) { return __fdiv_rn(a, b); }
+__device__ __forceinline__ double fadd(double a, double b) { return __dadd_rn(a, b); }
+__device__ __forceinline__ double fmul(double a, double b) { return __dmul_rn(a, b); }
+__device__ __forceinline__ double fdiv(double a, double b) { return __ddiv_rn(a, b); }
+
+template <typename T>
+__device__ __forceinline__ void float_instr(const EwInstr& ins, const RegFile& rf, int u) {
+  V4<T> a = rget<T>(rf, ins.a, u), r;
+  switch (ins.op) {
+    case E_ADD: { V4<T> b = rget<T>(rf, ins.b, u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = fadd(a.v[e], b.v[e]); break; }
+    case E_MUL: { V4<T> b = rget<T>(rf, ins.b, u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = fmul(a.v[e], b.v[e]); break; }
+    case E_DIV: { V4<T> b = rget<T>(rf, ins.b, u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = fdiv(a.v[e], b.v[e]); break; }
+    case E_NEG:
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = -a.v[e];
+      break;
+    case E_EXP:
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = f_exp<T>(a.v[e]);
+      break;
+    case E_LOG:
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = f_log<T>(a.v[e]);
+      break;
+    case E_ABS:
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = a.v[e] < 0 ? -a.v[e] : (a.v[e] == 0 ? T(0) : a.v[e]);
+      break;
+    case E_SIGN:
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = a.v[e] != a.v[e] ? a.v[e] : T((a.v[e] > 0) - (a.v[e] < 0));
+      break;
+    case E_SIN:
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = f_sin<T>(a.v[e]);
+      break;
+    default:  // E_COS
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = f_cos<T>(a.v[e]);
+      break;
+  }
+  rput<T>(rf, ins.dst, u, r);
+}
+
+__device__ __forceinline__ void int_instr(const EwInstr& ins, const RegFile& rf, int u) {
+  V4<long long> a = rget<long long>(rf, ins.a, u), r;
+  switch (ins.op) {
+    case E_ADD: { V4<long long> b = rget<long long>(rf, ins.b, u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = (long long)((unsigned long long)a.v[e] + (unsigned long long)b.v[e]); break; }
+    case E_MUL: { V4<long long> b = rget<long long>(rf, ins.b, u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = (long long)((unsigned long long)a.v[e] * (unsigned long long)b.v[e]); break; }
+    case E_DIV: { V4<long long> b = rget<long long>(rf, ins.b, u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = (long long)((double)a.v[e] / (double)b.v[e]); break; }
+    case E_NEG:
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = (long long)(0ull - (unsigned long long)a.v[e]);
+      break;
+    case E_ABS:
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = a.v[e] < 0 ? (long long)(0ull - (unsigned long long)a.v[e]) : a.v[e];
+      break;
+    default:  // E_SIGN
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = (a.v[e] > 0) - (a.v[e] < 0);
+      break;
+  }
+  rput<long long>(rf, ins.dst, u, r);
+}
+
+template <typename T> __device__ __forceinline__ void where_instr(const EwInstr& ins, const RegFile& rf, int u) {
+  V4<uint32_t> c = rget<uint32_t>(rf, ins.a, u);
+  V4<T> x = rget<T>(rf, ins.b, u), y = rget<T>(rf, ins.c, u), r;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) r.v[e] = c.v[e] ? x.v[e] : y.v[e];
+  rput<T>(rf, ins.dst, u, r);
+}
+
+template <typename T> __device__ __forceinline__ void cmp_instr(const EwInstr& ins, const RegFile& rf, int u) {
+  V4<T> a = rget<T>(rf, ins.a, u), b = rget<T>(rf, ins.b, u);
+  V4<uint32_t> r;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) r.v[e] = cmp_op<T>(a.v[e], b.v[e], ins.aux);
+  rput<uint32_t>(rf, ins.dst, u, r);
+}
+
+template <typename S, typename D> __device__ __forceinline__ D cvt1(S x) { return (D)x; }
+template <> __device__ __forceinline__ uint32_t cvt1<float, uint32_t>(float x) { return x != 0.0f; }
+template <> __device__ __forceinline__ uint32_t cvt1<double, uint32_t>(double x) { return x != 0.0; }
+template <> __device__ __forceinline__ uint32_t cvt1<long long, uint32_t>(long long x) { return x != 0; }
+template <> __device__ __forceinline__ float cvt1<double, float>(double x) { return __double2float_rn(x); }
+template <> __device__ __forceinline__ float cvt1<long long, float>(long long x) { return __ll2float_rn(x); }
+template <> __device__ __forceinline__ double cvt1<long long, double>(long long x) { return __ll2double_rn(x); }
+template <> __device__ __forceinline__ long long cvt1<float, long long>(float x) { return __float2ll_rz(x); }
+template <> __device__ __forceinline__ long long cvt1<double, long long>(double x) { return __double2ll_rz(x); }
+
+template <typename S, typename D> __device__ __forceinline__ void cvt_instr(const EwInstr& ins, const RegFile& rf, int u) {
+  V4<S> a = rget<S>(rf, ins.a, u);
+  V4<D> r;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) r.v[e] = cvt1<S, D>(a.v[e]);
+  rput<D>(rf, ins.dst, u, r);
+}
+
+template <typename S> __device__ __forceinline__ void cvt_from(const EwInstr& ins, const RegFile& rf, int u) {
+  switch (ins.type) {
+    case T_F32: cvt_instr<S, float>(ins, rf, u); break;
+    case T_F64: cvt_instr<S, double>(ins, rf, u); break;
+    case T_I64: cvt_instr<S, long long>(ins, rf, u); break;
+    default: cvt_instr<S, uint32_t>(ins, rf, u); break;
+  }
+}
+
+__device__ __forceinline__ void exec_instr(const EwProgram& p, const EwInstr& ins, const RegFile& rf, int u,
+                                           const ChunkPos& cp) {
+  switch (ins.op) {
+    case E_LOAD: do_load(p, ins, rf, u, cp); break;
+    case E_STORE: do_store(p, ins, rf, u, cp); break;
+    case E_CONST: {
+      const int64_t bits = p.consts[ins.aux];
+      if (ins.type == T_F32) {
+        float f = (float)__longlong_as_double(bits);
+        rput<float>(rf, ins.dst, u, {{f, f, f, f}});
+      } else if (ins.type == T_F64) {
+        double d = __longlong_as_double(bits);
+        rput<double>(rf, ins.dst, u, {{d, d, d, d}});
+      } else if (ins.type == T_I64) {
+        rput<long long>(rf, ins.dst, u, {{bits, bits, bits, bits}});
+      } else {
+        uint32_t b = bits != 0;
+        rput<uint32_t>(rf, ins.dst, u, {{b, b, b, b}});
+      }
+      break;
+    }
+    case E_CMP:
+      if (ins.type == T_F32) cmp_instr<float>(ins, rf, u);
+      else if (ins.type == T_F64) cmp_instr<double>(ins, rf, u);
+      else if (ins.type == T_I64) cmp_instr<long long>(ins, rf, u);
+      else cmp_instr<uint32_t>(ins, rf, u);
+      break;
+    case E_WHERE:
+      if (ins.type == T_F32) where_instr<float>(ins, rf, u);
+      else if (ins.type == T_F64) where_instr<double>(ins, rf, u);
+      else if (ins.type == T_I64) where_instr<long long>(ins, rf, u);
+      else where_instr<uint32_t>(ins, rf, u);
+      break;
+    case E_ISNAN: {
+      V4<uint32_t> r;
+      if (ins.type == T_F32) { V4<float> a = rget<float>(rf, ins.a, u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) r.v[e] = a.v[e] != a.v[e];
+      } else if (ins.type == T_F64) { V4<double> a = rget<double>(rf, ins.a, u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) r.v[e] = a.v[e] != a.v[e];
+      } else { r = {{0, 0, 0, 0}}; }
+      rput<uint32_t>(rf, ins.dst, u, r);
+      break;
+    }
+    case E_CVT:
+      switch (ins.aux & 0xF) {
+        case T_F32: cvt_from<float>(ins, rf, u); break;
+        case T_F64: cvt_from<double>(ins, rf, u); break;
+        case T_I64: cvt_from<long long>(ins, rf, u); break;
+        default: cvt_from<uint32_t>(ins, rf, u); break;
+      }
+      break;
+    case E_NARROW:
+      if (ins.type == T_F32) {
+        V4<float> a = rget<float>(rf, ins.a, u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) a.v[e] = narrow_f32(a.v[e], ins.aux);
+        rput<float>(rf, ins.dst, u, a);
+      } else if (ins.type == T_I64) {
+        V4<long long> a = rget<long long>(rf, ins.a, u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) a.v[e] = narrow_i64(a.v[e], ins.aux);
+        rput<long long>(rf, ins.dst, u, a);
+      }
+      break;
+    case E_AND: case E_OR: {
+      V4<uint32_t> a = rget<uint32_t>(rf, ins.a, u), b = rget<uint32_t>(rf, ins.b, u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) a.v[e] = ins.op == E_AND ? (a.v[e] & b.v[e]) : (a.v[e] | b.v[e]);
+      rput<uint32_t>(rf, ins.dst, u, a);
+      break;
+    }
+    default:
+      if (ins.type == T_F32) float_instr<float>(ins, rf, u);
+      else if (ins.type == T_F64) float_instr<double>(ins, rf, u);
+      else int_instr(ins, rf, u);
+      break;
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// Flat elementwise kernel
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kBlock) ew_kernel(const __grid_constant__ EwProgram p, int U, int64_t n_tiles) {
+  extern __shared__ __align__(16) char smem[];
+  RegFile rf{smem, U, p.wide ? 2 : 1};
+  const int64_t tile_elems = (int64_t)U * kChunk;
+  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const int64_t t0 = tile * tile_elems + (int64_t)threadIdx.x * kVec;
+#pragma unroll 1
+    for (int i = 0; i < p.n_instr; ++i) {
+      const EwInstr ins = p.instr[i];
+#pragma unroll 1
+      for (int u = 0; u < U; ++u) {
+        ChunkPos cp;
+        cp.idx = t0 + (int64_t)u * kChunk;
+        int64_t left = p.numel - cp.idx;
+        cp.nvalid = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+        if (cp.nvalid == 0 && (ins.op == E_LOAD || ins.op == E_STORE)) continue;
+        exec_instr(p, ins, rf, u, cp);
+      }
+    }
+  }
+}
+
+cudaError_t launch_elementwise(const EwProgram& p, cudaStream_t s, int sm_count) {
+  if (p.numel == 0) return cudaSuccess;
+  const int planes = p.wide ? 2 : 1;
+  const size_t per_chunk = (size_t)p.n_regs * planes * kBlock * 16;
+  int U = 2;
+  if (per_chunk * U > 48 * 1024) U = 1;
+  if (p.numel <= (int64_t)kChunk * sm_count) U = 1;
+  const size_t smem = per_chunk * U;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(ew_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
+    if (e != cudaSuccess) return e;
+  }
+  if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
+  const int64_t tile_elems = (int64_t)U * kChunk;
+  const int64_t n_tiles = (p.numel + tile_elems - 1) / tile_elems;
+  int ctas_per_sm = (int)(200 * 1024 / (smem ? smem : 1));
+  if (ctas_per_sm > 8) ctas_per_sm = 8;
+  if (ctas_per_sm < 1) ctas_per_sm = 1;
+  int64_t grid = (int64_t)sm_count * ctas_per_sm;
+  if (grid > n_tiles) grid = n_tiles;
+  ew_kernel<<<(unsigned)grid, kBlock, smem, s>>>(p, U, n_tiles);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------
+// Row kernel: program + on-chip tail over the last axis
+// ------------------------------------------------------------------------------------
+struct BlockRed {
+  // 8 warps x 16 bytes of scratch placed after the register file
+  char* scratch;
+};
+
+template <typename T, typename F>
+__device__ __forceinline__ T block_reduce(T v, F f, T ident, char* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    T other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = f(v, other);
+  }
+  T* s = reinterpret_cast<T*>(scratch);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) s[w] = v;
+  __syncthreads();
+  T r = l < (kBlock / 32) ? s[l] : ident;
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) {
+    T other = __shfl_xor_sync(0xffffffffu, r, o);
+    r = f(r, other);
+  }
+  r = __shfl_sync(0xffffffffu, r, 0);
+  return r;
+}
+
+template <typename T> __device__ __forceinline__ T lowest();
+template <> __device__ __forceinline__ float lowest<float>() { return -CUDART_INF_F; }
+template <> __device__ __forceinline__ double lowest<double>() { return -CUDART_INF; }
+template <> __device__ __forceinline__ long long lowest<long long>() { return (long long)0x8000000000000000ull; }
+template <typename T> __device__ __forceinline__ T highest();
+template <> __device__ __forceinline__ float highest<float>() { return CUDART_INF_F; }
+template <> __device__ __forceinline__ double highest<double>() { return CUDART_INF; }
+template <> __device__ __forceinline__ long long highest<long long>() { return 0x7fffffffffffffffll; }
+
+template <typename T>
+__device__ __forceinline__ bool arg_better(T v, long long i, T bv, long long bi, bool want_max) {
+  // First occurrence wins; a NaN beats every number (NumPy argmax/argmin propagate the first NaN).
+  const bool vn = v != v, bn = bv != bv;
+  if (bi < 0) return true;
+  if (vn || bn) {
+    if (vn && bn) return i < bi;
+    return vn;
+  }
+  if (v == bv) return i < bi;
+  return want_max ? v > bv : v < bv;
+}
+
+template <typename T>
+__device__ __forceinline__ void block_argreduce(T& v, long long& i, bool want_max, char* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    T ov = __shfl_xor_sync(0xffffffffu, v, o);
+    long long oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (oi >= 0 && arg_better<T>(ov, oi, v, i, want_max)) { v = ov; i = oi; }
+  }
+  T* sv = reinterpret_cast<T*>(scratch);
+  long long* si = reinterpret_cast<long long*>(scratch + 64);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) { sv[w] = v; si[w] = i; }
+  __syncthreads();
+  if (l < kBlock / 32) { v = sv[l]; i = si[l]; } else { i = -1; }
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) {
+    T ov = __shfl_xor_sync(0xffffffffu, v, o);
+    long long oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (oi >= 0 && arg_better<T>(ov, oi, v, i, want_max)) { v = ov; i = oi; }
+  }
+  v = __shfl_sync(0xffffffffu, v, 0);
+  i = __shfl_sync(0xffffffffu, i, 0);
+}
+
+__device__ __forceinline__ void store_scalar(void* ptr, int dt, int64_t i, double fv, long long iv, bool is_int) {
+  switch (dt) {
+    case BG_F32: reinterpret_cast<float*>(ptr)[i] = is_int ? (float)iv : (float)fv; break;
+    case BG_F64: reinterpret_cast<double*>(ptr)[i] = is_int ? (double)iv : fv; break;
+    case BG_F16: reinterpret_cast<__half*>(ptr)[i] = __float2half_rn(is_int ? (float)iv : (float)fv); break;
+    case BG_BF16: reinterpret_cast<__nv_bfloat16*>(ptr)[i] = __float2bfloat16_rn(is_int ? (float)iv : (float)fv); break;
+    case BG_BOOL: reinterpret_cast<unsigned char*>(ptr)[i] = is_int ? (iv != 0) : (fv != 0.0); break;
+    default: st_i64class(ptr, dt, i, is_int ? iv : (long long)fv); break;
+  }
+}
+
+// Reduction over one row with values of class T arriving chunk by chunk.
+template <typename T>
+__device__ __forceinline__ void row_reduce(const EwProgram& p, const RegFile& rf, int64_t row, int U, int64_t n_chunks,
+                                           char* scratch) {
+  const int op = p.tail_arg;
+  const bool is_arg = op == BG_RED_ARGMAX || op == BG_RED_ARGMIN;
+  T acc = T(0);
+  long long best_i = -1;
+  if (op == BG_RED_MAX) acc = lowest<T>();
+  if (op == BG_RED_MIN) acc = highest<T>();
+  bool any_nan = false;
+  for (int64_t c0 = 0; c0 < n_chunks; c0 += U) {
+#pragma unroll 1
+    for (int i = 0; i < p.n_instr; ++i) {
+      const EwInstr ins = p.instr[i];
+#pragma unroll 1
+      for (int u = 0; u < U; ++u) {
+        ChunkPos cp;
+        const int64_t col = (c0 + u) * kChunk + (int64_t)threadIdx.x * kVec;
+        cp.idx = row * p.cols + col;
+        int64_t left = p.cols - col;
+        cp.nvalid = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+        if (cp.nvalid == 0 && (ins.op == E_LOAD || ins.op == E_STORE)) continue;
+        exec_instr(p, ins, rf, u, cp);
+      }
+    }
+#pragma unroll 1
+    for (int u = 0; u < U; ++u) {
+      const int64_t col = (c0 + u) * kChunk + (int64_t)threadIdx.x * kVec;
+      int64_t left = p.cols - col;
+      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+      if (nv == 0) continue;
+      V4<T> x = rget<T>(rf, p.tail_reg, u);
+      for (int e = 0; e < nv; ++e) {
+        const T v = x.v[e];
+        if (is_arg) {
+          if (arg_better<T>(v, col + e, acc, best_i, op == BG_RED_ARGMAX)) { acc = v; best_i = col + e; }
+        } else if (op == BG_RED_SUM || op == BG_RED_MEAN) {
+          acc += v;
+        } else {
+          if (v != v) any_nan = true;
+          if (op == BG_RED_MAX) acc = v > acc ? v : acc;
+          else acc = v < acc ? v : acc;
+        }
+      }
+    }
+  }
+  constexpr bool kIsInt = sizeof(T) == 8 && (T(1) / T(2) == T(0));
+  if (is_arg) {
+    block_argreduce<T>(acc, best_i, op == BG_RED_ARGMAX, scratch);
+    if (threadIdx.x == 0) store_scalar(p.outputs[p.tail_out].ptr, p.tail_out_dtype, row, 0.0, best_i, true);
+    return;
+  }
+  if (op == BG_RED_SUM || op == BG_RED_MEAN) {
+    acc = block_reduce<T>(acc, [](T a, T b) { return a + b; }, T(0), scratch);
+    if (threadIdx.x == 0) {
+      if (op == BG_RED_MEAN) {
+        if (kIsInt) store_scalar(p.outputs[p.tail_out].ptr, p.tail_out_dtype, row, (double)acc / (double)p.cols, 0, false);
+        else store_scalar(p.outputs[p.tail_out].ptr, p.tail_out_dtype, row, (double)(acc / (T)p.cols), 0, false);
+      } else {
+        store_scalar(p.outputs[p.tail_out].ptr, p.tail_out_dtype, row, (double)acc, (long long)acc, kIsInt);
+      }
+    }
+    return;
+  }
+  const bool want_max = op == BG_RED_MAX;
+  acc = block_reduce<T>(acc, [want_max](T a, T b) { return want_max ? (a > b ? a : b) : (a < b ? a : b); }, acc, scratch);
+  int nan_any = __syncthreads_or(any_nan ? 1 : 0);
+  if (threadIdx.x == 0) {
+    double fv = (double)acc;
+    if (nan_any && !kIsInt) fv = CUDART_NAN;
+    store_scalar(p.outputs[p.tail_out].ptr, p.tail_out_dtype, row, fv, (long long)acc, kIsInt);
+  }
+}
+
+__device__ __forceinline__ void row_reduce_bool(const EwProgram& p, const RegFile& rf, int64_t row, int U,
+                                                int64_t n_chunks) {
+  // any / all over a T_B register (also sum/max of bools is not generated by the compiler)
+  const bool is_any = p.tail_arg == BG_RED_ANY;
+  int local = is_any ? 0 : 1;
+  for (int64_t c0 = 0; c0 < n_chunks; c0 += U) {
+#pragma unroll 1
+    for (int i = 0; i < p.n_instr; ++i) {
+      const EwInstr ins = p.instr[i];
+#pragma unroll 1
+      for (int u = 0; u < U; ++u) {
+        ChunkPos cp;
+        const int64_t col = (c0 + u) * kChunk + (int64_t)threadIdx.x * kVec;
+        cp.idx = row * p.cols + col;
+        int64_t left = p.cols - col;
+        cp.nvalid = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+        if (cp.nvalid == 0 && (ins.op == E_LOAD || ins.op == E_STORE)) continue;
+        exec_instr(p, ins, rf, u, cp);
+      }
+    }
+#pragma unroll 1
+    for (int u = 0; u < U; ++u) {
+      const int64_t col = (c0 + u) * kChunk + (int64_t)threadIdx.x * kVec;
+      int64_t left = p.cols - col;
+      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+      V4<uint32_t> x = rget<uint32_t>(rf, p.tail_reg, u);
+      for (int e = 0; e < nv; ++e) {
+        if (is_any) local |= (x.v[e] != 0);
+        else local &= (x.v[e] != 0);
+      }
+    }
+  }
+  int r = is_any ? __syncthreads_or(local) : __syncthreads_and(local);
+  if (threadIdx.x == 0) store_scalar(p.outputs[p.tail_out].ptr, p.tail_out_dtype, row, 0.0, r != 0, true);
+}
+
+// softmax / layer norm: the whole row stays in the register file (n_chunks <= U).
+template <typename T>
+__device__ __forceinline__ void row_resident_tail(const EwProgram& p, const RegFile& rf, int64_t row, int U,
+                                                  char* scratch) {
+#pragma unroll 1
+  for (int i = 0; i < p.n_instr; ++i) {
+    const EwInstr ins = p.instr[i];
+#pragma unroll 1
+    for (int u = 0; u < U; ++u) {
+      ChunkPos cp;
+      const int64_t col = (int64_t)u * kChunk + (int64_t)threadIdx.x * kVec;
+      cp.idx = row * p.cols + col;
+      int64_t left = p.cols - col;
+      cp.nvalid = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+      if (cp.nvalid == 0 && (ins.op == E_LOAD || ins.op == E_STORE)) continue;
+      exec_instr(p, ins, rf, u, cp);
+    }
+  }
+  const int r = p.tail_reg;
+  const EwOutput& out = p.outputs[p.tail_out];
+  if (p.tail == TAIL_SOFTMAX) {
+    T m = lowest<T>();
+    bool nan = false;
+#pragma unroll 1
+    for (int u = 0; u < U; ++u) {
+      const int64_t col = (int64_t)u * kChunk + (int64_t)threadIdx.x * kVec;
+      int64_t left = p.cols - col;
+      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+      V4<T> x = rget<T>(rf, r, u);
+      for (int e = 0; e < nv; ++e) {
+        if (x.v[e] != x.v[e]) nan = true;
+        m = x.v[e] > m ? x.v[e] : m;
+      }
+    }
+    m = block_reduce<T>(m, [](T a, T b) { return a > b ? a : b; }, m, scratch);
+    if (__syncthreads_or(nan ? 1 : 0)) m = (T)CUDART_NAN;
+    T sum = T(0);
+#pragma unroll 1
+    for (int u = 0; u < U; ++u) {
+      const int64_t col = (int64_t)u * kChunk + (int64_t)threadIdx.x * kVec;
+      int64_t left = p.cols - col;
+      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+      if (nv == 0) continue;
+      V4<T> x = rget<T>(rf, r, u);
+      for (int e = 0; e < 4; ++e) {
+        x.v[e] = f_exp<T>(fadd(x.v[e], -m));
+        if (e < nv) sum += x.v[e];
+      }
+      rput<T>(rf, r, u, x);
+    }
+    sum = block_reduce<T>(sum, [](T a, T b) { return a + b; }, T(0), scratch);
+#pragma unroll 1
+    for (int u = 0; u < U; ++u) {
+      const int64_t col = (int64_t)u * kChunk + (int64_t)threadIdx.x * kVec;
+      int64_t left = p.cols - col;
+      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+      if (nv == 0) continue;
+      V4<T> x = rget<T>(rf, r, u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) x.v[e] = fdiv(x.v[e], sum);
+      rput<T>(rf, r, u, x);
+      EwInstr st{E_STORE, (uint8_t)p.tail_type, 0, (uint8_t)r, 0, 0, (uint16_t)p.tail_out};
+      ChunkPos cp{row * p.cols + col, nv};
+      do_store(p, st, rf, u, cp);
+    }
+    (void)out;
+  } else {  // TAIL_LAYERNORM, fp32 statistics as in the reference (x.astype(float32))
+    float sum = 0.f;
+#pragma unroll 1
+    for (int u = 0; u < U; ++u) {
+      const int64_t col = (int64_t)u * kChunk + (int64_t)threadIdx.x * kVec;
+      int64_t left = p.cols - col;
+      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+      V4<T> x = rget<T>(rf, r, u);
+      for (int e = 0; e < nv; ++e) sum += (float)x.v[e];
+    }
+    sum = block_reduce<float>(sum, [](float a, float b) { return a + b; }, 0.f, scratch);
+    const float mean = sum / (float)p.cols;
+    float sq = 0.f;
+#pragma unroll 1
+    for (int u = 0; u < U; ++u) {
+      const int64_t col = (int64_t)u * kChunk + (int64_t)threadIdx.x * kVec;
+      int64_t left = p.cols - col;
+      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+      V4<T> x = rget<T>(rf, r, u);
+      for (int e = 0; e < nv; ++e) {
+        float c = __fadd_rn((float)x.v[e], -mean);
+        sq += __fmul_rn(c, c);
+      }
+    }
+    sq = block_reduce<float>(sq, [](float a, float b) { return a + b; }, 0.f, scratch);
+    const float var = sq / (float)p.cols;
+    const float inv = 1.0f / sqrtf(var + p.tail_eps);
+    const EwOperand& w = p.inputs[p.tail_w];
+    const EwOperand& b = p.inputs[p.tail_b];
+#pragma unroll 1
+    for (int u = 0; u < U; ++u) {
+      const int64_t col = (int64_t)u * kChunk + (int64_t)threadIdx.x * kVec;
+      int64_t left = p.cols - col;
+      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+      if (nv == 0) continue;
+      V4<T> x = rget<T>(rf, r, u);
+      for (int e = 0; e < nv; ++e) {
+        float c = __fadd_rn((float)x.v[e], -mean);
+        float xh = __fmul_rn(c, inv);
+        float wv = w.dtype == BG_F64 ? (float)reinterpret_cast<const double*>(w.ptr)[col + e] : ld_f32class(w.ptr, w.dtype, col + e);
+        float bv = b.dtype == BG_F64 ? (float)reinterpret_cast<const double*>(b.ptr)[col + e] : ld_f32class(b.ptr, b.dtype, col + e);
+        float y = __fadd_rn(__fmul_rn(xh, wv), bv);
+        store_scalar(out.ptr, out.dtype, row * p.cols + col + e, (double)y, 0, false);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kBlock) row_kernel(const __grid_constant__ EwProgram p, int U, int64_t n_chunks) {
+  extern __shared__ __align__(16) char smem[];
+  const int planes = p.wide ? 2 : 1;
+  RegFile rf{smem, U, planes};
+  char* scratch = smem + (size_t)p.n_regs * U * planes * kBlock * 16;
+  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    if (p.tail == TAIL_REDUCE) {
+      if (p.tail_type == T_F32) row_reduce<float>(p, rf, row, U, n_chunks, scratch);
+      else if (p.tail_type == T_F64) row_reduce<double>(p, rf, row, U, n_chunks, scratch);
+      else if (p.tail_type == T_I64) row_reduce<long long>(p, rf, row, U, n_chunks, scratch);
+      else row_reduce_bool(p, rf, row, U, n_chunks);
+    } else {
+      if (p.tail_type == T_F64) row_resident_tail<double>(p, rf, row, U, scratch);
+      else row_resident_tail<float>(p, rf, row, U, scratch);
+    }
+    __syncthreads();
+  }
+}
+
+int rowwise_max_chunks(int n_regs, int wide) {
+  const size_t per_chunk = (size_t)(n_regs > 0 ? n_regs : 1) * (wide ? 2 : 1) * kBlock * 16;
+  return (int)((200 * 1024 - 512) / per_chunk);
+}
+
+cudaError_t launch_rowwise(const EwProgram& p, cudaStream_t s, int sm_count, int* /*status_flag*/) {
+  if (p.rows == 0) return cudaSuccess;
+  const int planes = p.wide ? 2 : 1;
+  const size_t per_chunk = (size_t)p.n_regs * planes * kBlock * 16;
+  const int64_t n_chunks = (p.cols + kChunk - 1) / kChunk;
+  int U;
+  if (p.tail == TAIL_REDUCE) {
+    U = n_chunks < 2 ? (int)n_chunks : 2;
+    if (per_chunk * U > 64 * 1024) U = 1;
+  } else {
+    U = (int)n_chunks;
+  }
+  if (U < 1) U = 1;
+  const size_t smem = per_chunk * U + 512;
+  if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
+    if (e != cudaSuccess) return e;
+  }
+  int ctas_per_sm = (int)(200 * 1024 / smem);
+  if (ctas_per_sm > 8) ctas_per_sm = 8;
+  if (ctas_per_sm < 1) ctas_per_sm = 1;
+  int64_t grid = (int64_t)sm_count * ctas_per_sm;
+  if (grid > p.rows) grid = p.rows;
+  row_kernel<<<(unsigned)grid, kBlock, smem, s>>>(p, U, n_chunks);
+  return cudaGetLastError();
+}
+
+}  // namespace bg

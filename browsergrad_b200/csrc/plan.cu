@@ -1,0 +1,1747 @@
+// Plan compiler and executor.
+//
+// A tensor plan (the reference's GpuExecutionPlan wire format, flattened to bg_plan_step) is
+// compiled once per distinct plan into a list of kernel launches and cached by content hash:
+//   1. FUSED_ELEMENTWISE / ATTENTION_FORWARD steps are expanded into primitive nodes;
+//   2. LOAD / RESHAPE / PERMUTE / BROADCAST_TO become strided views (no data movement);
+//   3. elementwise nodes of equal shape and equal dependency depth are merged into fusion
+//      groups (the reference's own groups are single-consumer chains of six opcodes,
+//      packages/browsergrad-jit/src/python/_fusion.py:141-181; here CMP, WHERE, CAST, constants,
+//      broadcast operands and multi-consumer values fuse too);
+//   4. a REDUCE / FUSED_SOFTMAX / LAYER_NORM over trailing axes becomes the on-chip tail of the
+//      group that produces its input;
+//   5. each group is lowered to an EwProgram (register program) for the generic kernel;
+//   6. MATMUL, INDEX, CROSS_ENTROPY lower to their own kernels;
+//   7. units are scheduled topologically, intermediates are allocated stream-ordered at first
+//      use and freed after their last reader.
+#include "runtime.h"
+
+#include <string.h>
+
+#include <algorithm>
+#include <set>
+#include <sstream>
+
+namespace bg {
+
+struct View {
+  int slot = -1;        // storage slot, -1 for constants
+  int64_t off = 0;      // element offset into the slot
+  int rank = 0;
+  int64_t shape[kMaxRank] = {0};
+  int64_t stride[kMaxRank] = {0};
+  int dtype = BG_F32;
+  bool is_const = false;
+  double cf = 0;
+  int64_t ci = 0;
+  int64_t numel() const {
+    int64_t n = 1;
+    for (int i = 0; i < rank; ++i) n *= shape[i];
+    return n;
+  }
+  bool contiguous() const {
+    int64_t expect = 1;
+    for (int d = rank - 1; d >= 0; --d) {
+      if (shape[d] != 1 && stride[d] != expect) return false;
+      expect *= shape[d];
+    }
+    return true;
+  }
+  void set_dense(const int64_t* shp, int r) {
+    rank = r;
+    int64_t s = 1;
+    for (int d = r - 1; d >= 0; --d) {
+      shape[d] = shp[d];
+      stride[d] = s;
+      s *= shp[d];
+    }
+  }
+};
+
+struct Node {
+  int op = 0, dtype = BG_F32, rank = 0;
+  int64_t shape[kMaxRank] = {0};
+  std::vector<int> in;
+  int64_t iarg[kMaxRank] = {0};
+  double farg[2] = {0, 0};
+  int step = -1;
+  int64_t numel() const {
+    int64_t n = 1;
+    for (int i = 0; i < rank; ++i) n *= shape[i];
+    return n;
+  }
+};
+
+enum Kind { K_LEAF, K_CONST, K_ALIAS, K_VIEW, K_EW, K_ROW, K_OTHER, K_DEAD };
+
+struct Slot {
+  int64_t bytes = 0;
+  bool external = false;
+  int value_node = -1;   // for external slots: the BUFFER node
+  int first_unit = -1, last_unit = -1;
+};
+
+struct Run {
+  bg_context* ctx;
+  std::vector<void*> ptr;
+};
+
+struct Unit {
+  std::string name;
+  std::vector<int> reads, writes;   // slots
+  std::function<int(Run&)> fn;
+  int launches = 1;
+};
+
+struct CompiledPlan {
+  std::vector<Slot> slots;
+  std::vector<Unit> units;
+  std::vector<std::pair<int, int>> buffers;  // (step value_id, slot)
+  std::vector<int64_t> buffer_bytes;
+  int root_slot = -1;
+  int root_dtype = BG_F32;
+  int root_rank = 0;
+  int64_t root_shape[kMaxRank] = {0};
+  int64_t root_bytes = 0;
+  bool uses_status = false;
+  int64_t plan_peak = 0;
+  std::string trace;
+};
+
+namespace {
+
+inline EwType cls_of(int dt) {
+  if (dt == BG_F64) return T_F64;
+  if (dtype_is_float(dt)) return T_F32;
+  if (dt == BG_BOOL) return T_B;
+  return T_I64;
+}
+inline bool narrow_dtype(int dt) {
+  return dt == BG_F16 || dt == BG_BF16 || dt == BG_I8 || dt == BG_I16 || dt == BG_I32 || dt == BG_U8 || dt == BG_U16 ||
+         dt == BG_U32;
+}
+// np.promote_types for the dtypes of the IR (bfloat16 treated like float16 against integers).
+int promote(int a, int b) {
+  if (a == b) return a;
+  if (a == BG_BOOL) return b;
+  if (b == BG_BOOL) return a;
+  const bool fa = dtype_is_float(a), fb = dtype_is_float(b);
+  if (fa && fb) {
+    if (a == BG_F64 || b == BG_F64) return BG_F64;
+    if (a == BG_F32 || b == BG_F32) return BG_F32;
+    return (a == b) ? a : BG_F32;  // f16 with bf16
+  }
+  if (fa || fb) {
+    int f = fa ? a : b, i = fa ? b : a;
+    int ibits = dtype_size(i) * 8;
+    if (f == BG_F64) return BG_F64;
+    if (f == BG_F32) return ibits <= 16 ? BG_F32 : BG_F64;
+    return ibits <= 8 ? f : (ibits <= 16 ? BG_F32 : BG_F64);
+  }
+  const bool sa = a >= BG_I8 && a <= BG_I64, sb = b >= BG_I8 && b <= BG_I64;
+  const int ba = dtype_size(a), bb = dtype_size(b);
+  if (sa == sb) return ba >= bb ? a : b;
+  int s = sa ? a : b, u = sa ? b : a;
+  int bs = dtype_size(s), bu = dtype_size(u);
+  if (bs > bu) return s;
+  if (bu == 8) return BG_F64;
+  return bu == 1 ? BG_I16 : (bu == 2 ? BG_I32 : BG_I64);
+}
+
+bool is_ew_op(int op) {
+  switch (op) {
+    case BG_OP_CAST: case BG_OP_ADD: case BG_OP_MUL: case BG_OP_DIV: case BG_OP_NEG: case BG_OP_EXP: case BG_OP_LOG:
+    case BG_OP_ABS: case BG_OP_SIGN: case BG_OP_SIN: case BG_OP_COS: case BG_OP_ISNAN: case BG_OP_CMP: case BG_OP_WHERE:
+      return true;
+  }
+  return false;
+}
+
+uint64_t fnv1a(const void* data, size_t n, uint64_t h) {
+  const unsigned char* p = reinterpret_cast<const unsigned char*>(data);
+  for (size_t i = 0; i < n; ++i) { h ^= p[i]; h *= 1099511628211ull; }
+  return h;
+}
+
+struct CompileError {
+  int code;
+  std::string msg;
+};
+
+// A fusion group lowered to a program, with slot references to patch at run time.
+struct ProgramSpec {
+  EwProgram prog;
+  int in_slot[kEwMaxInputs];
+  int64_t in_off_bytes[kEwMaxInputs];
+  int out_slot[kEwMaxOutputs];
+  bool row = false;
+};
+
+class Compiler {
+ public:
+  Compiler(bg_context* ctx, const bg_plan* plan) : ctx_(ctx), plan_(plan) {}
+  std::shared_ptr<CompiledPlan> compile();
+
+ private:
+  bg_context* ctx_;
+  const bg_plan* plan_;
+  std::vector<Node> nodes_;
+  std::vector<int> step_node_;
+  std::vector<Kind> kind_;
+  std::vector<View> view_;
+  std::vector<std::vector<int>> cons_;
+  std::vector<int> depth_, group_, need_mat_, tail_of_group_, attached_;
+  std::vector<char> force_break_;
+  std::vector<char> leaflike_;
+  std::map<int, View> copy_src_;   // RESHAPE nodes that need a dense copy: the strided source view
+  std::shared_ptr<CompiledPlan> cp_;
+  int root_ = -1;
+  // scheduling
+  struct PUnit {
+    Unit u;
+    int order_key;
+    std::vector<int> dep_nodes;   // nodes whose storage must be ready
+    std::vector<int> out_nodes;   // nodes this unit makes ready
+  };
+  std::vector<PUnit> punits_;
+  std::vector<int> producer_;     // node -> punit index (-1: always ready)
+
+  [[noreturn]] void err(int code, const std::string& m) { throw CompileError{code, m}; }
+  int new_slot(int64_t bytes, bool external, int node) {
+    Slot s;
+    s.bytes = bytes;
+    s.external = external;
+    s.value_node = node;
+    cp_->slots.push_back(s);
+    return (int)cp_->slots.size() - 1;
+  }
+  int resolve(int n) const {  // through LOAD aliases
+    while (kind_[n] == K_ALIAS) n = nodes_[n].in[0];
+    return n;
+  }
+  int find(int g) {
+    while (group_[g] != g) { group_[g] = group_[group_[g]]; g = group_[g]; }
+    return g;
+  }
+  void expand();
+  void simplify();
+  std::vector<char> live_;
+  void build_views();
+  void analyse();
+  bool try_lower();
+  void own_slot(int n) {
+    if (view_[n].slot < 0) err(BG_ERR_INVALID, "internal: computed value without a slot");
+  }
+  bool build_program(const std::vector<int>& members, int tail_node, ProgramSpec& ps, std::vector<int>& dep_nodes,
+                     std::vector<int>& out_nodes, std::string& why);
+  void add_unit(PUnit&& pu) { punits_.push_back(std::move(pu)); }
+  void emit_group(const std::vector<int>& members, int tail_node, int key);
+  void emit_row_standalone(int r, int key);
+  void emit_matmul(int n, int key);
+  void emit_index(int n, int key);
+  void emit_ce(int n, int key);
+  void emit_copy(int n, const View& sv, int src, int key);
+  void emit_generic_reduce(int n, int key);
+  void emit_generic_softmax(int n, int key);
+  void emit_const_fill(int n, int key);
+  bool row_geometry(int r, int64_t& rows, int64_t& cols, View& xin, bool& trailing);
+  void schedule();
+};
+
+void Compiler::expand() {
+  const int ns = plan_->n_steps;
+  step_node_.assign(ns, -1);
+  for (int s = 0; s < ns; ++s) {
+    const bg_plan_step& st = plan_->steps[s];
+    if (st.op < 0 || st.op >= BG_OP_COUNT) err(BG_ERR_UNSUPPORTED, "plan step " + std::to_string(s) + ": unknown opcode");
+    if (st.rank < 0 || st.rank > BG_MAX_RANK) err(BG_ERR_INVALID, "plan step " + std::to_string(s) + ": bad rank");
+    if (!dtype_size(st.dtype)) err(BG_ERR_INVALID, "plan step " + std::to_string(s) + ": unknown dtype");
+    if (st.n_inputs < 0 || st.n_inputs > BG_MAX_STEP_INPUTS) err(BG_ERR_INVALID, "plan step " + std::to_string(s) + ": bad input count");
+    std::vector<int> ins;
+    for (int i = 0; i < st.n_inputs; ++i) {
+      int id = st.input_ids[i];
+      if (id < 0 || id >= s) err(BG_ERR_INVALID, "plan step " + std::to_string(s) + ": input " + std::to_string(id) + " does not precede it");
+      ins.push_back(step_node_[id]);
+    }
+    auto base = [&](int op) {
+      Node n;
+      n.op = op;
+      n.dtype = st.dtype;
+      n.rank = st.rank;
+      for (int d = 0; d < st.rank; ++d) {
+        if (st.shape[d] < 0) err(BG_ERR_INVALID, "plan step " + std::to_string(s) + ": negative extent");
+        n.shape[d] = st.shape[d];
+      }
+      memcpy(n.iarg, st.iarg, sizeof(n.iarg));
+      n.farg[0] = st.farg[0];
+      n.farg[1] = st.farg[1];
+      n.step = s;
+      return n;
+    };
+    if (st.op == BG_OP_FUSED_ELEMENTWISE) {
+      if (st.ext_count < 1 || st.ext_offset < 0 || (int64_t)st.ext_offset + 3ll * st.ext_count > plan_->n_ext)
+        err(BG_ERR_INVALID, "FUSED_ELEMENTWISE: op list out of range");
+      std::vector<int> made;
+      for (int k = 0; k < st.ext_count; ++k) {
+        const int32_t* t = plan_->ext + st.ext_offset + 3 * k;
+        int op = t[0];
+        if (!(op == BG_OP_ADD || op == BG_OP_MUL || op == BG_OP_DIV || op == BG_OP_NEG || op == BG_OP_EXP || op == BG_OP_LOG))
+          err(BG_ERR_UNSUPPORTED, std::string("FUSED_ELEMENTWISE: unsupported inner opcode ") + op_name(op));
+        auto ref = [&](int32_t r) -> int {
+          if (r < 0) {
+            int e = -r - 1;
+            if (e >= (int)ins.size()) err(BG_ERR_INVALID, "FUSED_ELEMENTWISE: external ref out of range");
+            return ins[e];
+          }
+          if (r >= k) err(BG_ERR_INVALID, "FUSED_ELEMENTWISE: step ref does not precede its use");
+          return made[r];
+        };
+        Node n = base(op);
+        n.in.push_back(ref(t[1]));
+        const bool binary = op == BG_OP_ADD || op == BG_OP_MUL || op == BG_OP_DIV;
+        if (binary) {
+          if (t[2] == BG_REF_NONE) err(BG_ERR_INVALID, "FUSED_ELEMENTWISE: binary op without rhs");
+          n.in.push_back(ref(t[2]));
+        }
+        nodes_.push_back(n);
+        made.push_back((int)nodes_.size() - 1);
+      }
+      step_node_[s] = made.back();
+    } else if (st.op == BG_OP_ATTENTION_FORWARD) {
+      if (ins.size() != 3 || st.rank != 4) err(BG_ERR_INVALID, "ATTENTION_FORWARD: three rank-4 inputs required");
+      const Node& q = nodes_[ins[0]];
+      const Node& k = nodes_[ins[1]];
+      if (q.rank != 4 || k.rank != 4) err(BG_ERR_INVALID, "ATTENTION_FORWARD: rank-4 inputs required");
+      Node kt = base(BG_OP_PERMUTE);
+      kt.shape[2] = k.shape[3]; kt.shape[3] = k.shape[2];
+      kt.shape[0] = k.shape[0]; kt.shape[1] = k.shape[1];
+      kt.in = {ins[1]};
+      kt.iarg[0] = 0; kt.iarg[1] = 1; kt.iarg[2] = 3; kt.iarg[3] = 2;
+      nodes_.push_back(kt);
+      int ikt = (int)nodes_.size() - 1;
+      Node mm = base(BG_OP_MATMUL);
+      mm.shape[3] = k.shape[2];
+      mm.in = {ins[0], ikt};
+      nodes_.push_back(mm);
+      int imm = (int)nodes_.size() - 1;
+      Node c = base(BG_OP_CONST);
+      c.rank = 0;
+      c.farg[0] = (double)(float)st.farg[0];
+      nodes_.push_back(c);
+      int ic = (int)nodes_.size() - 1;
+      Node mu = base(BG_OP_MUL);
+      mu.shape[3] = k.shape[2];
+      mu.in = {imm, ic};
+      nodes_.push_back(mu);
+      int imu = (int)nodes_.size() - 1;
+      Node sm = base(BG_OP_FUSED_SOFTMAX);
+      sm.shape[3] = k.shape[2];
+      sm.in = {imu};
+      sm.iarg[0] = 3;
+      nodes_.push_back(sm);
+      int ism = (int)nodes_.size() - 1;
+      Node pv = base(BG_OP_MATMUL);
+      pv.in = {ism, ins[2]};
+      nodes_.push_back(pv);
+      step_node_[s] = (int)nodes_.size() - 1;
+    } else {
+      Node n = base(st.op);
+      n.in = ins;
+      nodes_.push_back(n);
+      step_node_[s] = (int)nodes_.size() - 1;
+    }
+  }
+  if (plan_->root_id < 0 || plan_->root_id >= ns) err(BG_ERR_INVALID, "plan root out of range");
+  root_ = step_node_[plan_->root_id];
+}
+
+// Graph clean-up on the expanded node list:
+//  * CAST of a CONST folds into a CONST of the target dtype (the AMP pass wraps Python-scalar
+//    constants in CASTs, packages/browsergrad-jit/src/python/_amp.py:183-261);
+//  * the six-node softmax template REDUCE(max) -> NEG -> ADD -> EXP -> REDUCE(sum) -> DIV is
+//    rewritten to FUSED_SOFTMAX.  The reference's fuse pass does the same
+//    (_fusion.py:273-351) but loses the rewrite when a node downstream is substituted too
+//    (_fusion.py:383-388), so multi-layer graphs arrive with the primitive form;
+//  * nodes the root does not depend on are dropped.
+void Compiler::simplify() {
+  const int nn = (int)nodes_.size();
+  for (int i = 0; i < nn; ++i) {
+    Node& n = nodes_[i];
+    if (n.op == BG_OP_CAST && n.in.size() == 1 && nodes_[n.in[0]].op == BG_OP_CONST) {
+      const Node& c = nodes_[n.in[0]];
+      double cf = dtype_is_float(c.dtype) ? c.farg[0] : (double)c.iarg[0];
+      int64_t ci = dtype_is_float(c.dtype) ? (int64_t)c.farg[0] : c.iarg[0];
+      Node f = n;
+      f.op = BG_OP_CONST;
+      f.in.clear();
+      if (n.dtype == BG_F32) f.farg[0] = (double)(float)cf;
+      else if (n.dtype == BG_F64) f.farg[0] = cf;
+      else if (dtype_is_float(n.dtype)) continue;  // f16 / bf16 rounding stays on the device
+      else if (n.dtype == BG_BOOL) f.iarg[0] = dtype_is_float(c.dtype) ? (cf != 0.0) : (ci != 0);
+      else if (n.dtype == BG_I64) f.iarg[0] = ci;
+      else continue;
+      n = f;
+    }
+  }
+  auto compute_live = [&]() {
+    live_.assign(nn, 0);
+    std::vector<int> stack{root_};
+    while (!stack.empty()) {
+      int x = stack.back();
+      stack.pop_back();
+      if (live_[x]) continue;
+      live_[x] = 1;
+      for (int in : nodes_[x].in) stack.push_back(in);
+    }
+  };
+  compute_live();
+  std::vector<int> uses(nn, 0);
+  for (int i = 0; i < nn; ++i)
+    if (live_[i])
+      for (int in : nodes_[i].in) uses[in]++;
+  auto single_axis = [&](const Node& r, int& axis) {
+    uint64_t m = (uint64_t)r.iarg[1];
+    if (m == 0 || (m & (m - 1))) return false;
+    axis = 0;
+    while (!((m >> axis) & 1)) ++axis;
+    return true;
+  };
+  bool changed = false;
+  for (int i = 0; i < nn; ++i) {
+    Node& div = nodes_[i];
+    if (!live_[i] || div.op != BG_OP_DIV || div.in.size() != 2) continue;
+    const int ie = div.in[0], is = div.in[1];
+    const Node& e = nodes_[ie];
+    const Node& sum = nodes_[is];
+    int ax_s, ax_m;
+    if (e.op != BG_OP_EXP || sum.op != BG_OP_REDUCE || sum.iarg[0] != BG_RED_SUM || !sum.iarg[2]) continue;
+    if (sum.in.size() != 1 || sum.in[0] != ie || uses[ie] != 2 || uses[is] != 1 || !single_axis(sum, ax_s)) continue;
+    const int ia = e.in[0];
+    const Node& add = nodes_[ia];
+    if (add.op != BG_OP_ADD || add.in.size() != 2 || uses[ia] != 1) continue;
+    int ix = add.in[0], ineg = add.in[1];
+    if (nodes_[ineg].op != BG_OP_NEG) std::swap(ix, ineg);
+    const Node& neg = nodes_[ineg];
+    if (neg.op != BG_OP_NEG || uses[ineg] != 1) continue;
+    const int im = neg.in[0];
+    const Node& mx = nodes_[im];
+    if (mx.op != BG_OP_REDUCE || mx.iarg[0] != BG_RED_MAX || !mx.iarg[2] || uses[im] != 1) continue;
+    if (mx.in.size() != 1 || mx.in[0] != ix || !single_axis(mx, ax_m) || ax_m != ax_s) continue;
+    if (nodes_[ix].rank != div.rank || nodes_[ix].dtype != div.dtype) continue;
+    bool same = true;
+    for (int d = 0; d < div.rank; ++d) same &= nodes_[ix].shape[d] == div.shape[d];
+    if (!same) continue;
+    div.op = BG_OP_FUSED_SOFTMAX;
+    div.in = {ix};
+    memset(div.iarg, 0, sizeof(div.iarg));
+    div.iarg[0] = ax_s;
+    changed = true;
+    // uses of the absorbed nodes are stale now; recompute before the next match
+    compute_live();
+    std::fill(uses.begin(), uses.end(), 0);
+    for (int k = 0; k < nn; ++k)
+      if (live_[k])
+        for (int in : nodes_[k].in) uses[in]++;
+  }
+  (void)changed;
+}
+
+void Compiler::build_views() {
+  const int nn = (int)nodes_.size();
+  kind_.assign(nn, K_OTHER);
+  view_.assign(nn, View());
+  leaflike_.assign(nn, 0);
+  for (int i = 0; i < nn; ++i) {
+    Node& n = nodes_[i];
+    View& v = view_[i];
+    v.dtype = n.dtype;
+    if (!live_[i]) { kind_[i] = K_DEAD; continue; }
+    auto need_inputs = [&](size_t k) {
+      if (n.in.size() != k) err(BG_ERR_INVALID, std::string(op_name(n.op)) + ": expected " + std::to_string(k) + " inputs");
+    };
+    switch (n.op) {
+      case BG_OP_BUFFER: {
+        kind_[i] = K_LEAF;
+        leaflike_[i] = 1;
+        v.set_dense(n.shape, n.rank);
+        v.slot = new_slot(n.numel() * dtype_size(n.dtype), true, i);
+        cp_->buffers.push_back({n.step, v.slot});
+        cp_->buffer_bytes.push_back(n.numel() * dtype_size(n.dtype));
+        break;
+      }
+      case BG_OP_CONST:
+        kind_[i] = K_CONST;
+        leaflike_[i] = 1;
+        v.set_dense(n.shape, n.rank);
+        v.is_const = true;
+        if (dtype_is_float(n.dtype)) { v.cf = n.farg[0]; v.ci = (int64_t)n.farg[0]; }
+        else { v.ci = n.iarg[0]; v.cf = (double)n.iarg[0]; }
+        break;
+      case BG_OP_LOAD:
+        need_inputs(1);
+        kind_[i] = K_ALIAS;
+        leaflike_[i] = leaflike_[n.in[0]];
+        v = view_[n.in[0]];
+        break;
+      case BG_OP_PERMUTE: {
+        need_inputs(1);
+        const int src = resolve(n.in[0]);
+        if (nodes_[src].rank != n.rank) err(BG_ERR_INVALID, "PERMUTE: rank mismatch");
+        std::set<int64_t> seen;
+        for (int d = 0; d < n.rank; ++d) {
+          int64_t a = n.iarg[d];
+          if (a < 0 || a >= n.rank || !seen.insert(a).second) err(BG_ERR_INVALID, "PERMUTE: axes are not a permutation");
+          if (nodes_[src].shape[a] != n.shape[d]) err(BG_ERR_INVALID, "PERMUTE: declared shape does not match permuted input");
+        }
+        kind_[i] = K_VIEW;
+        break;
+      }
+      case BG_OP_BROADCAST_TO: case BG_OP_RESHAPE:
+        need_inputs(1);
+        kind_[i] = K_VIEW;
+        break;
+      case BG_OP_REDUCE: case BG_OP_FUSED_SOFTMAX: case BG_OP_LAYER_NORM:
+        kind_[i] = K_ROW;
+        v.set_dense(n.shape, n.rank);
+        v.slot = new_slot(n.numel() * dtype_size(n.dtype), false, i);
+        break;
+      case BG_OP_MATMUL: case BG_OP_INDEX: case BG_OP_CROSS_ENTROPY:
+        kind_[i] = K_OTHER;
+        v.set_dense(n.shape, n.rank);
+        v.slot = new_slot(n.numel() * dtype_size(n.dtype), false, i);
+        break;
+      default:
+        if (!is_ew_op(n.op)) err(BG_ERR_UNSUPPORTED, std::string("opcode ") + op_name(n.op) + " is not supported by the CUDA bridge");
+        kind_[i] = K_EW;
+        v.set_dense(n.shape, n.rank);
+        // every computed value gets a slot id up front so that views of it can name it; a slot
+        // that no unit writes is never allocated
+        v.slot = new_slot(n.numel() * dtype_size(n.dtype), false, i);
+        break;
+    }
+  }
+}
+
+// Second half of view construction: needs to know which EW nodes are materialised, so it runs
+// after `analyse` decided that every input of a VIEW node is materialised.
+static bool reshape_view(const View& in, const int64_t* shp, int rank, View& out) {
+  if (!in.contiguous()) return false;
+  out = in;
+  out.set_dense(shp, rank);
+  return true;
+}
+
+void Compiler::analyse() {
+  const int nn = (int)nodes_.size();
+  cons_.assign(nn, {});
+  for (int i = 0; i < nn; ++i)
+    if (kind_[i] != K_DEAD)
+      for (int in : nodes_[i].in) cons_[resolve(in)].push_back(i);
+  // views (metadata only; a RESHAPE of a non-contiguous view becomes a copy unit)
+  for (int i = 0; i < nn; ++i) {
+    if (kind_[i] != K_VIEW) continue;
+    Node& n = nodes_[i];
+    const int src = resolve(n.in[0]);
+    const View& sv = view_[src];
+    View v;
+    if (n.op == BG_OP_PERMUTE) {
+      v = sv;
+      for (int d = 0; d < n.rank; ++d) { v.shape[d] = sv.shape[n.iarg[d]]; v.stride[d] = sv.stride[n.iarg[d]]; }
+      leaflike_[i] = leaflike_[src];
+    } else if (n.op == BG_OP_BROADCAST_TO) {
+      v = sv;
+      v.rank = n.rank;
+      const int lead = n.rank - sv.rank;
+      if (lead < 0) err(BG_ERR_INVALID, "BROADCAST_TO: rank shrinks");
+      for (int d = 0; d < n.rank; ++d) {
+        v.shape[d] = n.shape[d];
+        if (d < lead) v.stride[d] = 0;
+        else if (sv.shape[d - lead] == n.shape[d]) v.stride[d] = sv.stride[d - lead];
+        else if (sv.shape[d - lead] == 1) v.stride[d] = 0;
+        else err(BG_ERR_INVALID, "BROADCAST_TO: shapes are not broadcastable");
+      }
+      leaflike_[i] = leaflike_[src];
+    } else {  // RESHAPE
+      if (nodes_[src].numel() != n.numel()) err(BG_ERR_INVALID, "RESHAPE: element count changes");
+      if (sv.is_const) { v = sv; v.set_dense(n.shape, n.rank); leaflike_[i] = 1; }
+      else if (reshape_view(sv, n.shape, n.rank, v)) leaflike_[i] = leaflike_[src];
+      else {
+        kind_[i] = K_OTHER;  // dense copy of the strided source, then a plain view of the copy
+        copy_src_[i] = sv;
+        v = View();
+        v.set_dense(n.shape, n.rank);
+        v.slot = new_slot(n.numel() * dtype_size(n.dtype), false, i);
+        leaflike_[i] = 0;
+      }
+    }
+    v.dtype = n.dtype;
+    view_[i] = v;
+  }
+  // depth + grouping
+  depth_.assign(nn, 0);
+  group_.resize(nn);
+  for (int i = 0; i < nn; ++i) group_[i] = i;
+  auto same_shape = [&](int a, int b) {
+    if (nodes_[a].rank != nodes_[b].rank) return false;
+    for (int d = 0; d < nodes_[a].rank; ++d)
+      if (nodes_[a].shape[d] != nodes_[b].shape[d]) return false;
+    return true;
+  };
+  auto mergeable = [&](int n, int i) {
+    return ctx_->fusion && kind_[i] == K_EW && kind_[n] == K_EW && same_shape(n, i) && !force_break_[i];
+  };
+  for (int i = 0; i < nn; ++i) {
+    const Node& n = nodes_[i];
+    int d = 0;
+    if (kind_[i] == K_LEAF || kind_[i] == K_CONST) d = 0;
+    else if (kind_[i] == K_ALIAS) d = depth_[n.in[0]];
+    else if (kind_[i] == K_VIEW) { int s = resolve(n.in[0]); d = depth_[s]; }
+    else if (kind_[i] == K_EW) {
+      for (int in : n.in) {
+        int s = resolve(in);
+        int c = mergeable(i, s) ? depth_[s] : depth_[s] + (leaflike_[s] ? 0 : 1);
+        d = std::max(d, c);
+      }
+    } else {
+      for (int in : n.in) { int s = resolve(in); d = std::max(d, depth_[s] + (leaflike_[s] ? 0 : 1)); }
+    }
+    depth_[i] = d;
+    if (kind_[i] == K_EW)
+      for (int in : n.in) {
+        int s = resolve(in);
+        if (mergeable(i, s) && depth_[s] == d) group_[find(i)] = find(s);
+      }
+  }
+  // tails
+  tail_of_group_.assign(nn, -1);
+  attached_.assign(nn, -1);
+  if (ctx_->fusion)
+    for (int i = 0; i < nn; ++i) {
+      if (kind_[i] != K_ROW) continue;
+      const int x = resolve(nodes_[i].in[0]);
+      if (kind_[x] != K_EW || force_break_[x]) continue;
+      int64_t rows, cols;
+      View xin;
+      bool trailing;
+      if (!row_geometry(i, rows, cols, xin, trailing) || !trailing) continue;
+      const int g = find(x);
+      if (tail_of_group_[g] >= 0) continue;
+      // layer norm weight/bias must not be produced inside the same group
+      bool ok = true;
+      for (size_t k = 1; k < nodes_[i].in.size(); ++k) {
+        int w = resolve(nodes_[i].in[k]);
+        if (kind_[w] == K_EW && find(w) == g) ok = false;
+        if (depth_[w] + (leaflike_[w] ? 0 : 1) > depth_[x]) ok = false;
+      }
+      if (!ok) continue;
+      tail_of_group_[g] = i;
+      attached_[i] = g;
+    }
+  // materialisation
+  need_mat_.assign(nn, 0);
+  for (int i = 0; i < nn; ++i) {
+    if (kind_[i] != K_EW) continue;
+    if (i == root_) need_mat_[i] = 1;
+    for (int c : cons_[i]) {
+      if (kind_[c] == K_EW && find(c) == find(i)) continue;
+      if (kind_[c] == K_ROW && attached_[c] == find(i) && resolve(nodes_[c].in[0]) == i) continue;
+      need_mat_[i] = 1;
+    }
+  }
+}
+
+bool Compiler::row_geometry(int r, int64_t& rows, int64_t& cols, View& xin, bool& trailing) {
+  const Node& n = nodes_[r];
+  const int x = resolve(n.in[0]);
+  const Node& xn = nodes_[x];
+  xin = view_[x];
+  trailing = false;
+  if (n.op == BG_OP_LAYER_NORM) {
+    rows = n.iarg[0];
+    cols = n.iarg[1];
+    if (rows * cols != xn.numel() || n.in.size() != 3) err(BG_ERR_INVALID, "LAYER_NORM: rows x cols does not match the input");
+    trailing = true;
+    return true;
+  }
+  if (n.op == BG_OP_FUSED_SOFTMAX) {
+    int64_t axis = n.iarg[0];
+    if (axis < 0 || axis >= xn.rank) err(BG_ERR_INVALID, "FUSED_SOFTMAX: axis out of range");
+    int64_t inner = 1;
+    for (int d = (int)axis + 1; d < xn.rank; ++d) inner *= xn.shape[d];
+    cols = xn.shape[axis];
+    rows = cols ? xn.numel() / cols : 0;
+    trailing = inner == 1;
+    return true;
+  }
+  // REDUCE
+  const uint64_t mask = (uint64_t)n.iarg[1];
+  int k = xn.rank;
+  while (k > 0 && ((mask >> (k - 1)) & 1)) --k;
+  bool tr = true;
+  for (int d = 0; d < k; ++d)
+    if ((mask >> d) & 1) tr = false;
+  cols = 1;
+  rows = 1;
+  for (int d = 0; d < xn.rank; ++d) {
+    if ((mask >> d) & 1) cols *= xn.shape[d]; else rows *= xn.shape[d];
+  }
+  trailing = tr;
+  return true;
+}
+
+// ---------------------------------------------------------------------------------------
+// Program construction
+// ---------------------------------------------------------------------------------------
+struct VInstr {
+  uint8_t op, type;
+  int dst, a, b, c;
+  uint16_t aux;
+};
+
+bool Compiler::build_program(const std::vector<int>& members, int tail_node, ProgramSpec& ps, std::vector<int>& dep_nodes,
+                             std::vector<int>& out_nodes, std::string& why) {
+  std::vector<VInstr> code;
+  int next_v = 0;
+  std::map<int, int> vreg;                        // node -> vreg (natural class)
+  std::map<std::pair<int, int>, int> cvt_memo;    // (vreg, class) -> vreg
+  std::map<int, int> load_memo;                   // external node -> vreg
+  std::vector<View> in_views;
+  std::vector<int> in_nodes;
+  std::vector<int64_t> consts;
+  std::set<int> member_set(members.begin(), members.end());
+  const Node& lead = nodes_[tail_node >= 0 ? resolve(nodes_[tail_node].in[0]) : members[0]];
+  // iteration shape = shape of the member nodes (all equal); for a standalone tail, the input's.
+  int it_rank = lead.rank;
+  int64_t it_shape[kMaxRank];
+  for (int d = 0; d < it_rank; ++d) it_shape[d] = lead.shape[d];
+
+  auto add_input = [&](int node, const View& v) -> int {
+    if ((int)in_views.size() >= kEwMaxInputs) return -1;
+    in_views.push_back(v);
+    in_nodes.push_back(node);
+    return (int)in_views.size() - 1;
+  };
+  auto add_const = [&](int64_t bits) -> int {
+    for (size_t i = 0; i < consts.size(); ++i)
+      if (consts[i] == bits) return (int)i;
+    if ((int)consts.size() >= kEwMaxConsts) return -1;
+    consts.push_back(bits);
+    return (int)consts.size() - 1;
+  };
+  bool failed = false;
+  auto emit = [&](uint8_t op, uint8_t type, int a, int b, int c, uint16_t aux) -> int {
+    int d = next_v++;
+    code.push_back({op, type, d, a, b, c, aux});
+    return d;
+  };
+  auto operand = [&](int node, EwType want) -> int {
+    node = resolve(node);
+    int v, c;
+    const View& vw = view_[node];
+    if (member_set.count(node)) {
+      v = vreg[node];
+      c = cls_of(nodes_[node].dtype);
+    } else if (vw.is_const) {
+      // a constant is emitted directly in the class its consumer computes in: that is the value
+      // NumPy's promotion (or an explicit CAST) would have produced
+      const EwType nat = cls_of(vw.dtype);
+      const bool want_f = want == T_F32 || want == T_F64;
+      int64_t bits;
+      EwType cc;
+      if (nat == T_F32 || nat == T_F64) {
+        double dv = nat == T_F32 ? (double)(float)vw.cf : vw.cf;
+        cc = want_f ? want : nat;
+        if (cc == T_F32) dv = (double)(float)dv;
+        memcpy(&bits, &dv, 8);
+      } else if (want_f) {
+        double dv = (double)vw.ci;
+        cc = want;
+        memcpy(&bits, &dv, 8);
+      } else {
+        cc = (nat == T_B && want == T_I64) ? T_I64 : nat;
+        bits = nat == T_B ? (vw.ci != 0) : vw.ci;
+      }
+      int ci = add_const(bits);
+      if (ci < 0) { failed = true; why = "too many constants"; return 0; }
+      auto key = std::make_pair(-1000 - ci, (int)cc);
+      auto it = cvt_memo.find(key);
+      if (it != cvt_memo.end()) v = it->second;
+      else { v = emit(E_CONST, cc, 0, 0, 0, (uint16_t)ci); cvt_memo[key] = v; }
+      c = cc;
+    } else {
+      auto it = load_memo.find(node);
+      if (it != load_memo.end()) v = it->second;
+      else {
+        int idx = add_input(node, vw);
+        if (idx < 0) { failed = true; why = "too many inputs"; return 0; }
+        v = emit(E_LOAD, cls_of(vw.dtype), 0, 0, 0, (uint16_t)idx);
+        load_memo[node] = v;
+      }
+      c = cls_of(vw.dtype);
+    }
+    if (c == (int)want) return v;
+    auto key = std::make_pair(v, (int)want);
+    auto it = cvt_memo.find(key);
+    if (it != cvt_memo.end()) return it->second;
+    int r = emit(E_CVT, want, v, 0, 0, (uint16_t)c);
+    cvt_memo[key] = r;
+    return r;
+  };
+
+  for (int m : members) {
+    const Node& n = nodes_[m];
+    const EwType nc = cls_of(n.dtype);
+    int r = -1;
+    auto need = [&](size_t k) {
+      if (n.in.size() != k) err(BG_ERR_INVALID, std::string(op_name(n.op)) + ": expected " + std::to_string(k) + " inputs");
+    };
+    switch (n.op) {
+      case BG_OP_ADD: case BG_OP_MUL: case BG_OP_DIV: {
+        need(2);
+        int a = operand(n.in[0], nc), b = operand(n.in[1], nc);
+        uint8_t op = n.op == BG_OP_ADD ? E_ADD : (n.op == BG_OP_MUL ? E_MUL : E_DIV);
+        if (nc == T_B) {
+          if (n.op == BG_OP_DIV) err(BG_ERR_UNSUPPORTED, "DIV on bool tensors is not supported");
+          op = n.op == BG_OP_ADD ? E_OR : E_AND;
+        }
+        r = emit(op, nc, a, b, 0, 0);
+        break;
+      }
+      case BG_OP_NEG: case BG_OP_EXP: case BG_OP_LOG: case BG_OP_ABS: case BG_OP_SIGN: case BG_OP_SIN: case BG_OP_COS: {
+        need(1);
+        if (nc == T_B) err(BG_ERR_UNSUPPORTED, std::string(op_name(n.op)) + " on bool tensors is not supported");
+        const bool transcend = n.op == BG_OP_EXP || n.op == BG_OP_LOG || n.op == BG_OP_SIN || n.op == BG_OP_COS;
+        if (nc == T_I64 && transcend) err(BG_ERR_UNSUPPORTED, std::string(op_name(n.op)) + " on integer tensors is not supported");
+        int a = operand(n.in[0], nc);
+        uint8_t op = E_NEG;
+        switch (n.op) {
+          case BG_OP_EXP: op = E_EXP; break;
+          case BG_OP_LOG: op = E_LOG; break;
+          case BG_OP_ABS: op = E_ABS; break;
+          case BG_OP_SIGN: op = E_SIGN; break;
+          case BG_OP_SIN: op = E_SIN; break;
+          case BG_OP_COS: op = E_COS; break;
+        }
+        r = emit(op, nc, a, 0, 0, 0);
+        break;
+      }
+      case BG_OP_ISNAN: {
+        need(1);
+        EwType ic = cls_of(nodes_[resolve(n.in[0])].dtype);
+        int a = operand(n.in[0], ic);
+        r = emit(E_ISNAN, ic, a, 0, 0, 0);
+        break;
+      }
+      case BG_OP_CMP: {
+        need(2);
+        int pd = promote(nodes_[resolve(n.in[0])].dtype, nodes_[resolve(n.in[1])].dtype);
+        EwType pc = cls_of(pd);
+        int a = operand(n.in[0], pc), b = operand(n.in[1], pc);
+        if (n.iarg[0] < 0 || n.iarg[0] > 5) err(BG_ERR_INVALID, "CMP: unknown comparison");
+        r = emit(E_CMP, pc, a, b, 0, (uint16_t)n.iarg[0]);
+        break;
+      }
+      case BG_OP_WHERE: {
+        need(3);
+        int c = operand(n.in[0], T_B), a = operand(n.in[1], nc), b = operand(n.in[2], nc);
+        r = emit(E_WHERE, nc, c, a, b, 0);
+        break;
+      }
+      case BG_OP_CAST: {
+        need(1);
+        int a = operand(n.in[0], nc);
+        // a CAST between dtypes of one class still needs its own register only when it narrows
+        r = narrow_dtype(n.dtype) ? emit(E_NARROW, nc, a, 0, 0, (uint16_t)n.dtype) : a;
+        break;
+      }
+      default:
+        err(BG_ERR_UNSUPPORTED, std::string("opcode ") + op_name(n.op) + " inside an elementwise group");
+    }
+    if (failed) return false;
+    if (n.op != BG_OP_CAST && narrow_dtype(n.dtype) && nc != T_B) r = emit(E_NARROW, nc, r, 0, 0, (uint16_t)n.dtype);
+    vreg[m] = r;
+  }
+  // outputs
+  std::vector<int> out_list;
+  for (int m : members)
+    if (need_mat_[m]) out_list.push_back(m);
+  int tail_reg_v = -1;
+  EwProgram& P = ps.prog;
+  memset(&P, 0, sizeof(P));
+  int n_out = 0;
+  for (int m : out_list) {
+    if (n_out >= kEwMaxOutputs) { why = "too many outputs"; return false; }
+    own_slot(m);
+    code.push_back({E_STORE, (uint8_t)cls_of(nodes_[m].dtype), -1, vreg[m], 0, 0, (uint16_t)n_out});
+    P.outputs[n_out].dtype = nodes_[m].dtype;
+    ps.out_slot[n_out] = view_[m].slot;
+    out_nodes.push_back(m);
+    ++n_out;
+  }
+  int64_t rows = 0, cols = 0;
+  if (tail_node >= 0) {
+    const Node& t = nodes_[tail_node];
+    View xin;
+    bool trailing;
+    row_geometry(tail_node, rows, cols, xin, trailing);
+    const int x = resolve(t.in[0]);
+    EwType xc = cls_of(nodes_[x].dtype);
+    EwType want = xc;
+    if (t.op == BG_OP_FUSED_SOFTMAX) {
+      if (xc != T_F32 && xc != T_F64) err(BG_ERR_UNSUPPORTED, "FUSED_SOFTMAX on non-float tensors");
+    } else if (t.op == BG_OP_LAYER_NORM) {
+      if (xc != T_F32 && xc != T_F64) err(BG_ERR_UNSUPPORTED, "LAYER_NORM on non-float tensors");
+    } else {
+      const int rop = (int)t.iarg[0];
+      if (rop < 0 || rop > BG_RED_ALL) err(BG_ERR_INVALID, "REDUCE: unknown reduction");
+      if (rop == BG_RED_ANY || rop == BG_RED_ALL) want = T_B;
+      else if (xc == T_B) want = T_I64;
+    }
+    tail_reg_v = operand(x, want);
+    if (failed) return false;
+    if (n_out >= kEwMaxOutputs) { why = "too many outputs"; return false; }
+    own_slot(tail_node);
+    P.outputs[n_out].dtype = t.dtype;
+    ps.out_slot[n_out] = view_[tail_node].slot;
+    out_nodes.push_back(tail_node);
+    P.tail_out = n_out;
+    P.tail_out_dtype = t.dtype;
+    P.tail_type = want;
+    ++n_out;
+    if (t.op == BG_OP_FUSED_SOFTMAX) P.tail = TAIL_SOFTMAX;
+    else if (t.op == BG_OP_LAYER_NORM) {
+      P.tail = TAIL_LAYERNORM;
+      P.tail_eps = (float)t.farg[0];
+      for (int k = 1; k <= 2; ++k) {
+        int w = resolve(t.in[k]);
+        const View& wv = view_[w];
+        if (wv.is_const || !wv.contiguous() || wv.numel() != cols || !dtype_is_float(wv.dtype))
+          err(BG_ERR_UNSUPPORTED, "LAYER_NORM: weight and bias must be dense float vectors of `cols` elements");
+        int idx = add_input(w, wv);
+        if (idx < 0) { why = "too many inputs"; return false; }
+        if (k == 1) P.tail_w = idx; else P.tail_b = idx;
+      }
+    } else {
+      P.tail = TAIL_REDUCE;
+      P.tail_arg = (int)t.iarg[0];
+    }
+    P.rows = rows;
+    P.cols = cols;
+  }
+  if ((int)code.size() > kEwMaxInstr) { why = "too many instructions"; return false; }
+  // register allocation (linear scan; a destination may take over a source that dies here)
+  std::vector<int> last(next_v, -1);
+  for (size_t i = 0; i < code.size(); ++i) {
+    const VInstr& I = code[i];
+    auto use = [&](int v) { if (v >= 0) last[v] = (int)i; };
+    const bool unary = I.op == E_NEG || I.op == E_EXP || I.op == E_LOG || I.op == E_ABS || I.op == E_SIGN || I.op == E_SIN ||
+                       I.op == E_COS || I.op == E_ISNAN || I.op == E_CVT || I.op == E_NARROW || I.op == E_STORE;
+    if (I.op == E_LOAD || I.op == E_CONST) continue;
+    use(I.a);
+    if (!unary) use(I.b);
+    if (I.op == E_WHERE) use(I.c);
+  }
+  if (tail_reg_v >= 0) last[tail_reg_v] = (int)code.size() + 1;
+  std::vector<int> phys(next_v, -1);
+  std::vector<char> busy;
+  auto alloc_reg = [&]() {
+    for (size_t i = 0; i < busy.size(); ++i)
+      if (!busy[i]) { busy[i] = 1; return (int)i; }
+    busy.push_back(1);
+    return (int)busy.size() - 1;
+  };
+  bool wide = false;
+  P.n_instr = (int)code.size();
+  for (size_t i = 0; i < code.size(); ++i) {
+    const VInstr& I = code[i];
+    EwInstr& O = P.instr[i];
+    O.op = I.op;
+    O.type = I.type;
+    O.aux = I.aux;
+    const bool unary = I.op == E_NEG || I.op == E_EXP || I.op == E_LOG || I.op == E_ABS || I.op == E_SIGN || I.op == E_SIN ||
+                       I.op == E_COS || I.op == E_ISNAN || I.op == E_CVT || I.op == E_NARROW || I.op == E_STORE;
+    const bool leaf = I.op == E_LOAD || I.op == E_CONST;
+    int srcs[3] = {leaf ? -1 : I.a, (leaf || unary) ? -1 : I.b, I.op == E_WHERE ? I.c : -1};
+    O.a = srcs[0] >= 0 ? (uint8_t)phys[srcs[0]] : 0;
+    O.b = srcs[1] >= 0 ? (uint8_t)phys[srcs[1]] : 0;
+    O.c = srcs[2] >= 0 ? (uint8_t)phys[srcs[2]] : 0;
+    for (int k = 0; k < 3; ++k)
+      if (srcs[k] >= 0 && last[srcs[k]] == (int)i && phys[srcs[k]] >= 0) {
+        bool dup = false;
+        for (int j = 0; j < k; ++j) dup |= srcs[j] == srcs[k];
+        if (!dup) busy[phys[srcs[k]]] = 0;
+      }
+    if (I.type == T_F64 || I.type == T_I64) wide = true;
+    if (I.op == E_CVT && ((I.aux & 0xF) == T_F64 || (I.aux & 0xF) == T_I64)) wide = true;
+    if (I.dst >= 0) {
+      if (last[I.dst] < 0 && I.op != E_STORE) {
+        // value never read (dead); still needs a slot for the write
+      }
+      phys[I.dst] = alloc_reg();
+      O.dst = (uint8_t)phys[I.dst];
+      if (last[I.dst] < 0) busy[phys[I.dst]] = 0;
+    }
+  }
+  P.n_regs = std::max<int>(1, (int)busy.size());
+  P.wide = wide ? 1 : 0;
+  if (tail_reg_v >= 0) P.tail_reg = phys[tail_reg_v];
+  const int64_t per_chunk = (int64_t)P.n_regs * (wide ? 2 : 1) * 4096;
+  if (per_chunk > 190 * 1024) { why = "register file does not fit shared memory"; return false; }
+  // iteration space: collapse dims that every operand walks contiguously
+  int64_t numel = 1;
+  for (int d = 0; d < it_rank; ++d) numel *= it_shape[d];
+  std::vector<std::vector<int64_t>> strides(in_views.size(), std::vector<int64_t>(it_rank, 0));
+  const int n_ew_inputs = (int)in_views.size();
+  for (int k = 0; k < n_ew_inputs; ++k) {
+    if (tail_node >= 0 && P.tail == TAIL_LAYERNORM && (k == P.tail_w || k == P.tail_b)) continue;
+    const View& v = in_views[k];
+    const int lead_d = it_rank - v.rank;
+    if (lead_d < 0) err(BG_ERR_INVALID, "elementwise operand has higher rank than the result");
+    for (int d = 0; d < it_rank; ++d) {
+      if (d < lead_d) { strides[k][d] = 0; continue; }
+      int64_t e = v.shape[d - lead_d];
+      if (e == it_shape[d]) strides[k][d] = e == 1 ? 0 : v.stride[d - lead_d];
+      else if (e == 1) strides[k][d] = 0;
+      else err(BG_ERR_INVALID, "elementwise operand shape is not broadcastable to the result");
+    }
+  }
+  std::vector<int64_t> cshape;
+  std::vector<std::vector<int64_t>> cstr(in_views.size());
+  for (int d = 0; d < it_rank; ++d) {
+    if (it_shape[d] == 1) continue;
+    bool merge = !cshape.empty();
+    if (merge)
+      for (int k = 0; k < n_ew_inputs; ++k) {
+        if (cstr[k].empty()) continue;
+        if (cstr[k].back() != strides[k][d] * it_shape[d]) { merge = false; break; }
+      }
+    if (merge) {
+      cshape.back() *= it_shape[d];
+      for (int k = 0; k < n_ew_inputs; ++k)
+        if (!cstr[k].empty()) cstr[k].back() = strides[k][d];
+    } else {
+      cshape.push_back(it_shape[d]);
+      for (int k = 0; k < n_ew_inputs; ++k) cstr[k].push_back(strides[k][d]);
+    }
+  }
+  if (cshape.empty()) {
+    cshape.push_back(1);
+    for (int k = 0; k < n_ew_inputs; ++k) cstr[k].assign(1, 0);
+  }
+  if ((int)cshape.size() > kEwMaxDims) { why = "iteration space has too many non-collapsible dimensions"; return false; }
+  P.ndim = (int)cshape.size();
+  for (int d = 0; d < P.ndim; ++d) P.shape[d] = cshape[d];
+  P.numel = numel;
+  if (tail_node < 0) { P.rows = 0; P.cols = 0; }
+  const bool row_vec = tail_node < 0 || (cols % 4 == 0);
+  P.n_inputs = n_ew_inputs;
+  for (int k = 0; k < n_ew_inputs; ++k) {
+    const View& v = in_views[k];
+    EwOperand& o = P.inputs[k];
+    o.dtype = v.dtype;
+    ps.in_slot[k] = v.slot;
+    ps.in_off_bytes[k] = v.off * dtype_size(v.dtype);
+    dep_nodes.push_back(in_nodes[k]);
+    if (tail_node >= 0 && P.tail == TAIL_LAYERNORM && (k == P.tail_w || k == P.tail_b)) { o.mode = A_CONTIG; continue; }
+    bool all_zero = true, contig = true;
+    int64_t expect = 1;
+    for (int d = P.ndim - 1; d >= 0; --d) {
+      o.stride[d] = cstr[k][d];
+      if (cstr[k][d] != 0) all_zero = false;
+      if (cstr[k][d] != expect) contig = false;
+      expect *= cshape[d];
+    }
+    if (numel <= 1) { all_zero = true; }
+    o.mode = all_zero ? A_SCALAR : (contig ? A_CONTIG : A_STRIDED);
+    const int es = dtype_size(v.dtype);
+    const int64_t vec_bytes = std::min<int64_t>(16, 4 * es);
+    bool ok = (ps.in_off_bytes[k] % vec_bytes) == 0 && row_vec;
+    if (o.mode == A_STRIDED) {
+      for (int d = 0; d + 1 < P.ndim; ++d)
+        if (o.stride[d] % 4 != 0) ok = false;
+    }
+    o.vec_ok = ok ? 1 : 0;
+  }
+  P.n_outputs = n_out;
+  for (int k = 0; k < n_out; ++k) P.outputs[k].vec_ok = row_vec ? 1 : 0;
+  P.n_consts = (int)consts.size();
+  for (size_t k = 0; k < consts.size(); ++k) P.consts[k] = consts[k];
+  ps.row = tail_node >= 0;
+  if (ps.row && P.tail != TAIL_REDUCE) {
+    const int64_t chunks = (cols + 1023) / 1024;
+    if (chunks > rowwise_max_chunks(P.n_regs, P.wide)) { why = "row does not fit the on-chip register file"; return false; }
+  }
+  return true;
+}
+
+static int run_program(Run& r, const ProgramSpec& ps) {
+  EwProgram p = ps.prog;
+  for (int k = 0; k < p.n_inputs; ++k)
+    p.inputs[k].ptr = reinterpret_cast<char*>(r.ptr[ps.in_slot[k]]) + ps.in_off_bytes[k];
+  for (int k = 0; k < p.n_outputs; ++k) p.outputs[k].ptr = r.ptr[ps.out_slot[k]];
+  cudaError_t e = ps.row ? launch_rowwise(p, r.ctx->stream, r.ctx->sm_count, r.ctx->d_status)
+                         : launch_elementwise(p, r.ctx->stream, r.ctx->sm_count);
+  if (e != cudaSuccess) return cuda_fail(r.ctx, e, ps.row ? "row kernel launch" : "elementwise kernel launch");
+  return BG_OK;
+}
+
+void Compiler::emit_group(const std::vector<int>& members, int tail_node, int key) {
+  auto ps = std::make_shared<ProgramSpec>();
+  PUnit pu;
+  std::string why;
+  if (!build_program(members, tail_node, *ps, pu.dep_nodes, pu.out_nodes, why)) throw CompileError{-1, why};
+  pu.order_key = key;
+  std::ostringstream nm;
+  nm << (tail_node >= 0 ? "row" : "ew") << "[";
+  for (size_t i = 0; i < members.size() && i < 6; ++i) nm << (i ? "," : "") << op_name(nodes_[members[i]].op);
+  if (members.size() > 6) nm << ",+" << members.size() - 6;
+  if (tail_node >= 0) nm << (members.empty() ? "" : "|") << op_name(nodes_[tail_node].op);
+  nm << "]";
+  pu.u.name = nm.str();
+  pu.u.fn = [ps](Run& r) { return run_program(r, *ps); };
+  add_unit(std::move(pu));
+}
+
+void Compiler::emit_row_standalone(int r, int key) {
+  std::vector<int> none;
+  emit_group(none, r, key);
+}
+
+void Compiler::emit_const_fill(int n, int key) {
+  // a constant that must exist in memory: CONST -> STORE over the node's shape
+  auto ps = std::make_shared<ProgramSpec>();
+  EwProgram& P = ps->prog;
+  memset(&P, 0, sizeof(P));
+  const View v = view_[n];
+  EwType c = cls_of(v.dtype);
+  int64_t bits;
+  if (c == T_F32 || c == T_F64) { double d = v.cf; memcpy(&bits, &d, 8); } else bits = v.ci;
+  P.consts[0] = bits;
+  P.n_consts = 1;
+  P.instr[0] = {E_CONST, (uint8_t)c, 0, 0, 0, 0, 0};
+  P.instr[1] = {E_STORE, (uint8_t)c, 0, 0, 0, 0, 0};
+  P.n_instr = 2;
+  P.n_regs = 1;
+  P.wide = (c == T_F64 || c == T_I64);
+  P.ndim = 1;
+  P.numel = nodes_[n].numel();
+  P.shape[0] = P.numel;
+  P.n_outputs = 1;
+  P.outputs[0].dtype = v.dtype;
+  P.outputs[0].vec_ok = 1;
+  View nv;
+  nv.set_dense(nodes_[n].shape, nodes_[n].rank);
+  nv.dtype = v.dtype;
+  nv.slot = new_slot(P.numel * dtype_size(v.dtype), false, n);
+  view_[n] = nv;
+  ps->out_slot[0] = nv.slot;
+  PUnit pu;
+  pu.order_key = key;
+  pu.out_nodes = {n};
+  pu.u.name = "fill[CONST]";
+  pu.u.fn = [ps](Run& r) { return run_program(r, *ps); };
+  add_unit(std::move(pu));
+}
+
+void Compiler::emit_copy(int n, const View& sv, int src, int key) {
+  // dense copy of a strided view (RESHAPE of a permuted tensor, or a view that is the plan root)
+  // into the slot already assigned to node n
+  const int es = dtype_size(nodes_[n].dtype);
+  const int64_t numel = nodes_[n].numel();
+  const int in_slot = sv.slot, out_slot = view_[n].slot;
+  StridedView tmpl{};
+  tmpl.dtype = sv.dtype;
+  tmpl.rank = sv.rank;
+  for (int d = 0; d < sv.rank; ++d) { tmpl.shape[d] = sv.shape[d]; tmpl.stride[d] = sv.stride[d]; }
+  const int64_t off_bytes = sv.off * es;
+  PUnit pu;
+  pu.order_key = key;
+  pu.dep_nodes = {src};
+  pu.out_nodes = {n};
+  pu.u.name = "copy[strided]";
+  pu.u.fn = [=](Run& r) {
+    StridedView v = tmpl;
+    v.ptr = reinterpret_cast<char*>(r.ptr[in_slot]) + off_bytes;
+    cudaError_t e = launch_strided_copy(v, r.ptr[out_slot], numel, r.ctx->stream);
+    return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "strided copy launch");
+  };
+  add_unit(std::move(pu));
+}
+
+void Compiler::emit_generic_reduce(int n, int key) {
+  // REDUCE over a contiguous block of non-trailing axes of a dense tensor: [outer, R, inner]
+  const Node& t = nodes_[n];
+  const int x = resolve(t.in[0]);
+  const View xv = view_[x];
+  const Node& xn = nodes_[x];
+  const uint64_t mask = (uint64_t)t.iarg[1];
+  int lo = -1, hi = -1;
+  for (int d = 0; d < xn.rank; ++d)
+    if ((mask >> d) & 1) { if (lo < 0) lo = d; hi = d; }
+  int64_t outer = 1, R = 1, inner = 1;
+  for (int d = 0; d < xn.rank; ++d) {
+    if (d < lo) outer *= xn.shape[d]; else if (d <= hi) R *= xn.shape[d]; else inner *= xn.shape[d];
+  }
+  own_slot(n);
+  const int in_slot = xv.slot, out_slot = view_[n].slot, in_dt = xv.dtype, out_dt = t.dtype, rop = (int)t.iarg[0];
+  const int64_t off_bytes = xv.off * dtype_size(xv.dtype);
+  PUnit pu;
+  pu.order_key = key;
+  pu.dep_nodes = {x};
+  pu.out_nodes = {n};
+  pu.u.name = "reduce[strided-axis]";
+  pu.u.fn = [=](Run& r) {
+    cudaError_t e = launch_reduce_generic(reinterpret_cast<char*>(r.ptr[in_slot]) + off_bytes, r.ptr[out_slot], in_dt, out_dt,
+                                          rop, outer, R, inner, r.ctx->stream);
+    return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "reduce launch");
+  };
+  add_unit(std::move(pu));
+}
+
+void Compiler::emit_generic_softmax(int n, int key) {
+  const Node& t = nodes_[n];
+  const int x = resolve(t.in[0]);
+  const View xv = view_[x];
+  const Node& xn = nodes_[x];
+  if (t.dtype != BG_F32 && t.dtype != BG_F64) err(BG_ERR_UNSUPPORTED, "FUSED_SOFTMAX: float32/float64 only");
+  if (xv.dtype != t.dtype) err(BG_ERR_UNSUPPORTED, "FUSED_SOFTMAX: input dtype differs from output dtype");
+  const int axis = (int)t.iarg[0];
+  int64_t outer = 1, R = xn.shape[axis], inner = 1;
+  for (int d = 0; d < axis; ++d) outer *= xn.shape[d];
+  for (int d = axis + 1; d < xn.rank; ++d) inner *= xn.shape[d];
+  own_slot(n);
+  const int in_slot = xv.slot, out_slot = view_[n].slot, dt = t.dtype;
+  const int64_t off_bytes = xv.off * dtype_size(xv.dtype);
+  PUnit pu;
+  pu.order_key = key;
+  pu.dep_nodes = {x};
+  pu.out_nodes = {n};
+  pu.u.name = "softmax[strided-axis]";
+  pu.u.fn = [=](Run& r) {
+    cudaError_t e = launch_softmax_generic(reinterpret_cast<char*>(r.ptr[in_slot]) + off_bytes, r.ptr[out_slot], dt, outer, R,
+                                           inner, r.ctx->stream);
+    return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "softmax launch");
+  };
+  add_unit(std::move(pu));
+}
+
+void Compiler::emit_matmul(int n, int key) {
+  const Node& t = nodes_[n];
+  if (t.in.size() != 2) err(BG_ERR_INVALID, "MATMUL: two inputs required");
+  const int a = resolve(t.in[0]), b = resolve(t.in[1]);
+  View av = view_[a], bv = view_[b];
+  if (av.is_const || bv.is_const) err(BG_ERR_UNSUPPORTED, "MATMUL with a scalar constant operand");
+  if (av.rank == 0 || bv.rank == 0) err(BG_ERR_INVALID, "MATMUL: 0-d operands");
+  // promote 1-D operands to matrices
+  bool a_vec = av.rank == 1, b_vec = bv.rank == 1;
+  if (a_vec) { av.rank = 2; av.shape[1] = av.shape[0]; av.stride[1] = av.stride[0]; av.shape[0] = 1; av.stride[0] = 0; }
+  if (b_vec) { bv.rank = 2; bv.shape[1] = 1; bv.stride[1] = 0; }
+  GemmProblem gp{};
+  gp.m = av.shape[av.rank - 2];
+  gp.k = av.shape[av.rank - 1];
+  gp.n = bv.shape[bv.rank - 1];
+  if (bv.shape[bv.rank - 2] != gp.k) err(BG_ERR_INVALID, "MATMUL: inner dimensions do not match");
+  gp.a.dtype = av.dtype;
+  gp.b.dtype = bv.dtype;
+  gp.a.row_stride = av.stride[av.rank - 2];
+  gp.a.col_stride = av.stride[av.rank - 1];
+  gp.b.row_stride = bv.stride[bv.rank - 2];
+  gp.b.col_stride = bv.stride[bv.rank - 1];
+  // batch dims: broadcast the leading dims, then collapse neighbours both operands walk densely
+  const int ba = av.rank - 2, bb = bv.rank - 2, nb = std::max(ba, bb);
+  std::vector<int64_t> bs, as, bsb;
+  for (int d = 0; d < nb; ++d) {
+    int ia = d - (nb - ba), ib = d - (nb - bb);
+    int64_t ea = ia >= 0 ? av.shape[ia] : 1, eb = ib >= 0 ? bv.shape[ib] : 1;
+    if (ea != eb && ea != 1 && eb != 1) err(BG_ERR_INVALID, "MATMUL: batch dimensions are not broadcastable");
+    int64_t e = std::max(ea, eb);
+    if (ea == 0 || eb == 0) e = 0;
+    int64_t sa = (ia >= 0 && ea != 1) ? av.stride[ia] : 0, sb = (ib >= 0 && eb != 1) ? bv.stride[ib] : 0;
+    if (e == 1) continue;
+    if (!bs.empty() && as.back() == sa * e && bsb.back() == sb * e) { bs.back() *= e; as.back() = sa; bsb.back() = sb; }
+    else { bs.push_back(e); as.push_back(sa); bsb.push_back(sb); }
+  }
+  if (bs.size() > 4) err(BG_ERR_UNSUPPORTED, "MATMUL: more than four non-collapsible batch dimensions");
+  gp.n_batch_dims = (int)bs.size();
+  int64_t nbatch = 1;
+  for (size_t d = 0; d < bs.size(); ++d) { gp.batch_shape[d] = bs[d]; gp.a.batch_stride[d] = as[d]; gp.b.batch_stride[d] = bsb[d]; nbatch *= bs[d]; }
+  if (t.numel() != nbatch * (a_vec ? 1 : gp.m) * (b_vec ? 1 : gp.n)) err(BG_ERR_INVALID, "MATMUL: declared shape does not match the operands");
+  gp.c_dtype = t.dtype;
+  own_slot(n);
+  const int sa = av.slot, sb = bv.slot, sc = view_[n].slot;
+  const int64_t offa = av.off * dtype_size(av.dtype), offb = bv.off * dtype_size(bv.dtype);
+  PUnit pu;
+  pu.order_key = key;
+  pu.dep_nodes = {a, b};
+  pu.out_nodes = {n};
+  pu.u.name = std::string("gemm_simt[") + dtype_name(t.dtype) + "]";
+  pu.u.fn = [=](Run& r) {
+    GemmProblem p = gp;
+    p.a.ptr = reinterpret_cast<char*>(r.ptr[sa]) + offa;
+    p.b.ptr = reinterpret_cast<char*>(r.ptr[sb]) + offb;
+    p.c = r.ptr[sc];
+    cudaError_t e = launch_gemm_simt(p, r.ctx->stream);
+    return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "gemm launch");
+  };
+  add_unit(std::move(pu));
+}
+
+void Compiler::emit_index(int n, int key) {
+  const Node& t = nodes_[n];
+  if (t.in.size() != 2) err(BG_ERR_INVALID, "INDEX: two inputs required");
+  const int x = resolve(t.in[0]), ix = resolve(t.in[1]);
+  const View xv = view_[x], iv = view_[ix];
+  if (iv.dtype != BG_I64) err(BG_ERR_INVALID, "INDEX: index dtype must be int64");
+  if (xv.rank != iv.rank || xv.rank == 0) err(BG_ERR_INVALID, "INDEX: source and index must have the same nonzero rank");
+  const int dim = (int)t.iarg[0];
+  if (dim < 0 || dim >= xv.rank) err(BG_ERR_INVALID, "INDEX: dimension out of range");
+  for (int d = 0; d < xv.rank; ++d)
+    if (d != dim && iv.shape[d] > xv.shape[d]) err(BG_ERR_INVALID, "INDEX: index extent exceeds source extent");
+  if (!xv.contiguous() || !iv.contiguous() || xv.is_const || iv.is_const) err(BG_ERR_UNSUPPORTED, "INDEX: operands must be dense tensors");
+  own_slot(n);
+  const int sx = xv.slot, si = iv.slot, so = view_[n].slot, es = dtype_size(xv.dtype), rank = xv.rank;
+  const int64_t offx = xv.off * es, offi = iv.off * 8;
+  std::vector<int64_t> xs(xv.shape, xv.shape + rank), is(iv.shape, iv.shape + rank);
+  cp_->uses_status = true;
+  PUnit pu;
+  pu.order_key = key;
+  pu.dep_nodes = {x, ix};
+  pu.out_nodes = {n};
+  pu.u.name = "gather[INDEX]";
+  pu.u.fn = [=](Run& r) {
+    cudaError_t e = launch_gather(reinterpret_cast<char*>(r.ptr[sx]) + offx,
+                                  reinterpret_cast<const int64_t*>(reinterpret_cast<char*>(r.ptr[si]) + offi), r.ptr[so], es, rank,
+                                  xs.data(), is.data(), dim, r.ctx->d_status, r.ctx->stream);
+    return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "gather launch");
+  };
+  add_unit(std::move(pu));
+}
+
+void Compiler::emit_ce(int n, int key) {
+  const Node& t = nodes_[n];
+  if (t.in.size() != 2) err(BG_ERR_UNSUPPORTED, "CROSS_ENTROPY: class weights are not supported");
+  const int x = resolve(t.in[0]), tg = resolve(t.in[1]);
+  const View xv = view_[x], tv = view_[tg];
+  if (tv.dtype != BG_I64) err(BG_ERR_UNSUPPORTED, "CROSS_ENTROPY: class-index (int64) targets only");
+  if (xv.dtype != BG_F32 && xv.dtype != BG_F64) err(BG_ERR_UNSUPPORTED, "CROSS_ENTROPY: float32/float64 logits only");
+  if (t.dtype != xv.dtype) err(BG_ERR_INVALID, "CROSS_ENTROPY: output dtype must equal the logits dtype");
+  if (!xv.contiguous() || !tv.contiguous() || xv.is_const || tv.is_const) err(BG_ERR_UNSUPPORTED, "CROSS_ENTROPY: operands must be dense tensors");
+  if (t.iarg[2] != 0) err(BG_ERR_UNSUPPORTED, "CROSS_ENTROPY: batch_rank must be 0");
+  const int reduction = (int)t.iarg[0];
+  const int64_t ignore = t.iarg[1];
+  int64_t outer, C, inner = 1;
+  if (xv.rank == 1) { outer = 1; C = xv.shape[0]; }
+  else { outer = xv.shape[0]; C = xv.shape[1]; for (int d = 2; d < xv.rank; ++d) inner *= xv.shape[d]; }
+  if (tv.numel() != outer * inner) err(BG_ERR_INVALID, "CROSS_ENTROPY: target shape does not match the logits");
+  if (C == 0) err(BG_ERR_INVALID, "CROSS_ENTROPY: empty class axis");
+  own_slot(n);
+  const int es = dtype_size(xv.dtype);
+  const int npos_slot = reduction == 0 ? view_[n].slot : new_slot(outer * inner * es, false, -1);
+  const int sx = xv.slot, st = tv.slot, so = view_[n].slot, dt = xv.dtype;
+  const int64_t offx = xv.off * es, offt = tv.off * 8, npos = outer * inner;
+  cp_->uses_status = true;
+  PUnit pu;
+  pu.order_key = key;
+  pu.dep_nodes = {x, tg};
+  pu.out_nodes = {n};
+  pu.u.name = "cross_entropy";
+  pu.u.launches = reduction == 0 ? 1 : 2;
+  if (npos_slot != so) pu.u.writes.push_back(npos_slot);
+  pu.u.fn = [=](Run& r) {
+    const int64_t* tp = reinterpret_cast<const int64_t*>(reinterpret_cast<char*>(r.ptr[st]) + offt);
+    cudaError_t e = launch_ce_rows(reinterpret_cast<char*>(r.ptr[sx]) + offx, tp, r.ptr[npos_slot], dt, outer, C, inner, ignore,
+                                   r.ctx->d_status, r.ctx->stream);
+    if (e == cudaSuccess && reduction != 0) e = launch_ce_reduce(r.ptr[npos_slot], tp, r.ptr[so], dt, npos, reduction, ignore, r.ctx->stream);
+    return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "cross entropy launch");
+  };
+  add_unit(std::move(pu));
+}
+
+bool Compiler::try_lower() {
+  cp_ = std::make_shared<CompiledPlan>();
+  punits_.clear();
+  nodes_.clear();
+  copy_src_.clear();
+  expand();
+  simplify();
+  build_views();
+  if (force_break_.size() != nodes_.size()) force_break_.assign(nodes_.size(), 0);
+  analyse();
+  const int nn = (int)nodes_.size();
+  // group membership lists in node order
+  std::map<int, std::vector<int>> groups;
+  for (int i = 0; i < nn; ++i)
+    if (kind_[i] == K_EW) groups[find(i)].push_back(i);
+  // only groups with a materialised member or a tail do any work
+  for (auto& kv : groups) {
+    const std::vector<int>& mem = kv.second;
+    bool live = tail_of_group_[kv.first] >= 0;
+    for (int m : mem) live |= need_mat_[m] != 0;
+    if (!live) continue;
+    try {
+      emit_group(mem, tail_of_group_[kv.first], mem.back());
+    } catch (CompileError& ce) {
+      if (ce.code != -1) throw;
+      // split: stop fusing through the middle member (or drop the tail) and recompile
+      if (tail_of_group_[kv.first] >= 0 && mem.size() <= 1) force_break_[mem[0]] = 1;
+      else if (tail_of_group_[kv.first] >= 0 && ce.msg.find("row does not fit") != std::string::npos) force_break_[resolve(nodes_[tail_of_group_[kv.first]].in[0])] = 1;
+      else if (mem.size() >= 2) force_break_[mem[mem.size() / 2 - 1]] = 1;
+      else err(BG_ERR_UNSUPPORTED, "elementwise group cannot be lowered: " + ce.msg);
+      return false;
+    }
+  }
+  for (int i = 0; i < nn; ++i) {
+    const Node& n = nodes_[i];
+    if (kind_[i] == K_ROW && attached_[i] < 0) {
+      int64_t rows, cols;
+      View xin;
+      bool trailing;
+      row_geometry(i, rows, cols, xin, trailing);
+      const int x = resolve(n.in[0]);
+      if (view_[x].is_const) err(BG_ERR_UNSUPPORTED, std::string(op_name(n.op)) + " of a scalar constant");
+      if (trailing) {
+        try {
+          emit_row_standalone(i, i);
+        } catch (CompileError& ce) {
+          if (ce.code != -1) throw;
+          if (n.op == BG_OP_FUSED_SOFTMAX && view_[x].contiguous()) emit_generic_softmax(i, i);
+          else err(BG_ERR_UNSUPPORTED, std::string(op_name(n.op)) + ": " + ce.msg);
+        }
+      } else if (n.op == BG_OP_FUSED_SOFTMAX) {
+        if (!view_[x].contiguous()) err(BG_ERR_UNSUPPORTED, "FUSED_SOFTMAX over a non-trailing axis of a strided view");
+        emit_generic_softmax(i, i);
+      } else {
+        const uint64_t mask = (uint64_t)n.iarg[1];
+        bool block = true;
+        int lo = -1, hi = -1;
+        for (int d = 0; d < nodes_[x].rank; ++d)
+          if ((mask >> d) & 1) { if (lo < 0) lo = d; hi = d; }
+        for (int d = lo; d <= hi && lo >= 0; ++d)
+          if (!((mask >> d) & 1)) block = false;
+        if (block && view_[x].contiguous()) emit_generic_reduce(i, i);
+        else {
+          // permute the view so that the reduced axes trail, then run the row kernel on it
+          View pv = view_[x];
+          View nv = pv;
+          int k = 0;
+          for (int d = 0; d < pv.rank; ++d)
+            if (!((mask >> d) & 1)) { nv.shape[k] = pv.shape[d]; nv.stride[k] = pv.stride[d]; ++k; }
+          for (int d = 0; d < pv.rank; ++d)
+            if ((mask >> d) & 1) { nv.shape[k] = pv.shape[d]; nv.stride[k] = pv.stride[d]; ++k; }
+          // temporarily present the permuted view as the input's view
+          const View saved = view_[x];
+          const Node saved_node = nodes_[x];
+          view_[x] = nv;
+          for (int d = 0; d < nv.rank; ++d) nodes_[x].shape[d] = nv.shape[d];
+          Node saved_r = nodes_[i];
+          uint64_t m2 = 0;
+          int kept = 0;
+          for (int d = 0; d < pv.rank; ++d) kept += !((mask >> d) & 1);
+          for (int d = kept; d < pv.rank; ++d) m2 |= 1ull << d;
+          nodes_[i].iarg[1] = (int64_t)m2;
+          try {
+            emit_row_standalone(i, i);
+          } catch (CompileError& ce) {
+            view_[x] = saved; nodes_[x] = saved_node; nodes_[i] = saved_r;
+            if (ce.code != -1) throw;
+            err(BG_ERR_UNSUPPORTED, "REDUCE: " + ce.msg);
+          }
+          view_[x] = saved;
+          nodes_[x] = saved_node;
+          nodes_[i] = saved_r;
+        }
+      }
+    } else if (kind_[i] == K_OTHER) {
+      switch (n.op) {
+        case BG_OP_MATMUL: emit_matmul(i, i); break;
+        case BG_OP_INDEX: emit_index(i, i); break;
+        case BG_OP_CROSS_ENTROPY: emit_ce(i, i); break;
+        case BG_OP_RESHAPE: emit_copy(i, copy_src_.at(i), resolve(n.in[0]), i); break;
+        default: err(BG_ERR_UNSUPPORTED, std::string("opcode ") + op_name(n.op));
+      }
+    }
+  }
+  // the root must be an owned dense buffer
+  {
+    int r = root_;
+    int rr = resolve(r);
+    const View& rv = view_[rr];
+    bool owned = !rv.is_const && rv.slot >= 0 && !cp_->slots[rv.slot].external && rv.contiguous() && rv.off == 0 &&
+                 cp_->slots[rv.slot].bytes == nodes_[rr].numel() * dtype_size(nodes_[rr].dtype);
+    if (!owned) {
+      if (rv.is_const) emit_const_fill(rr, nn);
+      else {
+        // copy through a synthetic RESHAPE-like node
+        Node c = nodes_[rr];
+        c.op = BG_OP_RESHAPE;
+        c.in = {rr};
+        nodes_.push_back(c);
+        kind_.push_back(K_OTHER);
+        View ov;
+        ov.set_dense(c.shape, c.rank);
+        ov.dtype = c.dtype;
+        ov.slot = new_slot(c.numel() * dtype_size(c.dtype), false, (int)nodes_.size() - 1);
+        view_.push_back(ov);
+        leaflike_.push_back(0);
+        const int id = (int)nodes_.size() - 1;
+        const View srcv = rv;
+        emit_copy(id, srcv, rr, nn);
+        rr = id;
+      }
+      root_ = rr;
+    } else {
+      root_ = rr;
+    }
+  }
+  return true;
+}
+
+void Compiler::schedule() {
+  const int nu = (int)punits_.size();
+  // node -> producing unit
+  std::map<int, int> prod;
+  for (int u = 0; u < nu; ++u)
+    for (int n : punits_[u].out_nodes) prod[n] = u;
+  auto storage_unit = [&](int n) -> int {
+    // follow views down to the node that owns the storage
+    int guard = 0;
+    while (guard++ < 100000) {
+      n = resolve(n);
+      auto it = prod.find(n);
+      if (it != prod.end()) return it->second;
+      if (kind_[n] == K_VIEW) { n = nodes_[n].in[0]; continue; }
+      return -1;
+    }
+    return -1;
+  };
+  std::vector<std::set<int>> deps(nu);
+  std::vector<std::vector<int>> users(nu);
+  for (int u = 0; u < nu; ++u)
+    for (int n : punits_[u].dep_nodes) {
+      int p = storage_unit(n);
+      if (p >= 0 && p != u && deps[u].insert(p).second) users[p].push_back(u);
+    }
+  std::vector<int> indeg(nu);
+  std::set<std::pair<int, int>> ready;
+  for (int u = 0; u < nu; ++u) {
+    indeg[u] = (int)deps[u].size();
+    if (!indeg[u]) ready.insert({punits_[u].order_key, u});
+  }
+  std::vector<int> order;
+  while (!ready.empty()) {
+    auto it = ready.begin();
+    int u = it->second;
+    ready.erase(it);
+    order.push_back(u);
+    for (int v : users[u])
+      if (--indeg[v] == 0) ready.insert({punits_[v].order_key, v});
+  }
+  if ((int)order.size() != nu) err(BG_ERR_INVALID, "plan has a dependency cycle between fusion groups");
+  // slots read / written per unit, lifetimes
+  for (int pos = 0; pos < nu; ++pos) {
+    PUnit& pu = punits_[order[pos]];
+    Unit u = pu.u;
+    for (int n : pu.dep_nodes) {
+      int s = view_[resolve(n)].slot;
+      if (s >= 0) u.reads.push_back(s);
+    }
+    for (int n : pu.out_nodes) {
+      int s = view_[n].slot;
+      if (s >= 0) u.writes.push_back(s);
+    }
+    for (int s : u.reads) {
+      Slot& sl = cp_->slots[s];
+      sl.last_unit = pos;
+    }
+    for (int s : u.writes) {
+      Slot& sl = cp_->slots[s];
+      if (sl.first_unit < 0) sl.first_unit = pos;
+      sl.last_unit = std::max(sl.last_unit, pos);
+    }
+    cp_->units.push_back(std::move(u));
+  }
+  const View& rv = view_[root_];
+  cp_->root_slot = rv.slot;
+  cp_->root_dtype = nodes_[root_].dtype;
+  cp_->root_rank = nodes_[root_].rank;
+  for (int d = 0; d < cp_->root_rank; ++d) cp_->root_shape[d] = nodes_[root_].shape[d];
+  cp_->root_bytes = nodes_[root_].numel() * dtype_size(nodes_[root_].dtype);
+  cp_->slots[cp_->root_slot].last_unit = nu;  // survives the plan
+  // logical peak over the schedule
+  int64_t live = 0, peak = 0;
+  for (auto& s : cp_->slots)
+    if (s.external) live += s.bytes;
+  peak = live;
+  for (int pos = 0; pos <= nu; ++pos) {
+    for (auto& s : cp_->slots)
+      if (!s.external && s.first_unit == pos) live += s.bytes;
+    peak = std::max(peak, live);
+    for (auto& s : cp_->slots)
+      if (!s.external && s.last_unit == pos && s.first_unit >= 0) live -= s.bytes;
+  }
+  cp_->plan_peak = peak;
+  std::ostringstream tr;
+  for (auto& u : cp_->units) tr << u.name << "\n";
+  cp_->trace = tr.str();
+}
+
+std::shared_ptr<CompiledPlan> Compiler::compile() {
+  for (int attempt = 0; attempt < 64; ++attempt) {
+    if (try_lower()) {
+      schedule();
+      return cp_;
+    }
+  }
+  err(BG_ERR_UNSUPPORTED, "plan could not be split into launchable fusion groups");
+}
+
+}  // namespace
+
+int run_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs, int n_inputs, void* out_host,
+             size_t out_nbytes, bg_handle* out_handle) {
+  if (!plan->steps || plan->n_steps <= 0) return fail(ctx, BG_ERR_INVALID, "run_tensor_plan: empty plan");
+  if (n_inputs > 0 && !inputs) return fail(ctx, BG_ERR_INVALID, "run_tensor_plan: null inputs");
+  cudaSetDevice(ctx->device);
+  uint64_t h = 1469598103934665603ull;
+  h = fnv1a(plan->steps, sizeof(bg_plan_step) * (size_t)plan->n_steps, h);
+  if (plan->n_ext > 0) h = fnv1a(plan->ext, sizeof(int32_t) * (size_t)plan->n_ext, h);
+  h = fnv1a(&plan->root_id, sizeof(int32_t), h);
+  std::shared_ptr<CompiledPlan> cp;
+  auto it = ctx->plan_cache.find(h);
+  if (it != ctx->plan_cache.end()) {
+    cp = it->second;
+    ctx->cache_hits++;
+  } else {
+    try {
+      Compiler c(ctx, plan);
+      cp = c.compile();
+    } catch (CompileError& ce) {
+      return fail(ctx, ce.code > 0 ? ce.code : BG_ERR_UNSUPPORTED, "run_tensor_plan: " + ce.msg);
+    }
+    if (ctx->plan_cache.size() > 256) ctx->plan_cache.clear();
+    ctx->plan_cache[h] = cp;
+    ctx->cache_misses++;
+  }
+  ctx->last_trace = cp->trace;
+  if (out_host && (int64_t)out_nbytes != cp->root_bytes)
+    return fail(ctx, BG_ERR_INVALID, "run_tensor_plan: destination holds " + std::to_string(out_nbytes) + " bytes, the root has " +
+                                         std::to_string(cp->root_bytes));
+  Run run;
+  run.ctx = ctx;
+  run.ptr.assign(cp->slots.size(), nullptr);
+  std::vector<std::pair<void*, int64_t>> temp_uploads;
+  std::vector<int> allocated;  // slots allocated by this run
+  auto cleanup = [&](bool keep_root) {
+    for (int s : allocated) {
+      if (keep_root && s == cp->root_slot) continue;
+      if (run.ptr[s]) dev_free(ctx, run.ptr[s], cp->slots[s].bytes);
+      run.ptr[s] = nullptr;
+    }
+    allocated.clear();
+    for (auto& t : temp_uploads) dev_free(ctx, t.first, t.second);
+    temp_uploads.clear();
+  };
+  // bind BUFFER steps
+  for (size_t b = 0; b < cp->buffers.size(); ++b) {
+    const int vid = cp->buffers[b].first, slot = cp->buffers[b].second;
+    const bg_plan_input* found = nullptr;
+    for (int i = 0; i < n_inputs; ++i)
+      if (inputs[i].value_id == vid) { found = &inputs[i]; break; }
+    if (!found) { cleanup(false); return fail(ctx, BG_ERR_INVALID, "run_tensor_plan: no input bound to BUFFER value_id " + std::to_string(vid)); }
+    const int64_t want = cp->buffer_bytes[b];
+    if (found->handle != 0) {
+      auto hit = ctx->handles.find(found->handle);
+      if (hit == ctx->handles.end()) { cleanup(false); return fail(ctx, BG_ERR_UNKNOWN_HANDLE, "run_tensor_plan: unknown handle " + std::to_string(found->handle)); }
+      if (hit->second.bytes != want) { cleanup(false); return fail(ctx, BG_ERR_INVALID, "run_tensor_plan: handle for value_id " + std::to_string(vid) + " holds " + std::to_string(hit->second.bytes) + " bytes, the plan declares " + std::to_string(want)); }
+      run.ptr[slot] = hit->second.ptr;
+    } else {
+      if ((int64_t)found->nbytes != want || (want > 0 && !found->data)) { cleanup(false); return fail(ctx, BG_ERR_INVALID, "run_tensor_plan: data for value_id " + std::to_string(vid) + " has " + std::to_string(found->nbytes) + " bytes, the plan declares " + std::to_string(want)); }
+      void* p = nullptr;
+      if (int rc = dev_alloc(ctx, want, &p)) { cleanup(false); return rc; }
+      temp_uploads.push_back({p, want});
+      if (int rc = h2d(ctx, p, found->data, (size_t)want)) { cleanup(false); return rc; }
+      run.ptr[slot] = p;
+    }
+  }
+  // execute
+  const int nu = (int)cp->units.size();
+  for (int pos = 0; pos < nu; ++pos) {
+    Unit& u = cp->units[pos];
+    for (int s : u.writes)
+      if (!run.ptr[s]) {
+        if (int rc = dev_alloc(ctx, cp->slots[s].bytes, &run.ptr[s])) { cleanup(false); return rc; }
+        allocated.push_back(s);
+      }
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (ctx->profiling) {
+      cudaEventCreate(&e0);
+      cudaEventCreate(&e1);
+      cudaEventRecord(e0, ctx->stream);
+    }
+    int rc = u.fn(run);
+    if (ctx->profiling) {
+      cudaEventRecord(e1, ctx->stream);
+      ctx->pending_events.push_back({u.name, {e0, e1}});
+    }
+    if (rc) { cleanup(false); return rc; }
+    ctx->launches += u.launches;
+    // free intermediates whose last reader this was
+    for (size_t k = 0; k < allocated.size();) {
+      int s = allocated[k];
+      if (cp->slots[s].last_unit == pos && s != cp->root_slot) {
+        dev_free(ctx, run.ptr[s], cp->slots[s].bytes);
+        run.ptr[s] = nullptr;
+        allocated[k] = allocated.back();
+        allocated.pop_back();
+      } else ++k;
+    }
+  }
+  if (cp->plan_peak > ctx->plan_peak) ctx->plan_peak = cp->plan_peak;
+  if (!run.ptr[cp->root_slot]) { cleanup(false); return fail(ctx, BG_ERR_INVALID, "run_tensor_plan: root was not produced"); }
+  int status_rc = BG_OK;
+  if (cp->uses_status) {
+    cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream);
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) { cleanup(false); return cuda_fail(ctx, e, "plan execution"); }
+    if (*ctx->h_status != 0) {
+      status_rc = *ctx->h_status;
+      cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
+    }
+  }
+  if (status_rc) {
+    cleanup(false);
+    return fail(ctx, status_rc, status_rc == BG_ERR_INDEX_RANGE ? "run_tensor_plan: gather / cross_entropy index outside its axis"
+                                                               : "run_tensor_plan: device-side status " + std::to_string(status_rc));
+  }
+  if (out_host) {
+    int rc = d2h(ctx, out_host, run.ptr[cp->root_slot], (size_t)cp->root_bytes);
+    cleanup(false);
+    return rc;
+  }
+  *out_handle = mint_handle(ctx, run.ptr[cp->root_slot], cp->root_bytes, cp->root_dtype, cp->root_shape, cp->root_rank);
+  cleanup(true);
+  return BG_OK;
+}
+
+}  // namespace bg
+
+extern "C" int bg_compile_plan_dry(const bg_plan* plan, int fusion, char* out, size_t capacity) {
+  // Host-only: compiles the plan into its launch list without touching a device.
+  if (!plan || !out || capacity == 0) return BG_ERR_INVALID;
+  bg_context fake;
+  fake.fusion = fusion != 0;
+  std::string text;
+  int rc = BG_OK;
+  try {
+    bg::Compiler c(&fake, plan);
+    auto cp = c.compile();
+    text = cp->trace;
+  } catch (bg::CompileError& ce) {
+    text = "error: " + ce.msg;
+    rc = ce.code > 0 ? ce.code : BG_ERR_UNSUPPORTED;
+  }
+  strncpy(out, text.c_str(), capacity - 1);
+  out[capacity - 1] = 0;
+  return rc;
+}
+

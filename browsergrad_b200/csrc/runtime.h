@@ -1,0 +1,69 @@
+// Host-side runtime of libbgcuda.so: context, handle table, stream-ordered allocator,
+// compiled-plan cache.  Internal to the library.
+#pragma once
+
+#include "common.h"
+
+namespace bg {
+
+struct HandleRec {
+  void* ptr = nullptr;
+  int64_t bytes = 0;       // logical bytes (numel * itemsize), what the accounting reports
+  int dtype = BG_F32;
+  std::vector<int64_t> shape;
+};
+
+struct CompiledPlan;
+
+struct ProfileAcc {
+  double ms = 0;
+  int launches = 0;
+};
+
+}  // namespace bg
+
+struct bg_context {
+  int device = 0;
+  int sm_count = 148;
+  cudaStream_t stream = nullptr;
+  std::string err;
+  std::unordered_map<int64_t, bg::HandleRec> handles;
+  int64_t next_handle = 1;
+  // byte accounting (logical bytes), mirrors the reference bridge's resource snapshot
+  int64_t cur_bytes = 0, peak_bytes = 0, total_alloc = 0, total_rel = 0, plan_peak = 0;
+  int64_t launches = 0, cache_hits = 0, cache_misses = 0;
+  // options
+  bool profiling = false;
+  int f64_mode = 2;
+  bool fusion = true;
+  bool tensor_cores = true;
+  // device status word written by kernels that can refuse (index range, bounded waits)
+  int* d_status = nullptr;
+  int* h_status = nullptr;  // pinned
+  // pinned staging for host <-> device copies
+  void* stage = nullptr;
+  size_t stage_bytes = 0;
+  std::unordered_map<uint64_t, std::shared_ptr<bg::CompiledPlan>> plan_cache;
+  std::map<std::string, bg::ProfileAcc> profile;
+  std::vector<std::pair<std::string, std::pair<cudaEvent_t, cudaEvent_t>>> pending_events;
+  std::string last_trace;
+};
+
+namespace bg {
+
+int fail(bg_context* ctx, int code, const std::string& msg);
+int cuda_fail(bg_context* ctx, cudaError_t e, const char* what);
+
+// Stream-ordered allocation with exact logical accounting.
+int dev_alloc(bg_context* ctx, int64_t logical_bytes, void** out);
+void dev_free(bg_context* ctx, void* p, int64_t logical_bytes);
+bg_handle mint_handle(bg_context* ctx, void* ptr, int64_t bytes, int dtype, const int64_t* shape, int rank);
+int h2d(bg_context* ctx, void* dst, const void* src, size_t n);
+int d2h(bg_context* ctx, void* dst, const void* src, size_t n);
+
+// Compile (or fetch from the cache) and run a plan.  When `out_host` is non-null the root is
+// copied to the host and the stream synchronised; otherwise a handle to the root is minted.
+int run_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs, int n_inputs, void* out_host,
+             size_t out_nbytes, bg_handle* out_handle);
+
+}  // namespace bg

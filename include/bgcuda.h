@@ -1,0 +1,209 @@
+/*
+ * bgcuda.h -- C ABI of the B200 (sm_100a) realizer bridge for browsergrad-jit.
+ *
+ * One bg_context is one bridge: the object `bg.register_webgpu_bridge(bridge)` stores
+ * (packages/browsergrad-jit/src/python/_realize_webgpu.py:628-636) and whose methods the
+ * realizers call (Protocol: packages/browsergrad-jit/src/python/_bridge.py:61-289; TypeScript
+ * interface: packages/browsergrad-kernels/src/realizer.ts:77-280).  Each entry point below
+ * names the bridge method it stands behind.  Host shims (Python ctypes, Node N-API) only
+ * translate argument encodings; all scheduling, fusion and memory management is in the
+ * library.
+ *
+ * Conventions
+ *  - every function returns a bg_status (0 = ok); on failure bg_last_error(ctx) holds a UTF-8
+ *    message prefixed "CUDA bridge: <op> ..."; nothing throws across the boundary;
+ *  - a context is used from one thread at a time (the reference bridge is never shared
+ *    between threads, realizer.ts:895-896); two contexts on one device are independent;
+ *  - handles are positive, minted from 1 upward and never reused (realizer.ts:907, :925);
+ *  - tensors are dense row-major little-endian, exactly the bytes of `ndarray.tobytes()`;
+ *  - all work of one context is ordered on one CUDA stream; calls that return bytes
+ *    synchronise that stream, calls that return handles do not.
+ */
+#ifndef BGCUDA_H
+#define BGCUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BG_MAX_RANK 8
+#define BG_MAX_STEP_INPUTS 8
+#define BG_ABI_VERSION 1
+
+typedef struct bg_context bg_context;
+typedef int64_t bg_handle;
+
+typedef enum bg_status {
+  BG_OK = 0,
+  BG_ERR_INVALID = 1,         /* malformed argument, shape/dtype/byte-length mismatch   */
+  BG_ERR_UNSUPPORTED = 2,     /* opcode or variant outside the forward path              */
+  BG_ERR_CUDA = 3,            /* a CUDA runtime/driver call failed                       */
+  BG_ERR_OOM = 4,             /* device allocation failed                                */
+  BG_ERR_UNKNOWN_HANDLE = 5,  /* handle was never minted or already released             */
+  BG_ERR_DEVICE_TIMEOUT = 6,  /* a bounded device-side wait ran out                      */
+  BG_ERR_INDEX_RANGE = 7      /* gather / cross-entropy index outside its axis           */
+} bg_status;
+
+/* dtype names of the IR (packages/browsergrad-jit/src/python/_ir.py:348-353) + bfloat16,
+ * which the reference does not have (extension used by the bf16 autocast path). */
+typedef enum bg_dtype {
+  BG_F16 = 0, BG_F32 = 1, BG_F64 = 2,
+  BG_I8 = 3, BG_I16 = 4, BG_I32 = 5, BG_I64 = 6,
+  BG_U8 = 7, BG_U16 = 8, BG_U32 = 9, BG_U64 = 10,
+  BG_BOOL = 11, BG_BF16 = 12
+} bg_dtype;
+
+/* Opcodes of the forward path (names as in _ir.py:203-247). */
+typedef enum bg_opcode {
+  BG_OP_BUFFER = 0, BG_OP_LOAD = 1, BG_OP_CONST = 2, BG_OP_CAST = 3,
+  BG_OP_ADD = 4, BG_OP_MUL = 5, BG_OP_DIV = 6, BG_OP_NEG = 7, BG_OP_EXP = 8, BG_OP_LOG = 9,
+  BG_OP_ABS = 10, BG_OP_SIGN = 11, BG_OP_SIN = 12, BG_OP_COS = 13, BG_OP_ISNAN = 14,
+  BG_OP_CMP = 15, BG_OP_WHERE = 16,
+  BG_OP_MATMUL = 17, BG_OP_REDUCE = 18, BG_OP_RESHAPE = 19, BG_OP_PERMUTE = 20,
+  BG_OP_BROADCAST_TO = 21, BG_OP_LAYER_NORM = 22, BG_OP_CROSS_ENTROPY = 23, BG_OP_INDEX = 24,
+  BG_OP_FUSED_ELEMENTWISE = 25, BG_OP_FUSED_SOFTMAX = 26, BG_OP_ATTENTION_FORWARD = 27,
+  BG_OP_COUNT = 28
+} bg_opcode;
+
+typedef enum bg_cmp { BG_CMP_EQ = 0, BG_CMP_NE = 1, BG_CMP_LT = 2, BG_CMP_LE = 3,
+                      BG_CMP_GT = 4, BG_CMP_GE = 5 } bg_cmp;
+typedef enum bg_reduce { BG_RED_SUM = 0, BG_RED_MAX = 1, BG_RED_MIN = 2, BG_RED_MEAN = 3,
+                         BG_RED_ARGMAX = 4, BG_RED_ARGMIN = 5, BG_RED_ANY = 6,
+                         BG_RED_ALL = 7 } bg_reduce;
+
+/*
+ * One scheduled step of a tensor plan: the C form of one entry of
+ * `GpuExecutionPlan.summary()["steps"]` (packages/browsergrad-jit/src/python/_gpu_plan.py:176-209).
+ * value ids equal step indices (webgpu_realizer.test.ts:1114-1161), inputs precede users.
+ * The live Python `arg` is flattened by the shim into iarg/farg/ext:
+ *   CONST            farg[0] = value as double; iarg[0] = value as int64 (integer/bool dtypes)
+ *   CAST             target dtype = .dtype
+ *   CMP              iarg[0] = bg_cmp
+ *   REDUCE           iarg[0] = bg_reduce; iarg[1] = bit mask of reduced input axes;
+ *                    iarg[2] = keepdims
+ *   PERMUTE          iarg[0..rank-1] = axes
+ *   FUSED_SOFTMAX    iarg[0] = axis (non-negative)
+ *   LAYER_NORM       iarg[0] = rows, iarg[1] = cols, farg[0] = eps
+ *   INDEX            iarg[0] = gather dimension
+ *   CROSS_ENTROPY    iarg[0] = 0 none / 1 mean / 2 sum; iarg[1] = ignore_index;
+ *                    iarg[2] = batch_rank (class-index targets, no weights, no smoothing)
+ *   ATTENTION_FORWARD farg[0] = scale
+ *   FUSED_ELEMENTWISE ext[ext_offset .. +3*ext_count) = (bg_opcode, lhs_ref, rhs_ref) triples;
+ *                    refs < 0 name input -ref-1, refs >= 0 an earlier triple
+ *                    (_fusion.py:184-232); rhs_ref = BG_REF_NONE for unary ops.
+ */
+#define BG_REF_NONE INT32_MIN
+
+typedef struct bg_plan_step {
+  int32_t op;       /* bg_opcode */
+  int32_t dtype;    /* bg_dtype of the step's value */
+  int32_t rank;
+  int32_t n_inputs;
+  int64_t shape[BG_MAX_RANK];
+  int32_t input_ids[BG_MAX_STEP_INPUTS];
+  int64_t iarg[BG_MAX_RANK];
+  double farg[2];
+  int32_t ext_offset;
+  int32_t ext_count;
+} bg_plan_step;
+
+typedef struct bg_plan {
+  const bg_plan_step* steps;
+  int32_t n_steps;
+  int32_t root_id;
+  const int32_t* ext;
+  int32_t n_ext;
+} bg_plan;
+
+/* Binding of one BUFFER step: an existing handle, or host bytes to upload for this run
+ * (`{value_id, handle}` | `{value_id, data}`, _realize_webgpu.py:490-519). */
+typedef struct bg_plan_input {
+  int32_t value_id;
+  int32_t reserved;
+  bg_handle handle;   /* 0 when `data` is given */
+  const void* data;
+  size_t nbytes;
+} bg_plan_input;
+
+/* Byte-exact accounting, the fields of `resourceSnapshot()` (realizer.ts:287-298). */
+typedef struct bg_resource_stats {
+  int64_t current_bytes;
+  int64_t peak_bytes;
+  int64_t total_allocated_bytes;
+  int64_t total_released_bytes;
+  int64_t alive_handles;
+  int64_t logical_tensor_plan_peak_bytes;
+  int64_t kernel_launches;      /* kernels of this library launched so far */
+  int64_t plan_cache_hits;
+  int64_t plan_cache_misses;
+} bg_resource_stats;
+
+/* One timed launch, the role of `DirectDispatchProfile` (runner.ts:409-507). */
+typedef struct bg_profile_entry {
+  char name[48];
+  float ms;
+  int32_t launches;
+} bg_profile_entry;
+
+/* -- lifecycle: createWebGpuRealizerBridge(device, {profiling}) (realizer.ts:902-1006) ---- */
+int bg_create(int device_ordinal, bg_context** out);
+int bg_destroy(bg_context* ctx);
+const char* bg_last_error(bg_context* ctx);
+int bg_abi_version(void);
+/* options: "profiling" (0/1), "f64_contraction" (0 = exact fp64 FMA, 1 = fp32-faithful tensor
+ * path, 2 = automatic: tensor path when no fp64 leaf enters the plan), "fusion" (0/1). */
+int bg_set_option(bg_context* ctx, const char* key, int64_t value);
+
+/* -- buffers: upload / materialize / release (_bridge.py:65-71; realizer.ts:1006-1041) ----- */
+int bg_upload(bg_context* ctx, const void* data, size_t nbytes, const int64_t* shape, int rank,
+              int dtype, bg_handle* out);
+int bg_materialize(bg_context* ctx, bg_handle h, void* out, size_t nbytes);
+int bg_release(bg_context* ctx, bg_handle h);     /* idempotent; unknown handle is a no-op */
+int bg_handle_nbytes(bg_context* ctx, bg_handle h, int64_t* out);
+
+/* -- per-op methods (_bridge.py:74-105; realizer.ts:1043-1151) --------------------------- */
+int bg_matmul(bg_context* ctx, bg_handle a, bg_handle b, int64_t m, int64_t k, int64_t n,
+              int dtype, bg_handle* out);
+int bg_fused_elementwise(bg_context* ctx, const bg_handle* inputs, int n_inputs,
+                         const int32_t* op_triples, int n_ops, const int64_t* shape, int rank,
+                         int dtype, bg_handle* out);
+int bg_cast(bg_context* ctx, bg_handle h, int src_dtype, int dst_dtype, const int64_t* shape,
+            int rank, bg_handle* out);
+/* mask = 0 for none, else an additive mask handle of shape mask_shape[4] = [B'|1,H'|1,Sq,Sk]
+ * (packages/browsergrad-kernels/src/kernels/flash_attention.ts:8-9). */
+int bg_flash_attention(bg_context* ctx, bg_handle q, bg_handle k, bg_handle v, bg_handle mask,
+                       const int64_t* mask_shape, int64_t b, int64_t h, int64_t sq, int64_t sk,
+                       int64_t d, double scale, int dtype, bg_handle* out);
+
+/* -- whole-plan methods: run_tensor_plan[_resident] (_bridge.py:262-289;
+ *    realizer.ts:1557-1652).  The *_semantic variants differ only in the shim, which checks
+ *    the dense-permutation-view-copy requests (_gpu_plan.py:668-734) and writes their axes
+ *    into the PERMUTE steps before calling these. -------------------------------------- */
+int bg_run_tensor_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs,
+                       int n_inputs, void* out_host, size_t out_nbytes);
+int bg_run_tensor_plan_resident(bg_context* ctx, const bg_plan* plan,
+                                const bg_plan_input* inputs, int n_inputs, bg_handle* out);
+
+/* -- diagnostics: aliveHandleCount / resourceSnapshot / flushProfiles
+ *    (realizer.ts:273-279, :287-298, :945-993) ------------------------------------------ */
+int bg_alive_handle_count(bg_context* ctx, int64_t* out);
+int bg_resource_snapshot(bg_context* ctx, bg_resource_stats* out);
+int bg_flush_profiles(bg_context* ctx, bg_profile_entry* out, int capacity, int* n_out);
+/* Text listing of the kernels the most recent plan compiled to, one per line. */
+int bg_last_plan_trace(bg_context* ctx, char* out, size_t capacity);
+/* Host-only diagnostic: compiles `plan` into its kernel list (one name per line) without a
+ * device or a context; `fusion` = 0 disables group formation.  Used to test the plan compiler
+ * on machines without a GPU. */
+int bg_compile_plan_dry(const bg_plan* plan, int fusion, char* out, size_t capacity);
+/* The CUDA stream all work of this context is ordered on (a cudaStream_t). */
+void* bg_stream(bg_context* ctx);
+/* Raw device pointer behind a handle, for callers that time kernels themselves. */
+int bg_device_pointer(bg_context* ctx, bg_handle h, void** out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BGCUDA_H */

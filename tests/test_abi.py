@@ -1,0 +1,125 @@
+"""CPU: the C-ABI library loads, exports every symbol ``include/bgcuda.h`` declares, refuses to
+create a context without a GPU, and its plan compiler lowers every parity case (dry run)."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from browsergrad_b200 import _lib, front, wire
+from browsergrad_b200.errors import JitNotImplementedError, KernelError
+from tests.cases import CASES
+from tests.util import build_case
+
+HEADER = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "bgcuda.h")
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(bg_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = declared_symbols()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in bgcuda.h but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert lib.bg_abi_version() == 1
+
+
+def test_struct_layout_matches_header():
+    assert C.sizeof(_lib.PlanStep) == 4 * 4 + 8 * 8 + 4 * 8 + 8 * 8 + 2 * 8 + 2 * 4
+    assert C.sizeof(_lib.PlanInput) == 32
+    assert C.sizeof(_lib.ResourceStats) == 72
+
+
+def dry(plan, fusion=1):
+    lib = _lib.load()
+    ep = wire.encode_plan(plan)
+    buf = C.create_string_buffer(1 << 16)
+    rc = lib.bg_compile_plan_dry(C.byref(ep.plan), fusion, buf, len(buf))
+    return rc, [ln for ln in buf.value.decode().split("\n") if ln]
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_plan_compiler_lowers_case(name):
+    t, store, _ = build_case(CASES[name])
+    _, plan = front.plan_for(t._uop)
+    rc, lines = dry(plan)
+    assert rc == 0, lines
+    assert lines
+    rc2, lines2 = dry(plan, fusion=0)
+    assert rc2 == 0, lines2
+    assert len(lines2) >= len(lines)
+
+
+def test_config2_chains_compile_to_one_kernel_each():
+    for name, kind in (("c2_y", "ew["), ("c2_rowsum", "row["), ("c2_rowsoftmax", "row[")):
+        t, _, _ = build_case(CASES[name])
+        _, plan = front.plan_for(t._uop)
+        rc, lines = dry(plan)
+        assert rc == 0 and len(lines) == 1 and lines[0].startswith(kind), lines
+
+
+def test_unsupported_opcode_mentions_numpy_fallback():
+    plan = {"step_count": 1, "root_id": 0, "steps": [
+        {"step": 0, "value_id": 0, "op": "CONV2D", "input_ids": [], "shape": [1], "dtype": "float32", "arg": None}]}
+    with pytest.raises(JitNotImplementedError, match=r"bg\.realize\(\)"):
+        wire.encode_plan(plan)
+
+
+def test_malformed_plans_are_refused():
+    t, _, _ = build_case(CASES["c2_y"])
+    _, plan = front.plan_for(t._uop)
+    bad = dict(plan, root_id=10 ** 6)
+    with pytest.raises(KernelError):
+        wire.encode_plan(bad)
+    bad = dict(plan, steps=[dict(s) for s in plan["steps"]])
+    bad["steps"][3]["value_id"] = 99
+    with pytest.raises(KernelError):
+        wire.encode_plan(bad)
+    # an input that does not precede its user is caught by the compiler
+    bad = dict(plan, steps=[dict(s) for s in plan["steps"]])
+    for s in bad["steps"]:
+        if s["op"] == "MUL":
+            s["input_ids"] = [len(bad["steps"]) - 1, s["input_ids"][1]]
+            break
+    rc, lines = dry(bad)
+    assert rc != 0 and "precede" in lines[0]
+
+
+def test_semantic_requests_validation():
+    from browsergrad_b200 import graph
+    import numpy as np
+    st = graph.BufferStore()
+    x = graph.from_numpy(np.zeros((3, 5), np.float32), st)
+    _, plan = front.plan_for(x.permute(1, 0)._uop)
+    vid = [s["value_id"] for s in plan["steps"] if s["op"] == "PERMUTE"][0]
+    import json
+    ok = {"schema": wire.SEMANTIC_SCHEMA, "version": {"major": 1, "minor": 0},
+          "requests": [{"kind": wire.VIEW_COPY_KIND, "valueId": vid, "inputShape": ["3", "5"], "axes": [1, 0],
+                        "dtype": "f32"}]}
+    assert wire.validate_semantic_requests(plan, json.dumps(ok)) == {vid: (1, 0)}
+    for mutate in (lambda d: d.update(schema="x"), lambda d: d["requests"][0].update(axes=[0, 0]),
+                   lambda d: d["requests"][0].update(inputShape=["5", "3"]),
+                   lambda d: d["requests"][0].update(valueId=0)):
+        bad = json.loads(json.dumps(ok))
+        mutate(bad)
+        with pytest.raises(KernelError):
+            wire.validate_semantic_requests(plan, json.dumps(bad))
+
+
+def test_no_gpu_means_loud_failure():
+    import ctypes
+    lib = _lib.load()
+    ctx = ctypes.c_void_p()
+    rc = lib.bg_create(0, ctypes.byref(ctx))
+    if rc == 0:
+        lib.bg_destroy(ctx)
+        pytest.skip("a GPU is present")
+    from browsergrad_b200 import CudaBridge
+    with pytest.raises(KernelError, match="no CPU fallback"):
+        CudaBridge(0)

@@ -1,0 +1,40 @@
+"""GPU: every parity case through the C ABI (``realize_cuda`` -> ``bg_run_tensor_plan``) against
+the CPU oracle on the same seeded inputs, and against the committed golden vectors.
+
+Tolerances: bit-exact for integer / bool / index / copy cases (``kind == "exact"``);
+max|diff| / max|ref| <= 1e-5 for fp32 and fp64 graphs; <= 2e-2 for the f16 / bf16 autocast path;
+the per-case value is ``Case.rtol``.
+"""
+import numpy as np
+import pytest
+
+from browsergrad_b200 import realize_cuda
+from tests.cases import CASES
+from tests.util import build_case, check, golden, oracle_value
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_case_matches_oracle_and_golden(bridge, name):
+    case = CASES[name]
+    t, store, _ = build_case(case)
+    want = oracle_value(t, store)
+    got = realize_cuda(t, bridge)
+    check(case, got, want, name + " vs oracle")
+    if case.reference_has_it:
+        check(case, got, golden()[name], name + " vs golden")
+    assert bridge.aliveHandleCount() == 0
+
+
+@pytest.mark.parametrize("name", ["c2_y", "c2_rowsoftmax", "c3_linear_gelu", "c4_attn_mask", "c5_gpt_tiny", "int_arith"])
+def test_unfused_execution_matches_too(bridge, name):
+    case = CASES[name]
+    t, store, _ = build_case(case)
+    want = oracle_value(t, store)
+    bridge.set_option("fusion", 0)
+    try:
+        got = realize_cuda(t, bridge)
+    finally:
+        bridge.set_option("fusion", 1)
+    check(case, got, want, name + " (fusion off)")

@@ -1,0 +1,60 @@
+"""Helpers shared by the parity tests."""
+from __future__ import annotations
+
+import os
+from typing import Any, Dict, Tuple
+
+import numpy as np
+
+from browsergrad_b200 import graph, passes
+from oracle import port
+from tests.cases import CASES, Case
+
+GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+_GOLDEN = None
+
+
+def golden() -> Any:
+    global _GOLDEN
+    if _GOLDEN is None:
+        _GOLDEN = np.load(os.path.join(GOLDEN_DIR, "outputs.npz"))
+    return _GOLDEN
+
+
+def build_case(case: Case) -> Tuple[Any, graph.BufferStore, Dict[str, np.ndarray]]:
+    raw = case.inputs()
+    store = graph.BufferStore()
+    t = {k: graph.from_numpy(v, store) for k, v in raw.items() if not k.startswith("_")}
+    return case.build(graph, t, raw), store, raw
+
+
+def oracle_value(tensor: Any, store: graph.BufferStore) -> np.ndarray:
+    return port.realize(passes.prepare(tensor._uop), store)
+
+
+def rel_err(got: np.ndarray, want: np.ndarray) -> float:
+    """max |got - want| / max |want| over the tensor (0 for empty tensors); non-finite entries
+    must match exactly."""
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    if want.size == 0:
+        return 0.0
+    fin = np.isfinite(want)
+    if not np.array_equal(fin, np.isfinite(got)):
+        return float("inf")
+    if not np.array_equal(got[~fin], want[~fin], equal_nan=True):
+        return float("inf")
+    if not fin.any():
+        return 0.0
+    scale = max(float(np.max(np.abs(want[fin]))), 1e-30)
+    return float(np.max(np.abs(got[fin] - want[fin]))) / scale
+
+
+def check(case: Case, got: np.ndarray, want: np.ndarray, name: str) -> None:
+    assert got.shape == want.shape, f"{name}: shape {got.shape} != {want.shape}"
+    assert got.dtype == want.dtype, f"{name}: dtype {got.dtype} != {want.dtype}"
+    if case.kind == "exact":
+        assert got.tobytes() == want.tobytes(), f"{name}: not bit-exact"
+    else:
+        e = rel_err(got, want)
+        assert e <= case.rtol, f"{name}: rel err {e:.3e} > {case.rtol:.1e}"
