@@ -1,0 +1,319 @@
+"""Benchmark of the realizer-bridge forward hot path on B200.
+
+Workload (``config.workload``): configuration 2 of the baseline, the fused elementwise/reduce
+chains over fp32 [16384, 4096] tensors -- one step = three realizations through the bridge,
+``y = relu(a*b+c)*exp(-d)``, ``y.sum(-1)`` and ``softmax(y, -1)`` -- on seeded N(0,1) inputs.
+``value`` is algorithmic HBM GB/s with the inputs already resident in HBM; ``e2e`` is the same
+metric through ``realize_cuda`` with pinned host buffers (host<->device copies inside the timed
+region).  Algorithmic bytes per step: (4 reads + 1 write) * 4 B * R*C for y and for the softmax,
+4 reads * 4 B * R*C + 4 B * R for the row sum.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Under torchrun every rank runs its own shard of the same size (weak scaling, no data-path
+collective); the timed region is bracketed by a barrier + synchronize and the slowest rank's
+device time is used.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+ROWS, COLS = 16384, 4096
+METRIC = "fused-eltwise HBM GB/s, GEMM TFLOP/s, attention tok/s at 1/2/4/8 B200 vs roofline"
+
+
+def algorithmic_bytes(rows: int, cols: int) -> dict:
+    rc = rows * cols
+    return {"y": 20 * rc, "rowsum": 16 * rc + 4 * rows, "rowsoftmax": 20 * rc}
+
+
+def measured_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            d = json.load(fh)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d.get("bf16_tflops", 1590.0)), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop_evt = threading.Event()
+
+    def run(self) -> None:
+        while not self._stop_evt.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
+                parts = [p.strip() for p in out.split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(float(parts[0]))
+                    self.max_mhz = float(parts[1])
+                    for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:6]):
+                        if val.lower().startswith("active"):
+                            self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop_evt.wait(0.1)
+
+    def stop(self) -> dict:
+        self._stop_evt.set()
+        self.join(timeout=6)
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def build_graphs(graph, configs, arrays):
+    store = graph.BufferStore()
+    t = {k: graph.from_numpy(v, store) for k, v in arrays.items()}
+    return store, t, {"y": configs.chain_y(graph, t), "rowsum": configs.chain_rowsum(graph, t),
+                      "rowsoftmax": configs.chain_rowsoftmax(graph, t)}
+
+
+def cpu_reference_realize():
+    """Returns (kind, realize(build, arrays) -> seconds).  Uses the unmodified reference realizer
+    when ``oracle/_ref`` travelled with the tree, else the NumPy restatement in ``oracle/port.py``."""
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    if os.path.isdir(os.path.join(ref_dir, "browsergrad_jit")):
+        sys.path.insert(0, ref_dir)
+        try:
+            import browsergrad_jit as bg
+            from tests.cases import RefApi
+            api = RefApi(bg)
+
+            def run(arrays):
+                from browsergrad_b200 import configs
+                t = {k: bg.from_numpy(v) for k, v in arrays.items()}
+                t0 = time.perf_counter()
+                configs.chain_y(api, t).numpy()
+                configs.chain_rowsum(api, t).numpy()
+                configs.chain_rowsoftmax(api, t).numpy()
+                return time.perf_counter() - t0
+            return "reference", run
+        except Exception:
+            pass
+    from browsergrad_b200 import configs, graph, passes
+    from oracle import port
+
+    def run(arrays):
+        store, t, roots = build_graphs(graph, configs, arrays)
+        prepared = {k: passes.prepare(v._uop) for k, v in roots.items()}
+        t0 = time.perf_counter()
+        for k in ("y", "rowsum", "rowsoftmax"):
+            port.realize(prepared[k], store)
+        return time.perf_counter() - t0
+    return "port", run
+
+
+def cpu_baseline(sample_rows: int, repeats: int = 1) -> dict:
+    from browsergrad_b200 import configs
+    kind, run = cpu_reference_realize()
+    arrays = configs.chain_inputs(sample_rows, COLS)
+    run(arrays)  # warm-up
+    best = min(run(arrays) for _ in range(max(1, repeats)))
+    nbytes = sum(algorithmic_bytes(sample_rows, COLS).values())
+    return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": kind,
+            "sample": f"{sample_rows} of {ROWS} rows x {COLS} cols, all three realizations, NumPy {np.__version__}, "
+                      f"best of {max(1, repeats)} after 1 warm-up",
+            "seconds": best}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample_rows = 1024
+    per_step = []
+    kind, run = cpu_reference_realize()
+    from browsergrad_b200 import configs
+    arrays = configs.chain_inputs(sample_rows, COLS)
+    for _ in range(args.warmup):
+        run(arrays)
+    for _ in range(args.steps):
+        per_step.append(run(arrays))
+    total = sum(per_step)
+    nbytes = sum(algorithmic_bytes(sample_rows, COLS).values())
+    value = nbytes * args.steps / total / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"config 2: fused elementwise/reduce chains y, row-sum, row-softmax over fp32 [{ROWS},{COLS}]",
+                   "sample": f"{sample_rows} rows per step on the host cores"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": os.cpu_count(), "kind": kind,
+                         "sample": f"{sample_rows} of {ROWS} rows x {COLS} cols per step, NumPy {np.__version__}"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="cuda")
+    ap.add_argument("--rows", type=int, default=ROWS)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from browsergrad_b200 import CudaBridge, configs, front, graph, realize_cuda
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rows = args.rows
+    bytes_step = algorithmic_bytes(rows, COLS)
+    total_bytes = sum(bytes_step.values())
+
+    bridge = CudaBridge(local)
+    stream = torch.cuda.ExternalStream(bridge.stream(), device=local)
+    arrays = configs.chain_inputs(rows, COLS)   # every rank: its own shard of the same size (weak scaling)
+    if world > 1:
+        for k in arrays:  # distinct data per rank
+            arrays[k] = np.roll(arrays[k], rank, axis=0)
+    store, t, roots = build_graphs(graph, configs, arrays)
+    table = front.DeviceBufferTable(bridge)
+    plans = {}
+    for name, root in roots.items():
+        prepared, plan = front.plan_for(root._uop)
+        inputs = front._bind_inputs(plan, store, table, True)   # uploads the leaves once
+        plans[name] = (plan, inputs, prepared.dtype)
+
+    def step() -> None:
+        for name in ("y", "rowsum", "rowsoftmax"):
+            plan, inputs, dtype = plans[name]
+            h = bridge.run_tensor_plan_resident(plan, inputs, dtype)
+            bridge.release(h)
+
+    def barrier() -> None:
+        if world > 1:
+            dist.barrier()
+        bridge.synchronize()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    bridge.synchronize()
+    bridge.flushProfiles()
+    bridge.set_option("profiling", 1)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = bridge.resourceSnapshot()["kernelLaunches"]
+    ev0.record(stream)
+    for _ in range(args.steps):
+        step()
+    ev1.record(stream)
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    launches = bridge.resourceSnapshot()["kernelLaunches"] - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    profiles = bridge.flushProfiles()
+    bridge.set_option("profiling", 0)
+    if world > 1:
+        tms = torch.tensor([ms], device=f"cuda:{local}")
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = float(tms.item())
+    value = world * total_bytes * args.steps / (ms * 1e-3) / 1e9
+
+    # roofline of the dominant kernel, from the CUDA events recorded around each launch above
+    peaks = measured_peaks()
+    per_kernel = {}
+    for p in profiles:
+        key = "rowsoftmax" if "FUSED_SOFTMAX" in p["name"] else ("rowsum" if "REDUCE" in p["name"] else "y")
+        per_kernel[key] = {"name": p["name"], "ms": p["ms"] / max(p["launches"], 1), "launches": p["launches"]}
+    roofline = None
+    if per_kernel:
+        top = max(per_kernel, key=lambda k: per_kernel[k]["ms"])
+        achieved = bytes_step[top] / (per_kernel[top]["ms"] * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": per_kernel[top]["name"], "achieved": achieved, "peak": peaks["hbm_gbs"],
+                    "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "traffic": None,
+                    "per_kernel": {k: {"name": v["name"], "ms_per_launch": v["ms"],
+                                       "achieved_gbs": bytes_step[k] / (v["ms"] * 1e-3) / 1e9,
+                                       "frac": bytes_step[k] / (v["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+                                   for k, v in per_kernel.items()}}
+
+    # end to end: pinned host inputs -> device -> kernels -> host result, through realize_cuda
+    e2e = None
+    if not args.no_e2e:
+        pinned = {k: torch.from_numpy(v).pin_memory().numpy() for k, v in arrays.items()}
+        pstore, pt, proots = build_graphs(graph, configs, pinned)
+        h2d = 3 * sum(v.nbytes for v in pinned.values())
+        d2h = rows * COLS * 4 * 2 + rows * 4
+
+        def e2e_step() -> None:
+            for name in ("y", "rowsum", "rowsoftmax"):
+                realize_cuda(proots[name], bridge)
+        e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        n_e2e = max(2, min(args.steps, 5))
+        for _ in range(n_e2e):
+            e2e_step()
+        barrier()
+        dt = time.perf_counter() - t0
+        if world > 1:
+            tdt = torch.tensor([dt], device=f"cuda:{local}")
+            dist.all_reduce(tdt, op=dist.ReduceOp.MAX)
+            dt = float(tdt.item())
+        e2e = {"value": world * total_bytes * n_e2e / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "steps": n_e2e, "ms_per_step": 1e3 * dt / n_e2e}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_baseline(1024, repeats=2)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"config 2: fused elementwise/reduce chains y, row-sum, row-softmax over fp32 [{rows},{COLS}] per GPU",
+                       "algorithmic_bytes_per_step": total_bytes, "l2": "inputs (4 x 268 MB) exceed the 126 MB L2",
+                       "parallelism": f"row-sharded x{world}, no collective"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+        }
+        print(json.dumps(line))
+    table.release_all()
+    bridge.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -74,6 +74,13 @@ static int ensure_stage(bg_context* ctx) {
   return BG_OK;
 }
 
+static bool is_pinned(const void* p) {
+  cudaPointerAttributes attr;
+  cudaError_t e = cudaPointerGetAttributes(&attr, p);
+  if (e != cudaSuccess) { cudaGetLastError(); return false; }
+  return attr.type == cudaMemoryTypeHost;
+}
+
 int h2d(bg_context* ctx, void* dst, const void* src, size_t n) {
   if (n == 0) return BG_OK;
   if (n <= (64u << 10)) {
@@ -81,6 +88,12 @@ int h2d(bg_context* ctx, void* dst, const void* src, size_t n) {
     if (e != cudaSuccess) return cuda_fail(ctx, e, "upload copy");
     // pageable source: the runtime has staged it before returning
     return BG_OK;
+  }
+  if (is_pinned(src)) {
+    // page-locked caller memory: one DMA straight from the caller's buffer
+    cudaError_t e = cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    return e == cudaSuccess ? BG_OK : cuda_fail(ctx, e, "upload copy");
   }
   if (int rc = ensure_stage(ctx)) return rc;
   cudaEvent_t ev[2];
@@ -114,6 +127,11 @@ int d2h(bg_context* ctx, void* dst, const void* src, size_t n) {
     return e == cudaSuccess ? BG_OK : cuda_fail(ctx, e, "stream synchronize");
   }
   if (n <= (64u << 10)) {
+    cudaError_t e = cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    return e == cudaSuccess ? BG_OK : cuda_fail(ctx, e, "materialize copy");
+  }
+  if (is_pinned(dst)) {
     cudaError_t e = cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToHost, ctx->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
     return e == cudaSuccess ? BG_OK : cuda_fail(ctx, e, "materialize copy");
