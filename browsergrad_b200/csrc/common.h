@@ -49,8 +49,18 @@ enum EwOp : uint8_t {
   E_NARROW,     // dst <- round/wrap a to the storage dtype in aux (f16, bf16, i8..u32, bool)
   E_AND, E_OR,  // bool arithmetic (NumPy: bool*bool = and, bool+bool = or)
   E_STORE,      // outputs[aux] <- a
+  // fp32 super-instructions formed by the compiler's peephole pass
+  E_SUB,        // dst <- a - b            (ADD of a NEG)
+  E_RELU,       // dst <- a > 0 ? a : +0   (CONST 0, CMP gt, WHERE)
+  E_EXPNEG,     // dst <- exp(-a)          (NEG, EXP)
   E_OPCOUNT
 };
+
+// Register fields of fp32 instructions may name global memory directly instead of a shared-memory
+// register: a source 0x80|k reads input k (dense fp32, vector-aligned) at the element's own linear
+// index, a destination 0x80|k writes output k.  The compiler folds single-use LOADs and final
+// STOREs this way, so a value that is consumed once never round-trips through shared memory.
+constexpr uint8_t kEwDirect = 0x80;
 
 struct EwInstr {
   uint8_t op, type, dst, a, b, c;

@@ -31,11 +31,27 @@ constexpr int kChunk = kBlock * kVec;  // 1024 elements
 // Register file access
 // ------------------------------------------------------------------------------------
 struct RegFile {
-  char* base;
-  int U;       // chunks per pass
-  int planes;  // 1 (4-byte classes only) or 2
+  char* tbase;       // shared-memory base of this thread's slots
+  int U;             // chunks per pass
+  uint32_t rstride;  // bytes between registers
+  uint32_t ustride;  // bytes between chunks of one register
+  __device__ __forceinline__ RegFile(char* base, int U_, int planes)
+      : tbase(base + threadIdx.x * 16), U(U_), rstride((uint32_t)U_ * planes * (kBlock * 16)),
+        ustride((uint32_t)planes * (kBlock * 16)) {}
   __device__ __forceinline__ char* slot(int r, int u, int h) const {
-    return base + ((size_t)((r * U + u) * planes + h) * kBlock + threadIdx.x) * 16;
+    return tbase + (uint32_t)r * rstride + (uint32_t)u * ustride + (uint32_t)h * (kBlock * 16);
+  }
+};
+
+// Position of a pass: chunk u starts at linear index idx0 + u * kChunk (lane 0 of this thread);
+// elements at or beyond `end` (tensor end, or row end in row mode) do not exist.
+struct Pos {
+  int64_t idx0;
+  int64_t end;
+  __device__ __forceinline__ int64_t idx(int u) const { return idx0 + (int64_t)u * kChunk; }
+  __device__ __forceinline__ int nvalid(int u) const {
+    int64_t left = end - idx(u);
+    return left >= 4 ? 4 : (left > 0 ? (int)left : 0);
   }
 };
 
@@ -141,8 +157,8 @@ struct ChunkPos {
 };
 
 // Offsets of the 4 lanes of a strided operand.
-__device__ __forceinline__ void strided_offsets(const EwProgram& p, const EwOperand& o, int64_t idx, int nvalid,
-                                                int64_t off[4]) {
+__device__ __noinline__ void strided_offsets(const EwProgram& p, const EwOperand& o, int64_t idx, int nvalid,
+                                             int64_t off[4]) {
   const int nd = p.ndim;
   const int64_t last = p.shape[nd - 1];
   if ((last & 3) == 0) {
@@ -173,8 +189,9 @@ __device__ __forceinline__ void strided_offsets(const EwProgram& p, const EwOper
   }
 }
 
-__device__ __forceinline__ void do_load(const EwProgram& p, const EwInstr& ins, const RegFile& rf, int u,
-                                        const ChunkPos& cp) {
+// General load of one chunk: any dtype, any addressing mode, partial chunks.
+__device__ __noinline__ void load_chunk(const EwProgram& p, const EwInstr ins, const RegFile rf, int u, ChunkPos cp) {
+  if (cp.nvalid == 0) return;
   const EwOperand& o = p.inputs[ins.aux];
   int64_t off[4];
   bool vec = false;
@@ -246,8 +263,8 @@ __device__ __forceinline__ void do_load(const EwProgram& p, const EwInstr& ins, 
   }
 }
 
-__device__ __forceinline__ void do_store(const EwProgram& p, const EwInstr& ins, const RegFile& rf, int u,
-                                         const ChunkPos& cp) {
+// General store of one chunk.
+__device__ __noinline__ void store_chunk(const EwProgram& p, const EwInstr ins, const RegFile rf, int u, ChunkPos cp) {
   if (cp.nvalid <= 0) return;
   const EwOutput& o = p.outputs[ins.aux];
   const int dt = o.dtype;
@@ -336,93 +353,202 @@ __device__ __forceinline__ double fadd(double a, double b) { return __dadd_rn(a,
 __device__ __forceinline__ double fmul(double a, double b) { return __dmul_rn(a, b); }
 __device__ __forceinline__ double fdiv(double a, double b) { return __ddiv_rn(a, b); }
 
-template <typename T>
-__device__ __forceinline__ void float_instr(const EwInstr& ins, const RegFile& rf, int u) {
-  V4<T> a = rget<T>(rf, ins.a, u), r;
-  switch (ins.op) {
-    case E_ADD: { V4<T> b = rget<T>(rf, ins.b, u);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = fadd(a.v[e], b.v[e]); break; }
-    case E_MUL: { V4<T> b = rget<T>(rf, ins.b, u);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = fmul(a.v[e], b.v[e]); break; }
-    case E_DIV: { V4<T> b = rget<T>(rf, ins.b, u);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = fdiv(a.v[e], b.v[e]); break; }
-    case E_NEG:
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = -a.v[e];
-      break;
-    case E_EXP:
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = f_exp<T>(a.v[e]);
-      break;
-    case E_LOG:
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = f_log<T>(a.v[e]);
-      break;
-    case E_ABS:
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = a.v[e] < 0 ? -a.v[e] : (a.v[e] == 0 ? T(0) : a.v[e]);
-      break;
-    case E_SIGN:
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = a.v[e] != a.v[e] ? a.v[e] : T((a.v[e] > 0) - (a.v[e] < 0));
-      break;
-    case E_SIN:
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = f_sin<T>(a.v[e]);
-      break;
-    default:  // E_COS
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = f_cos<T>(a.v[e]);
-      break;
+// The opcode switch sits outside the chunk loop: one decode per instruction per pass, then the
+// same operation over all U chunks (unrolled when UT > 0).
+#define BG_FOR_U _Pragma("unroll") for (int u = 0; u < nU; ++u)
+#define BG_UNARY(T, EXPR)                                   \
+  BG_FOR_U {                                                \
+    V4<T> a = rget<T>(rf, ins.a, u), r;                     \
+    _Pragma("unroll") for (int e = 0; e < 4; ++e) { const T x = a.v[e]; r.v[e] = (EXPR); } \
+    rput<T>(rf, ins.dst, u, r);                             \
   }
-  rput<T>(rf, ins.dst, u, r);
-}
-
-__device__ __forceinline__ void int_instr(const EwInstr& ins, const RegFile& rf, int u) {
-  V4<long long> a = rget<long long>(rf, ins.a, u), r;
-  switch (ins.op) {
-    case E_ADD: { V4<long long> b = rget<long long>(rf, ins.b, u);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = (long long)((unsigned long long)a.v[e] + (unsigned long long)b.v[e]); break; }
-    case E_MUL: { V4<long long> b = rget<long long>(rf, ins.b, u);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = (long long)((unsigned long long)a.v[e] * (unsigned long long)b.v[e]); break; }
-    case E_DIV: { V4<long long> b = rget<long long>(rf, ins.b, u);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = (long long)((double)a.v[e] / (double)b.v[e]); break; }
-    case E_NEG:
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = (long long)(0ull - (unsigned long long)a.v[e]);
-      break;
-    case E_ABS:
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = a.v[e] < 0 ? (long long)(0ull - (unsigned long long)a.v[e]) : a.v[e];
-      break;
-    default:  // E_SIGN
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = (a.v[e] > 0) - (a.v[e] < 0);
-      break;
+#define BG_BINARY(T, EXPR)                                  \
+  BG_FOR_U {                                                \
+    V4<T> a = rget<T>(rf, ins.a, u), b = rget<T>(rf, ins.b, u), r; \
+    _Pragma("unroll") for (int e = 0; e < 4; ++e) { const T x = a.v[e]; const T y = b.v[e]; r.v[e] = (EXPR); } \
+    rput<T>(rf, ins.dst, u, r);                             \
   }
-  rput<long long>(rf, ins.dst, u, r);
+
+// fp32 operand fetch / result store with the direct-global encoding (kEwDirect).
+__device__ __forceinline__ V4<float> getf(const EwProgram& p, const RegFile& rf, const Pos& pos, int r, int u) {
+  if (r & kEwDirect) {
+    const float* src = reinterpret_cast<const float*>(p.inputs[r & 0x7f].ptr) + pos.idx(u);
+    const int nv = pos.nvalid(u);
+    if (nv == 4) {
+      float4 t = __ldg(reinterpret_cast<const float4*>(src));
+      return {{t.x, t.y, t.z, t.w}};
+    }
+    V4<float> x;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) x.v[e] = e < nv ? src[e] : 0.f;
+    return x;
+  }
+  return rget<float>(rf, r, u);
+}
+__device__ __forceinline__ void putf(const EwProgram& p, const RegFile& rf, const Pos& pos, int r, int u, const V4<float>& x) {
+  if (r & kEwDirect) {
+    float* dst = reinterpret_cast<float*>(p.outputs[r & 0x7f].ptr) + pos.idx(u);
+    const int nv = pos.nvalid(u);
+    if (nv == 4) {
+      *reinterpret_cast<float4*>(dst) = make_float4(x.v[0], x.v[1], x.v[2], x.v[3]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (e < nv) dst[e] = x.v[e];
+    }
+    return;
+  }
+  rput<float>(rf, r, u, x);
 }
 
-template <typename T> __device__ __forceinline__ void where_instr(const EwInstr& ins, const RegFile& rf, int u) {
-  V4<uint32_t> c = rget<uint32_t>(rf, ins.a, u);
-  V4<T> x = rget<T>(rf, ins.b, u), y = rget<T>(rf, ins.c, u), r;
+template <int UT, typename F>
+__device__ __forceinline__ void f32_unary(const EwProgram& p, const EwInstr ins, const RegFile& rf, const Pos& pos, F f) {
+  constexpr int N = UT > 0 ? UT : 1;
+  if (UT > 0) {
+    // fetch every chunk first: independent global / shared loads are in flight together
+    V4<float> a[N];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) r.v[e] = c.v[e] ? x.v[e] : y.v[e];
-  rput<T>(rf, ins.dst, u, r);
+    for (int u = 0; u < N; ++u) a[u] = getf(p, rf, pos, ins.a, u);
+#pragma unroll
+    for (int u = 0; u < N; ++u) {
+      V4<float> r;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = f(a[u].v[e]);
+      putf(p, rf, pos, ins.dst, u, r);
+    }
+  } else {
+#pragma unroll 1
+    for (int u = 0; u < rf.U; ++u) {
+      V4<float> a = getf(p, rf, pos, ins.a, u), r;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = f(a.v[e]);
+      putf(p, rf, pos, ins.dst, u, r);
+    }
+  }
 }
 
-template <typename T> __device__ __forceinline__ void cmp_instr(const EwInstr& ins, const RegFile& rf, int u) {
-  V4<T> a = rget<T>(rf, ins.a, u), b = rget<T>(rf, ins.b, u);
-  V4<uint32_t> r;
+template <int UT, typename F>
+__device__ __forceinline__ void f32_binary(const EwProgram& p, const EwInstr ins, const RegFile& rf, const Pos& pos, F f) {
+  constexpr int N = UT > 0 ? UT : 1;
+  if (UT > 0) {
+    V4<float> a[N], b[N];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) r.v[e] = cmp_op<T>(a.v[e], b.v[e], ins.aux);
-  rput<uint32_t>(rf, ins.dst, u, r);
+    for (int u = 0; u < N; ++u) { a[u] = getf(p, rf, pos, ins.a, u); b[u] = getf(p, rf, pos, ins.b, u); }
+#pragma unroll
+    for (int u = 0; u < N; ++u) {
+      V4<float> r;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = f(a[u].v[e], b[u].v[e]);
+      putf(p, rf, pos, ins.dst, u, r);
+    }
+  } else {
+#pragma unroll 1
+    for (int u = 0; u < rf.U; ++u) {
+      V4<float> a = getf(p, rf, pos, ins.a, u), b = getf(p, rf, pos, ins.b, u), r;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r.v[e] = f(a.v[e], b.v[e]);
+      putf(p, rf, pos, ins.dst, u, r);
+    }
+  }
+}
+
+template <int UT>
+__device__ __forceinline__ void f32_instr(const EwProgram& p, const EwInstr ins, const RegFile& rf, const Pos& pos) {
+  switch (ins.op) {
+    case E_ADD: f32_binary<UT>(p, ins, rf, pos, [](float x, float y) { return fadd(x, y); }); break;
+    case E_SUB: f32_binary<UT>(p, ins, rf, pos, [](float x, float y) { return fadd(x, -y); }); break;
+    case E_MUL: f32_binary<UT>(p, ins, rf, pos, [](float x, float y) { return fmul(x, y); }); break;
+    case E_DIV: f32_binary<UT>(p, ins, rf, pos, [](float x, float y) { return fdiv(x, y); }); break;
+    case E_NEG: f32_unary<UT>(p, ins, rf, pos, [](float x) { return -x; }); break;
+    case E_RELU: f32_unary<UT>(p, ins, rf, pos, [](float x) { return x > 0.f ? x : 0.f; }); break;
+    case E_EXP: f32_unary<UT>(p, ins, rf, pos, [](float x) { return expf(x); }); break;
+    case E_EXPNEG: f32_unary<UT>(p, ins, rf, pos, [](float x) { return expf(-x); }); break;
+    case E_LOG: f32_unary<UT>(p, ins, rf, pos, [](float x) { return logf(x); }); break;
+    case E_ABS: f32_unary<UT>(p, ins, rf, pos, [](float x) { return x < 0 ? -x : (x == 0 ? 0.f : x); }); break;
+    case E_SIGN: f32_unary<UT>(p, ins, rf, pos, [](float x) { return x != x ? x : (float)((x > 0) - (x < 0)); }); break;
+    case E_SIN: f32_unary<UT>(p, ins, rf, pos, [](float x) { return sinf(x); }); break;
+    default: f32_unary<UT>(p, ins, rf, pos, [](float x) { return cosf(x); }); break;
+  }
+}
+
+template <int UT>
+__device__ __forceinline__ void f32_where(const EwProgram& p, const EwInstr ins, const RegFile& rf, const Pos& pos) {
+  const int nU = UT > 0 ? UT : rf.U;
+  BG_FOR_U {
+    V4<uint32_t> c = rget<uint32_t>(rf, ins.a, u);
+    V4<float> x = getf(p, rf, pos, ins.b, u), y = getf(p, rf, pos, ins.c, u), r;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) r.v[e] = c.v[e] ? x.v[e] : y.v[e];
+    putf(p, rf, pos, ins.dst, u, r);
+  }
+}
+
+template <int UT>
+__device__ __forceinline__ void f32_cmp(const EwProgram& p, const EwInstr ins, const RegFile& rf, const Pos& pos) {
+  const int nU = UT > 0 ? UT : rf.U;
+  BG_FOR_U {
+    V4<float> a = getf(p, rf, pos, ins.a, u), b = getf(p, rf, pos, ins.b, u);
+    V4<uint32_t> r;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) r.v[e] = cmp_op<float>(a.v[e], b.v[e], ins.aux);
+    rput<uint32_t>(rf, ins.dst, u, r);
+  }
+}
+
+template <int UT, typename T>
+__device__ __forceinline__ void float_instr(const EwInstr ins, const RegFile& rf) {
+  const int nU = UT > 0 ? UT : rf.U;
+  switch (ins.op) {
+    case E_ADD: BG_BINARY(T, fadd(x, y)) break;
+    case E_MUL: BG_BINARY(T, fmul(x, y)) break;
+    case E_DIV: BG_BINARY(T, fdiv(x, y)) break;
+    case E_NEG: BG_UNARY(T, -x) break;
+    case E_EXP: BG_UNARY(T, f_exp<T>(x)) break;
+    case E_LOG: BG_UNARY(T, f_log<T>(x)) break;
+    case E_ABS: BG_UNARY(T, x < 0 ? -x : (x == 0 ? T(0) : x)) break;
+    case E_SIGN: BG_UNARY(T, x != x ? x : T((x > 0) - (x < 0))) break;
+    case E_SIN: BG_UNARY(T, f_sin<T>(x)) break;
+    default: BG_UNARY(T, f_cos<T>(x)) break;
+  }
+}
+
+template <int UT>
+__device__ __forceinline__ void int_instr(const EwInstr ins, const RegFile& rf) {
+  const int nU = UT > 0 ? UT : rf.U;
+  typedef long long T;
+  typedef unsigned long long UL;
+  switch (ins.op) {
+    case E_ADD: BG_BINARY(T, (T)((UL)x + (UL)y)) break;
+    case E_MUL: BG_BINARY(T, (T)((UL)x * (UL)y)) break;
+    case E_DIV: BG_BINARY(T, (T)((double)x / (double)y)) break;
+    case E_NEG: BG_UNARY(T, (T)(0ull - (UL)x)) break;
+    case E_ABS: BG_UNARY(T, x < 0 ? (T)(0ull - (UL)x) : x) break;
+    default: BG_UNARY(T, (T)((x > 0) - (x < 0))) break;
+  }
+}
+
+template <int UT, typename T>
+__device__ __forceinline__ void where_instr(const EwInstr ins, const RegFile& rf) {
+  const int nU = UT > 0 ? UT : rf.U;
+  BG_FOR_U {
+    V4<uint32_t> c = rget<uint32_t>(rf, ins.a, u);
+    V4<T> x = rget<T>(rf, ins.b, u), y = rget<T>(rf, ins.c, u), r;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) r.v[e] = c.v[e] ? x.v[e] : y.v[e];
+    rput<T>(rf, ins.dst, u, r);
+  }
+}
+
+template <int UT, typename T>
+__device__ __forceinline__ void cmp_instr(const EwInstr ins, const RegFile& rf) {
+  const int nU = UT > 0 ? UT : rf.U;
+  BG_FOR_U {
+    V4<T> a = rget<T>(rf, ins.a, u), b = rget<T>(rf, ins.b, u);
+    V4<uint32_t> r;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) r.v[e] = cmp_op<T>(a.v[e], b.v[e], ins.aux);
+    rput<uint32_t>(rf, ins.dst, u, r);
+  }
 }
 
 template <typename S, typename D> __device__ __forceinline__ D cvt1(S x) { return (D)x; }
@@ -435,126 +561,189 @@ template <> __device__ __forceinline__ double cvt1<long long, double>(long long 
 template <> __device__ __forceinline__ long long cvt1<float, long long>(float x) { return __float2ll_rz(x); }
 template <> __device__ __forceinline__ long long cvt1<double, long long>(double x) { return __double2ll_rz(x); }
 
-template <typename S, typename D> __device__ __forceinline__ void cvt_instr(const EwInstr& ins, const RegFile& rf, int u) {
-  V4<S> a = rget<S>(rf, ins.a, u);
-  V4<D> r;
+template <typename S, typename D>
+__device__ __forceinline__ void cvt_instr(const EwInstr ins, const RegFile& rf) {
+  const int nU = rf.U;
+#pragma unroll 1
+  for (int u = 0; u < nU; ++u) {
+    V4<S> a = rget<S>(rf, ins.a, u);
+    V4<D> r;
 #pragma unroll
-  for (int e = 0; e < 4; ++e) r.v[e] = cvt1<S, D>(a.v[e]);
-  rput<D>(rf, ins.dst, u, r);
-}
-
-template <typename S> __device__ __forceinline__ void cvt_from(const EwInstr& ins, const RegFile& rf, int u) {
-  switch (ins.type) {
-    case T_F32: cvt_instr<S, float>(ins, rf, u); break;
-    case T_F64: cvt_instr<S, double>(ins, rf, u); break;
-    case T_I64: cvt_instr<S, long long>(ins, rf, u); break;
-    default: cvt_instr<S, uint32_t>(ins, rf, u); break;
+    for (int e = 0; e < 4; ++e) r.v[e] = cvt1<S, D>(a.v[e]);
+    rput<D>(rf, ins.dst, u, r);
   }
 }
 
-__device__ __forceinline__ void exec_instr(const EwProgram& p, const EwInstr& ins, const RegFile& rf, int u,
-                                           const ChunkPos& cp) {
+template <typename S> __device__ __forceinline__ void cvt_from(const EwInstr ins, const RegFile& rf) {
+  switch (ins.type) {
+    case T_F32: cvt_instr<S, float>(ins, rf); break;
+    case T_F64: cvt_instr<S, double>(ins, rf); break;
+    case T_I64: cvt_instr<S, long long>(ins, rf); break;
+    default: cvt_instr<S, uint32_t>(ins, rf); break;
+  }
+}
+
+// Less common instructions, kept out of line so the hot switch stays small.
+__device__ __noinline__ void misc_instr(const EwProgram& p, const EwInstr ins, const RegFile rf) {
+  const int nU = rf.U;
   switch (ins.op) {
-    case E_LOAD: do_load(p, ins, rf, u, cp); break;
-    case E_STORE: do_store(p, ins, rf, u, cp); break;
     case E_CONST: {
       const int64_t bits = p.consts[ins.aux];
-      if (ins.type == T_F32) {
-        float f = (float)__longlong_as_double(bits);
-        rput<float>(rf, ins.dst, u, {{f, f, f, f}});
-      } else if (ins.type == T_F64) {
-        double d = __longlong_as_double(bits);
-        rput<double>(rf, ins.dst, u, {{d, d, d, d}});
-      } else if (ins.type == T_I64) {
-        rput<long long>(rf, ins.dst, u, {{bits, bits, bits, bits}});
-      } else {
-        uint32_t b = bits != 0;
-        rput<uint32_t>(rf, ins.dst, u, {{b, b, b, b}});
+#pragma unroll 1
+      for (int u = 0; u < nU; ++u) {
+        if (ins.type == T_F32) {
+          float f = (float)__longlong_as_double(bits);
+          rput<float>(rf, ins.dst, u, {{f, f, f, f}});
+        } else if (ins.type == T_F64) {
+          double d = __longlong_as_double(bits);
+          rput<double>(rf, ins.dst, u, {{d, d, d, d}});
+        } else if (ins.type == T_I64) {
+          rput<long long>(rf, ins.dst, u, {{bits, bits, bits, bits}});
+        } else {
+          uint32_t b = bits != 0;
+          rput<uint32_t>(rf, ins.dst, u, {{b, b, b, b}});
+        }
       }
       break;
     }
-    case E_CMP:
-      if (ins.type == T_F32) cmp_instr<float>(ins, rf, u);
-      else if (ins.type == T_F64) cmp_instr<double>(ins, rf, u);
-      else if (ins.type == T_I64) cmp_instr<long long>(ins, rf, u);
-      else cmp_instr<uint32_t>(ins, rf, u);
-      break;
-    case E_WHERE:
-      if (ins.type == T_F32) where_instr<float>(ins, rf, u);
-      else if (ins.type == T_F64) where_instr<double>(ins, rf, u);
-      else if (ins.type == T_I64) where_instr<long long>(ins, rf, u);
-      else where_instr<uint32_t>(ins, rf, u);
-      break;
-    case E_ISNAN: {
-      V4<uint32_t> r;
-      if (ins.type == T_F32) { V4<float> a = rget<float>(rf, ins.a, u);
+    case E_ISNAN:
+#pragma unroll 1
+      for (int u = 0; u < nU; ++u) {
+        V4<uint32_t> r;
+        if (ins.type == T_F32) {
+          V4<float> a = rget<float>(rf, ins.a, u);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) r.v[e] = a.v[e] != a.v[e];
-      } else if (ins.type == T_F64) { V4<double> a = rget<double>(rf, ins.a, u);
+          for (int e = 0; e < 4; ++e) r.v[e] = a.v[e] != a.v[e];
+        } else if (ins.type == T_F64) {
+          V4<double> a = rget<double>(rf, ins.a, u);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) r.v[e] = a.v[e] != a.v[e];
-      } else { r = {{0, 0, 0, 0}}; }
-      rput<uint32_t>(rf, ins.dst, u, r);
+          for (int e = 0; e < 4; ++e) r.v[e] = a.v[e] != a.v[e];
+        } else {
+          r = {{0, 0, 0, 0}};
+        }
+        rput<uint32_t>(rf, ins.dst, u, r);
+      }
       break;
-    }
     case E_CVT:
       switch (ins.aux & 0xF) {
-        case T_F32: cvt_from<float>(ins, rf, u); break;
-        case T_F64: cvt_from<double>(ins, rf, u); break;
-        case T_I64: cvt_from<long long>(ins, rf, u); break;
-        default: cvt_from<uint32_t>(ins, rf, u); break;
+        case T_F32: cvt_from<float>(ins, rf); break;
+        case T_F64: cvt_from<double>(ins, rf); break;
+        case T_I64: cvt_from<long long>(ins, rf); break;
+        default: cvt_from<uint32_t>(ins, rf); break;
       }
       break;
     case E_NARROW:
-      if (ins.type == T_F32) {
-        V4<float> a = rget<float>(rf, ins.a, u);
+#pragma unroll 1
+      for (int u = 0; u < nU; ++u) {
+        if (ins.type == T_F32) {
+          V4<float> a = rget<float>(rf, ins.a, u);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) a.v[e] = narrow_f32(a.v[e], ins.aux);
-        rput<float>(rf, ins.dst, u, a);
-      } else if (ins.type == T_I64) {
-        V4<long long> a = rget<long long>(rf, ins.a, u);
+          for (int e = 0; e < 4; ++e) a.v[e] = narrow_f32(a.v[e], ins.aux);
+          rput<float>(rf, ins.dst, u, a);
+        } else if (ins.type == T_I64) {
+          V4<long long> a = rget<long long>(rf, ins.a, u);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) a.v[e] = narrow_i64(a.v[e], ins.aux);
-        rput<long long>(rf, ins.dst, u, a);
+          for (int e = 0; e < 4; ++e) a.v[e] = narrow_i64(a.v[e], ins.aux);
+          rput<long long>(rf, ins.dst, u, a);
+        }
       }
       break;
-    case E_AND: case E_OR: {
-      V4<uint32_t> a = rget<uint32_t>(rf, ins.a, u), b = rget<uint32_t>(rf, ins.b, u);
+    case E_AND: case E_OR:
+#pragma unroll 1
+      for (int u = 0; u < nU; ++u) {
+        V4<uint32_t> a = rget<uint32_t>(rf, ins.a, u), b = rget<uint32_t>(rf, ins.b, u);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) a.v[e] = ins.op == E_AND ? (a.v[e] & b.v[e]) : (a.v[e] | b.v[e]);
-      rput<uint32_t>(rf, ins.dst, u, a);
+        for (int e = 0; e < 4; ++e) a.v[e] = ins.op == E_AND ? (a.v[e] & b.v[e]) : (a.v[e] | b.v[e]);
+        rput<uint32_t>(rf, ins.dst, u, a);
+      }
       break;
-    }
+    case E_CMP:
+      if (ins.type == T_F64) cmp_instr<0, double>(ins, rf);
+      else if (ins.type == T_I64) cmp_instr<0, long long>(ins, rf);
+      else cmp_instr<0, uint32_t>(ins, rf);
+      break;
+    case E_WHERE:
+      if (ins.type == T_F64) where_instr<0, double>(ins, rf);
+      else if (ins.type == T_I64) where_instr<0, long long>(ins, rf);
+      else where_instr<0, uint32_t>(ins, rf);
+      break;
     default:
-      if (ins.type == T_F32) float_instr<float>(ins, rf, u);
-      else if (ins.type == T_F64) float_instr<double>(ins, rf, u);
-      else int_instr(ins, rf, u);
+      if (ins.type == T_F64) float_instr<0, double>(ins, rf);
+      else int_instr<0>(ins, rf);
       break;
   }
+}
+
+// One instruction over all chunks of a pass.
+template <int UT>
+__device__ __forceinline__ void exec_instr(const EwProgram& p, const EwInstr ins, const RegFile& rf, const Pos& pos) {
+  const int nU = UT > 0 ? UT : rf.U;
+  switch (ins.op) {
+    case E_LOAD: {
+      const EwOperand& o = p.inputs[ins.aux];
+      // hot path: dense fp32 operand, every chunk of this thread fully inside the tensor / row
+      if (UT > 0 && o.mode == A_CONTIG && o.vec_ok && o.dtype == BG_F32 && pos.end - pos.idx(UT - 1) >= 4) {
+        const float* src = reinterpret_cast<const float*>(o.ptr) + pos.idx0;
+        float4 t[UT > 0 ? UT : 1];
+#pragma unroll
+        for (int u = 0; u < nU; ++u) t[u] = __ldg(reinterpret_cast<const float4*>(src + (int64_t)u * kChunk));
+#pragma unroll
+        for (int u = 0; u < nU; ++u) *reinterpret_cast<float4*>(rf.slot(ins.dst, u, 0)) = t[u];
+      } else {
+#pragma unroll 1
+        for (int u = 0; u < nU; ++u) load_chunk(p, ins, rf, u, ChunkPos{pos.idx(u), pos.nvalid(u)});
+      }
+      break;
+    }
+    case E_STORE: {
+      const EwOutput& o = p.outputs[ins.aux];
+      if (UT > 0 && ins.type == T_F32 && o.vec_ok && o.dtype == BG_F32 && pos.end - pos.idx(UT - 1) >= 4) {
+        float* dst = reinterpret_cast<float*>(o.ptr) + pos.idx0;
+#pragma unroll
+        for (int u = 0; u < nU; ++u)
+          *reinterpret_cast<float4*>(dst + (int64_t)u * kChunk) = *reinterpret_cast<const float4*>(rf.slot(ins.a, u, 0));
+      } else {
+#pragma unroll 1
+        for (int u = 0; u < nU; ++u) store_chunk(p, ins, rf, u, ChunkPos{pos.idx(u), pos.nvalid(u)});
+      }
+      break;
+    }
+    case E_ADD: case E_MUL: case E_DIV: case E_NEG: case E_EXP: case E_LOG: case E_ABS: case E_SIGN: case E_SIN: case E_COS:
+    case E_SUB: case E_RELU: case E_EXPNEG:
+      if (ins.type == T_F32) f32_instr<UT>(p, ins, rf, pos);
+      else misc_instr(p, ins, rf);
+      break;
+    case E_CMP:
+      if (ins.type == T_F32) f32_cmp<UT>(p, ins, rf, pos);
+      else misc_instr(p, ins, rf);
+      break;
+    case E_WHERE:
+      if (ins.type == T_F32) f32_where<UT>(p, ins, rf, pos);
+      else misc_instr(p, ins, rf);
+      break;
+    default:
+      misc_instr(p, ins, rf);
+      break;
+  }
+}
+
+template <int UT>
+__device__ __forceinline__ void run_program(const EwProgram& p, const RegFile& rf, const Pos& pos) {
+#pragma unroll 1
+  for (int i = 0; i < p.n_instr; ++i) exec_instr<UT>(p, p.instr[i], rf, pos);
 }
 
 // ------------------------------------------------------------------------------------
 // Flat elementwise kernel
 // ------------------------------------------------------------------------------------
+template <int UT>
 __global__ void __launch_bounds__(kBlock) ew_kernel(const __grid_constant__ EwProgram p, int U, int64_t n_tiles) {
   extern __shared__ __align__(16) char smem[];
-  RegFile rf{smem, U, p.wide ? 2 : 1};
+  const RegFile rf(smem, U, p.wide ? 2 : 1);
   const int64_t tile_elems = (int64_t)U * kChunk;
   for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-    const int64_t t0 = tile * tile_elems + (int64_t)threadIdx.x * kVec;
-#pragma unroll 1
-    for (int i = 0; i < p.n_instr; ++i) {
-      const EwInstr ins = p.instr[i];
-#pragma unroll 1
-      for (int u = 0; u < U; ++u) {
-        ChunkPos cp;
-        cp.idx = t0 + (int64_t)u * kChunk;
-        int64_t left = p.numel - cp.idx;
-        cp.nvalid = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
-        if (cp.nvalid == 0 && (ins.op == E_LOAD || ins.op == E_STORE)) continue;
-        exec_instr(p, ins, rf, u, cp);
-      }
-    }
+    const Pos pos{tile * tile_elems + (int64_t)threadIdx.x * kVec, p.numel};
+    run_program<UT>(p, rf, pos);
   }
 }
 
@@ -562,15 +751,15 @@ cudaError_t launch_elementwise(const EwProgram& p, cudaStream_t s, int sm_count)
   if (p.numel == 0) return cudaSuccess;
   const int planes = p.wide ? 2 : 1;
   const size_t per_chunk = (size_t)p.n_regs * planes * kBlock * 16;
-  int U = 2;
-  if (per_chunk * U > 48 * 1024) U = 1;
-  if (p.numel <= (int64_t)kChunk * sm_count) U = 1;
+  int U = 4;
+  while (U > 1 && (per_chunk * U > 64 * 1024 || p.numel < (int64_t)kChunk * U * sm_count)) U >>= 1;
   const size_t smem = per_chunk * U;
+  if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
+  auto kern = U == 4 ? ew_kernel<4> : (U == 2 ? ew_kernel<2> : ew_kernel<1>);
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(ew_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
     if (e != cudaSuccess) return e;
   }
-  if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
   const int64_t tile_elems = (int64_t)U * kChunk;
   const int64_t n_tiles = (p.numel + tile_elems - 1) / tile_elems;
   int ctas_per_sm = (int)(200 * 1024 / (smem ? smem : 1));
@@ -578,18 +767,13 @@ cudaError_t launch_elementwise(const EwProgram& p, cudaStream_t s, int sm_count)
   if (ctas_per_sm < 1) ctas_per_sm = 1;
   int64_t grid = (int64_t)sm_count * ctas_per_sm;
   if (grid > n_tiles) grid = n_tiles;
-  ew_kernel<<<(unsigned)grid, kBlock, smem, s>>>(p, U, n_tiles);
+  kern<<<(unsigned)grid, kBlock, smem, s>>>(p, U, n_tiles);
   return cudaGetLastError();
 }
 
 // ------------------------------------------------------------------------------------
 // Row kernel: program + on-chip tail over the last axis
 // ------------------------------------------------------------------------------------
-struct BlockRed {
-  // 8 warps x 16 bytes of scratch placed after the register file
-  char* scratch;
-};
-
 template <typename T, typename F>
 __device__ __forceinline__ T block_reduce(T v, F f, T ident, char* scratch) {
 #pragma unroll
@@ -670,10 +854,11 @@ __device__ __forceinline__ void store_scalar(void* ptr, int dt, int64_t i, doubl
   }
 }
 
-// Reduction over one row with values of class T arriving chunk by chunk.
-template <typename T>
-__device__ __forceinline__ void row_reduce(const EwProgram& p, const RegFile& rf, int64_t row, int U, int64_t n_chunks,
+// Reduction over one row with values of class T arriving pass by pass (U chunks per pass).
+template <int UT, typename T>
+__device__ __forceinline__ void row_reduce(const EwProgram& p, const RegFile& rf, int64_t row, int64_t n_chunks,
                                            char* scratch) {
+  const int nU = UT > 0 ? UT : rf.U;
   const int op = p.tail_arg;
   const bool is_arg = op == BG_RED_ARGMAX || op == BG_RED_ARGMIN;
   T acc = T(0);
@@ -681,38 +866,42 @@ __device__ __forceinline__ void row_reduce(const EwProgram& p, const RegFile& rf
   if (op == BG_RED_MAX) acc = lowest<T>();
   if (op == BG_RED_MIN) acc = highest<T>();
   bool any_nan = false;
-  for (int64_t c0 = 0; c0 < n_chunks; c0 += U) {
+  const int64_t row_end = (row + 1) * p.cols;
+  for (int64_t c0 = 0; c0 < n_chunks; c0 += nU) {
+    const int64_t col0 = c0 * kChunk + (int64_t)threadIdx.x * kVec;
+    const Pos pos{row * p.cols + col0, row_end};
+    run_program<UT>(p, rf, pos);
+    if (op == BG_RED_SUM || op == BG_RED_MEAN) {
+      if (pos.end - pos.idx(nU - 1) >= 4) {
+#pragma unroll
+        for (int u = 0; u < nU; ++u) {
+          V4<T> x = rget<T>(rf, p.tail_reg, u);
+          acc += (x.v[0] + x.v[1]) + (x.v[2] + x.v[3]);
+        }
+      } else {
 #pragma unroll 1
-    for (int i = 0; i < p.n_instr; ++i) {
-      const EwInstr ins = p.instr[i];
-#pragma unroll 1
-      for (int u = 0; u < U; ++u) {
-        ChunkPos cp;
-        const int64_t col = (c0 + u) * kChunk + (int64_t)threadIdx.x * kVec;
-        cp.idx = row * p.cols + col;
-        int64_t left = p.cols - col;
-        cp.nvalid = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
-        if (cp.nvalid == 0 && (ins.op == E_LOAD || ins.op == E_STORE)) continue;
-        exec_instr(p, ins, rf, u, cp);
+        for (int u = 0; u < nU; ++u) {
+          const int nv = pos.nvalid(u);
+          V4<T> x = rget<T>(rf, p.tail_reg, u);
+          for (int e = 0; e < nv; ++e) acc += x.v[e];
+        }
       }
-    }
+    } else {
 #pragma unroll 1
-    for (int u = 0; u < U; ++u) {
-      const int64_t col = (c0 + u) * kChunk + (int64_t)threadIdx.x * kVec;
-      int64_t left = p.cols - col;
-      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
-      if (nv == 0) continue;
-      V4<T> x = rget<T>(rf, p.tail_reg, u);
-      for (int e = 0; e < nv; ++e) {
-        const T v = x.v[e];
-        if (is_arg) {
-          if (arg_better<T>(v, col + e, acc, best_i, op == BG_RED_ARGMAX)) { acc = v; best_i = col + e; }
-        } else if (op == BG_RED_SUM || op == BG_RED_MEAN) {
-          acc += v;
-        } else {
-          if (v != v) any_nan = true;
-          if (op == BG_RED_MAX) acc = v > acc ? v : acc;
-          else acc = v < acc ? v : acc;
+      for (int u = 0; u < nU; ++u) {
+        const int nv = pos.nvalid(u);
+        if (nv == 0) continue;
+        const int64_t col = col0 + (int64_t)u * kChunk;
+        V4<T> x = rget<T>(rf, p.tail_reg, u);
+        for (int e = 0; e < nv; ++e) {
+          const T v = x.v[e];
+          if (is_arg) {
+            if (arg_better<T>(v, col + e, acc, best_i, op == BG_RED_ARGMAX)) { acc = v; best_i = col + e; }
+          } else {
+            if (v != v) any_nan = true;
+            if (op == BG_RED_MAX) acc = v > acc ? v : acc;
+            else acc = v < acc ? v : acc;
+          }
         }
       }
     }
@@ -745,31 +934,17 @@ __device__ __forceinline__ void row_reduce(const EwProgram& p, const RegFile& rf
   }
 }
 
-__device__ __forceinline__ void row_reduce_bool(const EwProgram& p, const RegFile& rf, int64_t row, int U,
-                                                int64_t n_chunks) {
-  // any / all over a T_B register (also sum/max of bools is not generated by the compiler)
+__device__ __noinline__ void row_reduce_bool(const EwProgram& p, const RegFile rf, int64_t row, int64_t n_chunks) {
+  const int nU = rf.U;
   const bool is_any = p.tail_arg == BG_RED_ANY;
   int local = is_any ? 0 : 1;
-  for (int64_t c0 = 0; c0 < n_chunks; c0 += U) {
+  const int64_t row_end = (row + 1) * p.cols;
+  for (int64_t c0 = 0; c0 < n_chunks; c0 += nU) {
+    const Pos pos{row * p.cols + c0 * kChunk + (int64_t)threadIdx.x * kVec, row_end};
+    run_program<0>(p, rf, pos);
 #pragma unroll 1
-    for (int i = 0; i < p.n_instr; ++i) {
-      const EwInstr ins = p.instr[i];
-#pragma unroll 1
-      for (int u = 0; u < U; ++u) {
-        ChunkPos cp;
-        const int64_t col = (c0 + u) * kChunk + (int64_t)threadIdx.x * kVec;
-        cp.idx = row * p.cols + col;
-        int64_t left = p.cols - col;
-        cp.nvalid = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
-        if (cp.nvalid == 0 && (ins.op == E_LOAD || ins.op == E_STORE)) continue;
-        exec_instr(p, ins, rf, u, cp);
-      }
-    }
-#pragma unroll 1
-    for (int u = 0; u < U; ++u) {
-      const int64_t col = (c0 + u) * kChunk + (int64_t)threadIdx.x * kVec;
-      int64_t left = p.cols - col;
-      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+    for (int u = 0; u < nU; ++u) {
+      const int nv = pos.nvalid(u);
       V4<uint32_t> x = rget<uint32_t>(rf, p.tail_reg, u);
       for (int e = 0; e < nv; ++e) {
         if (is_any) local |= (x.v[e] != 0);
@@ -782,135 +957,132 @@ __device__ __forceinline__ void row_reduce_bool(const EwProgram& p, const RegFil
 }
 
 // softmax / layer norm: the whole row stays in the register file (n_chunks <= U).
-template <typename T>
-__device__ __forceinline__ void row_resident_tail(const EwProgram& p, const RegFile& rf, int64_t row, int U,
-                                                  char* scratch) {
-#pragma unroll 1
-  for (int i = 0; i < p.n_instr; ++i) {
-    const EwInstr ins = p.instr[i];
-#pragma unroll 1
-    for (int u = 0; u < U; ++u) {
-      ChunkPos cp;
-      const int64_t col = (int64_t)u * kChunk + (int64_t)threadIdx.x * kVec;
-      cp.idx = row * p.cols + col;
-      int64_t left = p.cols - col;
-      cp.nvalid = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
-      if (cp.nvalid == 0 && (ins.op == E_LOAD || ins.op == E_STORE)) continue;
-      exec_instr(p, ins, rf, u, cp);
-    }
-  }
+template <int UT, typename T>
+__device__ __forceinline__ void row_resident_tail(const EwProgram& p, const RegFile& rf, int64_t row, char* scratch) {
+  const int nU = UT > 0 ? UT : rf.U;
+  const int64_t col0 = (int64_t)threadIdx.x * kVec;
+  const Pos pos{row * p.cols + col0, (row + 1) * p.cols};
+  run_program<UT>(p, rf, pos);
   const int r = p.tail_reg;
   const EwOutput& out = p.outputs[p.tail_out];
+  const bool full = pos.end - pos.idx(nU - 1) >= 4;   // every chunk of this thread is complete
   if (p.tail == TAIL_SOFTMAX) {
     T m = lowest<T>();
     bool nan = false;
-#pragma unroll 1
-    for (int u = 0; u < U; ++u) {
-      const int64_t col = (int64_t)u * kChunk + (int64_t)threadIdx.x * kVec;
-      int64_t left = p.cols - col;
-      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+    BG_FOR_U {
+      const int nv = full ? 4 : pos.nvalid(u);
       V4<T> x = rget<T>(rf, r, u);
-      for (int e = 0; e < nv; ++e) {
-        if (x.v[e] != x.v[e]) nan = true;
-        m = x.v[e] > m ? x.v[e] : m;
-      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (e < nv) {
+          if (x.v[e] != x.v[e]) nan = true;
+          m = x.v[e] > m ? x.v[e] : m;
+        }
     }
     m = block_reduce<T>(m, [](T a, T b) { return a > b ? a : b; }, m, scratch);
     if (__syncthreads_or(nan ? 1 : 0)) m = (T)CUDART_NAN;
     T sum = T(0);
-#pragma unroll 1
-    for (int u = 0; u < U; ++u) {
-      const int64_t col = (int64_t)u * kChunk + (int64_t)threadIdx.x * kVec;
-      int64_t left = p.cols - col;
-      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
-      if (nv == 0) continue;
-      V4<T> x = rget<T>(rf, r, u);
-      for (int e = 0; e < 4; ++e) {
-        x.v[e] = f_exp<T>(fadd(x.v[e], -m));
-        if (e < nv) sum += x.v[e];
+    BG_FOR_U {
+      const int nv = full ? 4 : pos.nvalid(u);
+      if (nv > 0) {
+        V4<T> x = rget<T>(rf, r, u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          x.v[e] = f_exp<T>(fadd(x.v[e], -m));
+          if (e < nv) sum += x.v[e];
+        }
+        rput<T>(rf, r, u, x);
       }
-      rput<T>(rf, r, u, x);
     }
     sum = block_reduce<T>(sum, [](T a, T b) { return a + b; }, T(0), scratch);
-#pragma unroll 1
-    for (int u = 0; u < U; ++u) {
-      const int64_t col = (int64_t)u * kChunk + (int64_t)threadIdx.x * kVec;
-      int64_t left = p.cols - col;
-      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
-      if (nv == 0) continue;
-      V4<T> x = rget<T>(rf, r, u);
+    const EwInstr st{E_STORE, (uint8_t)p.tail_type, 0, (uint8_t)r, 0, 0, (uint16_t)p.tail_out};
+    BG_FOR_U {
+      const int nv = full ? 4 : pos.nvalid(u);
+      if (nv > 0) {
+        V4<T> x = rget<T>(rf, r, u);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) x.v[e] = fdiv(x.v[e], sum);
-      rput<T>(rf, r, u, x);
-      EwInstr st{E_STORE, (uint8_t)p.tail_type, 0, (uint8_t)r, 0, 0, (uint16_t)p.tail_out};
-      ChunkPos cp{row * p.cols + col, nv};
-      do_store(p, st, rf, u, cp);
+        for (int e = 0; e < 4; ++e) x.v[e] = fdiv(x.v[e], sum);
+        if (sizeof(T) == 4 && nv == 4 && out.vec_ok && out.dtype == BG_F32) {
+          *reinterpret_cast<float4*>(reinterpret_cast<float*>(out.ptr) + pos.idx(u)) =
+              make_float4((float)x.v[0], (float)x.v[1], (float)x.v[2], (float)x.v[3]);
+        } else {
+          rput<T>(rf, r, u, x);
+          store_chunk(p, st, rf, u, ChunkPos{pos.idx(u), nv});
+        }
+      }
     }
-    (void)out;
   } else {  // TAIL_LAYERNORM, fp32 statistics as in the reference (x.astype(float32))
     float sum = 0.f;
-#pragma unroll 1
-    for (int u = 0; u < U; ++u) {
-      const int64_t col = (int64_t)u * kChunk + (int64_t)threadIdx.x * kVec;
-      int64_t left = p.cols - col;
-      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+    BG_FOR_U {
+      const int nv = full ? 4 : pos.nvalid(u);
       V4<T> x = rget<T>(rf, r, u);
-      for (int e = 0; e < nv; ++e) sum += (float)x.v[e];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (e < nv) sum += (float)x.v[e];
     }
     sum = block_reduce<float>(sum, [](float a, float b) { return a + b; }, 0.f, scratch);
     const float mean = sum / (float)p.cols;
     float sq = 0.f;
-#pragma unroll 1
-    for (int u = 0; u < U; ++u) {
-      const int64_t col = (int64_t)u * kChunk + (int64_t)threadIdx.x * kVec;
-      int64_t left = p.cols - col;
-      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
+    BG_FOR_U {
+      const int nv = full ? 4 : pos.nvalid(u);
       V4<T> x = rget<T>(rf, r, u);
-      for (int e = 0; e < nv; ++e) {
-        float c = __fadd_rn((float)x.v[e], -mean);
-        sq += __fmul_rn(c, c);
-      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (e < nv) {
+          float c = __fadd_rn((float)x.v[e], -mean);
+          sq += __fmul_rn(c, c);
+        }
     }
     sq = block_reduce<float>(sq, [](float a, float b) { return a + b; }, 0.f, scratch);
     const float var = sq / (float)p.cols;
     const float inv = 1.0f / sqrtf(var + p.tail_eps);
     const EwOperand& w = p.inputs[p.tail_w];
     const EwOperand& b = p.inputs[p.tail_b];
-#pragma unroll 1
-    for (int u = 0; u < U; ++u) {
-      const int64_t col = (int64_t)u * kChunk + (int64_t)threadIdx.x * kVec;
-      int64_t left = p.cols - col;
-      const int nv = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
-      if (nv == 0) continue;
-      V4<T> x = rget<T>(rf, r, u);
-      for (int e = 0; e < nv; ++e) {
-        float c = __fadd_rn((float)x.v[e], -mean);
-        float xh = __fmul_rn(c, inv);
-        float wv = w.dtype == BG_F64 ? (float)reinterpret_cast<const double*>(w.ptr)[col + e] : ld_f32class(w.ptr, w.dtype, col + e);
-        float bv = b.dtype == BG_F64 ? (float)reinterpret_cast<const double*>(b.ptr)[col + e] : ld_f32class(b.ptr, b.dtype, col + e);
-        float y = __fadd_rn(__fmul_rn(xh, wv), bv);
-        store_scalar(out.ptr, out.dtype, row * p.cols + col + e, (double)y, 0, false);
+    BG_FOR_U {
+      const int nv = full ? 4 : pos.nvalid(u);
+      if (nv > 0) {
+        const int64_t col = col0 + (int64_t)u * kChunk;
+        V4<T> x = rget<T>(rf, r, u);
+        float y[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (e < nv) {
+            float c = __fadd_rn((float)x.v[e], -mean);
+            float xh = __fmul_rn(c, inv);
+            float wv = w.dtype == BG_F64 ? (float)reinterpret_cast<const double*>(w.ptr)[col + e] : ld_f32class(w.ptr, w.dtype, col + e);
+            float bv = b.dtype == BG_F64 ? (float)reinterpret_cast<const double*>(b.ptr)[col + e] : ld_f32class(b.ptr, b.dtype, col + e);
+            y[e] = __fadd_rn(__fmul_rn(xh, wv), bv);
+          }
+        if (nv == 4 && out.vec_ok && out.dtype == BG_F32) {
+          *reinterpret_cast<float4*>(reinterpret_cast<float*>(out.ptr) + pos.idx(u)) = make_float4(y[0], y[1], y[2], y[3]);
+        } else if (nv == 4 && out.vec_ok && out.dtype == BG_F64) {
+          double* q = reinterpret_cast<double*>(out.ptr) + pos.idx(u);
+          *reinterpret_cast<double2*>(q) = make_double2((double)y[0], (double)y[1]);
+          *reinterpret_cast<double2*>(q + 2) = make_double2((double)y[2], (double)y[3]);
+        } else {
+          for (int e = 0; e < nv; ++e) store_scalar(out.ptr, out.dtype, pos.idx(u) + e, (double)y[e], 0, false);
+        }
       }
     }
   }
 }
 
+template <int UT>
 __global__ void __launch_bounds__(kBlock) row_kernel(const __grid_constant__ EwProgram p, int U, int64_t n_chunks) {
   extern __shared__ __align__(16) char smem[];
   const int planes = p.wide ? 2 : 1;
-  RegFile rf{smem, U, planes};
+  const RegFile rf(smem, U, planes);
   char* scratch = smem + (size_t)p.n_regs * U * planes * kBlock * 16;
   for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
     if (p.tail == TAIL_REDUCE) {
-      if (p.tail_type == T_F32) row_reduce<float>(p, rf, row, U, n_chunks, scratch);
-      else if (p.tail_type == T_F64) row_reduce<double>(p, rf, row, U, n_chunks, scratch);
-      else if (p.tail_type == T_I64) row_reduce<long long>(p, rf, row, U, n_chunks, scratch);
-      else row_reduce_bool(p, rf, row, U, n_chunks);
+      if (p.tail_type == T_F32) row_reduce<UT, float>(p, rf, row, n_chunks, scratch);
+      else if (p.tail_type == T_F64) row_reduce<0, double>(p, rf, row, n_chunks, scratch);
+      else if (p.tail_type == T_I64) row_reduce<0, long long>(p, rf, row, n_chunks, scratch);
+      else row_reduce_bool(p, rf, row, n_chunks);
     } else {
-      if (p.tail_type == T_F64) row_resident_tail<double>(p, rf, row, U, scratch);
-      else row_resident_tail<float>(p, rf, row, U, scratch);
+      if (p.tail_type == T_F64) row_resident_tail<0, double>(p, rf, row, scratch);
+      else row_resident_tail<UT, float>(p, rf, row, scratch);
     }
-    __syncthreads();
   }
 }
 
@@ -926,16 +1098,17 @@ cudaError_t launch_rowwise(const EwProgram& p, cudaStream_t s, int sm_count, int
   const int64_t n_chunks = (p.cols + kChunk - 1) / kChunk;
   int U;
   if (p.tail == TAIL_REDUCE) {
-    U = n_chunks < 2 ? (int)n_chunks : 2;
-    if (per_chunk * U > 64 * 1024) U = 1;
+    U = n_chunks >= 4 ? 4 : (n_chunks >= 2 ? 2 : 1);
+    while (U > 1 && per_chunk * U > 64 * 1024) U >>= 1;
   } else {
     U = (int)n_chunks;
   }
   if (U < 1) U = 1;
   const size_t smem = per_chunk * U + 512;
   if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
+  auto kern = U == 4 ? row_kernel<4> : (U == 2 ? row_kernel<2> : (U == 1 ? row_kernel<1> : row_kernel<0>));
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
     if (e != cudaSuccess) return e;
   }
   int ctas_per_sm = (int)(200 * 1024 / smem);
@@ -943,7 +1116,7 @@ cudaError_t launch_rowwise(const EwProgram& p, cudaStream_t s, int sm_count, int
   if (ctas_per_sm < 1) ctas_per_sm = 1;
   int64_t grid = (int64_t)sm_count * ctas_per_sm;
   if (grid > p.rows) grid = p.rows;
-  row_kernel<<<(unsigned)grid, kBlock, smem, s>>>(p, U, n_chunks);
+  kern<<<(unsigned)grid, kBlock, smem, s>>>(p, U, n_chunks);
   return cudaGetLastError();
 }
 

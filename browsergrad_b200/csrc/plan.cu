@@ -928,65 +928,6 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
     P.rows = rows;
     P.cols = cols;
   }
-  if ((int)code.size() > kEwMaxInstr) { why = "too many instructions"; return false; }
-  // register allocation (linear scan; a destination may take over a source that dies here)
-  std::vector<int> last(next_v, -1);
-  for (size_t i = 0; i < code.size(); ++i) {
-    const VInstr& I = code[i];
-    auto use = [&](int v) { if (v >= 0) last[v] = (int)i; };
-    const bool unary = I.op == E_NEG || I.op == E_EXP || I.op == E_LOG || I.op == E_ABS || I.op == E_SIGN || I.op == E_SIN ||
-                       I.op == E_COS || I.op == E_ISNAN || I.op == E_CVT || I.op == E_NARROW || I.op == E_STORE;
-    if (I.op == E_LOAD || I.op == E_CONST) continue;
-    use(I.a);
-    if (!unary) use(I.b);
-    if (I.op == E_WHERE) use(I.c);
-  }
-  if (tail_reg_v >= 0) last[tail_reg_v] = (int)code.size() + 1;
-  std::vector<int> phys(next_v, -1);
-  std::vector<char> busy;
-  auto alloc_reg = [&]() {
-    for (size_t i = 0; i < busy.size(); ++i)
-      if (!busy[i]) { busy[i] = 1; return (int)i; }
-    busy.push_back(1);
-    return (int)busy.size() - 1;
-  };
-  bool wide = false;
-  P.n_instr = (int)code.size();
-  for (size_t i = 0; i < code.size(); ++i) {
-    const VInstr& I = code[i];
-    EwInstr& O = P.instr[i];
-    O.op = I.op;
-    O.type = I.type;
-    O.aux = I.aux;
-    const bool unary = I.op == E_NEG || I.op == E_EXP || I.op == E_LOG || I.op == E_ABS || I.op == E_SIGN || I.op == E_SIN ||
-                       I.op == E_COS || I.op == E_ISNAN || I.op == E_CVT || I.op == E_NARROW || I.op == E_STORE;
-    const bool leaf = I.op == E_LOAD || I.op == E_CONST;
-    int srcs[3] = {leaf ? -1 : I.a, (leaf || unary) ? -1 : I.b, I.op == E_WHERE ? I.c : -1};
-    O.a = srcs[0] >= 0 ? (uint8_t)phys[srcs[0]] : 0;
-    O.b = srcs[1] >= 0 ? (uint8_t)phys[srcs[1]] : 0;
-    O.c = srcs[2] >= 0 ? (uint8_t)phys[srcs[2]] : 0;
-    for (int k = 0; k < 3; ++k)
-      if (srcs[k] >= 0 && last[srcs[k]] == (int)i && phys[srcs[k]] >= 0) {
-        bool dup = false;
-        for (int j = 0; j < k; ++j) dup |= srcs[j] == srcs[k];
-        if (!dup) busy[phys[srcs[k]]] = 0;
-      }
-    if (I.type == T_F64 || I.type == T_I64) wide = true;
-    if (I.op == E_CVT && ((I.aux & 0xF) == T_F64 || (I.aux & 0xF) == T_I64)) wide = true;
-    if (I.dst >= 0) {
-      if (last[I.dst] < 0 && I.op != E_STORE) {
-        // value never read (dead); still needs a slot for the write
-      }
-      phys[I.dst] = alloc_reg();
-      O.dst = (uint8_t)phys[I.dst];
-      if (last[I.dst] < 0) busy[phys[I.dst]] = 0;
-    }
-  }
-  P.n_regs = std::max<int>(1, (int)busy.size());
-  P.wide = wide ? 1 : 0;
-  if (tail_reg_v >= 0) P.tail_reg = phys[tail_reg_v];
-  const int64_t per_chunk = (int64_t)P.n_regs * (wide ? 2 : 1) * 4096;
-  if (per_chunk > 190 * 1024) { why = "register file does not fit shared memory"; return false; }
   // iteration space: collapse dims that every operand walks contiguously
   int64_t numel = 1;
   for (int d = 0; d < it_rank; ++d) numel *= it_shape[d];
@@ -1066,6 +1007,176 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
   for (int k = 0; k < n_out; ++k) P.outputs[k].vec_ok = row_vec ? 1 : 0;
   P.n_consts = (int)consts.size();
   for (size_t k = 0; k < consts.size(); ++k) P.consts[k] = consts[k];
+  // ---- peephole pass (fp32): super-instructions and direct global operands -----------------
+  {
+    auto is_unary = [](uint8_t op) {
+      return op == E_NEG || op == E_EXP || op == E_LOG || op == E_ABS || op == E_SIGN || op == E_SIN || op == E_COS ||
+             op == E_ISNAN || op == E_CVT || op == E_NARROW || op == E_STORE || op == E_RELU || op == E_EXPNEG;
+    };
+    auto n_src = [&](const VInstr& I) { return (I.op == E_LOAD || I.op == E_CONST) ? 0 : (is_unary(I.op) ? 1 : (I.op == E_WHERE ? 3 : 2)); };
+    auto src = [](VInstr& I, int k) -> int& { return k == 0 ? I.a : (k == 1 ? I.b : I.c); };
+    std::vector<char> dead(code.size(), 0);
+    auto recount = [&](std::vector<int>& uses, std::vector<int>& def) {
+      uses.assign(next_v, 0);
+      def.assign(next_v, -1);
+      for (size_t i = 0; i < code.size(); ++i) {
+        if (dead[i]) continue;
+        VInstr& I = code[i];
+        for (int k = 0; k < n_src(I); ++k)
+          if (src(I, k) >= 0) uses[src(I, k)]++;
+        if (I.dst >= 0) def[I.dst] = (int)i;
+      }
+      if (tail_reg_v >= 0) uses[tail_reg_v] += 2;
+    };
+    std::vector<int> uses, def;
+    recount(uses, def);
+    for (size_t i = 0; i < code.size(); ++i) {
+      if (dead[i]) continue;
+      VInstr& I = code[i];
+      if (I.type != T_F32) continue;
+      if (I.op == E_WHERE && I.a >= 0 && I.b >= 0 && I.c >= 0 && def[I.a] >= 0 && def[I.c] >= 0) {
+        VInstr& C = code[def[I.a]];
+        VInstr& Z = code[def[I.c]];
+        if (C.op == E_CMP && C.type == T_F32 && C.aux == BG_CMP_GT && C.a == I.b && C.b == I.c && uses[I.a] == 1 &&
+            Z.op == E_CONST && Z.type == T_F32 && consts[Z.aux] == 0) {
+          dead[def[I.a]] = 1;
+          I.op = E_RELU;
+          I.a = I.b;
+          I.b = I.c = 0;
+          recount(uses, def);
+        }
+      } else if (I.op == E_EXP && I.a >= 0 && def[I.a] >= 0) {
+        VInstr& N = code[def[I.a]];
+        if (N.op == E_NEG && N.type == T_F32 && uses[I.a] == 1) {
+          dead[def[I.a]] = 1;
+          I.op = E_EXPNEG;
+          I.a = N.a;
+          recount(uses, def);
+        }
+      } else if (I.op == E_ADD && I.a >= 0 && I.b >= 0) {
+        for (int k = 1; k >= 0; --k) {
+          int v = k ? I.b : I.a;
+          if (def[v] < 0) continue;
+          VInstr& N = code[def[v]];
+          if (N.op == E_NEG && N.type == T_F32 && uses[v] == 1) {
+            int other = k ? I.a : I.b;
+            dead[def[v]] = 1;
+            I.op = E_SUB;
+            I.a = other;
+            I.b = N.a;
+            recount(uses, def);
+            break;
+          }
+        }
+      }
+    }
+    // constants nobody reads any more
+    for (size_t i = 0; i < code.size(); ++i)
+      if (!dead[i] && code[i].op == E_CONST && uses[code[i].dst] == 0) dead[i] = 1;
+    // single-use dense fp32 LOADs become direct operands of their consumer
+    auto f32_value_op = [](uint8_t op) {
+      return op == E_ADD || op == E_SUB || op == E_MUL || op == E_DIV || op == E_NEG || op == E_EXP || op == E_LOG ||
+             op == E_ABS || op == E_SIGN || op == E_SIN || op == E_COS || op == E_RELU || op == E_EXPNEG;
+    };
+    for (size_t i = 0; i < code.size(); ++i) {
+      if (dead[i]) continue;
+      VInstr& I = code[i];
+      if (I.type != T_F32) continue;
+      const bool arith = f32_value_op(I.op);
+      if (!arith && I.op != E_CMP && I.op != E_WHERE) continue;
+      for (int k = (I.op == E_WHERE ? 1 : 0); k < n_src(I); ++k) {
+        int v = src(I, k);
+        if (v < 0 || def[v] < 0 || uses[v] != 1) continue;
+        VInstr& L = code[def[v]];
+        if (L.op != E_LOAD || L.type != T_F32) continue;
+        const EwOperand& o = P.inputs[L.aux];
+        if (o.mode != A_CONTIG || o.dtype != BG_F32 || !o.vec_ok) continue;
+        dead[def[v]] = 1;
+        src(I, k) = -1000 - (int)L.aux;
+      }
+    }
+    // a final STORE of a value produced by fp32 arithmetic becomes that instruction's destination
+    for (size_t i = 0; i < code.size(); ++i) {
+      if (dead[i]) continue;
+      VInstr& S = code[i];
+      if (S.op != E_STORE || S.type != T_F32 || S.a < 0 || def[S.a] < 0) continue;
+      if (uses[S.a] != 1 || S.a == tail_reg_v) continue;
+      const EwOutput& o = P.outputs[S.aux];
+      if (o.dtype != BG_F32 || !o.vec_ok) continue;
+      VInstr& D = code[def[S.a]];
+      if (D.type != T_F32 || !(f32_value_op(D.op) || D.op == E_WHERE)) continue;
+      D.dst = -2000 - (int)S.aux;
+      dead[i] = 1;
+    }
+    std::vector<VInstr> kept;
+    for (size_t i = 0; i < code.size(); ++i)
+      if (!dead[i]) kept.push_back(code[i]);
+    code.swap(kept);
+  }
+  if ((int)code.size() > kEwMaxInstr) { why = "too many instructions"; return false; }
+  // register allocation (linear scan; a destination may take over a source that dies here)
+  std::vector<int> last(next_v, -1);
+  for (size_t i = 0; i < code.size(); ++i) {
+    const VInstr& I = code[i];
+    auto use = [&](int v) { if (v >= 0) last[v] = (int)i; };
+    const bool unary = I.op == E_NEG || I.op == E_EXP || I.op == E_LOG || I.op == E_ABS || I.op == E_SIGN || I.op == E_SIN ||
+                       I.op == E_COS || I.op == E_ISNAN || I.op == E_CVT || I.op == E_NARROW || I.op == E_STORE ||
+                       I.op == E_RELU || I.op == E_EXPNEG;
+    if (I.op == E_LOAD || I.op == E_CONST) continue;
+    use(I.a);
+    if (!unary) use(I.b);
+    if (I.op == E_WHERE) use(I.c);
+  }
+  if (tail_reg_v >= 0) last[tail_reg_v] = (int)code.size() + 1;
+  std::vector<int> phys(next_v, -1);
+  std::vector<char> busy;
+  auto alloc_reg = [&]() {
+    for (size_t i = 0; i < busy.size(); ++i)
+      if (!busy[i]) { busy[i] = 1; return (int)i; }
+    busy.push_back(1);
+    return (int)busy.size() - 1;
+  };
+  bool wide = false;
+  P.n_instr = (int)code.size();
+  for (size_t i = 0; i < code.size(); ++i) {
+    const VInstr& I = code[i];
+    EwInstr& O = P.instr[i];
+    O.op = I.op;
+    O.type = I.type;
+    O.aux = I.aux;
+    const bool unary = I.op == E_NEG || I.op == E_EXP || I.op == E_LOG || I.op == E_ABS || I.op == E_SIGN || I.op == E_SIN ||
+                       I.op == E_COS || I.op == E_ISNAN || I.op == E_CVT || I.op == E_NARROW || I.op == E_STORE ||
+                       I.op == E_RELU || I.op == E_EXPNEG;
+    const bool leaf = I.op == E_LOAD || I.op == E_CONST;
+    int srcs[3] = {leaf ? -1 : I.a, (leaf || unary) ? -1 : I.b, I.op == E_WHERE ? I.c : -1};
+    auto enc = [&](int v) -> uint8_t {
+      if (v <= -1000 && v > -2000) return (uint8_t)(kEwDirect | (-1000 - v));   // direct global input
+      return v >= 0 ? (uint8_t)phys[v] : 0;
+    };
+    O.a = enc(srcs[0]);
+    O.b = enc(srcs[1]);
+    O.c = enc(srcs[2]);
+    for (int k = 0; k < 3; ++k)
+      if (srcs[k] >= 0 && last[srcs[k]] == (int)i && phys[srcs[k]] >= 0) {
+        bool dup = false;
+        for (int j = 0; j < k; ++j) dup |= srcs[j] == srcs[k];
+        if (!dup) busy[phys[srcs[k]]] = 0;
+      }
+    if (I.type == T_F64 || I.type == T_I64) wide = true;
+    if (I.op == E_CVT && ((I.aux & 0xF) == T_F64 || (I.aux & 0xF) == T_I64)) wide = true;
+    if (I.dst <= -2000) O.dst = (uint8_t)(kEwDirect | (-2000 - I.dst));   // direct global output
+    if (I.dst >= 0) {
+      phys[I.dst] = alloc_reg();
+      O.dst = (uint8_t)phys[I.dst];
+      if (last[I.dst] < 0) busy[phys[I.dst]] = 0;
+    }
+  }
+  if (busy.size() > 120) { why = "too many live registers"; return false; }
+  P.n_regs = std::max<int>(1, (int)busy.size());
+  P.wide = wide ? 1 : 0;
+  if (tail_reg_v >= 0) P.tail_reg = phys[tail_reg_v];
+  const int64_t per_chunk = (int64_t)P.n_regs * (wide ? 2 : 1) * 4096;
+  if (per_chunk > 190 * 1024) { why = "register file does not fit shared memory"; return false; }
   ps.row = tail_node >= 0;
   if (ps.row && P.tail != TAIL_REDUCE) {
     const int64_t chunks = (cols + 1023) / 1024;
