@@ -55,7 +55,7 @@ class ResourceStats(C.Structure):
 
 
 class ProfileEntry(C.Structure):
-    _fields_ = [("name", C.c_char * 48), ("ms", C.c_float), ("launches", C.c_int32)]
+    _fields_ = [("name", C.c_char * 64), ("ms", C.c_float), ("launches", C.c_int32)]
 
 
 # name -> (restype, argtypes); every symbol include/bgcuda.h declares

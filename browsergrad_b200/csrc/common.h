@@ -129,6 +129,17 @@ cudaError_t launch_rowwise(const EwProgram& p, cudaStream_t s, int sm_count, int
 // Row-mode capacity: how many 1024-element chunks per row the shared-memory register file holds.
 int rowwise_max_chunks(int n_regs, int wide);
 
+// Specialised fp32 pattern kernels (ew_static.cu).
+struct StaticArgs {
+  const float* in[4];
+  float* out;
+  int64_t rows, cols, numel;
+};
+enum StaticKind { SK_FLAT = 0, SK_ROWSUM = 1, SK_SOFTMAX = 2 };
+int static_pattern_id(const std::string& signature, int* n_inputs);
+bool static_shape_ok(int kind, int64_t rows, int64_t cols, int64_t numel, int sm_count);
+cudaError_t launch_static(int pattern, int kind, const StaticArgs& a, int arg, cudaStream_t s, int sm_count);
+
 struct StridedView {
   const void* ptr;
   int32_t dtype;

@@ -175,6 +175,10 @@ struct ProgramSpec {
   int64_t in_off_bytes[kEwMaxInputs];
   int out_slot[kEwMaxOutputs];
   bool row = false;
+  int static_pattern = -1;   // >= 0: run the specialised kernel for this expression
+  int static_kind = 0;
+  int static_arg = 0;
+  std::string signature;
 };
 
 class Compiler {
@@ -1185,7 +1189,92 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
   return true;
 }
 
+// Expression of an all-fp32 single-result program as text, e.g. "mul(relu(add(mul(i0,i1),i2)),expneg(i3))".
+// Empty when the program is not a pure fp32 expression over dense vector-aligned operands.
+static std::string program_signature(const EwProgram& P, int* kind, int* arg) {
+  std::map<int, std::string> reg;
+  std::string result;
+  int n_results = 0;
+  auto opname = [](int op) -> const char* {
+    switch (op) {
+      case E_ADD: return "add"; case E_SUB: return "sub"; case E_MUL: return "mul"; case E_DIV: return "div";
+      case E_NEG: return "neg"; case E_EXP: return "exp"; case E_LOG: return "log"; case E_RELU: return "relu";
+      case E_EXPNEG: return "expneg"; case E_ABS: return "abs";
+    }
+    return nullptr;
+  };
+  auto dense = [&](int k) {
+    const EwOperand& o = P.inputs[k];
+    return o.mode == A_CONTIG && o.dtype == BG_F32 && o.vec_ok;
+  };
+  bool ok = true;
+  auto operand = [&](uint8_t r) -> std::string {
+    if (r & kEwDirect) {
+      if (!dense(r & 0x7f)) ok = false;
+      return "i" + std::to_string(r & 0x7f);
+    }
+    auto it = reg.find(r);
+    if (it == reg.end()) { ok = false; return "?"; }
+    return it->second;
+  };
+  for (int i = 0; i < P.n_instr && ok; ++i) {
+    const EwInstr& I = P.instr[i];
+    if (I.type != T_F32) return "";
+    std::string v;
+    if (I.op == E_LOAD) {
+      if (!dense(I.aux)) return "";
+      v = "i" + std::to_string(I.aux);
+    } else if (I.op == E_STORE) {
+      if (P.outputs[I.aux].dtype != BG_F32 || !P.outputs[I.aux].vec_ok) return "";
+      result = operand(I.a);
+      ++n_results;
+      continue;
+    } else {
+      const char* nm = opname(I.op);
+      if (!nm) return "";
+      const bool binary = I.op == E_ADD || I.op == E_SUB || I.op == E_MUL || I.op == E_DIV;
+      v = std::string(nm) + "(" + operand(I.a) + (binary ? "," + operand(I.b) : "") + ")";
+    }
+    if (I.dst & kEwDirect) {
+      if (P.outputs[I.dst & 0x7f].dtype != BG_F32 || !P.outputs[I.dst & 0x7f].vec_ok) return "";
+      result = v;
+      ++n_results;
+    } else {
+      reg[I.dst] = v;
+    }
+  }
+  if (!ok) return "";
+  if (P.tail == TAIL_NONE) {
+    if (n_results != 1 || P.n_outputs != 1) return "";
+    *kind = SK_FLAT;
+    return result;
+  }
+  if (n_results != 0 || P.n_outputs != 1 || P.tail_type != T_F32 || P.tail_out_dtype != BG_F32) return "";
+  auto it = reg.find(P.tail_reg);
+  if (it == reg.end()) return "";
+  if (P.tail == TAIL_SOFTMAX) { *kind = SK_SOFTMAX; return it->second; }
+  if (P.tail == TAIL_REDUCE && (P.tail_arg == BG_RED_SUM || P.tail_arg == BG_RED_MEAN)) {
+    *kind = SK_ROWSUM;
+    *arg = P.tail_arg == BG_RED_MEAN;
+    return it->second;
+  }
+  return "";
+}
+
 static int run_program(Run& r, const ProgramSpec& ps) {
+  if (ps.static_pattern >= 0) {
+    const EwProgram& P = ps.prog;
+    StaticArgs a{};
+    for (int k = 0; k < P.n_inputs && k < 4; ++k)
+      a.in[k] = reinterpret_cast<const float*>(reinterpret_cast<char*>(r.ptr[ps.in_slot[k]]) + ps.in_off_bytes[k]);
+    a.out = reinterpret_cast<float*>(r.ptr[ps.out_slot[0]]);
+    a.rows = P.rows;
+    a.cols = P.cols;
+    a.numel = P.numel;
+    cudaError_t e = launch_static(ps.static_pattern, ps.static_kind, a, ps.static_arg, r.ctx->stream, r.ctx->sm_count);
+    if (e != cudaSuccess) return cuda_fail(r.ctx, e, "pattern kernel launch");
+    return BG_OK;
+  }
   EwProgram p = ps.prog;
   for (int k = 0; k < p.n_inputs; ++k)
     p.inputs[k].ptr = reinterpret_cast<char*>(r.ptr[ps.in_slot[k]]) + ps.in_off_bytes[k];
@@ -1202,7 +1291,19 @@ void Compiler::emit_group(const std::vector<int>& members, int tail_node, int ke
   std::string why;
   if (!build_program(members, tail_node, *ps, pu.dep_nodes, pu.out_nodes, why)) throw CompileError{-1, why};
   pu.order_key = key;
+  if (ctx_->static_patterns) {
+    int kind = 0, arg = 0, nin = 0;
+    ps->signature = program_signature(ps->prog, &kind, &arg);
+    const int pat = ps->signature.empty() ? -1 : static_pattern_id(ps->signature, &nin);
+    if (pat >= 0 && nin == ps->prog.n_inputs &&
+        static_shape_ok(kind, ps->prog.rows, ps->prog.cols, ps->prog.numel, ctx_->sm_count)) {
+      ps->static_pattern = pat;
+      ps->static_kind = kind;
+      ps->static_arg = arg;
+    }
+  }
   std::ostringstream nm;
+  if (ps->static_pattern >= 0) nm << "static_";
   nm << (tail_node >= 0 ? "row" : "ew") << "[";
   for (size_t i = 0; i < members.size() && i < 6; ++i) nm << (i ? "," : "") << op_name(nodes_[members[i]].op);
   if (members.size() > 6) nm << ",+" << members.size() - 6;
@@ -1841,6 +1942,7 @@ extern "C" int bg_compile_plan_dry(const bg_plan* plan, int fusion, char* out, s
   if (!plan || !out || capacity == 0) return BG_ERR_INVALID;
   bg_context fake;
   fake.fusion = fusion != 0;
+  fake.sm_count = 148;
   std::string text;
   int rc = BG_OK;
   try {

@@ -37,6 +37,7 @@ struct bg_context {
   int f64_mode = 2;
   bool fusion = true;
   bool tensor_cores = true;
+  bool static_patterns = true;   // use the specialised pattern kernels where an expression matches
   // device status word written by kernels that can refuse (index range, bounded waits)
   int* d_status = nullptr;
   int* h_status = nullptr;  // pinned

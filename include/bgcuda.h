@@ -143,7 +143,7 @@ typedef struct bg_resource_stats {
 
 /* One timed launch, the role of `DirectDispatchProfile` (runner.ts:409-507). */
 typedef struct bg_profile_entry {
-  char name[48];
+  char name[64];
   float ms;
   int32_t launches;
 } bg_profile_entry;

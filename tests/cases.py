@@ -121,6 +121,13 @@ CASES: Dict[str, Case] = {
                                  lambda api, t, raw: configs.chain_rowsoftmax(api, t)),
     "c2_rowsoftmax_long": Case(lambda: configs.chain_inputs(3, 9001),
                                lambda api, t, raw: configs.chain_rowsoftmax(api, t)),
+    # shapes large enough to take the specialised pattern kernels (warp-per-row sum, CTA-per-row softmax)
+    "c2_y_static": Case(lambda: configs.chain_inputs(96, 1030),
+                        lambda api, t, raw: configs.chain_y(api, t)),
+    "c2_rowsum_static": Case(lambda: configs.chain_inputs(1280, 388),
+                             lambda api, t, raw: configs.chain_rowsum(api, t)),
+    "c2_rowsoftmax_static": Case(lambda: configs.chain_inputs(160, 1028),
+                                 lambda api, t, raw: configs.chain_rowsoftmax(api, t)),
     "c3_linear_gelu": Case(lambda: configs.linear_inputs(96, 80, 72),
                            lambda api, t, raw: configs.linear_gelu(api, t)),
     "c3_linear_gelu_128": Case(lambda: configs.linear_inputs(256, 128, 192),

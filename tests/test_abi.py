@@ -61,7 +61,18 @@ def test_config2_chains_compile_to_one_kernel_each():
         t, _, _ = build_case(CASES[name])
         _, plan = front.plan_for(t._uop)
         rc, lines = dry(plan)
-        assert rc == 0 and len(lines) == 1 and lines[0].startswith(kind), lines
+        assert rc == 0 and len(lines) == 1 and lines[0].replace("static_", "").startswith(kind), lines
+
+
+def test_full_size_config2_takes_the_pattern_kernels():
+    import numpy as np
+    from browsergrad_b200 import configs, graph
+    store = graph.BufferStore()
+    t = {k: graph.from_numpy(np.zeros((16384, 4096), np.float32), store) for k in "abcd"}
+    for build in (configs.chain_y, configs.chain_rowsum, configs.chain_rowsoftmax):
+        _, plan = front.plan_for(build(graph, t)._uop)
+        rc, lines = dry(plan)
+        assert rc == 0 and len(lines) == 1 and lines[0].startswith("static_"), lines
 
 
 def test_unsupported_opcode_mentions_numpy_fallback():

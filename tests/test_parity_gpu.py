@@ -38,3 +38,25 @@ def test_unfused_execution_matches_too(bridge, name):
     finally:
         bridge.set_option("fusion", 1)
     check(case, got, want, name + " (fusion off)")
+
+
+@pytest.mark.parametrize("name", ["c2_y", "c2_y_static", "c2_rowsum_static", "c2_rowsoftmax_static", "c2_rowsoftmax_long"])
+def test_pattern_kernels_and_interpreter_agree(bridge, name):
+    """The specialised pattern kernels and the generic interpreter compute the same bits."""
+    case = CASES[name]
+    t, store, _ = build_case(case)
+    got_static = realize_cuda(t, bridge)
+    static_trace = bridge.last_plan_trace()
+    bridge.set_option("static_patterns", 0)
+    try:
+        got_generic = realize_cuda(t, bridge)
+        generic_trace = bridge.last_plan_trace()
+    finally:
+        bridge.set_option("static_patterns", 1)
+    assert not any(ln.startswith("static_") for ln in generic_trace)
+    if name.endswith("_static"):
+        assert any(ln.startswith("static_") for ln in static_trace), static_trace
+    if "rowsum" in name:
+        check(case, got_static, got_generic, name)      # summation order differs
+    else:
+        assert got_static.tobytes() == got_generic.tobytes()
