@@ -184,4 +184,26 @@ struct GemmProblem {
 // Reference-order SIMT GEMM for every dtype (fp32 FMA, fp64 FMA, exact int64).
 cudaError_t launch_gemm_simt(const GemmProblem& p, cudaStream_t s);
 
+// Tensor-core GEMM (gemm_tc.cu): C[M,N] = epilogue(A[M,K] . B[N,K]^T), operands dense row-major.
+enum TcAct { TC_ACT_NONE = 0, TC_ACT_RELU = 1, TC_ACT_GELU = 2 };
+struct TcGemm {
+  int64_t M, N, K;
+  const void* A;        // [M,K]: f16 / bf16, or the tf32-rounded "hi" part of an fp32 operand
+  const void* B;        // [N,K]
+  const void* A_lo;     // fp32 residual parts (3xTF32 only)
+  const void* B_lo;
+  int ab_dtype;         // BG_F16, BG_BF16, or BG_F32 (3xTF32)
+  void* C;              // [M,N] dense
+  int c_dtype;          // BG_F32, BG_F16, BG_BF16, BG_F64
+  const void* bias;     // [N] or null
+  int bias_dtype;
+  int act;              // TcAct
+  int round_acc;        // 0, or dtype + 1: round the accumulator through f16 / bf16 before the epilogue
+  int wide;             // activation arithmetic in fp64 (for fp64 results)
+};
+bool tc_gemm_supported(int64_t M, int64_t N, int64_t K, int ab_dtype);
+cudaError_t launch_gemm_tc(const TcGemm& g, int* status, cudaStream_t s);
+// hi = tf32(x) (round to nearest), lo = x - hi, for fp32 or fp64 input; optional transpose is not done here.
+cudaError_t launch_tf32_split(const void* src, int src_dtype, float* hi, float* lo, int64_t n, cudaStream_t s);
+
 }  // namespace bg

@@ -1,0 +1,473 @@
+// Tensor-core GEMM for sm_100a: tcgen05.mma with the accumulator in tensor memory, operand tiles
+// staged in shared memory by TMA, fused bias / activation / conversion epilogue.
+//
+//   C[M,N] = epilogue( A[M,K] . B[N,K]^T )          both operands K-major (row-major [rows, K])
+//
+// One CTA computes one 128 x BN output tile (BN = 128 or 256) with three specialised roles:
+//   warp 0     TMA producer: cp.async.bulk.tensor loads of 128-byte-swizzled A / B tiles into a
+//              ring of shared-memory stages, completion counted on "full" mbarriers;
+//   warp 1     MMA issuer: one elected thread issues tcgen05.mma (128 x BN x 32 bytes of K per
+//              instruction) into the TMEM accumulator and releases stages with tcgen05.commit;
+//   warps 2-5  epilogue: tcgen05.ld of the 128 accumulator lanes, bias / activation / rounding,
+//              vector stores of the result rows.
+// Loads carry no cluster multicast.  Two operand encodings share the kernel:
+//   * 16-bit (f16 / bf16) operands, fp32 accumulate;
+//   * 3xTF32 for fp32-faithful results: A and B are pre-split into hi = tf32(x) and lo = x - hi;
+//     the K loop runs three passes (lo.hi, hi.lo, hi.hi - small terms first) into one accumulator.
+// Every wait is bounded by a clock deadline; on expiry the kernel records
+// BG_ERR_DEVICE_TIMEOUT in the status word, lets copies in flight land, frees its tensor memory
+// and returns.
+#include "common.h"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace bg {
+namespace {
+
+constexpr int BM = 128;
+constexpr int kStageRowBytes = 128;          // one swizzle row: 64 x 16-bit or 32 x tf32
+constexpr int kTcThreads = 192;
+constexpr long long kWaitCycles = 2000000000ll;   // ~1 s at 1.9 GHz
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the deadline passes (the caller then abandons its role).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, void* smem_dst, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+  // K-major operand tile, rows of 128 bytes, 128-byte swizzle: 8-row groups are 1024 bytes apart.
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);           // start address
+  d |= (uint64_t)1 << 16;                                // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                                // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                                // SWIZZLE_128B
+  return d;
+}
+
+template <bool TF32>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  if (TF32) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+struct TcParams {
+  int M, N;
+  int num_k_blocks;     // K blocks of 128 bytes per pass
+  int passes;           // 1, or 3 for the hi/lo split
+  int elems_per_block;  // K elements per 128-byte block (64 or 32)
+  void* C;
+  int c_dtype;
+  const void* bias;     // per-column (length N) or null
+  int bias_dtype;
+  int act;              // TcAct
+  int round_acc;        // 0: none, BG_F16 + 1 / BG_BF16 + 1: round the accumulator through that dtype first
+  int wide;             // activation arithmetic in fp64
+  uint32_t idesc;
+  int group_m;
+  int* status;
+};
+
+// gelu(x) with the op order of the reference graph: 0.5*x*(1 + tanh(c*(x + 0.044715*x*x*x))),
+// tanh(u) = (e^u - e^-u) / (e^u + e^-u)
+template <typename T>
+__device__ __forceinline__ T gelu_graph(T x) {
+  const T c = (T)0.7978845608028654;
+  T t = (T)0.044715 * x;
+  t = t * x;
+  t = t * x;
+  T u = c * (x + t);
+  T ep = sizeof(T) == 8 ? (T)exp((double)u) : (T)expf((float)u);
+  T en = sizeof(T) == 8 ? (T)exp((double)-u) : (T)expf((float)-u);
+  T th = (ep + (-en)) / (ep + en);
+  return ((T)0.5 * x) * ((T)1.0 + th);
+}
+
+__device__ __forceinline__ float load_bias(const void* b, int dt, int col) {
+  switch (dt) {
+    case BG_F32: return reinterpret_cast<const float*>(b)[col];
+    case BG_F16: return __half2float(reinterpret_cast<const __half*>(b)[col]);
+    case BG_BF16: return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(b)[col]);
+    default: return (float)reinterpret_cast<const double*>(b)[col];
+  }
+}
+
+template <int BN, bool TF32>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+               const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
+               const __grid_constant__ TcParams p) {
+  constexpr int kABytes = BM * kStageRowBytes;
+  constexpr int kBBytes = BN * kStageRowBytes;
+  constexpr int kStageBytes = kABytes + kBBytes;
+  constexpr int kStages = (BN == 256) ? 4 : 6;
+  constexpr int kTmemCols = BN;   // power of two >= 32
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* accum_bar = empty_bar + kStages;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // tile coordinates: groups of `group_m` row blocks share their B column blocks in L2
+  const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
+  const int tile = blockIdx.x;
+  const int gsz = p.group_m * num_n;
+  const int g = tile / gsz;
+  const int first_m = g * p.group_m;
+  const int gm = min(p.group_m, num_m - first_m);
+  const int m_blk = first_m + (tile % gsz) % gm;
+  const int n_blk = (tile % gsz) / gm;
+  const int m0 = m_blk * BM, n0 = n_blk * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = *tmem_holder;
+  const int total_iters = p.num_k_blocks * p.passes;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int it = 0; it < total_iters; ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) break;
+        const int pass = it / p.num_k_blocks, kb = it - pass * p.num_k_blocks;
+        // passes of the split product: lo.hi, hi.lo, hi.hi (a single pass uses map 0 of each operand)
+        const CUtensorMap* ma = (p.passes == 3 && pass == 0) ? &tmA1 : &tmA0;
+        const CUtensorMap* mb = (p.passes == 3 && pass == 1) ? &tmB1 : &tmB0;
+        unsigned char* sa = smem + s * kStageBytes;
+        mbar_expect_tx(&full_bar[s], kStageBytes);
+        tma_load_2d(ma, sa, &full_bar[s], kb * p.elems_per_block, m0);
+        tma_load_2d(mb, sa + kABytes, &full_bar[s], kb * p.elems_per_block, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int it = 0; it < total_iters && ok; ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+        if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + s * kStageBytes);
+        const uint64_t da = make_kmajor_sw128_desc(sa), db = make_kmajor_sw128_desc(sa + kABytes);
+#pragma unroll
+        for (int k = 0; k < kStageRowBytes / 32; ++k) {
+          // each instruction consumes 32 bytes of K; the start address advances inside the swizzle row
+          umma<TF32>(tmem_acc, da + (uint64_t)(k * 32 >> 4), db + (uint64_t)(k * 32 >> 4), p.idesc, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      if (ok) umma_commit(accum_bar);
+    }
+  } else {
+    // epilogue: warp w may read TMEM lanes 32*(w%4) .. +31
+    const int q = warp & 3;
+    const int row = m0 + q * 32 + lane;
+    bool ok = true;
+    if (total_iters > 0) ok = mbar_wait(accum_bar, 0, abort_flag);
+    tc_fence_after();
+    if (ok) {
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        if (total_iters > 0) tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+        else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0;
+        }
+        const int col0 = n0 + c * 32;
+        if (row >= p.M || col0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float x = __uint_as_float(r[j]);
+          if (p.round_acc == BG_F16 + 1) x = __half2float(__float2half_rn(x));
+          else if (p.round_acc == BG_BF16 + 1) x = __bfloat162float(__float2bfloat16_rn(x));
+          v[j] = x;
+        }
+        if (p.bias) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) v[j] = __fadd_rn(v[j], load_bias(p.bias, p.bias_dtype, col0 + j));
+        }
+        const bool full = col0 + 32 <= p.N;
+        const size_t base = (size_t)row * p.N + col0;
+        if (p.c_dtype == BG_F64) {
+          double* out = reinterpret_cast<double*>(p.C) + base;
+          double w[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            double x = (double)v[j];
+            if (p.act == TC_ACT_RELU) x = x > 0.0 ? x : 0.0;
+            else if (p.act == TC_ACT_GELU) x = p.wide ? gelu_graph<double>(x) : (double)gelu_graph<float>(v[j]);
+            w[j] = x;
+          }
+          if (full && (p.N & 1) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) *reinterpret_cast<double2*>(out + j) = make_double2(w[j], w[j + 1]);
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = w[j];
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float x = v[j];
+            if (p.act == TC_ACT_RELU) x = x > 0.f ? x : 0.f;
+            else if (p.act == TC_ACT_GELU) x = gelu_graph<float>(x);
+            v[j] = x;
+          }
+          if (p.c_dtype == BG_F32) {
+            float* out = reinterpret_cast<float*>(p.C) + base;
+            if (full && (p.N & 3) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = v[j];
+            }
+          } else if (p.c_dtype == BG_F16) {
+            __half* out = reinterpret_cast<__half*>(p.C) + base;
+            if (full && (p.N & 7) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                __half2 h[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) h[t] = __floats2half2_rn(v[j + 2 * t], v[j + 2 * t + 1]);
+                *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<uint4*>(h);
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = __float2half_rn(v[j]);
+            }
+          } else {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + base;
+            if (full && (p.N & 7) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                __nv_bfloat162 h[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(v[j + 2 * t], v[j + 2 * t + 1]);
+                *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<uint4*>(h);
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = __float2bfloat16_rn(v[j]);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // a wait ran out: report, give copies in flight time to land before shared memory is released
+    if (threadIdx.x == 0) atomicExch(p.status, BG_ERR_DEVICE_TIMEOUT);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) {}
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(kTmemCols) : "memory");
+  }
+}
+
+__global__ void tf32_split_kernel(const void* src, int src_dtype, float* hi, float* lo, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float x;
+    double xd = 0.0;
+    if (src_dtype == BG_F64) { xd = reinterpret_cast<const double*>(src)[i]; x = (float)xd; }
+    else x = reinterpret_cast<const float*>(src)[i];
+    uint32_t h;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+    const float fh = __uint_as_float(h);
+    hi[i] = fh;
+    // the residual is exact in fp32; for fp64 sources it also carries the bits fp32 dropped
+    lo[i] = src_dtype == BG_F64 ? (float)(xd - (double)fh) : __fadd_rn(x, -fh);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+        qr == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// [rows, K] row-major operand, box = one 128-byte swizzle row x box_rows; out-of-range elements read as zero.
+bool make_operand_map(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int64_t K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const int es = dtype_size(dtype);
+  CUtensorMapDataType dt = dtype == BG_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                           : dtype == BG_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * es};
+  cuuint32_t box[2] = {(cuuint32_t)(kStageRowBytes / es), (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <int BN, bool TF32>
+cudaError_t launch_variant(const TcGemm& g, int* status, cudaStream_t s) {
+  CUtensorMap a0, a1, b0, b1;
+  if (!make_operand_map(&a0, g.A, g.ab_dtype, g.M, g.K, BM)) return cudaErrorInvalidValue;
+  if (!make_operand_map(&b0, g.B, g.ab_dtype, g.N, g.K, BN)) return cudaErrorInvalidValue;
+  a1 = a0;
+  b1 = b0;
+  if (TF32) {
+    if (!make_operand_map(&a1, g.A_lo, g.ab_dtype, g.M, g.K, BM)) return cudaErrorInvalidValue;
+    if (!make_operand_map(&b1, g.B_lo, g.ab_dtype, g.N, g.K, BN)) return cudaErrorInvalidValue;
+  }
+  TcParams p{};
+  p.M = (int)g.M;
+  p.N = (int)g.N;
+  const int es = dtype_size(g.ab_dtype);
+  p.elems_per_block = kStageRowBytes / es;
+  p.num_k_blocks = (int)((g.K + p.elems_per_block - 1) / p.elems_per_block);
+  p.passes = TF32 ? 3 : 1;
+  p.C = g.C;
+  p.c_dtype = g.c_dtype;
+  p.bias = g.bias;
+  p.bias_dtype = g.bias_dtype;
+  p.act = g.act;
+  p.round_acc = g.round_acc;
+  p.wide = g.wide;
+  p.status = status;
+  p.group_m = 8;
+  const uint32_t fmt = TF32 ? 2u : (g.ab_dtype == BG_BF16 ? 1u : 0u);
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  constexpr int kStages = (BN == 256) ? 4 : 6;
+  const size_t smem = (size_t)kStages * (BM + BN) * kStageRowBytes + 256 + 1024;
+  auto kern = gemm_tc_kernel<BN, TF32>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  const int64_t tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
+  kern<<<(unsigned)tiles, kTcThreads, smem, s>>>(a0, a1, b0, b1, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool tc_gemm_supported(int64_t M, int64_t N, int64_t K, int ab_dtype) {
+  if (!encode_fn()) return false;
+  if (ab_dtype != BG_F16 && ab_dtype != BG_BF16 && ab_dtype != BG_F32) return false;
+  const int es = dtype_size(ab_dtype);
+  if (M <= 0 || N <= 0 || K <= 0) return false;
+  if ((K * es) % 16 != 0) return false;                 // TMA row pitch
+  if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return false;
+  return true;
+}
+
+cudaError_t launch_gemm_tc(const TcGemm& g, int* status, cudaStream_t s) {
+  const bool tf32 = g.ab_dtype == BG_F32;
+  const bool wide_tile = g.N > 128;
+  if (tf32) return wide_tile ? launch_variant<256, true>(g, status, s) : launch_variant<128, true>(g, status, s);
+  return wide_tile ? launch_variant<256, false>(g, status, s) : launch_variant<128, false>(g, status, s);
+}
+
+cudaError_t launch_tf32_split(const void* src, int src_dtype, float* hi, float* lo, int64_t n, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  int64_t grid = (n + 255) / 256;
+  if (grid > 148 * 16) grid = 148 * 16;
+  tf32_split_kernel<<<(unsigned)grid, 256, 0, s>>>(src, src_dtype, hi, lo, n);
+  return cudaGetLastError();
+}
+
+}  // namespace bg

@@ -168,6 +168,19 @@ struct CompileError {
   std::string msg;
 };
 
+// What a tensor-core GEMM unit applies to its accumulator before storing; filled in when the
+// elementwise group that consumes the product is folded into the GEMM.
+struct TcEpilogue {
+  int out_slot = -1;     // >= 0: store here (the folded group's output) instead of the MATMUL slot
+  int out_dtype = BG_F32;
+  int bias_slot = -1;
+  int64_t bias_off = 0;
+  int bias_dtype = BG_F32;
+  int act = TC_ACT_NONE;
+  int round_acc = 0;
+  int wide = 0;
+};
+
 // A fusion group lowered to a program, with slot references to patch at run time.
 struct ProgramSpec {
   EwProgram prog;
@@ -198,6 +211,9 @@ class Compiler {
   std::vector<char> force_break_;
   std::vector<char> leaflike_;
   std::map<int, View> copy_src_;   // RESHAPE nodes that need a dense copy: the strided source view
+  bool has_f64_leaf_ = false;
+  std::map<int, std::shared_ptr<TcEpilogue>> tc_epilogues_;   // MATMUL node -> epilogue fused into its kernel
+  std::map<int, int> tc_unit_of_;
   std::shared_ptr<CompiledPlan> cp_;
   int root_ = -1;
   // scheduling
@@ -467,6 +483,7 @@ void Compiler::build_views() {
       case BG_OP_BUFFER: {
         kind_[i] = K_LEAF;
         leaflike_[i] = 1;
+        if (n.dtype == BG_F64) has_f64_leaf_ = true;
         v.set_dense(n.shape, n.rank);
         v.slot = new_slot(n.numel() * dtype_size(n.dtype), true, i);
         cp_->buffers.push_back({n.step, v.slot});
@@ -1482,6 +1499,99 @@ void Compiler::emit_matmul(int n, int key) {
   own_slot(n);
   const int sa = av.slot, sb = bv.slot, sc = view_[n].slot;
   const int64_t offa = av.off * dtype_size(av.dtype), offb = bv.off * dtype_size(bv.dtype);
+  // ---- tensor-core path -------------------------------------------------------------
+  // 2-D problems whose operands are (or can be copied into) dense K-major matrices:
+  //   f16 x f16 / bf16 x bf16 -> tcgen05 kind::f16;   f32 x f32 -> 3xTF32;
+  //   fp64 results whose values all derive from fp32 data -> 3xTF32 with an fp64 store.
+  if (ctx_->tensor_cores && !a_vec && !b_vec && nbatch == 1 && bs.empty() && gp.m * gp.n * gp.k >= (1ll << 24)) {
+    int mode = -1;  // 0: 16-bit, 1: 3xTF32
+    if (av.dtype == bv.dtype && (av.dtype == BG_F16 || av.dtype == BG_BF16) && t.dtype == av.dtype) mode = 0;
+    else if (av.dtype == BG_F32 && bv.dtype == BG_F32 && t.dtype == BG_F32) mode = 1;
+    else if (t.dtype == BG_F64 && (av.dtype == BG_F32 || av.dtype == BG_F64) && (bv.dtype == BG_F32 || bv.dtype == BG_F64) &&
+             (ctx_->f64_mode == 1 || (ctx_->f64_mode == 2 && !has_f64_leaf_))) mode = 1;
+    const int ab = mode == 0 ? av.dtype : BG_F32;
+    if (mode >= 0 && tc_gemm_supported(gp.m, gp.n, gp.k, ab)) {
+      const int64_t M = gp.m, N = gp.n, K = gp.k;
+      // operand layouts: A wants [M,K] dense, B wants [N,K] dense (i.e. the [K,N] view with unit stride along K)
+      const bool a_dense = gp.a.col_stride == 1 && gp.a.row_stride == K;
+      const bool b_kmajor = gp.b.row_stride == 1 && gp.b.col_stride == K;
+      const int esa = dtype_size(av.dtype), esb = dtype_size(bv.dtype);
+      int a_src = av.slot, b_src = bv.slot;
+      int64_t a_off = offa, b_off = offb;
+      PUnit pu;
+      pu.order_key = key;
+      pu.dep_nodes = {a, b};
+      pu.out_nodes = {n};
+      int a_copy = -1, b_copy = -1;
+      StridedView ta{}, tb{};
+      if (!a_dense) {
+        a_copy = new_slot(M * K * esa, false, -1);
+        pu.u.writes.push_back(a_copy);
+        ta.dtype = av.dtype; ta.rank = 2; ta.shape[0] = M; ta.shape[1] = K; ta.stride[0] = gp.a.row_stride; ta.stride[1] = gp.a.col_stride;
+      }
+      if (!b_kmajor) {
+        b_copy = new_slot(N * K * esb, false, -1);
+        pu.u.writes.push_back(b_copy);
+        tb.dtype = bv.dtype; tb.rank = 2; tb.shape[0] = N; tb.shape[1] = K; tb.stride[0] = gp.b.col_stride; tb.stride[1] = gp.b.row_stride;
+      }
+      int a_hi = -1, a_lo = -1, b_hi = -1, b_lo = -1;
+      if (mode == 1) {
+        a_hi = new_slot(M * K * 4, false, -1); a_lo = new_slot(M * K * 4, false, -1);
+        b_hi = new_slot(N * K * 4, false, -1); b_lo = new_slot(N * K * 4, false, -1);
+        for (int sl : {a_hi, a_lo, b_hi, b_lo}) pu.u.writes.push_back(sl);
+      }
+      const int a_dt = av.dtype, b_dt = bv.dtype, c_dt = t.dtype;
+      auto epi = std::make_shared<TcEpilogue>();
+      tc_epilogues_[n] = epi;
+      pu.u.launches = 1 + (a_copy >= 0) + (b_copy >= 0) + (mode == 1 ? 2 : 0);
+      pu.u.name = std::string(mode == 0 ? "gemm_tc[" : "gemm_tc_3xtf32[") + dtype_name(t.dtype) + "]";
+      cp_->uses_status = true;
+      const int sc_slot = sc;
+      pu.u.fn = [=](Run& r) {
+        cudaStream_t st = r.ctx->stream;
+        const void* pa = reinterpret_cast<char*>(r.ptr[a_src]) + a_off;
+        const void* pb = reinterpret_cast<char*>(r.ptr[b_src]) + b_off;
+        cudaError_t e = cudaSuccess;
+        if (a_copy >= 0) {
+          StridedView v = ta; v.ptr = pa;
+          e = launch_strided_copy(v, r.ptr[a_copy], M * K, st);
+          if (e != cudaSuccess) return cuda_fail(r.ctx, e, "gemm operand copy");
+          pa = r.ptr[a_copy];
+        }
+        if (b_copy >= 0) {
+          StridedView v = tb; v.ptr = pb;
+          e = launch_strided_copy(v, r.ptr[b_copy], N * K, st);
+          if (e != cudaSuccess) return cuda_fail(r.ctx, e, "gemm operand copy");
+          pb = r.ptr[b_copy];
+        }
+        TcGemm g{};
+        g.M = M; g.N = N; g.K = K;
+        g.ab_dtype = ab;
+        if (mode == 1) {
+          e = launch_tf32_split(pa, a_dt, (float*)r.ptr[a_hi], (float*)r.ptr[a_lo], M * K, st);
+          if (e == cudaSuccess) e = launch_tf32_split(pb, b_dt, (float*)r.ptr[b_hi], (float*)r.ptr[b_lo], N * K, st);
+          if (e != cudaSuccess) return cuda_fail(r.ctx, e, "tf32 split launch");
+          g.A = r.ptr[a_hi]; g.A_lo = r.ptr[a_lo]; g.B = r.ptr[b_hi]; g.B_lo = r.ptr[b_lo];
+        } else {
+          g.A = pa; g.B = pb;
+        }
+        g.C = r.ptr[epi->out_slot >= 0 ? epi->out_slot : sc_slot];
+        g.c_dtype = epi->out_slot >= 0 ? epi->out_dtype : c_dt;
+        if (epi->bias_slot >= 0) {
+          g.bias = reinterpret_cast<char*>(r.ptr[epi->bias_slot]) + epi->bias_off;
+          g.bias_dtype = epi->bias_dtype;
+        }
+        g.act = epi->act;
+        g.round_acc = epi->round_acc;
+        g.wide = epi->wide;
+        e = launch_gemm_tc(g, r.ctx->d_status, st);
+        return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "tensor-core gemm launch");
+      };
+      tc_unit_of_[n] = (int)punits_.size();
+      add_unit(std::move(pu));
+      return;
+    }
+  }
   PUnit pu;
   pu.order_key = key;
   pu.dep_nodes = {a, b};
@@ -1574,6 +1684,9 @@ bool Compiler::try_lower() {
   punits_.clear();
   nodes_.clear();
   copy_src_.clear();
+  tc_epilogues_.clear();
+  tc_unit_of_.clear();
+  has_f64_leaf_ = false;
   expand();
   simplify();
   build_views();

@@ -140,6 +140,20 @@ CASES: Dict[str, Case] = {
     "c3_linear_gelu_bf16": Case(lambda: configs.linear_inputs(256, 128, 192),
                                 lambda api, t, raw: configs.linear_gelu(api, t, "bfloat16"),
                                 rtol=2e-2, reference_has_it=False),
+    # large enough for the tensor-core GEMM (>= 2^24 multiply-adds), with ragged M / N tiles
+    "c3_tc_f32": Case(lambda: configs.linear_inputs(256, 384, 320),
+                      lambda api, t, raw: configs.linear_gelu(api, t)),
+    "c3_tc_f16": Case(lambda: configs.linear_inputs(256, 384, 320),
+                      lambda api, t, raw: configs.linear_gelu(api, t, "float16"), rtol=2e-2),
+    "c3_tc_bf16": Case(lambda: configs.linear_inputs(256, 384, 320),
+                       lambda api, t, raw: configs.linear_gelu(api, t, "bfloat16"), rtol=2e-2,
+                       reference_has_it=False),
+    "c3_tc_ragged": Case(lambda: configs.linear_inputs(300, 264, 296),
+                         lambda api, t, raw: api.linear(t["x"], t["w"], t["bias"])),
+    "c3_tc_relu": Case(lambda: configs.linear_inputs(300, 264, 296),
+                       lambda api, t, raw: api.relu(api.linear(t["x"], t["w"], t["bias"]))),
+    "c3_tc_rowmajor_b": Case(lambda: configs.linear_inputs(256, 256, 256),
+                             lambda api, t, raw: t["x"] @ t["w"]),
     "c4_attn_mask": Case(_attn_small(2, 3, 64, 16),
                          lambda api, t, raw: configs.attention(api, t, "mask")),
     "c4_attn_causal": Case(_attn_small(2, 3, 64, 16),
