@@ -160,6 +160,93 @@ __device__ __forceinline__ float load_bias(const void* b, int dt, int col) {
   }
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Epilogue of one 32-column chunk of one accumulator row: rounding, bias, activation, store.
+__device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t* r, int row, int col0) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float x = __uint_as_float(r[j]);
+    if (p.round_acc == BG_F16 + 1) x = __half2float(__float2half_rn(x));
+    else if (p.round_acc == BG_BF16 + 1) x = __bfloat162float(__float2bfloat16_rn(x));
+    v[j] = x;
+  }
+  if (p.bias) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N) v[j] = __fadd_rn(v[j], load_bias(p.bias, p.bias_dtype, col0 + j));
+  }
+  const bool full = col0 + 32 <= p.N;
+  const size_t base = (size_t)row * p.N + col0;
+  if (p.c_dtype == BG_F64) {
+    double* out = reinterpret_cast<double*>(p.C) + base;
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      double w[2];
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        double x = (double)v[j + t];
+        if (p.act == TC_ACT_RELU) x = x > 0.0 ? x : 0.0;
+        else if (p.act == TC_ACT_GELU) x = p.wide ? gelu_graph<double>(x) : (double)gelu_graph<float>(v[j + t]);
+        w[t] = x;
+      }
+      if (full && (p.N & 1) == 0) *reinterpret_cast<double2*>(out + j) = make_double2(w[0], w[1]);
+      else {
+        if (col0 + j < p.N) out[j] = w[0];
+        if (col0 + j + 1 < p.N) out[j + 1] = w[1];
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float x = v[j];
+    if (p.act == TC_ACT_RELU) x = x > 0.f ? x : 0.f;
+    else if (p.act == TC_ACT_GELU) x = gelu_graph<float>(x);
+    v[j] = x;
+  }
+  if (p.c_dtype == BG_F32) {
+    float* out = reinterpret_cast<float*>(p.C) + base;
+    if (full && (p.N & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+      for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = v[j];
+    }
+  } else if (p.c_dtype == BG_F16) {
+    __half* out = reinterpret_cast<__half*>(p.C) + base;
+    if (full && (p.N & 7) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        __half2 h[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) h[t] = __floats2half2_rn(v[j + 2 * t], v[j + 2 * t + 1]);
+        *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<uint4*>(h);
+      }
+    } else {
+      for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = __float2half_rn(v[j]);
+    }
+  } else {
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + base;
+    if (full && (p.N & 7) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        __nv_bfloat162 h[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(v[j + 2 * t], v[j + 2 * t + 1]);
+        *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<uint4*>(h);
+      }
+    } else {
+      for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = __float2bfloat16_rn(v[j]);
+    }
+  }
+}
+
+// Persistent kernel: each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The accumulator is
+// double-buffered in tensor memory, so the epilogue of tile t overlaps the MMAs of tile t + 1.
 template <int BN, bool TF32>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
@@ -169,31 +256,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
   constexpr int kBBytes = BN * kStageRowBytes;
   constexpr int kStageBytes = kABytes + kBBytes;
   constexpr int kStages = (BN == 256) ? 4 : 6;
-  constexpr int kTmemCols = BN;   // power of two >= 32
+  constexpr int kTmemCols = 2 * BN;   // two accumulators; a power of two >= 32
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
   uint64_t* empty_bar = full_bar + kStages;
-  uint64_t* accum_bar = empty_bar + kStages;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  uint64_t* acc_full = empty_bar + kStages;    // [2] MMAs of a tile have completed
+  uint64_t* acc_empty = acc_full + 2;          // [2] the epilogue has drained the buffer
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // tile coordinates: groups of `group_m` row blocks share their B column blocks in L2
   const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
-  const int tile = blockIdx.x;
+  const int num_tiles = num_m * num_n;
   const int gsz = p.group_m * num_n;
-  const int g = tile / gsz;
-  const int first_m = g * p.group_m;
-  const int gm = min(p.group_m, num_m - first_m);
-  const int m_blk = first_m + (tile % gsz) % gm;
-  const int n_blk = (tile % gsz) / gm;
-  const int m0 = m_blk * BM, n0 = n_blk * BN;
+  // tile id -> block coordinates: groups of `group_m` row blocks share their B column blocks in L2
+  auto tile_origin = [&](int tile, int& m0, int& n0) {
+    const int g = tile / gsz;
+    const int first_m = g * p.group_m;
+    const int gm = min(p.group_m, num_m - first_m);
+    m0 = (first_m + (tile % gsz) % gm) * BM;
+    n0 = ((tile % gsz) / gm) * BN;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -204,138 +293,86 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_acc = *tmem_holder;
-  const int total_iters = p.num_k_blocks * p.passes;
+  const uint32_t tmem_base = *tmem_holder;
+  const int iters_per_tile = p.num_k_blocks * p.passes;
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int it = 0; it < total_iters; ++it) {
-        const int s = it % kStages;
-        const uint32_t ph = (uint32_t)(it / kStages) & 1u;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) break;
-        const int pass = it / p.num_k_blocks, kb = it - pass * p.num_k_blocks;
-        // passes of the split product: lo.hi, hi.lo, hi.hi (a single pass uses map 0 of each operand)
-        const CUtensorMap* ma = (p.passes == 3 && pass == 0) ? &tmA1 : &tmA0;
-        const CUtensorMap* mb = (p.passes == 3 && pass == 1) ? &tmB1 : &tmB0;
-        unsigned char* sa = smem + s * kStageBytes;
-        mbar_expect_tx(&full_bar[s], kStageBytes);
-        tma_load_2d(ma, sa, &full_bar[s], kb * p.elems_per_block, m0);
-        tma_load_2d(mb, sa + kABytes, &full_bar[s], kb * p.elems_per_block, n0);
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int m0, n0;
+        tile_origin(tile, m0, n0);
+        for (int k = 0; k < iters_per_tile; ++k, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+          const int pass = k / p.num_k_blocks, kb = k - pass * p.num_k_blocks;
+          // passes of the split product: lo.hi, hi.lo, hi.hi (a single pass uses map 0 of each operand)
+          const CUtensorMap* ma = (p.passes == 3 && pass == 0) ? &tmA1 : &tmA0;
+          const CUtensorMap* mb = (p.passes == 3 && pass == 1) ? &tmB1 : &tmB0;
+          unsigned char* sa = smem + s * kStageBytes;
+          mbar_expect_tx(&full_bar[s], kStageBytes);
+          tma_load_2d(ma, sa, &full_bar[s], kb * p.elems_per_block, m0);
+          tma_load_2d(mb, sa + kABytes, &full_bar[s], kb * p.elems_per_block, n0);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      int it = 0, t = 0;
       bool ok = true;
-      for (int it = 0; it < total_iters && ok; ++it) {
-        const int s = it % kStages;
-        const uint32_t ph = (uint32_t)(it / kStages) & 1u;
-        if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+        const int buf = t & 1;
+        if (!mbar_wait(&acc_empty[buf], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sa = smem_u32(smem + s * kStageBytes);
-        const uint64_t da = make_kmajor_sw128_desc(sa), db = make_kmajor_sw128_desc(sa + kABytes);
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN);
+        for (int k = 0; k < iters_per_tile; ++k, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * kStageBytes);
+          const uint64_t da = make_kmajor_sw128_desc(sa), db = make_kmajor_sw128_desc(sa + kABytes);
 #pragma unroll
-        for (int k = 0; k < kStageRowBytes / 32; ++k) {
-          // each instruction consumes 32 bytes of K; the start address advances inside the swizzle row
-          umma<TF32>(tmem_acc, da + (uint64_t)(k * 32 >> 4), db + (uint64_t)(k * 32 >> 4), p.idesc, (it > 0 || k > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kStageRowBytes / 32; ++kk) {
+            // each instruction consumes 32 bytes of K; the start address advances inside the swizzle row
+            umma<TF32>(tmem_acc, da + (uint64_t)(kk * 32 >> 4), db + (uint64_t)(kk * 32 >> 4), p.idesc, (k > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);
         }
-        umma_commit(&empty_bar[s]);
+        if (ok) umma_commit(&acc_full[buf]);
       }
-      if (ok) umma_commit(accum_bar);
     }
   } else {
     // epilogue: warp w may read TMEM lanes 32*(w%4) .. +31
     const int q = warp & 3;
-    const int row = m0 + q * 32 + lane;
+    int t = 0;
     bool ok = true;
-    if (total_iters > 0) ok = mbar_wait(accum_bar, 0, abort_flag);
-    tc_fence_after();
-    if (ok) {
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+      int m0, n0;
+      tile_origin(tile, m0, n0);
+      const int buf = t & 1;
+      const int row = m0 + q * 32 + lane;
+      if (iters_per_tile > 0) ok = mbar_wait(&acc_full[buf], (uint32_t)(t >> 1) & 1u, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
-        if (total_iters > 0) tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+        if (iters_per_tile > 0) tmem_ld32(tmem_acc + (uint32_t)(c * 32), r);
         else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0;
         }
         const int col0 = n0 + c * 32;
-        if (row >= p.M || col0 >= p.N) continue;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float x = __uint_as_float(r[j]);
-          if (p.round_acc == BG_F16 + 1) x = __half2float(__float2half_rn(x));
-          else if (p.round_acc == BG_BF16 + 1) x = __bfloat162float(__float2bfloat16_rn(x));
-          v[j] = x;
-        }
-        if (p.bias) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) v[j] = __fadd_rn(v[j], load_bias(p.bias, p.bias_dtype, col0 + j));
-        }
-        const bool full = col0 + 32 <= p.N;
-        const size_t base = (size_t)row * p.N + col0;
-        if (p.c_dtype == BG_F64) {
-          double* out = reinterpret_cast<double*>(p.C) + base;
-          double w[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            double x = (double)v[j];
-            if (p.act == TC_ACT_RELU) x = x > 0.0 ? x : 0.0;
-            else if (p.act == TC_ACT_GELU) x = p.wide ? gelu_graph<double>(x) : (double)gelu_graph<float>(v[j]);
-            w[j] = x;
-          }
-          if (full && (p.N & 1) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) *reinterpret_cast<double2*>(out + j) = make_double2(w[j], w[j + 1]);
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = w[j];
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = v[j];
-            if (p.act == TC_ACT_RELU) x = x > 0.f ? x : 0.f;
-            else if (p.act == TC_ACT_GELU) x = gelu_graph<float>(x);
-            v[j] = x;
-          }
-          if (p.c_dtype == BG_F32) {
-            float* out = reinterpret_cast<float*>(p.C) + base;
-            if (full && (p.N & 3) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = v[j];
-            }
-          } else if (p.c_dtype == BG_F16) {
-            __half* out = reinterpret_cast<__half*>(p.C) + base;
-            if (full && (p.N & 7) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                __half2 h[4];
-#pragma unroll
-                for (int t = 0; t < 4; ++t) h[t] = __floats2half2_rn(v[j + 2 * t], v[j + 2 * t + 1]);
-                *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<uint4*>(h);
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = __float2half_rn(v[j]);
-            }
-          } else {
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + base;
-            if (full && (p.N & 7) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                __nv_bfloat162 h[4];
-#pragma unroll
-                for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(v[j + 2 * t], v[j + 2 * t + 1]);
-                *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<uint4*>(h);
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = __float2bfloat16_rn(v[j]);
-            }
-          }
-        }
+        if (row < p.M && col0 < p.N) epilogue_chunk(p, r, row, col0);
       }
+      // the buffer's values are in registers / memory: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
   }
   tc_fence_before();
@@ -349,7 +386,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
   }
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -439,7 +476,11 @@ cudaError_t launch_variant(const TcGemm& g, int* status, cudaStream_t s) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const int64_t tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
-  kern<<<(unsigned)tiles, kTcThreads, smem, s>>>(a0, a1, b0, b1, p);
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t grid = tiles < sms ? tiles : sms;
+  kern<<<(unsigned)grid, kTcThreads, smem, s>>>(a0, a1, b0, b1, p);
   return cudaGetLastError();
 }
 

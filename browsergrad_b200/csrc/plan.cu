@@ -214,6 +214,19 @@ class Compiler {
   bool has_f64_leaf_ = false;
   std::map<int, std::shared_ptr<TcEpilogue>> tc_epilogues_;   // MATMUL node -> epilogue fused into its kernel
   std::map<int, int> tc_unit_of_;
+  struct EpiPlan {
+    int final_node = -1;   // node whose value the GEMM stores
+    int bias_node = -1;
+    int act = TC_ACT_NONE;
+    int round_acc = 0;
+    int wide = 0;
+    int group = -1;
+  };
+  std::map<int, EpiPlan> epi_plan_;       // MATMUL node -> folded epilogue
+  std::set<int> absorbed_groups_;
+  int tc_mode(int n);                      // -1: SIMT; 0: 16-bit operands; 1: 3xTF32
+  std::string act_expr(int node, int x, int g, int depth);
+  void plan_tc_epilogues(const std::map<int, std::vector<int>>& groups);
   std::shared_ptr<CompiledPlan> cp_;
   int root_ = -1;
   // scheduling
@@ -401,6 +414,31 @@ void Compiler::simplify() {
       else if (n.dtype == BG_I64) f.iarg[0] = ci;
       else continue;
       n = f;
+    }
+  }
+  // CAST(PERMUTE(x)) -> PERMUTE(CAST(x)): the conversion then reads x densely and the permutation stays
+  // a view (the AMP pass casts the transposed weight of every Linear, _amp.py:215-226).
+  {
+    std::vector<int> n_uses(nn, 0);
+    for (int i = 0; i < nn; ++i)
+      for (int in : nodes_[i].in) n_uses[in]++;
+    for (int i = 0; i < nn; ++i) {
+      Node& c = nodes_[i];
+      if (c.op != BG_OP_CAST || c.in.size() != 1) continue;
+      const int pi = c.in[0];
+      Node& pm = nodes_[pi];
+      if (pm.op != BG_OP_PERMUTE || pm.in.size() != 1 || n_uses[pi] != 1 || pi == root_) continue;
+      const Node& src = nodes_[pm.in[0]];
+      Node cast = c;           // becomes node pi: CAST of the un-permuted source
+      cast.in = pm.in;
+      cast.rank = src.rank;
+      for (int d = 0; d < src.rank; ++d) cast.shape[d] = src.shape[d];
+      Node perm = pm;          // becomes node i: PERMUTE of the cast
+      perm.in = {pi};
+      perm.dtype = c.dtype;
+      perm.step = c.step;
+      nodes_[pi] = cast;
+      nodes_[i] = perm;
     }
   }
   auto compute_live = [&]() {
@@ -1454,6 +1492,153 @@ void Compiler::emit_generic_softmax(int n, int key) {
   add_unit(std::move(pu));
 }
 
+
+// Which tensor-core encoding a MATMUL node can use, judged from the operand views alone.
+int Compiler::tc_mode(int n) {
+  const Node& t = nodes_[n];
+  if (!ctx_->tensor_cores || t.in.size() != 2) return -1;
+  const View& av = view_[resolve(t.in[0])];
+  const View& bv = view_[resolve(t.in[1])];
+  if (av.is_const || bv.is_const || av.rank != 2 || bv.rank != 2 || t.rank != 2) return -1;
+  const int64_t M = av.shape[0], K = av.shape[1], N = bv.shape[1];
+  if (bv.shape[0] != K || M * N * K < (1ll << 24)) return -1;
+  int mode = -1;
+  if (av.dtype == bv.dtype && (av.dtype == BG_F16 || av.dtype == BG_BF16) && t.dtype == av.dtype) mode = 0;
+  else if (av.dtype == BG_F32 && bv.dtype == BG_F32 && t.dtype == BG_F32) mode = 1;
+  else if (t.dtype == BG_F64 && (av.dtype == BG_F32 || av.dtype == BG_F64) && (bv.dtype == BG_F32 || bv.dtype == BG_F64) &&
+           (ctx_->f64_mode == 1 || (ctx_->f64_mode == 2 && !has_f64_leaf_))) mode = 1;
+  if (mode < 0) return -1;
+  if (!tc_gemm_supported(M, N, K, mode == 0 ? av.dtype : BG_F32)) return -1;
+  return mode;
+}
+
+// Expression of `node` in terms of the value `x`, constants, and elementwise members of group g.
+std::string Compiler::act_expr(int node, int x, int g, int depth) {
+  node = resolve(node);
+  if (node == x) return "x";
+  if (depth > 64) return "?";
+  const Node& n = nodes_[node];
+  if (kind_[node] == K_CONST) {
+    char buf[64];
+    snprintf(buf, sizeof(buf), "c%.6g", view_[node].is_const ? (dtype_is_float(n.dtype) ? view_[node].cf : (double)view_[node].ci) : 0.0);
+    return buf;
+  }
+  if (kind_[node] != K_EW || find(node) != g) return "?";
+  std::string nm;
+  switch (n.op) {
+    case BG_OP_ADD: nm = "add"; break;
+    case BG_OP_MUL: nm = "mul"; break;
+    case BG_OP_DIV: nm = "div"; break;
+    case BG_OP_NEG: nm = "neg"; break;
+    case BG_OP_EXP: nm = "exp"; break;
+    case BG_OP_WHERE: nm = "where"; break;
+    case BG_OP_CMP: nm = std::string("cmp") + std::to_string((int)n.iarg[0]); break;
+    default: return "?";
+  }
+  std::string out = nm + "(";
+  for (size_t i = 0; i < n.in.size(); ++i) out += (i ? "," : "") + act_expr(n.in[i], x, g, depth + 1);
+  return out + ")";
+}
+
+// Fold the elementwise group that consumes a tensor-core product into the GEMM's epilogue when the
+// whole group is [CAST to fp32] -> [+ bias row] -> [relu | gelu] of that product.
+void Compiler::plan_tc_epilogues(const std::map<int, std::vector<int>>& groups) {
+  epi_plan_.clear();
+  absorbed_groups_.clear();
+  if (!ctx_->fusion) return;
+  const std::string Z = "mul(c0.797885,add(x,mul(mul(mul(c0.044715,x),x),x)))";
+  const std::string gelu = "mul(mul(c0.5,x),add(c1,div(add(exp(" + Z + "),neg(exp(neg(" + Z + ")))),add(exp(" + Z + "),exp(neg(" + Z + "))))))";
+  const std::string relu = "where(cmp" + std::to_string((int)BG_CMP_GT) + "(x,c0),x,c0)";
+  for (int n = 0; n < (int)nodes_.size(); ++n) {
+    if (kind_[n] != K_OTHER || nodes_[n].op != BG_OP_MATMUL) continue;
+    if (tc_mode(n) < 0) continue;
+    const int64_t N = nodes_[n].shape[1];
+    EpiPlan ep;
+    std::set<int> absorbed;
+    int cur = n;
+    auto sole_consumer = [&](int v) -> int {
+      std::set<int> c(cons_[v].begin(), cons_[v].end());
+      return c.size() == 1 && v != root_ ? *c.begin() : -1;
+    };
+    int nx = sole_consumer(cur);
+    if (nx < 0 || kind_[nx] != K_EW) continue;
+    const int g = find(nx);
+    if (tail_of_group_[g] >= 0) continue;
+    // optional CAST of a 16-bit product to fp32
+    if (nodes_[nx].op == BG_OP_CAST && nodes_[nx].dtype == BG_F32 && (nodes_[n].dtype == BG_F16 || nodes_[n].dtype == BG_BF16)) {
+      ep.round_acc = nodes_[n].dtype + 1;
+      absorbed.insert(nx);
+      cur = nx;
+      nx = sole_consumer(cur);
+    } else if (nodes_[n].dtype == BG_F16 || nodes_[n].dtype == BG_BF16) {
+      continue;   // a 16-bit result is stored as is
+    }
+    // optional bias row
+    if (nx >= 0 && kind_[nx] == K_EW && find(nx) == g && nodes_[nx].op == BG_OP_ADD && nodes_[nx].in.size() == 2) {
+      const int i0 = resolve(nodes_[nx].in[0]), i1 = resolve(nodes_[nx].in[1]);
+      const int other = i0 == cur ? i1 : (i1 == cur ? i0 : -1);
+      if (other >= 0 && other != cur) {
+        const View& bv = view_[other];
+        const bool row = !bv.is_const && bv.numel() == N && bv.contiguous() && bv.rank >= 1 && bv.shape[bv.rank - 1] == N &&
+                         leaflike_[other] && (bv.dtype == BG_F32 || bv.dtype == BG_F64 || bv.dtype == BG_F16);
+        if (row && (nodes_[nx].dtype == BG_F32 || nodes_[nx].dtype == BG_F64)) {
+          ep.bias_node = other;
+          absorbed.insert(nx);
+          cur = nx;
+        }
+      }
+    }
+    if (cur == n) continue;   // nothing linear to fold
+    // activation: the rest of the group must be exactly relu(x) or gelu(x) of the folded value
+    const std::vector<int>& mem = groups.at(g);
+    std::vector<int> mats;
+    for (int m : mem)
+      if (need_mat_[m]) mats.push_back(m);
+    int final_node = -1;
+    if (mats.size() == 1) {
+      if (mats[0] == cur) final_node = cur;
+      else {
+        const std::string e = act_expr(mats[0], cur, g, 0);
+        if (e == relu) { ep.act = TC_ACT_RELU; final_node = mats[0]; }
+        else if (e == gelu) { ep.act = TC_ACT_GELU; final_node = mats[0]; }
+      }
+    }
+    if (final_node < 0) continue;
+    // every member of the group must be part of what was folded
+    bool all = true;
+    for (int m : mem) {
+      if (absorbed.count(m) || m == final_node) continue;
+      if (ep.act == TC_ACT_NONE) { all = false; break; }
+      // activation interior nodes are reachable only from final_node; accept members that feed it
+    }
+    if (!all) continue;
+    if (ep.act != TC_ACT_NONE) {
+      // interior check: each member must be reachable from final_node within the group
+      std::set<int> reach;
+      std::vector<int> stack{final_node};
+      while (!stack.empty()) {
+        int v = stack.back();
+        stack.pop_back();
+        if (!reach.insert(v).second) continue;
+        for (int in : nodes_[v].in) {
+          int r = resolve(in);
+          if (kind_[r] == K_EW && find(r) == g) stack.push_back(r);
+        }
+      }
+      for (int m : mem)
+        if (!reach.count(m)) { all = false; break; }
+      if (!all) continue;
+    }
+    const int fdt = nodes_[final_node].dtype;
+    if (fdt != BG_F32 && fdt != BG_F64) continue;
+    ep.wide = fdt == BG_F64 && ep.act == TC_ACT_GELU && nodes_[cur].dtype != BG_F64 ? 1 : (fdt == BG_F64 ? 1 : 0);
+    ep.final_node = final_node;
+    ep.group = g;
+    epi_plan_[n] = ep;
+    absorbed_groups_.insert(g);
+  }
+}
+
 void Compiler::emit_matmul(int n, int key) {
   const Node& t = nodes_[n];
   if (t.in.size() != 2) err(BG_ERR_INVALID, "MATMUL: two inputs required");
@@ -1503,14 +1688,10 @@ void Compiler::emit_matmul(int n, int key) {
   // 2-D problems whose operands are (or can be copied into) dense K-major matrices:
   //   f16 x f16 / bf16 x bf16 -> tcgen05 kind::f16;   f32 x f32 -> 3xTF32;
   //   fp64 results whose values all derive from fp32 data -> 3xTF32 with an fp64 store.
-  if (ctx_->tensor_cores && !a_vec && !b_vec && nbatch == 1 && bs.empty() && gp.m * gp.n * gp.k >= (1ll << 24)) {
-    int mode = -1;  // 0: 16-bit, 1: 3xTF32
-    if (av.dtype == bv.dtype && (av.dtype == BG_F16 || av.dtype == BG_BF16) && t.dtype == av.dtype) mode = 0;
-    else if (av.dtype == BG_F32 && bv.dtype == BG_F32 && t.dtype == BG_F32) mode = 1;
-    else if (t.dtype == BG_F64 && (av.dtype == BG_F32 || av.dtype == BG_F64) && (bv.dtype == BG_F32 || bv.dtype == BG_F64) &&
-             (ctx_->f64_mode == 1 || (ctx_->f64_mode == 2 && !has_f64_leaf_))) mode = 1;
+  {
+    const int mode = tc_mode(n);   // 0: 16-bit operands, 1: 3xTF32
     const int ab = mode == 0 ? av.dtype : BG_F32;
-    if (mode >= 0 && tc_gemm_supported(gp.m, gp.n, gp.k, ab)) {
+    if (mode >= 0) {
       const int64_t M = gp.m, N = gp.n, K = gp.k;
       // operand layouts: A wants [M,K] dense, B wants [N,K] dense (i.e. the [K,N] view with unit stride along K)
       const bool a_dense = gp.a.col_stride == 1 && gp.a.row_stride == K;
@@ -1543,8 +1724,29 @@ void Compiler::emit_matmul(int n, int key) {
       const int a_dt = av.dtype, b_dt = bv.dtype, c_dt = t.dtype;
       auto epi = std::make_shared<TcEpilogue>();
       tc_epilogues_[n] = epi;
+      std::string epi_name;
+      auto ep_it = epi_plan_.find(n);
+      if (ep_it != epi_plan_.end()) {
+        const EpiPlan& ep = ep_it->second;
+        epi->out_slot = view_[ep.final_node].slot;
+        epi->out_dtype = nodes_[ep.final_node].dtype;
+        epi->act = ep.act;
+        epi->round_acc = ep.round_acc;
+        epi->wide = ep.wide;
+        if (ep.bias_node >= 0) {
+          const View& bvw = view_[ep.bias_node];
+          epi->bias_slot = bvw.slot;
+          epi->bias_off = bvw.off * dtype_size(bvw.dtype);
+          epi->bias_dtype = bvw.dtype;
+          pu.dep_nodes.push_back(ep.bias_node);
+          epi_name += "+bias";
+        }
+        if (ep.act == TC_ACT_RELU) epi_name += "+relu";
+        if (ep.act == TC_ACT_GELU) epi_name += "+gelu";
+        pu.out_nodes = {ep.final_node};
+      }
       pu.u.launches = 1 + (a_copy >= 0) + (b_copy >= 0) + (mode == 1 ? 2 : 0);
-      pu.u.name = std::string(mode == 0 ? "gemm_tc[" : "gemm_tc_3xtf32[") + dtype_name(t.dtype) + "]";
+      pu.u.name = std::string(mode == 0 ? "gemm_tc" : "gemm_tc_3xtf32") + epi_name + "[" + dtype_name(t.dtype) + "]";
       cp_->uses_status = true;
       const int sc_slot = sc;
       pu.u.fn = [=](Run& r) {
@@ -1697,9 +1899,11 @@ bool Compiler::try_lower() {
   std::map<int, std::vector<int>> groups;
   for (int i = 0; i < nn; ++i)
     if (kind_[i] == K_EW) groups[find(i)].push_back(i);
+  plan_tc_epilogues(groups);
   // only groups with a materialised member or a tail do any work
   for (auto& kv : groups) {
     const std::vector<int>& mem = kv.second;
+    if (absorbed_groups_.count(kv.first)) continue;   // runs as the epilogue of a tensor-core GEMM
     bool live = tail_of_group_[kv.first] >= 0;
     for (int m : mem) live |= need_mat_[m] != 0;
     if (!live) continue;

@@ -60,3 +60,28 @@ def test_pattern_kernels_and_interpreter_agree(bridge, name):
         check(case, got_static, got_generic, name)      # summation order differs
     else:
         assert got_static.tobytes() == got_generic.tobytes()
+
+
+@pytest.mark.parametrize("name,expect", [
+    ("c3_tc_f32", "gemm_tc_3xtf32+bias+gelu[float32]"),
+    ("c3_tc_f16", "gemm_tc+bias+gelu[float16]"),
+    ("c3_tc_bf16", "gemm_tc+bias+gelu[bfloat16]"),
+    ("c3_tc_ragged", "gemm_tc_3xtf32+bias[float32]"),
+    ("c3_tc_relu", "gemm_tc_3xtf32+bias+relu[float32]"),
+    ("c3_tc_rowmajor_b", "gemm_tc_3xtf32[float32]"),
+])
+def test_linear_runs_on_tensor_cores_with_folded_epilogue(bridge, name, expect):
+    case = CASES[name]
+    t, store, _ = build_case(case)
+    want = oracle_value(t, store)
+    got = realize_cuda(t, bridge)
+    trace = bridge.last_plan_trace()
+    assert expect in trace, trace
+    assert not any(ln.startswith(("ew[", "static_ew[")) and "CAST" not in ln for ln in trace), trace
+    check(case, got, want, name)
+    bridge.set_option("tensor_cores", 0)
+    try:
+        simt = realize_cuda(t, bridge)
+    finally:
+        bridge.set_option("tensor_cores", 1)
+    check(case, simt, want, name + " (SIMT)")
