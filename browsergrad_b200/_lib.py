@@ -88,6 +88,8 @@ SIGNATURES = {
     "bg_flush_profiles": (C.c_int, [C.c_void_p, C.POINTER(ProfileEntry), C.c_int, C.POINTER(C.c_int)]),
     "bg_last_plan_trace": (C.c_int, [C.c_void_p, C.c_char_p, C.c_size_t]),
     "bg_compile_plan_dry": (C.c_int, [C.POINTER(Plan), C.c_int, C.c_char_p, C.c_size_t]),
+    "bg_cross_entropy_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int,
+                                           C.c_int64, C.c_void_p, C.c_char_p, C.c_size_t]),
     "bg_stream": (C.c_void_p, [C.c_void_p]),
     "bg_device_pointer": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p)]),
 }

@@ -194,6 +194,22 @@ int bg_resource_snapshot(bg_context* ctx, bg_resource_stats* out);
 int bg_flush_profiles(bg_context* ctx, bg_profile_entry* out, int capacity, int* n_out);
 /* Text listing of the kernels the most recent plan compiled to, one per line. */
 int bg_last_plan_trace(bg_context* ctx, char* out, size_t capacity);
+/*
+ * Cross entropy over class-index targets with no allocation of any kind (no counterpart in the
+ * reference).  For callers that may not allocate device memory while running -- a process whose
+ * own arena already owns the GPU, or a loop that cannot afford cudaMalloc's device-wide stall.
+ * logits [rows, classes, inner] fp32, targets [rows, inner] int64, out: one fp32; all three are
+ * DEVICE pointers owned by the caller.  reduction: 1 = mean over valid targets, 2 = sum.
+ * The per-position scratch is a static device array: rows * inner <= 1 048 576 (larger problems
+ * are refused with BG_ERR_UNSUPPORTED and a message in `err`); every GPU that loads the library
+ * holds those 4 MiB + 256 B until the process exits.  The first call on a device looks the array's
+ * device address up and should therefore come before any stream capture.  All calls share the
+ * array: calls that overlap on the GPU race, so order them on one stream.  The call synchronises
+ * `stream` (a cudaStream_t) and reports an out-of-range target as BG_ERR_INDEX_RANGE.
+ */
+int bg_cross_entropy_noalloc(const float* logits, const int64_t* targets, float* out, int64_t rows,
+                             int64_t classes, int64_t inner, int reduction, int64_t ignore_index,
+                             void* stream, char* err, size_t err_capacity);
 /* Host-only diagnostic: compiles `plan` into its kernel list (one name per line) without a
  * device or a context; `fusion` = 0 disables group formation.  Used to test the plan compiler
  * on machines without a GPU. */
