@@ -140,6 +140,70 @@ def cpu_baseline(sample_rows: int, repeats: int = 1) -> dict:
             "seconds": best}
 
 
+def time_plan(bridge, torch, stream, graph_root, store, front, steps: int, warmup: int = 3):
+    """Average device time (ms) of one realization with resident leaves, plus the per-kernel profile."""
+    prepared, plan = front.plan_for(graph_root._uop)
+    table = front.DeviceBufferTable(bridge)
+    inputs = front._bind_inputs(plan, store, table, True)
+    for _ in range(warmup):
+        bridge.release(bridge.run_tensor_plan_resident(plan, inputs, prepared.dtype))
+    bridge.synchronize()
+    bridge.flushProfiles()
+    bridge.set_option("profiling", 1)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        bridge.release(bridge.run_tensor_plan_resident(plan, inputs, prepared.dtype))
+    e1.record(stream)
+    bridge.synchronize()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    prof = bridge.flushProfiles()
+    bridge.set_option("profiling", 0)
+    trace = bridge.last_plan_trace()
+    table.release_all()
+    return ms, prof, trace
+
+
+def extra_measurements(bridge, torch, stream, peaks, steps: int) -> dict:
+    """Configs 3 and 4 of the baseline: Linear+bias+GELU GEMM TFLOP/s and causal attention tokens/s."""
+    from browsergrad_b200 import configs, front, graph
+    out = {"gemm": [], "attention": []}
+    for n in (4096, 8192):
+        for amp in ("bfloat16", ""):
+            arrays = configs.linear_inputs(n, n, n)
+            store = graph.BufferStore()
+            t = {k: graph.from_numpy(v, store) for k, v in arrays.items()}
+            root = configs.linear_gelu(graph, t, amp)
+            ms, prof, trace = time_plan(bridge, torch, stream, root, store, front, steps)
+            gemm = [p for p in prof if p["name"].startswith("gemm")]
+            k_ms = gemm[0]["ms"] / max(gemm[0]["launches"], 1) if gemm else ms
+            tf = 2.0 * n ** 3 / (k_ms * 1e-3) / 1e12
+            peak = peaks["bf16_tflops"] if amp else peaks["bf16_tflops"] / 2.0 / 3.0
+            out["gemm"].append({"workload": f"Linear+bias+GELU M=N=K={n} {'bf16 autocast' if amp else 'fp32 (3xTF32)'}",
+                                "tflops": tf, "kernel_ms": k_ms, "plan_ms": ms, "kernels": trace,
+                                "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+                                             "peak_note": "measured cuBLAS bf16 burst" if amp else
+                                             "measured bf16 burst / 2 (tf32) / 3 (three products per result)"}})
+            del arrays, store, t
+    b, h, s, d = 16, 12, 2048, 64
+    for amp in ("", "bfloat16"):
+        arrays = configs.attention_inputs(b, h, s, d)
+        arrays["mask"] = configs.causal_mask(s)
+        store = graph.BufferStore()
+        t = {k: graph.from_numpy(v, store) for k, v in arrays.items()}
+        root = configs.attention(graph, t, "mask", amp)
+        ms, prof, trace = time_plan(bridge, torch, stream, root, store, front, steps)
+        att = [p for p in prof if p["name"].startswith("attention")]
+        k_ms = att[0]["ms"] / max(att[0]["launches"], 1) if att else ms
+        flops = 4.0 * b * h * s * s * d
+        out["attention"].append({"workload": f"causal SDPA B={b} H={h} S={s} D={d} {'bf16 autocast' if amp else 'fp32 (3xTF32)'}, additive mask",
+                                 "tokens_per_s": b * s / (ms * 1e-3), "plan_ms": ms, "kernel_ms": k_ms, "kernels": trace,
+                                 "dense_equivalent_tflops": flops / (ms * 1e-3) / 1e12})
+        del arrays, store, t
+    return out
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -178,6 +242,7 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=ROWS)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-extra", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -297,6 +362,13 @@ def main() -> None:
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_baseline(1024, repeats=2)
+    extra = None
+    if rank == 0 and world == 1 and not args.no_extra:
+        table.release_all()
+        try:
+            extra = extra_measurements(bridge, torch, stream, peaks, max(3, min(args.steps, 10)))
+        except Exception as exc:   # the headline line must survive a failure in the extras
+            extra = {"error": repr(exc)}
 
     if rank == 0:
         line = {
@@ -307,6 +379,7 @@ def main() -> None:
                        "algorithmic_bytes_per_step": total_bytes, "l2": "inputs (4 x 268 MB) exceed the 126 MB L2",
                        "parallelism": f"row-sharded x{world}, no collective"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "extra": extra,
         }
         print(json.dumps(line))
     table.release_all()

@@ -78,8 +78,12 @@ def causal_mask(s: int) -> np.ndarray:
     return np.triu(np.full((s, s), -np.inf, dtype=np.float32), k=1)
 
 
-def attention(api: Any, t: Dict[str, Any], variant: str = "mask") -> Any:
-    """Config 4: causal SDPA, as an additive -inf mask ("mask") or ``is_causal`` ("causal")."""
+def attention(api: Any, t: Dict[str, Any], variant: str = "mask", amp: str = "") -> Any:
+    """Config 4: causal SDPA, as an additive -inf mask ("mask") or ``is_causal`` ("causal");
+    ``amp`` = "", "float16" or "bfloat16" runs it under autocast."""
+    if amp:
+        with api.autocast(dtype=amp):
+            return attention(api, t, variant)
     if variant == "mask":
         return api.scaled_dot_product_attention(t["q"], t["k"], t["v"], attn_mask=t["mask"])
     if variant == "causal":

@@ -1,0 +1,604 @@
+// Fused softmax attention forward for sm_100a (head dimension 64):
+//   O[b,h,q,:] = softmax_k( scale * Q[b,h,q,:].K[b,h,k,:] (+ mask) ) . V[b,h,k,:]
+// with the score tile kept on chip: S = Q K^T is produced by tcgen05.mma into tensor memory, the
+// softmax warps read it with tcgen05.ld, keep the running max / sum per query row, write the
+// probabilities P back to shared memory in the operand layout, and a second tcgen05.mma forms
+// P V into tensor memory, which the same warps fold into a register accumulator.
+//
+// One CTA owns 128 query rows of one (batch, head):
+//   warp 0     TMA producer: Q once, then K / V^T tiles into a ring of stages
+//   warp 1     MMA issuer (one thread): QK^T two tiles ahead, P.V as soon as P is published
+//   warps 2-5  softmax: one thread per query row
+// Operand encodings: f16 / bf16 (128 keys per tile), or 3xTF32 for fp32-faithful results (32 keys
+// per tile; Q, K, V^T pre-split into hi = tf32(x), lo = x - hi; P split on the fly; the three
+// cross products lo.hi, hi.lo, hi.hi go into one accumulator).  All operands are K-major tiles
+// with 128-byte swizzle; V is consumed as V^T [D, keys], prepared by a transposing pre-pass.
+// Masks: additive fp32 [B|1, H|1, Sq, Sk], or boolean "fill with -inf"; a per-(q tile, k tile)
+// class (skip / plain / mixed) computed by a pre-pass lets fully masked tiles (the causal upper
+// triangle) be skipped by every role alike.  No cluster multicast; every wait is clock-bounded.
+#include "common.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math_constants.h>
+
+#include "tc_common.cuh"
+
+namespace bg {
+namespace {
+
+using namespace tc;
+
+constexpr int kHeadDim = 64;
+constexpr int kQRows = 128;
+constexpr int kAttnThreads = 192;
+
+__device__ __forceinline__ void tma_load_4d(const CUtensorMap* map, void* smem_dst, uint64_t* bar, int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
+struct AttnParams {
+  int B, H, Sq, Sk;
+  float scale;                 // used when scale_buf is null or *scale_uniform != 0
+  const float* scale_buf;      // [B,H,Sq,Sk] or null
+  const int* scale_uniform;    // device flag: scale_buf holds one repeated value (then scale_buf[0] is used)
+  const void* mask;            // additive fp32 or bool (1 = fill -inf), or null
+  int mask_is_bool;
+  long long mask_sb, mask_sh;  // element strides over batch / head (0 when broadcast); rows are Sk apart
+  const unsigned char* tile_class;   // [ceil(Sq/128), ceil(Sk/BKV)]: 0 skip, 1 plain, 2 mixed; null = all plain
+  void* out;                   // [B,H,Sq,64]
+  int out_dtype;
+  int round_scores;            // dtype + 1: round S through f16 / bf16 before the softmax (autocast graphs)
+  uint32_t idesc_qk, idesc_pv;
+  int* status;
+};
+
+template <bool TF32>
+struct AttnCfg {
+  static constexpr int BKV = TF32 ? 32 : 128;                 // keys per tile
+  static constexpr int NST = TF32 ? 2 : 3;                    // K/V stages
+  static constexpr int QBytes = TF32 ? 2 * 2 * kQRows * 128 : kQRows * 128;     // hi+lo x 2 k-blocks | one k-block
+  static constexpr int KBytes = TF32 ? 2 * 2 * BKV * 128 : BKV * 128;           // per stage
+  static constexpr int VBytes = TF32 ? 2 * kHeadDim * 128 : 2 * kHeadDim * 128; // hi+lo x 1 k-block | 2 k-blocks
+  static constexpr int StageBytes = KBytes + VBytes;
+  static constexpr int PBytes = TF32 ? 2 * kQRows * 128 : 2 * kQRows * 128;     // hi+lo | 2 k-blocks
+  static constexpr int SCols = BKV;
+  static constexpr int TmemCols = TF32 ? 256 : 512;           // 2 x S + 2 x PV, rounded to a power of two
+  static constexpr int SmemBytes = QBytes + NST * StageBytes + 2 * PBytes;
+};
+
+template <bool TF32>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant__ CUtensorMap tmQ1,
+                const __grid_constant__ CUtensorMap tmK0, const __grid_constant__ CUtensorMap tmK1,
+                const __grid_constant__ CUtensorMap tmV0, const __grid_constant__ CUtensorMap tmV1,
+                const __grid_constant__ AttnParams p) {
+  using C = AttnCfg<TF32>;
+  constexpr int BKV = C::BKV;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* sQ = smem;
+  unsigned char* sKV = sQ + C::QBytes;
+  unsigned char* sP = sKV + C::NST * C::StageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * C::PBytes);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = q_full + 1;
+  uint64_t* kv_empty = kv_full + C::NST;
+  uint64_t* s_full = kv_empty + C::NST;   // [2]
+  uint64_t* p_full = s_full + 2;          // [2]
+  uint64_t* pv_full = p_full + 2;         // [2]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_full + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int q0 = q_tile * kQRows;
+  const int n_kv = (p.Sk + BKV - 1) / BKV;
+  const unsigned char* cls = p.tile_class ? p.tile_class + (size_t)q_tile * n_kv : nullptr;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < C::NST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&pv_full[i], 1); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(C::TmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_s = tmem_base;                       // S buffers: columns [0, 2*BKV)
+  const uint32_t tmem_pv = tmem_base + 2 * C::SCols;       // PV buffers: 2 x 64 columns
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // Q: loaded once
+      mbar_expect_tx(q_full, C::QBytes);
+      if (TF32) {
+        for (int kb = 0; kb < 2; ++kb) {
+          tma_load_4d(&tmQ0, sQ + kb * (kQRows * 128), q_full, kb * 32, q0, h, b);
+          tma_load_4d(&tmQ1, sQ + 2 * (kQRows * 128) + kb * (kQRows * 128), q_full, kb * 32, q0, h, b);
+        }
+      } else {
+        tma_load_4d(&tmQ0, sQ, q_full, 0, q0, h, b);
+      }
+      int jj = 0;
+      for (int j = 0; j < n_kv; ++j) {
+        if (cls && cls[j] == 0) continue;
+        const int s = jj % C::NST;
+        const uint32_t ph = (uint32_t)(jj / C::NST) & 1u;
+        if (!mbar_wait(&kv_empty[s], ph ^ 1u, abort_flag)) break;
+        unsigned char* st = sKV + s * C::StageBytes;
+        const int k0 = j * BKV;
+        mbar_expect_tx(&kv_full[s], C::StageBytes);
+        if (TF32) {
+          // K hi / lo: two k-blocks of 32 floats each; V^T hi / lo: one k-block of 32 keys
+          for (int kb = 0; kb < 2; ++kb) {
+            tma_load_4d(&tmK0, st + kb * (BKV * 128), &kv_full[s], kb * 32, k0, h, b);
+            tma_load_4d(&tmK1, st + 2 * (BKV * 128) + kb * (BKV * 128), &kv_full[s], kb * 32, k0, h, b);
+          }
+          tma_load_4d(&tmV0, st + C::KBytes, &kv_full[s], k0, 0, h, b);
+          tma_load_4d(&tmV1, st + C::KBytes + kHeadDim * 128, &kv_full[s], k0, 0, h, b);
+        } else {
+          tma_load_4d(&tmK0, st, &kv_full[s], 0, k0, h, b);
+          tma_load_4d(&tmV0, st + C::KBytes, &kv_full[s], k0, 0, h, b);
+          tma_load_4d(&tmV0, st + C::KBytes + kHeadDim * 128, &kv_full[s], k0 + 64, 0, h, b);
+        }
+        ++jj;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // number of tiles that are processed, and the order: QK(0), QK(1), PV(0), QK(2), PV(1), ...
+      int n_proc = 0;
+      for (int j = 0; j < n_kv; ++j) n_proc += !(cls && cls[j] == 0);
+      bool ok = n_proc == 0 || mbar_wait(q_full, 0, abort_flag);
+      const uint32_t q_addr = smem_u32(sQ);
+      auto issue_qk = [&](int t) -> bool {   // t-th processed tile
+        const int s = t % C::NST;
+        if (!mbar_wait(&kv_full[s], (uint32_t)(t / C::NST) & 1u, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sKV + s * C::StageBytes);
+        const uint32_t d_s = tmem_s + (uint32_t)((t & 1) * C::SCols);
+        if (TF32) {
+          // passes lo.hi, hi.lo, hi.hi; each: 2 k-blocks x 4 k-steps of 8 floats
+          uint32_t first = 1;
+          for (int pass = 0; pass < 3; ++pass) {
+            const uint32_t qa = q_addr + (pass == 0 ? 2 * (kQRows * 128) : 0);
+            const uint32_t ka = k_addr + (pass == 1 ? 2 * (BKV * 128) : 0);
+            for (int kb = 0; kb < 2; ++kb) {
+              const uint64_t da = make_kmajor_sw128_desc(qa + kb * (kQRows * 128));
+              const uint64_t db = make_kmajor_sw128_desc(ka + kb * (BKV * 128));
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                umma<true>(d_s, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_qk, first ? 0u : 1u);
+                first = 0;
+              }
+            }
+          }
+        } else {
+          const uint64_t da = make_kmajor_sw128_desc(q_addr), db = make_kmajor_sw128_desc(k_addr);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma<false>(d_s, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_qk, k ? 1u : 0u);
+        }
+        umma_commit(&s_full[t & 1]);
+        return true;
+      };
+      auto issue_pv = [&](int t) -> bool {
+        const int s = t % C::NST;
+        if (!mbar_wait(&p_full[t & 1], (uint32_t)(t >> 1) & 1u, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t p_addr = smem_u32(sP + (t & 1) * C::PBytes);
+        const uint32_t v_addr = smem_u32(sKV + s * C::StageBytes + C::KBytes);
+        const uint32_t d_pv = tmem_pv + (uint32_t)((t & 1) * kHeadDim);
+        if (TF32) {
+          uint32_t first = 1;
+          for (int pass = 0; pass < 3; ++pass) {
+            const uint64_t da = make_kmajor_sw128_desc(p_addr + (pass == 0 ? kQRows * 128 : 0));
+            const uint64_t db = make_kmajor_sw128_desc(v_addr + (pass == 1 ? kHeadDim * 128 : 0));
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              umma<true>(d_pv, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_pv, first ? 0u : 1u);
+              first = 0;
+            }
+          }
+        } else {
+          for (int kb = 0; kb < 2; ++kb) {
+            const uint64_t da = make_kmajor_sw128_desc(p_addr + kb * (kQRows * 128));
+            const uint64_t db = make_kmajor_sw128_desc(v_addr + kb * (kHeadDim * 128));
+#pragma unroll
+            for (int k = 0; k < 4; ++k) umma<false>(d_pv, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_pv, (kb || k) ? 1u : 0u);
+          }
+        }
+        umma_commit(&pv_full[t & 1]);
+        umma_commit(&kv_empty[s]);
+        return true;
+      };
+      if (ok && n_proc > 0) ok = issue_qk(0);
+      if (ok && n_proc > 1) ok = issue_qk(1);
+      for (int t = 0; t < n_proc && ok; ++t) {
+        ok = issue_pv(t);
+        if (ok && t + 2 < n_proc) ok = issue_qk(t + 2);
+      }
+    }
+  } else {
+    // ---- softmax: one thread per query row ----------------------------------------------------
+    const int quarter = warp & 3;
+    const int r_in_tile = quarter * 32 + lane;
+    const int row = q0 + r_in_tile;
+    const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+    float o[kHeadDim];
+#pragma unroll
+    for (int d = 0; d < kHeadDim; ++d) o[d] = 0.f;
+    float m = -CUDART_INF_F, l = 0.f;
+    float alpha_prev = 1.f;
+    float scale = p.scale;
+    const bool per_elem_scale = p.scale_buf != nullptr && !(p.scale_uniform && *p.scale_uniform);
+    if (p.scale_buf && !per_elem_scale) scale = p.scale_buf[0];
+    const size_t score_row = ((size_t)(b * p.H + h) * p.Sq + (row < p.Sq ? row : 0)) * (size_t)p.Sk;
+    const size_t mask_row = (size_t)b * p.mask_sb + (size_t)h * p.mask_sh + (size_t)(row < p.Sq ? row : 0) * p.Sk;
+    bool ok = true;
+    int t = 0;
+    auto fold_pv = [&](int tt, float alpha) -> bool {
+      if (!mbar_wait(&pv_full[tt & 1], (uint32_t)(tt >> 1) & 1u, abort_flag)) return false;
+      tc_fence_after();
+      const uint32_t src = tmem_pv + (uint32_t)((tt & 1) * kHeadDim) + lane_sel;
+#pragma unroll
+      for (int c = 0; c < kHeadDim / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(src + (uint32_t)(c * 32), r);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(r[i]));
+      }
+      return true;
+    };
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int tclass = cls ? cls[j] : (p.mask ? 2 : 1);
+      if (tclass == 0) continue;
+      const int buf = t & 1;
+      if (!mbar_wait(&s_full[buf], (uint32_t)(t >> 1) & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int k0 = j * BKV;
+      float sv[BKV];
+#pragma unroll
+      for (int c = 0; c < BKV / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_s + (uint32_t)(buf * C::SCols) + lane_sel + (uint32_t)(c * 32), r);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sv[c * 32 + i] = __uint_as_float(r[i]);
+      }
+      // scale, mask, row max
+      float mt = -CUDART_INF_F;
+      const bool need_mask = p.mask && tclass == 2;
+#pragma unroll
+      for (int i = 0; i < BKV; ++i) {
+        float x = sv[i];
+        if (p.round_scores == BG_F16 + 1) x = __half2float(__float2half_rn(x));
+        else if (p.round_scores == BG_BF16 + 1) x = __bfloat162float(__float2bfloat16_rn(x));
+        const int key = k0 + i;
+        const bool in_range = key < p.Sk;
+        x = __fmul_rn(x, per_elem_scale ? (in_range ? p.scale_buf[score_row + key] : 0.f) : scale);
+        if (need_mask && in_range) {
+          if (p.mask_is_bool) { if (reinterpret_cast<const unsigned char*>(p.mask)[mask_row + key]) x = -CUDART_INF_F; }
+          else x = __fadd_rn(x, reinterpret_cast<const float*>(p.mask)[mask_row + key]);
+        }
+        if (!in_range) x = -CUDART_INF_F;
+        sv[i] = x;
+        mt = fmaxf(mt, x);
+      }
+      const float m_new = fmaxf(m, mt);
+      const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;
+      const float alpha = expf(m - m_use);         // m = -inf gives 0: nothing accumulated yet
+      float psum = 0.f;
+#pragma unroll
+      for (int i = 0; i < BKV; ++i) {
+        sv[i] = expf(sv[i] - m_use);
+        psum += sv[i];
+      }
+      l = fmaf(l, alpha, psum);
+      m = m_new;
+      // publish P in the K-major 128-byte-swizzled operand layout: row r_in_tile, 16-byte chunk c of
+      // a 128-byte row lands at chunk (c ^ (row & 7))
+      unsigned char* pb = sP + buf * C::PBytes;
+      const int sw = r_in_tile & 7;
+      if (TF32) {
+        unsigned char* hi_row = pb + r_in_tile * 128;
+        unsigned char* lo_row = pb + kQRows * 128 + r_in_tile * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float hi[4], lo[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            uint32_t hbits;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hbits) : "f"(sv[c * 4 + e]));
+            hi[e] = __uint_as_float(hbits);
+            lo[e] = sv[c * 4 + e] - hi[e];
+          }
+          *reinterpret_cast<float4*>(hi_row + ((c ^ sw) << 4)) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+          *reinterpret_cast<float4*>(lo_row + ((c ^ sw) << 4)) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+        }
+      } else {
+        const bool bf = p.round_scores == BG_BF16 + 1;
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          unsigned char* prow = pb + kb * (kQRows * 128) + r_in_tile * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float a0 = sv[kb * 64 + c * 8 + 2 * e], a1 = sv[kb * 64 + c * 8 + 2 * e + 1];
+              if (bf) { __nv_bfloat162 v2 = __floats2bfloat162_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
+              else { __half2 v2 = __floats2half2_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
+            }
+            *reinterpret_cast<uint4*>(prow + ((c ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[buf]);
+      // fold the previous tile's P.V while the tensor core works on this one
+      if (t > 0) ok = fold_pv(t - 1, alpha_prev);
+      alpha_prev = alpha;
+      ++t;
+    }
+    if (ok && t > 0) ok = fold_pv(t - 1, alpha_prev);
+    if (ok && row < p.Sq) {
+      const float inv = 1.0f / l;   // l = 0 for a fully masked row: 0 * inf = NaN, as the reference's softmax gives
+      const size_t base = ((size_t)(b * p.H + h) * p.Sq + row) * kHeadDim;
+      if (p.out_dtype == BG_F32) {
+        float* out = reinterpret_cast<float*>(p.out) + base;
+#pragma unroll
+        for (int d = 0; d < kHeadDim; d += 4)
+          *reinterpret_cast<float4*>(out + d) = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
+      } else if (p.out_dtype == BG_F64) {
+        double* out = reinterpret_cast<double*>(p.out) + base;
+#pragma unroll
+        for (int d = 0; d < kHeadDim; d += 2) *reinterpret_cast<double2*>(out + d) = make_double2((double)(o[d] * inv), (double)(o[d + 1] * inv));
+      } else if (p.out_dtype == BG_F16) {
+        __half* out = reinterpret_cast<__half*>(p.out) + base;
+#pragma unroll
+        for (int d = 0; d < kHeadDim; d += 2) *reinterpret_cast<__half2*>(out + d) = __floats2half2_rn(o[d] * inv, o[d + 1] * inv);
+      } else {
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + base;
+#pragma unroll
+        for (int d = 0; d < kHeadDim; d += 2) *reinterpret_cast<__nv_bfloat162*>(out + d) = __floats2bfloat162_rn(o[d] * inv, o[d + 1] * inv);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(p.status, BG_ERR_DEVICE_TIMEOUT);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) {}
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TmemCols) : "memory");
+  }
+}
+
+
+// ---- pre-passes ---------------------------------------------------------------------------------
+struct PrepView {
+  const void* ptr;
+  int dtype;
+  long long stride[4];   // element strides of the [B,H,S,D] view
+};
+
+// dst (dense [B,H,S,D], or [B,H,D,S] when `transpose`) = convert(src view).  mode 0: copy 16-bit values;
+// mode 1: hi = tf32(x), lo = x - hi from fp32 / fp64 (fp16 / bf16 widen first).
+__global__ void attn_prep_kernel(PrepView src, void* dst_a, void* dst_b, int B, int H, int S, int D, int transpose, int mode) {
+  const long long n = (long long)B * H * S * D;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    // i enumerates the destination densely
+    long long rem = i;
+    int d, s;
+    if (transpose) { s = (int)(rem % S); rem /= S; d = (int)(rem % D); rem /= D; }
+    else { d = (int)(rem % D); rem /= D; s = (int)(rem % S); rem /= S; }
+    const int h = (int)(rem % H);
+    const int b = (int)(rem / H);
+    const long long off = b * src.stride[0] + h * src.stride[1] + s * src.stride[2] + d * src.stride[3];
+    if (mode == 0) {
+      reinterpret_cast<uint16_t*>(dst_a)[i] = reinterpret_cast<const uint16_t*>(src.ptr)[off];
+    } else {
+      double xd;
+      switch (src.dtype) {
+        case BG_F64: xd = reinterpret_cast<const double*>(src.ptr)[off]; break;
+        case BG_F32: xd = reinterpret_cast<const float*>(src.ptr)[off]; break;
+        case BG_F16: xd = __half2float(reinterpret_cast<const __half*>(src.ptr)[off]); break;
+        default: xd = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(src.ptr)[off]); break;
+      }
+      const float x = (float)xd;
+      uint32_t hb;
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x));
+      const float fh = __uint_as_float(hb);
+      reinterpret_cast<float*>(dst_a)[i] = fh;
+      reinterpret_cast<float*>(dst_b)[i] = (float)(xd - (double)fh);
+    }
+  }
+}
+
+// class of each (128-query, BKV-key) tile of a mask shared by all batches and heads:
+// 0 = every score masked out (skip), 1 = mask has no effect, 2 = mixed
+__global__ void attn_mask_class_kernel(const void* mask, int is_bool, int Sq, int Sk, int bkv, unsigned char* cls, int n_kv) {
+  const int qt = blockIdx.y, kt = blockIdx.x;
+  __shared__ int any_open, any_closed;
+  if (threadIdx.x == 0) { any_open = 0; any_closed = 0; }
+  __syncthreads();
+  int open = 0, closed = 0;
+  const int rows = min(kQRows, Sq - qt * kQRows), cols = min(bkv, Sk - kt * bkv);
+  for (int i = threadIdx.x; i < rows * cols; i += blockDim.x) {
+    const int r = qt * kQRows + i / cols, c = kt * bkv + i % cols;
+    const size_t off = (size_t)r * Sk + c;
+    if (is_bool) {
+      if (reinterpret_cast<const unsigned char*>(mask)[off]) closed = 1; else open = 1;
+    } else {
+      const float v = reinterpret_cast<const float*>(mask)[off];
+      if (v == -CUDART_INF_F) closed = 1;
+      else if (v == 0.f) open = 1;
+      else { open = 1; closed = 1; }   // a finite bias: must be applied
+    }
+  }
+  if (open) atomicOr(&any_open, 1);
+  if (closed) atomicOr(&any_closed, 1);
+  __syncthreads();
+  if (threadIdx.x == 0) cls[(size_t)qt * n_kv + kt] = any_closed ? (any_open ? 2 : 0) : 1;
+}
+
+__global__ void attn_uniform_kernel(const float* buf, long long n, int* flag) {
+  const float first = buf[0];
+  int bad = 0;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    bad |= buf[i] != first;
+  if (bad) *flag = 0;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn attn_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// dense [B, H, rows, cols] tensor, box = 128 bytes of cols x box_rows
+bool make_map4(CUtensorMap* map, const void* ptr, int dtype, int B, int H, long long rows, long long cols, int box_rows) {
+  EncodeTiledFn fn = attn_encode_fn();
+  if (!fn) return false;
+  const int es = dtype_size(dtype);
+  CUtensorMapDataType dt = dtype == BG_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                           : dtype == BG_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)cols * es, (cuuint64_t)cols * rows * es, (cuuint64_t)cols * rows * H * es};
+  cuuint32_t box[4] = {(cuuint32_t)(128 / es), (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(map, dt, 4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+unsigned prep_grid(long long n) {
+  long long g = (n + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  return (unsigned)(g < 1 ? 1 : g);
+}
+
+}  // namespace
+
+bool attn_tc_supported(const AttnProblem& a) {
+  if (!g_tc_assume_available && !attn_encode_fn()) return false;
+  if (a.D != kHeadDim || a.B <= 0 || a.H <= 0 || a.Sq <= 0 || a.Sk <= 0) return false;
+  if (a.H > 65535 || a.B > 65535) return false;
+  if (a.mode == 0 && (a.Sk % 8) != 0) return false;     // V^T rows of Sk 16-bit values must be 16-byte multiples
+  if (a.mode == 1 && (a.Sk % 4) != 0) return false;
+  return true;
+}
+
+void attn_scratch_sizes(const AttnProblem& a, int64_t bytes[8]) {
+  const int64_t nq = (int64_t)a.B * a.H * a.Sq * a.D, nk = (int64_t)a.B * a.H * a.Sk * a.D;
+  const int es = a.mode == 1 ? 4 : 2;
+  const int bkv = a.mode == 1 ? 32 : 128;
+  bytes[0] = nq * es;                       // Q (hi)
+  bytes[1] = a.mode == 1 ? nq * es : 0;     // Q lo
+  bytes[2] = nk * es;                       // K (hi)
+  bytes[3] = a.mode == 1 ? nk * es : 0;     // K lo
+  bytes[4] = nk * es;                       // V^T (hi)
+  bytes[5] = a.mode == 1 ? nk * es : 0;     // V^T lo
+  bytes[6] = a.mask ? (int64_t)((a.Sq + kQRows - 1) / kQRows) * ((a.Sk + bkv - 1) / bkv) : 0;   // tile classes
+  bytes[7] = a.scale_buf ? 4 : 0;           // uniform-scale flag
+}
+
+cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], int* status, cudaStream_t s) {
+  const bool tf32 = a.mode == 1;
+  const int bkv = tf32 ? 32 : 128;
+  const int sdt = tf32 ? BG_F32 : a.ab_dtype;
+  // operand staging: dense Q, K, V^T in the kernel's encoding
+  const AttnOperand* ops[3] = {&a.q, &a.k, &a.v};
+  const int seq[3] = {a.Sq, a.Sk, a.Sk};
+  for (int i = 0; i < 3; ++i) {
+    PrepView v{ops[i]->ptr, ops[i]->dtype, {ops[i]->stride[0], ops[i]->stride[1], ops[i]->stride[2], ops[i]->stride[3]}};
+    const long long n = (long long)a.B * a.H * seq[i] * a.D;
+    attn_prep_kernel<<<prep_grid(n), 256, 0, s>>>(v, scratch[2 * i], scratch[2 * i + 1], a.B, a.H, seq[i], a.D, i == 2, tf32 ? 1 : 0);
+  }
+  unsigned char* cls = nullptr;
+  if (a.mask && a.mask_sb == 0 && a.mask_sh == 0) {
+    cls = reinterpret_cast<unsigned char*>(scratch[6]);
+    const int n_kv = (a.Sk + bkv - 1) / bkv, n_q = (a.Sq + kQRows - 1) / kQRows;
+    attn_mask_class_kernel<<<dim3(n_kv, n_q), 256, 0, s>>>(a.mask, a.mask_is_bool, a.Sq, a.Sk, bkv, cls, n_kv);
+  }
+  int* uniform = nullptr;
+  if (a.scale_buf) {
+    uniform = reinterpret_cast<int*>(scratch[7]);
+    cudaError_t e = cudaMemsetAsync(uniform, 1, 1, s);   // low byte 1 -> flag != 0 (the other bytes are cleared next)
+    if (e != cudaSuccess) return e;
+    e = cudaMemsetAsync(reinterpret_cast<char*>(uniform) + 1, 0, 3, s);
+    if (e != cudaSuccess) return e;
+    const long long n = (long long)a.B * a.H * a.Sq * a.Sk;
+    attn_uniform_kernel<<<prep_grid(n), 256, 0, s>>>(a.scale_buf, n, uniform);
+  }
+  CUtensorMap q0, q1, k0, k1, v0, v1;
+  if (!make_map4(&q0, scratch[0], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
+  if (!make_map4(&k0, scratch[2], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
+  if (!make_map4(&v0, scratch[4], sdt, a.B, a.H, a.D, a.Sk, kHeadDim)) return cudaErrorInvalidValue;
+  q1 = q0; k1 = k0; v1 = v0;
+  if (tf32) {
+    if (!make_map4(&q1, scratch[1], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
+    if (!make_map4(&k1, scratch[3], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
+    if (!make_map4(&v1, scratch[5], sdt, a.B, a.H, a.D, a.Sk, kHeadDim)) return cudaErrorInvalidValue;
+  }
+  AttnParams p{};
+  p.B = a.B; p.H = a.H; p.Sq = a.Sq; p.Sk = a.Sk;
+  p.scale = a.scale;
+  p.scale_buf = a.scale_buf;
+  p.scale_uniform = uniform;
+  p.mask = a.mask;
+  p.mask_is_bool = a.mask_is_bool;
+  p.mask_sb = a.mask_sb;
+  p.mask_sh = a.mask_sh;
+  p.tile_class = cls;
+  p.out = a.out;
+  p.out_dtype = a.out_dtype;
+  p.round_scores = tf32 ? 0 : a.ab_dtype + 1;
+  p.status = status;
+  const uint32_t fmt = tf32 ? 2u : (a.ab_dtype == BG_BF16 ? 1u : 0u);
+  p.idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(bkv >> 3) << 17) | ((uint32_t)(kQRows >> 4) << 24);
+  p.idesc_pv = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kHeadDim >> 3) << 17) | ((uint32_t)(kQRows >> 4) << 24);
+  dim3 grid((a.Sq + kQRows - 1) / kQRows, a.H, a.B);
+  cudaError_t e;
+  if (tf32) {
+    const size_t smem = AttnCfg<true>::SmemBytes + 256 + 1024;
+    e = cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attn_fwd_kernel<true><<<grid, kAttnThreads, smem, s>>>(q0, q1, k0, k1, v0, v1, p);
+  } else {
+    const size_t smem = AttnCfg<false>::SmemBytes + 256 + 1024;
+    e = cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attn_fwd_kernel<false><<<grid, kAttnThreads, smem, s>>>(q0, q1, k0, k1, v0, v1, p);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace bg

@@ -201,9 +201,34 @@ struct TcGemm {
   int round_acc;        // 0, or dtype + 1: round the accumulator through f16 / bf16 before the epilogue
   int wide;             // activation arithmetic in fp64 (for fp64 results)
 };
+// Set by the host-only dry compile so that plans can be lowered as they would be on a B200.
+extern bool g_tc_assume_available;
 bool tc_gemm_supported(int64_t M, int64_t N, int64_t K, int ab_dtype);
 cudaError_t launch_gemm_tc(const TcGemm& g, int* status, cudaStream_t s);
 // hi = tf32(x) (round to nearest), lo = x - hi, for fp32 or fp64 input; optional transpose is not done here.
 cudaError_t launch_tf32_split(const void* src, int src_dtype, float* hi, float* lo, int64_t n, cudaStream_t s);
+
+// Fused attention (attn_tc.cu).  Operands are [B,H,S,D] views with element strides; D = 64.
+struct AttnOperand {
+  const void* ptr;
+  int dtype;
+  int64_t stride[4];
+};
+struct AttnProblem {
+  int B, H, Sq, Sk, D;
+  AttnOperand q, k, v;
+  const float* scale_buf;   // [B,H,Sq,Sk] multiplier or null (then `scale`)
+  float scale;
+  const void* mask;         // additive fp32 or bool, rows Sk apart, or null
+  int mask_is_bool;
+  int64_t mask_sb, mask_sh; // element strides over batch / head, 0 when broadcast
+  void* out;                // dense [B,H,Sq,D]
+  int out_dtype;
+  int mode;                 // 0: 16-bit operands (ab_dtype), 1: 3xTF32
+  int ab_dtype;
+};
+bool attn_tc_supported(const AttnProblem& a);
+void attn_scratch_sizes(const AttnProblem& a, int64_t bytes[8]);
+cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], int* status, cudaStream_t s);
 
 }  // namespace bg

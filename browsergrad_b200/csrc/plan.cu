@@ -222,6 +222,18 @@ class Compiler {
     int wide = 0;
     int group = -1;
   };
+  struct AttnPlan {
+    int q = -1, kt = -1, v = -1;      // operand nodes (kt: the [B,H,D,Sk] view fed to the first MATMUL)
+    int mask = -1, mask_is_bool = 0;
+    int scale_node = -1;              // BUFFER-backed multiplier, or -1 with scale_const
+    double scale_const = 1.0;
+    int mode = 1, ab_dtype = BG_F32;
+  };
+  std::map<int, AttnPlan> attn_plan_;     // final MATMUL node -> fused attention
+  std::set<int> attn_absorbed_;           // nodes that only exist inside a fused attention
+  bool match_attention(int n, AttnPlan& ap, std::vector<int>& interior);
+  void plan_attention();
+  void emit_attention(int n, int key);
   std::map<int, EpiPlan> epi_plan_;       // MATMUL node -> folded epilogue
   std::set<int> absorbed_groups_;
   int tc_mode(int n);                      // -1: SIMT; 0: 16-bit operands; 1: 3xTF32
@@ -1551,6 +1563,7 @@ void Compiler::plan_tc_epilogues(const std::map<int, std::vector<int>>& groups) 
   const std::string relu = "where(cmp" + std::to_string((int)BG_CMP_GT) + "(x,c0),x,c0)";
   for (int n = 0; n < (int)nodes_.size(); ++n) {
     if (kind_[n] != K_OTHER || nodes_[n].op != BG_OP_MATMUL) continue;
+    if (attn_plan_.count(n) || attn_absorbed_.count(n)) continue;
     if (tc_mode(n) < 0) continue;
     const int64_t N = nodes_[n].shape[1];
     EpiPlan ep;
@@ -1637,6 +1650,209 @@ void Compiler::plan_tc_epilogues(const std::map<int, std::vector<int>>& groups) 
     epi_plan_[n] = ep;
     absorbed_groups_.insert(g);
   }
+}
+
+// Recognise softmax(scale * Q K^T [+ mask]) V as built by scaled_dot_product_attention
+// (packages/browsergrad-jit/src/python/_functional.py:1505-1534) or by the typed attention op:
+//   MATMUL(q, permuted k) -> [CAST] -> MUL(scale) -> [ADD(mask) | WHERE(mask, -inf, .)] -> FUSED_SOFTMAX -> [CAST] -> MATMUL(., v)
+// Every interior value must have that single consumer.
+bool Compiler::match_attention(int n, AttnPlan& ap, std::vector<int>& interior) {
+  const Node& fin = nodes_[n];
+  if (fin.op != BG_OP_MATMUL || fin.rank != 4 || fin.in.size() != 2) return false;
+  auto single = [&](int v) {
+    std::set<int> c(cons_[v].begin(), cons_[v].end());
+    return c.size() == 1 && v != root_;
+  };
+  int cur = resolve(fin.in[0]);
+  ap.v = resolve(fin.in[1]);
+  if (!single(cur)) return false;
+  if (nodes_[cur].op == BG_OP_CAST) { interior.push_back(cur); cur = resolve(nodes_[cur].in[0]); if (!single(cur)) return false; }
+  if (nodes_[cur].op != BG_OP_FUSED_SOFTMAX || nodes_[cur].rank != 4 || nodes_[cur].iarg[0] != 3) return false;
+  interior.push_back(cur);
+  cur = resolve(nodes_[cur].in[0]);
+  if (!single(cur)) return false;
+  const int64_t B = fin.shape[0], H = fin.shape[1], Sq = fin.shape[2], D = fin.shape[3];
+  const int64_t Sk = nodes_[cur].shape[3];
+  auto is_scores = [&](int v) {
+    const Node& x = nodes_[v];
+    return x.rank == 4 && x.shape[0] == B && x.shape[1] == H && x.shape[2] == Sq && x.shape[3] == Sk;
+  };
+  if (!is_scores(cur)) return false;
+  // mask
+  if (nodes_[cur].op == BG_OP_ADD && nodes_[cur].in.size() == 2) {
+    const int a = resolve(nodes_[cur].in[0]), b = resolve(nodes_[cur].in[1]);
+    int m = -1, nx = -1;
+    for (int k = 0; k < 2; ++k) {
+      const int cand = k ? b : a, other = k ? a : b;
+      const View& mv = view_[cand];
+      if (leaflike_[cand] && !mv.is_const && mv.dtype == BG_F32 && mv.rank >= 2 && mv.rank <= 4 && mv.shape[mv.rank - 1] == Sk &&
+          mv.shape[mv.rank - 2] == Sq && mv.stride[mv.rank - 1] == 1 && mv.stride[mv.rank - 2] == Sk && kind_[other] != K_LEAF) {
+        m = cand; nx = other;
+        break;
+      }
+    }
+    if (m >= 0) {
+      ap.mask = m;
+      interior.push_back(cur);
+      cur = nx;
+      if (!single(cur) || !is_scores(cur)) return false;
+    }
+  } else if (nodes_[cur].op == BG_OP_WHERE && nodes_[cur].in.size() == 3) {
+    const int c = resolve(nodes_[cur].in[0]), f = resolve(nodes_[cur].in[1]), x = resolve(nodes_[cur].in[2]);
+    const View& mv = view_[c];
+    const View& fv = view_[f];
+    const bool neg_inf = fv.is_const && dtype_is_float(fv.dtype) && fv.cf < 0 && fv.cf * 2 == fv.cf;
+    if (!(leaflike_[c] && !mv.is_const && mv.dtype == BG_BOOL && neg_inf && mv.rank >= 2 && mv.rank <= 4 &&
+          mv.shape[mv.rank - 1] == Sk && mv.shape[mv.rank - 2] == Sq && mv.stride[mv.rank - 1] == 1 && mv.stride[mv.rank - 2] == Sk))
+      return false;
+    ap.mask = c;
+    ap.mask_is_bool = 1;
+    interior.push_back(cur);
+    cur = x;
+    if (!single(cur) || !is_scores(cur)) return false;
+  }
+  if (ap.mask >= 0) {
+    const View& mv = view_[ap.mask];
+    for (int d = 0; d < mv.rank - 2; ++d) {
+      const int64_t want = (mv.rank - 2 - d) == 2 ? B : H;   // leading dims line up with [B, H] from the right
+      if (mv.shape[d] != 1 && mv.shape[d] != want) return false;
+    }
+  }
+  // scale
+  if (nodes_[cur].op == BG_OP_MUL && nodes_[cur].in.size() == 2) {
+    const int a = resolve(nodes_[cur].in[0]), b = resolve(nodes_[cur].in[1]);
+    int nx = -1;
+    for (int k = 0; k < 2; ++k) {
+      const int cand = k ? b : a, other = k ? a : b;
+      const View& sv = view_[cand];
+      if (sv.is_const && dtype_is_float(sv.dtype)) { ap.scale_const = sv.cf; ap.scale_node = -1; nx = other; break; }
+      if (leaflike_[cand] && sv.dtype == BG_F32 && sv.rank == 4 && sv.contiguous() && sv.shape[0] == B && sv.shape[1] == H &&
+          sv.shape[2] == Sq && sv.shape[3] == Sk && kind_[other] != K_LEAF) {
+        ap.scale_node = cand; nx = other; break;
+      }
+    }
+    if (nx < 0) return false;
+    interior.push_back(cur);
+    cur = nx;
+    if (!single(cur) || !is_scores(cur)) return false;
+  }
+  if (nodes_[cur].op == BG_OP_CAST) { interior.push_back(cur); cur = resolve(nodes_[cur].in[0]); if (!single(cur) || !is_scores(cur)) return false; }
+  const Node& qk = nodes_[cur];
+  if (qk.op != BG_OP_MATMUL || qk.in.size() != 2) return false;
+  interior.push_back(cur);
+  ap.q = resolve(qk.in[0]);
+  ap.kt = resolve(qk.in[1]);
+  const View& qv = view_[ap.q];
+  const View& kv = view_[ap.kt];
+  const View& vv = view_[ap.v];
+  if (qv.is_const || kv.is_const || vv.is_const || qv.rank != 4 || kv.rank != 4 || vv.rank != 4) return false;
+  if (qv.shape[0] != B || qv.shape[1] != H || qv.shape[2] != Sq || qv.shape[3] != D) return false;
+  if (kv.shape[0] != B || kv.shape[1] != H || kv.shape[2] != D || kv.shape[3] != Sk) return false;
+  if (vv.shape[0] != B || vv.shape[1] != H || vv.shape[2] != Sk || vv.shape[3] != D) return false;
+  // encodings
+  const int qd = qv.dtype, kd = kv.dtype, vd = vv.dtype, od = fin.dtype;
+  if ((qd == BG_F16 || qd == BG_BF16) && kd == qd && vd == qd && od == qd && qk.dtype == qd) { ap.mode = 0; ap.ab_dtype = qd; }
+  else if (qd == BG_F32 && kd == BG_F32 && vd == BG_F32 && od == BG_F32) { ap.mode = 1; ap.ab_dtype = BG_F32; }
+  else if (od == BG_F64 && (ctx_->f64_mode == 1 || (ctx_->f64_mode == 2 && !has_f64_leaf_)) &&
+           (qd == BG_F32 || qd == BG_F64) && (kd == BG_F32 || kd == BG_F64) && (vd == BG_F32 || vd == BG_F64)) { ap.mode = 1; ap.ab_dtype = BG_F32; }
+  else return false;
+  AttnProblem pr{};
+  pr.B = (int)B; pr.H = (int)H; pr.Sq = (int)Sq; pr.Sk = (int)Sk; pr.D = (int)D;
+  pr.mode = ap.mode;
+  pr.ab_dtype = ap.ab_dtype;
+  if (B > 65535 || H > 65535 || Sq > (1 << 24) || Sk > (1 << 24)) return false;
+  return attn_tc_supported(pr);
+}
+
+void Compiler::plan_attention() {
+  attn_plan_.clear();
+  attn_absorbed_.clear();
+  if (!ctx_->fusion || !ctx_->tensor_cores) return;
+  for (int n = 0; n < (int)nodes_.size(); ++n) {
+    if (kind_[n] != K_OTHER || nodes_[n].op != BG_OP_MATMUL) continue;
+    AttnPlan ap;
+    std::vector<int> interior;
+    if (!match_attention(n, ap, interior)) continue;
+    attn_plan_[n] = ap;
+    for (int v : interior) attn_absorbed_.insert(v);
+  }
+}
+
+void Compiler::emit_attention(int n, int key) {
+  const AttnPlan ap = attn_plan_.at(n);
+  const Node& fin = nodes_[n];
+  AttnProblem tmpl{};
+  tmpl.B = (int)fin.shape[0]; tmpl.H = (int)fin.shape[1]; tmpl.Sq = (int)fin.shape[2]; tmpl.D = (int)fin.shape[3];
+  const View qv = view_[ap.q], ktv = view_[ap.kt], vv = view_[ap.v];
+  tmpl.Sk = (int)ktv.shape[3];
+  tmpl.mode = ap.mode;
+  tmpl.ab_dtype = ap.ab_dtype;
+  tmpl.out_dtype = fin.dtype;
+  tmpl.scale = (float)ap.scale_const;
+  tmpl.mask_is_bool = ap.mask_is_bool;
+  auto operand = [&](const View& v, bool swap_last) {
+    AttnOperand o{};
+    o.dtype = v.dtype;
+    for (int d = 0; d < 4; ++d) o.stride[d] = v.stride[d];
+    if (swap_last) std::swap(o.stride[2], o.stride[3]);   // the [B,H,D,Sk] view read as [B,H,Sk,D]
+    for (int d = 0; d < 4; ++d)
+      if (v.shape[d] == 1) o.stride[d] = 0;
+    return o;
+  };
+  tmpl.q = operand(qv, false);
+  tmpl.k = operand(ktv, true);
+  tmpl.v = operand(vv, false);
+  int mask_slot = -1;
+  int64_t mask_off = 0;
+  if (ap.mask >= 0) {
+    const View& mv = view_[ap.mask];
+    mask_slot = mv.slot;
+    mask_off = mv.off * dtype_size(mv.dtype);
+    // leading dims align with [B, H] from the right
+    const int lead = mv.rank - 2;
+    tmpl.mask_sh = lead >= 1 && mv.shape[lead - 1] != 1 ? mv.stride[lead - 1] : 0;
+    tmpl.mask_sb = lead >= 2 && mv.shape[lead - 2] != 1 ? mv.stride[lead - 2] : 0;
+  }
+  int scale_slot = -1;
+  int64_t scale_off = 0;
+  if (ap.scale_node >= 0) { scale_slot = view_[ap.scale_node].slot; scale_off = view_[ap.scale_node].off * 4; }
+  // scratch: Q/K/V^T staging (+ lo parts), tile classes, uniform flag
+  AttnProblem sized = tmpl;
+  sized.mask = ap.mask >= 0 ? (const void*)1 : nullptr;
+  sized.scale_buf = ap.scale_node >= 0 ? (const float*)1 : nullptr;
+  int64_t bytes[8];
+  attn_scratch_sizes(sized, bytes);
+  int scratch_slot[8];
+  PUnit pu;
+  for (int i = 0; i < 8; ++i) {
+    scratch_slot[i] = bytes[i] > 0 ? new_slot(bytes[i], false, -1) : -1;
+    if (scratch_slot[i] >= 0) pu.u.writes.push_back(scratch_slot[i]);
+  }
+  const int sq = qv.slot, sk = ktv.slot, sv = vv.slot, so = view_[n].slot;
+  const int64_t offq = qv.off * dtype_size(qv.dtype), offk = ktv.off * dtype_size(ktv.dtype), offv = vv.off * dtype_size(vv.dtype);
+  pu.order_key = key;
+  pu.dep_nodes = {ap.q, ap.kt, ap.v};
+  if (ap.mask >= 0) pu.dep_nodes.push_back(ap.mask);
+  if (ap.scale_node >= 0) pu.dep_nodes.push_back(ap.scale_node);
+  pu.out_nodes = {n};
+  pu.u.name = std::string(ap.mode == 1 ? "attention_tc_3xtf32" : "attention_tc") + (ap.mask >= 0 ? (ap.mask_is_bool ? "+boolmask" : "+mask") : "") +
+              "[" + dtype_name(fin.dtype) + "]";
+  pu.u.launches = 4 + (ap.mask >= 0) + (ap.scale_node >= 0);
+  cp_->uses_status = true;
+  pu.u.fn = [=](Run& r) {
+    AttnProblem a = tmpl;
+    a.q.ptr = reinterpret_cast<char*>(r.ptr[sq]) + offq;
+    a.k.ptr = reinterpret_cast<char*>(r.ptr[sk]) + offk;
+    a.v.ptr = reinterpret_cast<char*>(r.ptr[sv]) + offv;
+    a.mask = mask_slot >= 0 ? reinterpret_cast<char*>(r.ptr[mask_slot]) + mask_off : nullptr;
+    a.scale_buf = scale_slot >= 0 ? reinterpret_cast<const float*>(reinterpret_cast<char*>(r.ptr[scale_slot]) + scale_off) : nullptr;
+    a.out = r.ptr[so];
+    void* scratch[8];
+    for (int i = 0; i < 8; ++i) scratch[i] = scratch_slot[i] >= 0 ? r.ptr[scratch_slot[i]] : nullptr;
+    cudaError_t e = launch_attention_tc(a, scratch, r.ctx->d_status, r.ctx->stream);
+    return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "attention launch");
+  };
+  add_unit(std::move(pu));
 }
 
 void Compiler::emit_matmul(int n, int key) {
@@ -1888,6 +2104,8 @@ bool Compiler::try_lower() {
   copy_src_.clear();
   tc_epilogues_.clear();
   tc_unit_of_.clear();
+  attn_plan_.clear();
+  attn_absorbed_.clear();
   has_f64_leaf_ = false;
   expand();
   simplify();
@@ -1899,11 +2117,17 @@ bool Compiler::try_lower() {
   std::map<int, std::vector<int>> groups;
   for (int i = 0; i < nn; ++i)
     if (kind_[i] == K_EW) groups[find(i)].push_back(i);
+  plan_attention();
   plan_tc_epilogues(groups);
   // only groups with a materialised member or a tail do any work
   for (auto& kv : groups) {
     const std::vector<int>& mem = kv.second;
     if (absorbed_groups_.count(kv.first)) continue;   // runs as the epilogue of a tensor-core GEMM
+    {
+      bool in_attention = false;
+      for (int m : mem) in_attention |= attn_absorbed_.count(m) != 0;
+      if (in_attention) continue;                       // interior of a fused attention
+    }
     bool live = tail_of_group_[kv.first] >= 0;
     for (int m : mem) live |= need_mat_[m] != 0;
     if (!live) continue;
@@ -1921,6 +2145,8 @@ bool Compiler::try_lower() {
   }
   for (int i = 0; i < nn; ++i) {
     const Node& n = nodes_[i];
+    if (attn_absorbed_.count(i)) continue;
+    if (kind_[i] == K_OTHER && n.op == BG_OP_MATMUL && attn_plan_.count(i)) { emit_attention(i, i); continue; }
     if (kind_[i] == K_ROW && attached_[i] < 0) {
       int64_t rows, cols;
       View xin;
@@ -2258,8 +2484,9 @@ extern "C" int bg_compile_plan_dry(const bg_plan* plan, int fusion, char* out, s
   // Host-only: compiles the plan into its launch list without touching a device.
   if (!plan || !out || capacity == 0) return BG_ERR_INVALID;
   bg_context fake;
-  fake.fusion = fusion != 0;
+  fake.fusion = (fusion & 1) != 0;
   fake.sm_count = 148;
+  bg::g_tc_assume_available = (fusion & 2) != 0;   // lower as on a B200 (tensor-core kernels selectable)
   std::string text;
   int rc = BG_OK;
   try {
@@ -2270,6 +2497,7 @@ extern "C" int bg_compile_plan_dry(const bg_plan* plan, int fusion, char* out, s
     text = "error: " + ce.msg;
     rc = ce.code > 0 ? ce.code : BG_ERR_UNSUPPORTED;
   }
+  bg::g_tc_assume_available = false;
   strncpy(out, text.c_str(), capacity - 1);
   out[capacity - 1] = 0;
   return rc;

@@ -211,7 +211,8 @@ int bg_cross_entropy_noalloc(const float* logits, const int64_t* targets, float*
                              int64_t classes, int64_t inner, int reduction, int64_t ignore_index,
                              void* stream, char* err, size_t err_capacity);
 /* Host-only diagnostic: compiles `plan` into its kernel list (one name per line) without a
- * device or a context; `fusion` = 0 disables group formation.  Used to test the plan compiler
+ * device or a context; `fusion` bit 0 enables group formation, bit 1 lowers as on a B200 (tensor-core
+ * kernels selectable).  Used to test the plan compiler
  * on machines without a GPU. */
 int bg_compile_plan_dry(const bg_plan* plan, int fusion, char* out, size_t capacity);
 /* The CUDA stream all work of this context is ordered on (a cudaStream_t). */

@@ -162,6 +162,21 @@ CASES: Dict[str, Case] = {
                              lambda api, t, raw: configs.attention(api, t, "mask")),
     "c4_attn_causal_d64": Case(_attn_small(1, 2, 160, 64),
                                lambda api, t, raw: configs.attention(api, t, "causal")),
+    "c4_attn_causal_tiles": Case(_attn_small(2, 2, 320, 64),
+                                 lambda api, t, raw: configs.attention(api, t, "causal")),
+    "c4_attn_mask_tiles": Case(_attn_small(2, 2, 320, 64),
+                               lambda api, t, raw: configs.attention(api, t, "mask")),
+    "c4_attn_nomask_d64": Case(_attn_small(1, 3, 200, 64),
+                               lambda api, t, raw: configs.attention(api, t, "none")),
+    "c4_attn_mask_f16": Case(_attn_small(2, 2, 320, 64),
+                             lambda api, t, raw: configs.attention(api, t, "mask", "float16"), rtol=2e-2),
+    "c4_attn_causal_f16": Case(_attn_small(1, 2, 160, 64),
+                               lambda api, t, raw: configs.attention(api, t, "causal", "float16"), rtol=2e-2),
+    "c4_attn_mask_bf16": Case(_attn_small(2, 2, 320, 64),
+                              lambda api, t, raw: configs.attention(api, t, "mask", "bfloat16"), rtol=2e-2,
+                              reference_has_it=False),
+    "typed_attention_d64": Case(_attn_small(2, 2, 136, 64),
+                                lambda api, t, raw: api.attention_forward(t["q"], t["k"], t["v"])),
     "c4_attn_full": Case(_attn_small(1, 2, 96, 32),
                          lambda api, t, raw: configs.attention(api, t, "none")),
     "c5_gpt_tiny": Case(_gpt_tiny, lambda api, t, raw: configs.gpt_forward(api, t, raw["_meta"]),

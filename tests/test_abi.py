@@ -134,3 +134,28 @@ def test_no_gpu_means_loud_failure():
     from browsergrad_b200 import CudaBridge
     with pytest.raises(KernelError, match="no CPU fallback"):
         CudaBridge(0)
+
+
+def _lines_for(name, flags=3):
+    t, _, _ = build_case(CASES[name])
+    _, plan = front.plan_for(t._uop)
+    rc, lines = dry(plan, fusion=flags)
+    assert rc == 0, lines
+    return lines
+
+
+def test_b200_lowering_of_linear_and_attention():
+    """With tensor-core kernels selectable the Linear cases fold their epilogue into one GEMM and the
+    SDPA graphs collapse into one attention kernel."""
+    assert _lines_for("c3_tc_f32") == ["gemm_tc_3xtf32+bias+gelu[float32]"]
+    assert _lines_for("c3_tc_relu") == ["gemm_tc_3xtf32+bias+relu[float32]"]
+    assert _lines_for("c3_tc_ragged") == ["gemm_tc_3xtf32+bias[float32]"]
+    f16 = _lines_for("c3_tc_f16")
+    assert f16[-1] == "gemm_tc+bias+gelu[float16]" and all(ln.startswith(("ew[CAST", "static_ew[CAST")) for ln in f16[:-1]), f16
+    assert _lines_for("c4_attn_mask_d64") == ["attention_tc_3xtf32+mask[float32]"]
+    assert _lines_for("c4_attn_causal_tiles") == ["attention_tc_3xtf32+boolmask[float32]"]
+    assert _lines_for("typed_attention_d64") == ["attention_tc_3xtf32[float32]"]
+    amp = _lines_for("c4_attn_mask_f16")
+    assert amp[-1] == "attention_tc+mask[float16]", amp
+    # head dimension 16 is outside the fused kernel: composed path
+    assert any(ln.startswith("gemm_simt") for ln in _lines_for("c4_attn_mask"))

@@ -85,3 +85,31 @@ def test_linear_runs_on_tensor_cores_with_folded_epilogue(bridge, name, expect):
     finally:
         bridge.set_option("tensor_cores", 1)
     check(case, simt, want, name + " (SIMT)")
+
+
+@pytest.mark.parametrize("name,expect", [
+    ("c4_attn_mask_d64", "attention_tc_3xtf32+mask[float32]"),
+    ("c4_attn_causal_d64", "attention_tc_3xtf32+boolmask[float32]"),
+    ("c4_attn_causal_tiles", "attention_tc_3xtf32+boolmask[float32]"),
+    ("c4_attn_mask_tiles", "attention_tc_3xtf32+mask[float32]"),
+    ("c4_attn_nomask_d64", "attention_tc_3xtf32[float32]"),
+    ("typed_attention_d64", "attention_tc_3xtf32[float32]"),
+    ("c4_attn_mask_f16", "attention_tc+mask[float16]"),
+    ("c4_attn_causal_f16", "attention_tc+boolmask[float16]"),
+    ("c4_attn_mask_bf16", "attention_tc+mask[bfloat16]"),
+])
+def test_sdpa_runs_as_one_fused_attention_kernel(bridge, name, expect):
+    case = CASES[name]
+    t, store, _ = build_case(case)
+    want = oracle_value(t, store)
+    got = realize_cuda(t, bridge)
+    trace = bridge.last_plan_trace()
+    assert expect in trace, trace
+    assert not any(ln.startswith(("gemm", "row[", "static_row[")) for ln in trace), trace
+    check(case, got, want, name)
+    bridge.set_option("tensor_cores", 0)        # composed path: batched GEMM + fused softmax + batched GEMM
+    try:
+        composed = realize_cuda(t, bridge)
+    finally:
+        bridge.set_option("tensor_cores", 1)
+    check(case, composed, want, name + " (composed)")
