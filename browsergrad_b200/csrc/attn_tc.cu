@@ -8,7 +8,7 @@
 // One CTA owns 128 query rows of one (batch, head):
 //   warp 0     TMA producer: Q once, then K / V^T tiles into a ring of stages
 //   warp 1     MMA issuer (one thread): QK^T two tiles ahead, P.V as soon as P is published
-//   warps 2-5  softmax: one thread per query row
+//   warps 2-9  softmax: two threads per query row (each half of the keys / output columns)
 // Operand encodings: f16 / bf16 (128 keys per tile), or 3xTF32 for fp32-faithful results (32 keys
 // per tile; Q, K, V^T pre-split into hi = tf32(x), lo = x - hi; P split on the fly; the three
 // cross products lo.hi, hi.lo, hi.hi go into one accumulator).  All operands are K-major tiles
@@ -31,7 +31,7 @@ using namespace tc;
 
 constexpr int kHeadDim = 64;
 constexpr int kQRows = 128;
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;   // producer warp, MMA warp, 2 x 4 softmax warps
 
 __device__ __forceinline__ void tma_load_4d(const CUtensorMap* map, void* smem_dst, uint64_t* bar, int x, int y, int z, int w) {
   asm volatile(
@@ -39,6 +39,12 @@ __device__ __forceinline__ void tma_load_4d(const CUtensorMap* map, void* smem_d
       :
       : "r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 struct AttnParams {
@@ -49,7 +55,9 @@ struct AttnParams {
   const void* mask;            // additive fp32 or bool (1 = fill -inf), or null
   int mask_is_bool;
   long long mask_sb, mask_sh;  // element strides over batch / head (0 when broadcast); rows are Sk apart
-  const unsigned char* tile_class;   // [ceil(Sq/128), ceil(Sk/BKV)]: 0 skip, 1 plain, 2 mixed; null = all plain
+  const unsigned char* tile_class;   // [ceil(Sq/128), ceil(Sk/BKV)]: 0 skip, 1 plain, 2 binary mixed, 3 biased; null = none computed
+  const uint32_t* mask_bits;         // [Sq, mask_words] "masked" bits, valid where tile_class is
+  int mask_words;
   void* out;                   // [B,H,Sq,64]
   int out_dtype;
   int round_scores;            // dtype + 1: round S through f16 / bf16 before the softmax (autocast graphs)
@@ -93,9 +101,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
   uint64_t* pv_full = p_full + 2;         // [2]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_full + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* pmax = reinterpret_cast<float*>(tmem_holder + 4);   // [2 buffers][2 halves][128 rows] tile maxima
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // query tiles are issued last-first: under a causal mask the late tiles carry the most key tiles
+  const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int q0 = q_tile * kQRows;
   const int n_kv = (p.Sk + BKV - 1) / BKV;
   const unsigned char* cls = p.tile_class ? p.tile_class + (size_t)q_tile * n_kv : nullptr;
@@ -103,7 +113,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < C::NST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&pv_full[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 8); mbar_init(&pv_full[i], 1); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -230,14 +240,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
       }
     }
   } else {
-    // ---- softmax: one thread per query row ----------------------------------------------------
-    const int quarter = warp & 3;
+    // ---- softmax: two threads per query row, each owning half of the tile's keys and half of the
+    //      output columns; the row max and the row sum are combined through shared memory -----------
+    const int wg = (warp - 2) >> 2;                 // 0 / 1: which half
+    const int quarter = warp & 3;                   // TMEM lane quarter this warp may read
     const int r_in_tile = quarter * 32 + lane;
     const int row = q0 + r_in_tile;
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
-    float o[kHeadDim];
+    constexpr int HK = BKV / 2;                     // keys per thread per tile
+    constexpr int HD = kHeadDim / 2;                // output columns per thread
+    float o[HD];
 #pragma unroll
-    for (int d = 0; d < kHeadDim; ++d) o[d] = 0.f;
+    for (int d = 0; d < HD; ++d) o[d] = 0.f;
     float m = -CUDART_INF_F, l = 0.f;
     float alpha_prev = 1.f;
     float scale = p.scale;
@@ -250,59 +264,98 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
     auto fold_pv = [&](int tt, float alpha) -> bool {
       if (!mbar_wait(&pv_full[tt & 1], (uint32_t)(tt >> 1) & 1u, abort_flag)) return false;
       tc_fence_after();
-      const uint32_t src = tmem_pv + (uint32_t)((tt & 1) * kHeadDim) + lane_sel;
+      uint32_t r[32];
+      tmem_ld32(tmem_pv + (uint32_t)((tt & 1) * kHeadDim + wg * HD) + lane_sel, r);
 #pragma unroll
-      for (int c = 0; c < kHeadDim / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(src + (uint32_t)(c * 32), r);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(r[i]));
-      }
+      for (int i = 0; i < HD; ++i) o[i] = fmaf(o[i], alpha, __uint_as_float(r[i]));
       return true;
     };
     for (int j = 0; j < n_kv && ok; ++j) {
-      const int tclass = cls ? cls[j] : (p.mask ? 2 : 1);
+      const int tclass = cls ? cls[j] : (p.mask ? 3 : 1);
       if (tclass == 0) continue;
       const int buf = t & 1;
       if (!mbar_wait(&s_full[buf], (uint32_t)(t >> 1) & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const int k0 = j * BKV;
-      float sv[BKV];
+      const int k0 = j * BKV + wg * HK;             // first key of this thread's half
+      float sv[HK];
+      {
+        const uint32_t src = tmem_s + (uint32_t)(buf * C::SCols + wg * HK) + lane_sel;
+        if (HK == 16) {
+          uint32_t r[16];
+          tmem_ld16(src, r);
 #pragma unroll
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_s + (uint32_t)(buf * C::SCols) + lane_sel + (uint32_t)(c * 32), r);
+          for (int i = 0; i < 16; ++i) sv[i] = __uint_as_float(r[i]);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) sv[c * 32 + i] = __uint_as_float(r[i]);
-      }
-      // scale, mask, row max
-      float mt = -CUDART_INF_F;
-      const bool need_mask = p.mask && tclass == 2;
+          for (int c = 0; c < HK / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(src + (uint32_t)(c * 32), r);
 #pragma unroll
-      for (int i = 0; i < BKV; ++i) {
-        float x = sv[i];
-        if (p.round_scores == BG_F16 + 1) x = __half2float(__float2half_rn(x));
-        else if (p.round_scores == BG_BF16 + 1) x = __bfloat162float(__float2bfloat16_rn(x));
-        const int key = k0 + i;
-        const bool in_range = key < p.Sk;
-        x = __fmul_rn(x, per_elem_scale ? (in_range ? p.scale_buf[score_row + key] : 0.f) : scale);
-        if (need_mask && in_range) {
-          if (p.mask_is_bool) { if (reinterpret_cast<const unsigned char*>(p.mask)[mask_row + key]) x = -CUDART_INF_F; }
-          else x = __fadd_rn(x, reinterpret_cast<const float*>(p.mask)[mask_row + key]);
+            for (int i = 0; i < 32; ++i) sv[(c * 32 + i) % HK] = __uint_as_float(r[i]);
+          }
         }
-        if (!in_range) x = -CUDART_INF_F;
-        sv[i] = x;
-        mt = fmaxf(mt, x);
       }
+      // Probabilities: p = 2^((x - m) * log2(e)) with x = scale * s (+ mask).  The common case -- whole
+      // tile in range, no mask to apply, one positive scale -- folds scale and log2(e) into a single FMA
+      // per score ahead of the hardware exp2; anything else takes the element-wise path.
+      constexpr float kLog2e = 1.4426950408889634f;
+      // (autocast graphs round S to the 16-bit dtype between the two products; the fused kernel keeps
+      //  the scores in fp32, which stays inside the 2e-2 autocast tolerance)
+      const bool need_mask = p.mask && tclass == 3;
+      const bool fast = !need_mask && !per_elem_scale && scale > 0.f && (tclass == 2 || j * BKV + BKV <= p.Sk);
+      float mt = -CUDART_INF_F;
+      if (fast && tclass == 2) {
+        // binary mask: one word of "masked" bits covers 32 keys of this row
+        const uint32_t* wrow = p.mask_bits + (size_t)(row < p.Sq ? row : 0) * p.mask_words + (k0 >> 5);
+#pragma unroll
+        for (int w = 0; w < (HK + 31) / 32; ++w) {
+          uint32_t word = wrow[w] >> (k0 & 31);
+#pragma unroll
+          for (int i = 0; i < (HK < 32 ? HK : 32); ++i)
+            if ((word >> i) & 1u) sv[w * 32 + i] = -CUDART_INF_F;
+        }
+      }
+      if (fast) {
+#pragma unroll
+        for (int i = 0; i < HK; ++i) mt = fmaxf(mt, sv[i]);
+        mt *= scale;
+      } else {
+#pragma unroll
+        for (int i = 0; i < HK; ++i) {
+          const int key = k0 + i;
+          const bool in_range = key < p.Sk;
+          float x = __fmul_rn(sv[i], per_elem_scale ? (in_range ? p.scale_buf[score_row + key] : 0.f) : scale);
+          if (need_mask && in_range) {
+            if (p.mask_is_bool) { if (reinterpret_cast<const unsigned char*>(p.mask)[mask_row + key]) x = -CUDART_INF_F; }
+            else x = __fadd_rn(x, reinterpret_cast<const float*>(p.mask)[mask_row + key]);
+          }
+          if (!in_range) x = -CUDART_INF_F;
+          sv[i] = x;
+          mt = fmaxf(mt, x);
+        }
+      }
+      // the two halves of a row agree on the tile max
+      pmax[(buf * 2 + wg) * kQRows + r_in_tile] = mt;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      mt = fmaxf(mt, pmax[(buf * 2 + (wg ^ 1)) * kQRows + r_in_tile]);
       const float m_new = fmaxf(m, mt);
       const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;
-      const float alpha = expf(m - m_use);         // m = -inf gives 0: nothing accumulated yet
       float psum = 0.f;
+      if (fast) {
+        const float c = scale * kLog2e, ml = m_use * kLog2e;
 #pragma unroll
-      for (int i = 0; i < BKV; ++i) {
-        sv[i] = expf(sv[i] - m_use);
-        psum += sv[i];
+        for (int i = 0; i < HK; ++i) {
+          sv[i] = ex2_approx(fmaf(sv[i], c, -ml));
+          psum += sv[i];
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < HK; ++i) {
+          sv[i] = ex2_approx((sv[i] - m_use) * kLog2e);
+          psum += sv[i];
+        }
       }
+      const float alpha = ex2_approx((m - m_use) * kLog2e);    // m = -inf gives 0: nothing accumulated yet
       l = fmaf(l, alpha, psum);
       m = m_new;
       // publish P in the K-major 128-byte-swizzled operand layout: row r_in_tile, 16-byte chunk c of
@@ -310,37 +363,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
       unsigned char* pb = sP + buf * C::PBytes;
       const int sw = r_in_tile & 7;
       if (TF32) {
+        // 32 keys = one 128-byte row; this thread owns chunks wg*4 .. wg*4+3 (16 keys)
         unsigned char* hi_row = pb + r_in_tile * 128;
         unsigned char* lo_row = pb + kQRows * 128 + r_in_tile * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 4; ++c) {
           float hi[4], lo[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             uint32_t hbits;
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hbits) : "f"(sv[c * 4 + e]));
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hbits) : "f"(sv[(c * 4 + e) % HK]));
             hi[e] = __uint_as_float(hbits);
-            lo[e] = sv[c * 4 + e] - hi[e];
+            lo[e] = sv[(c * 4 + e) % HK] - hi[e];
           }
-          *reinterpret_cast<float4*>(hi_row + ((c ^ sw) << 4)) = make_float4(hi[0], hi[1], hi[2], hi[3]);
-          *reinterpret_cast<float4*>(lo_row + ((c ^ sw) << 4)) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+          const int chunk = (wg * 4 + c) ^ sw;
+          *reinterpret_cast<float4*>(hi_row + (chunk << 4)) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+          *reinterpret_cast<float4*>(lo_row + (chunk << 4)) = make_float4(lo[0], lo[1], lo[2], lo[3]);
         }
       } else {
+        // 128 keys = two k-blocks of 64; this thread owns k-block `wg`
         const bool bf = p.round_scores == BG_BF16 + 1;
+        unsigned char* prow = pb + wg * (kQRows * 128) + r_in_tile * 128;
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb) {
-          unsigned char* prow = pb + kb * (kQRows * 128) + r_in_tile * 128;
+        for (int c = 0; c < 8; ++c) {
+          uint32_t w[4];
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float a0 = sv[kb * 64 + c * 8 + 2 * e], a1 = sv[kb * 64 + c * 8 + 2 * e + 1];
-              if (bf) { __nv_bfloat162 v2 = __floats2bfloat162_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
-              else { __half2 v2 = __floats2half2_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
-            }
-            *reinterpret_cast<uint4*>(prow + ((c ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          for (int e = 0; e < 4; ++e) {
+            const float a0 = sv[(c * 8 + 2 * e) % HK], a1 = sv[(c * 8 + 2 * e + 1) % HK];
+            if (bf) { __nv_bfloat162 v2 = __floats2bfloat162_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
+            else { __half2 v2 = __floats2half2_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
           }
+          *reinterpret_cast<uint4*>(prow + ((c ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
       fence_async_smem();
@@ -353,26 +406,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
       ++t;
     }
     if (ok && t > 0) ok = fold_pv(t - 1, alpha_prev);
+    // combine the two halves' row sums (pmax is idle now; every softmax thread reaches this barrier)
+    pmax[wg * kQRows + r_in_tile] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l += pmax[(wg ^ 1) * kQRows + r_in_tile];
     if (ok && row < p.Sq) {
       const float inv = 1.0f / l;   // l = 0 for a fully masked row: 0 * inf = NaN, as the reference's softmax gives
-      const size_t base = ((size_t)(b * p.H + h) * p.Sq + row) * kHeadDim;
+      const size_t base = ((size_t)(b * p.H + h) * p.Sq + row) * kHeadDim + wg * HD;
       if (p.out_dtype == BG_F32) {
         float* out = reinterpret_cast<float*>(p.out) + base;
 #pragma unroll
-        for (int d = 0; d < kHeadDim; d += 4)
+        for (int d = 0; d < HD; d += 4)
           *reinterpret_cast<float4*>(out + d) = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
       } else if (p.out_dtype == BG_F64) {
         double* out = reinterpret_cast<double*>(p.out) + base;
 #pragma unroll
-        for (int d = 0; d < kHeadDim; d += 2) *reinterpret_cast<double2*>(out + d) = make_double2((double)(o[d] * inv), (double)(o[d + 1] * inv));
+        for (int d = 0; d < HD; d += 2) *reinterpret_cast<double2*>(out + d) = make_double2((double)(o[d] * inv), (double)(o[d + 1] * inv));
       } else if (p.out_dtype == BG_F16) {
         __half* out = reinterpret_cast<__half*>(p.out) + base;
 #pragma unroll
-        for (int d = 0; d < kHeadDim; d += 2) *reinterpret_cast<__half2*>(out + d) = __floats2half2_rn(o[d] * inv, o[d + 1] * inv);
+        for (int d = 0; d < HD; d += 2) *reinterpret_cast<__half2*>(out + d) = __floats2half2_rn(o[d] * inv, o[d + 1] * inv);
       } else {
         __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + base;
 #pragma unroll
-        for (int d = 0; d < kHeadDim; d += 2) *reinterpret_cast<__nv_bfloat162*>(out + d) = __floats2bfloat162_rn(o[d] * inv, o[d + 1] * inv);
+        for (int d = 0; d < HD; d += 2) *reinterpret_cast<__nv_bfloat162*>(out + d) = __floats2bfloat162_rn(o[d] * inv, o[d + 1] * inv);
       }
     }
   }
@@ -431,31 +488,43 @@ __global__ void attn_prep_kernel(PrepView src, void* dst_a, void* dst_b, int B, 
   }
 }
 
-// class of each (128-query, BKV-key) tile of a mask shared by all batches and heads:
-// 0 = every score masked out (skip), 1 = mask has no effect, 2 = mixed
-__global__ void attn_mask_class_kernel(const void* mask, int is_bool, int Sq, int Sk, int bkv, unsigned char* cls, int n_kv) {
+// Pre-pass over a mask shared by all batches and heads.  Per (128-query, BKV-key) tile it writes a class:
+//   0 = every score masked out (skip the tile), 1 = the mask has no effect, 2 = binary (0 / -inf, or
+//   boolean) and mixed, 3 = carries finite biases that must be added;
+// and per (row, 32 keys) one word of "masked" bits (keys beyond Sk count as masked), so that binary
+// tiles are applied from one 32/64-bit load per thread instead of one global load per score.
+__global__ void attn_mask_class_kernel(const void* mask, int is_bool, int Sq, int Sk, int bkv, unsigned char* cls, int n_kv,
+                                       uint32_t* bits, int words_per_row) {
   const int qt = blockIdx.y, kt = blockIdx.x;
-  __shared__ int any_open, any_closed;
-  if (threadIdx.x == 0) { any_open = 0; any_closed = 0; }
+  __shared__ int any_open, any_closed, any_general;
+  if (threadIdx.x == 0) { any_open = 0; any_closed = 0; any_general = 0; }
   __syncthreads();
-  int open = 0, closed = 0;
-  const int rows = min(kQRows, Sq - qt * kQRows), cols = min(bkv, Sk - kt * bkv);
-  for (int i = threadIdx.x; i < rows * cols; i += blockDim.x) {
-    const int r = qt * kQRows + i / cols, c = kt * bkv + i % cols;
-    const size_t off = (size_t)r * Sk + c;
-    if (is_bool) {
-      if (reinterpret_cast<const unsigned char*>(mask)[off]) closed = 1; else open = 1;
-    } else {
-      const float v = reinterpret_cast<const float*>(mask)[off];
-      if (v == -CUDART_INF_F) closed = 1;
-      else if (v == 0.f) open = 1;
-      else { open = 1; closed = 1; }   // a finite bias: must be applied
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  const int words = bkv / 32;
+  int open = 0, closed = 0, general = 0;
+  for (int item = warp; item < kQRows * words; item += n_warps) {
+    const int r = qt * kQRows + item / words, w = kt * words + item % words;
+    const int key = w * 32 + lane;
+    bool is_closed = true, is_general = false;
+    if (r < Sq && key < Sk) {
+      const size_t off = (size_t)r * Sk + key;
+      if (is_bool) is_closed = reinterpret_cast<const unsigned char*>(mask)[off] != 0;
+      else {
+        const float v = reinterpret_cast<const float*>(mask)[off];
+        is_closed = v == -CUDART_INF_F;
+        is_general = !is_closed && v != 0.f;
+      }
+      if (is_closed) closed = 1; else open = 1;
+      if (is_general) general = 1;
     }
+    const uint32_t word = __ballot_sync(0xffffffffu, is_closed);
+    if (lane == 0 && r < Sq && w < words_per_row) bits[(size_t)r * words_per_row + w] = word;
   }
   if (open) atomicOr(&any_open, 1);
   if (closed) atomicOr(&any_closed, 1);
+  if (general) atomicOr(&any_general, 1);
   __syncthreads();
-  if (threadIdx.x == 0) cls[(size_t)qt * n_kv + kt] = any_closed ? (any_open ? 2 : 0) : 1;
+  if (threadIdx.x == 0) cls[(size_t)qt * n_kv + kt] = any_general ? 3 : (any_closed ? (any_open ? 2 : 0) : 1);
 }
 
 __global__ void attn_uniform_kernel(const float* buf, long long n, int* flag) {
@@ -526,42 +595,59 @@ void attn_scratch_sizes(const AttnProblem& a, int64_t bytes[8]) {
   bytes[3] = a.mode == 1 ? nk * es : 0;     // K lo
   bytes[4] = nk * es;                       // V^T (hi)
   bytes[5] = a.mode == 1 ? nk * es : 0;     // V^T lo
-  bytes[6] = a.mask ? (int64_t)((a.Sq + kQRows - 1) / kQRows) * ((a.Sk + bkv - 1) / bkv) : 0;   // tile classes
+  // tile classes (rounded up to 256 bytes) followed by the per-row mask bit words
+  const int64_t n_cls = (int64_t)((a.Sq + kQRows - 1) / kQRows) * ((a.Sk + bkv - 1) / bkv);
+  const int64_t words = (int64_t)((a.Sk + bkv - 1) / bkv) * (bkv / 32);
+  bytes[6] = a.mask ? ((n_cls + 255) & ~(int64_t)255) + (int64_t)a.Sq * words * 4 : 0;
   bytes[7] = a.scale_buf ? 4 : 0;           // uniform-scale flag
 }
 
-cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], int* status, cudaStream_t s) {
+cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bool check_uniform, int* status, cudaStream_t s) {
   const bool tf32 = a.mode == 1;
   const int bkv = tf32 ? 32 : 128;
   const int sdt = tf32 ? BG_F32 : a.ab_dtype;
   // operand staging: dense Q, K, V^T in the kernel's encoding
   const AttnOperand* ops[3] = {&a.q, &a.k, &a.v};
   const int seq[3] = {a.Sq, a.Sk, a.Sk};
+  const void* staged[3] = {scratch[0], scratch[2], scratch[4]};
   for (int i = 0; i < 3; ++i) {
-    PrepView v{ops[i]->ptr, ops[i]->dtype, {ops[i]->stride[0], ops[i]->stride[1], ops[i]->stride[2], ops[i]->stride[3]}};
     const long long n = (long long)a.B * a.H * seq[i] * a.D;
+    // 16-bit Q / K that are already dense [B,H,S,D] feed the TMA maps directly
+    const bool dense = ops[i]->stride[3] == 1 && ops[i]->stride[2] == a.D && ops[i]->stride[1] == (long long)seq[i] * a.D &&
+                       ops[i]->stride[0] == (long long)a.H * seq[i] * a.D;
+    if (!tf32 && i < 2 && dense && ops[i]->dtype == a.ab_dtype && (reinterpret_cast<uintptr_t>(ops[i]->ptr) & 15) == 0) {
+      staged[i] = ops[i]->ptr;
+      continue;
+    }
+    PrepView v{ops[i]->ptr, ops[i]->dtype, {ops[i]->stride[0], ops[i]->stride[1], ops[i]->stride[2], ops[i]->stride[3]}};
     attn_prep_kernel<<<prep_grid(n), 256, 0, s>>>(v, scratch[2 * i], scratch[2 * i + 1], a.B, a.H, seq[i], a.D, i == 2, tf32 ? 1 : 0);
   }
   unsigned char* cls = nullptr;
+  uint32_t* bits = nullptr;
+  const int n_kv_tiles = (a.Sk + bkv - 1) / bkv;
+  const int words_per_row = n_kv_tiles * (bkv / 32);
   if (a.mask && a.mask_sb == 0 && a.mask_sh == 0) {
     cls = reinterpret_cast<unsigned char*>(scratch[6]);
-    const int n_kv = (a.Sk + bkv - 1) / bkv, n_q = (a.Sq + kQRows - 1) / kQRows;
-    attn_mask_class_kernel<<<dim3(n_kv, n_q), 256, 0, s>>>(a.mask, a.mask_is_bool, a.Sq, a.Sk, bkv, cls, n_kv);
+    const int n_q = (a.Sq + kQRows - 1) / kQRows;
+    bits = reinterpret_cast<uint32_t*>(cls + (((size_t)n_q * n_kv_tiles + 255) & ~(size_t)255));
+    attn_mask_class_kernel<<<dim3(n_kv_tiles, n_q), 256, 0, s>>>(a.mask, a.mask_is_bool, a.Sq, a.Sk, bkv, cls, n_kv_tiles, bits, words_per_row);
   }
   int* uniform = nullptr;
   if (a.scale_buf) {
     uniform = reinterpret_cast<int*>(scratch[7]);
-    cudaError_t e = cudaMemsetAsync(uniform, 1, 1, s);   // low byte 1 -> flag != 0 (the other bytes are cleared next)
-    if (e != cudaSuccess) return e;
-    e = cudaMemsetAsync(reinterpret_cast<char*>(uniform) + 1, 0, 3, s);
-    if (e != cudaSuccess) return e;
-    const long long n = (long long)a.B * a.H * a.Sq * a.Sk;
-    attn_uniform_kernel<<<prep_grid(n), 256, 0, s>>>(a.scale_buf, n, uniform);
+    if (check_uniform) {
+      cudaError_t e = cudaMemsetAsync(uniform, 1, 1, s);   // low byte 1 -> flag != 0 (the other bytes are cleared next)
+      if (e != cudaSuccess) return e;
+      e = cudaMemsetAsync(reinterpret_cast<char*>(uniform) + 1, 0, 3, s);
+      if (e != cudaSuccess) return e;
+      const long long n = (long long)a.B * a.H * a.Sq * a.Sk;
+      attn_uniform_kernel<<<prep_grid(n), 256, 0, s>>>(a.scale_buf, n, uniform);
+    }
   }
   CUtensorMap q0, q1, k0, k1, v0, v1;
-  if (!make_map4(&q0, scratch[0], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
-  if (!make_map4(&k0, scratch[2], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
-  if (!make_map4(&v0, scratch[4], sdt, a.B, a.H, a.D, a.Sk, kHeadDim)) return cudaErrorInvalidValue;
+  if (!make_map4(&q0, staged[0], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
+  if (!make_map4(&k0, staged[1], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
+  if (!make_map4(&v0, staged[2], sdt, a.B, a.H, a.D, a.Sk, kHeadDim)) return cudaErrorInvalidValue;
   q1 = q0; k1 = k0; v1 = v0;
   if (tf32) {
     if (!make_map4(&q1, scratch[1], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
@@ -578,6 +664,8 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], in
   p.mask_sb = a.mask_sb;
   p.mask_sh = a.mask_sh;
   p.tile_class = cls;
+  p.mask_bits = bits;
+  p.mask_words = words_per_row;
   p.out = a.out;
   p.out_dtype = a.out_dtype;
   p.round_scores = tf32 ? 0 : a.ab_dtype + 1;
@@ -588,12 +676,12 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], in
   dim3 grid((a.Sq + kQRows - 1) / kQRows, a.H, a.B);
   cudaError_t e;
   if (tf32) {
-    const size_t smem = AttnCfg<true>::SmemBytes + 256 + 1024;
+    const size_t smem = AttnCfg<true>::SmemBytes + 256 + 2048 + 1024;
     e = cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     attn_fwd_kernel<true><<<grid, kAttnThreads, smem, s>>>(q0, q1, k0, k1, v0, v1, p);
   } else {
-    const size_t smem = AttnCfg<false>::SmemBytes + 256 + 1024;
+    const size_t smem = AttnCfg<false>::SmemBytes + 256 + 2048 + 1024;
     e = cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     attn_fwd_kernel<false><<<grid, kAttnThreads, smem, s>>>(q0, q1, k0, k1, v0, v1, p);

@@ -169,6 +169,29 @@ int d2h(bg_context* ctx, void* dst, const void* src, size_t n) {
   return BG_OK;
 }
 
+int* uniform_flag_for(bg_context* ctx, const void* ptr, bool* fresh) {
+  *fresh = false;
+  auto it = ctx->uniform_flags.find(ptr);
+  if (it != ctx->uniform_flags.end()) return it->second;
+  if (!ctx->uniform_pool) {
+    if (cudaMalloc(&ctx->uniform_pool, 1024 * sizeof(int)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    for (int i = 1023; i >= 0; --i) ctx->uniform_free.push_back(i);
+  }
+  if (ctx->uniform_free.empty()) return nullptr;
+  int* flag = ctx->uniform_pool + ctx->uniform_free.back();
+  ctx->uniform_free.pop_back();
+  ctx->uniform_flags[ptr] = flag;
+  *fresh = true;
+  return flag;
+}
+
+void uniform_flag_drop(bg_context* ctx, const void* ptr) {
+  auto it = ctx->uniform_flags.find(ptr);
+  if (it == ctx->uniform_flags.end()) return;
+  ctx->uniform_free.push_back((int)(it->second - ctx->uniform_pool));
+  ctx->uniform_flags.erase(it);
+}
+
 static int64_t numel_of(const int64_t* shape, int rank) {
   int64_t n = 1;
   for (int i = 0; i < rank; ++i) n *= shape[i];
@@ -231,6 +254,7 @@ int bg_destroy(bg_context* ctx) {
     cudaEventDestroy(pe.second.second);
   }
   cudaStreamSynchronize(ctx->stream);
+  if (ctx->uniform_pool) cudaFree(ctx->uniform_pool);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   if (ctx->stage) cudaFreeHost(ctx->stage);
@@ -295,6 +319,7 @@ int bg_release(bg_context* ctx, bg_handle h) {
   auto it = ctx->handles.find(h);
   if (it == ctx->handles.end()) return BG_OK;  // idempotent, unknown handle is a no-op
   cudaSetDevice(ctx->device);
+  uniform_flag_drop(ctx, it->second.ptr);
   dev_free(ctx, it->second.ptr, it->second.bytes);
   ctx->handles.erase(it);
   return BG_OK;

@@ -84,6 +84,7 @@ struct Slot {
 struct Run {
   bg_context* ctx;
   std::vector<void*> ptr;
+  std::vector<char> from_handle;   // slot is bound to a caller-owned handle (its contents outlive the run)
 };
 
 struct Unit {
@@ -1849,7 +1850,14 @@ void Compiler::emit_attention(int n, int key) {
     a.out = r.ptr[so];
     void* scratch[8];
     for (int i = 0; i < 8; ++i) scratch[i] = scratch_slot[i] >= 0 ? r.ptr[scratch_slot[i]] : nullptr;
-    cudaError_t e = launch_attention_tc(a, scratch, r.ctx->d_status, r.ctx->stream);
+    // a multiplier bound by handle is examined once; its "one repeated value" flag is kept with the handle
+    bool check_uniform = a.scale_buf != nullptr;
+    if (a.scale_buf && scale_slot >= 0 && r.from_handle[scale_slot]) {
+      bool fresh = false;
+      int* flag = uniform_flag_for(r.ctx, a.scale_buf, &fresh);
+      if (flag) { scratch[7] = flag; check_uniform = fresh; }
+    }
+    cudaError_t e = launch_attention_tc(a, scratch, check_uniform, r.ctx->d_status, r.ctx->stream);
     return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "attention launch");
   };
   add_unit(std::move(pu));
@@ -2384,6 +2392,7 @@ int run_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs, 
   Run run;
   run.ctx = ctx;
   run.ptr.assign(cp->slots.size(), nullptr);
+  run.from_handle.assign(cp->slots.size(), 0);
   std::vector<std::pair<void*, int64_t>> temp_uploads;
   std::vector<int> allocated;  // slots allocated by this run
   auto cleanup = [&](bool keep_root) {
@@ -2409,6 +2418,7 @@ int run_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs, 
       if (hit == ctx->handles.end()) { cleanup(false); return fail(ctx, BG_ERR_UNKNOWN_HANDLE, "run_tensor_plan: unknown handle " + std::to_string(found->handle)); }
       if (hit->second.bytes != want) { cleanup(false); return fail(ctx, BG_ERR_INVALID, "run_tensor_plan: handle for value_id " + std::to_string(vid) + " holds " + std::to_string(hit->second.bytes) + " bytes, the plan declares " + std::to_string(want)); }
       run.ptr[slot] = hit->second.ptr;
+      run.from_handle[slot] = 1;
     } else {
       if ((int64_t)found->nbytes != want || (want > 0 && !found->data)) { cleanup(false); return fail(ctx, BG_ERR_INVALID, "run_tensor_plan: data for value_id " + std::to_string(vid) + " has " + std::to_string(found->nbytes) + " bytes, the plan declares " + std::to_string(want)); }
       void* p = nullptr;

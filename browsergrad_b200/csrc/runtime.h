@@ -48,6 +48,11 @@ struct bg_context {
   std::map<std::string, bg::ProfileAcc> profile;
   std::vector<std::pair<std::string, std::pair<cudaEvent_t, cudaEvent_t>>> pending_events;
   std::string last_trace;
+  // "this fp32 buffer holds one repeated value" flags for buffers bound by handle, keyed by device
+  // pointer; a flag is 1 when uniform, 0 when not; entries die with their handle
+  std::unordered_map<const void*, int*> uniform_flags;
+  int* uniform_pool = nullptr;      // 1024 device ints
+  std::vector<int> uniform_free;
 };
 
 namespace bg {
@@ -64,6 +69,11 @@ int d2h(bg_context* ctx, void* dst, const void* src, size_t n);
 
 // Compile (or fetch from the cache) and run a plan.  When `out_host` is non-null the root is
 // copied to the host and the stream synchronised; otherwise a handle to the root is minted.
+// Device flag telling whether the handle-backed buffer at `ptr` is uniform; *fresh is set when the flag
+// was just created and still has to be computed.  Returns nullptr when the pool is exhausted.
+int* uniform_flag_for(bg_context* ctx, const void* ptr, bool* fresh);
+void uniform_flag_drop(bg_context* ctx, const void* ptr);
+
 int run_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs, int n_inputs, void* out_host,
              size_t out_nbytes, bg_handle* out_handle);
 
