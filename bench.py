@@ -165,12 +165,20 @@ def time_plan(bridge, torch, stream, graph_root, store, front, steps: int, warmu
     return ms, prof, trace
 
 
-def extra_measurements(bridge, torch, stream, peaks, steps: int) -> dict:
-    """Configs 3 and 4 of the baseline: Linear+bias+GELU GEMM TFLOP/s and causal attention tokens/s."""
+EXTRA_NAMES = ("gemm_bf16_4096", "gemm_fp32_4096", "gemm_bf16_8192", "gemm_fp32_8192", "attn_fp32", "attn_bf16", "gpt")
+
+
+def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn_batch: int = 16) -> dict:
+    """Configs 3, 4 and 5 of the baseline: Linear+bias+GELU GEMM TFLOP/s, causal attention tokens/s and
+    the GPT decoder forward (one GPU's shard: batch 8) tokens/s.  ``only`` restricts the set (used
+    when a single kernel is captured under a profiler)."""
     from browsergrad_b200 import configs, front, graph
-    out = {"gemm": [], "attention": []}
+    want = set(only) if only else set(EXTRA_NAMES)
+    out = {"gemm": [], "attention": [], "gpt": []}
     for n in (4096, 8192):
         for amp in ("bfloat16", ""):
+            if f"gemm_{'bf16' if amp else 'fp32'}_{n}" not in want:
+                continue
             arrays = configs.linear_inputs(n, n, n)
             store = graph.BufferStore()
             t = {k: graph.from_numpy(v, store) for k, v in arrays.items()}
@@ -186,8 +194,10 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int) -> dict:
                                              "peak_note": "measured cuBLAS bf16 burst" if amp else
                                              "measured bf16 burst / 2 (tf32) / 3 (three products per result)"}})
             del arrays, store, t
-    b, h, s, d = 16, 12, 2048, 64
+    b, h, s, d = attn_batch, 12, 2048, 64
     for amp in ("", "bfloat16"):
+        if f"attn_{'bf16' if amp else 'fp32'}" not in want:
+            continue
         arrays = configs.attention_inputs(b, h, s, d)
         arrays["mask"] = configs.causal_mask(s)
         store = graph.BufferStore()
@@ -200,6 +210,18 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int) -> dict:
         out["attention"].append({"workload": f"causal SDPA B={b} H={h} S={s} D={d} {'bf16 autocast' if amp else 'fp32 (3xTF32)'}, additive mask",
                                  "tokens_per_s": b * s / (ms * 1e-3), "plan_ms": ms, "kernel_ms": k_ms, "kernels": trace,
                                  "dense_equivalent_tflops": flops / (ms * 1e-3) / 1e12})
+        del arrays, store, t
+    if "gpt" in want:
+        arrays = configs.gpt_inputs(batch=8)
+        meta = arrays.pop("_meta")
+        store = graph.BufferStore()
+        t = {k: graph.from_numpy(v, store) for k, v in arrays.items()}
+        root = configs.gpt_forward(graph, t, meta)
+        ms, prof, trace = time_plan(bridge, torch, stream, root, store, front, max(2, steps // 2), warmup=2)
+        top = sorted(prof, key=lambda p: -p["ms"])[:6]
+        out["gpt"].append({"workload": "GPT decoder forward 12L d768 h12 mlp3072 V32000 seq1024, batch 8 (one GPU's shard of 64), fp32 graph (3xTF32)",
+                           "tokens_per_s": 8 * 1024 / (ms * 1e-3), "plan_ms": ms, "units": len(trace),
+                           "top_kernels": [{"name": p["name"], "ms_per_forward": p["ms"] / max(2, steps // 2)} for p in top]})
         del arrays, store, t
     return out
 
@@ -243,6 +265,9 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
+    ap.add_argument("--only", default="", help="comma-separated extra workloads to run instead of the main benchmark: "
+                    + ", ".join(EXTRA_NAMES))
+    ap.add_argument("--attn-batch", type=int, default=16)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -265,6 +290,16 @@ def main() -> None:
 
     bridge = CudaBridge(local)
     stream = torch.cuda.ExternalStream(bridge.stream(), device=local)
+    if args.only:
+        names = [n for n in args.only.split(",") if n]
+        bad = [n for n in names if n not in EXTRA_NAMES]
+        if bad:
+            raise SystemExit(f"unknown workload(s) {bad}; choose from {EXTRA_NAMES}")
+        res = extra_measurements(bridge, torch, stream, measured_peaks(), max(1, args.steps), names, args.attn_batch)
+        if rank == 0:
+            print(json.dumps({"only": names, "extra": res}))
+        bridge.close()
+        return
     arrays = configs.chain_inputs(rows, COLS)   # every rank: its own shard of the same size (weak scaling)
     if world > 1:
         for k in arrays:  # distinct data per rank
