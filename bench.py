@@ -361,8 +361,12 @@ def main() -> None:
     if per_kernel:
         top = max(per_kernel, key=lambda k: per_kernel[k]["ms"])
         achieved = bytes_step[top] / (per_kernel[top]["ms"] * 1e-3) / 1e9
+        # DRAM read+write per launch from the ncu capture summarised in profiles/config2_pattern_kernels_rows4096.md
+        # (fp32 [4096, 4096]), scaled by the row count: traffic grows in proportion to the rows processed
+        ncu_traffic_4096_rows = {"y": 307.4e6, "rowsum": 272.7e6, "rowsoftmax": 306.6e6}
         roofline = {"bound": "hbm", "kernel": per_kernel[top]["name"], "achieved": achieved, "peak": peaks["hbm_gbs"],
-                    "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "traffic": None,
+                    "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                    "traffic": ncu_traffic_4096_rows[top] * rows / 4096.0, "algorithmic_bytes": bytes_step[top],
                     "per_kernel": {k: {"name": v["name"], "ms_per_launch": v["ms"],
                                        "achieved_gbs": bytes_step[k] / (v["ms"] * 1e-3) / 1e9,
                                        "frac": bytes_step[k] / (v["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"]}
