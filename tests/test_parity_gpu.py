@@ -56,8 +56,8 @@ def test_pattern_kernels_and_interpreter_agree(bridge, name):
     assert not any(ln.startswith("static_") for ln in generic_trace)
     if name.endswith("_static"):
         assert any(ln.startswith("static_") for ln in static_trace), static_trace
-    if "rowsum" in name:
-        check(case, got_static, got_generic, name)      # summation order differs
+    if "rowsum" in name or "softmax" in name:
+        check(case, got_static, got_generic, name)      # summation order / exp2-based tail differ within tolerance
     else:
         assert got_static.tobytes() == got_generic.tobytes()
 
