@@ -7,10 +7,10 @@ same lazy UOp graphs where browsergrad-jit is not installed.
 from .bridge import CudaBridge, create_cuda_realizer_bridge
 from .errors import JitNotImplementedError, KernelError, RealizationError
 from .front import (DeviceBufferTable, build_plan, materialize_resident, realize_cuda, realize_cuda_resident,
-                    register_cuda_bridge, unregister_cuda_bridge)
+                    register_cuda_bridge, release_resident_leaves, unregister_cuda_bridge)
 
 __all__ = [
     "CudaBridge", "create_cuda_realizer_bridge", "KernelError", "RealizationError", "JitNotImplementedError",
     "DeviceBufferTable", "build_plan", "realize_cuda", "realize_cuda_resident", "materialize_resident",
-    "register_cuda_bridge", "unregister_cuda_bridge",
+    "register_cuda_bridge", "unregister_cuda_bridge", "release_resident_leaves",
 ]

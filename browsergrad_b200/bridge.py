@@ -223,13 +223,18 @@ class CudaBridge:
         return self.run_tensor_plan_array(plan, inputs, dtype).tobytes()
 
     def run_tensor_plan_array(self, plan: Dict[str, Any], inputs: Sequence[Dict[str, Any]], dtype: str,
-                              requests_json: Optional[str] = None) -> np.ndarray:
-        """``run_tensor_plan`` returning an ndarray (no ``bytes`` round trip)."""
+                              requests_json: Optional[str] = None, out: Optional[np.ndarray] = None) -> np.ndarray:
+        """``run_tensor_plan`` returning an ndarray (no ``bytes`` round trip).  ``out`` may name a
+        caller-owned destination of the root's shape and dtype (page-locked memory is filled by one DMA)."""
         ep = self._encode(plan, requests_json)
         if dtype != ep.root_dtype:
             raise KernelError(f"CUDA bridge: run_tensor_plan: dtype {dtype!r} does not match the root's {ep.root_dtype!r}", 1)
         arr, n, keep = self._bind(ep, inputs)
-        if ep.root_dtype == "bfloat16":
+        if out is not None:
+            want_dtype = np.uint16 if ep.root_dtype == "bfloat16" else np.dtype(ep.root_dtype)
+            if tuple(out.shape) != tuple(ep.root_shape) or out.dtype != want_dtype or not out.flags["C_CONTIGUOUS"]:
+                raise KernelError(f"CUDA bridge: run_tensor_plan: `out` must be a C-contiguous {want_dtype} array of shape {ep.root_shape}", 1)
+        elif ep.root_dtype == "bfloat16":
             out = np.empty(ep.root_shape, dtype=np.uint16)
         else:
             out = np.empty(ep.root_shape, dtype=np.dtype(ep.root_dtype))

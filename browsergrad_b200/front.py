@@ -177,12 +177,13 @@ def _bind_inputs(plan: Dict[str, Any], store: Any, table: Optional[DeviceBufferT
 
 
 def realize_cuda(tensor: Any, bridge: Optional[CudaBridge] = None, *, resident_leaves: bool = False,
-                 fusion: bool = True) -> np.ndarray:
+                 fusion: bool = True, out: Optional[np.ndarray] = None) -> np.ndarray:
     """Realize ``tensor`` on the GPU and return the ndarray ``tensor.numpy()`` would return.
 
     With ``resident_leaves`` leaf buffers are uploaded once and kept on the device across calls
     (what ``GpuBufferTable.upload`` does for ``bg.realize_webgpu``); otherwise each call uploads
     its leaves and frees them, as ``realize_tensor_plan_webgpu`` does for unregistered buffers.
+    ``out`` optionally names the destination array (e.g. page-locked memory).
     """
     table = None
     if bridge is None:
@@ -199,8 +200,14 @@ def realize_cuda(tensor: Any, bridge: Optional[CudaBridge] = None, *, resident_l
     node, store = _unwrap(tensor)
     prepared, plan = plan_for(node, fusion)
     inputs = _bind_inputs(plan, store, table, resident_leaves)
-    out = bridge.run_tensor_plan_array(plan, inputs, prepared.dtype)
-    return out
+    return bridge.run_tensor_plan_array(plan, inputs, prepared.dtype, out=out)
+
+
+def release_resident_leaves(bridge: CudaBridge) -> None:
+    """Drop the leaves ``realize_cuda(..., resident_leaves=True)`` kept on the device for ``bridge``."""
+    table = _REGISTERED_TABLE if _REGISTERED is bridge else getattr(bridge, "_front_table", None)
+    if table is not None:
+        table.release_all()
 
 
 def realize_cuda_resident(tensor: Any, bridge: Optional[CudaBridge] = None) -> "graph.Tensor":
