@@ -73,6 +73,19 @@ __device__ __forceinline__ T gelu_graph(T x) {
   return ((T)0.5 * x) * ((T)1.0 + th);
 }
 
+// gelu for results that are stored as fp64: the product is fp32-accurate (3xTF32), so the activation
+// is evaluated in fp32 with the accurate expf and an IEEE divide (~1e-7 relative) and widened.
+__device__ __forceinline__ float gelu_accurate(float x) {
+  const float c = 0.7978845608028654f;
+  float t = 0.044715f * x;
+  t = t * x;
+  t = t * x;
+  const float u = c * (x + t);
+  const float ep = expf(u), en = expf(-u);
+  const float th = __fdiv_rn(ep - en, ep + en);
+  return (0.5f * x) * (1.0f + th);
+}
+
 __device__ __forceinline__ float load_bias(const void* b, int dt, int col) {
   switch (dt) {
     case BG_F32: return reinterpret_cast<const float*>(b)[col];
@@ -93,9 +106,21 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
     v[j] = x;
   }
   if (p.bias) {
+    if (p.bias_dtype == BG_F32 && col0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0 && (col0 & 3) == 0) {
+      const float4* b4 = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + col0);
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (col0 + j < p.N) v[j] = __fadd_rn(v[j], load_bias(p.bias, p.bias_dtype, col0 + j));
+      for (int j = 0; j < 8; ++j) {
+        const float4 bb = __ldg(b4 + j);
+        v[4 * j] = __fadd_rn(v[4 * j], bb.x);
+        v[4 * j + 1] = __fadd_rn(v[4 * j + 1], bb.y);
+        v[4 * j + 2] = __fadd_rn(v[4 * j + 2], bb.z);
+        v[4 * j + 3] = __fadd_rn(v[4 * j + 3], bb.w);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) v[j] = __fadd_rn(v[j], load_bias(p.bias, p.bias_dtype, col0 + j));
+    }
   }
   const bool full = col0 + 32 <= p.N;
   const size_t base = (size_t)row * p.N + col0;
@@ -108,7 +133,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
       for (int t = 0; t < 2; ++t) {
         double x = (double)v[j + t];
         if (p.act == TC_ACT_RELU) x = x > 0.0 ? x : 0.0;
-        else if (p.act == TC_ACT_GELU) x = p.wide ? gelu_graph<double>(x) : (double)gelu_graph<float>(v[j + t]);
+        else if (p.act == TC_ACT_GELU) x = (double)gelu_accurate(v[j + t]);
         w[t] = x;
       }
       if (full && (p.N & 1) == 0) *reinterpret_cast<double2*>(out + j) = make_double2(w[0], w[1]);
@@ -132,7 +157,9 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
 #pragma unroll
       for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
     } else {
-      for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = v[j];
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) out[j] = v[j];
     }
   } else if (p.c_dtype == BG_F16) {
     __half* out = reinterpret_cast<__half*>(p.C) + base;
@@ -145,7 +172,9 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
         *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<uint4*>(h);
       }
     } else {
-      for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = __float2half_rn(v[j]);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) out[j] = __float2half_rn(v[j]);
     }
   } else {
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + base;
@@ -158,7 +187,9 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
         *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<uint4*>(h);
       }
     } else {
-      for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = __float2bfloat16_rn(v[j]);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) out[j] = __float2bfloat16_rn(v[j]);
     }
   }
 }
