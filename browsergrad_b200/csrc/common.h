@@ -140,6 +140,25 @@ int static_pattern_id(const std::string& signature, int* n_inputs);
 bool static_shape_ok(int kind, int64_t rows, int64_t cols, int64_t numel, int sm_count);
 cudaError_t launch_static(int pattern, int kind, const StaticArgs& a, int arg, cudaStream_t s, int sm_count);
 
+// Layer-norm rows over a sum of terms (ln_static.cu): h = term0 + term1 + ..; out = LN(f32(h)) * w + b.
+struct LnArgs {
+  const void* term[4];
+  int32_t term_dtype[4];     // BG_F32 or BG_F64
+  int32_t term_rowvec[4];    // 1: a [cols] vector repeated on every row
+  int32_t n_terms;
+  int32_t wide;              // the sum is fp64 (else fp32; then every term is fp32)
+  void* sum_out;             // optional h, stored in the sum type
+  void* out;
+  int32_t out_dtype;         // BG_F32 or BG_F64
+  int32_t w_dtype, b_dtype;
+  float eps;
+  const void* w;
+  const void* b;
+  int64_t rows, cols;
+};
+bool static_ln_shape_ok(int64_t rows, int64_t cols);
+cudaError_t launch_static_ln(const LnArgs& a, cudaStream_t s, int sm_count);
+
 struct StridedView {
   const void* ptr;
   int32_t dtype;

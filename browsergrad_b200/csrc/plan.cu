@@ -193,6 +193,11 @@ struct ProgramSpec {
   int static_kind = 0;
   int static_arg = 0;
   std::string signature;
+  // layer norm over a sum of terms (ln_static.cu): operand index per term, output index of the stored sum
+  int ln_terms = 0;
+  int ln_term[4] = {0, 0, 0, 0};
+  int ln_rowvec[4] = {0, 0, 0, 0};
+  int ln_sum_out = -1;
 };
 
 class Compiler {
@@ -1329,7 +1334,108 @@ static std::string program_signature(const EwProgram& P, int* kind, int* arg) {
   return "";
 }
 
+// A layer-norm row program whose row value is a plain sum of loaded operands (residual adds and a
+// bias vector) runs in the specialised kernel.  Fills ps.ln_* and returns true when it matches.
+static bool match_static_ln(ProgramSpec& ps) {
+  const EwProgram& P = ps.prog;
+  if (P.tail != TAIL_LAYERNORM || !static_ln_shape_ok(P.rows, P.cols)) return false;
+  if (P.tail_type != T_F32 && P.tail_type != T_F64) return false;
+  if (P.n_outputs < 1 || P.n_outputs > 2) return false;
+  const bool wide = P.tail_type == T_F64;
+  const int sum_dtype = wide ? BG_F64 : BG_F32;
+  if (P.tail_out_dtype != BG_F32 && P.tail_out_dtype != BG_F64) return false;
+  auto float_vec = [&](int k) {
+    const EwOperand& o = P.inputs[k];
+    return (o.dtype == BG_F32 || o.dtype == BG_F64) && ps.in_off_bytes[k] % 32 == 0;
+  };
+  if (!float_vec(P.tail_w) || !float_vec(P.tail_b)) return false;
+  // 1 = dense rows, 2 = one vector for every row, 0 = neither
+  auto term_kind = [&](int k) -> int {
+    const EwOperand& o = P.inputs[k];
+    if (!float_vec(k) || (!wide && o.dtype != BG_F32)) return 0;
+    if (o.mode == A_CONTIG) return 1;
+    if (o.mode == A_STRIDED && P.ndim == 2 && P.shape[1] == P.cols && o.stride[0] == 0 && o.stride[1] == 1) return 2;
+    return 0;
+  };
+  std::map<int, std::vector<int>> reg;   // register -> operands whose left-to-right sum it holds
+  int sum_out = -1;
+  auto source = [&](uint8_t r, std::vector<int>& out) -> bool {
+    if (r & kEwDirect) { out.assign(1, r & 0x7f); return true; }
+    auto it = reg.find(r);
+    if (it == reg.end()) return false;
+    out = it->second;
+    return true;
+  };
+  for (int i = 0; i < P.n_instr; ++i) {
+    const EwInstr& I = P.instr[i];
+    std::vector<int> a, b;
+    if (I.op == E_LOAD) {
+      reg[I.dst] = {(int)I.aux};
+    } else if (I.op == E_CVT) {
+      // widening a loaded fp32 operand before it joins an fp64 sum
+      if (I.type != T_F64 || !source(I.a, a) || a.size() != 1 || P.inputs[a[0]].dtype != BG_F32) return false;
+      reg[I.dst] = a;
+    } else if (I.op == E_ADD) {
+      if (I.type != P.tail_type || !source(I.a, a) || !source(I.b, b)) return false;
+      // (sum) + x and x + (sum) give the same bits; (sum) + (sum) would re-associate
+      if (b.size() != 1 && a.size() != 1) return false;
+      std::vector<int> v = b.size() == 1 ? a : b;
+      v.push_back(b.size() == 1 ? b[0] : a[0]);
+      if (v.size() > 4) return false;
+      if (I.dst & kEwDirect) return false;
+      reg[I.dst] = v;
+    } else if (I.op == E_STORE) {
+      if (I.a != (uint8_t)P.tail_reg || sum_out >= 0 || P.outputs[I.aux].dtype != sum_dtype) return false;
+      sum_out = I.aux;
+    } else {
+      return false;
+    }
+  }
+  auto it = reg.find(P.tail_reg);
+  if (it == reg.end()) return false;
+  if ((sum_out >= 0) != (P.n_outputs == 2) || sum_out == P.tail_out) return false;
+  const std::vector<int>& terms = it->second;
+  // a lone fp32 operand feeding an fp64 row, or mixed widths in an fp32 sum, stay on the interpreter
+  if (terms.size() == 1 && P.inputs[terms[0]].dtype != sum_dtype) return false;
+  for (size_t k = 0; k < terms.size(); ++k) {
+    const int kind = term_kind(terms[k]);
+    if (kind == 0 || terms[k] == P.tail_w || terms[k] == P.tail_b) return false;
+    ps.ln_term[k] = terms[k];
+    ps.ln_rowvec[k] = kind == 2;
+  }
+  ps.ln_terms = (int)terms.size();
+  ps.ln_sum_out = sum_out;
+  return true;
+}
+
+static int run_static_ln(Run& r, const ProgramSpec& ps) {
+  const EwProgram& P = ps.prog;
+  auto in_ptr = [&](int k) { return reinterpret_cast<const char*>(r.ptr[ps.in_slot[k]]) + ps.in_off_bytes[k]; };
+  LnArgs a{};
+  a.n_terms = ps.ln_terms;
+  for (int k = 0; k < ps.ln_terms; ++k) {
+    a.term[k] = in_ptr(ps.ln_term[k]);
+    a.term_dtype[k] = P.inputs[ps.ln_term[k]].dtype;
+    a.term_rowvec[k] = ps.ln_rowvec[k];
+  }
+  a.wide = P.tail_type == T_F64;
+  a.sum_out = ps.ln_sum_out >= 0 ? r.ptr[ps.out_slot[ps.ln_sum_out]] : nullptr;
+  a.out = r.ptr[ps.out_slot[P.tail_out]];
+  a.out_dtype = P.tail_out_dtype;
+  a.w = in_ptr(P.tail_w);
+  a.b = in_ptr(P.tail_b);
+  a.w_dtype = P.inputs[P.tail_w].dtype;
+  a.b_dtype = P.inputs[P.tail_b].dtype;
+  a.eps = P.tail_eps;
+  a.rows = P.rows;
+  a.cols = P.cols;
+  cudaError_t e = launch_static_ln(a, r.ctx->stream, r.ctx->sm_count);
+  if (e != cudaSuccess) return cuda_fail(r.ctx, e, "layer norm kernel launch");
+  return BG_OK;
+}
+
 static int run_program(Run& r, const ProgramSpec& ps) {
+  if (ps.ln_terms > 0) return run_static_ln(r, ps);
   if (ps.static_pattern >= 0) {
     const EwProgram& P = ps.prog;
     StaticArgs a{};
@@ -1369,9 +1475,10 @@ void Compiler::emit_group(const std::vector<int>& members, int tail_node, int ke
       ps->static_kind = kind;
       ps->static_arg = arg;
     }
+    if (ps->static_pattern < 0) match_static_ln(*ps);
   }
   std::ostringstream nm;
-  if (ps->static_pattern >= 0) nm << "static_";
+  if (ps->static_pattern >= 0 || ps->ln_terms > 0) nm << "static_";
   nm << (tail_node >= 0 ? "row" : "ew") << "[";
   for (size_t i = 0; i < members.size() && i < 6; ++i) nm << (i ? "," : "") << op_name(nodes_[members[i]].op);
   if (members.size() > 6) nm << ",+" << members.size() - 6;

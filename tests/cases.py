@@ -101,8 +101,28 @@ def _attn_small(b: int, h: int, s: int, d: int) -> Callable[[], Dict[str, np.nda
     return make
 
 
+def _ln_inputs(rows: int, cols: int) -> Callable[[], Dict[str, np.ndarray]]:
+    def make() -> Dict[str, np.ndarray]:
+        r = _rng(300 + cols)
+        return {
+            "x": r.standard_normal((rows, cols), dtype=np.float32),
+            "y": r.standard_normal((rows, cols), dtype=np.float32),
+            "yd": r.standard_normal((rows, cols)),
+            "bias": r.standard_normal((cols,), dtype=np.float32),
+            "g": np.linspace(0.5, 1.5, cols, dtype=np.float32),
+            "be": np.linspace(-0.2, 0.2, cols, dtype=np.float32),
+        }
+    return make
+
+
 def _gpt_tiny() -> Dict[str, np.ndarray]:
     return configs.gpt_inputs(layers=2, d_model=64, heads=4, d_mlp=128, vocab=211, seq=32, batch=2)
+
+
+def _ln_stream(api: Any, t: Dict[str, Any], other: str, cols: int) -> Any:
+    """Pre-LayerNorm block step: the residual stream h is both normalised and carried on."""
+    h = t["x"] + (t[other] + t["bias"])
+    return api.layer_norm(h, (cols,), t["g"], t["be"]) * t["g"] + h
 
 
 CASES: Dict[str, Case] = {
@@ -185,6 +205,12 @@ CASES: Dict[str, Case] = {
     "typed_attention": Case(_attn_small(2, 2, 40, 24),
                             lambda api, t, raw: api.attention_forward(t["q"], t["k"], t["v"])),
     "layer_norm": Case(_misc_inputs, lambda api, t, raw: api.layer_norm(t["x"], (33,), t["g"], t["be"])),
+    # residual adds + bias feeding a layer norm: the warp-per-row kernel (cols % 4 == 0, <= 1024)
+    "ln_residual_static": Case(_ln_inputs(75, 768), lambda api, t, raw: api.layer_norm(
+        t["x"] + (t["y"] + t["bias"]), (768,), t["g"], t["be"])),
+    "ln_plain_static": Case(_ln_inputs(9, 1024), lambda api, t, raw: api.layer_norm(t["x"], (1024,), t["g"], t["be"])),
+    "ln_stream_static": Case(_ln_inputs(33, 200), lambda api, t, raw: _ln_stream(api, t, "y", 200)),
+    "ln_stream_f64_static": Case(_ln_inputs(41, 520), lambda api, t, raw: _ln_stream(api, t, "yd", 520)),
     "layer_norm_2axes": Case(_misc_inputs, lambda api, t, raw: api.layer_norm(t["x"], (5, 33))),
     "gather_rows": Case(_misc_inputs, lambda api, t, raw: t["table"].gather(0, t["tidx"]), kind="exact"),
     "gather_cols": Case(_misc_inputs, lambda api, t, raw: t["table"].gather(1, t["cidx"]), kind="exact"),

@@ -40,7 +40,8 @@ def test_unfused_execution_matches_too(bridge, name):
     check(case, got, want, name + " (fusion off)")
 
 
-@pytest.mark.parametrize("name", ["c2_y", "c2_y_static", "c2_rowsum_static", "c2_rowsoftmax_static", "c2_rowsoftmax_long"])
+@pytest.mark.parametrize("name", ["c2_y", "c2_y_static", "c2_rowsum_static", "c2_rowsoftmax_static", "c2_rowsoftmax_long",
+                                  "ln_residual_static", "ln_plain_static", "ln_stream_static", "ln_stream_f64_static"])
 def test_pattern_kernels_and_interpreter_agree(bridge, name):
     """The specialised pattern kernels and the generic interpreter compute the same bits."""
     case = CASES[name]
@@ -56,7 +57,7 @@ def test_pattern_kernels_and_interpreter_agree(bridge, name):
     assert not any(ln.startswith("static_") for ln in generic_trace)
     if name.endswith("_static"):
         assert any(ln.startswith("static_") for ln in static_trace), static_trace
-    if "rowsum" in name or "softmax" in name:
+    if "rowsum" in name or "softmax" in name or name.startswith("ln_"):
         check(case, got_static, got_generic, name)      # summation order / exp2-based tail differ within tolerance
     else:
         assert got_static.tobytes() == got_generic.tobytes()
