@@ -60,29 +60,58 @@ class ClockSampler(threading.Thread):
         self.samples = []
         self.reasons = set()
         self.max_mhz = None
+        self.source = "nvidia-smi"
         self._stop_evt = threading.Event()
 
+    def _sample_nvml(self, nv, handle) -> None:
+        self.samples.append(float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)))
+        self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+        bits = nv.nvmlDeviceGetCurrentClocksEventReasons(handle) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+            else nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+        for name, mask in (("hw_slowdown", 0x8), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40),
+                           ("sw_power_cap", 0x4)):
+            if bits & mask:
+                self.reasons.add(name)
+
+    def _sample_smi(self) -> None:
+        out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                              "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
+        parts = [p.strip() for p in out.split(",")]
+        if len(parts) >= 6:
+            self.samples.append(float(parts[0]))
+            self.max_mhz = float(parts[1])
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:6]):
+                if val.lower().startswith("active"):
+                    self.reasons.add(name)
+
     def run(self) -> None:
+        # read-only queries: NVML in-process (about a millisecond each) when the module is there,
+        # else one nvidia-smi process per sample
+        nv = handle = None
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            handle = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.source = "nvml"
+        except Exception:
+            nv = None
+            self.source = "nvidia-smi"
         while not self._stop_evt.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
-                parts = [p.strip() for p in out.split(",")]
-                if len(parts) >= 6:
-                    self.samples.append(float(parts[0]))
-                    self.max_mhz = float(parts[1])
-                    for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:6]):
-                        if val.lower().startswith("active"):
-                            self.reasons.add(name)
+                if nv is not None:
+                    self._sample_nvml(nv, handle)
+                else:
+                    self._sample_smi()
             except Exception:
                 pass
-            self._stop_evt.wait(0.1)
+            self._stop_evt.wait(0.01 if nv is not None else 0.1)
 
     def stop(self) -> dict:
         self._stop_evt.set()
         self.join(timeout=6)
         med = float(np.median(self.samples)) if self.samples else None
-        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples),
+                "source": self.source}
 
 
 def build_graphs(graph, configs, arrays):
@@ -127,17 +156,60 @@ def cpu_reference_realize():
     return "port", run
 
 
+def _cpu_worker(index: int, sample_rows: int, warmup: int, steps: int, gate) -> None:
+    """One host process of the CPU arm: realizes its own row block of the workload once per step.
+    NumPy's ufuncs and reductions run on one thread, so the reference's path uses all host cores
+    only when its rows are split over processes -- the same split the GPUs get."""
+    from browsergrad_b200 import configs
+    _, run = cpu_reference_realize()
+    arrays = configs.chain_inputs(sample_rows, COLS)
+    if index:
+        arrays = {k: np.roll(v, index, axis=0) for k, v in arrays.items()}
+    for _ in range(warmup):
+        run(arrays)
+    for _ in range(steps):
+        gate.wait()
+        run(arrays)
+        gate.wait()
+
+
+def cpu_reference_steps(sample_rows: int, workers: int, warmup: int, steps: int) -> list:
+    """Wall-clock seconds of each of ``steps`` concurrent passes of ``workers`` processes."""
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")      # never fork a process that may hold a CUDA context
+    gate = ctx.Barrier(workers + 1)
+    procs = [ctx.Process(target=_cpu_worker, args=(i, sample_rows, warmup, steps, gate), daemon=True) for i in range(workers)]
+    for pr in procs:
+        pr.start()
+    times = []
+    try:
+        for _ in range(steps):
+            gate.wait(timeout=600)
+            t0 = time.perf_counter()
+            gate.wait(timeout=600)
+            times.append(time.perf_counter() - t0)
+    finally:
+        for pr in procs:
+            pr.join(timeout=30)
+            if pr.is_alive():
+                pr.terminate()
+    return times
+
+
 def cpu_baseline(sample_rows: int, repeats: int = 1) -> dict:
     from browsergrad_b200 import configs
     kind, run = cpu_reference_realize()
     arrays = configs.chain_inputs(sample_rows, COLS)
     run(arrays)  # warm-up
-    best = min(run(arrays) for _ in range(max(1, repeats)))
+    single = min(run(arrays) for _ in range(max(1, repeats)))
     nbytes = sum(algorithmic_bytes(sample_rows, COLS).values())
-    return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": kind,
-            "sample": f"{sample_rows} of {ROWS} rows x {COLS} cols, all three realizations, NumPy {np.__version__}, "
-                      f"best of {max(1, repeats)} after 1 warm-up",
-            "seconds": best}
+    workers = os.cpu_count() or 1
+    times = cpu_reference_steps(sample_rows, workers, 1, max(2, repeats))
+    best = min(times)
+    return {"value": workers * nbytes / best / 1e9, "unit": "GB/s", "cores": workers, "kind": kind,
+            "sample": f"{workers} processes x {sample_rows} of {ROWS} rows x {COLS} cols each, all three realizations, "
+                      f"NumPy {np.__version__}, best of {max(2, repeats)} after 1 warm-up",
+            "seconds": best, "single_process_value": nbytes / single / 1e9}
 
 
 def time_plan(bridge, torch, stream, graph_root, store, front, steps: int, warmup: int = 3):
@@ -165,7 +237,9 @@ def time_plan(bridge, torch, stream, graph_root, store, front, steps: int, warmu
     return ms, prof, trace
 
 
-EXTRA_NAMES = ("gemm_bf16_4096", "gemm_fp32_4096", "gemm_bf16_8192", "gemm_fp32_8192", "attn_fp32", "attn_bf16", "gpt")
+EXTRA_NAMES = ("mlp", "gemm_bf16_1024", "gemm_fp32_1024", "gemm_bf16_4096", "gemm_fp32_4096", "gemm_bf16_8192", "gemm_fp32_8192",
+               "attn_fp32", "attn_bf16", "gpt")
+NOMINAL = {"hbm_gbs": 7700.0, "bf16_tflops": 2250.0}   # B200 data-sheet figures, printed beside the measured peaks
 
 
 def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn_batch: int = 16) -> dict:
@@ -174,8 +248,18 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn
     when a single kernel is captured under a profiler)."""
     from browsergrad_b200 import configs, front, graph
     want = set(only) if only else set(EXTRA_NAMES)
-    out = {"gemm": [], "attention": [], "gpt": []}
-    for n in (4096, 8192):
+    out = {"mlp": [], "gemm": [], "attention": [], "gpt": []}
+    if "mlp" in want:
+        # configuration 1 is latency-bound (13 MFLOP): report microseconds per forward, no roofline fraction
+        arrays = configs.mlp_inputs()
+        store = graph.BufferStore()
+        t = {k: graph.from_numpy(v, store) for k, v in arrays.items()}
+        root = configs.mlp_loss(graph, t)
+        ms, prof, trace = time_plan(bridge, torch, stream, root, store, front, max(steps, 20))
+        out["mlp"].append({"workload": "MLP 784-128(ReLU)-10 + cross entropy, batch 64, fp32", "us_per_forward": ms * 1e3,
+                           "kernels": trace})
+        del arrays, store, t
+    for n in (1024, 4096, 8192):
         for amp in ("bfloat16", ""):
             if f"gemm_{'bf16' if amp else 'fp32'}_{n}" not in want:
                 continue
@@ -188,9 +272,11 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn
             k_ms = gemm[0]["ms"] / max(gemm[0]["launches"], 1) if gemm else ms
             tf = 2.0 * n ** 3 / (k_ms * 1e-3) / 1e12
             peak = peaks["bf16_tflops"] if amp else peaks["bf16_tflops"] / 2.0 / 3.0
+            nominal = NOMINAL["bf16_tflops"] if amp else NOMINAL["bf16_tflops"] / 2.0 / 3.0
             out["gemm"].append({"workload": f"Linear+bias+GELU M=N=K={n} {'bf16 autocast' if amp else 'fp32 (3xTF32)'}",
                                 "tflops": tf, "kernel_ms": k_ms, "plan_ms": ms, "kernels": trace,
                                 "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+                                             "frac_of_nominal": tf / nominal, "nominal_peak": nominal,
                                              "peak_note": "measured cuBLAS bf16 burst" if amp else
                                              "measured bf16 burst / 2 (tf32) / 3 (three products per result)"}})
             del arrays, store, t
@@ -231,25 +317,21 @@ def run_reference(args) -> None:
     if rank != 0:
         return
     sample_rows = 1024
-    per_step = []
-    kind, run = cpu_reference_realize()
-    from browsergrad_b200 import configs
-    arrays = configs.chain_inputs(sample_rows, COLS)
-    for _ in range(args.warmup):
-        run(arrays)
-    for _ in range(args.steps):
-        per_step.append(run(arrays))
+    kind, _ = cpu_reference_realize()
+    workers = os.cpu_count() or 1
+    per_step = cpu_reference_steps(sample_rows, workers, max(1, args.warmup), args.steps)
     total = sum(per_step)
-    nbytes = sum(algorithmic_bytes(sample_rows, COLS).values())
+    nbytes = workers * sum(algorithmic_bytes(sample_rows, COLS).values())
     value = nbytes * args.steps / total / 1e9
+    sample = (f"{workers} processes x {sample_rows} of {ROWS} rows x {COLS} cols per step (NumPy runs this path on one "
+              f"thread per process), NumPy {np.__version__}")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"config 2: fused elementwise/reduce chains y, row-sum, row-softmax over fp32 [{ROWS},{COLS}]",
-                   "sample": f"{sample_rows} rows per step on the host cores"},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": os.cpu_count(), "kind": kind,
-                         "sample": f"{sample_rows} of {ROWS} rows x {COLS} cols per step, NumPy {np.__version__}"},
+                   "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": workers, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
@@ -258,7 +340,7 @@ def run_reference(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="cuda")
     ap.add_argument("--rows", type=int, default=ROWS)
@@ -268,6 +350,7 @@ def main() -> None:
     ap.add_argument("--only", default="", help="comma-separated extra workloads to run instead of the main benchmark: "
                     + ", ".join(EXTRA_NAMES))
     ap.add_argument("--attn-batch", type=int, default=16)
+    ap.add_argument("--e2e-chunks", type=int, default=16)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -366,6 +449,7 @@ def main() -> None:
         ncu_traffic_4096_rows = {"y": 307.4e6, "rowsum": 272.7e6, "rowsoftmax": 306.6e6}
         roofline = {"bound": "hbm", "kernel": per_kernel[top]["name"], "achieved": achieved, "peak": peaks["hbm_gbs"],
                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                    "frac_of_nominal": achieved / NOMINAL["hbm_gbs"], "nominal_peak": NOMINAL["hbm_gbs"],
                     "traffic": ncu_traffic_4096_rows[top] * rows / 4096.0, "algorithmic_bytes": bytes_step[top],
                     "per_kernel": {k: {"name": v["name"], "ms_per_launch": v["ms"],
                                        "achieved_gbs": bytes_step[k] / (v["ms"] * 1e-3) / 1e9,
@@ -390,20 +474,37 @@ def main() -> None:
             for name in ("y", "rowsum", "rowsoftmax"):
                 realize_cuda(proots[name], bridge, resident_leaves=True, out=outs[name])
             release_resident_leaves(bridge)
-        e2e_step()
-        barrier()
-        t0 = time.perf_counter()
+
+        def timed(fn, n: int) -> float:
+            fn()
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(n):
+                fn()
+            barrier()
+            dt = time.perf_counter() - t0
+            if world > 1:
+                tdt = torch.tensor([dt], device=f"cuda:{local}")
+                dist.all_reduce(tdt, op=dist.ReduceOp.MAX)
+                dt = float(tdt.item())
+            return dt
         n_e2e = max(2, min(args.steps, 5))
-        for _ in range(n_e2e):
-            e2e_step()
-        barrier()
-        dt = time.perf_counter() - t0
-        if world > 1:
-            tdt = torch.tensor([dt], device=f"cuda:{local}")
-            dist.all_reduce(tdt, op=dist.ReduceOp.MAX)
-            dt = float(tdt.item())
+        dt_single = timed(e2e_step, n_e2e)
+        # the same step streamed in row chunks over three bridges (one stream each) of this device, so that
+        # uploads, kernels and read-backs of neighbouring chunks overlap on the full-duplex PCIe link
+        from browsergrad_b200.sharded import cuda_row_pipeline
+        lanes = [bridge, CudaBridge(local), CudaBridge(local)]
+        pipe = cuda_row_pipeline(lambda tt: {"y": configs.chain_y(graph, tt), "rowsum": configs.chain_rowsum(graph, tt),
+                                             "rowsoftmax": configs.chain_rowsoftmax(graph, tt)},
+                                 pinned, list(pinned), lanes, n_chunks=args.e2e_chunks)
+        dt = timed(lambda: pipe.run(outs), n_e2e)
+        for extra_bridge in lanes[1:]:
+            extra_bridge.close()
         e2e = {"value": world * total_bytes * n_e2e / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h, "steps": n_e2e, "ms_per_step": 1e3 * dt / n_e2e}
+               "d2h_bytes_per_step": d2h, "steps": n_e2e, "ms_per_step": 1e3 * dt / n_e2e,
+               "api": f"sharded.cuda_row_pipeline(...).run(outs): {args.e2e_chunks} row chunks over 3 bridges",
+               "single_call": {"value": world * total_bytes * n_e2e / dt_single / 1e9, "ms_per_step": 1e3 * dt_single / n_e2e,
+                               "api": "realize_cuda(root, out=pinned) per root, leaves uploaded once per step"}}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:

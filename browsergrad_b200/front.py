@@ -203,9 +203,14 @@ def realize_cuda(tensor: Any, bridge: Optional[CudaBridge] = None, *, resident_l
     return bridge.run_tensor_plan_array(plan, inputs, prepared.dtype, out=out)
 
 
+def resident_table(bridge: CudaBridge) -> Optional[DeviceBufferTable]:
+    """The table of leaves ``realize_cuda(..., resident_leaves=True)`` keeps on the device for ``bridge``."""
+    return _REGISTERED_TABLE if _REGISTERED is bridge else getattr(bridge, "_front_table", None)
+
+
 def release_resident_leaves(bridge: CudaBridge) -> None:
     """Drop the leaves ``realize_cuda(..., resident_leaves=True)`` kept on the device for ``bridge``."""
-    table = _REGISTERED_TABLE if _REGISTERED is bridge else getattr(bridge, "_front_table", None)
+    table = resident_table(bridge)
     if table is not None:
         table.release_all()
 

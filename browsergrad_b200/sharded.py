@@ -117,3 +117,100 @@ def realize_sharded(build: Callable[[Dict[str, Any]], Any], arrays: Dict[str, np
     if not gather:
         return out
     return gather_rows(out, total, group, device)
+
+
+class RowPipeline:
+    """Streams one row-independent realization through a single GPU in row chunks so that the
+    host->device copy of chunk i+1, the kernels of chunk i and the device->host copy of chunk i-1
+    overlap.  PCIe is full duplex, and a bridge call is synchronous, so the overlap comes from
+    running the chunks on ``lanes`` independent bridges (one CUDA stream each), one host thread per
+    lane; ctypes releases the GIL for the duration of every C call.
+
+    The premise is the one row sharding across GPUs rests on: every root is independent along the
+    leading axis of the ``sharded_keys`` inputs.  ``build(tensors)`` returns a tensor or a dict of
+    named tensors; every root's leading axis must be the row axis.  The chunk graphs are built once;
+    ``run`` may be called repeatedly (the host arrays are read again on every call).
+
+    ``realize(tensor, lane, out)`` realizes into ``out`` (a row block of the caller's array) and
+    ``release(lane, row_tensors)`` drops the chunk's row-carrying leaves from the lane's device
+    table (replicated leaves stay resident on every lane until the caller drops them); the CUDA
+    front end's ``realize_cuda(..., resident_leaves=True, out=...)`` and its device buffer table are
+    the production pair (see ``cuda_row_pipeline``).  The reference has no counterpart.
+    """
+
+    def __init__(self, build: Callable[[Dict[str, Any]], Any], arrays: Dict[str, np.ndarray], sharded_keys: Sequence[str],
+                 make_tensor: Callable[[np.ndarray], Any], realize: Callable[[Any, int, np.ndarray], Any],
+                 release: Callable[[int, Dict[str, Any]], None], *, lanes: int = 2, n_chunks: int = 8) -> None:
+        keys = list(sharded_keys)
+        if not keys:
+            raise ValueError("RowPipeline: no row-carrying inputs named")
+        self.total = int(arrays[keys[0]].shape[0])
+        for k in keys:
+            if arrays[k].shape[0] != self.total:
+                raise ValueError(f"row-carrying inputs disagree on the row count: {k}")
+        self.lanes = max(1, int(lanes))
+        self.n_chunks = max(1, min(int(n_chunks), self.total)) if self.total else 1
+        self._realize, self._release = realize, release
+        self.chunks: List[Tuple[int, int, Dict[str, Any], Dict[str, Any]]] = []
+        replicated = {k: make_tensor(v) for k, v in arrays.items() if k not in keys}
+        for j in range(self.n_chunks):
+            lo, hi = shard_bounds(self.total, self.n_chunks, j)
+            tensors = dict(replicated)
+            for k in keys:
+                tensors[k] = make_tensor(arrays[k][lo:hi])     # a view: page-locked memory stays page-locked
+            roots = build(tensors)
+            if not isinstance(roots, dict):
+                roots = {"out": roots}
+            self.chunks.append((lo, hi, roots, {k: tensors[k] for k in keys}))
+
+    def output_shapes(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        """Full-size shape and dtype of every root (rows of all chunks stacked)."""
+        roots = self.chunks[0][2]
+        return {name: ((self.total,) + tuple(t.shape[1:]), str(t.dtype)) for name, t in roots.items()}
+
+    def _lane(self, lane: int, outs: Dict[str, np.ndarray], errors: List[BaseException]) -> None:
+        try:
+            for j in range(lane, self.n_chunks, self.lanes):
+                lo, hi, roots, row_tensors = self.chunks[j]
+                try:
+                    for name, root in roots.items():
+                        self._realize(root, lane, outs[name][lo:hi])
+                finally:
+                    self._release(lane, row_tensors)
+        except BaseException as exc:   # re-raised on the caller's thread
+            errors.append(exc)
+
+    def run(self, outs: Dict[str, np.ndarray]) -> Dict[str, np.ndarray]:
+        import threading
+        for name, (shape, _) in self.output_shapes().items():
+            if name not in outs or tuple(outs[name].shape) != shape:
+                raise ValueError(f"RowPipeline: output {name!r} must have shape {shape}")
+        errors: List[BaseException] = []
+        threads = [threading.Thread(target=self._lane, args=(lane, outs, errors)) for lane in range(1, self.lanes)]
+        for th in threads:
+            th.start()
+        self._lane(0, outs, errors)
+        for th in threads:
+            th.join()
+        if errors:
+            raise errors[0]
+        return outs
+
+
+def cuda_row_pipeline(build: Callable[[Dict[str, Any]], Any], arrays: Dict[str, np.ndarray], sharded_keys: Sequence[str],
+                      bridges: Sequence[Any], *, n_chunks: int = 8, store: Any = None) -> RowPipeline:
+    """``RowPipeline`` over ``bridges`` (one lane each, all on the same device) through ``realize_cuda``."""
+    from . import front, graph
+    st = store if store is not None else graph.BufferStore()
+
+    def realize(tensor: Any, lane: int, out: np.ndarray) -> Any:
+        return front.realize_cuda(tensor, bridges[lane], resident_leaves=True, out=out)
+
+    def release(lane: int, row_tensors: Dict[str, Any]) -> None:
+        table = front.resident_table(bridges[lane])
+        if table is not None:
+            for t in row_tensors.values():
+                table.release(t._uop.inputs[0].arg)     # LOAD(BUFFER id)
+
+    return RowPipeline(build, arrays, sharded_keys, lambda a: graph.from_numpy(a, st), realize, release,
+                       lanes=len(bridges), n_chunks=n_chunks)

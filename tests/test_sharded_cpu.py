@@ -75,3 +75,57 @@ def test_two_rank_gloo_matches_single_process(tmp_path):
         assert np.load(tmp_path / f"bool_{r}.npy").tobytes() == want_b.tobytes()
         loss = np.load(tmp_path / f"loss_{r}.npy")
         assert abs(float(loss) - float(want_loss)) <= 1e-5 * abs(float(want_loss))
+
+
+def test_row_pipeline_matches_unchunked_realization():
+    """Chunked, multi-lane streaming of a row-independent realization gives the same rows as one
+    realization of the whole input (host logic only; the oracle stands in for the device)."""
+    from browsergrad_b200 import configs, graph, passes
+    from browsergrad_b200.sharded import RowPipeline
+    from oracle import port
+
+    arrays = configs.chain_inputs(37, 64)
+    store = graph.BufferStore()
+    released = []
+
+    def build(t):
+        return {"y": configs.chain_y(graph, t), "rowsum": configs.chain_rowsum(graph, t),
+                "rowsoftmax": configs.chain_rowsoftmax(graph, t)}
+
+    def realize(tensor, lane, out):
+        out[...] = port.realize(passes.prepare(tensor._uop), store)
+
+    pipe = RowPipeline(build, arrays, list(arrays), lambda a: graph.from_numpy(a, store), realize,
+                       lambda lane, row_tensors: released.append((lane, sorted(row_tensors))), lanes=3, n_chunks=5)
+    shapes = pipe.output_shapes()
+    assert shapes["y"] == ((37, 64), "float32") and shapes["rowsum"] == ((37,), "float32")
+    outs = {k: np.empty(shape, dtype) for k, (shape, dtype) in shapes.items()}
+    pipe.run(outs)
+    whole = {k: graph.from_numpy(v, store) for k, v in arrays.items()}
+    for name, root in build(whole).items():
+        want = port.realize(passes.prepare(root._uop), store)
+        if name == "rowsum":
+            np.testing.assert_allclose(outs[name], want, rtol=1e-6)
+        else:
+            assert outs[name].tobytes() == want.tobytes(), name
+    assert len(released) == 5 and {lane for lane, _ in released} == {0, 1, 2}
+    with pytest.raises(ValueError):
+        pipe.run({"y": outs["y"]})
+
+
+def test_row_pipeline_propagates_lane_errors():
+    from browsergrad_b200 import configs, graph
+    from browsergrad_b200.sharded import RowPipeline
+
+    arrays = configs.chain_inputs(8, 16)
+    store = graph.BufferStore()
+
+    def realize(tensor, lane, out):
+        if lane == 1:
+            raise RuntimeError("lane failed")
+        out[...] = 0
+
+    pipe = RowPipeline(lambda t: configs.chain_y(graph, t), arrays, list(arrays), lambda a: graph.from_numpy(a, store),
+                       realize, lambda lane, rt: None, lanes=2, n_chunks=4)
+    with pytest.raises(RuntimeError, match="lane failed"):
+        pipe.run({"out": np.empty((8, 16), np.float32)})
