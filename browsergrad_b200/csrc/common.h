@@ -222,6 +222,8 @@ struct TcGemm {
 };
 // Set by the host-only dry compile so that plans can be lowered as they would be on a B200.
 extern bool g_tc_assume_available;
+// CTA-pair (cta_group::2) GEMM tiles: 0 never, 1 for problems that fill the device (default), 2 whenever legal.
+extern int g_tc_pair_mode;
 bool tc_gemm_supported(int64_t M, int64_t N, int64_t K, int ab_dtype);
 cudaError_t launch_gemm_tc(const TcGemm& g, int* status, cudaStream_t s);
 // hi = tf32(x) (round to nearest), lo = x - hi, for fp32 or fp64 input; optional transpose is not done here.

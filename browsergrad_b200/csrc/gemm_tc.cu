@@ -339,6 +339,170 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
   }
 }
 
+// CTA-pair variant: a cluster of two CTAs computes one 256 x 256 tile with tcgen05 cta_group::2.
+// Each CTA stages its own 128 rows of A and its own 128 rows (output columns) of B, so a pair reads
+// 64 KB of operands per K block where two independent 128 x 256 CTAs read 96 KB - the single-CTA
+// kernel is limited by shared-memory fill from L2, not by the tensor pipe.  CTA 0 of the pair issues
+// every MMA; the instruction reads both CTAs' shared memory and writes rows 0..127 of the tile into
+// CTA 0's tensor memory and rows 128..255 into CTA 1's.  Barrier protocol (s = stage, b = buffer):
+//   full[s]      lives in CTA 0; both producers arrive with their byte counts, both CTAs' copies
+//                complete on it (count 2 + 64 KB);
+//   empty[s]     one per CTA; CTA 0's MMA thread commits to its own and to CTA 1's;
+//   acc_full[b]  one per CTA, committed the same way after a tile's last MMA;
+//   acc_empty[b] lives in CTA 0; the eight epilogue warps of the pair arrive on it.
+// The two CTAs meet at a cluster barrier after set-up and before tear-down, so no remote arrive or
+// MMA ever targets a CTA that has exited.
+constexpr int kPairStages = 6;
+
+template <bool TF32>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                    const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
+                    const __grid_constant__ TcParams p) {
+  constexpr int kHalf = 128;                           // rows of A and of B each CTA stages
+  constexpr int kABytes = kHalf * kStageRowBytes;
+  constexpr int kStageBytes = 2 * kABytes;
+  constexpr int kTile = 256;
+  constexpr int kTmemCols = 2 * kTile;
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kPairStages * kStageBytes);
+  uint64_t* empty_bar = full_bar + kPairStages;
+  uint64_t* acc_full = empty_bar + kPairStages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_m = (p.M + kTile - 1) / kTile, num_n = (p.N + kTile - 1) / kTile;
+  const int num_tiles = num_m * num_n;
+  const int gsz = p.group_m * num_n;
+  auto tile_origin = [&](int tile, int& m0, int& n0) {
+    const int g = tile / gsz;
+    const int first_m = g * p.group_m;
+    const int gm = min(p.group_m, num_m - first_m);
+    m0 = (first_m + (tile % gsz) % gm) * kTile;
+    n0 = ((tile % gsz) / gm) * kTile;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) { mbar_init(&full_bar[s], 2); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    // the same warp of both CTAs allocates; each CTA receives the same column range of its own tensor memory
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const int iters_per_tile = p.num_k_blocks * p.passes;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int m0, n0;
+        tile_origin(tile, m0, n0);
+        for (int k = 0; k < iters_per_tile; ++k, ++it) {
+          const int s = it % kPairStages;
+          const uint32_t ph = (uint32_t)(it / kPairStages) & 1u;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+          const int pass = k / p.num_k_blocks, kb = k - pass * p.num_k_blocks;
+          const CUtensorMap* ma = (p.passes == 3 && pass == 0) ? &tmA1 : &tmA0;
+          const CUtensorMap* mb = (p.passes == 3 && pass == 1) ? &tmB1 : &tmB0;
+          unsigned char* sa = smem + s * kStageBytes;
+          const uint32_t full0 = map_to_cta(smem_u32(&full_bar[s]), 0);
+          mbar_expect_tx_at(full0, kStageBytes);
+          tma_load_2d_pair(ma, sa, full0, kb * p.elems_per_block, m0 + (int)rank * kHalf);
+          tma_load_2d_pair(mb, sa + kABytes, full0, kb * p.elems_per_block, n0 + (int)rank * kHalf);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      int it = 0, t = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++t) {
+        const int buf = t & 1;
+        if (!mbar_wait(&acc_empty[buf], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * kTile);
+        for (int k = 0; k < iters_per_tile; ++k, ++it) {
+          const int s = it % kPairStages;
+          const uint32_t ph = (uint32_t)(it / kPairStages) & 1u;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * kStageBytes);
+          const uint64_t da = make_kmajor_sw128_desc(sa), db = make_kmajor_sw128_desc(sa + kABytes);
+#pragma unroll
+          for (int kk = 0; kk < kStageRowBytes / 32; ++kk)
+            umma_pair<TF32>(tmem_acc, da + (uint64_t)(kk * 32 >> 4), db + (uint64_t)(kk * 32 >> 4), p.idesc, (k > 0 || kk > 0) ? 1u : 0u);
+          const uint32_t e = smem_u32(&empty_bar[s]);
+          umma_commit_pair(map_to_cta(e, 0));
+          umma_commit_pair(map_to_cta(e, 1));
+        }
+        if (ok) {
+          const uint32_t f = smem_u32(&acc_full[buf]);
+          umma_commit_pair(map_to_cta(f, 0));
+          umma_commit_pair(map_to_cta(f, 1));
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int t = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++t) {
+      int m0, n0;
+      tile_origin(tile, m0, n0);
+      const int buf = t & 1;
+      const int row = m0 + (int)rank * kHalf + q * 32 + lane;
+      if (iters_per_tile > 0) ok = mbar_wait(&acc_full[buf], (uint32_t)(t >> 1) & 1u, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * kTile) + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < kTile / 32; ++c) {
+        uint32_t r[32];
+        if (iters_per_tile > 0) tmem_ld32(tmem_acc + (uint32_t)(c * 32), r);
+        else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0;
+        }
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) epilogue_chunk(p, r, row, col0);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_at(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(p.status, BG_ERR_DEVICE_TIMEOUT);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) {}
+    __syncthreads();
+  }
+  // both CTAs are past their last remote arrive / MMA before either frees tensor memory or exits
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
 __global__ void tf32_split_kernel(const void* src, int src_dtype, float* hi, float* lo, int64_t n) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     float x;
@@ -433,6 +597,66 @@ cudaError_t launch_variant(const TcGemm& g, int* status, cudaStream_t s) {
   return cudaGetLastError();
 }
 
+template <bool TF32>
+cudaError_t launch_pair(const TcGemm& g, int* status, cudaStream_t s, bool* launched) {
+  *launched = false;
+  CUtensorMap a0, a1, b0, b1;
+  if (!make_operand_map(&a0, g.A, g.ab_dtype, g.M, g.K, 128)) return cudaErrorInvalidValue;
+  if (!make_operand_map(&b0, g.B, g.ab_dtype, g.N, g.K, 128)) return cudaErrorInvalidValue;
+  a1 = a0;
+  b1 = b0;
+  if (TF32) {
+    if (!make_operand_map(&a1, g.A_lo, g.ab_dtype, g.M, g.K, 128)) return cudaErrorInvalidValue;
+    if (!make_operand_map(&b1, g.B_lo, g.ab_dtype, g.N, g.K, 128)) return cudaErrorInvalidValue;
+  }
+  TcParams p{};
+  p.M = (int)g.M;
+  p.N = (int)g.N;
+  const int es = dtype_size(g.ab_dtype);
+  p.elems_per_block = kStageRowBytes / es;
+  p.num_k_blocks = (int)((g.K + p.elems_per_block - 1) / p.elems_per_block);
+  p.passes = TF32 ? 3 : 1;
+  p.C = g.C;
+  p.c_dtype = g.c_dtype;
+  p.bias = g.bias;
+  p.bias_dtype = g.bias_dtype;
+  p.act = g.act;
+  p.round_acc = g.round_acc;
+  p.wide = g.wide;
+  p.status = status;
+  p.group_m = 4;
+  const uint32_t fmt = TF32 ? 2u : (g.ab_dtype == BG_BF16 ? 1u : 0u);
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+  const size_t smem = (size_t)kPairStages * 2 * 128 * kStageRowBytes + 256 + 1024;
+  auto kern = gemm_tc_pair_kernel<TF32>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  // how many pairs the device can hold at once (two SMs of one TPC each)
+  static int max_pairs = -1;
+  if (max_pairs < 0) {
+    cudaLaunchConfig_t qc{};
+    qc.gridDim = dim3(2, 1, 1);
+    qc.blockDim = dim3(kTcThreads, 1, 1);
+    qc.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    qc.attrs = &attr;
+    qc.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &qc) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    max_pairs = n;
+  }
+  if (max_pairs <= 0) return cudaSuccess;   // not launched: the caller falls back to single CTAs
+  const int64_t tiles = ((g.M + 255) / 256) * ((g.N + 255) / 256);
+  const int64_t pairs = tiles < max_pairs ? tiles : max_pairs;
+  kern<<<(unsigned)(2 * pairs), kTcThreads, smem, s>>>(a0, a1, b0, b1, p);
+  *launched = true;
+  return cudaGetLastError();
+}
+
 }  // namespace
 
 bool g_tc_assume_available = false;
@@ -447,9 +671,23 @@ bool tc_gemm_supported(int64_t M, int64_t N, int64_t K, int ab_dtype) {
   return true;
 }
 
+int g_tc_pair_mode = 1;   // 0: never, 1: when the problem fills the device with 256 x 256 tiles, 2: whenever legal
+
 cudaError_t launch_gemm_tc(const TcGemm& g, int* status, cudaStream_t s) {
   const bool tf32 = g.ab_dtype == BG_F32;
-  const bool wide_tile = g.N > 128;
+  const int64_t tiles256 = ((g.M + 255) / 256) * ((g.N + 255) / 256);
+  const bool pair_ok = g.M > 128 && g.N > 128;
+  if (pair_ok && (g_tc_pair_mode == 2 || (g_tc_pair_mode == 1 && tiles256 >= 64))) {
+    bool launched = false;
+    cudaError_t e = tf32 ? launch_pair<true>(g, status, s, &launched) : launch_pair<false>(g, status, s, &launched);
+    if (e != cudaSuccess || launched) return e;
+  }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // 128 x 256 tiles halve the B traffic per flop; 128 x 128 tiles when the wide ones would leave SMs idle
+  const int64_t wide_tiles = ((g.M + BM - 1) / BM) * ((g.N + 255) / 256);
+  const bool wide_tile = g.N > 128 && wide_tiles >= sms;
   if (tf32) return wide_tile ? launch_variant<256, true>(g, status, s) : launch_variant<128, true>(g, status, s);
   return wide_tile ? launch_variant<256, false>(g, status, s) : launch_variant<128, false>(g, status, s);
 }

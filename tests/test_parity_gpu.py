@@ -114,3 +114,20 @@ def test_sdpa_runs_as_one_fused_attention_kernel(bridge, name, expect):
     finally:
         bridge.set_option("tensor_cores", 1)
     check(case, composed, want, name + " (composed)")
+
+
+@pytest.mark.parametrize("name", ["c3_tc_f32", "c3_tc_f16", "c3_tc_bf16", "c3_tc_ragged", "c3_tc_relu", "c3_tc_rowmajor_b"])
+def test_cta_pair_gemm_matches_oracle(bridge, name):
+    """The two-CTA (cta_group::2) 256 x 256 tile kernel, forced on shapes with ragged edges in M, N and K."""
+    case = CASES[name]
+    t, store, _ = build_case(case)
+    want = oracle_value(t, store)
+    single = realize_cuda(t, bridge)
+    bridge.set_option("gemm_cta_pairs", 2)
+    try:
+        got = realize_cuda(t, bridge)
+    finally:
+        bridge.set_option("gemm_cta_pairs", 1)
+    check(case, got, want, name + " (CTA pairs)")
+    # same products, same accumulation order per output element: the two tilings agree to the bit
+    assert got.tobytes() == single.tobytes()
