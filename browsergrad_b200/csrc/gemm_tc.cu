@@ -8,7 +8,7 @@
 //              ring of shared-memory stages, completion counted on "full" mbarriers;
 //   warp 1     MMA issuer: one elected thread issues tcgen05.mma (128 x BN x 32 bytes of K per
 //              instruction) into the TMEM accumulator and releases stages with tcgen05.commit;
-//   warps 2-5  epilogue: tcgen05.ld of the 128 accumulator lanes, bias / activation / rounding,
+//   warps 2-9  epilogue: tcgen05.ld of the 128 accumulator lanes, bias / activation / rounding,
 //              vector stores of the result rows.
 // Loads carry no cluster multicast.  Two operand encodings share the kernel:
 //   * 16-bit (f16 / bf16) operands, fp32 accumulate;
@@ -32,7 +32,7 @@ using namespace tc;
 
 constexpr int BM = 128;
 constexpr int kStageRowBytes = 128;          // one swizzle row: 64 x 16-bit or 32 x tf32
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 320;          // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per TMEM lane quarter)
 
 struct TcParams {
   int M, N;
@@ -74,16 +74,16 @@ __device__ __forceinline__ T gelu_graph(T x) {
 }
 
 // gelu for results that are stored as fp64: the product is fp32-accurate (3xTF32), so the activation
-// is evaluated in fp32 with the accurate expf and an IEEE divide (~1e-7 relative) and widened.
+// is evaluated in fp32 and widened.  With u = c*(x + 0.044715 x^3), the graph's
+// 0.5*x*(1 + (e^u - e^-u)/(e^u + e^-u)) equals x / (1 + e^(-2u)); this form needs one exponential,
+// has no cancellation for negative x and does not overflow to inf/inf for |u| > 88 (~1e-7 relative).
 __device__ __forceinline__ float gelu_accurate(float x) {
-  const float c = 0.7978845608028654f;
+  const float c2 = 2.0f * 0.7978845608028654f;
   float t = 0.044715f * x;
   t = t * x;
   t = t * x;
-  const float u = c * (x + t);
-  const float ep = expf(u), en = expf(-u);
-  const float th = __fdiv_rn(ep - en, ep + en);
-  return (0.5f * x) * (1.0f + th);
+  const float e = expf(-c2 * (x + t));
+  return __fdividef(x, 1.0f + e) ;
 }
 
 __device__ __forceinline__ float load_bias(const void* b, int dt, int col) {
@@ -231,7 +231,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -294,8 +294,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
       }
     }
   } else {
-    // epilogue: warp w may read TMEM lanes 32*(w%4) .. +31
+    // epilogue: warp w may read TMEM lanes 32*(w%4) .. +31; the two warps of a quarter split the columns
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     int t = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
@@ -308,7 +309,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
       tc_fence_after();
       const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
         uint32_t r[32];
         if (iters_per_tile > 0) tmem_ld32(tmem_acc + (uint32_t)(c * 32), r);
         else {
@@ -349,7 +350,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 //                complete on it (count 2 + 64 KB);
 //   empty[s]     one per CTA; CTA 0's MMA thread commits to its own and to CTA 1's;
 //   acc_full[b]  one per CTA, committed the same way after a tile's last MMA;
-//   acc_empty[b] lives in CTA 0; the eight epilogue warps of the pair arrive on it.
+//   acc_empty[b] lives in CTA 0; the sixteen epilogue warps of the pair arrive on it.
 // The two CTAs meet at a cluster barrier after set-up and before tear-down, so no remote arrive or
 // MMA ever targets a CTA that has exited.
 constexpr int kPairStages = 6;
@@ -390,7 +391,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) { mbar_init(&full_bar[s], 2); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 16); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -460,6 +461,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     }
   } else {
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     int t = 0;
     bool ok = true;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++t) {
@@ -472,7 +474,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
       tc_fence_after();
       const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * kTile) + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < kTile / 32; ++c) {
+      for (int c = half * (kTile / 64); c < (half + 1) * (kTile / 64); ++c) {
         uint32_t r[32];
         if (iters_per_tile > 0) tmem_ld32(tmem_acc + (uint32_t)(c * 32), r);
         else {
