@@ -9,7 +9,7 @@
 //   warp 0     TMA producer: Q once, then K / V^T tiles into a ring of stages
 //   warp 1     MMA issuer (one thread): QK^T two tiles ahead, P.V as soon as P is published
 //   warps 2-9  softmax: two threads per query row (each half of the keys / output columns)
-// Operand encodings: f16 / bf16 (128 keys per tile), or 3xTF32 for fp32-faithful results (32 keys
+// Operand encodings: f16 / bf16 (64 keys per tile, two CTAs per SM), or 3xTF32 for fp32-faithful results (32 keys
 // per tile; Q, K, V^T pre-split into hi = tf32(x), lo = x - hi; P split on the fly; the three
 // cross products lo.hi, hi.lo, hi.hi go into one accumulator).  All operands are K-major tiles
 // with 128-byte swizzle; V is consumed as V^T [D, keys], prepared by a transposing pre-pass.
@@ -67,20 +67,23 @@ struct AttnParams {
 
 template <bool TF32>
 struct AttnCfg {
-  static constexpr int BKV = TF32 ? 32 : 128;                 // keys per tile
+  static constexpr int BKV = TF32 ? 32 : 64;                  // keys per tile: one 128-byte operand row of P
   static constexpr int NST = TF32 ? 2 : 3;                    // K/V stages
   static constexpr int QBytes = TF32 ? 2 * 2 * kQRows * 128 : kQRows * 128;     // hi+lo x 2 k-blocks | one k-block
   static constexpr int KBytes = TF32 ? 2 * 2 * BKV * 128 : BKV * 128;           // per stage
-  static constexpr int VBytes = TF32 ? 2 * kHeadDim * 128 : 2 * kHeadDim * 128; // hi+lo x 1 k-block | 2 k-blocks
+  static constexpr int VBytes = TF32 ? 2 * kHeadDim * 128 : kHeadDim * 128;     // hi+lo | one k-block of 64 keys
   static constexpr int StageBytes = KBytes + VBytes;
-  static constexpr int PBytes = TF32 ? 2 * kQRows * 128 : 2 * kQRows * 128;     // hi+lo | 2 k-blocks
+  static constexpr int PBytes = TF32 ? 2 * kQRows * 128 : kQRows * 128;         // hi+lo | one k-block
   static constexpr int SCols = BKV;
-  static constexpr int TmemCols = TF32 ? 256 : 512;           // 2 x S + 2 x PV, rounded to a power of two
+  static constexpr int TmemCols = 256;                        // 2 x S + 2 x PV, rounded to a power of two
   static constexpr int SmemBytes = QBytes + NST * StageBytes + 2 * PBytes;
+  // the 16-bit configuration (96 KB, 256 TMEM columns, <= 102 registers) runs two CTAs per SM, so one
+  // CTA's softmax overlaps the other's tensor-core and copy phases
+  static constexpr int CtasPerSm = TF32 ? 1 : 2;
 };
 
 template <bool TF32>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kAttnThreads, AttnCfg<TF32>::CtasPerSm)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant__ CUtensorMap tmQ1,
                 const __grid_constant__ CUtensorMap tmK0, const __grid_constant__ CUtensorMap tmK1,
                 const __grid_constant__ CUtensorMap tmV0, const __grid_constant__ CUtensorMap tmV1,
@@ -160,7 +163,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
         } else {
           tma_load_4d(&tmK0, st, &kv_full[s], 0, k0, h, b);
           tma_load_4d(&tmV0, st + C::KBytes, &kv_full[s], k0, 0, h, b);
-          tma_load_4d(&tmV0, st + C::KBytes + kHeadDim * 128, &kv_full[s], k0 + 64, 0, h, b);
         }
         ++jj;
       }
@@ -221,12 +223,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
             }
           }
         } else {
-          for (int kb = 0; kb < 2; ++kb) {
-            const uint64_t da = make_kmajor_sw128_desc(p_addr + kb * (kQRows * 128));
-            const uint64_t db = make_kmajor_sw128_desc(v_addr + kb * (kHeadDim * 128));
+          const uint64_t da = make_kmajor_sw128_desc(p_addr), db = make_kmajor_sw128_desc(v_addr);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) umma<false>(d_pv, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_pv, (kb || k) ? 1u : 0u);
-          }
+          for (int k = 0; k < 4; ++k) umma<false>(d_pv, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_pv, k ? 1u : 0u);
         }
         umma_commit(&pv_full[t & 1]);
         umma_commit(&kv_empty[s]);
@@ -316,9 +315,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
         }
       }
       if (fast) {
+        // four independent chains: a single running max would serialise HK dependent instructions
+        float mx[4] = {sv[0], sv[1], sv[2], sv[3]};
 #pragma unroll
-        for (int i = 0; i < HK; ++i) mt = fmaxf(mt, sv[i]);
-        mt *= scale;
+        for (int i = 4; i < HK; ++i) mx[i & 3] = fmaxf(mx[i & 3], sv[i]);
+        mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale;
       } else {
 #pragma unroll
         for (int i = 0; i < HK; ++i) {
@@ -343,11 +344,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
       float psum = 0.f;
       if (fast) {
         const float c = scale * kLog2e, ml = m_use * kLog2e;
+        float ps[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < HK; ++i) {
           sv[i] = ex2_approx(fmaf(sv[i], c, -ml));
-          psum += sv[i];
+          ps[i & 3] += sv[i];
         }
+        psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
       } else {
 #pragma unroll
         for (int i = 0; i < HK; ++i) {
@@ -381,11 +384,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
           *reinterpret_cast<float4*>(lo_row + (chunk << 4)) = make_float4(lo[0], lo[1], lo[2], lo[3]);
         }
       } else {
-        // 128 keys = two k-blocks of 64; this thread owns k-block `wg`
+        // 64 keys = one 128-byte row; this thread owns chunks wg*4 .. wg*4+3 (32 keys)
         const bool bf = p.round_scores == BG_BF16 + 1;
-        unsigned char* prow = pb + wg * (kQRows * 128) + r_in_tile * 128;
+        unsigned char* prow = pb + r_in_tile * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 4; ++c) {
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -393,7 +396,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
             if (bf) { __nv_bfloat162 v2 = __floats2bfloat162_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
             else { __half2 v2 = __floats2half2_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
           }
-          *reinterpret_cast<uint4*>(prow + ((c ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(prow + (((wg * 4 + c) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
       fence_async_smem();
@@ -455,9 +458,37 @@ struct PrepView {
   long long stride[4];   // element strides of the [B,H,S,D] view
 };
 
-// dst (dense [B,H,S,D], or [B,H,D,S] when `transpose`) = convert(src view).  mode 0: copy 16-bit values;
-// mode 1: hi = tf32(x), lo = x - hi from fp32 / fp64 (fp16 / bf16 widen first).
-__global__ void attn_prep_kernel(PrepView src, void* dst_a, void* dst_b, int B, int H, int S, int D, int transpose, int mode) {
+// Encodings the forward kernel consumes: 16-bit values, or the hi = tf32(x) / lo = x - hi pair.
+enum PrepKind : int { PREP_F16 = 0, PREP_BF16 = 1, PREP_TF32 = 2 };
+
+__device__ __forceinline__ double prep_load(const void* p, int dtype, long long off) {
+  switch (dtype) {
+    case BG_F64: return reinterpret_cast<const double*>(p)[off];
+    case BG_F32: return reinterpret_cast<const float*>(p)[off];
+    case BG_F16: return __half2float(reinterpret_cast<const __half*>(p)[off]);
+    default: return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[off]);
+  }
+}
+
+// Rounds like the graph's CAST node would (float32 -> 16 bit, round to nearest even); 16-bit sources of
+// the same type pass through unchanged.
+__device__ __forceinline__ void prep_store(void* dst_a, void* dst_b, long long i, double xd, int kind) {
+  if (kind == PREP_TF32) {
+    const float x = (float)xd;
+    uint32_t hb;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x));
+    const float fh = __uint_as_float(hb);
+    reinterpret_cast<float*>(dst_a)[i] = fh;
+    reinterpret_cast<float*>(dst_b)[i] = (float)(xd - (double)fh);   // for fp64 sources lo also carries the bits fp32 dropped
+  } else if (kind == PREP_F16) {
+    reinterpret_cast<__half*>(dst_a)[i] = __float2half_rn((float)xd);
+  } else {
+    reinterpret_cast<__nv_bfloat16*>(dst_a)[i] = __float2bfloat16_rn((float)xd);
+  }
+}
+
+// dst (dense [B,H,S,D], or [B,H,D,S] when `transpose`) = encode(src view): any strides, one element per thread step.
+__global__ void attn_prep_kernel(PrepView src, void* dst_a, void* dst_b, int B, int H, int S, int D, int transpose, int kind) {
   const long long n = (long long)B * H * S * D;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     // i enumerates the destination densely
@@ -468,23 +499,65 @@ __global__ void attn_prep_kernel(PrepView src, void* dst_a, void* dst_b, int B, 
     const int h = (int)(rem % H);
     const int b = (int)(rem / H);
     const long long off = b * src.stride[0] + h * src.stride[1] + s * src.stride[2] + d * src.stride[3];
-    if (mode == 0) {
-      reinterpret_cast<uint16_t*>(dst_a)[i] = reinterpret_cast<const uint16_t*>(src.ptr)[off];
-    } else {
-      double xd;
-      switch (src.dtype) {
-        case BG_F64: xd = reinterpret_cast<const double*>(src.ptr)[off]; break;
-        case BG_F32: xd = reinterpret_cast<const float*>(src.ptr)[off]; break;
-        case BG_F16: xd = __half2float(reinterpret_cast<const __half*>(src.ptr)[off]); break;
-        default: xd = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(src.ptr)[off]); break;
+    prep_store(dst_a, dst_b, i, prep_load(src.ptr, src.dtype, off), kind);
+  }
+}
+
+// Same encoding for an fp32 source whose rows of D = 64 values are contiguous (strides over b, h, s are free
+// multiples of four), four elements per thread step: Q and K of fp32 graphs and of autocast graphs whose casts
+// were folded into this pass.
+__global__ void attn_prep_rows_f32_kernel(const float* __restrict__ src, long long sb, long long sh, long long ss, void* dst_a,
+                                          void* dst_b, int H, int S, long long n4, int kind) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i >> 4;              // 16 float4 groups per row of 64
+    const int c4 = (int)(i & 15);
+    const int sidx = (int)(row % S);
+    const long long bh = row / S;
+    const int h = (int)(bh % H);
+    const long long b = bh / H;
+    const float4 v = __ldcs(reinterpret_cast<const float4*>(src + b * sb + h * sh + sidx * ss) + c4);
+    const float x[4] = {v.x, v.y, v.z, v.w};
+    if (kind == PREP_TF32) {
+      float hi[4], lo[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        uint32_t hb;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x[e]));
+        hi[e] = __uint_as_float(hb);
+        lo[e] = __fadd_rn(x[e], -hi[e]);
       }
-      const float x = (float)xd;
-      uint32_t hb;
-      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x));
-      const float fh = __uint_as_float(hb);
-      reinterpret_cast<float*>(dst_a)[i] = fh;
-      reinterpret_cast<float*>(dst_b)[i] = (float)(xd - (double)fh);
+      reinterpret_cast<float4*>(dst_a)[i] = make_float4(hi[0], hi[1], hi[2], hi[3]);
+      reinterpret_cast<float4*>(dst_b)[i] = make_float4(lo[0], lo[1], lo[2], lo[3]);
+    } else if (kind == PREP_F16) {
+      __half2 a = __floats2half2_rn(x[0], x[1]), b2 = __floats2half2_rn(x[2], x[3]);
+      reinterpret_cast<uint2*>(dst_a)[i] = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b2));
+    } else {
+      __nv_bfloat162 a = __floats2bfloat162_rn(x[0], x[1]), b2 = __floats2bfloat162_rn(x[2], x[3]);
+      reinterpret_cast<uint2*>(dst_a)[i] = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b2));
     }
+  }
+}
+
+// V [B, H, S, 64] (rows of 64 contiguous; fp32, fp64 or the 16-bit operand type) -> V^T [B*H, 64, S] in the kernel's
+// encoding.  One CTA transposes 64 keys x 64 columns through shared memory: source rows are read whole, V^T rows
+// are written 64 keys at a time.
+__global__ void __launch_bounds__(256) attn_prep_vt_kernel(const void* __restrict__ src, int src_dtype, long long sb, long long sh,
+                                                           long long ss, void* dst_a, void* dst_b, int H, int S, int kind) {
+  __shared__ double tile[64][65];
+  const long long bh = blockIdx.y;
+  const long long base = (bh / H) * sb + (bh % H) * sh;
+  const int s0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;   // 64 x 4
+#pragma unroll 4
+  for (int r = ty; r < 64; r += 4) {
+    const int sidx = s0 + r;
+    tile[r][tx] = sidx < S ? prep_load(src, src_dtype, base + sidx * ss + tx) : 0.0;
+  }
+  __syncthreads();
+#pragma unroll 4
+  for (int d = ty; d < 64; d += 4) {
+    const int sidx = s0 + tx;
+    if (sidx < S) prep_store(dst_a, dst_b, (bh * 64 + d) * (long long)S + sidx, tile[tx][d], kind);
   }
 }
 
@@ -588,7 +661,7 @@ bool attn_tc_supported(const AttnProblem& a) {
 void attn_scratch_sizes(const AttnProblem& a, int64_t bytes[8]) {
   const int64_t nq = (int64_t)a.B * a.H * a.Sq * a.D, nk = (int64_t)a.B * a.H * a.Sk * a.D;
   const int es = a.mode == 1 ? 4 : 2;
-  const int bkv = a.mode == 1 ? 32 : 128;
+  const int bkv = a.mode == 1 ? 32 : 64;
   bytes[0] = nq * es;                       // Q (hi)
   bytes[1] = a.mode == 1 ? nq * es : 0;     // Q lo
   bytes[2] = nk * es;                       // K (hi)
@@ -602,25 +675,40 @@ void attn_scratch_sizes(const AttnProblem& a, int64_t bytes[8]) {
   bytes[7] = a.scale_buf ? 4 : 0;           // uniform-scale flag
 }
 
-cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bool check_uniform, int* status, cudaStream_t s) {
+cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bool check_uniform, bool classify_mask, int* status,
+                                cudaStream_t s) {
   const bool tf32 = a.mode == 1;
-  const int bkv = tf32 ? 32 : 128;
+  const int bkv = tf32 ? 32 : 64;
   const int sdt = tf32 ? BG_F32 : a.ab_dtype;
   // operand staging: dense Q, K, V^T in the kernel's encoding
+  const int kind = tf32 ? PREP_TF32 : (a.ab_dtype == BG_F16 ? PREP_F16 : PREP_BF16);
   const AttnOperand* ops[3] = {&a.q, &a.k, &a.v};
   const int seq[3] = {a.Sq, a.Sk, a.Sk};
   const void* staged[3] = {scratch[0], scratch[2], scratch[4]};
   for (int i = 0; i < 3; ++i) {
     const long long n = (long long)a.B * a.H * seq[i] * a.D;
-    // 16-bit Q / K that are already dense [B,H,S,D] feed the TMA maps directly
     const bool dense = ops[i]->stride[3] == 1 && ops[i]->stride[2] == a.D && ops[i]->stride[1] == (long long)seq[i] * a.D &&
                        ops[i]->stride[0] == (long long)a.H * seq[i] * a.D;
-    if (!tf32 && i < 2 && dense && ops[i]->dtype == a.ab_dtype && (reinterpret_cast<uintptr_t>(ops[i]->ptr) & 15) == 0) {
+    const bool aligned = (reinterpret_cast<uintptr_t>(ops[i]->ptr) & 15) == 0;
+    // 16-bit Q / K that are already dense [B,H,S,D] feed the TMA maps directly
+    if (!tf32 && i < 2 && dense && ops[i]->dtype == a.ab_dtype && aligned) {
       staged[i] = ops[i]->ptr;
       continue;
     }
-    PrepView v{ops[i]->ptr, ops[i]->dtype, {ops[i]->stride[0], ops[i]->stride[1], ops[i]->stride[2], ops[i]->stride[3]}};
-    attn_prep_kernel<<<prep_grid(n), 256, 0, s>>>(v, scratch[2 * i], scratch[2 * i + 1], a.B, a.H, seq[i], a.D, i == 2, tf32 ? 1 : 0);
+    const bool rows_contig = ops[i]->stride[3] == 1 && a.D == 64;
+    const bool rows_vec = rows_contig && aligned && ops[i]->dtype == BG_F32 && (ops[i]->stride[0] & 3) == 0 &&
+                          (ops[i]->stride[1] & 3) == 0 && (ops[i]->stride[2] & 3) == 0;
+    if (i == 2 && rows_contig) {
+      attn_prep_vt_kernel<<<dim3((unsigned)((seq[i] + 63) / 64), (unsigned)(a.B * a.H)), 256, 0, s>>>(
+          ops[i]->ptr, ops[i]->dtype, ops[i]->stride[0], ops[i]->stride[1], ops[i]->stride[2], scratch[4], scratch[5], a.H, seq[i], kind);
+    } else if (i < 2 && rows_vec) {
+      attn_prep_rows_f32_kernel<<<prep_grid(n / 4), 256, 0, s>>>(reinterpret_cast<const float*>(ops[i]->ptr), ops[i]->stride[0],
+                                                                ops[i]->stride[1], ops[i]->stride[2], scratch[2 * i], scratch[2 * i + 1],
+                                                                a.H, seq[i], n / 4, kind);
+    } else {
+      PrepView v{ops[i]->ptr, ops[i]->dtype, {ops[i]->stride[0], ops[i]->stride[1], ops[i]->stride[2], ops[i]->stride[3]}};
+      attn_prep_kernel<<<prep_grid(n), 256, 0, s>>>(v, scratch[2 * i], scratch[2 * i + 1], a.B, a.H, seq[i], a.D, i == 2, kind);
+    }
   }
   unsigned char* cls = nullptr;
   uint32_t* bits = nullptr;
@@ -630,7 +718,8 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
     cls = reinterpret_cast<unsigned char*>(scratch[6]);
     const int n_q = (a.Sq + kQRows - 1) / kQRows;
     bits = reinterpret_cast<uint32_t*>(cls + (((size_t)n_q * n_kv_tiles + 255) & ~(size_t)255));
-    attn_mask_class_kernel<<<dim3(n_kv_tiles, n_q), 256, 0, s>>>(a.mask, a.mask_is_bool, a.Sq, a.Sk, bkv, cls, n_kv_tiles, bits, words_per_row);
+    if (classify_mask)
+      attn_mask_class_kernel<<<dim3(n_kv_tiles, n_q), 256, 0, s>>>(a.mask, a.mask_is_bool, a.Sq, a.Sk, bkv, cls, n_kv_tiles, bits, words_per_row);
   }
   int* uniform = nullptr;
   if (a.scale_buf) {

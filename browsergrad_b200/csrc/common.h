@@ -251,6 +251,6 @@ struct AttnProblem {
 bool attn_tc_supported(const AttnProblem& a);
 void attn_scratch_sizes(const AttnProblem& a, int64_t bytes[8]);
 // scratch[7] is the device flag "scale_buf is uniform"; it is (re)computed when check_uniform is set.
-cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bool check_uniform, int* status, cudaStream_t s);
+cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bool check_uniform, bool classify_mask, int* status, cudaStream_t s);
 
 }  // namespace bg

@@ -192,6 +192,30 @@ void uniform_flag_drop(bg_context* ctx, const void* ptr) {
   ctx->uniform_flags.erase(it);
 }
 
+void* mask_classes_for(bg_context* ctx, const void* ptr, int64_t bytes, int sq, int sk, int bkv, int is_bool, bool* fresh) {
+  *fresh = false;
+  auto it = ctx->mask_classes.find(ptr);
+  if (it != ctx->mask_classes.end()) {
+    const auto& m = it->second;
+    if (m.bytes == bytes && m.sq == sq && m.sk == sk && m.bkv == bkv && m.is_bool == is_bool) return m.buf;
+    dev_free(ctx, m.buf, m.bytes);
+    ctx->mask_classes.erase(it);
+  }
+  if (ctx->mask_classes.size() >= 64) return nullptr;   // callers then fall back to per-run scratch
+  void* buf = nullptr;
+  if (dev_alloc(ctx, bytes, &buf) != BG_OK) return nullptr;
+  ctx->mask_classes[ptr] = {buf, bytes, sq, sk, bkv, is_bool};
+  *fresh = true;
+  return buf;
+}
+
+void mask_classes_drop(bg_context* ctx, const void* ptr) {
+  auto it = ctx->mask_classes.find(ptr);
+  if (it == ctx->mask_classes.end()) return;
+  dev_free(ctx, it->second.buf, it->second.bytes);
+  ctx->mask_classes.erase(it);
+}
+
 static int64_t numel_of(const int64_t* shape, int rank) {
   int64_t n = 1;
   for (int i = 0; i < rank; ++i) n *= shape[i];
@@ -248,6 +272,8 @@ int bg_destroy(bg_context* ctx) {
   cudaStreamSynchronize(ctx->stream);
   for (auto& kv : ctx->handles) cudaFreeAsync(kv.second.ptr, ctx->stream);
   ctx->handles.clear();
+  for (auto& kv : ctx->mask_classes) cudaFreeAsync(kv.second.buf, ctx->stream);
+  ctx->mask_classes.clear();
   ctx->plan_cache.clear();
   for (auto& pe : ctx->pending_events) {
     cudaEventDestroy(pe.second.first);
@@ -321,6 +347,7 @@ int bg_release(bg_context* ctx, bg_handle h) {
   if (it == ctx->handles.end()) return BG_OK;  // idempotent, unknown handle is a no-op
   cudaSetDevice(ctx->device);
   uniform_flag_drop(ctx, it->second.ptr);
+  mask_classes_drop(ctx, it->second.ptr);
   dev_free(ctx, it->second.ptr, it->second.bytes);
   ctx->handles.erase(it);
   return BG_OK;

@@ -230,6 +230,7 @@ class Compiler {
   };
   struct AttnPlan {
     int q = -1, kt = -1, v = -1;      // operand nodes (kt: the [B,H,D,Sk] view fed to the first MATMUL)
+    int q_src = -1, kt_src = -1, v_src = -1;   // fp32 node behind an absorbed fp32 -> 16-bit CAST of that operand, or -1
     int mask = -1, mask_is_bool = 0;
     int scale_node = -1;              // BUFFER-backed multiplier, or -1 with scale_const
     double scale_const = 1.0;
@@ -1864,6 +1865,40 @@ bool Compiler::match_attention(int n, AttnPlan& ap, std::vector<int>& interior) 
   else if (od == BG_F64 && (ctx_->f64_mode == 1 || (ctx_->f64_mode == 2 && !has_f64_leaf_)) &&
            (qd == BG_F32 || qd == BG_F64) && (kd == BG_F32 || kd == BG_F64) && (vd == BG_F32 || vd == BG_F64)) { ap.mode = 1; ap.ab_dtype = BG_F32; }
   else return false;
+  if (ap.mode == 0) {
+    // An autocast graph feeds Q, K, V through CAST(float32 -> 16 bit) nodes.  When such a cast exists only for
+    // this attention and reads a dense fp32 tensor, the operand staging pass does the rounding itself (same
+    // round-to-nearest-even), so the cast's own kernel and its 16-bit copy disappear.
+    auto cast_source = [&](int node, int& cast_node) -> int {
+      int pnode = node;
+      while (kind_[pnode] == K_VIEW || kind_[pnode] == K_ALIAS) {
+        if (!single(pnode)) return -1;
+        pnode = resolve(nodes_[pnode].in[0]);
+      }
+      if (kind_[pnode] != K_EW || nodes_[pnode].op != BG_OP_CAST || nodes_[pnode].dtype != ap.ab_dtype || !single(pnode)) return -1;
+      const int g = find(pnode);
+      for (int i = 0; i < (int)nodes_.size(); ++i)
+        if (i != pnode && kind_[i] == K_EW && find(i) == g) return -1;    // fused with other elementwise work
+      const int src = resolve(nodes_[pnode].in[0]);
+      const View& sv = view_[src];
+      if (sv.is_const || sv.slot < 0 || sv.dtype != BG_F32 || !sv.contiguous() || sv.rank != nodes_[pnode].rank) return -1;
+      for (int d = 0; d < sv.rank; ++d)
+        if (sv.shape[d] != nodes_[pnode].shape[d]) return -1;
+      cast_node = pnode;
+      return src;
+    };
+    int* srcs[3] = {&ap.q_src, &ap.kt_src, &ap.v_src};
+    const int operands[3] = {ap.q, ap.kt, ap.v};
+    std::set<int> seen;
+    for (int i = 0; i < 3; ++i) {
+      int cast_node = -1;
+      const int src = cast_source(operands[i], cast_node);
+      if (src < 0 || seen.count(cast_node)) continue;    // one cast feeding two operands stays a kernel of its own
+      seen.insert(cast_node);
+      *srcs[i] = src;
+      interior.push_back(cast_node);
+    }
+  }
   AttnProblem pr{};
   pr.B = (int)B; pr.H = (int)H; pr.Sq = (int)Sq; pr.Sk = (int)Sk; pr.D = (int)D;
   pr.mode = ap.mode;
@@ -1910,6 +1945,9 @@ void Compiler::emit_attention(int n, int key) {
   tmpl.q = operand(qv, false);
   tmpl.k = operand(ktv, true);
   tmpl.v = operand(vv, false);
+  if (ap.q_src >= 0) tmpl.q.dtype = BG_F32;
+  if (ap.kt_src >= 0) tmpl.k.dtype = BG_F32;
+  if (ap.v_src >= 0) tmpl.v.dtype = BG_F32;
   int mask_slot = -1;
   int64_t mask_off = 0;
   if (ap.mask >= 0) {
@@ -1931,15 +1969,21 @@ void Compiler::emit_attention(int n, int key) {
   int64_t bytes[8];
   attn_scratch_sizes(sized, bytes);
   int scratch_slot[8];
+  const int64_t class_bytes = bytes[6];
   PUnit pu;
   for (int i = 0; i < 8; ++i) {
     scratch_slot[i] = bytes[i] > 0 ? new_slot(bytes[i], false, -1) : -1;
     if (scratch_slot[i] >= 0) pu.u.writes.push_back(scratch_slot[i]);
   }
-  const int sq = qv.slot, sk = ktv.slot, sv = vv.slot, so = view_[n].slot;
-  const int64_t offq = qv.off * dtype_size(qv.dtype), offk = ktv.off * dtype_size(ktv.dtype), offv = vv.off * dtype_size(vv.dtype);
+  // an operand whose cast was absorbed is read from the fp32 tensor behind it: same index map, the source's storage
+  auto slot_of = [&](const View& v, int src) { return src >= 0 ? view_[src].slot : v.slot; };
+  auto off_of = [&](const View& v, int src) {
+    return src >= 0 ? (view_[src].off + v.off) * (int64_t)4 : v.off * (int64_t)dtype_size(v.dtype);
+  };
+  const int sq = slot_of(qv, ap.q_src), sk = slot_of(ktv, ap.kt_src), sv = slot_of(vv, ap.v_src), so = view_[n].slot;
+  const int64_t offq = off_of(qv, ap.q_src), offk = off_of(ktv, ap.kt_src), offv = off_of(vv, ap.v_src);
   pu.order_key = key;
-  pu.dep_nodes = {ap.q, ap.kt, ap.v};
+  pu.dep_nodes = {ap.q_src >= 0 ? ap.q_src : ap.q, ap.kt_src >= 0 ? ap.kt_src : ap.kt, ap.v_src >= 0 ? ap.v_src : ap.v};
   if (ap.mask >= 0) pu.dep_nodes.push_back(ap.mask);
   if (ap.scale_node >= 0) pu.dep_nodes.push_back(ap.scale_node);
   pu.out_nodes = {n};
@@ -1964,7 +2008,14 @@ void Compiler::emit_attention(int n, int key) {
       int* flag = uniform_flag_for(r.ctx, a.scale_buf, &fresh);
       if (flag) { scratch[7] = flag; check_uniform = fresh; }
     }
-    cudaError_t e = launch_attention_tc(a, scratch, check_uniform, r.ctx->d_status, r.ctx->stream);
+    // likewise the tile classes of a mask bound by handle are computed once and kept with the handle
+    bool classify_mask = a.mask != nullptr;
+    if (a.mask && mask_slot >= 0 && r.from_handle[mask_slot] && a.mask_sb == 0 && a.mask_sh == 0 && class_bytes > 0) {
+      bool fresh = false;
+      void* kept = mask_classes_for(r.ctx, a.mask, class_bytes, a.Sq, a.Sk, a.mode == 1 ? 32 : 64, a.mask_is_bool, &fresh);
+      if (kept) { scratch[6] = kept; classify_mask = fresh; }
+    }
+    cudaError_t e = launch_attention_tc(a, scratch, check_uniform, classify_mask, r.ctx->d_status, r.ctx->stream);
     return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "attention launch");
   };
   add_unit(std::move(pu));

@@ -53,6 +53,10 @@ struct bg_context {
   std::unordered_map<const void*, int*> uniform_flags;
   int* uniform_pool = nullptr;      // 1024 device ints
   std::vector<int> uniform_free;
+  // attention mask tile classes + per-row mask bit words for masks bound by handle (their contents cannot
+  // change while the handle lives), keyed by device pointer; entries die with their handle
+  struct MaskClasses { void* buf; int64_t bytes; int sq, sk, bkv, is_bool; };
+  std::unordered_map<const void*, MaskClasses> mask_classes;
 };
 
 namespace bg {
@@ -73,6 +77,10 @@ int d2h(bg_context* ctx, void* dst, const void* src, size_t n);
 // was just created and still has to be computed.  Returns nullptr when the pool is exhausted.
 int* uniform_flag_for(bg_context* ctx, const void* ptr, bool* fresh);
 void uniform_flag_drop(bg_context* ctx, const void* ptr);
+// Device buffer holding the tile classes of the handle-backed mask at `ptr` for this geometry; *fresh is set
+// when it was just allocated and still has to be computed.  Returns nullptr when the allocation fails.
+void* mask_classes_for(bg_context* ctx, const void* ptr, int64_t bytes, int sq, int sk, int bkv, int is_bool, bool* fresh);
+void mask_classes_drop(bg_context* ctx, const void* ptr);
 
 int run_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs, int n_inputs, void* out_host,
              size_t out_nbytes, bg_handle* out_handle);
