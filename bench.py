@@ -446,7 +446,7 @@ def main() -> None:
         achieved = bytes_step[top] / (per_kernel[top]["ms"] * 1e-3) / 1e9
         # DRAM read+write per launch from the ncu capture summarised in profiles/config2_pattern_kernels_rows4096.md
         # (fp32 [4096, 4096]), scaled by the row count: traffic grows in proportion to the rows processed
-        ncu_traffic_4096_rows = {"y": 307.4e6, "rowsum": 272.7e6, "rowsoftmax": 306.6e6}
+        ncu_traffic_4096_rows = {"y": 309.9e6, "rowsum": 275.3e6, "rowsoftmax": 307.8e6}
         roofline = {"bound": "hbm", "kernel": per_kernel[top]["name"], "achieved": achieved, "peak": peaks["hbm_gbs"],
                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                     "frac_of_nominal": achieved / NOMINAL["hbm_gbs"], "nominal_peak": NOMINAL["hbm_gbs"],
