@@ -6,11 +6,11 @@
 // P V into tensor memory, which the same warps fold into a register accumulator.
 //
 // One CTA owns 128 query rows of one (batch, head):
-//   warp 0     TMA producer: Q once, then K / V^T tiles into a ring of stages
+//   warp 0     TMA producer: Q once, then K tiles and V^T tiles (64 keys) into their rings
 //   warp 1     MMA issuer (one thread): QK^T two tiles ahead, P.V as soon as P is published
 //   warps 2-9  softmax: two threads per query row (each half of the keys / output columns)
-// Operand encodings: f16 / bf16 (64 keys per tile, two CTAs per SM), or 3xTF32 for fp32-faithful results (32 keys
-// per tile; Q, K, V^T pre-split into hi = tf32(x), lo = x - hi; P split on the fly; the three
+// Operand encodings: f16 / bf16 (two CTAs per SM), or 3xTF32 for fp32-faithful results (Q, K, V^T pre-split into
+// hi = tf32(x), lo = x - hi; P split on the fly; the three
 // cross products lo.hi, hi.lo, hi.hi go into one accumulator).  All operands are K-major tiles
 // with 128-byte swizzle; V is consumed as V^T [D, keys], prepared by a transposing pre-pass.
 // Masks: additive fp32 [B|1, H|1, Sq, Sk], or boolean "fill with -inf"; a per-(q tile, k tile)
@@ -67,16 +67,21 @@ struct AttnParams {
 
 template <bool TF32>
 struct AttnCfg {
-  static constexpr int BKV = TF32 ? 32 : 64;                  // keys per tile: one 128-byte operand row of P
-  static constexpr int NST = TF32 ? 2 : 3;                    // K/V stages
-  static constexpr int QBytes = TF32 ? 2 * 2 * kQRows * 128 : kQRows * 128;     // hi+lo x 2 k-blocks | one k-block
-  static constexpr int KBytes = TF32 ? 2 * 2 * BKV * 128 : BKV * 128;           // per stage
-  static constexpr int VBytes = TF32 ? 2 * kHeadDim * 128 : kHeadDim * 128;     // hi+lo | one k-block of 64 keys
-  static constexpr int StageBytes = KBytes + VBytes;
-  static constexpr int PBytes = TF32 ? 2 * kQRows * 128 : kQRows * 128;         // hi+lo | one k-block
+  static constexpr int BKV = 64;                              // keys per tile
+  // K and V^T tiles travel in rings of their own: K(t+1) can be fetched as soon as Q.K(t)^T has been issued,
+  // V(t+1) once P.V(t) has completed.  The 3xTF32 encoding (hi + lo planes, 4-byte elements) has room for one
+  // tile of each; the 16-bit encoding keeps three.
+  static constexpr int NK = TF32 ? 1 : 3;
+  static constexpr int NV = TF32 ? 1 : 3;
+  static constexpr int NP = TF32 ? 1 : 2;                     // P buffers
+  // 3xTF32 planes: hi k-block 0, hi k-block 1, lo k-block 0, lo k-block 1 (a k-block is 32 floats = 128 bytes)
+  static constexpr int QBytes = TF32 ? 4 * kQRows * 128 : kQRows * 128;
+  static constexpr int KBytes = TF32 ? 4 * BKV * 128 : BKV * 128;
+  static constexpr int VBytes = TF32 ? 4 * kHeadDim * 128 : kHeadDim * 128;     // V^T: 64 rows x (2 x 32 | 64) keys
+  static constexpr int PBytes = TF32 ? 4 * kQRows * 128 : kQRows * 128;
   static constexpr int SCols = BKV;
-  static constexpr int TmemCols = 256;                        // 2 x S + 2 x PV, rounded to a power of two
-  static constexpr int SmemBytes = QBytes + NST * StageBytes + 2 * PBytes;
+  static constexpr int TmemCols = 256;                        // 2 x S + 2 x PV
+  static constexpr int SmemBytes = QBytes + NK * KBytes + NV * VBytes + NP * PBytes;
   // the 16-bit configuration (96 KB, 256 TMEM columns, <= 102 registers) runs two CTAs per SM, so one
   // CTA's softmax overlaps the other's tensor-core and copy phases
   static constexpr int CtasPerSm = TF32 ? 1 : 2;
@@ -93,15 +98,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* sQ = smem;
-  unsigned char* sKV = sQ + C::QBytes;
-  unsigned char* sP = sKV + C::NST * C::StageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * C::PBytes);
+  unsigned char* sK = sQ + C::QBytes;
+  unsigned char* sV = sK + C::NK * C::KBytes;
+  unsigned char* sP = sV + C::NV * C::VBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::NP * C::PBytes);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = q_full + 1;
-  uint64_t* kv_empty = kv_full + C::NST;
-  uint64_t* s_full = kv_empty + C::NST;   // [2]
-  uint64_t* p_full = s_full + 2;          // [2]
-  uint64_t* pv_full = p_full + 2;         // [2]
+  uint64_t* k_full = q_full + 1;
+  uint64_t* k_empty = k_full + C::NK;
+  uint64_t* v_full = k_empty + C::NK;
+  uint64_t* v_empty = v_full + C::NV;
+  uint64_t* s_full = v_empty + C::NV;     // [2]
+  uint64_t* p_full = s_full + 2;          // [NP]
+  uint64_t* pv_full = p_full + C::NP;     // [2]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_full + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   float* pmax = reinterpret_cast<float*>(tmem_holder + 4);   // [2 buffers][2 halves][128 rows] tile maxima
@@ -115,8 +123,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < C::NST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 8); mbar_init(&pv_full[i], 1); }
+    for (int s = 0; s < C::NK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    for (int s = 0; s < C::NV; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&pv_full[i], 1); }
+    for (int i = 0; i < C::NP; ++i) mbar_init(&p_full[i], 8);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -143,28 +153,51 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
       } else {
         tma_load_4d(&tmQ0, sQ, q_full, 0, q0, h, b);
       }
-      int jj = 0;
-      for (int j = 0; j < n_kv; ++j) {
-        if (cls && cls[j] == 0) continue;
-        const int s = jj % C::NST;
-        const uint32_t ph = (uint32_t)(jj / C::NST) & 1u;
-        if (!mbar_wait(&kv_empty[s], ph ^ 1u, abort_flag)) break;
-        unsigned char* st = sKV + s * C::StageBytes;
+      // K runs one tile ahead of V in issue order: its slot frees as soon as Q.K^T of the previous occupant is done
+      auto next_tile = [&](int j) { while (j < n_kv && cls && cls[j] == 0) ++j; return j; };
+      auto load_k = [&](int j, int t) -> bool {
+        const int s = t % C::NK;
+        if (!mbar_wait(&k_empty[s], ((uint32_t)(t / C::NK) & 1u) ^ 1u, abort_flag)) return false;
+        unsigned char* st = sK + s * C::KBytes;
         const int k0 = j * BKV;
-        mbar_expect_tx(&kv_full[s], C::StageBytes);
+        mbar_expect_tx(&k_full[s], C::KBytes);
         if (TF32) {
-          // K hi / lo: two k-blocks of 32 floats each; V^T hi / lo: one k-block of 32 keys
           for (int kb = 0; kb < 2; ++kb) {
-            tma_load_4d(&tmK0, st + kb * (BKV * 128), &kv_full[s], kb * 32, k0, h, b);
-            tma_load_4d(&tmK1, st + 2 * (BKV * 128) + kb * (BKV * 128), &kv_full[s], kb * 32, k0, h, b);
+            tma_load_4d(&tmK0, st + kb * (BKV * 128), &k_full[s], kb * 32, k0, h, b);
+            tma_load_4d(&tmK1, st + (2 + kb) * (BKV * 128), &k_full[s], kb * 32, k0, h, b);
           }
-          tma_load_4d(&tmV0, st + C::KBytes, &kv_full[s], k0, 0, h, b);
-          tma_load_4d(&tmV1, st + C::KBytes + kHeadDim * 128, &kv_full[s], k0, 0, h, b);
         } else {
-          tma_load_4d(&tmK0, st, &kv_full[s], 0, k0, h, b);
-          tma_load_4d(&tmV0, st + C::KBytes, &kv_full[s], k0, 0, h, b);
+          tma_load_4d(&tmK0, st, &k_full[s], 0, k0, h, b);
         }
-        ++jj;
+        return true;
+      };
+      auto load_v = [&](int j, int t) -> bool {
+        const int s = t % C::NV;
+        if (!mbar_wait(&v_empty[s], ((uint32_t)(t / C::NV) & 1u) ^ 1u, abort_flag)) return false;
+        unsigned char* st = sV + s * C::VBytes;
+        const int k0 = j * BKV;
+        mbar_expect_tx(&v_full[s], C::VBytes);
+        if (TF32) {
+          for (int kb = 0; kb < 2; ++kb) {
+            tma_load_4d(&tmV0, st + kb * (kHeadDim * 128), &v_full[s], k0 + kb * 32, 0, h, b);
+            tma_load_4d(&tmV1, st + (2 + kb) * (kHeadDim * 128), &v_full[s], k0 + kb * 32, 0, h, b);
+          }
+        } else {
+          tma_load_4d(&tmV0, st, &v_full[s], k0, 0, h, b);
+        }
+        return true;
+      };
+      int jk = next_tile(0), jv = jk, tk = 0, tv = 0;
+      bool okp = true;
+      while (jv < n_kv && okp) {
+        while (okp && jk < n_kv && tk <= tv + 1) {
+          okp = load_k(jk, tk);
+          ++tk;
+          jk = next_tile(jk + 1);
+        }
+        if (okp) okp = load_v(jv, tv);
+        ++tv;
+        jv = next_tile(jv + 1);
       }
     }
   } else if (warp == 1) {
@@ -175,10 +208,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
       bool ok = n_proc == 0 || mbar_wait(q_full, 0, abort_flag);
       const uint32_t q_addr = smem_u32(sQ);
       auto issue_qk = [&](int t) -> bool {   // t-th processed tile
-        const int s = t % C::NST;
-        if (!mbar_wait(&kv_full[s], (uint32_t)(t / C::NST) & 1u, abort_flag)) return false;
+        const int s = t % C::NK;
+        if (!mbar_wait(&k_full[s], (uint32_t)(t / C::NK) & 1u, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(sKV + s * C::StageBytes);
+        const uint32_t k_addr = smem_u32(sK + s * C::KBytes);
         const uint32_t d_s = tmem_s + (uint32_t)((t & 1) * C::SCols);
         if (TF32) {
           // passes lo.hi, hi.lo, hi.hi; each: 2 k-blocks x 4 k-steps of 8 floats
@@ -202,24 +235,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
           for (int k = 0; k < 4; ++k) umma<false>(d_s, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_qk, k ? 1u : 0u);
         }
         umma_commit(&s_full[t & 1]);
+        umma_commit(&k_empty[s]);
         return true;
       };
       auto issue_pv = [&](int t) -> bool {
-        const int s = t % C::NST;
-        if (!mbar_wait(&p_full[t & 1], (uint32_t)(t >> 1) & 1u, abort_flag)) return false;
+        const int s = t % C::NV, pbuf = t % C::NP;
+        if (!mbar_wait(&p_full[pbuf], (uint32_t)(t / C::NP) & 1u, abort_flag)) return false;
+        if (!mbar_wait(&v_full[s], (uint32_t)(t / C::NV) & 1u, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t p_addr = smem_u32(sP + (t & 1) * C::PBytes);
-        const uint32_t v_addr = smem_u32(sKV + s * C::StageBytes + C::KBytes);
+        const uint32_t p_addr = smem_u32(sP + pbuf * C::PBytes);
+        const uint32_t v_addr = smem_u32(sV + s * C::VBytes);
         const uint32_t d_pv = tmem_pv + (uint32_t)((t & 1) * kHeadDim);
         if (TF32) {
+          // passes lo.hi, hi.lo, hi.hi over the tile's two k-blocks of 32 keys
           uint32_t first = 1;
           for (int pass = 0; pass < 3; ++pass) {
-            const uint64_t da = make_kmajor_sw128_desc(p_addr + (pass == 0 ? kQRows * 128 : 0));
-            const uint64_t db = make_kmajor_sw128_desc(v_addr + (pass == 1 ? kHeadDim * 128 : 0));
+            const uint32_t pa = p_addr + (pass == 0 ? 2 * (kQRows * 128) : 0);
+            const uint32_t va = v_addr + (pass == 1 ? 2 * (kHeadDim * 128) : 0);
+            for (int kb = 0; kb < 2; ++kb) {
+              const uint64_t da = make_kmajor_sw128_desc(pa + kb * (kQRows * 128));
+              const uint64_t db = make_kmajor_sw128_desc(va + kb * (kHeadDim * 128));
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              umma<true>(d_pv, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_pv, first ? 0u : 1u);
-              first = 0;
+              for (int k = 0; k < 4; ++k) {
+                umma<true>(d_pv, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_pv, first ? 0u : 1u);
+                first = 0;
+              }
             }
           }
         } else {
@@ -228,7 +268,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
           for (int k = 0; k < 4; ++k) umma<false>(d_pv, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_pv, k ? 1u : 0u);
         }
         umma_commit(&pv_full[t & 1]);
-        umma_commit(&kv_empty[s]);
+        umma_commit(&v_empty[s]);
         return true;
       };
       if (ok && n_proc > 0) ok = issue_qk(0);
@@ -279,20 +319,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
       float sv[HK];
       {
         const uint32_t src = tmem_s + (uint32_t)(buf * C::SCols + wg * HK) + lane_sel;
-        if (HK == 16) {
-          uint32_t r[16];
-          tmem_ld16(src, r);
+        uint32_t r[32];
+        tmem_ld32(src, r);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) sv[i] = __uint_as_float(r[i]);
-        } else {
-#pragma unroll
-          for (int c = 0; c < HK / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld32(src + (uint32_t)(c * 32), r);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) sv[(c * 32 + i) % HK] = __uint_as_float(r[i]);
-          }
-        }
+        for (int i = 0; i < 32; ++i) sv[i] = __uint_as_float(r[i]);
       }
       // Probabilities: p = 2^((x - m) * log2(e)) with x = scale * s (+ mask).  The common case -- whole
       // tile in range, no mask to apply, one positive scale -- folds scale and log2(e) into a single FMA
@@ -363,23 +393,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
       m = m_new;
       // publish P in the K-major 128-byte-swizzled operand layout: row r_in_tile, 16-byte chunk c of
       // a 128-byte row lands at chunk (c ^ (row & 7))
-      unsigned char* pb = sP + buf * C::PBytes;
+      // with a single P buffer the previous tile's P.V must have consumed it first; its result is folded here
+      if (C::NP == 1 && t > 0) {
+        ok = fold_pv(t - 1, alpha_prev);
+        if (!ok) break;
+      }
+      const int pbuf = t % C::NP;
+      unsigned char* pb = sP + pbuf * C::PBytes;
       const int sw = r_in_tile & 7;
       if (TF32) {
-        // 32 keys = one 128-byte row; this thread owns chunks wg*4 .. wg*4+3 (16 keys)
-        unsigned char* hi_row = pb + r_in_tile * 128;
-        unsigned char* lo_row = pb + kQRows * 128 + r_in_tile * 128;
+        // this thread's 32 keys are k-block `wg`: one 128-byte row in the hi plane and one in the lo plane
+        unsigned char* hi_row = pb + wg * (kQRows * 128) + r_in_tile * 128;
+        unsigned char* lo_row = pb + (2 + wg) * (kQRows * 128) + r_in_tile * 128;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 8; ++c) {
           float hi[4], lo[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             uint32_t hbits;
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hbits) : "f"(sv[(c * 4 + e) % HK]));
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hbits) : "f"(sv[c * 4 + e]));
             hi[e] = __uint_as_float(hbits);
-            lo[e] = sv[(c * 4 + e) % HK] - hi[e];
+            lo[e] = sv[c * 4 + e] - hi[e];
           }
-          const int chunk = (wg * 4 + c) ^ sw;
+          const int chunk = c ^ sw;
           *reinterpret_cast<float4*>(hi_row + (chunk << 4)) = make_float4(hi[0], hi[1], hi[2], hi[3]);
           *reinterpret_cast<float4*>(lo_row + (chunk << 4)) = make_float4(lo[0], lo[1], lo[2], lo[3]);
         }
@@ -392,7 +428,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float a0 = sv[(c * 8 + 2 * e) % HK], a1 = sv[(c * 8 + 2 * e + 1) % HK];
+            const float a0 = sv[c * 8 + 2 * e], a1 = sv[c * 8 + 2 * e + 1];
             if (bf) { __nv_bfloat162 v2 = __floats2bfloat162_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
             else { __half2 v2 = __floats2half2_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
           }
@@ -402,9 +438,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[buf]);
+      if (lane == 0) mbar_arrive(&p_full[pbuf]);
       // fold the previous tile's P.V while the tensor core works on this one
-      if (t > 0) ok = fold_pv(t - 1, alpha_prev);
+      if (C::NP == 2 && t > 0) ok = fold_pv(t - 1, alpha_prev);
       alpha_prev = alpha;
       ++t;
     }
@@ -661,7 +697,7 @@ bool attn_tc_supported(const AttnProblem& a) {
 void attn_scratch_sizes(const AttnProblem& a, int64_t bytes[8]) {
   const int64_t nq = (int64_t)a.B * a.H * a.Sq * a.D, nk = (int64_t)a.B * a.H * a.Sk * a.D;
   const int es = a.mode == 1 ? 4 : 2;
-  const int bkv = a.mode == 1 ? 32 : 64;
+  const int bkv = 64;
   bytes[0] = nq * es;                       // Q (hi)
   bytes[1] = a.mode == 1 ? nq * es : 0;     // Q lo
   bytes[2] = nk * es;                       // K (hi)
@@ -678,7 +714,7 @@ void attn_scratch_sizes(const AttnProblem& a, int64_t bytes[8]) {
 cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bool check_uniform, bool classify_mask, int* status,
                                 cudaStream_t s) {
   const bool tf32 = a.mode == 1;
-  const int bkv = tf32 ? 32 : 64;
+  const int bkv = 64;
   const int sdt = tf32 ? BG_F32 : a.ab_dtype;
   // operand staging: dense Q, K, V^T in the kernel's encoding
   const int kind = tf32 ? PREP_TF32 : (a.ab_dtype == BG_F16 ? PREP_F16 : PREP_BF16);

@@ -167,6 +167,18 @@ struct StridedView {
   int64_t stride[kMaxRank];   // elements
 };
 
+// Data-movement kernels over a strided input view and a dense output (shape_kernels.cu).
+// tri: keep the lower (upper = 0) or upper triangle of the last two dims relative to `diagonal`, zero elsewhere.
+cudaError_t launch_tri(const StridedView& in, void* out, int64_t numel, int upper, int64_t diagonal, cudaStream_t s);
+// flip: out[..., i, ...] = in[..., n - 1 - i, ...] along `axis`.
+cudaError_t launch_flip(const StridedView& in, void* out, int64_t numel, int axis, cudaStream_t s);
+// place: copies `in` (converted to out_dtype) into the block of the dense output `out_shape` that starts at
+// `axis_offset` along `axis` (one launch per CONCAT input).
+cudaError_t launch_place(const StridedView& in, void* out, int out_dtype, const int64_t* out_shape, int axis, int64_t axis_offset,
+                         cudaStream_t s);
+// cumsum along `axis` in the output dtype, sequential per line as NumPy's add.accumulate.
+cudaError_t launch_cumsum(const StridedView& in, void* out, int out_dtype, int axis, int reverse, cudaStream_t s);
+
 // out[...] = in[view] : dense copy of a strided view (permute / broadcast materialisation).
 cudaError_t launch_strided_copy(const StridedView& in, void* out, int64_t numel, cudaStream_t s);
 // Generic [outer, R, inner] reductions / softmax on dense data (any inner), fp32/fp64/int64.

@@ -17,7 +17,8 @@ const char* op_name(int op) {
   static const char* names[] = {"BUFFER", "LOAD", "CONST", "CAST", "ADD", "MUL", "DIV", "NEG", "EXP", "LOG",
                                 "ABS", "SIGN", "SIN", "COS", "ISNAN", "CMP", "WHERE", "MATMUL", "REDUCE",
                                 "RESHAPE", "PERMUTE", "BROADCAST_TO", "LAYER_NORM", "CROSS_ENTROPY", "INDEX",
-                                "FUSED_ELEMENTWISE", "FUSED_SOFTMAX", "ATTENTION_FORWARD"};
+                                "FUSED_ELEMENTWISE", "FUSED_SOFTMAX", "ATTENTION_FORWARD", "TRIL", "TRIU", "FLIP", "CONCAT",
+                                "CUMSUM"};
   return (op >= 0 && op < BG_OP_COUNT) ? names[op] : "?";
 }
 

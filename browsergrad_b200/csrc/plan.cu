@@ -241,6 +241,7 @@ class Compiler {
   bool match_attention(int n, AttnPlan& ap, std::vector<int>& interior);
   void plan_attention();
   void emit_attention(int n, int key);
+  void emit_shape_op(int n, int key);
   std::map<int, EpiPlan> epi_plan_;       // MATMUL node -> folded epilogue
   std::set<int> absorbed_groups_;
   int tc_mode(int n);                      // -1: SIMT; 0: 16-bit operands; 1: 3xTF32
@@ -584,6 +585,7 @@ void Compiler::build_views() {
         v.slot = new_slot(n.numel() * dtype_size(n.dtype), false, i);
         break;
       case BG_OP_MATMUL: case BG_OP_INDEX: case BG_OP_CROSS_ENTROPY:
+      case BG_OP_TRIL: case BG_OP_TRIU: case BG_OP_FLIP: case BG_OP_CONCAT: case BG_OP_CUMSUM:
         kind_[i] = K_OTHER;
         v.set_dense(n.shape, n.rank);
         v.slot = new_slot(n.numel() * dtype_size(n.dtype), false, i);
@@ -2012,7 +2014,7 @@ void Compiler::emit_attention(int n, int key) {
     bool classify_mask = a.mask != nullptr;
     if (a.mask && mask_slot >= 0 && r.from_handle[mask_slot] && a.mask_sb == 0 && a.mask_sh == 0 && class_bytes > 0) {
       bool fresh = false;
-      void* kept = mask_classes_for(r.ctx, a.mask, class_bytes, a.Sq, a.Sk, a.mode == 1 ? 32 : 64, a.mask_is_bool, &fresh);
+      void* kept = mask_classes_for(r.ctx, a.mask, class_bytes, a.Sq, a.Sk, 64, a.mask_is_bool, &fresh);
       if (kept) { scratch[6] = kept; classify_mask = fresh; }
     }
     cudaError_t e = launch_attention_tc(a, scratch, check_uniform, classify_mask, r.ctx->d_status, r.ctx->stream);
@@ -2223,6 +2225,87 @@ void Compiler::emit_index(int n, int key) {
   add_unit(std::move(pu));
 }
 
+// TRIL / TRIU / FLIP / CUMSUM (one input) and CONCAT (several): strided views in, one dense tensor out.
+void Compiler::emit_shape_op(int n, int key) {
+  const Node& t = nodes_[n];
+  const int n_in = (int)t.in.size();
+  if (t.op == BG_OP_CONCAT) { if (n_in < 1) err(BG_ERR_INVALID, "CONCAT: no inputs"); }
+  else if (n_in != 1) err(BG_ERR_INVALID, std::string(op_name(t.op)) + ": one input required");
+  struct Src { int slot; int64_t off_bytes; StridedView v; };
+  std::vector<Src> srcs;
+  std::vector<int> deps;
+  for (int k = 0; k < n_in; ++k) {
+    const int x = resolve(t.in[k]);
+    const View& xv = view_[x];
+    if (xv.is_const) err(BG_ERR_UNSUPPORTED, std::string(op_name(t.op)) + " of a scalar constant");
+    Src sc{};
+    sc.slot = xv.slot;
+    sc.off_bytes = xv.off * dtype_size(xv.dtype);
+    sc.v.dtype = xv.dtype;
+    sc.v.rank = xv.rank;
+    for (int d = 0; d < xv.rank; ++d) { sc.v.shape[d] = xv.shape[d]; sc.v.stride[d] = xv.shape[d] == 1 ? 0 : xv.stride[d]; }
+    srcs.push_back(sc);
+    deps.push_back(x);
+  }
+  const int rank = t.rank;
+  const int64_t a0 = t.iarg[0];
+  const View& x0 = view_[resolve(t.in[0])];
+  if (t.op != BG_OP_CONCAT) {
+    if (x0.rank != rank) err(BG_ERR_INVALID, std::string(op_name(t.op)) + ": result rank differs from the input's");
+    for (int d = 0; d < rank; ++d)
+      if (x0.shape[d] != t.shape[d]) err(BG_ERR_INVALID, std::string(op_name(t.op)) + ": result shape differs from the input's");
+  }
+  if ((t.op == BG_OP_TRIL || t.op == BG_OP_TRIU)) {
+    if (rank < 2) err(BG_ERR_INVALID, "TRIL/TRIU: at least two dimensions required");
+    if (x0.dtype != t.dtype) err(BG_ERR_INVALID, "TRIL/TRIU: dtype must be preserved");
+  }
+  if (t.op == BG_OP_FLIP) {
+    if (a0 < 0 || a0 >= rank) err(BG_ERR_INVALID, "FLIP: axis out of range");
+    if (x0.dtype != t.dtype) err(BG_ERR_INVALID, "FLIP: dtype must be preserved");
+  }
+  if (t.op == BG_OP_CUMSUM && (a0 < 0 || a0 >= rank)) err(BG_ERR_INVALID, "CUMSUM: axis out of range");
+  std::vector<int64_t> axis_off;
+  if (t.op == BG_OP_CONCAT) {
+    if (a0 < 0 || a0 >= rank) err(BG_ERR_INVALID, "CONCAT: axis out of range");
+    int64_t total = 0;
+    for (const Src& sc : srcs) {
+      if (sc.v.rank != rank) err(BG_ERR_INVALID, "CONCAT: inputs must have the result's rank");
+      for (int d = 0; d < rank; ++d)
+        if (d != a0 && sc.v.shape[d] != t.shape[d]) err(BG_ERR_INVALID, "CONCAT: input extents off the axis must match the result");
+      axis_off.push_back(total);
+      total += sc.v.shape[a0];
+    }
+    if (total != t.shape[a0]) err(BG_ERR_INVALID, "CONCAT: input extents along the axis do not add up to the result's");
+  }
+  own_slot(n);
+  const int so = view_[n].slot, op = t.op, out_dt = t.dtype;
+  const int64_t numel = t.numel();
+  const int reverse = (int)t.iarg[1];
+  std::vector<int64_t> oshape(t.shape, t.shape + rank);
+  PUnit pu;
+  pu.order_key = key;
+  pu.dep_nodes = deps;
+  pu.out_nodes = {n};
+  pu.u.launches = op == BG_OP_CONCAT ? n_in : 1;
+  pu.u.name = op == BG_OP_CONCAT ? "place[CONCAT]" : (op == BG_OP_CUMSUM ? "scan[CUMSUM]" : std::string("index_map[") + op_name(op) + "]");
+  pu.u.fn = [=](Run& r) {
+    cudaError_t e = cudaSuccess;
+    for (size_t k = 0; k < srcs.size() && e == cudaSuccess; ++k) {
+      StridedView v = srcs[k].v;
+      v.ptr = reinterpret_cast<char*>(r.ptr[srcs[k].slot]) + srcs[k].off_bytes;
+      switch (op) {
+        case BG_OP_TRIL: e = launch_tri(v, r.ptr[so], numel, 0, a0, r.ctx->stream); break;
+        case BG_OP_TRIU: e = launch_tri(v, r.ptr[so], numel, 1, a0, r.ctx->stream); break;
+        case BG_OP_FLIP: e = launch_flip(v, r.ptr[so], numel, (int)a0, r.ctx->stream); break;
+        case BG_OP_CUMSUM: e = launch_cumsum(v, r.ptr[so], out_dt, (int)a0, reverse, r.ctx->stream); break;
+        default: e = launch_place(v, r.ptr[so], out_dt, oshape.data(), (int)a0, axis_off[k], r.ctx->stream); break;
+      }
+    }
+    return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "data-movement kernel launch");
+  };
+  add_unit(std::move(pu));
+}
+
 void Compiler::emit_ce(int n, int key) {
   const Node& t = nodes_[n];
   if (t.in.size() != 2) err(BG_ERR_UNSUPPORTED, "CROSS_ENTROPY: class weights are not supported");
@@ -2377,6 +2460,7 @@ bool Compiler::try_lower() {
         case BG_OP_MATMUL: emit_matmul(i, i); break;
         case BG_OP_INDEX: emit_index(i, i); break;
         case BG_OP_CROSS_ENTROPY: emit_ce(i, i); break;
+        case BG_OP_TRIL: case BG_OP_TRIU: case BG_OP_FLIP: case BG_OP_CONCAT: case BG_OP_CUMSUM: emit_shape_op(i, i); break;
         case BG_OP_RESHAPE: emit_copy(i, copy_src_.at(i), resolve(n.in[0]), i); break;
         default: err(BG_ERR_UNSUPPORTED, std::string("opcode ") + op_name(n.op));
       }

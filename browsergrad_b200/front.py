@@ -143,7 +143,7 @@ def plan_for(node: Any, fusion: bool = True) -> Tuple[Any, Dict[str, Any]]:
     hit = _PLAN_MEMO.get(id(node))
     if hit is not None and hit[0] is node:
         return hit[1], hit[2]
-    prepared = passes.prepare(node, fusion=fusion)
+    prepared = passes.lower_composites(passes.prepare(node, fusion=fusion))
     plan = build_plan(prepared)
     for s in plan["steps"]:
         if s["op"] not in _lib.OP_CODE:

@@ -293,6 +293,57 @@ class Tensor:
     def argmin(self, axis: Any = None, keepdims: bool = False) -> "Tensor":
         return self._reduce("argmin", axis, keepdims)
 
+    def var(self, axis: Any = None, dim: Any = None, keepdims: bool = False, keepdim: bool = False,
+            unbiased: Any = None, correction: Any = None) -> "Tensor":
+        """``VAR`` node of ``TensorProxy.var`` (_tensor_proxy.py:1438-1483): biased when
+        ``correction=0`` / ``unbiased=False``, Bessel-corrected by default."""
+        if self.dtype not in ("float16", "float32", "float64"):
+            raise ValueError(f"var: floating dtypes only, got {self.dtype!r}")
+        if correction is not None and unbiased is not None:
+            raise ValueError("var: specify only one of unbiased or correction")
+        corr = int(correction) if correction is not None else (1 if unbiased is None or unbiased else 0)
+        reduce_axis = dim if dim is not None else axis
+        keep = bool(keepdim or keepdims)
+        nd = self.ndim
+        if reduce_axis is None:
+            axes = tuple(range(nd))
+        else:
+            axes = tuple(sorted({a % nd for a in ((reduce_axis,) if isinstance(reduce_axis, int) else tuple(reduce_axis))}))
+        out_shape = tuple(1 if keep and i in axes else d for i, d in enumerate(self.shape) if keep or i not in axes)
+        node = Node("VAR", (self._uop,), out_shape, self.dtype, {"axes": axes, "correction": corr, "keepdims": keep})
+        return self._wrap(node)
+
+    def clamp(self, min: Any = None, max: Any = None) -> "Tensor":
+        """``CLAMP`` node (_tensor_proxy.py:992-1023); bounds are finite Python floats or ``None``."""
+        if min is None and max is None:
+            raise ValueError("clamp: at least one of min or max must be provided")
+        lo = None if min is None else float(min)
+        hi = None if max is None else float(max)
+        if lo is not None and hi is not None and lo > hi:
+            raise ValueError(f"clamp: min {lo} must be <= max {hi}")
+        return self._wrap(Node("CLAMP", (self._uop,), self.shape, self.dtype, {"min": lo, "max": hi}))
+
+    def flip(self, dim: int) -> "Tensor":
+        """``FLIP`` node (_tensor_proxy.py:1122-1139)."""
+        axis = int(dim) % self.ndim
+        return self._wrap(Node("FLIP", (self._uop,), self.shape, self.dtype, {"axis": axis}))
+
+    def _triangular(self, diagonal: int, upper: bool) -> "Tensor":
+        if self.ndim < 2:
+            raise ValueError("tril/triu: at least two dimensions required")
+        return self._wrap(Node("TRIU" if upper else "TRIL", (self._uop,), self.shape, self.dtype,
+                               {"diagonal": int(diagonal)}))
+
+    def tril(self, diagonal: int = 0) -> "Tensor":
+        """``TRIL`` node (_tensor_proxy.py:1143-1173)."""
+        return self._triangular(diagonal, False)
+
+    def triu(self, diagonal: int = 0) -> "Tensor":
+        return self._triangular(diagonal, True)
+
+    def cumsum(self, dim: int, dtype: Any = None) -> "Tensor":
+        return cumsum(self, dim=dim, dtype=dtype)
+
     # -- shape ops ----------------------------------------------------------------
     def reshape(self, *shape: Any) -> "Tensor":
         new_shape = tuple(shape[0]) if len(shape) == 1 and isinstance(shape[0], (tuple, list)) \
@@ -486,6 +537,47 @@ def attention_forward(q: Tensor, k: Tensor, v: Tensor) -> Tensor:
     scale = float(np.float32(1.0 / np.sqrt(q.shape[-1])))
     return Tensor(Node("ATTENTION_FORWARD", (q._uop, k._uop, v._uop), q.shape, "float32",
                        {"scale": scale, "mask": "none"}), q._store)
+
+
+def cumsum(x: Tensor, dim: int = 0, *, dtype: Any = None) -> Tensor:
+    """``CUMSUM`` node (_tensor_proxy.py:2512-2545): running sum along ``dim`` in ``dtype`` (the input's
+    dtype when not given; bool and small integers accumulate as int64, as the reference normalises)."""
+    axis = int(dim) % x.ndim
+    if dtype is None:
+        out_dtype = "int64" if x.dtype in ("bool", "int8", "int16", "int32", "uint8", "uint16", "uint32") else x.dtype
+    else:
+        out_dtype = np.dtype(dtype).name if not isinstance(dtype, str) else dtype
+    return x._wrap(Node("CUMSUM", (x._uop,), x.shape, out_dtype, {"axis": axis, "reverse": False}))
+
+
+def cat(tensors: Sequence[Tensor], dim: int = 0) -> Tensor:
+    """``CONCAT`` node (_tensor_proxy.py:2328-2389): inputs agree off ``dim``; the result dtype is NumPy's
+    promotion of the input dtypes."""
+    ts = tuple(tensors)
+    if not ts:
+        raise ValueError("cat: empty tensor list")
+    rank = ts[0].ndim
+    axis = int(dim) % rank
+    for t in ts[1:]:
+        if t.ndim != rank or any(a != b for i, (a, b) in enumerate(zip(t.shape, ts[0].shape)) if i != axis):
+            raise ValueError("cat: inputs must agree on every dimension but the concatenated one")
+    out_shape = tuple(sum(t.shape[axis] for t in ts) if i == axis else d for i, d in enumerate(ts[0].shape))
+    out_dtype = np.result_type(*[np.dtype(t.dtype) if t.dtype != "bfloat16" else np.float32 for t in ts]).name \
+        if len({t.dtype for t in ts}) > 1 else ts[0].dtype
+    return ts[0]._wrap(Node("CONCAT", tuple(t._uop for t in ts), out_shape, out_dtype, {"axis": axis}))
+
+
+def stack(tensors: Sequence[Tensor], dim: int = 0) -> Tensor:
+    """``STACK`` node (_tensor_proxy.py:2391-2449): equal shapes, a new axis at ``dim``."""
+    ts = tuple(tensors)
+    if not ts:
+        raise ValueError("stack: empty tensor list")
+    if any(t.shape != ts[0].shape for t in ts[1:]):
+        raise ValueError("stack: inputs must have equal shapes")
+    axis = int(dim) % (ts[0].ndim + 1)
+    out_shape = ts[0].shape[:axis] + (len(ts),) + ts[0].shape[axis:]
+    out_dtype = np.result_type(*[np.dtype(t.dtype) for t in ts]).name if len({t.dtype for t in ts}) > 1 else ts[0].dtype
+    return ts[0]._wrap(Node("STACK", tuple(t._uop for t in ts), out_shape, out_dtype, {"axis": axis}))
 
 
 def toposort(root: Node) -> list:

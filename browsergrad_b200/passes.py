@@ -19,6 +19,7 @@ from __future__ import annotations
 
 from typing import Any, Dict, List, Optional, Set, Tuple
 
+from .errors import JitNotImplementedError
 from .graph import toposort
 
 ELEMENTWISE_OPS = frozenset({"ADD", "MUL", "DIV", "NEG", "EXP", "LOG"})
@@ -228,3 +229,73 @@ def prepare(root: Any, *, fusion: bool = True) -> Any:
     """Cast pass then fusion, the order of ``_realize.realize`` (_realize.py:1890-1893)."""
     root = insert_cast_pass(root)
     return fuse(root) if fusion else root
+
+
+def _rebuild(root: Any, rewrite) -> Any:
+    """Bottom-up rewrite of a graph: ``rewrite(node, new_inputs)`` returns the replacement node."""
+    done = {}
+    for node in toposort(root):
+        ins = tuple(done[id(i)] for i in node.inputs)
+        done[id(node)] = rewrite(node, ins)
+    return done[id(root)]
+
+
+def lower_composites(root: Any) -> Any:
+    """Rewrites CLAMP, VAR and STACK into opcodes the CUDA plan compiler schedules, with NumPy's
+    evaluation order, so that they fuse with their neighbours like any other elementwise / reduce
+    chain (the reference evaluates them with one NumPy call each, _realize.py:254-260, :299-306,
+    :346-357):
+
+    * ``CLAMP(x; lo, hi)`` -> ``where(t > hi, hi, t)`` with ``t = where(x < lo, lo, x)`` -- ``np.clip``
+      for floats, NaN passes through both comparisons;
+    * ``VAR(x; axes, correction)`` -> ``sum((x - mean(x))**2) / max(n - correction, 0)`` with the mean kept
+      in the result dtype -- the two passes of ``np.var(dtype=...)``;
+    * ``STACK`` -> ``CONCAT`` of the inputs reshaped with a unit axis.
+    """
+    def make(like: Any, op: str, inputs: tuple, shape: tuple, dtype: str, arg: Any) -> Any:
+        return type(like)(op=op, inputs=inputs, shape=tuple(shape), dtype=dtype, arg=arg)
+
+    def rewrite(node: Any, ins: tuple) -> Any:
+        if node.op == "CLAMP":
+            (x,) = ins
+            if node.dtype not in ("float16", "float32", "float64", "bfloat16"):
+                raise JitNotImplementedError("CUDA realizer: CLAMP of a non-floating tensor is not supported. "
+                                             "Fall back to bg.realize() (NumPy).")
+            out = x
+            lo, hi = node.arg.get("min"), node.arg.get("max")
+            if lo is not None:
+                c = make(node, "CONST", (), (), node.dtype, {"value": float(lo)})
+                cmp = make(node, "CMP", (out, c), node.shape, "bool", {"op": "lt"})
+                out = make(node, "WHERE", (cmp, c, out), node.shape, node.dtype, None)
+            if hi is not None:
+                c = make(node, "CONST", (), (), node.dtype, {"value": float(hi)})
+                cmp = make(node, "CMP", (out, c), node.shape, "bool", {"op": "gt"})
+                out = make(node, "WHERE", (cmp, c, out), node.shape, node.dtype, None)
+            return out
+        if node.op == "VAR":
+            (x,) = ins
+            axes = tuple(int(a) for a in node.arg["axes"])
+            keep = bool(node.arg.get("keepdims", False))
+            n = 1
+            for a in axes:
+                n *= int(x.shape[a])
+            kept = tuple(1 if i in axes else d for i, d in enumerate(x.shape))
+            mean = make(node, "REDUCE", (x,), kept, node.dtype, {"op": "mean", "axis": axes, "keepdims": True})
+            neg = make(node, "NEG", (mean,), kept, node.dtype, None)
+            centered = make(node, "ADD", (x, neg), x.shape, node.dtype, None)
+            sq = make(node, "MUL", (centered, centered), x.shape, node.dtype, None)
+            total = make(node, "REDUCE", (sq,), node.shape, node.dtype, {"op": "sum", "axis": axes, "keepdims": keep})
+            count = make(node, "CONST", (), (), node.dtype, {"value": float(max(n - int(node.arg.get("correction", 1)), 0))})
+            return make(node, "DIV", (total, count), node.shape, node.dtype, None)
+        if node.op == "STACK":
+            axis = int(node.arg["axis"])
+            parts = []
+            for x in ins:
+                shp = tuple(x.shape[:axis]) + (1,) + tuple(x.shape[axis:])
+                parts.append(make(node, "RESHAPE", (x,), shp, x.dtype, {"new_shape": shp}))
+            return make(node, "CONCAT", tuple(parts), node.shape, node.dtype, {"axis": axis})
+        if all(a is b for a, b in zip(ins, node.inputs)):
+            return node
+        return make(node, node.op, ins, node.shape, node.dtype, node.arg)
+
+    return _rebuild(root, rewrite)

@@ -169,6 +169,13 @@ def encode_plan(plan: Dict[str, Any], permute_axes: Optional[Dict[int, Tuple[int
             st.farg[0] = float(arg.get("eps", 1e-5))
         elif op == "INDEX":
             st.iarg[0] = int(arg["dim"])
+        elif op in ("TRIL", "TRIU"):
+            st.iarg[0] = int(arg["diagonal"])
+        elif op in ("FLIP", "CONCAT"):
+            st.iarg[0] = int(arg["axis"])
+        elif op == "CUMSUM":
+            st.iarg[0] = int(arg["axis"])
+            st.iarg[1] = 1 if arg.get("reverse") else 0
         elif op == "CROSS_ENTROPY":
             if arg.get("target_mode", "indices") != "indices" or arg.get("has_weight") or arg.get("label_smoothing"):
                 raise JitNotImplementedError(

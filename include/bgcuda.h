@@ -65,7 +65,11 @@ typedef enum bg_opcode {
   BG_OP_MATMUL = 17, BG_OP_REDUCE = 18, BG_OP_RESHAPE = 19, BG_OP_PERMUTE = 20,
   BG_OP_BROADCAST_TO = 21, BG_OP_LAYER_NORM = 22, BG_OP_CROSS_ENTROPY = 23, BG_OP_INDEX = 24,
   BG_OP_FUSED_ELEMENTWISE = 25, BG_OP_FUSED_SOFTMAX = 26, BG_OP_ATTENTION_FORWARD = 27,
-  BG_OP_COUNT = 28
+  /* Data-movement opcodes beyond the 28 of the forward configs (_ir.py:93-99; handlers
+     _realize.py:268-327): iarg[0] = axis (FLIP, CUMSUM, CONCAT) or diagonal (TRIL, TRIU);
+     CUMSUM iarg[1] = reverse.  CONCAT takes up to BG_MAX_STEP_INPUTS inputs. */
+  BG_OP_TRIL = 28, BG_OP_TRIU = 29, BG_OP_FLIP = 30, BG_OP_CONCAT = 31, BG_OP_CUMSUM = 32,
+  BG_OP_COUNT = 33
 } bg_opcode;
 
 typedef enum bg_cmp { BG_CMP_EQ = 0, BG_CMP_NE = 1, BG_CMP_LT = 2, BG_CMP_LE = 3,

@@ -151,6 +151,49 @@ def _h_reduce(node, vt, store):  # _realize.py:1094-1111
     return np.asarray(out, dtype=np.dtype(node.dtype))
 
 
+def _h_clamp(node, vt, store):  # _realize.py:254-260
+    return np.clip(_in(node, vt, 0), node.arg.get("min"), node.arg.get("max")).astype(np.dtype(node.dtype), copy=False)
+
+
+def _h_flip(node, vt, store):  # _realize.py:268-270
+    return np.flip(_in(node, vt, 0), axis=int(node.arg["axis"])).copy()
+
+
+def _h_cumsum(node, vt, store):  # _realize.py:273-285
+    axis, reverse = int(node.arg["axis"]), bool(node.arg.get("reverse", False))
+    source = _in(node, vt, 0)
+    if reverse:
+        source = np.flip(source, axis=axis)
+    scanned = np.cumsum(source, axis=axis, dtype=np.dtype(node.dtype))
+    if reverse:
+        scanned = np.flip(scanned, axis=axis)
+    return np.array(scanned, dtype=np.dtype(node.dtype), copy=True)
+
+
+def _h_concat(node, vt, store):  # _realize.py:288-296 (without the legacy empty-operand skip)
+    arrays = [np.asarray(vt[id(src)], dtype=np.dtype(node.dtype)) for src in node.inputs]
+    return np.array(np.concatenate(arrays, axis=int(node.arg["axis"])), dtype=np.dtype(node.dtype), copy=True)
+
+
+def _h_stack(node, vt, store):  # _realize.py:299-306
+    arrays = [np.asarray(vt[id(src)], dtype=np.dtype(node.dtype)) for src in node.inputs]
+    return np.array(np.stack(arrays, axis=int(node.arg["axis"])), dtype=np.dtype(node.dtype), copy=True)
+
+
+def _h_tril(node, vt, store):  # _realize.py:317-320
+    return np.array(np.tril(_in(node, vt, 0), k=int(node.arg["diagonal"])), dtype=np.dtype(node.dtype), copy=True)
+
+
+def _h_triu(node, vt, store):  # _realize.py:323-326
+    return np.array(np.triu(_in(node, vt, 0), k=int(node.arg["diagonal"])), dtype=np.dtype(node.dtype), copy=True)
+
+
+def _h_var(node, vt, store):  # _realize.py:346-357
+    variance = np.var(_in(node, vt, 0), axis=tuple(node.arg["axes"]), keepdims=bool(node.arg.get("keepdims", False)),
+                      ddof=int(node.arg.get("correction", 1)), dtype=np.dtype(node.dtype))
+    return np.array(variance, dtype=np.dtype(node.dtype), copy=True).reshape(node.shape)
+
+
 def _h_where(node, vt, store):  # _realize.py:1453-1459
     sel = np.where(_in(node, vt, 0), _in(node, vt, 1), _in(node, vt, 2))
     return np.array(sel, dtype=np.dtype(node.dtype), copy=True).reshape(node.shape)
@@ -300,6 +343,8 @@ _DISPATCH: Dict[str, Callable] = {
     "RESHAPE": lambda n, vt, s: _in(n, vt, 0).reshape(n.arg["new_shape"]),         # :1114-1116
     "PERMUTE": lambda n, vt, s: np.transpose(_in(n, vt, 0), axes=n.arg["axes"]),   # :1119-1121
     "WHERE": _h_where,
+    "CLAMP": _h_clamp, "FLIP": _h_flip, "CUMSUM": _h_cumsum, "CONCAT": _h_concat, "STACK": _h_stack,
+    "TRIL": _h_tril, "TRIU": _h_triu, "VAR": _h_var,
     "INDEX": _h_index,
     "BROADCAST_TO": _h_broadcast_to,
     "FUSED_ELEMENTWISE": _h_fused_elementwise,

@@ -27,6 +27,7 @@ class RefApi:
         self.attention_forward = bg.kernels.attention_forward
         self.autocast = lambda dtype="float16": bg.amp.autocast(dtype=dtype)
         self.from_numpy = bg.from_numpy
+        self.cat, self.stack, self.cumsum = bg.cat, bg.stack, bg.cumsum
 
 
 def canonical_arg(op: str, arg: Any) -> Any:
@@ -212,6 +213,25 @@ CASES: Dict[str, Case] = {
     "ln_stream_static": Case(_ln_inputs(33, 200), lambda api, t, raw: _ln_stream(api, t, "y", 200)),
     "ln_stream_f64_static": Case(_ln_inputs(41, 520), lambda api, t, raw: _ln_stream(api, t, "yd", 520)),
     "layer_norm_2axes": Case(_misc_inputs, lambda api, t, raw: api.layer_norm(t["x"], (5, 33))),
+    # -- data-movement and composite opcodes beyond the five configurations ----------------
+    "tril_causal": Case(_misc_inputs, lambda api, t, raw: t["bm"].tril(), kind="exact"),
+    "triu_diag2": Case(_misc_inputs, lambda api, t, raw: t["x"].triu(2), kind="exact"),
+    "tril_int_neg": Case(_misc_inputs, lambda api, t, raw: t["i"].tril(-1), kind="exact"),
+    "tril_of_permute": Case(_misc_inputs, lambda api, t, raw: t["x"].permute(0, 2, 1).tril(1), kind="exact"),
+    "flip_last": Case(_misc_inputs, lambda api, t, raw: t["x"].flip(2), kind="exact"),
+    "flip_first_int": Case(_misc_inputs, lambda api, t, raw: t["i"].flip(0), kind="exact"),
+    "cat_rows": Case(_misc_inputs, lambda api, t, raw: api.cat([t["x"], t["p"], t["x"]], 0), kind="exact"),
+    "cat_last_mixed": Case(_misc_inputs, lambda api, t, raw: api.cat([t["x"], t["d"]], 2), kind="exact"),
+    "cat_then_sum": Case(_misc_inputs, lambda api, t, raw: api.cat([t["x"] * t["p"], t["x"] + t["row"]], 1).sum(axis=-1)),
+    "stack_mid": Case(_misc_inputs, lambda api, t, raw: api.stack([t["x"], t["p"]], 1), kind="exact"),
+    "cumsum_last": Case(_misc_inputs, lambda api, t, raw: api.cumsum(t["x"], 2), kind="exact"),
+    "cumsum_first_int": Case(_misc_inputs, lambda api, t, raw: api.cumsum(t["i32"], 0), kind="exact"),
+    "cumsum_mid_f64": Case(_misc_inputs, lambda api, t, raw: api.cumsum(t["d"], 1), kind="exact"),
+    "clamp_both": Case(_misc_inputs, lambda api, t, raw: t["x"].clamp(-0.5, 0.75), kind="exact"),
+    "clamp_min_chain": Case(_misc_inputs, lambda api, t, raw: (t["x"] * t["p"]).clamp(min=0.0) + t["row"]),
+    "var_last": Case(_misc_inputs, lambda api, t, raw: t["x"].var(axis=-1)),
+    "var_biased_keep": Case(_misc_inputs, lambda api, t, raw: t["x"].var(axis=(0, 2), keepdims=True, correction=0)),
+    "var_all_f64": Case(_misc_inputs, lambda api, t, raw: t["d"].var()),
     "gather_rows": Case(_misc_inputs, lambda api, t, raw: t["table"].gather(0, t["tidx"]), kind="exact"),
     "gather_cols": Case(_misc_inputs, lambda api, t, raw: t["table"].gather(1, t["cidx"]), kind="exact"),
     "int_arith": Case(_misc_inputs, lambda api, t, raw: (t["i"] * t["j"] + t["i"]) * 3 + (-t["j"]),
