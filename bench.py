@@ -351,6 +351,7 @@ def main() -> None:
                     + ", ".join(EXTRA_NAMES))
     ap.add_argument("--attn-batch", type=int, default=16)
     ap.add_argument("--e2e-chunks", type=int, default=16)
+    ap.add_argument("--e2e-lanes", type=int, default=3)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -490,10 +491,10 @@ def main() -> None:
             return dt
         n_e2e = max(2, min(args.steps, 5))
         dt_single = timed(e2e_step, n_e2e)
-        # the same step streamed in row chunks over three bridges (one stream each) of this device, so that
+        # the same step streamed in row chunks over several bridges (one stream each) of this device, so that
         # uploads, kernels and read-backs of neighbouring chunks overlap on the full-duplex PCIe link
         from browsergrad_b200.sharded import cuda_row_pipeline
-        lanes = [bridge, CudaBridge(local), CudaBridge(local)]
+        lanes = [bridge] + [CudaBridge(local) for _ in range(max(1, args.e2e_lanes) - 1)]
         pipe = cuda_row_pipeline(lambda tt: {"y": configs.chain_y(graph, tt), "rowsum": configs.chain_rowsum(graph, tt),
                                              "rowsoftmax": configs.chain_rowsoftmax(graph, tt)},
                                  pinned, list(pinned), lanes, n_chunks=args.e2e_chunks)
@@ -502,7 +503,7 @@ def main() -> None:
             extra_bridge.close()
         e2e = {"value": world * total_bytes * n_e2e / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "steps": n_e2e, "ms_per_step": 1e3 * dt / n_e2e,
-               "api": f"sharded.cuda_row_pipeline(...).run(outs): {args.e2e_chunks} row chunks over 3 bridges",
+               "api": f"sharded.cuda_row_pipeline(...).run(outs): {args.e2e_chunks} row chunks over {len(lanes)} bridges",
                "single_call": {"value": world * total_bytes * n_e2e / dt_single / 1e9, "ms_per_step": 1e3 * dt_single / n_e2e,
                                "api": "realize_cuda(root, out=pinned) per root, leaves uploaded once per step"}}
 

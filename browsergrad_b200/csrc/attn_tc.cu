@@ -539,20 +539,31 @@ __global__ void attn_prep_kernel(PrepView src, void* dst_a, void* dst_b, int B, 
   }
 }
 
-// Same encoding for an fp32 source whose rows of D = 64 values are contiguous (strides over b, h, s are free
-// multiples of four), four elements per thread step: Q and K of fp32 graphs and of autocast graphs whose casts
-// were folded into this pass.
-__global__ void attn_prep_rows_f32_kernel(const float* __restrict__ src, long long sb, long long sh, long long ss, void* dst_a,
-                                          void* dst_b, int H, int S, long long n4, int kind) {
+// Same encoding for an fp32 or fp64 source whose rows of D = 64 values are contiguous (strides over b, h, s are
+// free multiples of four), four elements per thread step: Q and K of fp32 / fp64 graphs and of autocast graphs
+// whose casts were folded into this pass.
+template <typename T>
+__global__ void attn_prep_rows_kernel(const T* __restrict__ src, long long sb, long long sh, long long ss, void* dst_a,
+                                      void* dst_b, int H, int S, long long n4, int kind) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
-    const long long row = i >> 4;              // 16 float4 groups per row of 64
+    const long long row = i >> 4;              // 16 groups of four per row of 64
     const int c4 = (int)(i & 15);
     const int sidx = (int)(row % S);
     const long long bh = row / S;
     const int h = (int)(bh % H);
     const long long b = bh / H;
-    const float4 v = __ldcs(reinterpret_cast<const float4*>(src + b * sb + h * sh + sidx * ss) + c4);
-    const float x[4] = {v.x, v.y, v.z, v.w};
+    const T* p = src + b * sb + h * sh + sidx * ss + c4 * 4;
+    double xd[4];
+    if (sizeof(T) == 8) {
+      const double2 v0 = __ldcs(reinterpret_cast<const double2*>(p)), v1 = __ldcs(reinterpret_cast<const double2*>(p) + 1);
+      xd[0] = v0.x; xd[1] = v0.y; xd[2] = v1.x; xd[3] = v1.y;
+    } else {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(p));
+      xd[0] = v.x; xd[1] = v.y; xd[2] = v.z; xd[3] = v.w;
+    }
+    float x[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) x[e] = (float)xd[e];
     if (kind == PREP_TF32) {
       float hi[4], lo[4];
 #pragma unroll
@@ -560,7 +571,8 @@ __global__ void attn_prep_rows_f32_kernel(const float* __restrict__ src, long lo
         uint32_t hb;
         asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x[e]));
         hi[e] = __uint_as_float(hb);
-        lo[e] = __fadd_rn(x[e], -hi[e]);
+        // for fp64 sources lo also carries the bits fp32 dropped
+        lo[e] = sizeof(T) == 8 ? (float)(xd[e] - (double)hi[e]) : __fadd_rn(x[e], -hi[e]);
       }
       reinterpret_cast<float4*>(dst_a)[i] = make_float4(hi[0], hi[1], hi[2], hi[3]);
       reinterpret_cast<float4*>(dst_b)[i] = make_float4(lo[0], lo[1], lo[2], lo[3]);
@@ -732,15 +744,21 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
       continue;
     }
     const bool rows_contig = ops[i]->stride[3] == 1 && a.D == 64;
-    const bool rows_vec = rows_contig && aligned && ops[i]->dtype == BG_F32 && (ops[i]->stride[0] & 3) == 0 &&
+    // an fp64 source only ever feeds the 3xTF32 encoding here (16-bit operands never derive from fp64 values)
+    const bool rows_vec = rows_contig && (ops[i]->dtype == BG_F32 || (ops[i]->dtype == BG_F64 && tf32)) &&
+                          (reinterpret_cast<uintptr_t>(ops[i]->ptr) & 31) == 0 && (ops[i]->stride[0] & 3) == 0 &&
                           (ops[i]->stride[1] & 3) == 0 && (ops[i]->stride[2] & 3) == 0;
     if (i == 2 && rows_contig) {
       attn_prep_vt_kernel<<<dim3((unsigned)((seq[i] + 63) / 64), (unsigned)(a.B * a.H)), 256, 0, s>>>(
           ops[i]->ptr, ops[i]->dtype, ops[i]->stride[0], ops[i]->stride[1], ops[i]->stride[2], scratch[4], scratch[5], a.H, seq[i], kind);
+    } else if (i < 2 && rows_vec && ops[i]->dtype == BG_F32) {
+      attn_prep_rows_kernel<float><<<prep_grid(n / 4), 256, 0, s>>>(reinterpret_cast<const float*>(ops[i]->ptr), ops[i]->stride[0],
+                                                                   ops[i]->stride[1], ops[i]->stride[2], scratch[2 * i],
+                                                                   scratch[2 * i + 1], a.H, seq[i], n / 4, kind);
     } else if (i < 2 && rows_vec) {
-      attn_prep_rows_f32_kernel<<<prep_grid(n / 4), 256, 0, s>>>(reinterpret_cast<const float*>(ops[i]->ptr), ops[i]->stride[0],
-                                                                ops[i]->stride[1], ops[i]->stride[2], scratch[2 * i], scratch[2 * i + 1],
-                                                                a.H, seq[i], n / 4, kind);
+      attn_prep_rows_kernel<double><<<prep_grid(n / 4), 256, 0, s>>>(reinterpret_cast<const double*>(ops[i]->ptr), ops[i]->stride[0],
+                                                                    ops[i]->stride[1], ops[i]->stride[2], scratch[2 * i],
+                                                                    scratch[2 * i + 1], a.H, seq[i], n / 4, kind);
     } else {
       PrepView v{ops[i]->ptr, ops[i]->dtype, {ops[i]->stride[0], ops[i]->stride[1], ops[i]->stride[2], ops[i]->stride[3]}};
       attn_prep_kernel<<<prep_grid(n), 256, 0, s>>>(v, scratch[2 * i], scratch[2 * i + 1], a.B, a.H, seq[i], a.D, i == 2, kind);

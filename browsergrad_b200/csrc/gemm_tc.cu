@@ -32,12 +32,14 @@ using namespace tc;
 
 constexpr int BM = 128;
 constexpr int kStageRowBytes = 128;          // one swizzle row: 64 x 16-bit or 32 x tf32
+constexpr int kTf32ChunkBlocks = 16;         // 3xTF32: K blocks (of 32 floats) summed in tensor memory before a register add
 constexpr int kTcThreads = 320;          // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per TMEM lane quarter)
 
 struct TcParams {
   int M, N;
   int num_k_blocks;     // K blocks of 128 bytes per pass
   int passes;           // 1, or 3 for the hi/lo split
+  int chunk_blocks;     // K blocks accumulated in tensor memory before the epilogue warps take the partial sum over
   int elems_per_block;  // K elements per 128-byte block (64 or 32)
   void* C;
   int c_dtype;
@@ -194,6 +196,40 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
   }
 }
 
+// The tensor core adds into its fp32 accumulator with truncation, so a long K loop drifts by about
+// 2^-24 of the accumulated magnitude per instruction (2e-5 relative at K = 8192 with three passes).  The
+// 3xTF32 kernels therefore accumulate at most `chunk_blocks` K blocks in tensor memory; the epilogue warps
+// add each partial sum into registers with round-to-nearest fp32 adds (one warp owns NC x 32 columns of 32
+// rows) and apply the epilogue to the total.  `use` counts accumulator buffers consumed by this CTA.
+template <int NC>
+__device__ __forceinline__ bool drain_chunks(const TcParams& p, uint64_t* acc_full, uint32_t tmem_lane_base, int buf_cols, int first_chunk_col,
+                                             int n_chunks, int& use, volatile int* abort_flag, float (&acc)[NC][32], int lane,
+                                             uint32_t acc_empty_addr0, bool remote_arrive, uint64_t* acc_empty_local) {
+#pragma unroll
+  for (int c = 0; c < NC; ++c)
+#pragma unroll
+    for (int j = 0; j < 32; ++j) acc[c][j] = 0.f;
+  for (int ch = 0; ch < n_chunks; ++ch, ++use) {
+    const int buf = use & 1;
+    if (!mbar_wait(&acc_full[buf], (uint32_t)(use >> 1) & 1u, abort_flag)) return false;
+    tc_fence_after();
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      uint32_t r[32];
+      tmem_ld32(tmem_lane_base + (uint32_t)(buf * buf_cols + (first_chunk_col + c) * 32), r);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[c][j] = __fadd_rn(acc[c][j], __uint_as_float(r[j]));
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) {
+      if (remote_arrive) mbar_arrive_at(acc_empty_addr0 + (uint32_t)(buf * 8));
+      else mbar_arrive(&acc_empty_local[buf]);
+    }
+  }
+  return true;
+}
+
 // Persistent kernel: each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The accumulator is
 // double-buffered in tensor memory, so the epilogue of tile t overlaps the MMAs of tile t + 1.
 template <int BN, bool TF32>
@@ -243,7 +279,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  const int iters_per_tile = p.num_k_blocks * p.passes;
+  const int n_chunks = p.num_k_blocks > 0 ? (p.num_k_blocks + p.chunk_blocks - 1) / p.chunk_blocks : 0;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -252,77 +288,100 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m0, n0;
         tile_origin(tile, m0, n0);
-        for (int k = 0; k < iters_per_tile; ++k, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (uint32_t)(it / kStages) & 1u;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-          const int pass = k / p.num_k_blocks, kb = k - pass * p.num_k_blocks;
-          // passes of the split product: lo.hi, hi.lo, hi.hi (a single pass uses map 0 of each operand)
-          const CUtensorMap* ma = (p.passes == 3 && pass == 0) ? &tmA1 : &tmA0;
-          const CUtensorMap* mb = (p.passes == 3 && pass == 1) ? &tmB1 : &tmB0;
-          unsigned char* sa = smem + s * kStageBytes;
-          mbar_expect_tx(&full_bar[s], kStageBytes);
-          tma_load_2d(ma, sa, &full_bar[s], kb * p.elems_per_block, m0);
-          tma_load_2d(mb, sa + kABytes, &full_bar[s], kb * p.elems_per_block, n0);
+        for (int ch = 0; ch < n_chunks && ok; ++ch) {
+          const int kb0 = ch * p.chunk_blocks, kb1 = min(kb0 + p.chunk_blocks, p.num_k_blocks);
+          for (int pass = 0; pass < p.passes && ok; ++pass) {
+            // passes of the split product: lo.hi, hi.lo, hi.hi (a single pass uses map 0 of each operand)
+            const CUtensorMap* ma = (p.passes == 3 && pass == 0) ? &tmA1 : &tmA0;
+            const CUtensorMap* mb = (p.passes == 3 && pass == 1) ? &tmB1 : &tmB0;
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+              const int s = it % kStages;
+              const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+              if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+              unsigned char* sa = smem + s * kStageBytes;
+              mbar_expect_tx(&full_bar[s], kStageBytes);
+              tma_load_2d(ma, sa, &full_bar[s], kb * p.elems_per_block, m0);
+              tma_load_2d(mb, sa + kABytes, &full_bar[s], kb * p.elems_per_block, n0);
+            }
+          }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      int it = 0, t = 0;
+      int it = 0, use = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
-        const int buf = t & 1;
-        if (!mbar_wait(&acc_empty[buf], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN);
-        for (int k = 0; k < iters_per_tile; ++k, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (uint32_t)(it / kStages) & 1u;
-          if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int ch = 0; ch < n_chunks && ok; ++ch, ++use) {
+          const int buf = use & 1;
+          if (!mbar_wait(&acc_empty[buf], ((uint32_t)(use >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + s * kStageBytes);
-          const uint64_t da = make_kmajor_sw128_desc(sa), db = make_kmajor_sw128_desc(sa + kABytes);
+          const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN);
+          const int kb0 = ch * p.chunk_blocks, kb1 = min(kb0 + p.chunk_blocks, p.num_k_blocks);
+          uint32_t accumulate = 0;
+          for (int k = 0; k < (kb1 - kb0) * p.passes; ++k, ++it) {
+            const int s = it % kStages;
+            const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+            if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + s * kStageBytes);
+            const uint64_t da = make_kmajor_sw128_desc(sa), db = make_kmajor_sw128_desc(sa + kABytes);
 #pragma unroll
-          for (int kk = 0; kk < kStageRowBytes / 32; ++kk) {
-            // each instruction consumes 32 bytes of K; the start address advances inside the swizzle row
-            umma<TF32>(tmem_acc, da + (uint64_t)(kk * 32 >> 4), db + (uint64_t)(kk * 32 >> 4), p.idesc, (k > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < kStageRowBytes / 32; ++kk) {
+              // each instruction consumes 32 bytes of K; the start address advances inside the swizzle row
+              umma<TF32>(tmem_acc, da + (uint64_t)(kk * 32 >> 4), db + (uint64_t)(kk * 32 >> 4), p.idesc, accumulate);
+              accumulate = 1;
+            }
+            umma_commit(&empty_bar[s]);
           }
-          umma_commit(&empty_bar[s]);
+          if (ok) umma_commit(&acc_full[buf]);
         }
-        if (ok) umma_commit(&acc_full[buf]);
       }
     }
   } else {
     // epilogue: warp w may read TMEM lanes 32*(w%4) .. +31; the two warps of a quarter split the columns
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
-    int t = 0;
+    int use = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int m0, n0;
       tile_origin(tile, m0, n0);
-      const int buf = t & 1;
       const int row = m0 + q * 32 + lane;
-      if (iters_per_tile > 0) ok = mbar_wait(&acc_full[buf], (uint32_t)(t >> 1) & 1u, abort_flag);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(q * 32) << 16);
-#pragma unroll 1
-      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
-        uint32_t r[32];
-        if (iters_per_tile > 0) tmem_ld32(tmem_acc + (uint32_t)(c * 32), r);
-        else {
+      const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+      if (TF32) {
+        constexpr int NC = BN / 64;
+        float acc[NC][32];
+        ok = drain_chunks<NC>(p, acc_full, lane_base, BN, half * NC, n_chunks, use, abort_flag, acc, lane, 0u, false, acc_empty);
+        if (!ok) break;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = 0;
+        for (int c = 0; c < NC; ++c) {
+          const int col0 = n0 + (half * NC + c) * 32;
+          if (row < p.M && col0 < p.N) epilogue_chunk(p, reinterpret_cast<const uint32_t*>(acc[c]), row, col0);
         }
-        const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) epilogue_chunk(p, r, row, col0);
+      } else {
+        const int buf = use & 1;
+        if (n_chunks > 0) ok = mbar_wait(&acc_full[buf], (uint32_t)(use >> 1) & 1u, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_acc = lane_base + (uint32_t)(buf * BN);
+#pragma unroll 1
+        for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
+          uint32_t r[32];
+          if (n_chunks > 0) tmem_ld32(tmem_acc + (uint32_t)(c * 32), r);
+          else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0;
+          }
+          const int col0 = n0 + c * 32;
+          if (row < p.M && col0 < p.N) epilogue_chunk(p, r, row, col0);
+        }
+        // the buffer's values are in registers / memory: hand it back to the MMA warp
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0 && n_chunks > 0) mbar_arrive(&acc_empty[buf]);
+        use += n_chunks;
       }
-      // the buffer's values are in registers / memory: hand it back to the MMA warp
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
   }
   tc_fence_before();
@@ -405,7 +464,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
   cluster_sync_all();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  const int iters_per_tile = p.num_k_blocks * p.passes;
+  const int n_chunks = p.num_k_blocks > 0 ? (p.num_k_blocks + p.chunk_blocks - 1) / p.chunk_blocks : 0;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -414,79 +473,104 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         int m0, n0;
         tile_origin(tile, m0, n0);
-        for (int k = 0; k < iters_per_tile; ++k, ++it) {
-          const int s = it % kPairStages;
-          const uint32_t ph = (uint32_t)(it / kPairStages) & 1u;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-          const int pass = k / p.num_k_blocks, kb = k - pass * p.num_k_blocks;
-          const CUtensorMap* ma = (p.passes == 3 && pass == 0) ? &tmA1 : &tmA0;
-          const CUtensorMap* mb = (p.passes == 3 && pass == 1) ? &tmB1 : &tmB0;
-          unsigned char* sa = smem + s * kStageBytes;
-          const uint32_t full0 = map_to_cta(smem_u32(&full_bar[s]), 0);
-          mbar_expect_tx_at(full0, kStageBytes);
-          tma_load_2d_pair(ma, sa, full0, kb * p.elems_per_block, m0 + (int)rank * kHalf);
-          tma_load_2d_pair(mb, sa + kABytes, full0, kb * p.elems_per_block, n0 + (int)rank * kHalf);
+        for (int ch = 0; ch < n_chunks && ok; ++ch) {
+          const int kb0 = ch * p.chunk_blocks, kb1 = min(kb0 + p.chunk_blocks, p.num_k_blocks);
+          for (int pass = 0; pass < p.passes && ok; ++pass) {
+            const CUtensorMap* ma = (p.passes == 3 && pass == 0) ? &tmA1 : &tmA0;
+            const CUtensorMap* mb = (p.passes == 3 && pass == 1) ? &tmB1 : &tmB0;
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+              const int s = it % kPairStages;
+              const uint32_t ph = (uint32_t)(it / kPairStages) & 1u;
+              if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+              unsigned char* sa = smem + s * kStageBytes;
+              const uint32_t full0 = map_to_cta(smem_u32(&full_bar[s]), 0);
+              mbar_expect_tx_at(full0, kStageBytes);
+              tma_load_2d_pair(ma, sa, full0, kb * p.elems_per_block, m0 + (int)rank * kHalf);
+              tma_load_2d_pair(mb, sa + kABytes, full0, kb * p.elems_per_block, n0 + (int)rank * kHalf);
+            }
+          }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
-      int it = 0, t = 0;
+      int it = 0, use = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++t) {
-        const int buf = t & 1;
-        if (!mbar_wait(&acc_empty[buf], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * kTile);
-        for (int k = 0; k < iters_per_tile; ++k, ++it) {
-          const int s = it % kPairStages;
-          const uint32_t ph = (uint32_t)(it / kPairStages) & 1u;
-          if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        for (int ch = 0; ch < n_chunks && ok; ++ch, ++use) {
+          const int buf = use & 1;
+          if (!mbar_wait(&acc_empty[buf], ((uint32_t)(use >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + s * kStageBytes);
-          const uint64_t da = make_kmajor_sw128_desc(sa), db = make_kmajor_sw128_desc(sa + kABytes);
+          const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * kTile);
+          const int kb0 = ch * p.chunk_blocks, kb1 = min(kb0 + p.chunk_blocks, p.num_k_blocks);
+          uint32_t accumulate = 0;
+          for (int k = 0; k < (kb1 - kb0) * p.passes; ++k, ++it) {
+            const int s = it % kPairStages;
+            const uint32_t ph = (uint32_t)(it / kPairStages) & 1u;
+            if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + s * kStageBytes);
+            const uint64_t da = make_kmajor_sw128_desc(sa), db = make_kmajor_sw128_desc(sa + kABytes);
 #pragma unroll
-          for (int kk = 0; kk < kStageRowBytes / 32; ++kk)
-            umma_pair<TF32>(tmem_acc, da + (uint64_t)(kk * 32 >> 4), db + (uint64_t)(kk * 32 >> 4), p.idesc, (k > 0 || kk > 0) ? 1u : 0u);
-          const uint32_t e = smem_u32(&empty_bar[s]);
-          umma_commit_pair(map_to_cta(e, 0));
-          umma_commit_pair(map_to_cta(e, 1));
-        }
-        if (ok) {
-          const uint32_t f = smem_u32(&acc_full[buf]);
-          umma_commit_pair(map_to_cta(f, 0));
-          umma_commit_pair(map_to_cta(f, 1));
+            for (int kk = 0; kk < kStageRowBytes / 32; ++kk) {
+              umma_pair<TF32>(tmem_acc, da + (uint64_t)(kk * 32 >> 4), db + (uint64_t)(kk * 32 >> 4), p.idesc, accumulate);
+              accumulate = 1;
+            }
+            const uint32_t e = smem_u32(&empty_bar[s]);
+            umma_commit_pair(map_to_cta(e, 0));
+            umma_commit_pair(map_to_cta(e, 1));
+          }
+          if (ok) {
+            const uint32_t f = smem_u32(&acc_full[buf]);
+            umma_commit_pair(map_to_cta(f, 0));
+            umma_commit_pair(map_to_cta(f, 1));
+          }
         }
       }
     }
   } else {
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
-    int t = 0;
+    int use = 0;
     bool ok = true;
-    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++t) {
+    const uint32_t acc_empty0 = map_to_cta(smem_u32(&acc_empty[0]), 0);   // the barriers live in CTA 0, 8 bytes apart
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
       int m0, n0;
       tile_origin(tile, m0, n0);
-      const int buf = t & 1;
       const int row = m0 + (int)rank * kHalf + q * 32 + lane;
-      if (iters_per_tile > 0) ok = mbar_wait(&acc_full[buf], (uint32_t)(t >> 1) & 1u, abort_flag);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * kTile) + ((uint32_t)(q * 32) << 16);
-#pragma unroll 1
-      for (int c = half * (kTile / 64); c < (half + 1) * (kTile / 64); ++c) {
-        uint32_t r[32];
-        if (iters_per_tile > 0) tmem_ld32(tmem_acc + (uint32_t)(c * 32), r);
-        else {
+      const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+      if (TF32) {
+        constexpr int NC = kTile / 64;
+        float acc[NC][32];
+        ok = drain_chunks<NC>(p, acc_full, lane_base, kTile, half * NC, n_chunks, use, abort_flag, acc, lane, acc_empty0, true, nullptr);
+        if (!ok) break;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = 0;
+        for (int c = 0; c < NC; ++c) {
+          const int col0 = n0 + (half * NC + c) * 32;
+          if (row < p.M && col0 < p.N) epilogue_chunk(p, reinterpret_cast<const uint32_t*>(acc[c]), row, col0);
         }
-        const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) epilogue_chunk(p, r, row, col0);
+      } else {
+        const int buf = use & 1;
+        if (n_chunks > 0) ok = mbar_wait(&acc_full[buf], (uint32_t)(use >> 1) & 1u, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_acc = lane_base + (uint32_t)(buf * kTile);
+#pragma unroll 1
+        for (int c = half * (kTile / 64); c < (half + 1) * (kTile / 64); ++c) {
+          uint32_t r[32];
+          if (n_chunks > 0) tmem_ld32(tmem_acc + (uint32_t)(c * 32), r);
+          else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0;
+          }
+          const int col0 = n0 + c * 32;
+          if (row < p.M && col0 < p.N) epilogue_chunk(p, r, row, col0);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0 && n_chunks > 0) mbar_arrive_at(acc_empty0 + (uint32_t)(buf * 8));
+        use += n_chunks;
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_at(map_to_cta(smem_u32(&acc_empty[buf]), 0));
     }
   }
   tc_fence_before();
@@ -574,6 +658,7 @@ cudaError_t launch_variant(const TcGemm& g, int* status, cudaStream_t s) {
   p.elems_per_block = kStageRowBytes / es;
   p.num_k_blocks = (int)((g.K + p.elems_per_block - 1) / p.elems_per_block);
   p.passes = TF32 ? 3 : 1;
+  p.chunk_blocks = TF32 ? (p.num_k_blocks < kTf32ChunkBlocks ? (p.num_k_blocks > 0 ? p.num_k_blocks : 1) : kTf32ChunkBlocks) : (p.num_k_blocks > 0 ? p.num_k_blocks : 1);
   p.C = g.C;
   p.c_dtype = g.c_dtype;
   p.bias = g.bias;
@@ -618,6 +703,7 @@ cudaError_t launch_pair(const TcGemm& g, int* status, cudaStream_t s, bool* laun
   p.elems_per_block = kStageRowBytes / es;
   p.num_k_blocks = (int)((g.K + p.elems_per_block - 1) / p.elems_per_block);
   p.passes = TF32 ? 3 : 1;
+  p.chunk_blocks = TF32 ? (p.num_k_blocks < kTf32ChunkBlocks ? (p.num_k_blocks > 0 ? p.num_k_blocks : 1) : kTf32ChunkBlocks) : (p.num_k_blocks > 0 ? p.num_k_blocks : 1);
   p.C = g.C;
   p.c_dtype = g.c_dtype;
   p.bias = g.bias;

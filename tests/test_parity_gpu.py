@@ -131,3 +131,24 @@ def test_cta_pair_gemm_matches_oracle(bridge, name):
     check(case, got, want, name + " (CTA pairs)")
     # same products, same accumulation order per output element: the two tilings agree to the bit
     assert got.tobytes() == single.tobytes()
+
+
+def test_autocast_attention_is_one_unit_and_keeps_mask_classes_with_the_handle(bridge):
+    """The fp32 -> 16-bit casts of Q, K, V are folded into the operand staging of the fused kernel, and the
+    mask tile classes computed for a mask bound by handle live exactly as long as that handle."""
+    from browsergrad_b200 import release_resident_leaves
+    case = CASES["c4_attn_mask_bf16"]
+    t, store, _ = build_case(case)
+    want = oracle_value(t, store)
+    base = bridge.resourceSnapshot()["currentBytes"]
+    first = realize_cuda(t, bridge, resident_leaves=True)
+    trace = bridge.last_plan_trace()
+    assert trace == ["attention_tc+mask[bfloat16]"], trace
+    held = bridge.resourceSnapshot()["currentBytes"]
+    second = realize_cuda(t, bridge, resident_leaves=True)       # classes come from the cache this time
+    assert bridge.resourceSnapshot()["currentBytes"] == held
+    check(case, first, want, "autocast attention")
+    assert first.tobytes() == second.tobytes()
+    release_resident_leaves(bridge)
+    assert bridge.resourceSnapshot()["currentBytes"] == base
+    assert bridge.aliveHandleCount() == 0
