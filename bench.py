@@ -351,7 +351,7 @@ def main() -> None:
                     + ", ".join(EXTRA_NAMES))
     ap.add_argument("--attn-batch", type=int, default=16)
     ap.add_argument("--e2e-chunks", type=int, default=16)
-    ap.add_argument("--e2e-lanes", type=int, default=3)
+    ap.add_argument("--e2e-lanes", type=int, default=4)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
