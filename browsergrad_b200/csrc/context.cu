@@ -217,6 +217,29 @@ void mask_classes_drop(bg_context* ctx, const void* ptr) {
   ctx->mask_classes.erase(it);
 }
 
+float* split_planes_for(bg_context* ctx, const void* ptr, int64_t n, int dtype, bool* fresh) {
+  *fresh = false;
+  auto it = ctx->split_planes.find(ptr);
+  if (it != ctx->split_planes.end()) {
+    if (it->second.n == n && it->second.dtype == dtype) return it->second.buf;
+    dev_free(ctx, it->second.buf, 2 * it->second.n * 4);
+    ctx->split_planes.erase(it);
+  }
+  if (ctx->split_planes.size() >= 4096) return nullptr;
+  void* buf = nullptr;
+  if (dev_alloc(ctx, 2 * n * 4, &buf) != BG_OK) return nullptr;
+  ctx->split_planes[ptr] = {reinterpret_cast<float*>(buf), n, dtype};
+  *fresh = true;
+  return reinterpret_cast<float*>(buf);
+}
+
+void split_planes_drop(bg_context* ctx, const void* ptr) {
+  auto it = ctx->split_planes.find(ptr);
+  if (it == ctx->split_planes.end()) return;
+  dev_free(ctx, it->second.buf, 2 * it->second.n * 4);
+  ctx->split_planes.erase(it);
+}
+
 static int64_t numel_of(const int64_t* shape, int rank) {
   int64_t n = 1;
   for (int i = 0; i < rank; ++i) n *= shape[i];
@@ -275,6 +298,8 @@ int bg_destroy(bg_context* ctx) {
   ctx->handles.clear();
   for (auto& kv : ctx->mask_classes) cudaFreeAsync(kv.second.buf, ctx->stream);
   ctx->mask_classes.clear();
+  for (auto& kv : ctx->split_planes) cudaFreeAsync(kv.second.buf, ctx->stream);
+  ctx->split_planes.clear();
   ctx->plan_cache.clear();
   for (auto& pe : ctx->pending_events) {
     cudaEventDestroy(pe.second.first);
@@ -349,6 +374,7 @@ int bg_release(bg_context* ctx, bg_handle h) {
   cudaSetDevice(ctx->device);
   uniform_flag_drop(ctx, it->second.ptr);
   mask_classes_drop(ctx, it->second.ptr);
+  split_planes_drop(ctx, it->second.ptr);
   dev_free(ctx, it->second.ptr, it->second.bytes);
   ctx->handles.erase(it);
   return BG_OK;

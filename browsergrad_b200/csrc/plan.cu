@@ -255,7 +255,12 @@ class Compiler {
     int order_key;
     std::vector<int> dep_nodes;   // nodes whose storage must be ready
     std::vector<int> out_nodes;   // nodes this unit makes ready
+    std::vector<int> dep_punits;  // units whose scratch output this unit reads (index into punits_)
   };
+  // hi / lo planes of a 3xTF32 operand, produced once per plan for every tensor-core GEMM that reads the same
+  // dense operand: (slot, byte offset, elements) -> (hi slot, lo slot, producing unit)
+  struct SplitMemo { int hi, lo, punit; };
+  std::map<std::tuple<int, int64_t, int64_t>, SplitMemo> split_memo_;
   std::vector<PUnit> punits_;
   std::vector<int> producer_;     // node -> punit index (-1: always ready)
 
@@ -2100,10 +2105,27 @@ void Compiler::emit_matmul(int n, int key) {
         tb.dtype = bv.dtype; tb.rank = 2; tb.shape[0] = N; tb.shape[1] = K; tb.stride[0] = gp.b.col_stride; tb.stride[1] = gp.b.row_stride;
       }
       int a_hi = -1, a_lo = -1, b_hi = -1, b_lo = -1;
+      bool a_shared = false;
+      // a weight matrix bound by handle keeps its hi / lo planes with the handle (see split_planes_for)
+      const bool b_leaf = mode == 1 && b_copy < 0 && cp_->slots[b_src].external;
       if (mode == 1) {
-        a_hi = new_slot(M * K * 4, false, -1); a_lo = new_slot(M * K * 4, false, -1);
-        b_hi = new_slot(N * K * 4, false, -1); b_lo = new_slot(N * K * 4, false, -1);
-        for (int sl : {a_hi, a_lo, b_hi, b_lo}) pu.u.writes.push_back(sl);
+        const auto a_key = std::make_tuple(a_src, a_off, M * K);
+        auto hit = a_copy < 0 ? split_memo_.find(a_key) : split_memo_.end();
+        if (hit != split_memo_.end()) {
+          // another GEMM of this plan already splits the same operand (q / k / v projections of one LayerNorm output)
+          a_hi = hit->second.hi; a_lo = hit->second.lo;
+          a_shared = true;
+          pu.dep_punits.push_back(hit->second.punit);
+          pu.u.reads.push_back(a_hi); pu.u.reads.push_back(a_lo);
+        } else {
+          a_hi = new_slot(M * K * 4, false, -1); a_lo = new_slot(M * K * 4, false, -1);
+          pu.u.writes.push_back(a_hi); pu.u.writes.push_back(a_lo);
+          if (a_copy < 0) split_memo_[a_key] = {a_hi, a_lo, (int)punits_.size()};
+        }
+        if (!b_leaf) {
+          b_hi = new_slot(N * K * 4, false, -1); b_lo = new_slot(N * K * 4, false, -1);
+          pu.u.writes.push_back(b_hi); pu.u.writes.push_back(b_lo);
+        }
       }
       const int a_dt = av.dtype, b_dt = bv.dtype, c_dt = t.dtype;
       auto epi = std::make_shared<TcEpilogue>();
@@ -2129,7 +2151,7 @@ void Compiler::emit_matmul(int n, int key) {
         if (ep.act == TC_ACT_GELU) epi_name += "+gelu";
         pu.out_nodes = {ep.final_node};
       }
-      pu.u.launches = 1 + (a_copy >= 0) + (b_copy >= 0) + (mode == 1 ? 2 : 0);
+      pu.u.launches = 1 + (a_copy >= 0) + (b_copy >= 0) + (mode == 1 ? (a_shared ? 0 : 1) + 1 : 0);
       pu.u.name = std::string(mode == 0 ? "gemm_tc" : "gemm_tc_3xtf32") + epi_name + "[" + dtype_name(t.dtype) + "]";
       cp_->uses_status = true;
       const int sc_slot = sc;
@@ -2153,11 +2175,24 @@ void Compiler::emit_matmul(int n, int key) {
         TcGemm g{};
         g.M = M; g.N = N; g.K = K;
         g.ab_dtype = ab;
+        void* tmp_planes = nullptr;     // hi / lo planes of a B operand that is neither a slot nor kept with a handle
         if (mode == 1) {
-          e = launch_tf32_split(pa, a_dt, (float*)r.ptr[a_hi], (float*)r.ptr[a_lo], M * K, st);
-          if (e == cudaSuccess) e = launch_tf32_split(pb, b_dt, (float*)r.ptr[b_hi], (float*)r.ptr[b_lo], N * K, st);
-          if (e != cudaSuccess) return cuda_fail(r.ctx, e, "tf32 split launch");
-          g.A = r.ptr[a_hi]; g.A_lo = r.ptr[a_lo]; g.B = r.ptr[b_hi]; g.B_lo = r.ptr[b_lo];
+          if (!a_shared) e = launch_tf32_split(pa, a_dt, (float*)r.ptr[a_hi], (float*)r.ptr[a_lo], M * K, st);
+          float* bh = b_leaf ? nullptr : (float*)r.ptr[b_hi];
+          float* bl = b_leaf ? nullptr : (float*)r.ptr[b_lo];
+          bool split_b = true;
+          if (b_leaf) {
+            bool fresh = false;
+            float* kept = r.from_handle[b_src] ? split_planes_for(r.ctx, pb, N * K, b_dt, &fresh) : nullptr;
+            if (kept) { bh = kept; bl = kept + N * K; split_b = fresh; }
+            else {
+              if (int rc = dev_alloc(r.ctx, 2 * N * K * 4, &tmp_planes)) return rc;
+              bh = reinterpret_cast<float*>(tmp_planes); bl = bh + N * K;
+            }
+          }
+          if (e == cudaSuccess && split_b) e = launch_tf32_split(pb, b_dt, bh, bl, N * K, st);
+          if (e != cudaSuccess) { if (tmp_planes) dev_free(r.ctx, tmp_planes, 2 * N * K * 4); return cuda_fail(r.ctx, e, "tf32 split launch"); }
+          g.A = r.ptr[a_hi]; g.A_lo = r.ptr[a_lo]; g.B = bh; g.B_lo = bl;
         } else {
           g.A = pa; g.B = pb;
         }
@@ -2171,6 +2206,7 @@ void Compiler::emit_matmul(int n, int key) {
         g.round_acc = epi->round_acc;
         g.wide = epi->wide;
         e = launch_gemm_tc(g, r.ctx->d_status, st);
+        if (tmp_planes) dev_free(r.ctx, tmp_planes, 2 * N * K * 4);    // stream-ordered: released after the GEMM has run
         return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "tensor-core gemm launch");
       };
       tc_unit_of_[n] = (int)punits_.size();
@@ -2352,6 +2388,7 @@ bool Compiler::try_lower() {
   nodes_.clear();
   copy_src_.clear();
   tc_epilogues_.clear();
+  split_memo_.clear();
   tc_unit_of_.clear();
   attn_plan_.clear();
   attn_absorbed_.clear();
@@ -2521,11 +2558,14 @@ void Compiler::schedule() {
   };
   std::vector<std::set<int>> deps(nu);
   std::vector<std::vector<int>> users(nu);
-  for (int u = 0; u < nu; ++u)
+  for (int u = 0; u < nu; ++u) {
     for (int n : punits_[u].dep_nodes) {
       int p = storage_unit(n);
       if (p >= 0 && p != u && deps[u].insert(p).second) users[p].push_back(u);
     }
+    for (int p : punits_[u].dep_punits)
+      if (p >= 0 && p != u && deps[u].insert(p).second) users[p].push_back(u);
+  }
   std::vector<int> indeg(nu);
   std::set<std::pair<int, int>> ready;
   for (int u = 0; u < nu; ++u) {

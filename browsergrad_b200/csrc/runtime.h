@@ -57,6 +57,10 @@ struct bg_context {
   // change while the handle lives), keyed by device pointer; entries die with their handle
   struct MaskClasses { void* buf; int64_t bytes; int sq, sk, bkv, is_bool; };
   std::unordered_map<const void*, MaskClasses> mask_classes;
+  // hi / lo tf32 planes (2 x n floats, hi first) of fp32 / fp64 matrices bound by handle that feed 3xTF32 GEMMs as the
+  // B operand (weights): split once, kept until the handle is released
+  struct SplitPlanes { float* buf; int64_t n; int dtype; };
+  std::unordered_map<const void*, SplitPlanes> split_planes;
 };
 
 namespace bg {
@@ -81,6 +85,10 @@ void uniform_flag_drop(bg_context* ctx, const void* ptr);
 // when it was just allocated and still has to be computed.  Returns nullptr when the allocation fails.
 void* mask_classes_for(bg_context* ctx, const void* ptr, int64_t bytes, int sq, int sk, int bkv, int is_bool, bool* fresh);
 void mask_classes_drop(bg_context* ctx, const void* ptr);
+// hi / lo planes kept for the handle-backed matrix at `ptr` (hi at the returned pointer, lo n floats later); *fresh is
+// set when they were just allocated and still have to be computed.  nullptr when the allocation fails.
+float* split_planes_for(bg_context* ctx, const void* ptr, int64_t n, int dtype, bool* fresh);
+void split_planes_drop(bg_context* ctx, const void* ptr);
 
 int run_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs, int n_inputs, void* out_host,
              size_t out_nbytes, bg_handle* out_handle);
