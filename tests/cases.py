@@ -169,6 +169,9 @@ CASES: Dict[str, Case] = {
     "c3_tc_bf16": Case(lambda: configs.linear_inputs(256, 384, 320),
                        lambda api, t, raw: configs.linear_gelu(api, t, "bfloat16"), rtol=2e-2,
                        reference_has_it=False),
+    # K = 1100: three accumulation chunks (16 + 16 + 3 blocks of 32) in the 3xTF32 kernels
+    "c3_tc_f32_long_k": Case(lambda: configs.linear_inputs(264, 272, 1100),
+                             lambda api, t, raw: configs.linear_gelu(api, t, "")),
     "c3_tc_ragged": Case(lambda: configs.linear_inputs(300, 264, 296),
                          lambda api, t, raw: api.linear(t["x"], t["w"], t["bias"])),
     "c3_tc_relu": Case(lambda: configs.linear_inputs(300, 264, 296),

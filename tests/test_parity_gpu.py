@@ -116,7 +116,8 @@ def test_sdpa_runs_as_one_fused_attention_kernel(bridge, name, expect):
     check(case, composed, want, name + " (composed)")
 
 
-@pytest.mark.parametrize("name", ["c3_tc_f32", "c3_tc_f16", "c3_tc_bf16", "c3_tc_ragged", "c3_tc_relu", "c3_tc_rowmajor_b"])
+@pytest.mark.parametrize("name", ["c3_tc_f32", "c3_tc_f16", "c3_tc_bf16", "c3_tc_ragged", "c3_tc_relu", "c3_tc_rowmajor_b",
+                                  "c3_tc_f32_long_k"])
 def test_cta_pair_gemm_matches_oracle(bridge, name):
     """The two-CTA (cta_group::2) 256 x 256 tile kernel, forced on shapes with ragged edges in M, N and K."""
     case = CASES[name]
@@ -152,3 +153,51 @@ def test_autocast_attention_is_one_unit_and_keeps_mask_classes_with_the_handle(b
     release_resident_leaves(bridge)
     assert bridge.resourceSnapshot()["currentBytes"] == base
     assert bridge.aliveHandleCount() == 0
+
+
+def test_row_pipeline_equals_one_realization(bridge):
+    """Row chunks streamed over three bridges of the device give the rows of one whole realization."""
+    from browsergrad_b200 import CudaBridge, configs, graph
+    from browsergrad_b200.sharded import cuda_row_pipeline
+    arrays = configs.chain_inputs(1500, 1028)
+    store = graph.BufferStore()
+    t = {k: graph.from_numpy(v, store) for k, v in arrays.items()}
+
+    def build(tt):
+        return {"y": configs.chain_y(graph, tt), "rowsum": configs.chain_rowsum(graph, tt),
+                "rowsoftmax": configs.chain_rowsoftmax(graph, tt)}
+    whole = {name: realize_cuda(root, bridge) for name, root in build(t).items()}
+    lanes = [bridge, CudaBridge(0), CudaBridge(0)]
+    try:
+        pipe = cuda_row_pipeline(build, arrays, list(arrays), lanes, n_chunks=7)
+        outs = {name: np.empty(shape, dtype) for name, (shape, dtype) in pipe.output_shapes().items()}
+        for _ in range(2):
+            pipe.run(outs)
+            for name in whole:
+                if name == "rowsum":      # small chunks take the generic row kernel: another summation order
+                    np.testing.assert_allclose(outs[name], whole[name], rtol=1e-6)
+                else:
+                    assert outs[name].tobytes() == whole[name].tobytes(), name
+        for lane in lanes:
+            assert lane.aliveHandleCount() == 0
+    finally:
+        for lane in lanes[1:]:
+            lane.close()
+
+
+def test_weight_planes_live_and_die_with_their_handle(bridge):
+    """A 3xTF32 Linear with resident leaves keeps the hi / lo planes of its weight with the weight's handle:
+    the second realization allocates nothing new, releasing the leaves returns every byte."""
+    from browsergrad_b200 import release_resident_leaves
+    case = CASES["c3_tc_f32"]
+    t, store, _ = build_case(case)
+    want = oracle_value(t, store)
+    base = bridge.resourceSnapshot()["currentBytes"]
+    first = realize_cuda(t, bridge, resident_leaves=True)
+    held = bridge.resourceSnapshot()["currentBytes"]
+    second = realize_cuda(t, bridge, resident_leaves=True)
+    assert bridge.resourceSnapshot()["currentBytes"] == held
+    check(case, first, want, "resident linear")
+    assert first.tobytes() == second.tobytes()
+    release_resident_leaves(bridge)
+    assert bridge.resourceSnapshot()["currentBytes"] == base
