@@ -517,6 +517,33 @@ def main() -> None:
             extra = extra_measurements(bridge, torch, stream, peaks, max(3, min(args.steps, 10)))
         except Exception as exc:   # the headline line must survive a failure in the extras
             extra = {"error": repr(exc)}
+    elif world > 1 and not args.no_extra:
+        # the batch-sharded configurations on every rank (its own shard of the same size): one GPU's shard of the
+        # GPT decoder, the causal attention config and the largest bf16 Linear; aggregate = N x work / slowest rank
+        table.release_all()
+        mine, failure, vals = None, None, [float("nan")] * 4
+        try:
+            mine = extra_measurements(bridge, torch, stream, peaks, max(3, min(args.steps, 10)),
+                                      ("gpt", "attn_bf16", "attn_fp32", "gemm_bf16_8192"), args.attn_batch)
+            vals = [mine["gpt"][0]["plan_ms"], mine["attention"][0]["plan_ms"], mine["attention"][1]["plan_ms"],
+                    mine["gemm"][0]["kernel_ms"]]
+        except Exception as exc:   # every rank still joins the reduction below
+            failure = repr(exc)
+        times = torch.tensor(vals, device=f"cuda:{local}", dtype=torch.float64)
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)     # NaN from a failed rank propagates
+        gpt_ms, attn32_ms, attn16_ms, gemm_ms = (float(x) for x in times.tolist())
+        if mine is None or any(x != x for x in (gpt_ms, attn32_ms, attn16_ms, gemm_ms)):
+            extra = {"error": failure or "a rank failed its sharded extras"}
+        else:
+            extra = {"note": f"every rank runs its own shard; times are the slowest rank's, throughput is the sum over {world} ranks",
+                     "gpt": {"workload": mine["gpt"][0]["workload"], "ms_per_forward": gpt_ms,
+                             "tokens_per_s": world * 8 * 1024 / (gpt_ms * 1e-3)},
+                     "attention": [{"workload": mine["attention"][0]["workload"], "plan_ms": attn32_ms,
+                                    "tokens_per_s": world * args.attn_batch * 2048 / (attn32_ms * 1e-3)},
+                                   {"workload": mine["attention"][1]["workload"], "plan_ms": attn16_ms,
+                                    "tokens_per_s": world * args.attn_batch * 2048 / (attn16_ms * 1e-3)}],
+                     "gemm": {"workload": mine["gemm"][0]["workload"], "kernel_ms": gemm_ms,
+                              "tflops": world * 2.0 * 8192 ** 3 / (gemm_ms * 1e-3) / 1e12}}
 
     if rank == 0:
         line = {
