@@ -301,7 +301,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
     bool ok = true;
     int t = 0;
     auto fold_pv = [&](int tt, float alpha) -> bool {
-      if (!mbar_wait(&pv_full[tt & 1], (uint32_t)(tt >> 1) & 1u, abort_flag)) return false;
+      if (!__all_sync(0xffffffffu, mbar_wait(&pv_full[tt & 1], (uint32_t)(tt >> 1) & 1u, abort_flag))) return false;
       tc_fence_after();
       uint32_t r[32];
       tmem_ld32(tmem_pv + (uint32_t)((tt & 1) * kHeadDim + wg * HD) + lane_sel, r);
@@ -309,11 +309,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
       for (int i = 0; i < HD; ++i) o[i] = fmaf(o[i], alpha, __uint_as_float(r[i]));
       return true;
     };
-    for (int j = 0; j < n_kv && ok; ++j) {
+    for (int j = 0; j < n_kv; ++j) {
       const int tclass = cls ? cls[j] : (p.mask ? 3 : 1);
       if (tclass == 0) continue;
       const int buf = t & 1;
-      if (!mbar_wait(&s_full[buf], (uint32_t)(t >> 1) & 1u, abort_flag)) { ok = false; break; }
+      // a thread whose wait ran out keeps walking the tiles (its values no longer matter) so that the named
+      // barrier below still sees all 256 softmax threads once per tile
+      if (ok) ok = mbar_wait(&s_full[buf], (uint32_t)(t >> 1) & 1u, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);      // tensor-memory loads are warp-wide: keep the warp together
       tc_fence_after();
       const int k0 = j * BKV + wg * HK;             // first key of this thread's half
       float sv[HK];
@@ -394,10 +397,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
       // publish P in the K-major 128-byte-swizzled operand layout: row r_in_tile, 16-byte chunk c of
       // a 128-byte row lands at chunk (c ^ (row & 7))
       // with a single P buffer the previous tile's P.V must have consumed it first; its result is folded here
-      if (C::NP == 1 && t > 0) {
-        ok = fold_pv(t - 1, alpha_prev);
-        if (!ok) break;
-      }
+      if (ok && C::NP == 1 && t > 0) ok = __all_sync(0xffffffffu, fold_pv(t - 1, alpha_prev));
       const int pbuf = t % C::NP;
       unsigned char* pb = sP + pbuf * C::PBytes;
       const int sw = r_in_tile & 7;
@@ -438,9 +438,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[pbuf]);
+      if (ok && lane == 0) mbar_arrive(&p_full[pbuf]);
       // fold the previous tile's P.V while the tensor core works on this one
-      if (C::NP == 2 && t > 0) ok = fold_pv(t - 1, alpha_prev);
+      if (ok && C::NP == 2 && t > 0) ok = __all_sync(0xffffffffu, fold_pv(t - 1, alpha_prev));
       alpha_prev = alpha;
       ++t;
     }
@@ -449,6 +449,328 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
     pmax[wg * kQRows + r_in_tile] = l;
     asm volatile("bar.sync 1, 256;" ::: "memory");
     l += pmax[(wg ^ 1) * kQRows + r_in_tile];
+    if (ok && row < p.Sq) {
+      const float inv = 1.0f / l;   // l = 0 for a fully masked row: 0 * inf = NaN, as the reference's softmax gives
+      const size_t base = ((size_t)(b * p.H + h) * p.Sq + row) * kHeadDim + wg * HD;
+      if (p.out_dtype == BG_F32) {
+        float* out = reinterpret_cast<float*>(p.out) + base;
+#pragma unroll
+        for (int d = 0; d < HD; d += 4)
+          *reinterpret_cast<float4*>(out + d) = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
+      } else if (p.out_dtype == BG_F64) {
+        double* out = reinterpret_cast<double*>(p.out) + base;
+#pragma unroll
+        for (int d = 0; d < HD; d += 2) *reinterpret_cast<double2*>(out + d) = make_double2((double)(o[d] * inv), (double)(o[d + 1] * inv));
+      } else if (p.out_dtype == BG_F16) {
+        __half* out = reinterpret_cast<__half*>(p.out) + base;
+#pragma unroll
+        for (int d = 0; d < HD; d += 2) *reinterpret_cast<__half2*>(out + d) = __floats2half2_rn(o[d] * inv, o[d + 1] * inv);
+      } else {
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + base;
+#pragma unroll
+        for (int d = 0; d < HD; d += 2) *reinterpret_cast<__nv_bfloat162*>(out + d) = __floats2bfloat162_rn(o[d] * inv, o[d + 1] * inv);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(p.status, BG_ERR_DEVICE_TIMEOUT);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) {}
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TmemCols) : "memory");
+  }
+}
+
+
+// ---- 16-bit operands: 128-key tiles, output accumulated in tensor memory ------------------------------
+// Differences from the kernel above, which the 3xTF32 encoding keeps:
+//   * a tile is 128 keys, so the per-tile handshakes and address arithmetic are paid once per 64 keys per thread;
+//   * P.V accumulates in tensor memory across tiles (the MMA's accumulate flag) instead of being folded into
+//     registers after every tile.  The exponentials are taken relative to a reference maximum that is only
+//     raised when the running maximum exceeds it by more than 2^8 ("lazy rescaling"): then, and only then, a
+//     thread multiplies its half row of O in tensor memory (tcgen05.ld / tcgen05.st) and its row sum by
+//     2^(old - new).  Until then probabilities may reach 2^8, which bf16 / fp16 and the fp32 sums hold easily;
+//     the final O / l is the same quotient.
+//   * S has one buffer (128 columns) and P one; with O that is 192 tensor-memory columns, and with Q, two K
+//     tiles, one V^T tile and P 96 KB of shared memory: two CTAs per SM, each reading S twice (row maximum,
+//     then exponentials) so that no thread holds more than 32 scores.
+struct Attn16 {
+  static constexpr int BKV = 128;
+  static constexpr int NK = 2;
+  static constexpr int QBytes = kQRows * 128;
+  static constexpr int KBytes = BKV * 128;
+  static constexpr int VBytes = 2 * kHeadDim * 128;     // V^T: two k-blocks of 64 keys
+  static constexpr int PBytes = 2 * kQRows * 128;       // two k-blocks of 64 keys
+  static constexpr int SmemBytes = QBytes + NK * KBytes + VBytes + PBytes;
+  static constexpr int TmemCols = 256;                  // S: columns [0, 128), O: [128, 192)
+};
+constexpr float kLazyRescaleLog2 = 8.0f;
+
+__global__ void __launch_bounds__(kAttnThreads, 2)
+attn16_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ AttnParams p) {
+  using C = Attn16;
+  constexpr int BKV = C::BKV;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* sQ = smem;
+  unsigned char* sK = sQ + C::QBytes;
+  unsigned char* sV = sK + C::NK * C::KBytes;
+  unsigned char* sP = sV + C::VBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::PBytes);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = q_full + 1;          // [2]
+  uint64_t* k_empty = k_full + C::NK;     // [2]
+  uint64_t* v_full = k_empty + C::NK;
+  uint64_t* v_empty = v_full + 1;
+  uint64_t* s_full = v_empty + 1;         // Q.K^T of a tile has completed
+  uint64_t* s_empty = s_full + 1;         // the softmax warps have read S for the last time (8 arrivals)
+  uint64_t* p_full = s_empty + 1;         // P is in shared memory (8 arrivals)
+  uint64_t* pv_full = p_full + 1;         // P.V of a tile has completed
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* pmax = reinterpret_cast<float*>(tmem_holder + 4);   // [2 buffers][2 halves][128 rows]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int q0 = q_tile * kQRows;
+  const int n_kv = (p.Sk + BKV - 1) / BKV;
+  const unsigned char* cls = p.tile_class ? p.tile_class + (size_t)q_tile * n_kv : nullptr;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < C::NK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    mbar_init(v_full, 1); mbar_init(v_empty, 1);
+    mbar_init(s_full, 1); mbar_init(s_empty, 8);
+    mbar_init(p_full, 8); mbar_init(pv_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(C::TmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_s = tmem_base;
+  const uint32_t tmem_o = tmem_base + BKV;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, C::QBytes);
+      tma_load_4d(&tmQ, sQ, q_full, 0, q0, h, b);
+      auto next_tile = [&](int j) { while (j < n_kv && cls && cls[j] == 0) ++j; return j; };
+      int jk = next_tile(0), jv = jk, tk = 0, tv = 0;
+      bool okp = true;
+      while (jv < n_kv && okp) {
+        while (okp && jk < n_kv && tk <= tv + 1) {
+          const int s = tk % C::NK;
+          if (!mbar_wait(&k_empty[s], ((uint32_t)(tk / C::NK) & 1u) ^ 1u, abort_flag)) { okp = false; break; }
+          mbar_expect_tx(&k_full[s], C::KBytes);
+          tma_load_4d(&tmK, sK + s * C::KBytes, &k_full[s], 0, jk * BKV, h, b);
+          ++tk;
+          jk = next_tile(jk + 1);
+        }
+        if (!okp) break;
+        if (!mbar_wait(v_empty, ((uint32_t)tv & 1u) ^ 1u, abort_flag)) break;
+        mbar_expect_tx(v_full, C::VBytes);
+        tma_load_4d(&tmV, sV, v_full, jv * BKV, 0, h, b);
+        tma_load_4d(&tmV, sV + kHeadDim * 128, v_full, jv * BKV + 64, 0, h, b);
+        ++tv;
+        jv = next_tile(jv + 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int n_proc = 0;
+      for (int j = 0; j < n_kv; ++j) n_proc += !(cls && cls[j] == 0);
+      bool ok = n_proc == 0 || mbar_wait(q_full, 0, abort_flag);
+      const uint32_t q_addr = smem_u32(sQ);
+      auto issue_qk = [&](int t) -> bool {
+        const int s = t % C::NK;
+        // the single S buffer is free once the softmax warps have taken tile t-1 out of it
+        if (t > 0 && !mbar_wait(s_empty, (uint32_t)(t - 1) & 1u, abort_flag)) return false;
+        if (!mbar_wait(&k_full[s], (uint32_t)(t / C::NK) & 1u, abort_flag)) return false;
+        tc_fence_after();
+        const uint64_t da = make_kmajor_sw128_desc(q_addr), db = make_kmajor_sw128_desc(smem_u32(sK + s * C::KBytes));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma<false>(tmem_s, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_qk, k ? 1u : 0u);
+        umma_commit(s_full);
+        umma_commit(&k_empty[s]);
+        return true;
+      };
+      auto issue_pv = [&](int t) -> bool {
+        if (!mbar_wait(p_full, (uint32_t)t & 1u, abort_flag)) return false;
+        if (!mbar_wait(v_full, (uint32_t)t & 1u, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t p_addr = smem_u32(sP), v_addr = smem_u32(sV);
+        for (int kb = 0; kb < 2; ++kb) {
+          const uint64_t da = make_kmajor_sw128_desc(p_addr + kb * (kQRows * 128));
+          const uint64_t db = make_kmajor_sw128_desc(v_addr + kb * (kHeadDim * 128));
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma<false>(tmem_o, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_pv, (t > 0 || kb || k) ? 1u : 0u);
+        }
+        umma_commit(pv_full);
+        umma_commit(v_empty);
+        return true;
+      };
+      if (ok && n_proc > 0) ok = issue_qk(0);
+      for (int t = 0; t < n_proc && ok; ++t) {
+        if (t + 1 < n_proc) ok = issue_qk(t + 1);     // S(t) has been read by the time P(t) is published
+        if (ok) ok = issue_pv(t);
+      }
+    }
+  } else {
+    const int wg = (warp - 2) >> 2;                 // which 64 keys of a tile / which 32 output columns
+    const int quarter = warp & 3;
+    const int r_in_tile = quarter * 32 + lane;
+    const int row = q0 + r_in_tile;
+    const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+    constexpr int HD = kHeadDim / 2;
+    constexpr float kLog2e = 1.4426950408889634f;
+    float m_ref = -CUDART_INF_F, l = 0.f;
+    float scale = p.scale;
+    const bool per_elem_scale = p.scale_buf != nullptr && !(p.scale_uniform && *p.scale_uniform);
+    if (p.scale_buf && !per_elem_scale) scale = p.scale_buf[0];
+    const size_t score_row = ((size_t)(b * p.H + h) * p.Sq + (row < p.Sq ? row : 0)) * (size_t)p.Sk;
+    const size_t mask_row = (size_t)b * p.mask_sb + (size_t)h * p.mask_sh + (size_t)(row < p.Sq ? row : 0) * p.Sk;
+    const bool bf = p.round_scores == BG_BF16 + 1;
+    const int sw = r_in_tile & 7;
+    bool ok = true;
+    int t = 0;
+    for (int j = 0; j < n_kv; ++j) {
+      const int tclass = cls ? cls[j] : (p.mask ? 3 : 1);
+      if (tclass == 0) continue;
+      // a thread whose wait ran out keeps walking the tiles (doing nothing) so that the named barrier below still
+      // sees all 256 softmax threads once per tile
+      if (ok) ok = mbar_wait(s_full, (uint32_t)t & 1u, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);      // tensor-memory loads below are warp-wide: keep the warp together
+      tc_fence_after();
+      const int k0 = j * BKV + wg * 64;             // first key of this thread's half
+      const bool need_mask = p.mask && tclass == 3;
+      const bool fast = !need_mask && !per_elem_scale && scale > 0.f && (tclass == 2 || j * BKV + BKV <= p.Sk);
+      const uint32_t* wrow = (fast && tclass == 2) ? p.mask_bits + (size_t)(row < p.Sq ? row : 0) * p.mask_words + (k0 >> 5) : nullptr;
+      // 32 scores (chunk c of this thread's 64), ready for the exponential: raw S with masked keys at -inf on the
+      // fast path (scale folded into the exponent later), else scale * S (+ mask) element by element
+      auto load_scores = [&](int c, float (&x)[32]) {
+        uint32_t r[32];
+        tmem_ld32(tmem_s + (uint32_t)(wg * 64 + c * 32) + lane_sel, r);
+        if (fast) {
+          const uint32_t word = wrow ? wrow[c] : 0u;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) x[i] = ((word >> i) & 1u) ? -CUDART_INF_F : __uint_as_float(r[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = k0 + c * 32 + i;
+            const bool in_range = key < p.Sk;
+            float v = __fmul_rn(__uint_as_float(r[i]), per_elem_scale ? (in_range ? p.scale_buf[score_row + key] : 0.f) : scale);
+            if (need_mask && in_range) {
+              if (p.mask_is_bool) { if (reinterpret_cast<const unsigned char*>(p.mask)[mask_row + key]) v = -CUDART_INF_F; }
+              else v = __fadd_rn(v, reinterpret_cast<const float*>(p.mask)[mask_row + key]);
+            }
+            x[i] = in_range ? v : -CUDART_INF_F;
+          }
+        }
+      };
+      // pass 1: the tile maximum of this row, in natural units
+      float mt = -CUDART_INF_F;
+      if (ok) {
+        float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          float x[32];
+          load_scores(c, x);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], x[i]);
+        }
+        mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        if (fast) mt *= scale;
+      }
+      const int pbuf = t & 1;
+      pmax[(pbuf * 2 + wg) * kQRows + r_in_tile] = mt;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      mt = fmaxf(mt, pmax[(pbuf * 2 + (wg ^ 1)) * kQRows + r_in_tile]);
+      // P of the previous tile has been consumed (and O is quiescent) once its P.V has completed
+      if (ok && t > 0) ok = mbar_wait(pv_full, (uint32_t)(t - 1) & 1u, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { ++t; continue; }
+      // Lazy rescaling.  tcgen05.ld / tcgen05.st are warp-wide instructions: when any row of this warp has to
+      // rescale, all 32 lanes run the load / multiply / store, the others with a factor of one.
+      const bool raise = m_ref != -CUDART_INF_F && (mt - m_ref) * kLog2e > kLazyRescaleLog2;
+      if (__any_sync(0xffffffffu, raise)) {
+        const float alpha = raise ? ex2_approx((m_ref - mt) * kLog2e) : 1.0f;
+        tc_fence_after();
+        uint32_t r[32];
+        tmem_ld32(tmem_o + (uint32_t)(wg * HD) + lane_sel, r);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+        tmem_st32(tmem_o + (uint32_t)(wg * HD) + lane_sel, r);
+        if (raise) { l *= alpha; m_ref = mt; }
+      }
+      if (m_ref == -CUDART_INF_F) m_ref = mt;        // nothing (or only zeros) accumulated so far
+      const float m_use = m_ref == -CUDART_INF_F ? 0.f : m_ref;
+      const float cc = fast ? scale * kLog2e : kLog2e, ml = m_use * kLog2e;
+      // pass 2: exponentials, row sum, P in the operand layout (k-block wg: this thread's 64 keys are one 128-byte row)
+      unsigned char* prow = sP + wg * (kQRows * 128) + r_in_tile * 128;
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        float x[32];
+        load_scores(c, x);
+        if (c == 1) {
+          // last read of S: the MMA warp may start the next tile's Q.K^T
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_empty);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          x[i] = ex2_approx(fmaf(x[i], cc, -ml));
+          ps[i & 3] += x[i];
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float a0 = x[q * 8 + 2 * e], a1 = x[q * 8 + 2 * e + 1];
+            if (bf) { __nv_bfloat162 v2 = __floats2bfloat162_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
+            else { __half2 v2 = __floats2half2_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
+          }
+          *reinterpret_cast<uint4*>(prow + (((c * 4 + q) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+      ++t;
+    }
+    if (ok && t > 0) ok = mbar_wait(pv_full, (uint32_t)(t - 1) & 1u, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    // combine the two halves' row sums
+    pmax[wg * kQRows + r_in_tile] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l += pmax[(wg ^ 1) * kQRows + r_in_tile];
+    // the accumulator is read by whole warps (tcgen05.ld is warp-wide); only the stores are per row
+    float o[HD];
+    {
+      tc_fence_after();
+      uint32_t r[32];
+      tmem_ld32(tmem_o + (uint32_t)(wg * HD) + lane_sel, r);
+#pragma unroll
+      for (int i = 0; i < HD; ++i) o[i] = t > 0 ? __uint_as_float(r[i]) : 0.f;
+    }
     if (ok && row < p.Sq) {
       const float inv = 1.0f / l;   // l = 0 for a fully masked row: 0 * inf = NaN, as the reference's softmax gives
       const size_t base = ((size_t)(b * p.H + h) * p.Sq + row) * kHeadDim + wg * HD;
@@ -709,7 +1031,7 @@ bool attn_tc_supported(const AttnProblem& a) {
 void attn_scratch_sizes(const AttnProblem& a, int64_t bytes[8]) {
   const int64_t nq = (int64_t)a.B * a.H * a.Sq * a.D, nk = (int64_t)a.B * a.H * a.Sk * a.D;
   const int es = a.mode == 1 ? 4 : 2;
-  const int bkv = 64;
+  const int bkv = a.mode == 1 ? 64 : Attn16::BKV;
   bytes[0] = nq * es;                       // Q (hi)
   bytes[1] = a.mode == 1 ? nq * es : 0;     // Q lo
   bytes[2] = nk * es;                       // K (hi)
@@ -726,7 +1048,7 @@ void attn_scratch_sizes(const AttnProblem& a, int64_t bytes[8]) {
 cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bool check_uniform, bool classify_mask, int* status,
                                 cudaStream_t s) {
   const bool tf32 = a.mode == 1;
-  const int bkv = 64;
+  const int bkv = tf32 ? 64 : Attn16::BKV;
   const int sdt = tf32 ? BG_F32 : a.ab_dtype;
   // operand staging: dense Q, K, V^T in the kernel's encoding
   const int kind = tf32 ? PREP_TF32 : (a.ab_dtype == BG_F16 ? PREP_F16 : PREP_BF16);
@@ -824,10 +1146,10 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
     if (e != cudaSuccess) return e;
     attn_fwd_kernel<true><<<grid, kAttnThreads, smem, s>>>(q0, q1, k0, k1, v0, v1, p);
   } else {
-    const size_t smem = AttnCfg<false>::SmemBytes + 256 + 2048 + 1024;
-    e = cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = Attn16::SmemBytes + 256 + 2048 + 1024;
+    e = cudaFuncSetAttribute(attn16_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    attn_fwd_kernel<false><<<grid, kAttnThreads, smem, s>>>(q0, q1, k0, k1, v0, v1, p);
+    attn16_fwd_kernel<<<grid, kAttnThreads, smem, s>>>(q0, k0, v0, p);
   }
   return cudaGetLastError();
 }

@@ -2019,7 +2019,7 @@ void Compiler::emit_attention(int n, int key) {
     bool classify_mask = a.mask != nullptr;
     if (a.mask && mask_slot >= 0 && r.from_handle[mask_slot] && a.mask_sb == 0 && a.mask_sh == 0 && class_bytes > 0) {
       bool fresh = false;
-      void* kept = mask_classes_for(r.ctx, a.mask, class_bytes, a.Sq, a.Sk, 64, a.mask_is_bool, &fresh);
+      void* kept = mask_classes_for(r.ctx, a.mask, class_bytes, a.Sq, a.Sk, a.mode == 1 ? 64 : 128, a.mask_is_bool, &fresh);
       if (kept) { scratch[6] = kept; classify_mask = fresh; }
     }
     cudaError_t e = launch_attention_tc(a, scratch, check_uniform, classify_mask, r.ctx->d_status, r.ctx->stream);

@@ -116,6 +116,18 @@ def _ln_inputs(rows: int, cols: int) -> Callable[[], Dict[str, np.ndarray]]:
     return make
 
 
+def _attn_growing(b: int, h: int, s: int, d: int) -> Callable[[], Dict[str, np.ndarray]]:
+    """Keys whose scale grows along the sequence: the running row maximum keeps rising by many e-folds from
+    one key tile to the next, which forces the fused kernels to rescale what they have accumulated."""
+    def make() -> Dict[str, np.ndarray]:
+        t = configs.attention_inputs(b, h, s, d)
+        ramp = (1.0 + 40.0 * np.arange(s, dtype=np.float32) / s).reshape(1, 1, s, 1)
+        t["k"] = (t["k"] * ramp).astype(np.float32)
+        t["mask"] = configs.causal_mask(s)
+        return t
+    return make
+
+
 def _gpt_tiny() -> Dict[str, np.ndarray]:
     return configs.gpt_inputs(layers=2, d_model=64, heads=4, d_mlp=128, vocab=211, seq=32, batch=2)
 
@@ -199,6 +211,12 @@ CASES: Dict[str, Case] = {
     "c4_attn_mask_bf16": Case(_attn_small(2, 2, 320, 64),
                               lambda api, t, raw: configs.attention(api, t, "mask", "bfloat16"), rtol=2e-2,
                               reference_has_it=False),
+    "c4_attn_growing_f16": Case(_attn_growing(1, 2, 640, 64),
+                                lambda api, t, raw: configs.attention(api, t, "none", "float16"), rtol=2e-2),
+    "c4_attn_growing_causal_f16": Case(_attn_growing(1, 2, 640, 64),
+                                       lambda api, t, raw: configs.attention(api, t, "mask", "float16"), rtol=2e-2),
+    "c4_attn_growing_f32": Case(_attn_growing(1, 2, 640, 64),
+                                lambda api, t, raw: configs.attention(api, t, "mask")),
     "typed_attention_d64": Case(_attn_small(2, 2, 136, 64),
                                 lambda api, t, raw: api.attention_forward(t["q"], t["k"], t["v"])),
     "c4_attn_full": Case(_attn_small(1, 2, 96, 32),
