@@ -511,6 +511,7 @@ struct Attn16 {
 };
 constexpr float kLazyRescaleLog2 = 8.0f;
 
+template <bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, 2)
 attn16_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ AttnParams p) {
@@ -642,7 +643,6 @@ attn16_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (p.scale_buf && !per_elem_scale) scale = p.scale_buf[0];
     const size_t score_row = ((size_t)(b * p.H + h) * p.Sq + (row < p.Sq ? row : 0)) * (size_t)p.Sk;
     const size_t mask_row = (size_t)b * p.mask_sb + (size_t)h * p.mask_sh + (size_t)(row < p.Sq ? row : 0) * p.Sk;
-    const bool bf = p.round_scores == BG_BF16 + 1;
     const int sw = r_in_tile & 7;
     bool ok = true;
     int t = 0;
@@ -663,8 +663,11 @@ attn16_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       auto load_scores = [&](int c, float (&x)[32]) {
         uint32_t r[32];
         tmem_ld32(tmem_s + (uint32_t)(wg * 64 + c * 32) + lane_sel, r);
-        if (fast) {
-          const uint32_t word = wrow ? wrow[c] : 0u;
+        if (fast && !wrow) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(r[i]);
+        } else if (fast) {
+          const uint32_t word = wrow[c];
 #pragma unroll
           for (int i = 0; i < 32; ++i) x[i] = ((word >> i) & 1u) ? -CUDART_INF_F : __uint_as_float(r[i]);
         } else {
@@ -743,7 +746,7 @@ attn16_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float a0 = x[q * 8 + 2 * e], a1 = x[q * 8 + 2 * e + 1];
-            if (bf) { __nv_bfloat162 v2 = __floats2bfloat162_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
+            if (BF16) { __nv_bfloat162 v2 = __floats2bfloat162_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
             else { __half2 v2 = __floats2half2_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
           }
           *reinterpret_cast<uint4*>(prow + (((c * 4 + q) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -1147,9 +1150,10 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
     attn_fwd_kernel<true><<<grid, kAttnThreads, smem, s>>>(q0, q1, k0, k1, v0, v1, p);
   } else {
     const size_t smem = Attn16::SmemBytes + 256 + 2048 + 1024;
-    e = cudaFuncSetAttribute(attn16_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    auto kern = a.ab_dtype == BG_BF16 ? attn16_fwd_kernel<true> : attn16_fwd_kernel<false>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    attn16_fwd_kernel<<<grid, kAttnThreads, smem, s>>>(q0, k0, v0, p);
+    kern<<<grid, kAttnThreads, smem, s>>>(q0, k0, v0, p);
   }
   return cudaGetLastError();
 }
