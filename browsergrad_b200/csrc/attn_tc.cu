@@ -41,6 +41,13 @@ __device__ __forceinline__ void tma_load_4d(const CUtensorMap* map, void* smem_d
       : "memory");
 }
 
+// max of three in one instruction (sm_100 has the three-input form)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -351,7 +358,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
         // four independent chains: a single running max would serialise HK dependent instructions
         float mx[4] = {sv[0], sv[1], sv[2], sv[3]};
 #pragma unroll
-        for (int i = 4; i < HK; ++i) mx[i & 3] = fmaxf(mx[i & 3], sv[i]);
+        for (int i = 4; i < HK; i += 2) mx[(i >> 1) & 3] = fmax3(mx[(i >> 1) & 3], sv[i], sv[i + 1]);
         mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale;
       } else {
 #pragma unroll
@@ -693,7 +700,7 @@ attn16_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           float x[32];
           load_scores(c, x);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], x[i]);
+          for (int i = 0; i < 32; i += 2) mx[(i >> 1) & 3] = fmax3(mx[(i >> 1) & 3], x[i], x[i + 1]);
         }
         mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         if (fast) mt *= scale;
