@@ -2,20 +2,24 @@
 //   O[b,h,q,:] = softmax_k( scale * Q[b,h,q,:].K[b,h,k,:] (+ mask) ) . V[b,h,k,:]
 // with the score tile kept on chip: S = Q K^T is produced by tcgen05.mma into tensor memory, the
 // softmax warps read it with tcgen05.ld, keep the running max / sum per query row, write the
-// probabilities P back to shared memory in the operand layout, and a second tcgen05.mma forms
-// P V into tensor memory, which the same warps fold into a register accumulator.
+// probabilities P back to shared memory in the operand layout, and a second tcgen05.mma forms P V.
 //
 // One CTA owns 128 query rows of one (batch, head):
-//   warp 0     TMA producer: Q once, then K tiles and V^T tiles (64 keys) into their rings
-//   warp 1     MMA issuer (one thread): QK^T two tiles ahead, P.V as soon as P is published
+//   warp 0     TMA producer: Q once, then K tiles and V^T tiles into their rings
+//   warp 1     MMA issuer (one thread): QK^T ahead of the softmax, P.V as soon as P is published
 //   warps 2-9  softmax: two threads per query row (each half of the keys / output columns)
-// Operand encodings: f16 / bf16 (two CTAs per SM), or 3xTF32 for fp32-faithful results (Q, K, V^T pre-split into
-// hi = tf32(x), lo = x - hi; P split on the fly; the three
-// cross products lo.hi, hi.lo, hi.hi go into one accumulator).  All operands are K-major tiles
-// with 128-byte swizzle; V is consumed as V^T [D, keys], prepared by a transposing pre-pass.
+// Two kernels, one per operand encoding:
+//   attn_tf32_fwd_kernel  3xTF32 for fp32-faithful results: Q, K, V^T pre-split into hi = tf32(x), lo = x - hi, P split
+//                         on the fly, the cross products lo.hi, hi.lo, hi.hi in one accumulator; 64-key tiles, the
+//                         previous tile's P.V folded into registers while the tensor core works on the current one;
+//   attn16_fwd_kernel     f16 / bf16 operands: 128-key tiles, P.V accumulated in tensor memory with lazy rescaling,
+//                         two CTAs per SM (described at the kernel).
+// All operands are K-major tiles with 128-byte swizzle; V is consumed as V^T [D, keys], prepared by a
+// transposing pre-pass that also performs the autocast casts.
 // Masks: additive fp32 [B|1, H|1, Sq, Sk], or boolean "fill with -inf"; a per-(q tile, k tile)
 // class (skip / plain / mixed) computed by a pre-pass lets fully masked tiles (the causal upper
-// triangle) be skipped by every role alike.  No cluster multicast; every wait is clock-bounded.
+// triangle) be skipped by every role alike.  No cluster multicast; every wait is clock-bounded; tensor-memory
+// loads and stores are issued by whole warps.
 #include "common.h"
 
 #include <cuda_bf16.h>
@@ -72,35 +76,29 @@ struct AttnParams {
   int* status;
 };
 
-template <bool TF32>
 struct AttnCfg {
   static constexpr int BKV = 64;                              // keys per tile
   // K and V^T tiles travel in rings of their own: K(t+1) can be fetched as soon as Q.K(t)^T has been issued,
-  // V(t+1) once P.V(t) has completed.  The 3xTF32 encoding (hi + lo planes, 4-byte elements) has room for one
-  // tile of each; the 16-bit encoding keeps three.
-  static constexpr int NK = TF32 ? 1 : 3;
-  static constexpr int NV = TF32 ? 1 : 3;
-  static constexpr int NP = TF32 ? 1 : 2;                     // P buffers
-  // 3xTF32 planes: hi k-block 0, hi k-block 1, lo k-block 0, lo k-block 1 (a k-block is 32 floats = 128 bytes)
-  static constexpr int QBytes = TF32 ? 4 * kQRows * 128 : kQRows * 128;
-  static constexpr int KBytes = TF32 ? 4 * BKV * 128 : BKV * 128;
-  static constexpr int VBytes = TF32 ? 4 * kHeadDim * 128 : kHeadDim * 128;     // V^T: 64 rows x (2 x 32 | 64) keys
-  static constexpr int PBytes = TF32 ? 4 * kQRows * 128 : kQRows * 128;
+  // V(t+1) once P.V(t) has completed.  With hi + lo planes of 4-byte elements there is room for one tile of each.
+  static constexpr int NK = 1;
+  static constexpr int NV = 1;
+  static constexpr int NP = 1;                                // P buffers
+  // planes: hi k-block 0, hi k-block 1, lo k-block 0, lo k-block 1 (a k-block is 32 floats = 128 bytes)
+  static constexpr int QBytes = 4 * kQRows * 128;
+  static constexpr int KBytes = 4 * BKV * 128;
+  static constexpr int VBytes = 4 * kHeadDim * 128;           // V^T: 64 rows x (2 x 32) keys
+  static constexpr int PBytes = 4 * kQRows * 128;
   static constexpr int SCols = BKV;
   static constexpr int TmemCols = 256;                        // 2 x S + 2 x PV
-  static constexpr int SmemBytes = QBytes + NK * KBytes + NV * VBytes + NP * PBytes;
-  // the 16-bit configuration (96 KB, 256 TMEM columns, <= 102 registers) runs two CTAs per SM, so one
-  // CTA's softmax overlaps the other's tensor-core and copy phases
-  static constexpr int CtasPerSm = TF32 ? 1 : 2;
+  static constexpr int SmemBytes = QBytes + NK * KBytes + NV * VBytes + NP * PBytes;   // 192 KB: one CTA per SM
 };
 
-template <bool TF32>
-__global__ void __launch_bounds__(kAttnThreads, AttnCfg<TF32>::CtasPerSm)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant__ CUtensorMap tmQ1,
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_tf32_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant__ CUtensorMap tmQ1,
                 const __grid_constant__ CUtensorMap tmK0, const __grid_constant__ CUtensorMap tmK1,
                 const __grid_constant__ CUtensorMap tmV0, const __grid_constant__ CUtensorMap tmV1,
                 const __grid_constant__ AttnParams p) {
-  using C = AttnCfg<TF32>;
+  using C = AttnCfg;
   constexpr int BKV = C::BKV;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -152,13 +150,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
     if (lane == 0) {
       // Q: loaded once
       mbar_expect_tx(q_full, C::QBytes);
-      if (TF32) {
+      {
         for (int kb = 0; kb < 2; ++kb) {
           tma_load_4d(&tmQ0, sQ + kb * (kQRows * 128), q_full, kb * 32, q0, h, b);
           tma_load_4d(&tmQ1, sQ + 2 * (kQRows * 128) + kb * (kQRows * 128), q_full, kb * 32, q0, h, b);
         }
-      } else {
-        tma_load_4d(&tmQ0, sQ, q_full, 0, q0, h, b);
       }
       // K runs one tile ahead of V in issue order: its slot frees as soon as Q.K^T of the previous occupant is done
       auto next_tile = [&](int j) { while (j < n_kv && cls && cls[j] == 0) ++j; return j; };
@@ -168,13 +164,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
         unsigned char* st = sK + s * C::KBytes;
         const int k0 = j * BKV;
         mbar_expect_tx(&k_full[s], C::KBytes);
-        if (TF32) {
+        {
           for (int kb = 0; kb < 2; ++kb) {
             tma_load_4d(&tmK0, st + kb * (BKV * 128), &k_full[s], kb * 32, k0, h, b);
             tma_load_4d(&tmK1, st + (2 + kb) * (BKV * 128), &k_full[s], kb * 32, k0, h, b);
           }
-        } else {
-          tma_load_4d(&tmK0, st, &k_full[s], 0, k0, h, b);
         }
         return true;
       };
@@ -184,13 +178,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
         unsigned char* st = sV + s * C::VBytes;
         const int k0 = j * BKV;
         mbar_expect_tx(&v_full[s], C::VBytes);
-        if (TF32) {
+        {
           for (int kb = 0; kb < 2; ++kb) {
             tma_load_4d(&tmV0, st + kb * (kHeadDim * 128), &v_full[s], k0 + kb * 32, 0, h, b);
             tma_load_4d(&tmV1, st + (2 + kb) * (kHeadDim * 128), &v_full[s], k0 + kb * 32, 0, h, b);
           }
-        } else {
-          tma_load_4d(&tmV0, st, &v_full[s], k0, 0, h, b);
         }
         return true;
       };
@@ -220,7 +212,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
         tc_fence_after();
         const uint32_t k_addr = smem_u32(sK + s * C::KBytes);
         const uint32_t d_s = tmem_s + (uint32_t)((t & 1) * C::SCols);
-        if (TF32) {
+        {
           // passes lo.hi, hi.lo, hi.hi; each: 2 k-blocks x 4 k-steps of 8 floats
           uint32_t first = 1;
           for (int pass = 0; pass < 3; ++pass) {
@@ -236,10 +228,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
               }
             }
           }
-        } else {
-          const uint64_t da = make_kmajor_sw128_desc(q_addr), db = make_kmajor_sw128_desc(k_addr);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) umma<false>(d_s, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_qk, k ? 1u : 0u);
         }
         umma_commit(&s_full[t & 1]);
         umma_commit(&k_empty[s]);
@@ -253,7 +241,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
         const uint32_t p_addr = smem_u32(sP + pbuf * C::PBytes);
         const uint32_t v_addr = smem_u32(sV + s * C::VBytes);
         const uint32_t d_pv = tmem_pv + (uint32_t)((t & 1) * kHeadDim);
-        if (TF32) {
+        {
           // passes lo.hi, hi.lo, hi.hi over the tile's two k-blocks of 32 keys
           uint32_t first = 1;
           for (int pass = 0; pass < 3; ++pass) {
@@ -269,10 +257,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
               }
             }
           }
-        } else {
-          const uint64_t da = make_kmajor_sw128_desc(p_addr), db = make_kmajor_sw128_desc(v_addr);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) umma<false>(d_pv, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_pv, k ? 1u : 0u);
         }
         umma_commit(&pv_full[t & 1]);
         umma_commit(&v_empty[s]);
@@ -408,7 +392,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
       const int pbuf = t % C::NP;
       unsigned char* pb = sP + pbuf * C::PBytes;
       const int sw = r_in_tile & 7;
-      if (TF32) {
+      {
         // this thread's 32 keys are k-block `wg`: one 128-byte row in the hi plane and one in the lo plane
         unsigned char* hi_row = pb + wg * (kQRows * 128) + r_in_tile * 128;
         unsigned char* lo_row = pb + (2 + wg) * (kQRows * 128) + r_in_tile * 128;
@@ -425,21 +409,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant_
           const int chunk = c ^ sw;
           *reinterpret_cast<float4*>(hi_row + (chunk << 4)) = make_float4(hi[0], hi[1], hi[2], hi[3]);
           *reinterpret_cast<float4*>(lo_row + (chunk << 4)) = make_float4(lo[0], lo[1], lo[2], lo[3]);
-        }
-      } else {
-        // 64 keys = one 128-byte row; this thread owns chunks wg*4 .. wg*4+3 (32 keys)
-        const bool bf = p.round_scores == BG_BF16 + 1;
-        unsigned char* prow = pb + r_in_tile * 128;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float a0 = sv[c * 8 + 2 * e], a1 = sv[c * 8 + 2 * e + 1];
-            if (bf) { __nv_bfloat162 v2 = __floats2bfloat162_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
-            else { __half2 v2 = __floats2half2_rn(a0, a1); w[e] = *reinterpret_cast<uint32_t*>(&v2); }
-          }
-          *reinterpret_cast<uint4*>(prow + (((wg * 4 + c) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
       fence_async_smem();
@@ -1151,10 +1120,10 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
   dim3 grid((a.Sq + kQRows - 1) / kQRows, a.H, a.B);
   cudaError_t e;
   if (tf32) {
-    const size_t smem = AttnCfg<true>::SmemBytes + 256 + 2048 + 1024;
-    e = cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = AttnCfg::SmemBytes + 256 + 2048 + 1024;
+    e = cudaFuncSetAttribute(attn_tf32_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    attn_fwd_kernel<true><<<grid, kAttnThreads, smem, s>>>(q0, q1, k0, k1, v0, v1, p);
+    attn_tf32_fwd_kernel<<<grid, kAttnThreads, smem, s>>>(q0, q1, k0, k1, v0, v1, p);
   } else {
     const size_t smem = Attn16::SmemBytes + 256 + 2048 + 1024;
     auto kern = a.ab_dtype == BG_BF16 ? attn16_fwd_kernel<true> : attn16_fwd_kernel<false>;

@@ -323,6 +323,24 @@ class Tensor:
             raise ValueError(f"clamp: min {lo} must be <= max {hi}")
         return self._wrap(Node("CLAMP", (self._uop,), self.shape, self.dtype, {"min": lo, "max": hi}))
 
+    def repeat(self, *sizes: Any) -> "Tensor":
+        """``REPEAT`` node (_tensor_proxy.py:1091-1120): ``np.tile`` with one factor per (left-padded) dimension."""
+        reps = tuple(int(r) for r in (sizes[0] if len(sizes) == 1 and isinstance(sizes[0], (tuple, list)) else sizes))
+        if len(reps) < self.ndim or any(r < 0 for r in reps):
+            raise ValueError("repeat: one non-negative factor per dimension (more factors add leading dimensions)")
+        padded = (1,) * (len(reps) - self.ndim) + self.shape
+        out_shape = tuple(r * d for r, d in zip(reps, padded))
+        return self._wrap(Node("REPEAT", (self._uop,), out_shape, self.dtype, {"repeats": reps}))
+
+    def repeat_interleave(self, repeats: int, dim: int) -> "Tensor":
+        """``REPEAT_INTERLEAVE`` node (_tensor_proxy.py:1393-1428): every slice along ``dim`` ``repeats`` times in place."""
+        axis = int(dim) % self.ndim
+        r = int(repeats)
+        if r < 0:
+            raise ValueError("repeat_interleave: repeats must be non-negative")
+        out_shape = tuple(d * r if i == axis else d for i, d in enumerate(self.shape))
+        return self._wrap(Node("REPEAT_INTERLEAVE", (self._uop,), out_shape, self.dtype, {"repeats": r, "axis": axis}))
+
     def flip(self, dim: int) -> "Tensor":
         """``FLIP`` node (_tensor_proxy.py:1122-1139)."""
         axis = int(dim) % self.ndim

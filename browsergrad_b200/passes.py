@@ -250,7 +250,9 @@ def lower_composites(root: Any) -> Any:
       for floats, NaN passes through both comparisons;
     * ``VAR(x; axes, correction)`` -> ``sum((x - mean(x))**2) / max(n - correction, 0)`` with the mean kept
       in the result dtype -- the two passes of ``np.var(dtype=...)``;
-    * ``STACK`` -> ``CONCAT`` of the inputs reshaped with a unit axis.
+    * ``STACK`` -> ``CONCAT`` of the inputs reshaped with a unit axis;
+    * ``REPEAT`` / ``REPEAT_INTERLEAVE`` -> ``RESHAPE`` / ``BROADCAST_TO`` / ``RESHAPE`` (``np.tile`` / ``np.repeat``,
+      _realize.py:329-332, :360-363).
     """
     def make(like: Any, op: str, inputs: tuple, shape: tuple, dtype: str, arg: Any) -> Any:
         return type(like)(op=op, inputs=inputs, shape=tuple(shape), dtype=dtype, arg=arg)
@@ -294,6 +296,21 @@ def lower_composites(root: Any) -> Any:
                 shp = tuple(x.shape[:axis]) + (1,) + tuple(x.shape[axis:])
                 parts.append(make(node, "RESHAPE", (x,), shp, x.dtype, {"new_shape": shp}))
             return make(node, "CONCAT", tuple(parts), node.shape, node.dtype, {"axis": axis})
+        if node.op in ("REPEAT", "REPEAT_INTERLEAVE"):
+            # a unit axis beside every repeated one, broadcast to the factor, folded back: views until the final RESHAPE
+            (x,) = ins
+            if node.op == "REPEAT":
+                reps = tuple(int(r) for r in node.arg["repeats"])
+                padded = (1,) * (len(reps) - len(x.shape)) + tuple(x.shape)
+                split = tuple(v for d in padded for v in (1, d))
+                wide = tuple(v for r, d in zip(reps, padded) for v in (r, d))
+            else:
+                axis, r = int(node.arg["axis"]), int(node.arg["repeats"])
+                split = tuple(x.shape[:axis + 1]) + (1,) + tuple(x.shape[axis + 1:])
+                wide = tuple(x.shape[:axis + 1]) + (r,) + tuple(x.shape[axis + 1:])
+            a = make(node, "RESHAPE", (x,), split, node.dtype, {"new_shape": split})
+            b = make(node, "BROADCAST_TO", (a,), wide, node.dtype, {"shape": wide})
+            return make(node, "RESHAPE", (b,), node.shape, node.dtype, {"new_shape": tuple(node.shape)})
         if all(a is b for a, b in zip(ins, node.inputs)):
             return node
         return make(node, node.op, ins, node.shape, node.dtype, node.arg)

@@ -194,6 +194,15 @@ def _h_var(node, vt, store):  # _realize.py:346-357
     return np.array(variance, dtype=np.dtype(node.dtype), copy=True).reshape(node.shape)
 
 
+def _h_repeat(node, vt, store):  # _realize.py:329-332
+    return np.array(np.tile(_in(node, vt, 0), tuple(node.arg["repeats"])), dtype=np.dtype(node.dtype), copy=True)
+
+
+def _h_repeat_interleave(node, vt, store):  # _realize.py:360-363
+    return np.array(np.repeat(_in(node, vt, 0), int(node.arg["repeats"]), axis=int(node.arg["axis"])),
+                    dtype=np.dtype(node.dtype), copy=True)
+
+
 def _h_where(node, vt, store):  # _realize.py:1453-1459
     sel = np.where(_in(node, vt, 0), _in(node, vt, 1), _in(node, vt, 2))
     return np.array(sel, dtype=np.dtype(node.dtype), copy=True).reshape(node.shape)
@@ -344,7 +353,7 @@ _DISPATCH: Dict[str, Callable] = {
     "PERMUTE": lambda n, vt, s: np.transpose(_in(n, vt, 0), axes=n.arg["axes"]),   # :1119-1121
     "WHERE": _h_where,
     "CLAMP": _h_clamp, "FLIP": _h_flip, "CUMSUM": _h_cumsum, "CONCAT": _h_concat, "STACK": _h_stack,
-    "TRIL": _h_tril, "TRIU": _h_triu, "VAR": _h_var,
+    "TRIL": _h_tril, "TRIU": _h_triu, "VAR": _h_var, "REPEAT": _h_repeat, "REPEAT_INTERLEAVE": _h_repeat_interleave,
     "INDEX": _h_index,
     "BROADCAST_TO": _h_broadcast_to,
     "FUSED_ELEMENTWISE": _h_fused_elementwise,

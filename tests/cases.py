@@ -253,6 +253,10 @@ CASES: Dict[str, Case] = {
     "var_last": Case(_misc_inputs, lambda api, t, raw: t["x"].var(axis=-1)),
     "var_biased_keep": Case(_misc_inputs, lambda api, t, raw: t["x"].var(axis=(0, 2), keepdims=True, correction=0)),
     "var_all_f64": Case(_misc_inputs, lambda api, t, raw: t["d"].var()),
+    "repeat_tile": Case(_misc_inputs, lambda api, t, raw: t["x"].repeat(2, 1, 3), kind="exact"),
+    "repeat_new_axis": Case(_misc_inputs, lambda api, t, raw: t["row"].repeat(4, 2), kind="exact"),
+    "repeat_interleave_mid": Case(_misc_inputs, lambda api, t, raw: t["i"].repeat_interleave(3, 1), kind="exact"),
+    "repeat_interleave_fused": Case(_misc_inputs, lambda api, t, raw: (t["x"] * t["p"]).repeat_interleave(2, 2) + 1.0),
     "gather_rows": Case(_misc_inputs, lambda api, t, raw: t["table"].gather(0, t["tidx"]), kind="exact"),
     "gather_cols": Case(_misc_inputs, lambda api, t, raw: t["table"].gather(1, t["cidx"]), kind="exact"),
     "int_arith": Case(_misc_inputs, lambda api, t, raw: (t["i"] * t["j"] + t["i"]) * 3 + (-t["j"]),
