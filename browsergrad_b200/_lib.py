@@ -22,7 +22,8 @@ DTYPE_SIZE = {"float16": 2, "float32": 4, "float64": 8, "int8": 1, "int16": 2, "
 OPCODES = ("BUFFER", "LOAD", "CONST", "CAST", "ADD", "MUL", "DIV", "NEG", "EXP", "LOG", "ABS", "SIGN",
            "SIN", "COS", "ISNAN", "CMP", "WHERE", "MATMUL", "REDUCE", "RESHAPE", "PERMUTE",
            "BROADCAST_TO", "LAYER_NORM", "CROSS_ENTROPY", "INDEX", "FUSED_ELEMENTWISE",
-           "FUSED_SOFTMAX", "ATTENTION_FORWARD", "TRIL", "TRIU", "FLIP", "CONCAT", "CUMSUM")
+           "FUSED_SOFTMAX", "ATTENTION_FORWARD", "TRIL", "TRIU", "FLIP", "CONCAT", "CUMSUM",
+           "SORT_INDICES", "TOPK_INDICES")
 OP_CODE = {n: i for i, n in enumerate(OPCODES)}
 CMP_CODE = {"eq": 0, "ne": 1, "lt": 2, "le": 3, "gt": 4, "ge": 5}
 REDUCE_CODE = {"sum": 0, "max": 1, "min": 2, "mean": 3, "argmax": 4, "argmin": 5, "any": 6, "all": 7}

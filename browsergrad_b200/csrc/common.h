@@ -179,6 +179,11 @@ cudaError_t launch_place(const StridedView& in, void* out, int out_dtype, const 
 // cumsum along `axis` in the output dtype, sequential per line as NumPy's add.accumulate.
 cudaError_t launch_cumsum(const StridedView& in, void* out, int out_dtype, int axis, int reverse, cudaStream_t s);
 
+// Stable argsort of every line along `axis` (at most kSortMaxLine elements per line); the first `keep` positions of
+// each sorted line are written as int64 to the dense output (keep = line length for a full sort, k for top-k).
+constexpr int kSortMaxLine = 4096;
+cudaError_t launch_sort_lines(const StridedView& in, int64_t* out, int axis, int descending, int64_t keep, cudaStream_t s);
+
 // out[...] = in[view] : dense copy of a strided view (permute / broadcast materialisation).
 cudaError_t launch_strided_copy(const StridedView& in, void* out, int64_t numel, cudaStream_t s);
 // Generic [outer, R, inner] reductions / softmax on dense data (any inner), fp32/fp64/int64.

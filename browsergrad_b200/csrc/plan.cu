@@ -591,6 +591,7 @@ void Compiler::build_views() {
         break;
       case BG_OP_MATMUL: case BG_OP_INDEX: case BG_OP_CROSS_ENTROPY:
       case BG_OP_TRIL: case BG_OP_TRIU: case BG_OP_FLIP: case BG_OP_CONCAT: case BG_OP_CUMSUM:
+      case BG_OP_SORT_INDICES: case BG_OP_TOPK_INDICES:
         kind_[i] = K_OTHER;
         v.set_dense(n.shape, n.rank);
         v.slot = new_slot(n.numel() * dtype_size(n.dtype), false, i);
@@ -2286,10 +2287,24 @@ void Compiler::emit_shape_op(int n, int key) {
   const int rank = t.rank;
   const int64_t a0 = t.iarg[0];
   const View& x0 = view_[resolve(t.in[0])];
+  const bool ordering = t.op == BG_OP_SORT_INDICES || t.op == BG_OP_TOPK_INDICES;
   if (t.op != BG_OP_CONCAT) {
     if (x0.rank != rank) err(BG_ERR_INVALID, std::string(op_name(t.op)) + ": result rank differs from the input's");
     for (int d = 0; d < rank; ++d)
-      if (x0.shape[d] != t.shape[d]) err(BG_ERR_INVALID, std::string(op_name(t.op)) + ": result shape differs from the input's");
+      if (x0.shape[d] != t.shape[d] && !(t.op == BG_OP_TOPK_INDICES && d == a0))
+        err(BG_ERR_INVALID, std::string(op_name(t.op)) + ": result shape differs from the input's");
+  }
+  int64_t keep = 0;
+  if (ordering) {
+    if (rank == 0 || a0 < 0 || a0 >= rank) err(BG_ERR_INVALID, std::string(op_name(t.op)) + ": axis out of range");
+    if (t.dtype != BG_I64) err(BG_ERR_INVALID, std::string(op_name(t.op)) + ": positions are int64");
+    if (x0.shape[a0] > kSortMaxLine)
+      err(BG_ERR_UNSUPPORTED, std::string(op_name(t.op)) + ": lines longer than " + std::to_string(kSortMaxLine) + " elements are not supported");
+    keep = t.op == BG_OP_SORT_INDICES ? x0.shape[a0] : t.iarg[1];
+    if (t.op == BG_OP_TOPK_INDICES) {
+      if (keep < 0 || keep > x0.shape[a0] || t.shape[a0] != keep) err(BG_ERR_INVALID, "TOPK_INDICES: k does not match the shapes");
+      if (!t.iarg[3]) err(BG_ERR_UNSUPPORTED, "TOPK_INDICES: sorted=False has no defined order to reproduce");
+    }
   }
   if ((t.op == BG_OP_TRIL || t.op == BG_OP_TRIU)) {
     if (rank < 2) err(BG_ERR_INVALID, "TRIL/TRIU: at least two dimensions required");
@@ -2316,14 +2331,16 @@ void Compiler::emit_shape_op(int n, int key) {
   own_slot(n);
   const int so = view_[n].slot, op = t.op, out_dt = t.dtype;
   const int64_t numel = t.numel();
-  const int reverse = (int)t.iarg[1];
+  const int reverse = (int)t.iarg[1];      // CUMSUM: reverse; SORT_INDICES: descending
+  const int largest = (int)t.iarg[2];
   std::vector<int64_t> oshape(t.shape, t.shape + rank);
   PUnit pu;
   pu.order_key = key;
   pu.dep_nodes = deps;
   pu.out_nodes = {n};
   pu.u.launches = op == BG_OP_CONCAT ? n_in : 1;
-  pu.u.name = op == BG_OP_CONCAT ? "place[CONCAT]" : (op == BG_OP_CUMSUM ? "scan[CUMSUM]" : std::string("index_map[") + op_name(op) + "]");
+  pu.u.name = op == BG_OP_CONCAT ? "place[CONCAT]" : (op == BG_OP_CUMSUM ? "scan[CUMSUM]"
+              : (ordering ? std::string("sort_lines[") + op_name(op) + "]" : std::string("index_map[") + op_name(op) + "]"));
   pu.u.fn = [=](Run& r) {
     cudaError_t e = cudaSuccess;
     for (size_t k = 0; k < srcs.size() && e == cudaSuccess; ++k) {
@@ -2334,6 +2351,10 @@ void Compiler::emit_shape_op(int n, int key) {
         case BG_OP_TRIU: e = launch_tri(v, r.ptr[so], numel, 1, a0, r.ctx->stream); break;
         case BG_OP_FLIP: e = launch_flip(v, r.ptr[so], numel, (int)a0, r.ctx->stream); break;
         case BG_OP_CUMSUM: e = launch_cumsum(v, r.ptr[so], out_dt, (int)a0, reverse, r.ctx->stream); break;
+        case BG_OP_SORT_INDICES:
+          e = launch_sort_lines(v, reinterpret_cast<int64_t*>(r.ptr[so]), (int)a0, reverse, keep, r.ctx->stream); break;
+        case BG_OP_TOPK_INDICES:
+          e = launch_sort_lines(v, reinterpret_cast<int64_t*>(r.ptr[so]), (int)a0, largest, keep, r.ctx->stream); break;
         default: e = launch_place(v, r.ptr[so], out_dt, oshape.data(), (int)a0, axis_off[k], r.ctx->stream); break;
       }
     }
@@ -2497,7 +2518,8 @@ bool Compiler::try_lower() {
         case BG_OP_MATMUL: emit_matmul(i, i); break;
         case BG_OP_INDEX: emit_index(i, i); break;
         case BG_OP_CROSS_ENTROPY: emit_ce(i, i); break;
-        case BG_OP_TRIL: case BG_OP_TRIU: case BG_OP_FLIP: case BG_OP_CONCAT: case BG_OP_CUMSUM: emit_shape_op(i, i); break;
+        case BG_OP_TRIL: case BG_OP_TRIU: case BG_OP_FLIP: case BG_OP_CONCAT: case BG_OP_CUMSUM:
+        case BG_OP_SORT_INDICES: case BG_OP_TOPK_INDICES: emit_shape_op(i, i); break;
         case BG_OP_RESHAPE: emit_copy(i, copy_src_.at(i), resolve(n.in[0]), i); break;
         default: err(BG_ERR_UNSUPPORTED, std::string("opcode ") + op_name(n.op));
       }

@@ -215,3 +215,97 @@ cudaError_t launch_cumsum(const StridedView& in, void* out, int out_dtype, int a
 }
 
 }  // namespace bg
+
+// ---- stable ordering of lines (SORT_INDICES, TOPK_INDICES) ------------------------------------------
+// One CTA sorts one line in shared memory with a bitonic network over (key, position) pairs.  Keys are the
+// values mapped to unsigned integers whose order is NumPy's sort order: -0.0 and +0.0 compare equal, NaNs
+// are the largest values and equal to each other; ties keep their original order because the position is
+// the low word of the comparison.  A descending order complements the key, which puts NaNs first and still
+// keeps ties in original order -- what the reference obtains by sorting the reversed line and flipping back.
+namespace bg {
+namespace {
+
+__device__ __forceinline__ unsigned long long sort_key(const void* p, int dt, int64_t off) {
+  switch (dt) {
+    case BG_F64: {
+      double v = reinterpret_cast<const double*>(p)[off];
+      if (v != v) return ~0ull;
+      if (v == 0.0) v = 0.0;
+      unsigned long long b = (unsigned long long)__double_as_longlong(v);
+      return (b >> 63) ? ~b : (b | 0x8000000000000000ull);
+    }
+    case BG_F32: case BG_F16: case BG_BF16: {
+      float v = dt == BG_F32 ? reinterpret_cast<const float*>(p)[off]
+                : dt == BG_F16 ? __half2float(reinterpret_cast<const __half*>(p)[off])
+                               : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[off]);
+      if (v != v) return ~0ull;
+      if (v == 0.f) v = 0.f;
+      unsigned b = __float_as_uint(v);
+      b = (b >> 31) ? ~b : (b | 0x80000000u);
+      return (unsigned long long)b << 32;
+    }
+    case BG_U64: return reinterpret_cast<const unsigned long long*>(p)[off];
+    default: return (unsigned long long)load_as_i64(p, dt, off) ^ 0x8000000000000000ull;
+  }
+}
+
+__global__ void __launch_bounds__(256) sort_lines_kernel(ViewArg in, int in_dtype, int64_t* out, int axis, int descending, int64_t keep,
+                                                         int64_t inner, int n2) {
+  extern __shared__ __align__(16) unsigned char sort_smem[];
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(sort_smem);
+  unsigned* pos = reinterpret_cast<unsigned*>(keys + n2);
+  const int64_t len = in.shape[axis];
+  const int64_t line = blockIdx.x;
+  const int64_t in_pos = line % inner, outer = line / inner;
+  int64_t src0 = 0, rem = in_pos;
+  for (int d = in.rank - 1; d > axis; --d) { src0 += (rem % in.shape[d]) * in.stride[d]; rem /= in.shape[d]; }
+  rem = outer;
+  for (int d = axis - 1; d >= 0; --d) { src0 += (rem % in.shape[d]) * in.stride[d]; rem /= in.shape[d]; }
+  for (int i = threadIdx.x; i < n2; i += blockDim.x) {
+    if (i < len) {
+      const unsigned long long k = sort_key(in.ptr, in_dtype, src0 + i * in.stride[axis]);
+      keys[i] = descending ? ~k : k;
+      pos[i] = (unsigned)i;
+    } else {
+      keys[i] = ~0ull;             // padding sorts behind every element (its position word is the largest too)
+      pos[i] = 0xffffffffu;
+    }
+  }
+  __syncthreads();
+  for (int size = 2; size <= n2; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = threadIdx.x; i < n2 / 2; i += blockDim.x) {
+        const int lo = 2 * i - (i & (stride - 1)), hi = lo + stride;
+        const bool up = (lo & size) == 0;
+        const unsigned long long ka = keys[lo], kb = keys[hi];
+        const unsigned pa = pos[lo], pb = pos[hi];
+        const bool a_after_b = ka > kb || (ka == kb && pa > pb);
+        if (a_after_b == up) { keys[lo] = kb; keys[hi] = ka; pos[lo] = pb; pos[hi] = pa; }
+      }
+      __syncthreads();
+    }
+  }
+  const int64_t dst0 = outer * keep * inner + in_pos;
+  for (int64_t i = threadIdx.x; i < keep; i += blockDim.x) out[dst0 + i * inner] = (int64_t)pos[i];
+}
+
+}  // namespace
+
+cudaError_t launch_sort_lines(const StridedView& in, int64_t* out, int axis, int descending, int64_t keep, cudaStream_t s) {
+  if (axis < 0 || axis >= in.rank) return cudaErrorInvalidValue;
+  const int64_t len = in.shape[axis];
+  if (len > kSortMaxLine || keep > len) return cudaErrorInvalidValue;
+  int64_t lines = 1, inner = 1;
+  for (int d = 0; d < in.rank; ++d)
+    if (d != axis) lines *= in.shape[d];
+  for (int d = axis + 1; d < in.rank; ++d) inner *= in.shape[d];
+  if (lines == 0 || len == 0 || keep == 0) return cudaSuccess;
+  if (lines > 0x7fffffff) return cudaErrorInvalidValue;
+  int n2 = 2;
+  while (n2 < len) n2 <<= 1;
+  const size_t smem = (size_t)n2 * 12;
+  sort_lines_kernel<<<(unsigned)lines, 256, smem, s>>>(to_arg(in), in.dtype, out, axis, descending, keep, inner, n2);
+  return cudaGetLastError();
+}
+
+}  // namespace bg

@@ -359,6 +359,12 @@ class Tensor:
     def triu(self, diagonal: int = 0) -> "Tensor":
         return self._triangular(diagonal, True)
 
+    def sort(self, dim: int = -1, descending: bool = False, *, stable: bool = False) -> Tuple["Tensor", "Tensor"]:
+        return sort(self, dim=dim, descending=descending, stable=stable)
+
+    def topk(self, k: int, dim: Any = None, largest: bool = True, sorted: bool = True) -> Tuple["Tensor", "Tensor"]:
+        return topk(self, k, dim=dim, largest=largest, sorted=sorted)
+
     def cumsum(self, dim: int, dtype: Any = None) -> "Tensor":
         return cumsum(self, dim=dim, dtype=dtype)
 
@@ -555,6 +561,29 @@ def attention_forward(q: Tensor, k: Tensor, v: Tensor) -> Tensor:
     scale = float(np.float32(1.0 / np.sqrt(q.shape[-1])))
     return Tensor(Node("ATTENTION_FORWARD", (q._uop, k._uop, v._uop), q.shape, "float32",
                        {"scale": scale, "mask": "none"}), q._store)
+
+
+def sort(x: Tensor, dim: int = -1, descending: bool = False, *, stable: bool = False) -> Tuple[Tensor, Tensor]:
+    """``(values, indices)`` as ``SORT_VALUES(x, SORT_INDICES(x))`` (_tensor_proxy.py:2558-2628); the order is
+    always the stable one (equal values keep their original order, ascending or descending)."""
+    axis = int(dim) % max(x.ndim, 1)
+    arg = {"axis": axis, "descending": bool(descending), "stable": bool(stable)}
+    idx = Node("SORT_INDICES", (x._uop,), x.shape, "int64", dict(arg))
+    val = Node("SORT_VALUES", (x._uop, idx), x.shape, x.dtype, dict(arg))
+    return x._wrap(val), x._wrap(idx)
+
+
+def topk(x: Tensor, k: int, dim: Any = None, largest: bool = True, sorted: bool = True) -> Tuple[Tensor, Tensor]:
+    """``(values, indices)`` as ``TOPK_VALUES(x, TOPK_INDICES(x))`` (_tensor_proxy.py:2630-2701)."""
+    axis = (x.ndim - 1 if dim is None else int(dim)) % max(x.ndim, 1)
+    k = int(k)
+    if k < 0 or k > x.shape[axis]:
+        raise ValueError(f"topk: k={k} outside [0, {x.shape[axis]}]")
+    out_shape = tuple(k if i == axis else d for i, d in enumerate(x.shape))
+    arg = {"axis": axis, "k": k, "largest": bool(largest), "sorted": bool(sorted)}
+    idx = Node("TOPK_INDICES", (x._uop,), out_shape, "int64", dict(arg))
+    val = Node("TOPK_VALUES", (x._uop, idx), out_shape, x.dtype, dict(arg))
+    return x._wrap(val), x._wrap(idx)
 
 
 def cumsum(x: Tensor, dim: int = 0, *, dtype: Any = None) -> Tensor:

@@ -252,7 +252,8 @@ def lower_composites(root: Any) -> Any:
       in the result dtype -- the two passes of ``np.var(dtype=...)``;
     * ``STACK`` -> ``CONCAT`` of the inputs reshaped with a unit axis;
     * ``REPEAT`` / ``REPEAT_INTERLEAVE`` -> ``RESHAPE`` / ``BROADCAST_TO`` / ``RESHAPE`` (``np.tile`` / ``np.repeat``,
-      _realize.py:329-332, :360-363).
+      _realize.py:329-332, :360-363);
+    * ``SORT_VALUES`` / ``TOPK_VALUES`` -> ``INDEX`` along the ordering axis (_realize.py:1149-1176).
     """
     def make(like: Any, op: str, inputs: tuple, shape: tuple, dtype: str, arg: Any) -> Any:
         return type(like)(op=op, inputs=inputs, shape=tuple(shape), dtype=dtype, arg=arg)
@@ -296,6 +297,9 @@ def lower_composites(root: Any) -> Any:
                 shp = tuple(x.shape[:axis]) + (1,) + tuple(x.shape[axis:])
                 parts.append(make(node, "RESHAPE", (x,), shp, x.dtype, {"new_shape": shp}))
             return make(node, "CONCAT", tuple(parts), node.shape, node.dtype, {"axis": axis})
+        if node.op in ("SORT_VALUES", "TOPK_VALUES"):
+            # np.take_along_axis(source, indices, axis): the gather opcode with the same axis
+            return make(node, "INDEX", ins, node.shape, node.dtype, {"dim": int(node.arg["axis"])})
         if node.op in ("REPEAT", "REPEAT_INTERLEAVE"):
             # a unit axis beside every repeated one, broadcast to the factor, folded back: views until the final RESHAPE
             (x,) = ins

@@ -176,6 +176,14 @@ def encode_plan(plan: Dict[str, Any], permute_axes: Optional[Dict[int, Tuple[int
         elif op == "CUMSUM":
             st.iarg[0] = int(arg["axis"])
             st.iarg[1] = 1 if arg.get("reverse") else 0
+        elif op == "SORT_INDICES":
+            st.iarg[0] = int(arg["axis"])
+            st.iarg[1] = 1 if arg.get("descending") else 0
+        elif op == "TOPK_INDICES":
+            st.iarg[0] = int(arg["axis"])
+            st.iarg[1] = int(arg["k"])
+            st.iarg[2] = 1 if arg.get("largest", True) else 0
+            st.iarg[3] = 1 if arg.get("sorted", True) else 0
         elif op == "CROSS_ENTROPY":
             if arg.get("target_mode", "indices") != "indices" or arg.get("has_weight") or arg.get("label_smoothing"):
                 raise JitNotImplementedError(

@@ -69,7 +69,11 @@ typedef enum bg_opcode {
      _realize.py:268-327): iarg[0] = axis (FLIP, CUMSUM, CONCAT) or diagonal (TRIL, TRIU);
      CUMSUM iarg[1] = reverse.  CONCAT takes up to BG_MAX_STEP_INPUTS inputs. */
   BG_OP_TRIL = 28, BG_OP_TRIU = 29, BG_OP_FLIP = 30, BG_OP_CONCAT = 31, BG_OP_CUMSUM = 32,
-  BG_OP_COUNT = 33
+  /* Stable ordering along iarg[0] (_framework_contracts.py:4921-4936, :5063-5089), int64 positions out:
+     SORT_INDICES iarg[1] = descending; TOPK_INDICES iarg[1] = k, iarg[2] = largest, iarg[3] = sorted (must be 1).
+     The *_VALUES opcodes of the reference are gathers along the same axis and arrive as INDEX. */
+  BG_OP_SORT_INDICES = 33, BG_OP_TOPK_INDICES = 34,
+  BG_OP_COUNT = 35
 } bg_opcode;
 
 typedef enum bg_cmp { BG_CMP_EQ = 0, BG_CMP_NE = 1, BG_CMP_LT = 2, BG_CMP_LE = 3,

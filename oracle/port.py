@@ -203,6 +203,46 @@ def _h_repeat_interleave(node, vt, store):  # _realize.py:360-363
                     dtype=np.dtype(node.dtype), copy=True)
 
 
+def _stable_sort_indices(array, axis, descending):  # _framework_contracts.py:4921-4936
+    if array.ndim == 0:
+        return np.asarray(0, dtype=np.int64)
+    if descending:
+        reversed_indices = np.argsort(np.flip(array, axis=axis), axis=axis, kind="stable")
+        result = array.shape[axis] - 1 - np.flip(reversed_indices, axis=axis)
+    else:
+        result = np.argsort(array, axis=axis, kind="stable")
+    return np.array(result, dtype=np.int64, copy=True)
+
+
+def _h_sort_indices(node, vt, store):  # _realize.py:1143-1146
+    return _stable_sort_indices(_in(node, vt, 0), int(node.arg["axis"]), bool(node.arg.get("descending", False)))
+
+
+def _h_take_along(node, vt, store):  # SORT_VALUES / TOPK_VALUES, _realize.py:1149-1176
+    source, indices = _in(node, vt, 0), _in(node, vt, 1)
+    if source.ndim == 0:
+        return np.array(source, dtype=np.dtype(node.dtype), copy=True)
+    return np.array(np.take_along_axis(source, indices, axis=int(node.arg["axis"])), dtype=np.dtype(node.dtype), copy=True)
+
+
+def _h_topk_indices(node, vt, store):  # _framework_contracts.py:5063-5089
+    array, axis, k = _in(node, vt, 0), int(node.arg["axis"]), int(node.arg["k"])
+    largest, sorted_output = bool(node.arg.get("largest", True)), bool(node.arg.get("sorted", True))
+    out_shape = list(array.shape)
+    out_shape[axis] = k
+    if k == 0:
+        return np.empty(tuple(out_shape), dtype=np.int64)
+    extent = array.shape[axis]
+    partition = np.argpartition(array, kth=extent - k if largest else k - 1, axis=axis)
+    slices = [slice(None)] * array.ndim
+    slices[axis] = slice(extent - k, None) if largest else slice(0, k)
+    selected = np.array(partition[tuple(slices)], dtype=np.int64, copy=True)
+    if sorted_output:
+        order = _stable_sort_indices(np.take_along_axis(array, selected, axis=axis), axis, largest)
+        selected = np.take_along_axis(selected, order, axis=axis)
+    return np.array(selected, dtype=np.int64, copy=True)
+
+
 def _h_where(node, vt, store):  # _realize.py:1453-1459
     sel = np.where(_in(node, vt, 0), _in(node, vt, 1), _in(node, vt, 2))
     return np.array(sel, dtype=np.dtype(node.dtype), copy=True).reshape(node.shape)
@@ -354,6 +394,7 @@ _DISPATCH: Dict[str, Callable] = {
     "WHERE": _h_where,
     "CLAMP": _h_clamp, "FLIP": _h_flip, "CUMSUM": _h_cumsum, "CONCAT": _h_concat, "STACK": _h_stack,
     "TRIL": _h_tril, "TRIU": _h_triu, "VAR": _h_var, "REPEAT": _h_repeat, "REPEAT_INTERLEAVE": _h_repeat_interleave,
+    "SORT_INDICES": _h_sort_indices, "SORT_VALUES": _h_take_along, "TOPK_INDICES": _h_topk_indices, "TOPK_VALUES": _h_take_along,
     "INDEX": _h_index,
     "BROADCAST_TO": _h_broadcast_to,
     "FUSED_ELEMENTWISE": _h_fused_elementwise,

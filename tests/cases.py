@@ -28,6 +28,7 @@ class RefApi:
         self.autocast = lambda dtype="float16": bg.amp.autocast(dtype=dtype)
         self.from_numpy = bg.from_numpy
         self.cat, self.stack, self.cumsum = bg.cat, bg.stack, bg.cumsum
+        self.sort, self.topk = bg.sort, bg.topk
 
 
 def canonical_arg(op: str, arg: Any) -> Any:
@@ -126,6 +127,23 @@ def _attn_growing(b: int, h: int, s: int, d: int) -> Callable[[], Dict[str, np.n
         t["mask"] = configs.causal_mask(s)
         return t
     return make
+
+
+def _sort_inputs() -> Dict[str, np.ndarray]:
+    r = _rng(400)
+    special = r.standard_normal((5, 40), dtype=np.float32)
+    special[:, ::7] = np.nan
+    special[:, 1::9] = 0.0
+    special[:, 2::9] = -0.0
+    special[:, 3::11] = np.inf
+    special[:, 5::13] = -np.inf
+    return {
+        "x": r.standard_normal((4, 9, 37), dtype=np.float32),
+        "d": r.standard_normal((6, 100)),
+        "ties": r.integers(0, 4, (33, 50), dtype=np.int64),
+        "special": special,
+        "long": r.standard_normal((3, 3000), dtype=np.float32),
+    }
 
 
 def _gpt_tiny() -> Dict[str, np.ndarray]:
@@ -253,6 +271,18 @@ CASES: Dict[str, Case] = {
     "var_last": Case(_misc_inputs, lambda api, t, raw: t["x"].var(axis=-1)),
     "var_biased_keep": Case(_misc_inputs, lambda api, t, raw: t["x"].var(axis=(0, 2), keepdims=True, correction=0)),
     "var_all_f64": Case(_misc_inputs, lambda api, t, raw: t["d"].var()),
+    # stable orderings: ties (small integer keys, repeated floats, signed zeros, NaNs) must keep their original order
+    "sort_idx_last": Case(_sort_inputs, lambda api, t, raw: api.sort(t["x"], 2)[1], kind="exact"),
+    "sort_val_desc_mid": Case(_sort_inputs, lambda api, t, raw: api.sort(t["x"], 1, True)[0], kind="exact"),
+    "sort_idx_ties_desc": Case(_sort_inputs, lambda api, t, raw: api.sort(t["ties"], 1, True)[1], kind="exact"),
+    "sort_idx_ties_first": Case(_sort_inputs, lambda api, t, raw: api.sort(t["ties"], 0)[1], kind="exact"),
+    "sort_idx_special": Case(_sort_inputs, lambda api, t, raw: api.sort(t["special"], 1)[1], kind="exact"),
+    "sort_idx_special_desc": Case(_sort_inputs, lambda api, t, raw: api.sort(t["special"], 1, True)[1], kind="exact"),
+    "sort_idx_long": Case(_sort_inputs, lambda api, t, raw: api.sort(t["long"], 1)[1], kind="exact"),
+    "sort_val_f64": Case(_sort_inputs, lambda api, t, raw: api.sort(t["d"], 1)[0], kind="exact"),
+    "topk_val_last": Case(_sort_inputs, lambda api, t, raw: api.topk(t["x"], 5, 2)[0], kind="exact"),
+    "topk_idx_smallest_mid": Case(_sort_inputs, lambda api, t, raw: api.topk(t["x"], 3, 1, False)[1], kind="exact"),
+    "topk_then_softmax": Case(_sort_inputs, lambda api, t, raw: api.softmax(api.topk(t["long"], 64, 1)[0], dim=-1)),
     "repeat_tile": Case(_misc_inputs, lambda api, t, raw: t["x"].repeat(2, 1, 3), kind="exact"),
     "repeat_new_axis": Case(_misc_inputs, lambda api, t, raw: t["row"].repeat(4, 2), kind="exact"),
     "repeat_interleave_mid": Case(_misc_inputs, lambda api, t, raw: t["i"].repeat_interleave(3, 1), kind="exact"),
