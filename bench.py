@@ -307,11 +307,12 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn
         store = graph.BufferStore()
         t = {k: graph.from_numpy(v, store) for k, v in arrays.items()}
         root = configs.gpt_forward(graph, t, meta)
-        ms, prof, trace = time_plan(bridge, torch, stream, root, store, front, max(2, steps // 2), warmup=2)
+        gpt_steps = max(3, steps // 2)
+        ms, prof, trace = time_plan(bridge, torch, stream, root, store, front, gpt_steps, warmup=3)
         top = sorted(prof, key=lambda p: -p["ms"])[:6]
         out["gpt"].append({"workload": "GPT decoder forward 12L d768 h12 mlp3072 V32000 seq1024, batch 8 (one GPU's shard of 64), fp32 graph (3xTF32)",
                            "tokens_per_s": 8 * 1024 / (ms * 1e-3), "plan_ms": ms, "units": len(trace),
-                           "top_kernels": [{"name": p["name"], "ms_per_forward": p["ms"] / max(2, steps // 2)} for p in top]})
+                           "top_kernels": [{"name": p["name"], "ms_per_forward": p["ms"] / gpt_steps} for p in top]})
         del arrays, store, t
     return out
 
