@@ -245,6 +245,8 @@ bool tc_gemm_supported(int64_t M, int64_t N, int64_t K, int ab_dtype);
 cudaError_t launch_gemm_tc(const TcGemm& g, int* status, cudaStream_t s);
 // hi = tf32(x) (round to nearest), lo = x - hi, for fp32 or fp64 input; optional transpose is not done here.
 cudaError_t launch_tf32_split(const void* src, int src_dtype, float* hi, float* lo, int64_t n, cudaStream_t s);
+// dst (f16 / bf16) = round-to-nearest-even(src fp32), dense, eight elements per thread step.
+cudaError_t launch_convert16(const float* src, void* dst, int64_t n, int dtype16, cudaStream_t s);
 
 // Fused attention (attn_tc.cu).  Operands are [B,H,S,D] views with element strides; D = 64.
 struct AttnOperand {

@@ -32,12 +32,34 @@ int cuda_fail(bg_context* ctx, cudaError_t e, const char* what) {
   return fail(ctx, e == cudaErrorMemoryAllocation ? BG_ERR_OOM : BG_ERR_CUDA, m);
 }
 
+static size_t padded_size(int64_t logical_bytes) { return ((size_t)(logical_bytes > 0 ? logical_bytes : 1) + 255) & ~(size_t)255; }
+
+static void flush_block_cache(bg_context* ctx) {
+  for (auto& kv : ctx->block_cache) cudaFreeAsync(kv.second, ctx->stream);
+  ctx->block_cache.clear();
+  ctx->block_cache_bytes = 0;
+}
+
 int dev_alloc(bg_context* ctx, int64_t logical_bytes, void** out) {
-  size_t padded = ((size_t)(logical_bytes > 0 ? logical_bytes : 1) + 255) & ~(size_t)255;
-  cudaError_t e = cudaMallocAsync(out, padded, ctx->stream);
-  if (e != cudaSuccess) {
-    cudaGetLastError();
-    return cuda_fail(ctx, e, "device allocation");
+  const size_t padded = padded_size(logical_bytes);
+  auto hit = ctx->block_cache.find(padded);
+  if (hit != ctx->block_cache.end()) {
+    *out = hit->second;
+    ctx->block_cache.erase(hit);
+    ctx->block_cache_bytes -= padded;
+  } else {
+    cudaError_t e = cudaMallocAsync(out, padded, ctx->stream);
+    if (e != cudaSuccess && !ctx->block_cache.empty()) {
+      // give the kept blocks back to the pool and try once more
+      cudaGetLastError();
+      flush_block_cache(ctx);
+      cudaStreamSynchronize(ctx->stream);
+      e = cudaMallocAsync(out, padded, ctx->stream);
+    }
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return cuda_fail(ctx, e, "device allocation");
+    }
   }
   ctx->cur_bytes += logical_bytes;
   ctx->total_alloc += logical_bytes;
@@ -47,7 +69,13 @@ int dev_alloc(bg_context* ctx, int64_t logical_bytes, void** out) {
 
 void dev_free(bg_context* ctx, void* p, int64_t logical_bytes) {
   if (!p) return;
-  cudaFreeAsync(p, ctx->stream);
+  const size_t padded = padded_size(logical_bytes);
+  if (padded >= (64u << 10) && ctx->block_cache_bytes + padded <= ctx->block_cache_cap && ctx->block_cache.size() < 4096) {
+    ctx->block_cache.emplace(padded, p);
+    ctx->block_cache_bytes += padded;
+  } else {
+    cudaFreeAsync(p, ctx->stream);
+  }
   ctx->cur_bytes -= logical_bytes;
   ctx->total_rel += logical_bytes;
 }
@@ -240,6 +268,29 @@ void split_planes_drop(bg_context* ctx, const void* ptr) {
   ctx->split_planes.erase(it);
 }
 
+void* cast_copy_for(bg_context* ctx, const void* ptr, int64_t bytes, int dtype, bool* fresh) {
+  *fresh = false;
+  auto it = ctx->cast_copies.find(ptr);
+  if (it != ctx->cast_copies.end()) {
+    if (it->second.bytes == bytes && it->second.dtype == dtype) return it->second.buf;
+    dev_free(ctx, it->second.buf, it->second.bytes);
+    ctx->cast_copies.erase(it);
+  }
+  if (ctx->cast_copies.size() >= 4096) return nullptr;
+  void* buf = nullptr;
+  if (dev_alloc(ctx, bytes, &buf) != BG_OK) return nullptr;
+  ctx->cast_copies[ptr] = {buf, bytes, dtype};
+  *fresh = true;
+  return buf;
+}
+
+void cast_copy_drop(bg_context* ctx, const void* ptr) {
+  auto it = ctx->cast_copies.find(ptr);
+  if (it == ctx->cast_copies.end()) return;
+  dev_free(ctx, it->second.buf, it->second.bytes);
+  ctx->cast_copies.erase(it);
+}
+
 static int64_t numel_of(const int64_t* shape, int rank) {
   int64_t n = 1;
   for (int i = 0; i < rank; ++i) n *= shape[i];
@@ -296,10 +347,13 @@ int bg_destroy(bg_context* ctx) {
   cudaStreamSynchronize(ctx->stream);
   for (auto& kv : ctx->handles) cudaFreeAsync(kv.second.ptr, ctx->stream);
   ctx->handles.clear();
+  flush_block_cache(ctx);
   for (auto& kv : ctx->mask_classes) cudaFreeAsync(kv.second.buf, ctx->stream);
   ctx->mask_classes.clear();
   for (auto& kv : ctx->split_planes) cudaFreeAsync(kv.second.buf, ctx->stream);
   ctx->split_planes.clear();
+  for (auto& kv : ctx->cast_copies) cudaFreeAsync(kv.second.buf, ctx->stream);
+  ctx->cast_copies.clear();
   ctx->plan_cache.clear();
   for (auto& pe : ctx->pending_events) {
     cudaEventDestroy(pe.second.first);
@@ -375,6 +429,7 @@ int bg_release(bg_context* ctx, bg_handle h) {
   uniform_flag_drop(ctx, it->second.ptr);
   mask_classes_drop(ctx, it->second.ptr);
   split_planes_drop(ctx, it->second.ptr);
+  cast_copy_drop(ctx, it->second.ptr);
   dev_free(ctx, it->second.ptr, it->second.bytes);
   ctx->handles.erase(it);
   return BG_OK;

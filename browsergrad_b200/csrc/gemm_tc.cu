@@ -604,6 +604,32 @@ __global__ void tf32_split_kernel(const void* src, int src_dtype, float* hi, flo
   }
 }
 
+__global__ void convert16_kernel(const float* __restrict__ src, void* dst, int64_t n, int bf16) {
+  const int64_t n8 = n >> 3;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    const float4 a = __ldcs(reinterpret_cast<const float4*>(src) + 2 * i), b = __ldcs(reinterpret_cast<const float4*>(src) + 2 * i + 1);
+    uint32_t w[4];
+    if (bf16) {
+      __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
+      __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+      w[0] = *reinterpret_cast<uint32_t*>(&p0); w[1] = *reinterpret_cast<uint32_t*>(&p1);
+      w[2] = *reinterpret_cast<uint32_t*>(&p2); w[3] = *reinterpret_cast<uint32_t*>(&p3);
+    } else {
+      __half2 p0 = __floats2half2_rn(a.x, a.y), p1 = __floats2half2_rn(a.z, a.w);
+      __half2 p2 = __floats2half2_rn(b.x, b.y), p3 = __floats2half2_rn(b.z, b.w);
+      w[0] = *reinterpret_cast<uint32_t*>(&p0); w[1] = *reinterpret_cast<uint32_t*>(&p1);
+      w[2] = *reinterpret_cast<uint32_t*>(&p2); w[3] = *reinterpret_cast<uint32_t*>(&p3);
+    }
+    reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  // ragged end
+  if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
+    const int64_t i = (n8 << 3) + threadIdx.x;
+    if (bf16) reinterpret_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn(src[i]);
+    else reinterpret_cast<__half*>(dst)[i] = __float2half_rn(src[i]);
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -778,6 +804,18 @@ cudaError_t launch_gemm_tc(const TcGemm& g, int* status, cudaStream_t s) {
   const bool wide_tile = g.N > 128 && wide_tiles >= sms;
   if (tf32) return wide_tile ? launch_variant<256, true>(g, status, s) : launch_variant<128, true>(g, status, s);
   return wide_tile ? launch_variant<256, false>(g, status, s) : launch_variant<128, false>(g, status, s);
+}
+
+cudaError_t launch_convert16(const float* src, void* dst, int64_t n, int dtype16, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  // vector path needs 32-byte aligned source and 16-byte aligned destination; slots and handles are 256-byte aligned,
+  // view offsets inside them need not be
+  if ((reinterpret_cast<uintptr_t>(src) & 31) || (reinterpret_cast<uintptr_t>(dst) & 15)) return cudaErrorInvalidValue;
+  int64_t grid = (n / 8 + 255) / 256;
+  if (grid > 148 * 16) grid = 148 * 16;
+  if (grid < 1) grid = 1;
+  convert16_kernel<<<(unsigned)grid, 256, 0, s>>>(src, dst, n, dtype16 == BG_BF16 ? 1 : 0);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_tf32_split(const void* src, int src_dtype, float* hi, float* lo, int64_t n, cudaStream_t s) {

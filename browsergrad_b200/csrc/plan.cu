@@ -243,6 +243,10 @@ class Compiler {
   void emit_attention(int n, int key);
   void emit_shape_op(int n, int key);
   std::map<int, EpiPlan> epi_plan_;       // MATMUL node -> folded epilogue
+  // MATMUL node -> fp32 nodes behind absorbed fp32 -> 16-bit CASTs of its A / B operand (-1: operand used as is)
+  std::map<int, std::pair<int, int>> gemm_cast_src_;
+  int absorbable_cast(int node, int dtype16, int& cast_node);
+  void plan_gemm_casts();
   std::set<int> absorbed_groups_;
   int tc_mode(int n);                      // -1: SIMT; 0: 16-bit operands; 1: 3xTF32
   std::string act_expr(int node, int x, int g, int depth);
@@ -1671,6 +1675,62 @@ std::string Compiler::act_expr(int node, int x, int g, int depth) {
 
 // Fold the elementwise group that consumes a tensor-core product into the GEMM's epilogue when the
 // whole group is [CAST to fp32] -> [+ bias row] -> [relu | gelu] of that product.
+// The fp32 node whose CAST to `dtype16` is all that stands between it and `node` (through views only), when that
+// cast exists for this one consumer chain, is an elementwise group of its own and reads a dense fp32 tensor; -1 else.
+int Compiler::absorbable_cast(int node, int dtype16, int& cast_node) {
+  auto single = [&](int v) {
+    std::set<int> c(cons_[v].begin(), cons_[v].end());
+    return c.size() == 1 && v != root_;
+  };
+  int pnode = node;
+  while (kind_[pnode] == K_VIEW || kind_[pnode] == K_ALIAS) {
+    if (!single(pnode)) return -1;
+    pnode = resolve(nodes_[pnode].in[0]);
+  }
+  if (kind_[pnode] != K_EW || nodes_[pnode].op != BG_OP_CAST || nodes_[pnode].dtype != dtype16 || !single(pnode)) return -1;
+  const int g = find(pnode);
+  for (int i = 0; i < (int)nodes_.size(); ++i)
+    if (i != pnode && kind_[i] == K_EW && find(i) == g) return -1;    // fused with other elementwise work
+  const int src = resolve(nodes_[pnode].in[0]);
+  const View& sv = view_[src];
+  if (sv.is_const || sv.slot < 0 || sv.dtype != BG_F32 || !sv.contiguous() || sv.rank != nodes_[pnode].rank) return -1;
+  for (int d = 0; d < sv.rank; ++d)
+    if (sv.shape[d] != nodes_[pnode].shape[d]) return -1;
+  cast_node = pnode;
+  return src;
+}
+
+// Autocast Linear layers reach the tensor-core GEMM as MATMUL(CAST(x), PERMUTE(CAST(W))).  Where such a cast only
+// feeds this GEMM, the GEMM unit converts the operand itself with a vectorised pass (and keeps the converted copy
+// of a weight bound by handle with that handle), so the interpreter's CAST kernels and their outputs disappear.
+void Compiler::plan_gemm_casts() {
+  gemm_cast_src_.clear();
+  if (!ctx_->fusion || !ctx_->tensor_cores) return;
+  for (int n = 0; n < (int)nodes_.size(); ++n) {
+    if (kind_[n] != K_OTHER || nodes_[n].op != BG_OP_MATMUL) continue;
+    if (attn_plan_.count(n) || attn_absorbed_.count(n)) continue;
+    if (tc_mode(n) != 0) continue;
+    const int a = resolve(nodes_[n].in[0]), b = resolve(nodes_[n].in[1]);
+    const View& av = view_[a];
+    const View& bv = view_[b];
+    const int64_t K = av.shape[1];
+    // only operands the kernel reads in place: A dense [M,K], B dense [N,K] seen as [K,N]
+    const bool a_dense = av.stride[1] == 1 && av.stride[0] == K;
+    const bool b_kmajor = bv.stride[0] == 1 && bv.stride[1] == K;
+    int ca = -1, cb = -1;
+    int sa = a_dense ? absorbable_cast(a, av.dtype, ca) : -1;
+    int sb = b_kmajor ? absorbable_cast(b, bv.dtype, cb) : -1;
+    if (sa >= 0 && sb >= 0 && ca == cb) sb = -1;
+    // the conversion pass moves eight elements per step: the operand must start on a 32-byte boundary of its slot
+    if (sa >= 0 && (view_[sa].off + av.off) % 8 != 0) sa = -1;
+    if (sb >= 0 && (view_[sb].off + bv.off) % 8 != 0) sb = -1;
+    if (sa < 0 && sb < 0) continue;
+    gemm_cast_src_[n] = {sa, sb};
+    if (sa >= 0) attn_absorbed_.insert(ca);
+    if (sb >= 0) attn_absorbed_.insert(cb);
+  }
+}
+
 void Compiler::plan_tc_epilogues(const std::map<int, std::vector<int>>& groups) {
   epi_plan_.clear();
   absorbed_groups_.clear();
@@ -2093,6 +2153,44 @@ void Compiler::emit_matmul(int n, int key) {
       pu.order_key = key;
       pu.dep_nodes = {a, b};
       pu.out_nodes = {n};
+      // operands whose fp32 -> 16-bit cast was absorbed (plan_gemm_casts): read the fp32 tensor, convert here
+      int a_f32 = -1, b_f32 = -1;
+      {
+        auto it = gemm_cast_src_.find(n);
+        if (it != gemm_cast_src_.end()) { a_f32 = it->second.first; b_f32 = it->second.second; }
+      }
+      int a_conv = -1, b_conv = -1;
+      bool b_f32_leaf = false;
+      if (a_f32 >= 0) {
+        // the activation is converted by a unit of its own (its time shows up beside the GEMM's, not inside it)
+        const View& sv = view_[a_f32];
+        const int f32_slot = sv.slot;
+        const int64_t f32_off = (sv.off + av.off) * 4;
+        a_conv = new_slot(M * K * 2, false, -1);
+        PUnit cu;
+        cu.order_key = key;
+        cu.dep_nodes = {a_f32};
+        cu.u.writes.push_back(a_conv);
+        cu.u.name = std::string("convert16[") + dtype_name(ab) + "]";
+        const int conv_slot = a_conv;
+        cu.u.fn = [=](Run& r) {
+          cudaError_t e = launch_convert16(reinterpret_cast<const float*>(reinterpret_cast<char*>(r.ptr[f32_slot]) + f32_off),
+                                           r.ptr[conv_slot], M * K, ab, r.ctx->stream);
+          return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "operand conversion launch");
+        };
+        pu.dep_punits.push_back((int)punits_.size());
+        add_unit(std::move(cu));
+        pu.u.reads.push_back(a_conv);
+        a_src = a_conv; a_off = 0;
+        pu.dep_nodes.erase(pu.dep_nodes.begin());      // A now comes from the conversion unit
+      }
+      if (b_f32 >= 0) {
+        const View& sv = view_[b_f32];
+        b_src = sv.slot; b_off = (sv.off + bv.off) * 4;
+        b_f32_leaf = cp_->slots[b_src].external;
+        if (!b_f32_leaf) { b_conv = new_slot(N * K * 2, false, -1); pu.u.writes.push_back(b_conv); }
+        for (int& dn : pu.dep_nodes) if (dn == b) dn = b_f32;
+      }
       int a_copy = -1, b_copy = -1;
       StridedView ta{}, tb{};
       if (!a_dense) {
@@ -2152,7 +2250,7 @@ void Compiler::emit_matmul(int n, int key) {
         if (ep.act == TC_ACT_GELU) epi_name += "+gelu";
         pu.out_nodes = {ep.final_node};
       }
-      pu.u.launches = 1 + (a_copy >= 0) + (b_copy >= 0) + (mode == 1 ? (a_shared ? 0 : 1) + 1 : 0);
+      pu.u.launches = 1 + (a_copy >= 0) + (b_copy >= 0) + (mode == 1 ? (a_shared ? 0 : 1) + 1 : 0) + (b_f32 >= 0);
       pu.u.name = std::string(mode == 0 ? "gemm_tc" : "gemm_tc_3xtf32") + epi_name + "[" + dtype_name(t.dtype) + "]";
       cp_->uses_status = true;
       const int sc_slot = sc;
@@ -2195,6 +2293,25 @@ void Compiler::emit_matmul(int n, int key) {
           if (e != cudaSuccess) { if (tmp_planes) dev_free(r.ctx, tmp_planes, 2 * N * K * 4); return cuda_fail(r.ctx, e, "tf32 split launch"); }
           g.A = r.ptr[a_hi]; g.A_lo = r.ptr[a_lo]; g.B = bh; g.B_lo = bl;
         } else {
+          if (e == cudaSuccess && b_f32 >= 0) {
+            void* dst = nullptr;
+            bool convert = true;
+            if (b_f32_leaf) {
+              // a weight bound by handle keeps its 16-bit copy with the handle
+              bool fresh = false;
+              dst = r.from_handle[b_src] ? cast_copy_for(r.ctx, pb, N * K * 2, ab, &fresh) : nullptr;
+              if (dst) convert = fresh;
+              else {
+                if (int rc = dev_alloc(r.ctx, N * K * 2, &tmp_planes)) return rc;
+                dst = tmp_planes;
+              }
+            } else {
+              dst = r.ptr[b_conv];
+            }
+            if (convert) e = launch_convert16(reinterpret_cast<const float*>(pb), dst, N * K, ab, st);
+            pb = dst;
+          }
+          if (e != cudaSuccess) { if (tmp_planes) dev_free(r.ctx, tmp_planes, N * K * 2); return cuda_fail(r.ctx, e, "operand conversion launch"); }
           g.A = pa; g.B = pb;
         }
         g.C = r.ptr[epi->out_slot >= 0 ? epi->out_slot : sc_slot];
@@ -2207,7 +2324,7 @@ void Compiler::emit_matmul(int n, int key) {
         g.round_acc = epi->round_acc;
         g.wide = epi->wide;
         e = launch_gemm_tc(g, r.ctx->d_status, st);
-        if (tmp_planes) dev_free(r.ctx, tmp_planes, 2 * N * K * 4);    // stream-ordered: released after the GEMM has run
+        if (tmp_planes) dev_free(r.ctx, tmp_planes, mode == 1 ? 2 * N * K * 4 : N * K * 2);    // stream-ordered: released after the GEMM has run
         return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "tensor-core gemm launch");
       };
       tc_unit_of_[n] = (int)punits_.size();
@@ -2425,6 +2542,7 @@ bool Compiler::try_lower() {
   for (int i = 0; i < nn; ++i)
     if (kind_[i] == K_EW) groups[find(i)].push_back(i);
   plan_attention();
+  plan_gemm_casts();
   plan_tc_epilogues(groups);
   // only groups with a materialised member or a tail do any work
   for (auto& kv : groups) {

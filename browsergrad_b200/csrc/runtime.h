@@ -61,6 +61,15 @@ struct bg_context {
   // B operand (weights): split once, kept until the handle is released
   struct SplitPlanes { float* buf; int64_t n; int dtype; };
   std::unordered_map<const void*, SplitPlanes> split_planes;
+  // f16 / bf16 copies of fp32 matrices bound by handle that an autocast graph casts ahead of a GEMM (weights)
+  struct CastCopy { void* buf; int64_t bytes; int dtype; };
+  std::unordered_map<const void*, CastCopy> cast_copies;
+  // Freed device blocks kept for the next allocation of exactly the same (padded) size: repeated plans ask for the
+  // same sizes in the same order, so steady state makes no driver allocator call at all.  One stream per context, so
+  // reuse is ordered behind the block's last use.  Bounded by block_cache_cap; flushed on allocation failure.
+  std::unordered_multimap<size_t, void*> block_cache;
+  size_t block_cache_bytes = 0;
+  size_t block_cache_cap = (size_t)16 << 30;
 };
 
 namespace bg {
@@ -89,6 +98,9 @@ void mask_classes_drop(bg_context* ctx, const void* ptr);
 // set when they were just allocated and still have to be computed.  nullptr when the allocation fails.
 float* split_planes_for(bg_context* ctx, const void* ptr, int64_t n, int dtype, bool* fresh);
 void split_planes_drop(bg_context* ctx, const void* ptr);
+// 16-bit copy kept for the handle-backed fp32 matrix at `ptr`; *fresh is set when it still has to be computed.
+void* cast_copy_for(bg_context* ctx, const void* ptr, int64_t bytes, int dtype, bool* fresh);
+void cast_copy_drop(bg_context* ctx, const void* ptr);
 
 int run_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs, int n_inputs, void* out_host,
              size_t out_nbytes, bg_handle* out_handle);

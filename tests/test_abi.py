@@ -151,7 +151,7 @@ def test_b200_lowering_of_linear_and_attention():
     assert _lines_for("c3_tc_relu") == ["gemm_tc_3xtf32+bias+relu[float32]"]
     assert _lines_for("c3_tc_ragged") == ["gemm_tc_3xtf32+bias[float32]"]
     f16 = _lines_for("c3_tc_f16")
-    assert f16[-1] == "gemm_tc+bias+gelu[float16]" and all(ln.startswith(("ew[CAST", "static_ew[CAST")) for ln in f16[:-1]), f16
+    assert f16[-1] == "gemm_tc+bias+gelu[float16]" and all(ln.startswith(("ew[CAST", "static_ew[CAST", "convert16[")) for ln in f16[:-1]), f16
     assert _lines_for("c4_attn_mask_d64") == ["attention_tc_3xtf32+mask[float32]"]
     assert _lines_for("c4_attn_causal_tiles") == ["attention_tc_3xtf32+boolmask[float32]"]
     assert _lines_for("typed_attention_d64") == ["attention_tc_3xtf32[float32]"]

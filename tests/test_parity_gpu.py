@@ -201,3 +201,26 @@ def test_weight_planes_live_and_die_with_their_handle(bridge):
     assert first.tobytes() == second.tobytes()
     release_resident_leaves(bridge)
     assert bridge.resourceSnapshot()["currentBytes"] == base
+
+
+def test_autocast_linear_is_one_unit_and_keeps_the_weight_copy_with_its_handle(bridge):
+    """The fp32 -> 16-bit casts of x and W leave the interpreter: x is converted by a vectorised unit, the converted weight lives
+    with the weight's handle (second realization allocates nothing, release returns every byte)."""
+    from browsergrad_b200 import release_resident_leaves
+    for name, expect in (("c3_tc_bf16", ["convert16[bfloat16]", "gemm_tc+bias+gelu[bfloat16]"]),
+                         ("c3_tc_f16", ["convert16[float16]", "gemm_tc+bias+gelu[float16]"])):
+        case = CASES[name]
+        t, store, _ = build_case(case)
+        want = oracle_value(t, store)
+        base = bridge.resourceSnapshot()["currentBytes"]
+        first = realize_cuda(t, bridge, resident_leaves=True)
+        assert bridge.last_plan_trace() == expect
+        held = bridge.resourceSnapshot()["currentBytes"]
+        second = realize_cuda(t, bridge, resident_leaves=True)
+        assert bridge.resourceSnapshot()["currentBytes"] == held
+        check(case, first, want, name)
+        assert first.tobytes() == second.tobytes()
+        third = realize_cuda(t, bridge)                  # leaves passed by value: converted into temporaries
+        assert third.tobytes() == first.tobytes()
+        release_resident_leaves(bridge)
+        assert bridge.resourceSnapshot()["currentBytes"] == base
