@@ -26,7 +26,7 @@ OPCODES = ("BUFFER", "LOAD", "CONST", "CAST", "ADD", "MUL", "DIV", "NEG", "EXP",
            "SORT_INDICES", "TOPK_INDICES")
 OP_CODE = {n: i for i, n in enumerate(OPCODES)}
 CMP_CODE = {"eq": 0, "ne": 1, "lt": 2, "le": 3, "gt": 4, "ge": 5}
-REDUCE_CODE = {"sum": 0, "max": 1, "min": 2, "mean": 3, "argmax": 4, "argmin": 5, "any": 6, "all": 7}
+REDUCE_CODE = {"sum": 0, "max": 1, "min": 2, "mean": 3, "argmax": 4, "argmin": 5, "any": 6, "all": 7, "prod": 8}
 
 STATUS_NAMES = {1: "invalid argument", 2: "unsupported", 3: "CUDA error", 4: "out of device memory",
                 5: "unknown handle", 6: "device-side wait timed out", 7: "index out of range"}

@@ -69,7 +69,8 @@ struct AttnParams {
   const unsigned char* tile_class;   // [ceil(Sq/128), ceil(Sk/BKV)]: 0 skip, 1 plain, 2 binary mixed, 3 biased; null = none computed
   const uint32_t* mask_bits;         // [Sq, mask_words] "masked" bits, valid where tile_class is
   int mask_words;
-  void* out;                   // [B,H,Sq,64]
+  void* out;                   // rows of 64 at b * out_sb + h * out_sh + row * out_ss elements
+  long long out_sb, out_sh, out_ss;
   int out_dtype;
   int round_scores;            // dtype + 1: round S through f16 / bf16 before the softmax (autocast graphs)
   uint32_t idesc_qk, idesc_pv;
@@ -427,7 +428,7 @@ attn_tf32_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_cons
     l += pmax[(wg ^ 1) * kQRows + r_in_tile];
     if (ok && row < p.Sq) {
       const float inv = 1.0f / l;   // l = 0 for a fully masked row: 0 * inf = NaN, as the reference's softmax gives
-      const size_t base = ((size_t)(b * p.H + h) * p.Sq + row) * kHeadDim + wg * HD;
+      const size_t base = (size_t)((long long)b * p.out_sb + (long long)h * p.out_sh + (long long)row * p.out_ss) + wg * HD;
       if (p.out_dtype == BG_F32) {
         float* out = reinterpret_cast<float*>(p.out) + base;
 #pragma unroll
@@ -752,7 +753,7 @@ attn16_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     }
     if (ok && row < p.Sq) {
       const float inv = 1.0f / l;   // l = 0 for a fully masked row: 0 * inf = NaN, as the reference's softmax gives
-      const size_t base = ((size_t)(b * p.H + h) * p.Sq + row) * kHeadDim + wg * HD;
+      const size_t base = (size_t)((long long)b * p.out_sb + (long long)h * p.out_sh + (long long)row * p.out_ss) + wg * HD;
       if (p.out_dtype == BG_F32) {
         float* out = reinterpret_cast<float*>(p.out) + base;
 #pragma unroll
@@ -1111,6 +1112,7 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
   p.mask_bits = bits;
   p.mask_words = words_per_row;
   p.out = a.out;
+  p.out_sb = a.out_sb; p.out_sh = a.out_sh; p.out_ss = a.out_ss;
   p.out_dtype = a.out_dtype;
   p.round_scores = tf32 ? 0 : a.ab_dtype + 1;
   p.status = status;

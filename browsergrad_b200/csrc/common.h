@@ -173,9 +173,11 @@ cudaError_t launch_tri(const StridedView& in, void* out, int64_t numel, int uppe
 // flip: out[..., i, ...] = in[..., n - 1 - i, ...] along `axis`.
 cudaError_t launch_flip(const StridedView& in, void* out, int64_t numel, int axis, cudaStream_t s);
 // place: copies `in` (converted to out_dtype) into the block of the dense output `out_shape` that starts at
-// `axis_offset` along `axis` (one launch per CONCAT input).
+// `axis_offset` along `axis` (one launch per CONCAT input).  With `fill` the block is set to that constant
+// and `in` only gives the block's shape (a broadcast scalar as a CONCAT input: the borders of a constant PAD).
+struct PlaceFill { int is_int; double f; long long n; };
 cudaError_t launch_place(const StridedView& in, void* out, int out_dtype, const int64_t* out_shape, int axis, int64_t axis_offset,
-                         cudaStream_t s);
+                         cudaStream_t s, const PlaceFill* fill = nullptr);
 // cumsum along `axis` in the output dtype, sequential per line as NumPy's add.accumulate.
 cudaError_t launch_cumsum(const StridedView& in, void* out, int out_dtype, int axis, int reverse, cudaStream_t s);
 
@@ -241,6 +243,7 @@ struct TcGemm {
 extern bool g_tc_assume_available;
 // CTA-pair (cta_group::2) GEMM tiles: 0 never, 1 for problems that fill the device (default), 2 whenever legal.
 extern int g_tc_pair_mode;
+extern int g_tc_pair_width;
 bool tc_gemm_supported(int64_t M, int64_t N, int64_t K, int ab_dtype);
 cudaError_t launch_gemm_tc(const TcGemm& g, int* status, cudaStream_t s);
 // hi = tf32(x) (round to nearest), lo = x - hi, for fp32 or fp64 input; optional transpose is not done here.
@@ -262,7 +265,8 @@ struct AttnProblem {
   const void* mask;         // additive fp32 or bool, rows Sk apart, or null
   int mask_is_bool;
   int64_t mask_sb, mask_sh; // element strides over batch / head, 0 when broadcast
-  void* out;                // dense [B,H,Sq,D]
+  void* out;                // [B,H,Sq,D] addressed through out_sb / out_sh / out_ss; rows of D are dense
+  int64_t out_sb, out_sh, out_ss;   // element strides over batch / head / query row
   int out_dtype;
   int mode;                 // 0: 16-bit operands (ab_dtype), 1: 3xTF32
   int ab_dtype;

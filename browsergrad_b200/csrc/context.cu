@@ -379,6 +379,10 @@ int bg_set_option(bg_context* ctx, const char* key, int64_t value) {
   else if (k == "fusion") { ctx->fusion = value != 0; ctx->plan_cache.clear(); }
   else if (k == "tensor_cores") { ctx->tensor_cores = value != 0; ctx->plan_cache.clear(); }
   else if (k == "gemm_cta_pairs") g_tc_pair_mode = (int)value;   // process-wide: a launch policy, not plan state
+  else if (k == "gemm_pair_tile_width") {
+    if (value != 0 && value != 256 && value != 192 && value != 128) return fail(ctx, BG_ERR_INVALID, "set_option: gemm_pair_tile_width is 0, 256, 192 or 128");
+    g_tc_pair_width = (int)value;
+  }
   else if (k == "static_patterns") { ctx->static_patterns = value != 0; ctx->plan_cache.clear(); }
   else return fail(ctx, BG_ERR_INVALID, "set_option: unknown option '" + k + "'");
   if (k == "f64_contraction") ctx->plan_cache.clear();

@@ -865,6 +865,7 @@ __device__ __forceinline__ void row_reduce(const EwProgram& p, const RegFile& rf
   long long best_i = -1;
   if (op == BG_RED_MAX) acc = lowest<T>();
   if (op == BG_RED_MIN) acc = highest<T>();
+  if (op == BG_RED_PROD) acc = T(1);
   bool any_nan = false;
   const int64_t row_end = (row + 1) * p.cols;
   for (int64_t c0 = 0; c0 < n_chunks; c0 += nU) {
@@ -895,6 +896,7 @@ __device__ __forceinline__ void row_reduce(const EwProgram& p, const RegFile& rf
         V4<T> x = rget<T>(rf, p.tail_reg, u);
         for (int e = 0; e < nv; ++e) {
           const T v = x.v[e];
+          if (op == BG_RED_PROD) { acc *= v; continue; }
           if (is_arg) {
             if (arg_better<T>(v, col + e, acc, best_i, op == BG_RED_ARGMAX)) { acc = v; best_i = col + e; }
           } else {
@@ -922,6 +924,11 @@ __device__ __forceinline__ void row_reduce(const EwProgram& p, const RegFile& rf
         store_scalar(p.outputs[p.tail_out].ptr, p.tail_out_dtype, row, (double)acc, (long long)acc, kIsInt);
       }
     }
+    return;
+  }
+  if (op == BG_RED_PROD) {
+    acc = block_reduce<T>(acc, [](T a, T b) { return a * b; }, T(1), scratch);
+    if (threadIdx.x == 0) store_scalar(p.outputs[p.tail_out].ptr, p.tail_out_dtype, row, (double)acc, (long long)acc, kIsInt);
     return;
   }
   const bool want_max = op == BG_RED_MAX;

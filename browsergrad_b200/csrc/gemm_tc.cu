@@ -414,16 +414,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 // MMA ever targets a CTA that has exited.
 constexpr int kPairStages = 6;
 
-template <bool TF32>
+template <bool TF32, int TN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                     const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
                     const __grid_constant__ TcParams p) {
-  constexpr int kHalf = 128;                           // rows of A and of B each CTA stages
+  constexpr int kHalf = 128;                           // rows of A each CTA stages
+  constexpr int kBHalf = TN / 2;                       // rows of B each CTA stages
   constexpr int kABytes = kHalf * kStageRowBytes;
-  constexpr int kStageBytes = 2 * kABytes;
-  constexpr int kTile = 256;
-  constexpr int kTmemCols = 2 * kTile;
+  constexpr int kStageBytes = kABytes + kBHalf * kStageRowBytes;
+  constexpr int kTile = 256;                           // tile rows; the tile is kTile x TN
+  constexpr int kTmemCols = TN > 128 ? 512 : 256;      // two accumulators of TN columns; a power of two
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -437,7 +438,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  const int num_m = (p.M + kTile - 1) / kTile, num_n = (p.N + kTile - 1) / kTile;
+  const int num_m = (p.M + kTile - 1) / kTile, num_n = (p.N + TN - 1) / TN;
   const int num_tiles = num_m * num_n;
   const int gsz = p.group_m * num_n;
   auto tile_origin = [&](int tile, int& m0, int& n0) {
@@ -445,7 +446,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     const int first_m = g * p.group_m;
     const int gm = min(p.group_m, num_m - first_m);
     m0 = (first_m + (tile % gsz) % gm) * kTile;
-    n0 = ((tile % gsz) / gm) * kTile;
+    n0 = ((tile % gsz) / gm) * TN;
   };
 
   if (threadIdx.x == 0) {
@@ -486,7 +487,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
               const uint32_t full0 = map_to_cta(smem_u32(&full_bar[s]), 0);
               mbar_expect_tx_at(full0, kStageBytes);
               tma_load_2d_pair(ma, sa, full0, kb * p.elems_per_block, m0 + (int)rank * kHalf);
-              tma_load_2d_pair(mb, sa + kABytes, full0, kb * p.elems_per_block, n0 + (int)rank * kHalf);
+              tma_load_2d_pair(mb, sa + kABytes, full0, kb * p.elems_per_block, n0 + (int)rank * kBHalf);
             }
           }
         }
@@ -501,7 +502,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
           const int buf = use & 1;
           if (!mbar_wait(&acc_empty[buf], ((uint32_t)(use >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * kTile);
+          const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * TN);
           const int kb0 = ch * p.chunk_blocks, kb1 = min(kb0 + p.chunk_blocks, p.num_k_blocks);
           uint32_t accumulate = 0;
           for (int k = 0; k < (kb1 - kb0) * p.passes; ++k, ++it) {
@@ -540,9 +541,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
       const int row = m0 + (int)rank * kHalf + q * 32 + lane;
       const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
       if (TF32) {
-        constexpr int NC = kTile / 64;
+        constexpr int NC = TN / 64;
         float acc[NC][32];
-        ok = drain_chunks<NC>(p, acc_full, lane_base, kTile, half * NC, n_chunks, use, abort_flag, acc, lane, acc_empty0, true, nullptr);
+        ok = drain_chunks<NC>(p, acc_full, lane_base, TN, half * NC, n_chunks, use, abort_flag, acc, lane, acc_empty0, true, nullptr);
         if (!ok) break;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
@@ -554,9 +555,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         if (n_chunks > 0) ok = mbar_wait(&acc_full[buf], (uint32_t)(use >> 1) & 1u, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t tmem_acc = lane_base + (uint32_t)(buf * kTile);
+        const uint32_t tmem_acc = lane_base + (uint32_t)(buf * TN);
 #pragma unroll 1
-        for (int c = half * (kTile / 64); c < (half + 1) * (kTile / 64); ++c) {
+        for (int c = half * (TN / 64); c < (half + 1) * (TN / 64); ++c) {
           uint32_t r[32];
           if (n_chunks > 0) tmem_ld32(tmem_acc + (uint32_t)(c * 32), r);
           else {
@@ -710,17 +711,17 @@ cudaError_t launch_variant(const TcGemm& g, int* status, cudaStream_t s) {
   return cudaGetLastError();
 }
 
-template <bool TF32>
+template <bool TF32, int TN>
 cudaError_t launch_pair(const TcGemm& g, int* status, cudaStream_t s, bool* launched) {
   *launched = false;
   CUtensorMap a0, a1, b0, b1;
   if (!make_operand_map(&a0, g.A, g.ab_dtype, g.M, g.K, 128)) return cudaErrorInvalidValue;
-  if (!make_operand_map(&b0, g.B, g.ab_dtype, g.N, g.K, 128)) return cudaErrorInvalidValue;
+  if (!make_operand_map(&b0, g.B, g.ab_dtype, g.N, g.K, TN / 2)) return cudaErrorInvalidValue;
   a1 = a0;
   b1 = b0;
   if (TF32) {
     if (!make_operand_map(&a1, g.A_lo, g.ab_dtype, g.M, g.K, 128)) return cudaErrorInvalidValue;
-    if (!make_operand_map(&b1, g.B_lo, g.ab_dtype, g.N, g.K, 128)) return cudaErrorInvalidValue;
+    if (!make_operand_map(&b1, g.B_lo, g.ab_dtype, g.N, g.K, TN / 2)) return cudaErrorInvalidValue;
   }
   TcParams p{};
   p.M = (int)g.M;
@@ -740,9 +741,9 @@ cudaError_t launch_pair(const TcGemm& g, int* status, cudaStream_t s, bool* laun
   p.status = status;
   p.group_m = 4;
   const uint32_t fmt = TF32 ? 2u : (g.ab_dtype == BG_BF16 ? 1u : 0u);
-  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
-  const size_t smem = (size_t)kPairStages * 2 * 128 * kStageRowBytes + 256 + 1024;
-  auto kern = gemm_tc_pair_kernel<TF32>;
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+  const size_t smem = (size_t)kPairStages * (128 + TN / 2) * kStageRowBytes + 256 + 1024;
+  auto kern = gemm_tc_pair_kernel<TF32, TN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   // how many pairs the device can hold at once (two SMs of one TPC each)
@@ -764,7 +765,7 @@ cudaError_t launch_pair(const TcGemm& g, int* status, cudaStream_t s, bool* laun
     max_pairs = n;
   }
   if (max_pairs <= 0) return cudaSuccess;   // not launched: the caller falls back to single CTAs
-  const int64_t tiles = ((g.M + 255) / 256) * ((g.N + 255) / 256);
+  const int64_t tiles = ((g.M + 255) / 256) * ((g.N + TN - 1) / TN);
   const int64_t pairs = tiles < max_pairs ? tiles : max_pairs;
   kern<<<(unsigned)(2 * pairs), kTcThreads, smem, s>>>(a0, a1, b0, b1, p);
   *launched = true;
@@ -787,18 +788,45 @@ bool tc_gemm_supported(int64_t M, int64_t N, int64_t K, int ab_dtype) {
 
 int g_tc_pair_mode = 1;   // 0: never, 1: when the problem fills the device with 256 x 256 tiles, 2: whenever legal
 
+// Width of the CTA-pair tile (256 rows x TN columns).  A pair works through ceil(tiles / pairs) tiles one
+// after the other; a tile costs about TN + 64 (the A half of every stage does not shrink with TN), so a
+// narrower tile wins when it removes a mostly idle last round: M = 8192, N = 768 is 96 tiles of 256 columns
+// (two rounds on 74 pairs, the second a third full) but 128 tiles of 192 columns (two shorter rounds).
+static int pair_tile_width(int64_t M, int64_t N, int pairs) {
+  int best = 256;
+  int64_t best_cost = -1;
+  const int widths[3] = {256, 192, 128};
+  for (int w : widths) {
+    const int64_t tiles = ((M + 255) / 256) * ((N + w - 1) / w);
+    const int64_t rounds = (tiles + pairs - 1) / pairs;
+    const int64_t cost = rounds * (w + 64);
+    if (best_cost < 0 || cost < best_cost) { best = w; best_cost = cost; }
+  }
+  return best;
+}
+
+template <bool TF32>
+static cudaError_t launch_pair_width(int tn, const TcGemm& g, int* status, cudaStream_t s, bool* launched) {
+  if (tn == 192) return launch_pair<TF32, 192>(g, status, s, launched);
+  if (tn == 128) return launch_pair<TF32, 128>(g, status, s, launched);
+  return launch_pair<TF32, 256>(g, status, s, launched);
+}
+
+int g_tc_pair_width = 0;   // 0: chosen by pair_tile_width; 256 / 192 / 128: forced
+
 cudaError_t launch_gemm_tc(const TcGemm& g, int* status, cudaStream_t s) {
   const bool tf32 = g.ab_dtype == BG_F32;
   const int64_t tiles256 = ((g.M + 255) / 256) * ((g.N + 255) / 256);
   const bool pair_ok = g.M > 128 && g.N > 128;
-  if (pair_ok && (g_tc_pair_mode == 2 || (g_tc_pair_mode == 1 && tiles256 >= 64))) {
-    bool launched = false;
-    cudaError_t e = tf32 ? launch_pair<true>(g, status, s, &launched) : launch_pair<false>(g, status, s, &launched);
-    if (e != cudaSuccess || launched) return e;
-  }
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (pair_ok && (g_tc_pair_mode == 2 || (g_tc_pair_mode == 1 && tiles256 >= 64))) {
+    bool launched = false;
+    const int tn = g_tc_pair_width ? g_tc_pair_width : pair_tile_width(g.M, g.N, sms / 2);
+    cudaError_t e = tf32 ? launch_pair_width<true>(tn, g, status, s, &launched) : launch_pair_width<false>(tn, g, status, s, &launched);
+    if (e != cudaSuccess || launched) return e;
+  }
   // 128 x 256 tiles halve the B traffic per flop; 128 x 128 tiles when the wide ones would leave SMs idle
   const int64_t wide_tiles = ((g.M + BM - 1) / BM) * ((g.N + 255) / 256);
   const bool wide_tile = g.N > 128 && wide_tiles >= sms;

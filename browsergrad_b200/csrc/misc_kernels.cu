@@ -122,6 +122,7 @@ __global__ void reduce_generic_kernel(const void* in, void* out, int in_dt, int 
       else v = (ACC)load_as_double(in, in_dt, base + r * inner);
       switch (op) {
         case BG_RED_SUM: case BG_RED_MEAN: acc += v; break;
+        case BG_RED_PROD: acc = r == 0 ? v : acc * v; break;
         case BG_RED_MAX: if (v != v) nan = true; acc = (r == 0 || v > acc) ? v : acc; break;
         case BG_RED_MIN: if (v != v) nan = true; acc = (r == 0 || v < acc) ? v : acc; break;
         case BG_RED_ARGMAX: case BG_RED_ARGMIN: {
@@ -138,7 +139,7 @@ __global__ void reduce_generic_kernel(const void* in, void* out, int in_dt, int 
         default: acc = (r == 0 ? true : acc != ACC(0)) && (v != ACC(0)) ? ACC(1) : ACC(0); break;
       }
     }
-    if (op == BG_RED_ALL && R == 0) acc = ACC(1);
+    if ((op == BG_RED_ALL || op == BG_RED_PROD) && R == 0) acc = ACC(1);
     if (op == BG_RED_ARGMAX || op == BG_RED_ARGMIN) {
       store_from(out, out_dt, t, 0.0, best < 0 ? 0 : best, true);
     } else if (op == BG_RED_MEAN) {

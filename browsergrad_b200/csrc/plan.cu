@@ -235,7 +235,11 @@ class Compiler {
     int scale_node = -1;              // BUFFER-backed multiplier, or -1 with scale_const
     double scale_const = 1.0;
     int mode = 1, ab_dtype = BG_F32;
+    // RESHAPE node whose dense copy of PERMUTE(result) the kernel writes directly (head merge), or -1
+    int out_node = -1;
+    int64_t out_stride[3] = {0, 0, 0};   // element strides of the result over batch / head / query row
   };
+  std::set<int> copy_elided_;             // RESHAPE copies produced by the attention kernel itself
   std::map<int, AttnPlan> attn_plan_;     // final MATMUL node -> fused attention
   std::set<int> attn_absorbed_;           // nodes that only exist inside a fused attention
   bool match_attention(int n, AttnPlan& ap, std::vector<int>& interior);
@@ -633,6 +637,8 @@ void Compiler::analyse() {
     Node& n = nodes_[i];
     const int src = resolve(n.in[0]);
     const View& sv = view_[src];
+    if (n.dtype != sv.dtype) err(BG_ERR_INVALID, std::string(op_name(n.op)) + ": a view cannot change the dtype of its input (" +
+                                                 dtype_name(sv.dtype) + " -> " + dtype_name(n.dtype) + ")");
     View v;
     if (n.op == BG_OP_PERMUTE) {
       v = sv;
@@ -983,7 +989,8 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
       if (xc != T_F32 && xc != T_F64) err(BG_ERR_UNSUPPORTED, "LAYER_NORM on non-float tensors");
     } else {
       const int rop = (int)t.iarg[0];
-      if (rop < 0 || rop > BG_RED_ALL) err(BG_ERR_INVALID, "REDUCE: unknown reduction");
+      if (rop < 0 || rop > BG_RED_PROD) err(BG_ERR_INVALID, "REDUCE: unknown reduction");
+      if (rop == BG_RED_PROD && nodes_[x].dtype != BG_F32 && nodes_[x].dtype != BG_F64 && nodes_[x].dtype != BG_I64) err(BG_ERR_UNSUPPORTED, "REDUCE prod: float32, float64 and int64 only");
       if (rop == BG_RED_ANY || rop == BG_RED_ALL) want = T_B;
       else if (xc == T_B) want = T_I64;
     }
@@ -1582,6 +1589,9 @@ void Compiler::emit_generic_reduce(int n, int key) {
   for (int d = 0; d < xn.rank; ++d) {
     if (d < lo) outer *= xn.shape[d]; else if (d <= hi) R *= xn.shape[d]; else inner *= xn.shape[d];
   }
+  if (t.iarg[0] < 0 || t.iarg[0] > BG_RED_PROD) err(BG_ERR_INVALID, "REDUCE: unknown reduction");
+  if (t.iarg[0] == BG_RED_PROD && xv.dtype != BG_F32 && xv.dtype != BG_F64 && xv.dtype != BG_I64)
+    err(BG_ERR_UNSUPPORTED, "REDUCE prod: float32, float64 and int64 only");
   own_slot(n);
   const int in_slot = xv.slot, out_slot = view_[n].slot, in_dt = xv.dtype, out_dt = t.dtype, rop = (int)t.iarg[0];
   const int64_t off_bytes = xv.off * dtype_size(xv.dtype);
@@ -1978,12 +1988,33 @@ bool Compiler::match_attention(int n, AttnPlan& ap, std::vector<int>& interior) 
 void Compiler::plan_attention() {
   attn_plan_.clear();
   attn_absorbed_.clear();
+  copy_elided_.clear();
   if (!ctx_->fusion || !ctx_->tensor_cores) return;
   for (int n = 0; n < (int)nodes_.size(); ++n) {
     if (kind_[n] != K_OTHER || nodes_[n].op != BG_OP_MATMUL) continue;
     AttnPlan ap;
     std::vector<int> interior;
     if (!match_attention(n, ap, interior)) continue;
+    // result -> PERMUTE (head dim stays last) -> RESHAPE that needs a dense copy, each with one consumer:
+    // the kernel stores its rows at the copy's addresses and the copy unit disappears
+    const Node& fin = nodes_[n];
+    ap.out_stride[0] = fin.shape[1] * fin.shape[2] * fin.shape[3];
+    ap.out_stride[1] = fin.shape[2] * fin.shape[3];
+    ap.out_stride[2] = fin.shape[3];
+    auto only_consumer = [&](int v) {
+      std::set<int> c(cons_[v].begin(), cons_[v].end());
+      return c.size() == 1 && v != root_ ? *c.begin() : -1;
+    };
+    const int pm = only_consumer(n);
+    const int rs = pm >= 0 && nodes_[pm].op == BG_OP_PERMUTE && kind_[pm] == K_VIEW ? only_consumer(pm) : -1;
+    if (rs >= 0 && nodes_[rs].op == BG_OP_RESHAPE && kind_[rs] == K_OTHER && copy_src_.count(rs) && nodes_[pm].iarg[3] == 3 &&
+        nodes_[rs].dtype == fin.dtype) {
+      int64_t dense[4], run = 1;
+      for (int d = 3; d >= 0; --d) { dense[d] = run; run *= nodes_[pm].shape[d]; }
+      for (int d = 0; d < 3; ++d) ap.out_stride[nodes_[pm].iarg[d]] = dense[d];
+      ap.out_node = rs;
+      copy_elided_.insert(rs);
+    }
     attn_plan_[n] = ap;
     for (int v : interior) attn_absorbed_.insert(v);
   }
@@ -2048,15 +2079,17 @@ void Compiler::emit_attention(int n, int key) {
   auto off_of = [&](const View& v, int src) {
     return src >= 0 ? (view_[src].off + v.off) * (int64_t)4 : v.off * (int64_t)dtype_size(v.dtype);
   };
-  const int sq = slot_of(qv, ap.q_src), sk = slot_of(ktv, ap.kt_src), sv = slot_of(vv, ap.v_src), so = view_[n].slot;
+  const int out_node = ap.out_node >= 0 ? ap.out_node : n;
+  tmpl.out_sb = ap.out_stride[0]; tmpl.out_sh = ap.out_stride[1]; tmpl.out_ss = ap.out_stride[2];
+  const int sq = slot_of(qv, ap.q_src), sk = slot_of(ktv, ap.kt_src), sv = slot_of(vv, ap.v_src), so = view_[out_node].slot;
   const int64_t offq = off_of(qv, ap.q_src), offk = off_of(ktv, ap.kt_src), offv = off_of(vv, ap.v_src);
   pu.order_key = key;
   pu.dep_nodes = {ap.q_src >= 0 ? ap.q_src : ap.q, ap.kt_src >= 0 ? ap.kt_src : ap.kt, ap.v_src >= 0 ? ap.v_src : ap.v};
   if (ap.mask >= 0) pu.dep_nodes.push_back(ap.mask);
   if (ap.scale_node >= 0) pu.dep_nodes.push_back(ap.scale_node);
-  pu.out_nodes = {n};
+  pu.out_nodes = {out_node};
   pu.u.name = std::string(ap.mode == 1 ? "attention_tc_3xtf32" : "attention_tc") + (ap.mask >= 0 ? (ap.mask_is_bool ? "+boolmask" : "+mask") : "") +
-              "[" + dtype_name(fin.dtype) + "]";
+              (ap.out_node >= 0 ? "+merge" : "") + "[" + dtype_name(fin.dtype) + "]";
   pu.u.launches = 4 + (ap.mask >= 0) + (ap.scale_node >= 0);
   cp_->uses_status = true;
   pu.u.fn = [=](Run& r) {
@@ -2385,21 +2418,28 @@ void Compiler::emit_shape_op(int n, int key) {
   const int n_in = (int)t.in.size();
   if (t.op == BG_OP_CONCAT) { if (n_in < 1) err(BG_ERR_INVALID, "CONCAT: no inputs"); }
   else if (n_in != 1) err(BG_ERR_INVALID, std::string(op_name(t.op)) + ": one input required");
-  struct Src { int slot; int64_t off_bytes; StridedView v; };
+  struct Src { int slot; int64_t off_bytes; StridedView v; bool is_fill; PlaceFill fill; };
   std::vector<Src> srcs;
   std::vector<int> deps;
   for (int k = 0; k < n_in; ++k) {
     const int x = resolve(t.in[k]);
     const View& xv = view_[x];
-    if (xv.is_const) err(BG_ERR_UNSUPPORTED, std::string(op_name(t.op)) + " of a scalar constant");
+    if (xv.is_const && t.op != BG_OP_CONCAT) err(BG_ERR_UNSUPPORTED, std::string(op_name(t.op)) + " of a scalar constant");
     Src sc{};
+    sc.is_fill = xv.is_const;
+    if (xv.is_const) {
+      // the constant converted to its own dtype first, as the reference materialises it before concatenating
+      sc.fill.is_int = !dtype_is_float(xv.dtype);
+      sc.fill.f = xv.dtype == BG_F32 ? (double)(float)xv.cf : xv.cf;
+      sc.fill.n = xv.dtype == BG_BOOL ? (xv.ci != 0) : xv.ci;
+    }
     sc.slot = xv.slot;
     sc.off_bytes = xv.off * dtype_size(xv.dtype);
     sc.v.dtype = xv.dtype;
     sc.v.rank = xv.rank;
     for (int d = 0; d < xv.rank; ++d) { sc.v.shape[d] = xv.shape[d]; sc.v.stride[d] = xv.shape[d] == 1 ? 0 : xv.stride[d]; }
     srcs.push_back(sc);
-    deps.push_back(x);
+    if (!xv.is_const) deps.push_back(x);
   }
   const int rank = t.rank;
   const int64_t a0 = t.iarg[0];
@@ -2462,7 +2502,7 @@ void Compiler::emit_shape_op(int n, int key) {
     cudaError_t e = cudaSuccess;
     for (size_t k = 0; k < srcs.size() && e == cudaSuccess; ++k) {
       StridedView v = srcs[k].v;
-      v.ptr = reinterpret_cast<char*>(r.ptr[srcs[k].slot]) + srcs[k].off_bytes;
+      v.ptr = srcs[k].is_fill ? nullptr : reinterpret_cast<char*>(r.ptr[srcs[k].slot]) + srcs[k].off_bytes;
       switch (op) {
         case BG_OP_TRIL: e = launch_tri(v, r.ptr[so], numel, 0, a0, r.ctx->stream); break;
         case BG_OP_TRIU: e = launch_tri(v, r.ptr[so], numel, 1, a0, r.ctx->stream); break;
@@ -2472,7 +2512,7 @@ void Compiler::emit_shape_op(int n, int key) {
           e = launch_sort_lines(v, reinterpret_cast<int64_t*>(r.ptr[so]), (int)a0, reverse, keep, r.ctx->stream); break;
         case BG_OP_TOPK_INDICES:
           e = launch_sort_lines(v, reinterpret_cast<int64_t*>(r.ptr[so]), (int)a0, largest, keep, r.ctx->stream); break;
-        default: e = launch_place(v, r.ptr[so], out_dt, oshape.data(), (int)a0, axis_off[k], r.ctx->stream); break;
+        default: e = launch_place(v, r.ptr[so], out_dt, oshape.data(), (int)a0, axis_off[k], r.ctx->stream, srcs[k].is_fill ? &srcs[k].fill : nullptr); break;
       }
     }
     return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "data-movement kernel launch");
@@ -2638,7 +2678,9 @@ bool Compiler::try_lower() {
         case BG_OP_CROSS_ENTROPY: emit_ce(i, i); break;
         case BG_OP_TRIL: case BG_OP_TRIU: case BG_OP_FLIP: case BG_OP_CONCAT: case BG_OP_CUMSUM:
         case BG_OP_SORT_INDICES: case BG_OP_TOPK_INDICES: emit_shape_op(i, i); break;
-        case BG_OP_RESHAPE: emit_copy(i, copy_src_.at(i), resolve(n.in[0]), i); break;
+        case BG_OP_RESHAPE:
+          if (!copy_elided_.count(i)) emit_copy(i, copy_src_.at(i), resolve(n.in[0]), i);
+          break;
         default: err(BG_ERR_UNSUPPORTED, std::string("opcode ") + op_name(n.op));
       }
     }

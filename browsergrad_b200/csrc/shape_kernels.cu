@@ -121,6 +121,10 @@ __device__ __forceinline__ void store_value(void* p, int dt, int64_t i, double f
 struct PlaceArg {
   int64_t out_stride[kMaxRank];   // dense strides of the output
   int64_t base;                   // axis_offset * out_stride[axis]
+  int fill;                       // 1: every element is the constant below (the source view gives the block's shape only)
+  int fill_is_int;
+  double fill_f;
+  long long fill_n;
 };
 
 __global__ void place_kernel(ViewArg in, int in_dtype, void* out, int out_dtype, PlaceArg pa, int64_t numel) {
@@ -133,7 +137,8 @@ __global__ void place_kernel(ViewArg in, int in_dtype, void* out, int out_dtype,
       src += c * in.stride[d];
       dst += c * pa.out_stride[d];
     }
-    if (from_int) store_value(out, out_dtype, dst, 0.0, load_as_i64(in.ptr, in_dtype, src), true);
+    if (pa.fill) store_value(out, out_dtype, dst, pa.fill_f, pa.fill_n, pa.fill_is_int != 0);
+    else if (from_int) store_value(out, out_dtype, dst, 0.0, load_as_i64(in.ptr, in_dtype, src), true);
     else store_value(out, out_dtype, dst, load_as_double(in.ptr, in_dtype, src), 0, false);
   }
 }
@@ -184,7 +189,7 @@ cudaError_t launch_flip(const StridedView& in, void* out, int64_t numel, int axi
 }
 
 cudaError_t launch_place(const StridedView& in, void* out, int out_dtype, const int64_t* out_shape, int axis, int64_t axis_offset,
-                         cudaStream_t s) {
+                         cudaStream_t s, const PlaceFill* fill) {
   if (axis < 0 || axis >= in.rank) return cudaErrorInvalidValue;
   int64_t numel = 1;
   for (int d = 0; d < in.rank; ++d) numel *= in.shape[d];
@@ -193,6 +198,7 @@ cudaError_t launch_place(const StridedView& in, void* out, int out_dtype, const 
   int64_t st = 1;
   for (int d = in.rank - 1; d >= 0; --d) { pa.out_stride[d] = st; st *= out_shape[d]; }
   pa.base = axis_offset * pa.out_stride[axis];
+  if (fill) { pa.fill = 1; pa.fill_is_int = fill->is_int; pa.fill_f = fill->f; pa.fill_n = fill->n; }
   place_kernel<<<grid_for(numel), 256, 0, s>>>(to_arg(in), in.dtype, out, out_dtype, pa, numel);
   return cudaGetLastError();
 }

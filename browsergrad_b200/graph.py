@@ -313,6 +313,24 @@ class Tensor:
         node = Node("VAR", (self._uop,), out_shape, self.dtype, {"axes": axes, "correction": corr, "keepdims": keep})
         return self._wrap(node)
 
+    def prod(self, axis: Any = None, dim: Any = None, keepdims: bool = False, keepdim: bool = False) -> "Tensor":
+        """``PROD`` node of ``TensorProxy.prod`` (_tensor_proxy.py:1278-1308): the product over the sorted,
+        de-duplicated axes in the input dtype."""
+        if axis is not None and dim is not None:
+            raise ValueError("prod: specify only one of axis or dim")
+        reduce_axis = dim if dim is not None else axis
+        keep = bool(keepdim or keepdims)
+        nd = self.ndim
+        if reduce_axis is None:
+            axes = tuple(range(nd))
+        else:
+            raw = (reduce_axis,) if isinstance(reduce_axis, (int, np.integer)) else tuple(reduce_axis)
+            axes = tuple(sorted(int(a) % nd for a in raw))
+            if len(set(axes)) != len(axes):
+                raise ValueError("prod: axes must be unique after normalization")
+        out_shape = tuple(1 if keep and i in axes else d for i, d in enumerate(self.shape) if keep or i not in axes)
+        return self._wrap(Node("PROD", (self._uop,), out_shape, self.dtype, {"axes": axes, "keepdims": keep}))
+
     def clamp(self, min: Any = None, max: Any = None) -> "Tensor":
         """``CLAMP`` node (_tensor_proxy.py:992-1023); bounds are finite Python floats or ``None``."""
         if min is None and max is None:
@@ -612,6 +630,31 @@ def cat(tensors: Sequence[Tensor], dim: int = 0) -> Tensor:
     out_dtype = np.result_type(*[np.dtype(t.dtype) if t.dtype != "bfloat16" else np.float32 for t in ts]).name \
         if len({t.dtype for t in ts}) > 1 else ts[0].dtype
     return ts[0]._wrap(Node("CONCAT", tuple(t._uop for t in ts), out_shape, out_dtype, {"axis": axis}))
+
+
+def pad(x: Tensor, pad: Sequence[int], mode: str = "constant", value: Any = None) -> Tensor:
+    """``PAD`` node of ``F.pad`` (_functional.py:1397-1417): ``pad`` lists (before, after) pairs from the
+    LAST axis backwards; constant mode only; the fill value is normalised to the input dtype
+    (_framework_contracts.py:4694-4726, :4756-4791)."""
+    if mode != "constant":
+        raise ValueError(f"pad: mode {mode!r} is not supported; expected 'constant'")
+    if len(pad) % 2 != 0 or len(pad) // 2 > x.ndim:
+        raise ValueError("pad: an even number of widths, at most two per dimension")
+    width = [(0, 0)] * x.ndim
+    for i in range(len(pad) // 2):
+        lo, hi = int(pad[2 * i]), int(pad[2 * i + 1])
+        if lo < 0 or hi < 0:
+            raise ValueError("pad: negative padding is not supported")
+        width[x.ndim - 1 - i] = (lo, hi)
+    if x.dtype == "bool":
+        fill: Any = bool(value) if value is not None else False
+    elif x.dtype.startswith("float"):
+        fill = float(np.asarray(0 if value is None else value, dtype=np.dtype(x.dtype)).item())
+        fill = 0.0 if fill == 0.0 else fill
+    else:
+        fill = int(0 if value is None else value)
+    out_shape = tuple(d + lo + hi for d, (lo, hi) in zip(x.shape, width))
+    return x._wrap(Node("PAD", (x._uop,), out_shape, x.dtype, {"pad_width": tuple(width), "mode": "constant", "value": fill}))
 
 
 def stack(tensors: Sequence[Tensor], dim: int = 0) -> Tensor:

@@ -253,7 +253,10 @@ def lower_composites(root: Any) -> Any:
     * ``STACK`` -> ``CONCAT`` of the inputs reshaped with a unit axis;
     * ``REPEAT`` / ``REPEAT_INTERLEAVE`` -> ``RESHAPE`` / ``BROADCAST_TO`` / ``RESHAPE`` (``np.tile`` / ``np.repeat``,
       _realize.py:329-332, :360-363);
-    * ``SORT_VALUES`` / ``TOPK_VALUES`` -> ``INDEX`` along the ordering axis (_realize.py:1149-1176).
+    * ``SORT_VALUES`` / ``TOPK_VALUES`` -> ``INDEX`` along the ordering axis (_realize.py:1149-1176);
+    * ``PROD`` -> ``REDUCE`` with the product combiner (``np.prod(dtype=...)``, _realize.py:335-343);
+    * ``PAD`` -> one ``CONCAT`` per padded axis whose outer inputs are the broadcast fill constant
+      (``np.pad(mode="constant")``, _realize.py:1131-1140).
     """
     def make(like: Any, op: str, inputs: tuple, shape: tuple, dtype: str, arg: Any) -> Any:
         return type(like)(op=op, inputs=inputs, shape=tuple(shape), dtype=dtype, arg=arg)
@@ -290,6 +293,31 @@ def lower_composites(root: Any) -> Any:
             total = make(node, "REDUCE", (sq,), node.shape, node.dtype, {"op": "sum", "axis": axes, "keepdims": keep})
             count = make(node, "CONST", (), (), node.dtype, {"value": float(max(n - int(node.arg.get("correction", 1)), 0))})
             return make(node, "DIV", (total, count), node.shape, node.dtype, None)
+        if node.op == "PROD":
+            (x,) = ins
+            if node.dtype not in ("float32", "float64", "int64"):
+                raise JitNotImplementedError("CUDA realizer: PROD of a " + node.dtype + " tensor is not supported. "
+                                             "Fall back to bg.realize() (NumPy).")
+            return make(node, "REDUCE", (x,), node.shape, node.dtype,
+                        {"op": "prod", "axis": tuple(int(a) for a in node.arg["axes"]), "keepdims": bool(node.arg.get("keepdims", False))})
+        if node.op == "PAD":
+            (x,) = ins
+            out = x
+            shape = list(x.shape)
+            fill = make(node, "CONST", (), (), node.dtype, {"value": node.arg["value"]})
+            for axis, (lo, hi) in enumerate(node.arg["pad_width"]):
+                if lo == 0 and hi == 0:
+                    continue
+                parts = []
+                for extent in (int(lo), None, int(hi)):
+                    if extent is None:
+                        parts.append(out)
+                    elif extent > 0:
+                        blk = tuple(shape[:axis]) + (extent,) + tuple(shape[axis + 1:])
+                        parts.append(make(node, "BROADCAST_TO", (fill,), blk, node.dtype, {"shape": blk}))
+                shape[axis] += int(lo) + int(hi)
+                out = make(node, "CONCAT", tuple(parts), tuple(shape), node.dtype, {"axis": axis})
+            return out
         if node.op == "STACK":
             axis = int(node.arg["axis"])
             parts = []
@@ -315,6 +343,11 @@ def lower_composites(root: Any) -> Any:
             a = make(node, "RESHAPE", (x,), split, node.dtype, {"new_shape": split})
             b = make(node, "BROADCAST_TO", (a,), wide, node.dtype, {"shape": wide})
             return make(node, "RESHAPE", (b,), node.shape, node.dtype, {"new_shape": tuple(node.shape)})
+        if node.op in ("PERMUTE", "RESHAPE", "BROADCAST_TO", "LOAD") and len(ins) == 1 and ins[0].dtype != node.dtype:
+            # A view built outside the autocast block keeps the dtype its input had before the cast pass
+            # narrowed it; the reference's realizer hands the narrow array through unchanged
+            # (_realize.py:1114-1121), so the view carries its input's real dtype here.
+            return make(node, node.op, ins, node.shape, ins[0].dtype, node.arg)
         if all(a is b for a, b in zip(ins, node.inputs)):
             return node
         return make(node, node.op, ins, node.shape, node.dtype, node.arg)

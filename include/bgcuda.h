@@ -80,7 +80,7 @@ typedef enum bg_cmp { BG_CMP_EQ = 0, BG_CMP_NE = 1, BG_CMP_LT = 2, BG_CMP_LE = 3
                       BG_CMP_GT = 4, BG_CMP_GE = 5 } bg_cmp;
 typedef enum bg_reduce { BG_RED_SUM = 0, BG_RED_MAX = 1, BG_RED_MIN = 2, BG_RED_MEAN = 3,
                          BG_RED_ARGMAX = 4, BG_RED_ARGMIN = 5, BG_RED_ANY = 6,
-                         BG_RED_ALL = 7 } bg_reduce;
+                         BG_RED_ALL = 7, BG_RED_PROD = 8 } bg_reduce;
 
 /*
  * One scheduled step of a tensor plan: the C form of one entry of

@@ -194,6 +194,18 @@ def _h_var(node, vt, store):  # _realize.py:346-357
     return np.array(variance, dtype=np.dtype(node.dtype), copy=True).reshape(node.shape)
 
 
+def _h_prod(node, vt, store):  # _realize.py:335-343
+    product = np.prod(_in(node, vt, 0), axis=tuple(node.arg["axes"]), keepdims=bool(node.arg.get("keepdims", False)),
+                      dtype=np.dtype(node.dtype))
+    return np.array(product, dtype=np.dtype(node.dtype), copy=True).reshape(node.shape)
+
+
+def _h_pad(node, vt, store):  # _realize.py:1131-1140
+    padded = np.pad(_in(node, vt, 0), pad_width=tuple(tuple(p) for p in node.arg["pad_width"]), mode="constant",
+                    constant_values=node.arg["value"])
+    return np.array(padded, dtype=np.dtype(node.dtype), copy=True)
+
+
 def _h_repeat(node, vt, store):  # _realize.py:329-332
     return np.array(np.tile(_in(node, vt, 0), tuple(node.arg["repeats"])), dtype=np.dtype(node.dtype), copy=True)
 
@@ -393,7 +405,7 @@ _DISPATCH: Dict[str, Callable] = {
     "PERMUTE": lambda n, vt, s: np.transpose(_in(n, vt, 0), axes=n.arg["axes"]),   # :1119-1121
     "WHERE": _h_where,
     "CLAMP": _h_clamp, "FLIP": _h_flip, "CUMSUM": _h_cumsum, "CONCAT": _h_concat, "STACK": _h_stack,
-    "TRIL": _h_tril, "TRIU": _h_triu, "VAR": _h_var, "REPEAT": _h_repeat, "REPEAT_INTERLEAVE": _h_repeat_interleave,
+    "TRIL": _h_tril, "TRIU": _h_triu, "VAR": _h_var, "PROD": _h_prod, "PAD": _h_pad, "REPEAT": _h_repeat, "REPEAT_INTERLEAVE": _h_repeat_interleave,
     "SORT_INDICES": _h_sort_indices, "SORT_VALUES": _h_take_along, "TOPK_INDICES": _h_topk_indices, "TOPK_VALUES": _h_take_along,
     "INDEX": _h_index,
     "BROADCAST_TO": _h_broadcast_to,

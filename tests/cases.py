@@ -29,6 +29,7 @@ class RefApi:
         self.from_numpy = bg.from_numpy
         self.cat, self.stack, self.cumsum = bg.cat, bg.stack, bg.cumsum
         self.sort, self.topk = bg.sort, bg.topk
+        self.pad = F.pad
 
 
 def canonical_arg(op: str, arg: Any) -> Any:
@@ -220,6 +221,11 @@ CASES: Dict[str, Case] = {
                                  lambda api, t, raw: configs.attention(api, t, "causal")),
     "c4_attn_mask_tiles": Case(_attn_small(2, 2, 320, 64),
                                lambda api, t, raw: configs.attention(api, t, "mask")),
+    "c4_attn_merge_heads": Case(_attn_small(2, 3, 200, 64),
+                                lambda api, t, raw: configs.attention(api, t, "mask").permute(0, 2, 1, 3).reshape(2 * 200, 3 * 64) * 2.0),
+    "c4_attn_merge_heads_bf16": Case(_attn_small(2, 2, 320, 64),
+                                     lambda api, t, raw: configs.attention(api, t, "causal", "bfloat16").permute(0, 2, 1, 3).reshape(2, 320, 128),
+                                     rtol=2e-2, reference_has_it=False),
     "c4_attn_nomask_d64": Case(_attn_small(1, 3, 200, 64),
                                lambda api, t, raw: configs.attention(api, t, "none")),
     "c4_attn_mask_f16": Case(_attn_small(2, 2, 320, 64),
@@ -263,6 +269,16 @@ CASES: Dict[str, Case] = {
     "cat_last_mixed": Case(_misc_inputs, lambda api, t, raw: api.cat([t["x"], t["d"]], 2), kind="exact"),
     "cat_then_sum": Case(_misc_inputs, lambda api, t, raw: api.cat([t["x"] * t["p"], t["x"] + t["row"]], 1).sum(axis=-1)),
     "stack_mid": Case(_misc_inputs, lambda api, t, raw: api.stack([t["x"], t["p"]], 1), kind="exact"),
+    "prod_last": Case(_misc_inputs, lambda api, t, raw: t["p"].prod(-1)),
+    "prod_mid_keepdims": Case(_misc_inputs, lambda api, t, raw: t["x"].prod(1, keepdims=True)),
+    "prod_two_axes_f64": Case(_misc_inputs, lambda api, t, raw: t["d"].prod((0, 1))),
+    "prod_after_chain": Case(_misc_inputs, lambda api, t, raw: (t["x"] * t["row"] + 1.0).prod(2)),
+    "prod_int_wraps": Case(_misc_inputs, lambda api, t, raw: t["i"].prod(2), kind="exact"),
+    "prod_int_first": Case(_misc_inputs, lambda api, t, raw: t["j"].prod(0), kind="exact"),
+    "pad_last": Case(_misc_inputs, lambda api, t, raw: api.pad(t["x"], (2, 3)), kind="exact"),
+    "pad_two_axes_value": Case(_misc_inputs, lambda api, t, raw: api.pad(t["x"], (1, 0, 0, 2), value=-1.5), kind="exact"),
+    "pad_all_axes_int": Case(_misc_inputs, lambda api, t, raw: api.pad(t["i"], (0, 4, 3, 0, 1, 1), value=7), kind="exact"),
+    "pad_f64_then_chain": Case(_misc_inputs, lambda api, t, raw: api.relu(api.pad(t["d"], (1, 1)) * 2.0)),
     "cumsum_last": Case(_misc_inputs, lambda api, t, raw: api.cumsum(t["x"], 2), kind="exact"),
     "cumsum_first_int": Case(_misc_inputs, lambda api, t, raw: api.cumsum(t["i32"], 0), kind="exact"),
     "cumsum_mid_f64": Case(_misc_inputs, lambda api, t, raw: api.cumsum(t["d"], 1), kind="exact"),

@@ -119,19 +119,23 @@ def test_sdpa_runs_as_one_fused_attention_kernel(bridge, name, expect):
 @pytest.mark.parametrize("name", ["c3_tc_f32", "c3_tc_f16", "c3_tc_bf16", "c3_tc_ragged", "c3_tc_relu", "c3_tc_rowmajor_b",
                                   "c3_tc_f32_long_k"])
 def test_cta_pair_gemm_matches_oracle(bridge, name):
-    """The two-CTA (cta_group::2) 256 x 256 tile kernel, forced on shapes with ragged edges in M, N and K."""
+    """The two-CTA (cta_group::2) kernel with 256 x 256, 256 x 192 and 256 x 128 tiles, forced on shapes with
+    ragged edges in M, N and K."""
     case = CASES[name]
     t, store, _ = build_case(case)
     want = oracle_value(t, store)
     single = realize_cuda(t, bridge)
     bridge.set_option("gemm_cta_pairs", 2)
     try:
-        got = realize_cuda(t, bridge)
+        for width in (256, 192, 128):
+            bridge.set_option("gemm_pair_tile_width", width)
+            got = realize_cuda(t, bridge)
+            check(case, got, want, f"{name} (CTA pairs, {width} columns)")
+            # same products, same accumulation order per output element: every tiling agrees to the bit
+            assert got.tobytes() == single.tobytes(), width
     finally:
         bridge.set_option("gemm_cta_pairs", 1)
-    check(case, got, want, name + " (CTA pairs)")
-    # same products, same accumulation order per output element: the two tilings agree to the bit
-    assert got.tobytes() == single.tobytes()
+        bridge.set_option("gemm_pair_tile_width", 0)
 
 
 def test_autocast_attention_is_one_unit_and_keeps_mask_classes_with_the_handle(bridge):
@@ -153,6 +157,19 @@ def test_autocast_attention_is_one_unit_and_keeps_mask_classes_with_the_handle(b
     release_resident_leaves(bridge)
     assert bridge.resourceSnapshot()["currentBytes"] == base
     assert bridge.aliveHandleCount() == 0
+
+
+@pytest.mark.parametrize("name,unit", [("c4_attn_merge_heads", "attention_tc_3xtf32+mask+merge[float32]"),
+                                       ("c4_attn_merge_heads_bf16", "attention_tc+boolmask+merge[bfloat16]")])
+def test_head_merge_after_attention_is_written_by_the_attention_kernel(bridge, name, unit):
+    """permute(0, 2, 1, 3).reshape(...) of the attention result needs no copy: the kernel stores its rows at the
+    merged layout's addresses."""
+    case = CASES[name]
+    t, store, _ = build_case(case)
+    got = realize_cuda(t, bridge)
+    trace = bridge.last_plan_trace()
+    assert unit in trace and "copy[strided]" not in trace, trace
+    check(case, got, oracle_value(t, store), "merged heads")
 
 
 def test_row_pipeline_equals_one_realization(bridge):
