@@ -301,6 +301,23 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn
                                  "tokens_per_s": b * s / (ms * 1e-3), "plan_ms": ms, "kernel_ms": k_ms, "kernels": trace,
                                  "dense_equivalent_tflops": flops / (ms * 1e-3) / 1e12})
         del arrays, store, t
+    if "gemm_widths" in want:
+        # the decoder's projection shapes with the CTA-pair tile width forced (0 = the launcher's own choice)
+        out["gemm_widths"] = []
+        for (m, n, k) in ((8192, 768, 768), (8192, 768, 3072), (8192, 3072, 768), (8192, 2304, 768), (4096, 4096, 4096)):
+            for amp in ("", "bfloat16"):
+                arrays = configs.linear_inputs(m, n, k)
+                store = graph.BufferStore()
+                t = {kk: graph.from_numpy(v, store) for kk, v in arrays.items()}
+                root = configs.linear_gelu(graph, t, amp)
+                row = {"workload": f"Linear+bias+GELU M={m} N={n} K={k} {'bf16 autocast' if amp else 'fp32 (3xTF32)'}", "us_per_launch": {}}
+                for width in (256, 192, 128, 0):
+                    bridge.set_option("gemm_pair_tile_width", width)
+                    ms, prof, trace = time_plan(bridge, torch, stream, root, store, front, max(5, steps // 4))
+                    gemm = [p for p in prof if p["name"].startswith("gemm")]
+                    row["us_per_launch"]["auto" if width == 0 else str(width)] = 1e3 * gemm[0]["ms"] / max(gemm[0]["launches"], 1)
+                out["gemm_widths"].append(row)
+                del arrays, store, t
     if "gpt" in want:
         arrays = configs.gpt_inputs(batch=8)
         meta = arrays.pop("_meta")
@@ -381,9 +398,9 @@ def main() -> None:
     stream = torch.cuda.ExternalStream(bridge.stream(), device=local)
     if args.only:
         names = [n for n in args.only.split(",") if n]
-        bad = [n for n in names if n not in EXTRA_NAMES]
+        bad = [n for n in names if n not in EXTRA_NAMES + ("gemm_widths",)]
         if bad:
-            raise SystemExit(f"unknown workload(s) {bad}; choose from {EXTRA_NAMES}")
+            raise SystemExit(f"unknown workload(s) {bad}; choose from {EXTRA_NAMES + ('gemm_widths',)}")
         res = extra_measurements(bridge, torch, stream, measured_peaks(), max(1, args.steps), names, args.attn_batch)
         if rank == 0:
             print(json.dumps({"only": names, "extra": res}))

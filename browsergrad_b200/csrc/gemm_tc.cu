@@ -51,7 +51,14 @@ struct TcParams {
   uint32_t idesc;
   int group_m;
   int* status;
+  // grouped launch of the CTA-pair kernel: n_prob problems that share A, M, N, K and the epilogue kind and
+  // differ in B, bias and C (the q / k / v projections of one activation); tiles of all problems form one grid
+  int n_prob;
+  void* Cg[3];
+  const void* biasg[3];
 };
+constexpr int kMaxGroup = 3;
+struct PairBMaps { CUtensorMap m[2 * kMaxGroup]; };   // per problem: B (or its hi plane), then its lo plane
 
 // gelu(x) with the op order of the reference graph: 0.5*x*(1 + tanh(c*(x + 0.044715*x*x*x))),
 // tanh(u) = (e^u - e^-u) / (e^u + e^-u)
@@ -98,7 +105,7 @@ __device__ __forceinline__ float load_bias(const void* b, int dt, int col) {
 }
 
 // Epilogue of one 32-column chunk of one accumulator row: rounding, bias, activation, store.
-__device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t* r, int row, int col0) {
+__device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t* r, int row, int col0, void* C, const void* bias) {
   float v[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
@@ -107,9 +114,9 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
     else if (p.round_acc == BG_BF16 + 1) x = __bfloat162float(__float2bfloat16_rn(x));
     v[j] = x;
   }
-  if (p.bias) {
-    if (p.bias_dtype == BG_F32 && col0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0 && (col0 & 3) == 0) {
-      const float4* b4 = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + col0);
+  if (bias) {
+    if (p.bias_dtype == BG_F32 && col0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(bias) & 15) == 0 && (col0 & 3) == 0) {
+      const float4* b4 = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(bias) + col0);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float4 bb = __ldg(b4 + j);
@@ -121,13 +128,13 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (col0 + j < p.N) v[j] = __fadd_rn(v[j], load_bias(p.bias, p.bias_dtype, col0 + j));
+        if (col0 + j < p.N) v[j] = __fadd_rn(v[j], load_bias(bias, p.bias_dtype, col0 + j));
     }
   }
   const bool full = col0 + 32 <= p.N;
   const size_t base = (size_t)row * p.N + col0;
   if (p.c_dtype == BG_F64) {
-    double* out = reinterpret_cast<double*>(p.C) + base;
+    double* out = reinterpret_cast<double*>(C) + base;
 #pragma unroll
     for (int j = 0; j < 32; j += 2) {
       double w[2];
@@ -154,7 +161,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
     v[j] = x;
   }
   if (p.c_dtype == BG_F32) {
-    float* out = reinterpret_cast<float*>(p.C) + base;
+    float* out = reinterpret_cast<float*>(C) + base;
     if (full && (p.N & 3) == 0) {
 #pragma unroll
       for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
@@ -164,7 +171,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
         if (col0 + j < p.N) out[j] = v[j];
     }
   } else if (p.c_dtype == BG_F16) {
-    __half* out = reinterpret_cast<__half*>(p.C) + base;
+    __half* out = reinterpret_cast<__half*>(C) + base;
     if (full && (p.N & 7) == 0) {
 #pragma unroll
       for (int j = 0; j < 32; j += 8) {
@@ -179,7 +186,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
         if (col0 + j < p.N) out[j] = __float2half_rn(v[j]);
     }
   } else {
-    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + base;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(C) + base;
     if (full && (p.N & 7) == 0) {
 #pragma unroll
       for (int j = 0; j < 32; j += 8) {
@@ -357,7 +364,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
           const int col0 = n0 + (half * NC + c) * 32;
-          if (row < p.M && col0 < p.N) epilogue_chunk(p, reinterpret_cast<const uint32_t*>(acc[c]), row, col0);
+          if (row < p.M && col0 < p.N) epilogue_chunk(p, reinterpret_cast<const uint32_t*>(acc[c]), row, col0, p.C, p.bias);
         }
       } else {
         const int buf = use & 1;
@@ -374,7 +381,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             for (int j = 0; j < 32; ++j) r[j] = 0;
           }
           const int col0 = n0 + c * 32;
-          if (row < p.M && col0 < p.N) epilogue_chunk(p, r, row, col0);
+          if (row < p.M && col0 < p.N) epilogue_chunk(p, r, row, col0, p.C, p.bias);
         }
         // the buffer's values are in registers / memory: hand it back to the MMA warp
         tc_fence_before();
@@ -417,8 +424,7 @@ constexpr int kPairStages = 6;
 template <bool TF32, int TN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
-                    const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
-                    const __grid_constant__ TcParams p) {
+                    const __grid_constant__ PairBMaps tmB, const __grid_constant__ TcParams p) {
   constexpr int kHalf = 128;                           // rows of A each CTA stages
   constexpr int kBHalf = TN / 2;                       // rows of B each CTA stages
   constexpr int kABytes = kHalf * kStageRowBytes;
@@ -438,15 +444,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  const int num_m = (p.M + kTile - 1) / kTile, num_n = (p.N + TN - 1) / TN;
+  const int num_m = (p.M + kTile - 1) / kTile, num_n1 = (p.N + TN - 1) / TN;
+  const int num_n = num_n1 * p.n_prob;              // column tiles of all problems of the group, side by side
   const int num_tiles = num_m * num_n;
   const int gsz = p.group_m * num_n;
-  auto tile_origin = [&](int tile, int& m0, int& n0) {
+  auto tile_origin = [&](int tile, int& m0, int& n0, int& prob) {
     const int g = tile / gsz;
     const int first_m = g * p.group_m;
     const int gm = min(p.group_m, num_m - first_m);
     m0 = (first_m + (tile % gsz) % gm) * kTile;
-    n0 = ((tile % gsz) / gm) * TN;
+    const int nt = (tile % gsz) / gm;
+    prob = nt / num_n1;
+    n0 = (nt - prob * num_n1) * TN;
   };
 
   if (threadIdx.x == 0) {
@@ -472,13 +481,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
       int it = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        int m0, n0;
-        tile_origin(tile, m0, n0);
+        int m0, n0, prob;
+        tile_origin(tile, m0, n0, prob);
         for (int ch = 0; ch < n_chunks && ok; ++ch) {
           const int kb0 = ch * p.chunk_blocks, kb1 = min(kb0 + p.chunk_blocks, p.num_k_blocks);
           for (int pass = 0; pass < p.passes && ok; ++pass) {
             const CUtensorMap* ma = (p.passes == 3 && pass == 0) ? &tmA1 : &tmA0;
-            const CUtensorMap* mb = (p.passes == 3 && pass == 1) ? &tmB1 : &tmB0;
+            const CUtensorMap* mb = &tmB.m[2 * prob + ((p.passes == 3 && pass == 1) ? 1 : 0)];
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
               const int s = it % kPairStages;
               const uint32_t ph = (uint32_t)(it / kPairStages) & 1u;
@@ -536,8 +545,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     bool ok = true;
     const uint32_t acc_empty0 = map_to_cta(smem_u32(&acc_empty[0]), 0);   // the barriers live in CTA 0, 8 bytes apart
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-      int m0, n0;
-      tile_origin(tile, m0, n0);
+      int m0, n0, prob;
+      tile_origin(tile, m0, n0, prob);
+      void* const Cp = p.Cg[prob];
+      const void* const biasp = p.biasg[prob];
       const int row = m0 + (int)rank * kHalf + q * 32 + lane;
       const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
       if (TF32) {
@@ -548,7 +559,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
           const int col0 = n0 + (half * NC + c) * 32;
-          if (row < p.M && col0 < p.N) epilogue_chunk(p, reinterpret_cast<const uint32_t*>(acc[c]), row, col0);
+          if (row < p.M && col0 < p.N) epilogue_chunk(p, reinterpret_cast<const uint32_t*>(acc[c]), row, col0, Cp, biasp);
         }
       } else {
         const int buf = use & 1;
@@ -565,7 +576,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             for (int j = 0; j < 32; ++j) r[j] = 0;
           }
           const int col0 = n0 + c * 32;
-          if (row < p.M && col0 < p.N) epilogue_chunk(p, r, row, col0);
+          if (row < p.M && col0 < p.N) epilogue_chunk(p, r, row, col0, Cp, biasp);
         }
         tc_fence_before();
         __syncwarp();
@@ -712,16 +723,19 @@ cudaError_t launch_variant(const TcGemm& g, int* status, cudaStream_t s) {
 }
 
 template <bool TF32, int TN>
-cudaError_t launch_pair(const TcGemm& g, int* status, cudaStream_t s, bool* launched) {
+cudaError_t launch_pair(const TcGemm* gs, int n_prob, int* status, cudaStream_t s, bool* launched) {
   *launched = false;
-  CUtensorMap a0, a1, b0, b1;
+  const TcGemm& g = gs[0];
+  CUtensorMap a0, a1;
+  PairBMaps bm;
   if (!make_operand_map(&a0, g.A, g.ab_dtype, g.M, g.K, 128)) return cudaErrorInvalidValue;
-  if (!make_operand_map(&b0, g.B, g.ab_dtype, g.N, g.K, TN / 2)) return cudaErrorInvalidValue;
   a1 = a0;
-  b1 = b0;
-  if (TF32) {
-    if (!make_operand_map(&a1, g.A_lo, g.ab_dtype, g.M, g.K, 128)) return cudaErrorInvalidValue;
-    if (!make_operand_map(&b1, g.B_lo, g.ab_dtype, g.N, g.K, TN / 2)) return cudaErrorInvalidValue;
+  if (TF32 && !make_operand_map(&a1, g.A_lo, g.ab_dtype, g.M, g.K, 128)) return cudaErrorInvalidValue;
+  for (int i = 0; i < kMaxGroup; ++i) {
+    const TcGemm& gi = gs[i < n_prob ? i : 0];
+    if (!make_operand_map(&bm.m[2 * i], gi.B, gi.ab_dtype, gi.N, gi.K, TN / 2)) return cudaErrorInvalidValue;
+    bm.m[2 * i + 1] = bm.m[2 * i];
+    if (TF32 && !make_operand_map(&bm.m[2 * i + 1], gi.B_lo, gi.ab_dtype, gi.N, gi.K, TN / 2)) return cudaErrorInvalidValue;
   }
   TcParams p{};
   p.M = (int)g.M;
@@ -740,6 +754,8 @@ cudaError_t launch_pair(const TcGemm& g, int* status, cudaStream_t s, bool* laun
   p.wide = g.wide;
   p.status = status;
   p.group_m = 4;
+  p.n_prob = n_prob;
+  for (int i = 0; i < kMaxGroup; ++i) { p.Cg[i] = gs[i < n_prob ? i : 0].C; p.biasg[i] = gs[i < n_prob ? i : 0].bias; }
   const uint32_t fmt = TF32 ? 2u : (g.ab_dtype == BG_BF16 ? 1u : 0u);
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
   const size_t smem = (size_t)kPairStages * (128 + TN / 2) * kStageRowBytes + 256 + 1024;
@@ -765,9 +781,9 @@ cudaError_t launch_pair(const TcGemm& g, int* status, cudaStream_t s, bool* laun
     max_pairs = n;
   }
   if (max_pairs <= 0) return cudaSuccess;   // not launched: the caller falls back to single CTAs
-  const int64_t tiles = ((g.M + 255) / 256) * ((g.N + TN - 1) / TN);
+  const int64_t tiles = ((g.M + 255) / 256) * ((g.N + TN - 1) / TN) * n_prob;
   const int64_t pairs = tiles < max_pairs ? tiles : max_pairs;
-  kern<<<(unsigned)(2 * pairs), kTcThreads, smem, s>>>(a0, a1, b0, b1, p);
+  kern<<<(unsigned)(2 * pairs), kTcThreads, smem, s>>>(a0, a1, bm, p);
   *launched = true;
   return cudaGetLastError();
 }
@@ -792,12 +808,12 @@ int g_tc_pair_mode = 1;   // 0: never, 1: when the problem fills the device with
 // after the other; a tile costs about TN + 64 (the A half of every stage does not shrink with TN), so a
 // narrower tile wins when it removes a mostly idle last round: M = 8192, N = 768 is 96 tiles of 256 columns
 // (two rounds on 74 pairs, the second a third full) but 128 tiles of 192 columns (two shorter rounds).
-static int pair_tile_width(int64_t M, int64_t N, int pairs) {
+static int pair_tile_width(int64_t M, int64_t N, int pairs, int n_prob = 1) {
   int best = 256;
   int64_t best_cost = -1;
   const int widths[3] = {256, 192, 128};
   for (int w : widths) {
-    const int64_t tiles = ((M + 255) / 256) * ((N + w - 1) / w);
+    const int64_t tiles = ((M + 255) / 256) * ((N + w - 1) / w) * n_prob;
     const int64_t rounds = (tiles + pairs - 1) / pairs;
     const int64_t cost = rounds * (w + 64);
     if (best_cost < 0 || cost < best_cost) { best = w; best_cost = cost; }
@@ -806,13 +822,38 @@ static int pair_tile_width(int64_t M, int64_t N, int pairs) {
 }
 
 template <bool TF32>
-static cudaError_t launch_pair_width(int tn, const TcGemm& g, int* status, cudaStream_t s, bool* launched) {
-  if (tn == 192) return launch_pair<TF32, 192>(g, status, s, launched);
-  if (tn == 128) return launch_pair<TF32, 128>(g, status, s, launched);
-  return launch_pair<TF32, 256>(g, status, s, launched);
+static cudaError_t launch_pair_width(int tn, const TcGemm* gs, int n_prob, int* status, cudaStream_t s, bool* launched) {
+  if (tn == 192) return launch_pair<TF32, 192>(gs, n_prob, status, s, launched);
+  if (tn == 128) return launch_pair<TF32, 128>(gs, n_prob, status, s, launched);
+  return launch_pair<TF32, 256>(gs, n_prob, status, s, launched);
 }
 
 int g_tc_pair_width = 0;   // 0: chosen by pair_tile_width; 256 / 192 / 128: forced
+
+// Problems that share A, the shape and the epilogue kind (checked by the caller) as one launch of the CTA-pair
+// kernel: their column tiles lie side by side, so the last round of the grid is shared (three N = 768
+// projections: 3 x 2 rounds alone, 4 rounds together).  Falls back to one launch per problem.
+cudaError_t launch_gemm_tc_group(const TcGemm* gs, int n_prob, int* status, cudaStream_t s) {
+  if (n_prob < 1 || n_prob > kMaxGroup) return cudaErrorInvalidValue;
+  const TcGemm& g = gs[0];
+  const bool tf32 = g.ab_dtype == BG_F32;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (n_prob > 1 && g.M > 128 && g.N > 128 && g_tc_pair_mode != 0) {
+    bool launched = false;
+    const int tn = g_tc_pair_width ? g_tc_pair_width : pair_tile_width(g.M, g.N, sms / 2, n_prob);
+    {
+      cudaError_t e = tf32 ? launch_pair_width<true>(tn, gs, n_prob, status, s, &launched) : launch_pair_width<false>(tn, gs, n_prob, status, s, &launched);
+      if (e != cudaSuccess || launched) return e;
+    }
+  }
+  for (int i = 0; i < n_prob; ++i) {
+    cudaError_t e = launch_gemm_tc(gs[i], status, s);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
 
 cudaError_t launch_gemm_tc(const TcGemm& g, int* status, cudaStream_t s) {
   const bool tf32 = g.ab_dtype == BG_F32;
@@ -824,7 +865,7 @@ cudaError_t launch_gemm_tc(const TcGemm& g, int* status, cudaStream_t s) {
   if (pair_ok && (g_tc_pair_mode == 2 || (g_tc_pair_mode == 1 && tiles256 >= 64))) {
     bool launched = false;
     const int tn = g_tc_pair_width ? g_tc_pair_width : pair_tile_width(g.M, g.N, sms / 2);
-    cudaError_t e = tf32 ? launch_pair_width<true>(tn, g, status, s, &launched) : launch_pair_width<false>(tn, g, status, s, &launched);
+    cudaError_t e = tf32 ? launch_pair_width<true>(tn, &g, 1, status, s, &launched) : launch_pair_width<false>(tn, &g, 1, status, s, &launched);
     if (e != cudaSuccess || launched) return e;
   }
   // 128 x 256 tiles halve the B traffic per flop; 128 x 128 tiles when the wide ones would leave SMs idle

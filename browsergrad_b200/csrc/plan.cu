@@ -251,6 +251,26 @@ class Compiler {
   std::map<int, std::pair<int, int>> gemm_cast_src_;
   int absorbable_cast(int node, int dtype16, int& cast_node);
   void plan_gemm_casts();
+  // Tensor-core GEMMs of one plan that read the same A and differ only in their leaf B / bias (the q / k / v
+  // projections of one activation) run as one launch: every member prepares its operands in a unit of its own,
+  // the last member launches all of them and is the producer of every member's result.
+  struct GroupRun {
+    TcGemm g[3]; void* tmp[3]; size_t tmp_bytes[3];
+    // where each member's result goes: resolved by the launching member, when every result slot exists
+    std::shared_ptr<TcEpilogue> epi[3];
+    int sc_slot[3], c_dt[3];
+  };
+  struct GemmGroup {
+    std::vector<int> members;       // MATMUL nodes in node order
+    std::vector<int> punits;        // units of the members emitted so far
+    std::vector<int> finals;        // result nodes of the members emitted so far
+    std::vector<int> keep_slots;    // scratch the members wrote that the joint launch reads
+    std::shared_ptr<GroupRun> run;
+  };
+  std::vector<GemmGroup> gemm_groups_;
+  std::map<int, int> gemm_group_of_;
+  void plan_gemm_groups();
+  std::map<std::tuple<int, int64_t, int64_t, int>, std::pair<int, int>> conv_memo_;   // fp32 A operand -> (16-bit slot, converting unit)
   std::set<int> absorbed_groups_;
   int tc_mode(int n);                      // -1: SIMT; 0: 16-bit operands; 1: 3xTF32
   std::string act_expr(int node, int x, int g, int depth);
@@ -1713,6 +1733,56 @@ int Compiler::absorbable_cast(int node, int dtype16, int& cast_node) {
 // Autocast Linear layers reach the tensor-core GEMM as MATMUL(CAST(x), PERMUTE(CAST(W))).  Where such a cast only
 // feeds this GEMM, the GEMM unit converts the operand itself with a vectorised pass (and keeps the converted copy
 // of a weight bound by handle with that handle), so the interpreter's CAST kernels and their outputs disappear.
+void Compiler::plan_gemm_groups() {
+  gemm_groups_.clear();
+  gemm_group_of_.clear();
+  if (!ctx_->fusion || !ctx_->tensor_cores) return;
+  typedef std::vector<int64_t> Key;
+  std::map<Key, std::vector<int>> buckets;
+  for (int n = 0; n < (int)nodes_.size(); ++n) {
+    if (kind_[n] != K_OTHER || nodes_[n].op != BG_OP_MATMUL || nodes_[n].rank != 2) continue;
+    if (attn_plan_.count(n) || attn_absorbed_.count(n)) continue;
+    const int mode = tc_mode(n);
+    if (mode < 0) continue;
+    const int a = resolve(nodes_[n].in[0]), b = resolve(nodes_[n].in[1]);
+    const View& av = view_[a];
+    const View& bv = view_[b];
+    int a_f32 = -1, b_f32 = -1;
+    {
+      auto cs = gemm_cast_src_.find(n);
+      if (cs != gemm_cast_src_.end()) { a_f32 = cs->second.first; b_f32 = cs->second.second; }
+    }
+    // B (or the fp32 tensor behind its absorbed cast) is bound from outside: nothing of this plan produces it
+    const int b_leaf = b_f32 >= 0 ? b_f32 : b;
+    if (!leaflike_[b_leaf] || bv.is_const || view_[b_leaf].slot < 0 || !cp_->slots[view_[b_leaf].slot].external) continue;
+    const int64_t M = av.shape[0], K = av.shape[1], N = bv.shape[1];
+    if (M <= 128 || N <= 128) continue;                       // the joint launch is a CTA-pair launch
+    if (!(bv.stride[0] == 1 && bv.stride[1] == K)) continue;  // B read in place
+    int fin = n, bias_dt = -1, act = 0, round_acc = 0, wide = 0;
+    auto ep = epi_plan_.find(n);
+    if (ep != epi_plan_.end()) {
+      fin = ep->second.final_node; act = ep->second.act; round_acc = ep->second.round_acc; wide = ep->second.wide;
+      if (ep->second.bias_node >= 0) {
+        if (!leaflike_[ep->second.bias_node]) continue;
+        bias_dt = view_[ep->second.bias_node].dtype;
+      }
+    }
+    Key key = {a_f32 >= 0 ? a_f32 : a, M, N, K, mode, av.dtype, bv.dtype, nodes_[n].dtype, nodes_[fin].dtype, act, round_acc, wide, bias_dt,
+               a_f32, b_f32 >= 0 ? 1 : 0};
+    buckets[key].push_back(n);
+  }
+  for (auto& kv : buckets) {
+    const std::vector<int>& mem = kv.second;
+    for (size_t i = 0; i + 1 < mem.size(); i += 3) {
+      GemmGroup g;
+      for (size_t j = i; j < mem.size() && j < i + 3; ++j) g.members.push_back(mem[j]);
+      g.run = std::make_shared<GroupRun>();
+      for (int m : g.members) gemm_group_of_[m] = (int)gemm_groups_.size();
+      gemm_groups_.push_back(std::move(g));
+    }
+  }
+}
+
 void Compiler::plan_gemm_casts() {
   gemm_cast_src_.clear();
   if (!ctx_->fusion || !ctx_->tensor_cores) return;
@@ -2199,7 +2269,18 @@ void Compiler::emit_matmul(int n, int key) {
         const View& sv = view_[a_f32];
         const int f32_slot = sv.slot;
         const int64_t f32_off = (sv.off + av.off) * 4;
+        const auto ckey = std::make_tuple(f32_slot, f32_off, M * K, ab);
+        auto chit = conv_memo_.find(ckey);
+        if (chit != conv_memo_.end()) {
+          // another GEMM of this plan already converts the same activation
+          a_conv = chit->second.first;
+          pu.dep_punits.push_back(chit->second.second);
+          pu.u.reads.push_back(a_conv);
+          a_src = a_conv; a_off = 0;
+          pu.dep_nodes.erase(pu.dep_nodes.begin());
+        } else {
         a_conv = new_slot(M * K * 2, false, -1);
+        conv_memo_[ckey] = {a_conv, (int)punits_.size()};
         PUnit cu;
         cu.order_key = key;
         cu.dep_nodes = {a_f32};
@@ -2216,6 +2297,7 @@ void Compiler::emit_matmul(int n, int key) {
         pu.u.reads.push_back(a_conv);
         a_src = a_conv; a_off = 0;
         pu.dep_nodes.erase(pu.dep_nodes.begin());      // A now comes from the conversion unit
+        }
       }
       if (b_f32 >= 0) {
         const View& sv = view_[b_f32];
@@ -2285,6 +2367,35 @@ void Compiler::emit_matmul(int n, int key) {
       }
       pu.u.launches = 1 + (a_copy >= 0) + (b_copy >= 0) + (mode == 1 ? (a_shared ? 0 : 1) + 1 : 0) + (b_f32 >= 0);
       pu.u.name = std::string(mode == 0 ? "gemm_tc" : "gemm_tc_3xtf32") + epi_name + "[" + dtype_name(t.dtype) + "]";
+      // member of a joint launch: every member but the last only prepares; the last one launches and produces all results
+      std::shared_ptr<GroupRun> grun;
+      int gidx = 0, gcount = 1;
+      {
+        auto gi = gemm_group_of_.find(n);
+        if (gi != gemm_group_of_.end() && a_copy < 0) {
+          GemmGroup& G = gemm_groups_[gi->second];
+          grun = G.run;
+          gcount = (int)G.members.size();
+          gidx = (int)(std::find(G.members.begin(), G.members.end(), n) - G.members.begin());
+          const int my_final = pu.out_nodes[0];
+          grun->epi[gidx] = epi;
+          grun->sc_slot[gidx] = sc;
+          grun->c_dt[gidx] = c_dt;
+          for (int w : pu.u.writes) G.keep_slots.push_back(w);
+          if (gidx + 1 < gcount) {
+            G.finals.push_back(my_final);
+            G.punits.push_back((int)punits_.size());
+            pu.out_nodes.clear();
+            pu.u.launches -= 1;
+            pu.u.name = std::string("gemm_operands[") + dtype_name(t.dtype) + "]";
+          } else {
+            for (int f : G.finals) pu.out_nodes.push_back(f);
+            for (int u : G.punits) pu.dep_punits.push_back(u);
+            for (int w : G.keep_slots) pu.u.reads.push_back(w);
+            pu.u.name += " x" + std::to_string(gcount);
+          }
+        }
+      }
       cp_->uses_status = true;
       const int sc_slot = sc;
       pu.u.fn = [=](Run& r) {
@@ -2356,8 +2467,25 @@ void Compiler::emit_matmul(int n, int key) {
         g.act = epi->act;
         g.round_acc = epi->round_acc;
         g.wide = epi->wide;
+        const size_t tmp_bytes = mode == 1 ? 2 * N * K * 4 : N * K * 2;
+        if (grun) {
+          grun->g[gidx] = g;
+          grun->tmp[gidx] = tmp_planes;
+          grun->tmp_bytes[gidx] = tmp_bytes;
+          if (gidx + 1 < gcount) return (int)BG_OK;
+          for (int i = 0; i < gcount; ++i) {
+            const TcEpilogue& ei = *grun->epi[i];
+            grun->g[i].C = r.ptr[ei.out_slot >= 0 ? ei.out_slot : grun->sc_slot[i]];
+            grun->g[i].c_dtype = ei.out_slot >= 0 ? ei.out_dtype : grun->c_dt[i];
+            grun->g[i].bias = ei.bias_slot >= 0 ? reinterpret_cast<char*>(r.ptr[ei.bias_slot]) + ei.bias_off : nullptr;
+          }
+          e = launch_gemm_tc_group(grun->g, gcount, r.ctx->d_status, st);
+          for (int i = 0; i < gcount; ++i)
+            if (grun->tmp[i]) { dev_free(r.ctx, grun->tmp[i], grun->tmp_bytes[i]); grun->tmp[i] = nullptr; }
+          return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "tensor-core gemm launch");
+        }
         e = launch_gemm_tc(g, r.ctx->d_status, st);
-        if (tmp_planes) dev_free(r.ctx, tmp_planes, mode == 1 ? 2 * N * K * 4 : N * K * 2);    // stream-ordered: released after the GEMM has run
+        if (tmp_planes) dev_free(r.ctx, tmp_planes, tmp_bytes);    // stream-ordered: released after the GEMM has run
         return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "tensor-core gemm launch");
       };
       tc_unit_of_[n] = (int)punits_.size();
@@ -2567,6 +2695,7 @@ bool Compiler::try_lower() {
   copy_src_.clear();
   tc_epilogues_.clear();
   split_memo_.clear();
+  conv_memo_.clear();
   tc_unit_of_.clear();
   attn_plan_.clear();
   attn_absorbed_.clear();
@@ -2584,6 +2713,7 @@ bool Compiler::try_lower() {
   plan_attention();
   plan_gemm_casts();
   plan_tc_epilogues(groups);
+  plan_gemm_groups();
   // only groups with a materialised member or a tail do any work
   for (auto& kv : groups) {
     const std::vector<int>& mem = kv.second;

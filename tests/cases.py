@@ -104,6 +104,26 @@ def _attn_small(b: int, h: int, s: int, d: int) -> Callable[[], Dict[str, np.nda
     return make
 
 
+def _qkv_inputs(m: int, n: int, k: int) -> Callable[[], Dict[str, np.ndarray]]:
+    def make() -> Dict[str, np.ndarray]:
+        r = _rng(77)
+        out = {"x": r.standard_normal((m, k), dtype=np.float32)}
+        for name in "qkv":
+            out["w" + name] = (r.standard_normal((n, k), dtype=np.float32) / np.float32(np.sqrt(k)))
+            out["b" + name] = r.standard_normal((n,), dtype=np.float32) * np.float32(0.1)
+        return out
+    return make
+
+
+def _qkv(api: Any, t: Dict[str, Any], names: str, amp: str = "") -> Any:
+    def build() -> Any:
+        return api.cat([api.linear(t["x"], t["w" + c], t["b" + c]) for c in names], 1)
+    if amp:
+        with api.autocast(dtype=amp):
+            return build()
+    return build()
+
+
 def _ln_inputs(rows: int, cols: int) -> Callable[[], Dict[str, np.ndarray]]:
     def make() -> Dict[str, np.ndarray]:
         r = _rng(300 + cols)
@@ -209,6 +229,11 @@ CASES: Dict[str, Case] = {
                        lambda api, t, raw: api.relu(api.linear(t["x"], t["w"], t["bias"]))),
     "c3_tc_rowmajor_b": Case(lambda: configs.linear_inputs(256, 256, 256),
                              lambda api, t, raw: t["x"] @ t["w"]),
+    "c3_group_qkv_f32": Case(_qkv_inputs(300, 272, 264), lambda api, t, raw: _qkv(api, t, "qkv")),
+    "c3_group_pair_f32_long_k": Case(_qkv_inputs(264, 192, 1100), lambda api, t, raw: _qkv(api, t, "qk")),
+    "c3_group_qkv_f16": Case(_qkv_inputs(300, 272, 264), lambda api, t, raw: _qkv(api, t, "qkv", "float16"), rtol=2e-2),
+    "c3_group_four_bf16": Case(_qkv_inputs(520, 160, 264), lambda api, t, raw: _qkv(api, t, "qkvq", "bfloat16"), rtol=2e-2,
+                               reference_has_it=False),
     "c4_attn_mask": Case(_attn_small(2, 3, 64, 16),
                          lambda api, t, raw: configs.attention(api, t, "mask")),
     "c4_attn_causal": Case(_attn_small(2, 3, 64, 16),
