@@ -384,6 +384,7 @@ int bg_set_option(bg_context* ctx, const char* key, int64_t value) {
     g_tc_pair_width = (int)value;
   }
   else if (k == "static_patterns") { ctx->static_patterns = value != 0; ctx->plan_cache.clear(); }
+  else if (k == "gemm_groups") { ctx->gemm_groups = value != 0; ctx->plan_cache.clear(); }
   else return fail(ctx, BG_ERR_INVALID, "set_option: unknown option '" + k + "'");
   if (k == "f64_contraction") ctx->plan_cache.clear();
   return BG_OK;

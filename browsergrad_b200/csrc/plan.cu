@@ -1736,7 +1736,7 @@ int Compiler::absorbable_cast(int node, int dtype16, int& cast_node) {
 void Compiler::plan_gemm_groups() {
   gemm_groups_.clear();
   gemm_group_of_.clear();
-  if (!ctx_->fusion || !ctx_->tensor_cores) return;
+  if (!ctx_->fusion || !ctx_->tensor_cores || !ctx_->gemm_groups) return;
   typedef std::vector<int64_t> Key;
   std::map<Key, std::vector<int>> buckets;
   for (int n = 0; n < (int)nodes_.size(); ++n) {

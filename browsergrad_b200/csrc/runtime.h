@@ -38,6 +38,7 @@ struct bg_context {
   bool fusion = true;
   bool tensor_cores = true;
   bool static_patterns = true;   // use the specialised pattern kernels where an expression matches
+  bool gemm_groups = true;       // launch tensor-core GEMMs that share their A operand together
   // device status word written by kernels that can refuse (index range, bounded waits)
   int* d_status = nullptr;
   int* h_status = nullptr;  // pinned

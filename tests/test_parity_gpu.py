@@ -138,6 +138,37 @@ def test_cta_pair_gemm_matches_oracle(bridge, name):
         bridge.set_option("gemm_pair_tile_width", 0)
 
 
+@pytest.mark.parametrize("name,unit,members", [
+    ("c3_group_qkv_f32", "gemm_tc_3xtf32+bias[float32] x3", 3),
+    ("c3_group_pair_f32_long_k", "gemm_tc_3xtf32+bias[float32] x2", 2),
+    ("c3_group_qkv_f16", "gemm_tc+bias[float16] x3", 3),
+    ("c3_group_four_bf16", "gemm_tc+bias[bfloat16] x3", 3),
+])
+def test_projections_of_one_activation_launch_together(bridge, name, unit, members):
+    """Linear layers that read the same activation (q / k / v) run as one CTA-pair launch whose grid holds the tiles
+    of all of them; the activation is split / converted once.  Same products and order as separate launches."""
+    case = CASES[name]
+    t, store, _ = build_case(case)
+    want = oracle_value(t, store)
+    for width in (0, 192):
+        bridge.set_option("gemm_pair_tile_width", width)
+        try:
+            got = realize_cuda(t, bridge)
+        finally:
+            bridge.set_option("gemm_pair_tile_width", 0)
+        trace = bridge.last_plan_trace()
+        assert unit in trace and sum(ln.startswith("gemm_operands[") for ln in trace) == members - 1, trace
+        assert sum(ln.startswith("convert16[") for ln in trace) <= 1, trace
+        check(case, got, want, f"{name} (joint launch, width {width})")
+    bridge.set_option("gemm_groups", 0)
+    try:
+        apart = realize_cuda(t, bridge)
+        assert not any(ln.startswith("gemm_operands[") for ln in bridge.last_plan_trace())
+    finally:
+        bridge.set_option("gemm_groups", 1)
+    assert got.tobytes() == apart.tobytes()
+
+
 def test_autocast_attention_is_one_unit_and_keeps_mask_classes_with_the_handle(bridge):
     """The fp32 -> 16-bit casts of Q, K, V are folded into the operand staging of the fused kernel, and the
     mask tile classes computed for a mask bound by handle live exactly as long as that handle."""
