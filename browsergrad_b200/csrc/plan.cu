@@ -2469,6 +2469,11 @@ void Compiler::emit_matmul(int n, int key) {
         g.wide = epi->wide;
         const size_t tmp_bytes = mode == 1 ? 2 * N * K * 4 : N * K * 2;
         if (grun) {
+          // a run that stopped between the members leaves their temporary planes behind: the next run's
+          // first member releases them
+          if (gidx == 0)
+            for (int i = 0; i < gcount; ++i)
+              if (grun->tmp[i]) { dev_free(r.ctx, grun->tmp[i], grun->tmp_bytes[i]); grun->tmp[i] = nullptr; }
           grun->g[gidx] = g;
           grun->tmp[gidx] = tmp_planes;
           grun->tmp_bytes[gidx] = tmp_bytes;
