@@ -178,6 +178,10 @@ cudaError_t launch_flip(const StridedView& in, void* out, int64_t numel, int axi
 struct PlaceFill { int is_int; double f; long long n; };
 cudaError_t launch_place(const StridedView& in, void* out, int out_dtype, const int64_t* out_shape, int axis, int64_t axis_offset,
                          cudaStream_t s, const PlaceFill* fill = nullptr);
+// scatter: out (already a dense copy of the target) receives src[i] (or the constant) at the place index entry i
+// names along `dim`; `claim` is scratch of one int per output element.  Bad or repeated destinations set *status.
+cudaError_t launch_scatter(const int64_t* idx, const void* src, void* out, int* claim, int esize, int rank, const int64_t* out_shape,
+                           const int64_t* idx_shape, int dim, bool src_is_const, unsigned long long const_bits, int* status, cudaStream_t s);
 // cumsum along `axis` in the output dtype, sequential per line as NumPy's add.accumulate.
 cudaError_t launch_cumsum(const StridedView& in, void* out, int out_dtype, int axis, int reverse, cudaStream_t s);
 

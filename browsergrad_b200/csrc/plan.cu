@@ -246,6 +246,7 @@ class Compiler {
   void plan_attention();
   void emit_attention(int n, int key);
   void emit_shape_op(int n, int key);
+  void emit_scatter(int n, int key);
   std::map<int, EpiPlan> epi_plan_;       // MATMUL node -> folded epilogue
   // MATMUL node -> fp32 nodes behind absorbed fp32 -> 16-bit CASTs of its A / B operand (-1: operand used as is)
   std::map<int, std::pair<int, int>> gemm_cast_src_;
@@ -619,7 +620,7 @@ void Compiler::build_views() {
         break;
       case BG_OP_MATMUL: case BG_OP_INDEX: case BG_OP_CROSS_ENTROPY:
       case BG_OP_TRIL: case BG_OP_TRIU: case BG_OP_FLIP: case BG_OP_CONCAT: case BG_OP_CUMSUM:
-      case BG_OP_SORT_INDICES: case BG_OP_TOPK_INDICES:
+      case BG_OP_SORT_INDICES: case BG_OP_TOPK_INDICES: case BG_OP_SCATTER:
         kind_[i] = K_OTHER;
         v.set_dense(n.shape, n.rank);
         v.slot = new_slot(n.numel() * dtype_size(n.dtype), false, i);
@@ -2653,6 +2654,74 @@ void Compiler::emit_shape_op(int n, int key) {
   add_unit(std::move(pu));
 }
 
+// SCATTER: dense copy of the target, then one thread per index entry stores its source value.
+void Compiler::emit_scatter(int n, int key) {
+  const Node& t = nodes_[n];
+  if (t.in.size() != 3) err(BG_ERR_INVALID, "SCATTER: target, index and source inputs required");
+  const int tg = resolve(t.in[0]), ix = resolve(t.in[1]), sr = resolve(t.in[2]);
+  const View tv = view_[tg], iv = view_[ix], sv = view_[sr];
+  const int rank = t.rank, dim = (int)t.iarg[0];
+  if (rank == 0 || tv.rank != rank || iv.rank != rank) err(BG_ERR_INVALID, "SCATTER: target and index must have the same nonzero rank");
+  if (dim < 0 || dim >= rank) err(BG_ERR_INVALID, "SCATTER: dimension out of range");
+  if (iv.dtype != BG_I64) err(BG_ERR_INVALID, "SCATTER: index dtype must be int64");
+  if (tv.dtype != t.dtype || sv.dtype != t.dtype) err(BG_ERR_INVALID, "SCATTER: target, source and result share one dtype");
+  for (int d = 0; d < rank; ++d) {
+    if (tv.shape[d] != t.shape[d]) err(BG_ERR_INVALID, "SCATTER: result shape must equal the target's");
+    if (iv.shape[d] > tv.shape[d]) err(BG_ERR_INVALID, "SCATTER: index extent exceeds target extent");
+  }
+  if (tv.is_const || iv.is_const) err(BG_ERR_UNSUPPORTED, "SCATTER: target and index must be tensors");
+  if (!iv.contiguous()) err(BG_ERR_UNSUPPORTED, "SCATTER: index must be a dense tensor");
+  const bool src_const = sv.is_const;
+  if (!src_const) {
+    if (sv.rank != rank || !sv.contiguous()) err(BG_ERR_UNSUPPORTED, "SCATTER: source must be a dense tensor of the index's shape or a scalar");
+    for (int d = 0; d < rank; ++d)
+      if (sv.shape[d] != iv.shape[d]) err(BG_ERR_INVALID, "SCATTER: source shape must equal the index shape");
+  }
+  // the scalar source in the result's own representation
+  unsigned long long bits = 0;
+  if (src_const) {
+    switch (t.dtype) {
+      case BG_F64: { double v = sv.cf; memcpy(&bits, &v, 8); break; }
+      case BG_F32: { float v = (float)sv.cf; memcpy(&bits, &v, 4); break; }
+      case BG_F16: case BG_BF16: err(BG_ERR_UNSUPPORTED, "SCATTER: scalar sources of 16-bit tensors are not supported");
+      case BG_BOOL: bits = sv.ci != 0; break;
+      default: bits = (unsigned long long)sv.ci; break;
+    }
+  }
+  own_slot(n);
+  const int es = dtype_size(t.dtype);
+  const int64_t numel = t.numel();
+  const int claim_slot = new_slot(std::max<int64_t>(numel, 1) * 4, false, -1);
+  const int st = tv.slot, si = iv.slot, ss = src_const ? -1 : sv.slot, so = view_[n].slot;
+  const int64_t off_t = tv.off * es, off_i = iv.off * 8, off_s = src_const ? 0 : sv.off * es;
+  StridedView tmpl{};
+  tmpl.dtype = tv.dtype;
+  tmpl.rank = rank;
+  for (int d = 0; d < rank; ++d) { tmpl.shape[d] = tv.shape[d]; tmpl.stride[d] = tv.shape[d] == 1 ? 0 : tv.stride[d]; }
+  std::vector<int64_t> oshape(t.shape, t.shape + rank), ishape(iv.shape, iv.shape + rank);
+  cp_->uses_status = true;
+  PUnit pu;
+  pu.order_key = key;
+  pu.dep_nodes = {tg, ix};
+  if (!src_const) pu.dep_nodes.push_back(sr);
+  pu.out_nodes = {n};
+  pu.u.writes.push_back(claim_slot);
+  pu.u.launches = 3;
+  pu.u.name = "scatter[SCATTER]";
+  pu.u.fn = [=](Run& r) {
+    StridedView v = tmpl;
+    v.ptr = reinterpret_cast<char*>(r.ptr[st]) + off_t;
+    cudaError_t e = launch_strided_copy(v, r.ptr[so], numel, r.ctx->stream);
+    if (e == cudaSuccess)
+      e = launch_scatter(reinterpret_cast<const int64_t*>(reinterpret_cast<char*>(r.ptr[si]) + off_i),
+                         ss >= 0 ? reinterpret_cast<char*>(r.ptr[ss]) + off_s : nullptr, r.ptr[so],
+                         reinterpret_cast<int*>(r.ptr[claim_slot]), es, rank, oshape.data(), ishape.data(), dim, src_const, bits,
+                         r.ctx->d_status, r.ctx->stream);
+    return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "scatter launch");
+  };
+  add_unit(std::move(pu));
+}
+
 void Compiler::emit_ce(int n, int key) {
   const Node& t = nodes_[n];
   if (t.in.size() != 2) err(BG_ERR_UNSUPPORTED, "CROSS_ENTROPY: class weights are not supported");
@@ -2813,6 +2882,7 @@ bool Compiler::try_lower() {
         case BG_OP_CROSS_ENTROPY: emit_ce(i, i); break;
         case BG_OP_TRIL: case BG_OP_TRIU: case BG_OP_FLIP: case BG_OP_CONCAT: case BG_OP_CUMSUM:
         case BG_OP_SORT_INDICES: case BG_OP_TOPK_INDICES: emit_shape_op(i, i); break;
+        case BG_OP_SCATTER: emit_scatter(i, i); break;
         case BG_OP_RESHAPE:
           if (!copy_elided_.count(i)) emit_copy(i, copy_src_.at(i), resolve(n.in[0]), i);
           break;
@@ -3074,7 +3144,7 @@ int run_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs, 
   }
   if (status_rc) {
     cleanup(false);
-    return fail(ctx, status_rc, status_rc == BG_ERR_INDEX_RANGE ? "run_tensor_plan: gather / cross_entropy index outside its axis"
+    return fail(ctx, status_rc, status_rc == BG_ERR_INDEX_RANGE ? "run_tensor_plan: gather / scatter / cross_entropy index outside its axis, or scatter indices naming one destination twice"
                                                                : "run_tensor_plan: device-side status " + std::to_string(status_rc));
   }
   if (out_host) {

@@ -203,6 +203,56 @@ cudaError_t launch_place(const StridedView& in, void* out, int out_dtype, const 
   return cudaGetLastError();
 }
 
+// One thread per index entry: its coordinates, with the entry's value in place of the coordinate along `dim`,
+// name the destination in the dense output.  `claim` (one int per output element, zeroed) catches two entries
+// that name one destination.
+struct ScatterArg {
+  int64_t idx_shape[kMaxRank];
+  int64_t out_stride[kMaxRank];
+  int64_t axis_extent;
+  int rank, dim, esize;
+  int src_is_const;
+  unsigned long long const_bits;   // the scalar source in the output's representation
+};
+
+__global__ void scatter_kernel(const int64_t* idx, const char* src, char* out, int* claim, ScatterArg a, int64_t numel, int* status) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < numel; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t g = idx[i];
+    if (g < 0 || g >= a.axis_extent) { atomicExch(status, BG_ERR_INDEX_RANGE); continue; }
+    int64_t rem = i, dst = 0;
+    for (int d = a.rank - 1; d >= 0; --d) {
+      const int64_t c = rem % a.idx_shape[d];
+      rem /= a.idx_shape[d];
+      dst += (d == a.dim ? g : c) * a.out_stride[d];
+    }
+    if (atomicExch(&claim[dst], 1) != 0) { atomicExch(status, BG_ERR_INDEX_RANGE); continue; }
+    switch (a.esize) {
+      case 1: reinterpret_cast<uint8_t*>(out)[dst] = a.src_is_const ? (uint8_t)a.const_bits : reinterpret_cast<const uint8_t*>(src)[i]; break;
+      case 2: reinterpret_cast<uint16_t*>(out)[dst] = a.src_is_const ? (uint16_t)a.const_bits : reinterpret_cast<const uint16_t*>(src)[i]; break;
+      case 4: reinterpret_cast<uint32_t*>(out)[dst] = a.src_is_const ? (uint32_t)a.const_bits : reinterpret_cast<const uint32_t*>(src)[i]; break;
+      default: reinterpret_cast<unsigned long long*>(out)[dst] = a.src_is_const ? a.const_bits : reinterpret_cast<const unsigned long long*>(src)[i]; break;
+    }
+  }
+}
+
+cudaError_t launch_scatter(const int64_t* idx, const void* src, void* out, int* claim, int esize, int rank, const int64_t* out_shape,
+                           const int64_t* idx_shape, int dim, bool src_is_const, unsigned long long const_bits, int* status, cudaStream_t s) {
+  if (dim < 0 || dim >= rank || rank > kMaxRank) return cudaErrorInvalidValue;
+  ScatterArg a{};
+  int64_t numel = 1, st = 1, out_numel = 1;
+  for (int d = rank - 1; d >= 0; --d) { a.out_stride[d] = st; st *= out_shape[d]; }
+  for (int d = 0; d < rank; ++d) { a.idx_shape[d] = idx_shape[d]; numel *= idx_shape[d]; out_numel *= out_shape[d]; }
+  if (numel == 0 || out_numel == 0) return cudaSuccess;
+  a.axis_extent = out_shape[dim];
+  a.rank = rank; a.dim = dim; a.esize = esize;
+  a.src_is_const = src_is_const ? 1 : 0;
+  a.const_bits = const_bits;
+  cudaError_t e = cudaMemsetAsync(claim, 0, (size_t)out_numel * sizeof(int), s);
+  if (e != cudaSuccess) return e;
+  scatter_kernel<<<grid_for(numel), 256, 0, s>>>(idx, reinterpret_cast<const char*>(src), reinterpret_cast<char*>(out), claim, a, numel, status);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_cumsum(const StridedView& in, void* out, int out_dtype, int axis, int reverse, cudaStream_t s) {
   if (axis < 0 || axis >= in.rank) return cudaErrorInvalidValue;
   int64_t lines = 1, inner = 1;

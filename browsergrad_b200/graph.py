@@ -456,6 +456,35 @@ class Tensor:
                                {"dim": axis}))
 
 
+    def scatter(self, dim: int, index: "Tensor", src: Any) -> "Tensor":
+        """``SCATTER`` node (_tensor_proxy.py:2703-2751): a copy of ``self`` with ``src`` stored at the places
+        ``index`` names along ``dim``.  ``src`` is a tensor of the index's shape and the target's dtype, or a
+        scalar that is normalised to the target dtype (_tensor_proxy.py:291-320).  Indices outside the axis or
+        naming one destination twice are refused when the graph is realized."""
+        if index.dtype != "int64":
+            raise ValueError("scatter: index dtype must be int64")
+        if index.ndim != self.ndim or self.ndim == 0:
+            raise ValueError("scatter: target and index must have the same nonzero rank")
+        axis = int(dim) + self.ndim if int(dim) < 0 else int(dim)
+        if axis < 0 or axis >= self.ndim:
+            raise ValueError("scatter: dim out of range")
+        if any(i > s for s, i in zip(self.shape, index.shape)):
+            raise ValueError("scatter: index extent exceeds target extent")
+        if isinstance(src, Tensor):
+            if src.dtype != self.dtype or src.shape not in ((), index.shape):
+                raise ValueError("scatter: source must have the target's dtype and the index's shape")
+            source = src._uop
+        else:
+            if self.dtype == "bool":
+                value: Any = bool(src)
+            elif self.dtype.startswith("float"):
+                value = float(np.asarray(src, dtype=np.dtype(self.dtype)).item())
+            else:
+                value = int(src)
+            source = Node("CONST", (), (), self.dtype, {"value": value})
+        return self._wrap(Node("SCATTER", (self._uop, index._uop, source), self.shape, self.dtype, {"dim": axis}))
+
+
 def _to_tensor(value: Any, store: Optional[BufferStore] = None) -> Tensor:
     if isinstance(value, Tensor):
         return value

@@ -167,7 +167,7 @@ def encode_plan(plan: Dict[str, Any], permute_axes: Optional[Dict[int, Tuple[int
             st.iarg[0] = int(arg["rows"])
             st.iarg[1] = int(arg["cols"])
             st.farg[0] = float(arg.get("eps", 1e-5))
-        elif op == "INDEX":
+        elif op in ("INDEX", "SCATTER"):
             st.iarg[0] = int(arg["dim"])
         elif op in ("TRIL", "TRIU"):
             st.iarg[0] = int(arg["diagonal"])

@@ -73,7 +73,12 @@ typedef enum bg_opcode {
      SORT_INDICES iarg[1] = descending; TOPK_INDICES iarg[1] = k, iarg[2] = largest, iarg[3] = sorted (must be 1).
      The *_VALUES opcodes of the reference are gathers along the same axis and arrive as INDEX. */
   BG_OP_SORT_INDICES = 33, BG_OP_TOPK_INDICES = 34,
-  BG_OP_COUNT = 35
+  /* Overwrite scatter along iarg[0] (_realize.py:1179-1189; contract _framework_contracts.py:5494-5630):
+     inputs (target, int64 index, source of the index's shape or a scalar constant); the result is a copy
+     of the target with source values stored at the indexed places.  An index outside the axis or two
+     index entries naming one destination end the plan with BG_ERR_INDEX_RANGE, as the reference raises. */
+  BG_OP_SCATTER = 35,
+  BG_OP_COUNT = 36
 } bg_opcode;
 
 typedef enum bg_cmp { BG_CMP_EQ = 0, BG_CMP_NE = 1, BG_CMP_LT = 2, BG_CMP_LE = 3,

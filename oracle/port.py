@@ -206,6 +206,24 @@ def _h_pad(node, vt, store):  # _realize.py:1131-1140
     return np.array(padded, dtype=np.dtype(node.dtype), copy=True)
 
 
+def _h_scatter(node, vt, store):  # _realize.py:1179-1189, index rules _framework_contracts.py:5609-5630
+    axis = int(node.arg["dim"])
+    target, index, source = _in(node, vt, 0), _in(node, vt, 1), _in(node, vt, 2)
+    if index.size:
+        if bool(np.any(index < 0)) or bool(np.any(index >= target.shape[axis])):
+            raise ValueError(f"scatter: index values must be in [0, {target.shape[axis]})")
+        if index.shape[axis] > 1:
+            ordered = np.sort(index, axis=axis)
+            lo = [slice(None)] * index.ndim
+            hi = [slice(None)] * index.ndim
+            lo[axis], hi[axis] = slice(None, -1), slice(1, None)
+            if bool(np.any(ordered[tuple(lo)] == ordered[tuple(hi)])):
+                raise ValueError("scatter: duplicate destination indices are outside the deterministic overwrite profile")
+    output = np.array(target, dtype=np.dtype(node.dtype), copy=True)
+    np.put_along_axis(output, index, source, axis=axis)
+    return output
+
+
 def _h_repeat(node, vt, store):  # _realize.py:329-332
     return np.array(np.tile(_in(node, vt, 0), tuple(node.arg["repeats"])), dtype=np.dtype(node.dtype), copy=True)
 
@@ -405,7 +423,7 @@ _DISPATCH: Dict[str, Callable] = {
     "PERMUTE": lambda n, vt, s: np.transpose(_in(n, vt, 0), axes=n.arg["axes"]),   # :1119-1121
     "WHERE": _h_where,
     "CLAMP": _h_clamp, "FLIP": _h_flip, "CUMSUM": _h_cumsum, "CONCAT": _h_concat, "STACK": _h_stack,
-    "TRIL": _h_tril, "TRIU": _h_triu, "VAR": _h_var, "PROD": _h_prod, "PAD": _h_pad, "REPEAT": _h_repeat, "REPEAT_INTERLEAVE": _h_repeat_interleave,
+    "TRIL": _h_tril, "TRIU": _h_triu, "VAR": _h_var, "PROD": _h_prod, "PAD": _h_pad, "SCATTER": _h_scatter, "REPEAT": _h_repeat, "REPEAT_INTERLEAVE": _h_repeat_interleave,
     "SORT_INDICES": _h_sort_indices, "SORT_VALUES": _h_take_along, "TOPK_INDICES": _h_topk_indices, "TOPK_VALUES": _h_take_along,
     "INDEX": _h_index,
     "BROADCAST_TO": _h_broadcast_to,

@@ -91,6 +91,10 @@ def _misc_inputs() -> Dict[str, np.ndarray]:
         "m79": r.standard_normal((7, 9), dtype=np.float32),
         "logits": r.standard_normal((12, 7), dtype=np.float32) * np.float32(3),
         "tgt": np.array([0, 6, 3, -100, 2, 2, 5, -100, 1, 0, 4, 6], dtype=np.int64),
+        "perm_last": np.argsort(r.standard_normal((6, 5, 33)), axis=2).astype(np.int64),
+        "perm_mid_part": np.argsort(r.standard_normal((6, 5, 33)), axis=1).astype(np.int64)[:, :3, :],
+        "perm_first_i": np.argsort(r.standard_normal((6, 5, 33)), axis=0).astype(np.int64),
+        "src_part": r.standard_normal((6, 3, 33), dtype=np.float32),
         "logits3": r.standard_normal((4, 7, 5), dtype=np.float32),
         "tgt3": r.integers(0, 7, (4, 5), dtype=np.int64),
     }
@@ -304,6 +308,11 @@ CASES: Dict[str, Case] = {
     "pad_two_axes_value": Case(_misc_inputs, lambda api, t, raw: api.pad(t["x"], (1, 0, 0, 2), value=-1.5), kind="exact"),
     "pad_all_axes_int": Case(_misc_inputs, lambda api, t, raw: api.pad(t["i"], (0, 4, 3, 0, 1, 1), value=7), kind="exact"),
     "pad_f64_then_chain": Case(_misc_inputs, lambda api, t, raw: api.relu(api.pad(t["d"], (1, 1)) * 2.0)),
+    "scatter_last_perm": Case(_misc_inputs, lambda api, t, raw: t["x"].scatter(2, t["perm_last"], t["p"]), kind="exact"),
+    "scatter_mid_partial": Case(_misc_inputs, lambda api, t, raw: t["x"].scatter(1, t["perm_mid_part"], t["src_part"]), kind="exact"),
+    "scatter_scalar_source": Case(_misc_inputs, lambda api, t, raw: t["x"].scatter(-2, t["perm_mid_part"], -2.5), kind="exact"),
+    "scatter_int_first": Case(_misc_inputs, lambda api, t, raw: t["i"].scatter(0, t["perm_first_i"], t["big"]), kind="exact"),
+    "scatter_then_chain": Case(_misc_inputs, lambda api, t, raw: api.relu(t["x"].scatter(2, t["perm_last"], t["p"]) * t["row"])),
     "cumsum_last": Case(_misc_inputs, lambda api, t, raw: api.cumsum(t["x"], 2), kind="exact"),
     "cumsum_first_int": Case(_misc_inputs, lambda api, t, raw: api.cumsum(t["i32"], 0), kind="exact"),
     "cumsum_mid_f64": Case(_misc_inputs, lambda api, t, raw: api.cumsum(t["d"], 1), kind="exact"),
