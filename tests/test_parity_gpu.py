@@ -203,6 +203,29 @@ def test_head_merge_after_attention_is_written_by_the_attention_kernel(bridge, n
     check(case, got, oracle_value(t, store), "merged heads")
 
 
+@pytest.mark.parametrize("bad", ["range", "duplicate"])
+def test_scatter_refuses_what_the_reference_refuses(bridge, bad):
+    """An index outside the axis, or two index entries naming one destination, end the plan with an index error
+    (the reference raises RealizationError for both, _realize.py:1184-1186); the bridge stays usable."""
+    from browsergrad_b200 import graph
+    from browsergrad_b200.errors import KernelError
+    store = graph.BufferStore()
+    x = graph.from_numpy(np.zeros((4, 6), np.float32), store)
+    idx = np.tile(np.arange(6, dtype=np.int64), (4, 1))
+    if bad == "range":
+        idx[2, 3] = 6
+    else:
+        idx[1, 0] = idx[1, 5]
+    src = graph.from_numpy(np.ones((4, 6), np.float32), store)
+    with pytest.raises(KernelError, match="scatter") as info:
+        realize_cuda(x.scatter(1, graph.from_numpy(idx, store), src), bridge)
+    assert info.value.status == 7
+    good = np.tile(np.arange(6, dtype=np.int64)[::-1], (4, 1))
+    got = realize_cuda(x.scatter(1, graph.from_numpy(np.ascontiguousarray(good), store), src), bridge)
+    assert np.array_equal(got, np.ones((4, 6), np.float32))
+    assert bridge.aliveHandleCount() == 0
+
+
 def test_row_pipeline_equals_one_realization(bridge):
     """Row chunks streamed over three bridges of the device give the rows of one whole realization."""
     from browsergrad_b200 import CudaBridge, configs, graph
