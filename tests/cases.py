@@ -392,6 +392,13 @@ CASES: Dict[str, Case] = {
     "scalar_only": Case(_misc_inputs, lambda api, t, raw: t["row"].sum() * 2.0 + 1.0),
     "empty_rows": Case(lambda: {"a": np.zeros((0, 8), np.float32), "b": np.ones((0, 8), np.float32)},
                        lambda api, t, raw: api.relu(t["a"] * t["b"])),
+    "prod_empty_axis": Case(lambda: {"a": np.zeros((0, 8), np.float32)}, lambda api, t, raw: t["a"].prod(0) + 1.0),
+    "prod_empty_rows": Case(lambda: {"a": np.zeros((0, 8), np.float32)}, lambda api, t, raw: t["a"].prod(1), kind="exact"),
+    "pad_empty_rows": Case(lambda: {"a": np.zeros((0, 8), np.float32)}, lambda api, t, raw: api.pad(t["a"], (1, 2, 2, 1), value=3.0),
+                           kind="exact"),
+    "scatter_empty_index": Case(lambda: {"a": np.arange(12, dtype=np.float32).reshape(3, 4), "i": np.zeros((0, 4), np.int64),
+                                         "s": np.zeros((0, 4), np.float32)},
+                                lambda api, t, raw: t["a"].scatter(0, t["i"], t["s"]), kind="exact"),
     "single_element": Case(lambda: {"a": np.array([[2.5]], np.float32)},
                            lambda api, t, raw: api.softmax(t["a"] * t["a"], dim=-1)),
 }
