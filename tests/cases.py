@@ -128,6 +128,13 @@ def _qkv(api: Any, t: Dict[str, Any], names: str, amp: str = "") -> Any:
     return build()
 
 
+def _mlp2_inputs() -> Dict[str, np.ndarray]:
+    r = _rng(78)
+    return {"x": r.standard_normal((264, 272), dtype=np.float32),
+            "w1": r.standard_normal((300, 272), dtype=np.float32) / np.float32(16), "b1": r.standard_normal((300,), dtype=np.float32) * np.float32(0.1),
+            "w2": r.standard_normal((272, 300), dtype=np.float32) / np.float32(17), "b2": r.standard_normal((272,), dtype=np.float32) * np.float32(0.1)}
+
+
 def _ln_inputs(rows: int, cols: int) -> Callable[[], Dict[str, np.ndarray]]:
     def make() -> Dict[str, np.ndarray]:
         r = _rng(300 + cols)
@@ -238,6 +245,10 @@ CASES: Dict[str, Case] = {
     "c3_group_qkv_f16": Case(_qkv_inputs(300, 272, 264), lambda api, t, raw: _qkv(api, t, "qkv", "float16"), rtol=2e-2),
     "c3_group_four_bf16": Case(_qkv_inputs(520, 160, 264), lambda api, t, raw: _qkv(api, t, "qkvq", "bfloat16"), rtol=2e-2,
                                reference_has_it=False),
+    "c3_chain_relu_f32": Case(_mlp2_inputs, lambda api, t, raw: api.linear(api.relu(api.linear(t["x"], t["w1"], t["b1"])), t["w2"], t["b2"])),
+    "c3_chain_gelu_f64": Case(_mlp2_inputs, lambda api, t, raw: api.linear(api.gelu(api.linear(t["x"], t["w1"], t["b1"])), t["w2"], t["b2"])),
+    "c3_chain_kept_hidden": Case(_mlp2_inputs, lambda api, t, raw: (lambda h: api.cat([api.linear(h, t["w2"], t["b2"]), h], 1))(
+        api.gelu(api.linear(t["x"], t["w1"], t["b1"])))),
     "c4_attn_mask": Case(_attn_small(2, 3, 64, 16),
                          lambda api, t, raw: configs.attention(api, t, "mask")),
     "c4_attn_causal": Case(_attn_small(2, 3, 64, 16),

@@ -169,6 +169,23 @@ def test_projections_of_one_activation_launch_together(bridge, name, unit, membe
     assert got.tobytes() == apart.tobytes()
 
 
+@pytest.mark.parametrize("name", ["c3_chain_relu_f32", "c3_chain_gelu_f64", "c3_chain_kept_hidden"])
+def test_gemm_feeding_a_gemm(bridge, name):
+    """Two chained Linear layers on tensor cores (the hidden activation is the A operand of the second GEMM, in fp32
+    after relu and in fp64 after gelu), fused and unfused."""
+    case = CASES[name]
+    t, store, _ = build_case(case)
+    got = realize_cuda(t, bridge)
+    assert sum(ln.startswith("gemm_tc_3xtf32") for ln in bridge.last_plan_trace()) == 2, bridge.last_plan_trace()
+    check(case, got, oracle_value(t, store), name)
+    bridge.set_option("fusion", 0)
+    try:
+        plain = realize_cuda(t, bridge)
+    finally:
+        bridge.set_option("fusion", 1)
+    check(case, plain, oracle_value(t, store), name + " (unfused)")
+
+
 def test_autocast_attention_is_one_unit_and_keeps_mask_classes_with_the_handle(bridge):
     """The fp32 -> 16-bit casts of Q, K, V are folded into the operand staging of the fused kernel, and the
     mask tile classes computed for a mask bound by handle live exactly as long as that handle."""
