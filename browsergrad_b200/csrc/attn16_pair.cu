@@ -1,0 +1,471 @@
+// Fused softmax attention forward for f16 / bf16 operands, head dimension 64, two query tiles per CTA (sm_100a).
+//
+// One CTA owns 256 query rows of one (batch, head) as two tiles of 128 ("A" and "B") that share every K and V tile
+// brought into shared memory and take turns on the tensor core: while the softmax threads of one tile work on their
+// scores, the products of the other tile run.
+//   warp 0      producer: lane 0 fetches K tiles, lane 1 V tiles (TMA, rings of their own)
+//   warp 1      MMA issuer (one thread): S = Q K^T into tensor memory, O += P V
+//   warps 4-7   softmax of tile A: one thread per query row, the row's 128 scores in registers
+//   warps 8-11  softmax of tile B
+// (warps 2 and 3 only fill the first warpgroup, which hands most of its registers to the softmax warpgroups with
+// setmaxnreg: a softmax thread holds a whole row of scores.)
+// A softmax thread reads its row of S once (tcgen05.ld), frees S for the next Q K^T at once, takes the row maximum,
+// the exponentials against a lazily raised reference maximum (O in tensor memory is rescaled only when the running
+// maximum exceeds the reference by more than 2^8) and the row sum without any exchange with other threads, and
+// publishes P either in shared memory (operand layout, 128-byte swizzle) or in tensor memory (the A operand of the
+// P V product is then read from there).  Query rows are read by the softmax threads themselves from the tensor the
+// graph names (fp32 rows are rounded to the operand type as the graph's CAST would), so Q needs no staging pass.
+// V is consumed either as V^T tiles (K-major) or directly as rows of V (MN-major operand), chosen at launch.
+// CTAs are numbered heaviest first (late query tiles see the most keys under a causal mask).
+// No cluster multicast; every wait is clock-bounded; tensor-memory loads and stores are issued by whole warps.
+#include "common.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math_constants.h>
+
+#include "attn_common.cuh"
+#include "tc_common.cuh"
+
+namespace bg {
+namespace {
+
+using namespace tc;
+using namespace attn;
+
+struct PairCfg {
+  static constexpr int BKV = 128;
+  static constexpr int NK = 2, NV = 2;
+  static constexpr int QBytes = kQRows * 128;          // one query tile: 128 rows of 64 16-bit values
+  static constexpr int KBytes = BKV * 128;
+  static constexpr int VBytes = BKV * 128;
+  static constexpr int PBytes = 2 * kQRows * 128;      // two k-blocks of 64 keys
+  static constexpr int TmemCols = 512;
+  static constexpr int ColS = 0;                       // S of tile A, S of tile B: 2 x 128 columns
+  static constexpr int ColO = 256;                     // O of tile A, of tile B: 2 x 64
+  static constexpr int ColP = 384;                     // P of tile A, of tile B (16-bit pairs): 2 x 64
+  static constexpr int smem_bytes(bool p_in_tmem) { return 2 * QBytes + NK * KBytes + NV * VBytes + (p_in_tmem ? 0 : 2 * PBytes); }
+};
+constexpr float kLazyRescaleLog2 = 8.0f;
+constexpr int kPairThreads = 384;        // three warpgroups: producer + MMA, softmax A, softmax B
+// The register pool of a CTA is what it was launched with (168 per thread for 384 threads); the first warpgroup
+// shrinks to kRegsLight so that the softmax warpgroups can grow to kRegsSoftmax.  A request beyond the pool would wait
+// for ever, hence the assertion.
+constexpr int kRegsLaunch = 168, kRegsLight = 72, kRegsSoftmax = 216;
+static_assert(128 * kRegsLight + 256 * kRegsSoftmax <= kRegsLaunch * kPairThreads, "setmaxnreg requests exceed the CTA's register pool");
+static_assert(kRegsLight % 8 == 0 && kRegsSoftmax % 8 == 0, "setmaxnreg takes multiples of 8");
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack16(float a0, float a1) {
+  if (BF16) { __nv_bfloat162 v = __floats2bfloat162_rn(a0, a1); return *reinterpret_cast<uint32_t*>(&v); }
+  __half2 v = __floats2half2_rn(a0, a1);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// VMN: V tiles are rows of V (MN-major B operand), else V^T tiles (K-major).  PT: P lives in tensor memory.
+template <bool BF16, bool VMN, bool PT>
+__global__ void __launch_bounds__(kPairThreads, 1)
+attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const __grid_constant__ AttnParams p) {
+  using C = PairCfg;
+  constexpr int BKV = C::BKV;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* sQ = smem;                                   // [2][QBytes]
+  unsigned char* sK = sQ + 2 * C::QBytes;                     // [NK][KBytes]
+  unsigned char* sV = sK + C::NK * C::KBytes;                 // [NV][VBytes]
+  unsigned char* sP = sV + C::NV * C::VBytes;                 // [2][PBytes] unless PT
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + (PT ? 0 : 2 * C::PBytes));
+  uint64_t* q_full = bars;                // [2] query rows of a tile are in shared memory (4 arrivals)
+  uint64_t* k_full = q_full + 2;          // [NK]
+  uint64_t* k_empty = k_full + C::NK;     // [NK]
+  uint64_t* v_full = k_empty + C::NK;     // [NV]
+  uint64_t* v_empty = v_full + C::NV;     // [NV]
+  uint64_t* s_full = v_empty + C::NV;     // [2] Q K^T of the tile's current key tile has completed
+  uint64_t* s_empty = s_full + 2;         // [2] its softmax warps hold the scores in registers (4 arrivals)
+  uint64_t* p_full = s_empty + 2;         // [2] P is published (4 arrivals)
+  uint64_t* pv_full = p_full + 2;         // [2] P V has completed
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_full + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_bh = p.B * p.H;
+  const int n_qt = (p.Sq + kQRows - 1) / kQRows;
+  const int n_pairs = (n_qt + 1) / 2;
+  const int pair = n_pairs - 1 - (int)(blockIdx.x / (unsigned)n_bh);
+  const int bh = (int)(blockIdx.x % (unsigned)n_bh);
+  const int b = bh / p.H, h = bh % p.H;
+  const int n_kv = (p.Sk + BKV - 1) / BKV;
+  // tile classes of the two query tiles (null: every key tile is processed); tile B may not exist
+  const bool has_b = 2 * pair + 1 < n_qt;
+  const unsigned char* cls_a = p.tile_class ? p.tile_class + (size_t)(2 * pair) * n_kv : nullptr;
+  const unsigned char* cls_b = p.tile_class && has_b ? p.tile_class + (size_t)(2 * pair + 1) * n_kv : nullptr;
+  auto need_a = [&](int j) { return !(cls_a && cls_a[j] == 0); };
+  auto need_b = [&](int j) { return has_b && !(cls_b && cls_b[j] == 0); };
+  auto next_union = [&](int j) { while (j < n_kv && !need_a(j) && !need_b(j)) ++j; return j; };
+
+  if (threadIdx.x == 0) {
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(&q_full[g], 4);
+      mbar_init(&s_full[g], 1); mbar_init(&s_empty[g], 4);
+      mbar_init(&p_full[g], 4); mbar_init(&pv_full[g], 1);
+    }
+    for (int s = 0; s < C::NK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    for (int s = 0; s < C::NV; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(C::TmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLight));
+    if (warp == 0) {
+      if (lane == 0) {
+        int u = 0;
+        for (int j = next_union(0); j < n_kv; j = next_union(j + 1), ++u) {
+          const int s = u % C::NK;
+          if (!mbar_wait(&k_empty[s], ((uint32_t)(u / C::NK) & 1u) ^ 1u, abort_flag)) break;
+          mbar_expect_tx(&k_full[s], C::KBytes);
+          tma_load_4d(&tmK, sK + s * C::KBytes, &k_full[s], 0, j * BKV, h, b);
+        }
+      } else if (lane == 1) {
+        int u = 0;
+        for (int j = next_union(0); j < n_kv; j = next_union(j + 1), ++u) {
+          const int s = u % C::NV;
+          if (!mbar_wait(&v_empty[s], ((uint32_t)(u / C::NV) & 1u) ^ 1u, abort_flag)) break;
+          mbar_expect_tx(&v_full[s], C::VBytes);
+          unsigned char* st = sV + s * C::VBytes;
+          if (VMN) {
+            tma_load_4d(&tmV, st, &v_full[s], 0, j * BKV, h, b);
+          } else {
+            tma_load_4d(&tmV, st, &v_full[s], j * BKV, 0, h, b);
+            tma_load_4d(&tmV, st + kHeadDim * 128, &v_full[s], j * BKV + 64, 0, h, b);
+          }
+        }
+      }
+    } else if (warp == 1) {
+      if (lane == 0) {
+        bool ok = true;
+        int n_qk[2] = {0, 0}, n_pv[2] = {0, 0};
+        auto issue_qk = [&](int g, int slot) -> bool {
+          const int n = n_qk[g]++;
+          if (n == 0 && !mbar_wait(&q_full[g], 0, abort_flag)) return false;
+          if (n > 0 && !mbar_wait(&s_empty[g], (uint32_t)(n - 1) & 1u, abort_flag)) return false;
+          tc_fence_after();
+          const uint64_t da = make_kmajor_sw128_desc(smem_u32(sQ + g * C::QBytes));
+          const uint64_t db = make_kmajor_sw128_desc(smem_u32(sK + slot * C::KBytes));
+          const uint32_t d_s = tmem_base + (uint32_t)(C::ColS + g * BKV);
+  #pragma unroll
+          for (int k = 0; k < 4; ++k) umma<false>(d_s, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_qk, k ? 1u : 0u);
+          umma_commit(&s_full[g]);
+          return true;
+        };
+        auto issue_pv = [&](int g, int slot) -> bool {
+          const int n = n_pv[g]++;
+          if (!mbar_wait(&p_full[g], (uint32_t)n & 1u, abort_flag)) return false;
+          tc_fence_after();
+          const uint32_t v_addr = smem_u32(sV + slot * C::VBytes);
+          const uint32_t d_o = tmem_base + (uint32_t)(C::ColO + g * kHeadDim);
+  #pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint64_t db = VMN ? make_mnmajor_sw128_desc(v_addr + (uint32_t)(k * 2048))
+                                    : make_kmajor_sw128_desc(v_addr + (uint32_t)((k >> 2) * (kHeadDim * 128))) + (uint64_t)((k & 3) * 2);
+            const uint32_t acc = (n > 0 || k > 0) ? 1u : 0u;
+            if (PT) {
+              umma_ts_f16(d_o, tmem_base + (uint32_t)(C::ColP + g * 64 + k * 8), db, p.idesc_pv, acc);
+            } else {
+              const uint64_t da = make_kmajor_sw128_desc(smem_u32(sP + g * C::PBytes + (k >> 2) * (kQRows * 128))) + (uint64_t)((k & 3) * 2);
+              umma<false>(d_o, da, db, p.idesc_pv, acc);
+            }
+          }
+          umma_commit(&pv_full[g]);
+          return true;
+        };
+        // key tiles in order; tile u+1's Q K^T is issued ahead of tile u's P V for each query tile
+        int jc = next_union(0), u = 0;
+        if (jc < n_kv) {
+          ok = mbar_wait(&k_full[0], 0, abort_flag);
+          if (ok && need_a(jc)) ok = issue_qk(0, 0);
+          if (ok && need_b(jc)) ok = issue_qk(1, 0);
+          if (ok) umma_commit(&k_empty[0]);
+        }
+        while (jc < n_kv && ok) {
+          const int jn = next_union(jc + 1), un = u + 1;
+          const bool more = jn < n_kv;
+          const int ks = un % C::NK, vs = u % C::NV;
+          if (more) ok = mbar_wait(&k_full[ks], (uint32_t)(un / C::NK) & 1u, abort_flag);
+          if (ok && more && need_a(jn)) ok = issue_qk(0, ks);
+          if (ok) ok = mbar_wait(&v_full[vs], (uint32_t)(u / C::NV) & 1u, abort_flag);
+          if (ok && need_a(jc)) ok = issue_pv(0, vs);
+          if (ok && more && need_b(jn)) ok = issue_qk(1, ks);
+          if (ok && more) umma_commit(&k_empty[ks]);
+          if (ok && need_b(jc)) ok = issue_pv(1, vs);
+          if (ok) umma_commit(&v_empty[vs]);
+          jc = jn;
+          u = un;
+        }
+      }
+    }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
+    const int g = (warp - 4) >> 2;                  // query tile of this warp
+    const int quarter = warp & 3;                   // tensor-memory lane quarter this warp may access
+    const int r_in_tile = quarter * 32 + lane;
+    const int q_tile = 2 * pair + g;
+    const bool active = g == 0 || has_b;
+    const int row = q_tile * kQRows + r_in_tile;
+    const bool row_ok = active && row < p.Sq;
+    const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+    const int sw = r_in_tile & 7;
+    constexpr float kLog2e = 1.4426950408889634f;
+    const unsigned char* cls = g == 0 ? cls_a : cls_b;
+
+    if (active) {
+      // ---- this thread's query row -> shared memory in the operand layout ---------------------------------------
+      unsigned char* qrow = sQ + g * C::QBytes + r_in_tile * 128;
+      const long long qoff = (long long)b * p.q_sb + (long long)h * p.q_sh + (long long)(row_ok ? row : 0) * p.q_ss;
+      if (p.q_f32) {
+        const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q_ptr) + qoff);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+          if (row_ok) { lo = __ldg(src + 2 * c); hi = __ldg(src + 2 * c + 1); }
+          *reinterpret_cast<uint4*>(qrow + ((c ^ sw) << 4)) =
+              make_uint4(pack16<BF16>(lo.x, lo.y), pack16<BF16>(lo.z, lo.w), pack16<BF16>(hi.x, hi.y), pack16<BF16>(hi.z, hi.w));
+        }
+      } else {
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q_ptr) + qoff);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint4 v = make_uint4(0u, 0u, 0u, 0u);
+          if (row_ok) v = __ldg(src + c);
+          *reinterpret_cast<uint4*>(qrow + ((c ^ sw) << 4)) = v;
+        }
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&q_full[g]);
+
+      float m_ref = -CUDART_INF_F, l = 0.f;
+      float scale = p.scale;
+      const bool per_elem_scale = p.scale_buf != nullptr && !(p.scale_uniform && *p.scale_uniform);
+      if (p.scale_buf && !per_elem_scale) scale = p.scale_buf[0];
+      const size_t score_row = ((size_t)(b * p.H + h) * p.Sq + (row_ok ? row : 0)) * (size_t)p.Sk;
+      const size_t mask_row = (size_t)b * p.mask_sb + (size_t)h * p.mask_sh + (size_t)(row_ok ? row : 0) * p.Sk;
+      const uint32_t t_s = tmem_base + (uint32_t)(C::ColS + g * BKV) + lane_sel;
+      const uint32_t t_o = tmem_base + (uint32_t)(C::ColO + g * kHeadDim) + lane_sel;
+      const uint32_t t_p = tmem_base + (uint32_t)(C::ColP + g * 64) + lane_sel;
+      bool ok = true;
+      int t = 0;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int tclass = cls ? cls[j] : (p.mask ? 3 : 1);
+        if (tclass == 0) continue;
+        ok = __all_sync(0xffffffffu, mbar_wait(&s_full[g], (uint32_t)t & 1u, abort_flag));
+        if (!ok) break;
+        tc_fence_after();
+        float x[BKV];
+        {
+          uint32_t* xu = reinterpret_cast<uint32_t*>(x);
+          tmem_ld32_issue(t_s, xu);
+          tmem_ld32_issue(t_s + 32, xu + 32);
+          tmem_ld32_issue(t_s + 64, xu + 64);
+          tmem_ld32_issue(t_s + 96, xu + 96);
+          tmem_ld_wait();
+        }
+        // the scores are in registers: the next Q K^T of this query tile may overwrite S
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_empty[g]);
+
+        const int k0 = j * BKV;
+        const bool simple_scale = !per_elem_scale && scale > 0.f;
+        // a binary mask is applied from its bit words only on the folded-scale path; otherwise element by element
+        const bool need_mask = p.mask && (tclass == 3 || (tclass == 2 && !simple_scale));
+        const bool fast = !need_mask && simple_scale && (tclass == 2 || k0 + BKV <= p.Sk);
+        if (fast) {
+          if (tclass == 2) {
+            // binary mask: four words of "masked" bits cover this row's 128 keys
+            const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(p.mask_bits + (size_t)(row_ok ? row : 0) * p.mask_words + (k0 >> 5)));
+            const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+            for (int i = 0; i < BKV; ++i)
+              if ((w[i >> 5] >> (i & 31)) & 1u) x[i] = -CUDART_INF_F;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < BKV; ++i) {
+            const int key = k0 + i;
+            const bool in_range = key < p.Sk;
+            float v = __fmul_rn(x[i], per_elem_scale ? (in_range ? p.scale_buf[score_row + key] : 0.f) : scale);
+            if (need_mask && in_range) {
+              if (p.mask_is_bool) { if (reinterpret_cast<const unsigned char*>(p.mask)[mask_row + key]) v = -CUDART_INF_F; }
+              else v = __fadd_rn(v, reinterpret_cast<const float*>(p.mask)[mask_row + key]);
+            }
+            x[i] = in_range ? v : -CUDART_INF_F;
+          }
+        }
+        // row maximum of the tile, in natural units
+        float mt;
+        {
+          float mx[4] = {x[0], x[1], x[2], x[3]};
+#pragma unroll
+          for (int i = 4; i < BKV; i += 2) mx[(i >> 1) & 3] = fmax3(mx[(i >> 1) & 3], x[i], x[i + 1]);
+          mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+          if (fast) mt *= scale;
+        }
+        // Lazy rescaling.  O must be quiescent (the previous P V complete) before it is touched; tcgen05.ld / st are
+        // warp-wide, so when any row of this warp has to rescale all 32 lanes do, the others by a factor of one.
+        bool pv_done = t == 0;
+        const bool raise = m_ref != -CUDART_INF_F && (mt - m_ref) * kLog2e > kLazyRescaleLog2;
+        if (__any_sync(0xffffffffu, raise)) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&pv_full[g], (uint32_t)(t - 1) & 1u, abort_flag));
+          if (!ok) break;
+          pv_done = true;
+          tc_fence_after();
+          const float alpha = raise ? ex2_approx((m_ref - mt) * kLog2e) : 1.0f;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t r[32];
+            tmem_ld32(t_o + (uint32_t)(half * 32), r);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st32(t_o + (uint32_t)(half * 32), r);
+          }
+          tc_fence_before();
+          if (raise) { l *= alpha; m_ref = mt; }
+        }
+        if (m_ref == -CUDART_INF_F) m_ref = mt;        // nothing (or only zeros) accumulated so far
+        const float m_use = m_ref == -CUDART_INF_F ? 0.f : m_ref;
+        const float cc = fast ? scale * kLog2e : kLog2e, ml = m_use * kLog2e;
+        {
+          float ps[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int i = 0; i < BKV; ++i) {
+            x[i] = ex2_approx(fmaf(x[i], cc, -ml));
+            ps[i & 3] += x[i];
+          }
+          l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+        }
+        // P of the previous key tile has been consumed once its P V has completed
+        if (!pv_done) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&pv_full[g], (uint32_t)(t - 1) & 1u, abort_flag));
+          if (!ok) break;
+          tc_fence_after();
+        }
+        if (PT) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t w[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) w[i] = pack16<BF16>(x[half * 64 + 2 * i], x[half * 64 + 2 * i + 1]);
+            tmem_st32_issue(t_p + (uint32_t)(half * 32), w);
+          }
+          tmem_st_wait();
+        } else {
+          unsigned char* prow = sP + g * C::PBytes + r_in_tile * 128;
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) w[e] = pack16<BF16>(x[q * 8 + 2 * e], x[q * 8 + 2 * e + 1]);
+            *reinterpret_cast<uint4*>(prow + (q >> 3) * (kQRows * 128) + (((q & 7) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          fence_async_smem();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[g]);
+        ++t;
+      }
+      if (ok && t > 0) ok = __all_sync(0xffffffffu, mbar_wait(&pv_full[g], (uint32_t)(t - 1) & 1u, abort_flag));
+      if (ok) {
+        tc_fence_after();
+        const float inv = 1.0f / l;   // l = 0 for a fully masked row: 0 * inf = NaN, as the reference's softmax gives
+        const size_t base = (size_t)((long long)b * p.out_sb + (long long)h * p.out_sh + (long long)(row_ok ? row : 0) * p.out_ss);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld32(t_o + (uint32_t)(half * 32), r);     // warp-wide; only the stores are per row
+          float o[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = (t > 0 ? __uint_as_float(r[i]) : 0.f) * inv;
+          if (!row_ok) continue;
+          if (p.out_dtype == BG_F32) {
+            float* out = reinterpret_cast<float*>(p.out) + base + half * 32;
+#pragma unroll
+            for (int d = 0; d < 32; d += 4) *reinterpret_cast<float4*>(out + d) = make_float4(o[d], o[d + 1], o[d + 2], o[d + 3]);
+          } else if (p.out_dtype == BG_F64) {
+            double* out = reinterpret_cast<double*>(p.out) + base + half * 32;
+#pragma unroll
+            for (int d = 0; d < 32; d += 2) *reinterpret_cast<double2*>(out + d) = make_double2((double)o[d], (double)o[d + 1]);
+          } else {
+            uint32_t* out = reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(p.out) + base + half * 32);
+#pragma unroll
+            for (int d = 0; d < 32; d += 8) {
+              uint4 v;
+              if (p.out_dtype == BG_BF16) v = make_uint4(pack16<true>(o[d], o[d + 1]), pack16<true>(o[d + 2], o[d + 3]), pack16<true>(o[d + 4], o[d + 5]), pack16<true>(o[d + 6], o[d + 7]));
+              else v = make_uint4(pack16<false>(o[d], o[d + 1]), pack16<false>(o[d + 2], o[d + 3]), pack16<false>(o[d + 4], o[d + 5]), pack16<false>(o[d + 6], o[d + 7]));
+              *reinterpret_cast<uint4*>(out + d / 2) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(p.status, BG_ERR_DEVICE_TIMEOUT);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) {}
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TmemCols) : "memory");
+  }
+}
+
+template <bool BF16>
+cudaError_t launch_variant(bool vmn, bool pt, dim3 grid, size_t smem, cudaStream_t s, const CUtensorMap& k, const CUtensorMap& v, const AttnParams& p) {
+  void (*kern)(const CUtensorMap, const CUtensorMap, const AttnParams) =
+      vmn ? (pt ? attn16_pair_kernel<BF16, true, true> : attn16_pair_kernel<BF16, true, false>)
+          : (pt ? attn16_pair_kernel<BF16, false, true> : attn16_pair_kernel<BF16, false, false>);
+  // the register hand-over in the kernel assumes the pool of a launch at kRegsLaunch registers per thread
+  cudaFuncAttributes fa;
+  cudaError_t e = cudaFuncGetAttributes(&fa, kern);
+  if (e != cudaSuccess) return e;
+  if (fa.numRegs < kRegsLaunch) return cudaErrorLaunchOutOfResources;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  kern<<<grid, kPairThreads, smem, s>>>(k, v, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool attn16_pair_out_ok(int out_dtype, const void* out, long long out_sb, long long out_sh, long long out_ss) {
+  // output rows are written in 16-byte pieces
+  const int es = dtype_size(out_dtype);
+  const long long per16 = 16 / es;
+  return (reinterpret_cast<uintptr_t>(out) & 15) == 0 && out_sb % per16 == 0 && out_sh % per16 == 0 && out_ss % per16 == 0;
+}
+
+cudaError_t launch_attn16_pair(const attn::AttnParams& p, bool bf16, bool v_mn, bool p_in_tmem, const CUtensorMap& tm_k,
+                               const CUtensorMap& tm_v, cudaStream_t s) {
+  const int n_qt = (p.Sq + kQRows - 1) / kQRows;
+  const long long n_cta = (long long)((n_qt + 1) / 2) * p.B * p.H;
+  if (n_cta <= 0 || n_cta > 0x7fffffffll) return cudaErrorInvalidValue;
+  const size_t smem = (size_t)PairCfg::smem_bytes(p_in_tmem) + 256 + 1024;
+  dim3 grid((unsigned)n_cta);
+  return bf16 ? launch_variant<true>(v_mn, p_in_tmem, grid, smem, s, tm_k, tm_v, p)
+              : launch_variant<false>(v_mn, p_in_tmem, grid, smem, s, tm_k, tm_v, p);
+}
+
+}  // namespace bg

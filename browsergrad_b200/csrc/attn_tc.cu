@@ -26,56 +26,14 @@
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
+#include "attn_common.cuh"
 #include "tc_common.cuh"
 
 namespace bg {
 namespace {
 
 using namespace tc;
-
-constexpr int kHeadDim = 64;
-constexpr int kQRows = 128;
-constexpr int kAttnThreads = 320;   // producer warp, MMA warp, 2 x 4 softmax warps
-
-__device__ __forceinline__ void tma_load_4d(const CUtensorMap* map, void* smem_dst, uint64_t* bar, int x, int y, int z, int w) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      :
-      : "r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
-      : "memory");
-}
-
-// max of three in one instruction (sm_100 has the three-input form)
-__device__ __forceinline__ float fmax3(float a, float b, float c) {
-  float r;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-  return r;
-}
-
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-struct AttnParams {
-  int B, H, Sq, Sk;
-  float scale;                 // used when scale_buf is null or *scale_uniform != 0
-  const float* scale_buf;      // [B,H,Sq,Sk] or null
-  const int* scale_uniform;    // device flag: scale_buf holds one repeated value (then scale_buf[0] is used)
-  const void* mask;            // additive fp32 or bool (1 = fill -inf), or null
-  int mask_is_bool;
-  long long mask_sb, mask_sh;  // element strides over batch / head (0 when broadcast); rows are Sk apart
-  const unsigned char* tile_class;   // [ceil(Sq/128), ceil(Sk/BKV)]: 0 skip, 1 plain, 2 binary mixed, 3 biased; null = none computed
-  const uint32_t* mask_bits;         // [Sq, mask_words] "masked" bits, valid where tile_class is
-  int mask_words;
-  void* out;                   // rows of 64 at b * out_sb + h * out_sh + row * out_ss elements
-  long long out_sb, out_sh, out_ss;
-  int out_dtype;
-  int round_scores;            // dtype + 1: round S through f16 / bf16 before the softmax (autocast graphs)
-  uint32_t idesc_qk, idesc_pv;
-  int* status;
-};
+using namespace attn;
 
 struct AttnCfg {
   static constexpr int BKV = 64;                              // keys per tile
@@ -325,8 +283,10 @@ attn_tf32_fwd_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_cons
       constexpr float kLog2e = 1.4426950408889634f;
       // (autocast graphs round S to the 16-bit dtype between the two products; the fused kernel keeps
       //  the scores in fp32, which stays inside the 2e-2 autocast tolerance)
-      const bool need_mask = p.mask && tclass == 3;
-      const bool fast = !need_mask && !per_elem_scale && scale > 0.f && (tclass == 2 || j * BKV + BKV <= p.Sk);
+      const bool simple_scale = !per_elem_scale && scale > 0.f;
+        // a binary mask is applied from its bit words only on the folded-scale path; otherwise element by element
+        const bool need_mask = p.mask && (tclass == 3 || (tclass == 2 && !simple_scale));
+      const bool fast = !need_mask && simple_scale && (tclass == 2 || j * BKV + BKV <= p.Sk);
       float mt = -CUDART_INF_F;
       if (fast && tclass == 2) {
         // binary mask: one word of "masked" bits covers 32 keys of this row
@@ -632,8 +592,10 @@ attn16_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       ok = __all_sync(0xffffffffu, ok);      // tensor-memory loads below are warp-wide: keep the warp together
       tc_fence_after();
       const int k0 = j * BKV + wg * 64;             // first key of this thread's half
-      const bool need_mask = p.mask && tclass == 3;
-      const bool fast = !need_mask && !per_elem_scale && scale > 0.f && (tclass == 2 || j * BKV + BKV <= p.Sk);
+      const bool simple_scale = !per_elem_scale && scale > 0.f;
+        // a binary mask is applied from its bit words only on the folded-scale path; otherwise element by element
+        const bool need_mask = p.mask && (tclass == 3 || (tclass == 2 && !simple_scale));
+      const bool fast = !need_mask && simple_scale && (tclass == 2 || j * BKV + BKV <= p.Sk);
       const uint32_t* wrow = (fast && tclass == 2) ? p.mask_bits + (size_t)(row < p.Sq ? row : 0) * p.mask_words + (k0 >> 5) : nullptr;
       // 32 scores (chunk c of this thread's 64), ready for the exponential: raw S with masked keys at -inf on the
       // fast path (scale folded into the exponent later), else scale * S (+ mask) element by element
@@ -1025,23 +987,40 @@ void attn_scratch_sizes(const AttnProblem& a, int64_t bytes[8]) {
   bytes[7] = a.scale_buf ? 4 : 0;           // uniform-scale flag
 }
 
+// 16-bit kernel choice: bit 0 the two-tile (pair) kernel, bit 1 V as an MN-major operand (no transposing pass),
+// bit 2 P in tensor memory.  0 selects the single-tile kernel.
+int g_attn16_variant = kAttn16DefaultVariant;
+
 cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bool check_uniform, bool classify_mask, int* status,
                                 cudaStream_t s) {
   const bool tf32 = a.mode == 1;
   const int bkv = tf32 ? 64 : Attn16::BKV;
   const int sdt = tf32 ? BG_F32 : a.ab_dtype;
-  // operand staging: dense Q, K, V^T in the kernel's encoding
+  const bool pair = !tf32 && (g_attn16_variant & 1) && attn16_pair_out_ok(a.out_dtype, a.out, a.out_sb, a.out_sh, a.out_ss);
+  const bool v_mn = pair && (g_attn16_variant & 2);
+  const bool p_tmem = pair && (g_attn16_variant & 4);
+  // operand staging: dense Q, K, V^T (or V) in the kernel's encoding
   const int kind = tf32 ? PREP_TF32 : (a.ab_dtype == BG_F16 ? PREP_F16 : PREP_BF16);
   const AttnOperand* ops[3] = {&a.q, &a.k, &a.v};
   const int seq[3] = {a.Sq, a.Sk, a.Sk};
   const void* staged[3] = {scratch[0], scratch[2], scratch[4]};
+  bool q_in_kernel = false;
   for (int i = 0; i < 3; ++i) {
     const long long n = (long long)a.B * a.H * seq[i] * a.D;
     const bool dense = ops[i]->stride[3] == 1 && ops[i]->stride[2] == a.D && ops[i]->stride[1] == (long long)seq[i] * a.D &&
                        ops[i]->stride[0] == (long long)a.H * seq[i] * a.D;
     const bool aligned = (reinterpret_cast<uintptr_t>(ops[i]->ptr) & 15) == 0;
-    // 16-bit Q / K that are already dense [B,H,S,D] feed the TMA maps directly
-    if (!tf32 && i < 2 && dense && ops[i]->dtype == a.ab_dtype && aligned) {
+    const bool as_rows = i < 2 || v_mn;        // consumed as [S, 64] rows (not transposed)
+    // the pair kernel reads query rows itself: fp32 or operand-type rows of 64 contiguous values, 16-byte aligned
+    if (pair && i == 0 && ops[i]->stride[3] == 1 && aligned && (ops[i]->dtype == BG_F32 || ops[i]->dtype == a.ab_dtype)) {
+      const long long per16 = ops[i]->dtype == BG_F32 ? 4 : 8;
+      if (ops[i]->stride[0] % per16 == 0 && ops[i]->stride[1] % per16 == 0 && ops[i]->stride[2] % per16 == 0) {
+        q_in_kernel = true;
+        continue;
+      }
+    }
+    // 16-bit operands that are already dense [B,H,S,D] feed the TMA maps directly
+    if (!tf32 && as_rows && dense && ops[i]->dtype == a.ab_dtype && aligned) {
       staged[i] = ops[i]->ptr;
       continue;
     }
@@ -1050,20 +1029,20 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
     const bool rows_vec = rows_contig && (ops[i]->dtype == BG_F32 || (ops[i]->dtype == BG_F64 && tf32)) &&
                           (reinterpret_cast<uintptr_t>(ops[i]->ptr) & 31) == 0 && (ops[i]->stride[0] & 3) == 0 &&
                           (ops[i]->stride[1] & 3) == 0 && (ops[i]->stride[2] & 3) == 0;
-    if (i == 2 && rows_contig) {
+    if (!as_rows && rows_contig) {
       attn_prep_vt_kernel<<<dim3((unsigned)((seq[i] + 63) / 64), (unsigned)(a.B * a.H)), 256, 0, s>>>(
           ops[i]->ptr, ops[i]->dtype, ops[i]->stride[0], ops[i]->stride[1], ops[i]->stride[2], scratch[4], scratch[5], a.H, seq[i], kind);
-    } else if (i < 2 && rows_vec && ops[i]->dtype == BG_F32) {
+    } else if (as_rows && rows_vec && ops[i]->dtype == BG_F32) {
       attn_prep_rows_kernel<float><<<prep_grid(n / 4), 256, 0, s>>>(reinterpret_cast<const float*>(ops[i]->ptr), ops[i]->stride[0],
                                                                    ops[i]->stride[1], ops[i]->stride[2], scratch[2 * i],
                                                                    scratch[2 * i + 1], a.H, seq[i], n / 4, kind);
-    } else if (i < 2 && rows_vec) {
+    } else if (as_rows && rows_vec) {
       attn_prep_rows_kernel<double><<<prep_grid(n / 4), 256, 0, s>>>(reinterpret_cast<const double*>(ops[i]->ptr), ops[i]->stride[0],
                                                                     ops[i]->stride[1], ops[i]->stride[2], scratch[2 * i],
                                                                     scratch[2 * i + 1], a.H, seq[i], n / 4, kind);
     } else {
       PrepView v{ops[i]->ptr, ops[i]->dtype, {ops[i]->stride[0], ops[i]->stride[1], ops[i]->stride[2], ops[i]->stride[3]}};
-      attn_prep_kernel<<<prep_grid(n), 256, 0, s>>>(v, scratch[2 * i], scratch[2 * i + 1], a.B, a.H, seq[i], a.D, i == 2, kind);
+      attn_prep_kernel<<<prep_grid(n), 256, 0, s>>>(v, scratch[2 * i], scratch[2 * i + 1], a.B, a.H, seq[i], a.D, !as_rows, kind);
     }
   }
   unsigned char* cls = nullptr;
@@ -1090,9 +1069,11 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
     }
   }
   CUtensorMap q0, q1, k0, k1, v0, v1;
-  if (!make_map4(&q0, staged[0], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
+  if (!pair && !make_map4(&q0, staged[0], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
   if (!make_map4(&k0, staged[1], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
-  if (!make_map4(&v0, staged[2], sdt, a.B, a.H, a.D, a.Sk, kHeadDim)) return cudaErrorInvalidValue;
+  if (v_mn) {
+    if (!make_map4(&v0, staged[2], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
+  } else if (!make_map4(&v0, staged[2], sdt, a.B, a.H, a.D, a.Sk, kHeadDim)) return cudaErrorInvalidValue;
   q1 = q0; k1 = k0; v1 = v0;
   if (tf32) {
     if (!make_map4(&q1, scratch[1], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
@@ -1119,6 +1100,17 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
   const uint32_t fmt = tf32 ? 2u : (a.ab_dtype == BG_BF16 ? 1u : 0u);
   p.idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(bkv >> 3) << 17) | ((uint32_t)(kQRows >> 4) << 24);
   p.idesc_pv = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kHeadDim >> 3) << 17) | ((uint32_t)(kQRows >> 4) << 24);
+  if (pair) {
+    if (v_mn) p.idesc_pv |= 1u << 16;      // B operand (V) is MN-major
+    if (q_in_kernel) {
+      p.q_ptr = a.q.ptr; p.q_sb = a.q.stride[0]; p.q_sh = a.q.stride[1]; p.q_ss = a.q.stride[2];
+      p.q_f32 = a.q.dtype == BG_F32;
+    } else {
+      p.q_ptr = staged[0]; p.q_sb = (long long)a.H * a.Sq * a.D; p.q_sh = (long long)a.Sq * a.D; p.q_ss = a.D;
+      p.q_f32 = 0;
+    }
+    return launch_attn16_pair(p, a.ab_dtype == BG_BF16, v_mn, p_tmem, k0, v0, s);
+  }
   dim3 grid((a.Sq + kQRows - 1) / kQRows, a.H, a.B);
   cudaError_t e;
   if (tf32) {

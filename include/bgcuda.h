@@ -167,7 +167,10 @@ int bg_destroy(bg_context* ctx);
 const char* bg_last_error(bg_context* ctx);
 int bg_abi_version(void);
 /* options: "profiling" (0/1), "f64_contraction" (0 = exact fp64 FMA, 1 = fp32-faithful tensor
- * path, 2 = automatic: tensor path when no fp64 leaf enters the plan), "fusion" (0/1). */
+ * path, 2 = automatic: tensor path when no fp64 leaf enters the plan), "fusion" (0/1), "tensor_cores" (0/1),
+ * "static_patterns" (0/1), "gemm_groups" (0/1), "gemm_cta_pairs" (0/1/2), "gemm_pair_tile_width" (0/256/192/128),
+ * "attention16_kernel" (bit set: 1 two query tiles per CTA, 2 V as an MN-major operand, 4 P in tensor memory;
+ * 0 one query tile per CTA; -1 restores the default). */
 int bg_set_option(bg_context* ctx, const char* key, int64_t value);
 
 /* -- buffers: upload / materialize / release (_bridge.py:65-71; realizer.ts:1006-1041) ----- */

@@ -18,3 +18,16 @@ def bridge():
     b = CudaBridge(0)
     yield b
     b.close()
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """When BG_PARITY_REPORT names a file, leaves the measured error of every parity comparison of this run there
+    as JSON."""
+    import json
+    from tests import util
+    path = os.environ.get("BG_PARITY_REPORT")
+    if not path or not util.ERROR_LOG:
+        return
+    import numpy as np
+    with open(path, "w") as fh:
+        json.dump({"numpy": np.__version__, "floor_bits": util.FLOOR_BITS, "comparisons": util.ERROR_LOG}, fh, indent=1)

@@ -116,6 +116,27 @@ def test_sdpa_runs_as_one_fused_attention_kernel(bridge, name, expect):
     check(case, composed, want, name + " (composed)")
 
 
+ATTN16_CASES = ["c4_attn_mask_f16", "c4_attn_causal_f16", "c4_attn_mask_bf16", "c4_attn_growing_f16", "c4_attn_growing_causal_f16",
+                "c4_attn_merge_heads_bf16"]
+
+
+@pytest.mark.parametrize("variant", [0, 1, 3, 5, 7])
+@pytest.mark.parametrize("name", ATTN16_CASES)
+def test_every_16bit_attention_kernel_matches_oracle(bridge, name, variant):
+    """Option attention16_kernel: 0 = one query tile per CTA; bit 0 = two query tiles per CTA, bit 1 = V consumed as an
+    MN-major operand (no transposing pass), bit 2 = P kept in tensor memory."""
+    case = CASES[name]
+    t, store, _ = build_case(case)
+    want = oracle_value(t, store)
+    bridge.set_option("attention16_kernel", variant)
+    try:
+        got = realize_cuda(t, bridge)
+    finally:
+        bridge.set_option("attention16_kernel", -1)       # back to the library's default
+    assert any(ln.startswith("attention_tc") for ln in bridge.last_plan_trace())
+    check(case, got, want, f"{name} (attention16_kernel={variant})")
+
+
 @pytest.mark.parametrize("name", ["c3_tc_f32", "c3_tc_f16", "c3_tc_bf16", "c3_tc_ragged", "c3_tc_relu", "c3_tc_rowmajor_b",
                                   "c3_tc_f32_long_k"])
 def test_cta_pair_gemm_matches_oracle(bridge, name):

@@ -50,11 +50,41 @@ def rel_err(got: np.ndarray, want: np.ndarray) -> float:
     return float(np.max(np.abs(got[fin] - want[fin]))) / scale
 
 
+# Element-wise gate: |got_i - want_i| <= rtol * (|want_i| + max|want| * 2^-FLOOR_BITS) for every element.  The floor
+# keeps elements that are small by cancellation (a GEMM output near zero among outputs of order one) from being
+# held to a relative error no fp32 evaluation order can meet, while an element that is 2^-FLOOR_BITS of the largest
+# one or more must itself be right to rtol -- the max-norm gate alone would let it be wrong by 100 %.
+FLOOR_BITS = 4
+
+
+def elementwise_err(got: np.ndarray, want: np.ndarray, floor_bits: int = FLOOR_BITS) -> float:
+    """max_i |got_i - want_i| / (|want_i| + max|want| * 2^-floor_bits) over the finite entries."""
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    fin = np.isfinite(want)
+    if want.size == 0 or not fin.any() or not np.array_equal(fin, np.isfinite(got)):
+        return 0.0 if want.size == 0 or not fin.any() else float("inf")
+    scale = max(float(np.max(np.abs(want[fin]))), 1e-30)
+    denom = np.abs(want[fin]) + scale * 2.0 ** -floor_bits
+    return float(np.max(np.abs(got[fin] - want[fin]) / denom))
+
+
+# every comparison made through check(), written out by the session hook in conftest.py
+ERROR_LOG: list = []
+
+
 def check(case: Case, got: np.ndarray, want: np.ndarray, name: str) -> None:
     assert got.shape == want.shape, f"{name}: shape {got.shape} != {want.shape}"
     assert got.dtype == want.dtype, f"{name}: dtype {got.dtype} != {want.dtype}"
     if case.kind == "exact":
-        assert got.tobytes() == want.tobytes(), f"{name}: not bit-exact"
+        same = got.tobytes() == want.tobytes()
+        ERROR_LOG.append({"name": name, "kind": "exact", "ok": bool(same)})
+        assert same, f"{name}: not bit-exact"
     else:
         e = rel_err(got, want)
+        ew = elementwise_err(got, want)
+        ERROR_LOG.append({"name": name, "kind": "float", "rtol": case.rtol, "max_norm_err": e, "elementwise_err": ew,
+                          "elementwise_err_floor8": elementwise_err(got, want, 8), "floor_bits": FLOOR_BITS,
+                          "dtype": str(np.asarray(want).dtype), "numel": int(np.asarray(want).size)})
         assert e <= case.rtol, f"{name}: rel err {e:.3e} > {case.rtol:.1e}"
+        assert ew <= case.rtol, f"{name}: element-wise err {ew:.3e} > {case.rtol:.1e} (floor 2^-{FLOOR_BITS} of max|ref|)"
