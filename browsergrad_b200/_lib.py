@@ -23,7 +23,7 @@ OPCODES = ("BUFFER", "LOAD", "CONST", "CAST", "ADD", "MUL", "DIV", "NEG", "EXP",
            "SIN", "COS", "ISNAN", "CMP", "WHERE", "MATMUL", "REDUCE", "RESHAPE", "PERMUTE",
            "BROADCAST_TO", "LAYER_NORM", "CROSS_ENTROPY", "INDEX", "FUSED_ELEMENTWISE",
            "FUSED_SOFTMAX", "ATTENTION_FORWARD", "TRIL", "TRIU", "FLIP", "CONCAT", "CUMSUM",
-           "SORT_INDICES", "TOPK_INDICES", "SCATTER")
+           "SORT_INDICES", "TOPK_INDICES", "SCATTER", "SLICE")
 OP_CODE = {n: i for i, n in enumerate(OPCODES)}
 CMP_CODE = {"eq": 0, "ne": 1, "lt": 2, "le": 3, "gt": 4, "ge": 5}
 REDUCE_CODE = {"sum": 0, "max": 1, "min": 2, "mean": 3, "argmax": 4, "argmin": 5, "any": 6, "all": 7, "prod": 8}

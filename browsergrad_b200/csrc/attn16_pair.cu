@@ -4,10 +4,11 @@
 // brought into shared memory and take turns on the tensor core: while the softmax threads of one tile work on their
 // scores, the products of the other tile run.
 //   warp 0      producer: lane 0 fetches K tiles, lane 1 V tiles (TMA, rings of their own)
-//   warp 1      MMA issuer (one thread): S = Q K^T into tensor memory, O += P V
+//   warps 1, 2  MMA issuers (warp 1 for tile A, warp 2 for tile B; all lanes run the loop, an elected lane issues):
+//               S = Q K^T into tensor memory, O += P V
 //   warps 4-7   softmax of tile A: one thread per query row, the row's 128 scores in registers
 //   warps 8-11  softmax of tile B
-// (warps 2 and 3 only fill the first warpgroup, which hands most of its registers to the softmax warpgroups with
+// (warp 3 only fills the first warpgroup, which hands most of its registers to the softmax warpgroups with
 // setmaxnreg: a softmax thread holds a whole row of scores.)
 // A softmax thread reads its row of S once (tcgen05.ld), frees S for the next Q K^T at once, takes the row maximum,
 // the exponentials against a lazily raised reference maximum (O in tensor memory is rescaled only when the running
@@ -62,6 +63,54 @@ __device__ __forceinline__ uint32_t pack16(float a0, float a1) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// The rare per-tile work of a softmax thread lives in functions of their own, away from the straight-line code of
+// the common case: a taken branch over a long cold block costs an instruction fetch the loop cannot afford.
+
+// Puts a score tile into the form the main path expects (see the kernel): masked and out-of-range scores become
+// -inf; with `by_element` the scores become scale * s (+ mask), element by element.  32 scores per step.
+__device__ __noinline__ void fixup_scores(const AttnParams& p, uint32_t t_s, int k0, bool by_element, int tclass, uint4 w4, float scale,
+                                          bool per_elem_scale, size_t score_row, size_t mask_row) {
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    uint32_t r[32];
+    tmem_ld32(t_s + (uint32_t)(c * 32), r);
+    if (by_element) {
+      const bool with_mask = p.mask && tclass >= 2;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int key = k0 + c * 32 + i;
+        const bool in_range = key < p.Sk;
+        float v = __fmul_rn(__uint_as_float(r[i]), per_elem_scale ? (in_range ? p.scale_buf[score_row + key] : 0.f) : scale);
+        if (with_mask && in_range) {
+          if (p.mask_is_bool) { if (reinterpret_cast<const unsigned char*>(p.mask)[mask_row + key]) v = -CUDART_INF_F; }
+          else v = __fadd_rn(v, reinterpret_cast<const float*>(p.mask)[mask_row + key]);
+        }
+        r[i] = __float_as_uint(in_range ? v : -CUDART_INF_F);
+      }
+    } else {
+      uint32_t word = c == 0 ? w4.x : (c == 1 ? w4.y : (c == 2 ? w4.z : w4.w));
+      const int left = p.Sk - (k0 + c * 32);          // keys of this piece that exist
+      if (left < 32) word |= left <= 0 ? 0xffffffffu : (0xffffffffu << left);
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if ((word >> i) & 1u) r[i] = __float_as_uint(-CUDART_INF_F);
+    }
+    tmem_st32(t_s + (uint32_t)(c * 32), r);
+  }
+}
+
+// O[row, 0..63] *= alpha in tensor memory (tcgen05.ld / st are warp-wide: every lane of the warp calls this).
+__device__ __noinline__ void rescale_o(uint32_t t_o, float alpha) {
+#pragma unroll 1
+  for (int half = 0; half < 2; ++half) {
+    uint32_t r[32];
+    tmem_ld32(t_o + (uint32_t)(half * 32), r);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+    tmem_st32(t_o + (uint32_t)(half * 32), r);
+  }
+}
+
 // VMN: V tiles are rows of V (MN-major B operand), else V^T tiles (K-major).  PT: P lives in tensor memory.
 template <bool BF16, bool VMN, bool PT>
 __global__ void __launch_bounds__(kPairThreads, 1)
@@ -86,8 +135,10 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   uint64_t* pv_full = p_full + 2;         // [2] P V has completed
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_full + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  unsigned char* s_cls = reinterpret_cast<unsigned char*>(tmem_holder + 4);   // [2][n_kv] tile classes of the two query tiles
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);   // the same in every lane, and known to be
+  const int lane = threadIdx.x & 31;
   const int n_bh = p.B * p.H;
   const int n_qt = (p.Sq + kQRows - 1) / kQRows;
   const int n_pairs = (n_qt + 1) / 2;
@@ -95,12 +146,21 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   const int bh = (int)(blockIdx.x % (unsigned)n_bh);
   const int b = bh / p.H, h = bh % p.H;
   const int n_kv = (p.Sk + BKV - 1) / BKV;
-  // tile classes of the two query tiles (null: every key tile is processed); tile B may not exist
+  // Tile classes of the two query tiles, copied to shared memory once: every role consults them once or more per
+  // key tile, and a global load in the MMA thread's loop delays every product behind it.  Without a class table
+  // every key tile is processed (class 3 with a mask, else 1); a tile B that does not exist has class 0 throughout.
   const bool has_b = 2 * pair + 1 < n_qt;
-  const unsigned char* cls_a = p.tile_class ? p.tile_class + (size_t)(2 * pair) * n_kv : nullptr;
-  const unsigned char* cls_b = p.tile_class && has_b ? p.tile_class + (size_t)(2 * pair + 1) * n_kv : nullptr;
-  auto need_a = [&](int j) { return !(cls_a && cls_a[j] == 0); };
-  auto need_b = [&](int j) { return has_b && !(cls_b && cls_b[j] == 0); };
+  {
+    const unsigned char* cls_a = p.tile_class ? p.tile_class + (size_t)(2 * pair) * n_kv : nullptr;
+    const unsigned char* cls_b = p.tile_class && has_b ? p.tile_class + (size_t)(2 * pair + 1) * n_kv : nullptr;
+    const unsigned char dflt = p.mask ? 3 : 1;
+    for (int j = threadIdx.x; j < n_kv; j += kPairThreads) {
+      s_cls[j] = cls_a ? cls_a[j] : dflt;
+      s_cls[n_kv + j] = has_b ? (cls_b ? cls_b[j] : dflt) : (unsigned char)0;
+    }
+  }
+  auto need_a = [&](int j) { return s_cls[j] != 0; };
+  auto need_b = [&](int j) { return s_cls[n_kv + j] != 0; };
   auto next_union = [&](int j) { while (j < n_kv && !need_a(j) && !need_b(j)) ++j; return j; };
 
   if (threadIdx.x == 0) {
@@ -109,8 +169,9 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       mbar_init(&s_full[g], 1); mbar_init(&s_empty[g], 4);
       mbar_init(&p_full[g], 4); mbar_init(&pv_full[g], 1);
     }
-    for (int s = 0; s < C::NK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
-    for (int s = 0; s < C::NV; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    // a K or V slot is free once both issuers are done with it
+    for (int s = 0; s < C::NK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 2); }
+    for (int s = 0; s < C::NV; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 2); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -149,67 +210,86 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           }
         }
       }
-    } else if (warp == 1) {
-      if (lane == 0) {
-        bool ok = true;
-        int n_qk[2] = {0, 0}, n_pv[2] = {0, 0};
-        auto issue_qk = [&](int g, int slot) -> bool {
-          const int n = n_qk[g]++;
-          if (n == 0 && !mbar_wait(&q_full[g], 0, abort_flag)) return false;
-          if (n > 0 && !mbar_wait(&s_empty[g], (uint32_t)(n - 1) & 1u, abort_flag)) return false;
-          tc_fence_after();
-          const uint64_t da = make_kmajor_sw128_desc(smem_u32(sQ + g * C::QBytes));
-          const uint64_t db = make_kmajor_sw128_desc(smem_u32(sK + slot * C::KBytes));
-          const uint32_t d_s = tmem_base + (uint32_t)(C::ColS + g * BKV);
-  #pragma unroll
-          for (int k = 0; k < 4; ++k) umma<false>(d_s, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc_qk, k ? 1u : 0u);
+    } else if (warp <= 2) {
+      // One issuer warp per query tile (warp 1: tile A, warp 2: tile B): neither tile's products wait behind a
+      // barrier of the other.  All 32 lanes run the loop (see elect_one); the elected lane issues.  Key tiles are
+      // walked in the producers' order; a tile this query tile skips is released with a plain arrival once it has
+      // landed (so that the arrival counts for that tile and no earlier one).
+      const int g = warp - 1;
+      auto need = [&](int j) { return s_cls[g * n_kv + j] != 0; };
+      const uint64_t desc_q = make_kmajor_sw128_desc(smem_u32(sQ + g * C::QBytes));
+      const uint32_t d_s = tmem_base + (uint32_t)(C::ColS + g * BKV);
+      const uint32_t d_o = tmem_base + (uint32_t)(C::ColO + g * kHeadDim);
+      const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
+      bool ok = true;
+      int n_qk = 0, n_pv = 0;
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0; };
+      auto issue_qk = [&](int slot) -> bool {
+        const int n = n_qk++;
+        if (n == 0 && !wait_all(&q_full[g], 0)) return false;
+        if (n > 0 && !wait_all(&s_empty[g], (uint32_t)(n - 1) & 1u)) return false;
+        tc_fence_after();
+        const uint64_t db = make_kmajor_sw128_desc(smem_u32(sK + slot * C::KBytes));
+        if (elect_one()) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma<false>(d_s, desc_q + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_qk, k ? 1u : 0u);
           umma_commit(&s_full[g]);
-          return true;
-        };
-        auto issue_pv = [&](int g, int slot) -> bool {
-          const int n = n_pv[g]++;
-          if (!mbar_wait(&p_full[g], (uint32_t)n & 1u, abort_flag)) return false;
-          tc_fence_after();
-          const uint32_t v_addr = smem_u32(sV + slot * C::VBytes);
-          const uint32_t d_o = tmem_base + (uint32_t)(C::ColO + g * kHeadDim);
-  #pragma unroll
+        }
+        __syncwarp();
+        return true;
+      };
+      auto issue_pv = [&](int slot) -> bool {
+        const int n = n_pv++;
+        if (!wait_all(&p_full[g], (uint32_t)n & 1u)) return false;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sV + slot * C::VBytes);
+        const uint32_t p_addr = smem_u32(sP + g * C::PBytes);
+        const uint32_t first = n > 0 ? 1u : 0u;
+        if (elect_one()) {
+#pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint64_t db = VMN ? make_mnmajor_sw128_desc(v_addr + (uint32_t)(k * 2048))
                                     : make_kmajor_sw128_desc(v_addr + (uint32_t)((k >> 2) * (kHeadDim * 128))) + (uint64_t)((k & 3) * 2);
-            const uint32_t acc = (n > 0 || k > 0) ? 1u : 0u;
+            const uint32_t acc = k > 0 ? 1u : first;
             if (PT) {
-              umma_ts_f16(d_o, tmem_base + (uint32_t)(C::ColP + g * 64 + k * 8), db, p.idesc_pv, acc);
+              umma_ts_f16(d_o, tmem_base + (uint32_t)(C::ColP + g * 64 + k * 8), db, idesc_pv, acc);
             } else {
-              const uint64_t da = make_kmajor_sw128_desc(smem_u32(sP + g * C::PBytes + (k >> 2) * (kQRows * 128))) + (uint64_t)((k & 3) * 2);
-              umma<false>(d_o, da, db, p.idesc_pv, acc);
+              const uint64_t da = make_kmajor_sw128_desc(p_addr + (uint32_t)((k >> 2) * (kQRows * 128))) + (uint64_t)((k & 3) * 2);
+              umma<false>(d_o, da, db, idesc_pv, acc);
             }
           }
           umma_commit(&pv_full[g]);
-          return true;
-        };
-        // key tiles in order; tile u+1's Q K^T is issued ahead of tile u's P V for each query tile
-        int jc = next_union(0), u = 0;
-        if (jc < n_kv) {
-          ok = mbar_wait(&k_full[0], 0, abort_flag);
-          if (ok && need_a(jc)) ok = issue_qk(0, 0);
-          if (ok && need_b(jc)) ok = issue_qk(1, 0);
-          if (ok) umma_commit(&k_empty[0]);
         }
-        while (jc < n_kv && ok) {
-          const int jn = next_union(jc + 1), un = u + 1;
-          const bool more = jn < n_kv;
-          const int ks = un % C::NK, vs = u % C::NV;
-          if (more) ok = mbar_wait(&k_full[ks], (uint32_t)(un / C::NK) & 1u, abort_flag);
-          if (ok && more && need_a(jn)) ok = issue_qk(0, ks);
-          if (ok) ok = mbar_wait(&v_full[vs], (uint32_t)(u / C::NV) & 1u, abort_flag);
-          if (ok && need_a(jc)) ok = issue_pv(0, vs);
-          if (ok && more && need_b(jn)) ok = issue_qk(1, ks);
-          if (ok && more) umma_commit(&k_empty[ks]);
-          if (ok && need_b(jc)) ok = issue_pv(1, vs);
-          if (ok) umma_commit(&v_empty[vs]);
-          jc = jn;
-          u = un;
+        __syncwarp();
+        return true;
+      };
+      auto release = [&](uint64_t* bar, bool used) {
+        if (elect_one()) { if (used) umma_commit(bar); else mbar_arrive(bar); }
+        __syncwarp();
+      };
+      // tile u+1's Q K^T is issued ahead of tile u's P V: S(u+1) is ready when the softmax warps finish tile u
+      int jc = next_union(0), u = 0;
+      if (jc < n_kv) {
+        ok = wait_all(&k_full[0], 0);
+        const bool used = need(jc);
+        if (ok && used) ok = issue_qk(0);
+        if (ok) release(&k_empty[0], used);
+      }
+      while (jc < n_kv && ok) {
+        const int jn = next_union(jc + 1), un = u + 1;
+        const int ks = un % C::NK, vs = u % C::NV;
+        if (jn < n_kv) {
+          ok = wait_all(&k_full[ks], (uint32_t)(un / C::NK) & 1u);
+          const bool used = need(jn);
+          if (ok && used) ok = issue_qk(ks);
+          if (ok) release(&k_empty[ks], used);
         }
+        if (ok) ok = wait_all(&v_full[vs], (uint32_t)(u / C::NV) & 1u);
+        const bool used = need(jc);
+        if (ok && used) ok = issue_pv(vs);
+        if (ok) release(&v_empty[vs], used);
+        jc = jn;
+        u = un;
       }
     }
   } else {
@@ -224,7 +304,7 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
     const int sw = r_in_tile & 7;
     constexpr float kLog2e = 1.4426950408889634f;
-    const unsigned char* cls = g == 0 ? cls_a : cls_b;
+    const unsigned char* cls = s_cls + g * n_kv;
 
     if (active) {
       // ---- this thread's query row -> shared memory in the operand layout ---------------------------------------
@@ -263,12 +343,29 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       const uint32_t t_p = tmem_base + (uint32_t)(C::ColP + g * 64) + lane_sel;
       bool ok = true;
       int t = 0;
+      const bool simple_scale = !per_elem_scale && scale > 0.f;
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int tclass = cls ? cls[j] : (p.mask ? 3 : 1);
+        const int tclass = cls[j];
         if (tclass == 0) continue;
+        const int k0 = j * BKV;
+        // The main path below is straight-line code over the row's 128 scores and assumes a plain tile: every key
+        // in range, nothing masked, one positive scale (folded into the exponent).  Any other tile is first put
+        // into that form in tensor memory by a short loop over 32-score pieces (`fixup`): masked or out-of-range
+        // scores become -inf; with a per-element scale or an additive mask the scores are replaced by
+        // scale * s (+ mask) and the exponent scale becomes one.  Keeping the rare cases out of the unrolled path
+        // keeps it small enough for the instruction cache.
+        const bool ragged = k0 + BKV > p.Sk;
+        const bool by_element = !simple_scale || (p.mask && tclass == 3);
+        const bool fixup = by_element || tclass == 2 || ragged;
+        // binary mask: four words of "masked" bits cover this row's 128 keys (fetched ahead of the wait for S)
+        uint4 w4 = make_uint4(0u, 0u, 0u, 0u);
+        if (!by_element && tclass == 2)
+          w4 = __ldg(reinterpret_cast<const uint4*>(p.mask_bits + (size_t)(row_ok ? row : 0) * p.mask_words + (k0 >> 5)));
         ok = __all_sync(0xffffffffu, mbar_wait(&s_full[g], (uint32_t)t & 1u, abort_flag));
         if (!ok) break;
         tc_fence_after();
+        if (fixup) fixup_scores(p, t_s, k0, by_element, tclass, w4, scale, per_elem_scale, score_row, mask_row);
+        const bool fast = !by_element;      // scale still to be applied (folded into the exponent)
         float x[BKV];
         {
           uint32_t* xu = reinterpret_cast<uint32_t*>(x);
@@ -282,34 +379,6 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_empty[g]);
-
-        const int k0 = j * BKV;
-        const bool simple_scale = !per_elem_scale && scale > 0.f;
-        // a binary mask is applied from its bit words only on the folded-scale path; otherwise element by element
-        const bool need_mask = p.mask && (tclass == 3 || (tclass == 2 && !simple_scale));
-        const bool fast = !need_mask && simple_scale && (tclass == 2 || k0 + BKV <= p.Sk);
-        if (fast) {
-          if (tclass == 2) {
-            // binary mask: four words of "masked" bits cover this row's 128 keys
-            const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(p.mask_bits + (size_t)(row_ok ? row : 0) * p.mask_words + (k0 >> 5)));
-            const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
-#pragma unroll
-            for (int i = 0; i < BKV; ++i)
-              if ((w[i >> 5] >> (i & 31)) & 1u) x[i] = -CUDART_INF_F;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < BKV; ++i) {
-            const int key = k0 + i;
-            const bool in_range = key < p.Sk;
-            float v = __fmul_rn(x[i], per_elem_scale ? (in_range ? p.scale_buf[score_row + key] : 0.f) : scale);
-            if (need_mask && in_range) {
-              if (p.mask_is_bool) { if (reinterpret_cast<const unsigned char*>(p.mask)[mask_row + key]) v = -CUDART_INF_F; }
-              else v = __fadd_rn(v, reinterpret_cast<const float*>(p.mask)[mask_row + key]);
-            }
-            x[i] = in_range ? v : -CUDART_INF_F;
-          }
-        }
         // row maximum of the tile, in natural units
         float mt;
         {
@@ -329,14 +398,7 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           pv_done = true;
           tc_fence_after();
           const float alpha = raise ? ex2_approx((m_ref - mt) * kLog2e) : 1.0f;
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t r[32];
-            tmem_ld32(t_o + (uint32_t)(half * 32), r);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(t_o + (uint32_t)(half * 32), r);
-          }
+          rescale_o(t_o, alpha);
           tc_fence_before();
           if (raise) { l *= alpha; m_ref = mt; }
         }
@@ -450,7 +512,10 @@ cudaError_t launch_variant(bool vmn, bool pt, dim3 grid, size_t smem, cudaStream
 
 }  // namespace
 
-bool attn16_pair_out_ok(int out_dtype, const void* out, long long out_sb, long long out_sh, long long out_ss) {
+bool attn16_pair_usable(int Sk, int out_dtype, const void* out, long long out_sb, long long out_sh, long long out_ss) {
+  // the tile classes of both query tiles are kept in shared memory beside the operand tiles
+  const int n_kv = (Sk + PairCfg::BKV - 1) / PairCfg::BKV;
+  if ((size_t)PairCfg::smem_bytes(false) + 256 + 1024 + 2 * (size_t)n_kv > 227 * 1024) return false;
   // output rows are written in 16-byte pieces
   const int es = dtype_size(out_dtype);
   const long long per16 = 16 / es;
@@ -462,7 +527,9 @@ cudaError_t launch_attn16_pair(const attn::AttnParams& p, bool bf16, bool v_mn, 
   const int n_qt = (p.Sq + kQRows - 1) / kQRows;
   const long long n_cta = (long long)((n_qt + 1) / 2) * p.B * p.H;
   if (n_cta <= 0 || n_cta > 0x7fffffffll) return cudaErrorInvalidValue;
-  const size_t smem = (size_t)PairCfg::smem_bytes(p_in_tmem) + 256 + 1024;
+  const int n_kv = (p.Sk + PairCfg::BKV - 1) / PairCfg::BKV;
+  const size_t smem = (size_t)PairCfg::smem_bytes(p_in_tmem) + 256 + 1024 + 2 * (size_t)n_kv;
+  if (smem > 227 * 1024) return cudaErrorInvalidValue;
   dim3 grid((unsigned)n_cta);
   return bf16 ? launch_variant<true>(v_mn, p_in_tmem, grid, smem, s, tm_k, tm_v, p)
               : launch_variant<false>(v_mn, p_in_tmem, grid, smem, s, tm_k, tm_v, p);

@@ -65,7 +65,7 @@ struct AttnParams {
 
 // Two-query-tile 16-bit kernel (attn16_pair.cu).  `p` carries the query rows' address and strides; K tiles are
 // [128 keys, 64] boxes of tm_k; tm_v gives [128 keys, 64] boxes of V (v_mn) or [64, 64 keys] boxes of V^T.
-bool attn16_pair_out_ok(int out_dtype, const void* out, long long out_sb, long long out_sh, long long out_ss);
+bool attn16_pair_usable(int Sk, int out_dtype, const void* out, long long out_sb, long long out_sh, long long out_ss);
 cudaError_t launch_attn16_pair(const attn::AttnParams& p, bool bf16, bool v_mn, bool p_in_tmem, const CUtensorMap& tm_k,
                                const CUtensorMap& tm_v, cudaStream_t s);
 

@@ -996,7 +996,7 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
   const bool tf32 = a.mode == 1;
   const int bkv = tf32 ? 64 : Attn16::BKV;
   const int sdt = tf32 ? BG_F32 : a.ab_dtype;
-  const bool pair = !tf32 && (g_attn16_variant & 1) && attn16_pair_out_ok(a.out_dtype, a.out, a.out_sb, a.out_sh, a.out_ss);
+  const bool pair = !tf32 && (g_attn16_variant & 1) && attn16_pair_usable(a.Sk, a.out_dtype, a.out, a.out_sb, a.out_sh, a.out_ss);
   const bool v_mn = pair && (g_attn16_variant & 2);
   const bool p_tmem = pair && (g_attn16_variant & 4);
   // operand staging: dense Q, K, V^T (or V) in the kernel's encoding

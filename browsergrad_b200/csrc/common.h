@@ -201,13 +201,27 @@ cudaError_t launch_softmax_generic(const void* in, void* out, int dtype, int64_t
 cudaError_t launch_gather(const void* x, const int64_t* idx, void* out, int esize, int rank,
                           const int64_t* x_shape, const int64_t* idx_shape, int dim, int* status,
                           cudaStream_t s);
-// Cross entropy epilogue: per-position losses (fp32/fp64) -> none/mean/sum over valid targets.
-cudaError_t launch_ce_reduce(const void* per_pos, const int64_t* targets, void* out, int dtype,
-                             int64_t n, int reduction, int64_t ignore_index, cudaStream_t s);
-// Cross entropy per-position term for logits [outer, C, inner] (class axis strided by inner).
-cudaError_t launch_ce_rows(const void* logits, const int64_t* targets, void* per_pos, int dtype,
-                           int64_t outer, int64_t C, int64_t inner, int64_t ignore_index, int* status,
-                           cudaStream_t s);
+// Cross entropy (misc_kernels.cu).  launch_ce_rows writes one loss per position of logits [outer, C, inner] (class axis
+// strided by inner): class-index targets (int64, `ignore_index` skipped, values outside [0, C) set *status) or
+// probability targets of the logits' shape and type; optional class weights [C] of the logits' type and label
+// smoothing.  `sel_w`, when given, receives each position's target weight (0 for ignored targets).
+struct CeProblem {
+  const void* logits;
+  const void* targets;
+  const void* weight;
+  void* per_pos;
+  void* sel_w;
+  int dtype;                 // BG_F32 or BG_F64
+  int prob_targets;
+  int64_t outer, C, inner, ignore_index;
+  double label_smoothing;
+  int* status;
+};
+cudaError_t launch_ce_rows(const CeProblem& c, cudaStream_t s);
+// Per-position losses -> sum (reduction 2) or mean (1): the mean divides by the summed `sel_w` when given, else by the
+// number of `targets` that differ from ignore_index when given, else by `fixed_count`.
+cudaError_t launch_ce_reduce(const void* per_pos, const int64_t* targets, const void* sel_w, void* out, int dtype, int64_t n,
+                             int reduction, int64_t ignore_index, double fixed_count, cudaStream_t s);
 
 struct GemmOperand {
   const void* ptr;

@@ -18,7 +18,7 @@ const char* op_name(int op) {
                                 "ABS", "SIGN", "SIN", "COS", "ISNAN", "CMP", "WHERE", "MATMUL", "REDUCE",
                                 "RESHAPE", "PERMUTE", "BROADCAST_TO", "LAYER_NORM", "CROSS_ENTROPY", "INDEX",
                                 "FUSED_ELEMENTWISE", "FUSED_SOFTMAX", "ATTENTION_FORWARD", "TRIL", "TRIU", "FLIP", "CONCAT",
-                                "CUMSUM", "SORT_INDICES", "TOPK_INDICES", "SCATTER"};
+                                "CUMSUM", "SORT_INDICES", "TOPK_INDICES", "SCATTER", "SLICE"};
   return (op >= 0 && op < BG_OP_COUNT) ? names[op] : "?";
 }
 

@@ -210,52 +210,233 @@ __global__ void gather_kernel(const __grid_constant__ GatherParams p) {
   }
 }
 
-// per-position cross entropy: -(log_softmax(logits)[target]) over the class axis of [outer, C, inner]
+// ---- cross entropy (execute_cross_entropy_arrays, _framework_contracts.py:3756-3835) ---------------------------
+// Per position, over the class axis of logits [outer, C, inner], in the logits' own float type T:
+//   M = max_c x_c, S = sum_c exp(x_c - M), lse = log S, logp_c = (x_c - M) - lse                      (:3644-3664)
+//   class-index targets:  loss = -logp_t * w_t; with label smoothing eps the loss becomes
+//                         loss * (1 - eps) + (-sum_c logp_c w_c) * (eps / C); an ignored target gives 0    (:3801-3824)
+//   probability targets:  loss = -sum_c logp_c * (p_c (1 - eps) + eps / C) * w_c                            (:3776-3799)
+// Both class sums have the form sum_c q_c logp_c = T1 - lse * T2 with T1 = sum_c q_c (x_c - M), T2 = sum_c q_c, so one
+// pass over the classes after the maximum yields S, T1 and T2 together.  w is all ones without class weights.
 template <typename T>
-__global__ void ce_rows_kernel(const T* logits, const int64_t* targets, T* per_pos, int64_t outer, int64_t C,
-                               int64_t inner, int64_t ignore_index, int* status) {
-  const int64_t n = outer * inner;
+struct CeRowArgs {
+  const T* logits;
+  const int64_t* idx;     // class-index targets, or null
+  const T* prob;          // probability targets (same shape as logits), or null
+  const T* weight;        // [C] or null
+  T* per_pos;             // [outer * inner]
+  T* sel_w;               // [outer * inner] weight of each position's target (0 when ignored), or null
+  int64_t outer, C, inner, ignore_index;
+  T smoothing;            // eps
+  int* status;
+};
+
+template <typename T> __device__ __forceinline__ T ce_exp(T x);
+template <> __device__ __forceinline__ float ce_exp<float>(float x) { return expf(x); }
+template <> __device__ __forceinline__ double ce_exp<double>(double x) { return exp(x); }
+template <typename T> __device__ __forceinline__ T ce_log(T x);
+template <> __device__ __forceinline__ float ce_log<float>(float x) { return logf(x); }
+template <> __device__ __forceinline__ double ce_log<double>(double x) { return log(x); }
+template <typename T> __device__ __forceinline__ T ce_neg_inf();
+template <> __device__ __forceinline__ float ce_neg_inf<float>() { return -CUDART_INF_F; }
+template <> __device__ __forceinline__ double ce_neg_inf<double>() { return -CUDART_INF; }
+
+// The loss of one position from its reduced statistics; x_t is the target's logit (index targets).
+template <typename T>
+__device__ __forceinline__ void ce_finish(const CeRowArgs<T>& a, int64_t pos, T M, T S, T T1, T T2, bool need_sums) {
+  const T lse = ce_log<T>(S);
+  const T eps = a.smoothing;
+  if (a.prob) {
+    a.per_pos[pos] = -(T1 - lse * T2);
+    return;
+  }
+  const int64_t tg = a.idx[pos];
+  if (tg == a.ignore_index) {
+    a.per_pos[pos] = T(0);
+    if (a.sel_w) a.sel_w[pos] = T(0);
+    return;
+  }
+  if (tg < 0 || tg >= a.C) {
+    atomicExch(a.status, BG_ERR_INDEX_RANGE);
+    a.per_pos[pos] = T(0);
+    if (a.sel_w) a.sel_w[pos] = T(0);
+    return;
+  }
+  const int64_t o = pos / a.inner, i = pos - o * a.inner;
+  const T xt = a.logits[(o * a.C + tg) * a.inner + i];
+  const T wt = a.weight ? a.weight[tg] : T(1);
+  T loss = -((xt - M) - lse);
+  if (a.weight) loss *= wt;
+  if (need_sums) loss = loss * (T(1) - eps) + (-(T1 - lse * T2)) * (eps / (T)a.C);
+  a.per_pos[pos] = loss;
+  if (a.sel_w) a.sel_w[pos] = wt;
+}
+
+template <typename T, int VEC> __device__ __forceinline__ void ce_load_vec(const T* p, T* out);
+template <> __device__ __forceinline__ void ce_load_vec<float, 4>(const float* p, float* out) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+template <> __device__ __forceinline__ void ce_load_vec<double, 2>(const double* p, double* out) {
+  const double2 v = *reinterpret_cast<const double2*>(p);
+  out[0] = v.x; out[1] = v.y;
+}
+
+// One thread per position; the class axis is `inner` elements apart, so neighbouring threads read neighbouring
+// addresses when inner > 1.  Used for spatial logits and for short class axes.
+template <typename T>
+__global__ void ce_pos_kernel(const CeRowArgs<T> a) {
+  const int64_t n = a.outer * a.inner;
+  const bool need_sums = a.prob != nullptr || a.smoothing != T(0);
   for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t o = t / inner, i = t - o * inner;
-    const int64_t base = o * C * inner + i;
-    const int64_t tg = targets[t];
-    if (tg == ignore_index) { per_pos[t] = T(0); continue; }
-    if (tg < 0 || tg >= C) { atomicExch(status, BG_ERR_INDEX_RANGE); per_pos[t] = T(0); continue; }
-    T m = logits[base];
-    for (int64_t c = 1; c < C; ++c) { T v = logits[base + c * inner]; m = v > m ? v : m; }
-    T sum = T(0);
-    for (int64_t c = 0; c < C; ++c) {
-      T sh = logits[base + c * inner] - m;
-      sum += sizeof(T) == 4 ? (T)expf((float)sh) : (T)exp((double)sh);
+    const int64_t o = t / a.inner, i = t - o * a.inner;
+    const int64_t base = o * a.C * a.inner + i;
+    if (!a.prob && a.idx[t] == a.ignore_index) { ce_finish<T>(a, t, T(0), T(1), T(0), T(0), false); continue; }
+    T M = a.logits[base];
+    for (int64_t c = 1; c < a.C; ++c) { const T v = a.logits[base + c * a.inner]; M = v > M ? v : M; }
+    T S = T(0), T1 = T(0), T2 = T(0);
+    for (int64_t c = 0; c < a.C; ++c) {
+      const T sh = a.logits[base + c * a.inner] - M;
+      S += ce_exp<T>(sh);
+      if (need_sums) {
+        T q = a.weight ? a.weight[c] : T(1);
+        if (a.prob) q *= a.prob[base + c * a.inner] * (T(1) - a.smoothing) + a.smoothing / (T)a.C;
+        T1 += q * sh;
+        T2 += q;
+      }
     }
-    T lse = sizeof(T) == 4 ? (T)logf((float)sum) : (T)log((double)sum);
-    T lp = (logits[base + tg * inner] - m) - lse;
-    per_pos[t] = -lp;
+    ce_finish<T>(a, t, M, S, T1, T2, need_sums);
   }
 }
 
-// Deterministic single-CTA reduction of per-position losses (sum, count of valid targets).
+// One CTA per position for class axes that are contiguous (inner == 1) and long: every thread walks the row in
+// 16-byte vectors (coalesced), keeping a running maximum that is raised once per group of vectors, and the partial
+// (M, S, T1, T2) of all threads are combined through shared memory.  The row is read from DRAM once; the statistics
+// are rescaled, never the data.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) ce_row_kernel(const CeRowArgs<T> a, int vec_ok) {
+  constexpr int kGroup = 4;                       // vectors per thread between maximum updates
+  const int64_t row = blockIdx.x;
+  const T* x = a.logits + row * a.C;
+  const T* pr = a.prob ? a.prob + row * a.C : nullptr;
+  const bool need_sums = a.prob != nullptr || a.smoothing != T(0);
+  const T eps = a.smoothing, unif = a.smoothing / (T)a.C;
+  __shared__ T sh_m[8], sh_s[8], sh_t1[8], sh_t2[8];
+  const bool skip = !a.prob && a.idx[row] == a.ignore_index;      // the whole CTA agrees
+  T M = ce_neg_inf<T>(), S = T(0), T1 = T(0), T2 = T(0);           // T1 is kept relative to the running M
+  if (!skip) {
+    const bool use_w = a.weight != nullptr && need_sums;
+    // raise the reference maximum to gm: S scales by exp(M - gm), T1 (kept relative to M) shifts by (M - gm) * T2
+    auto raise = [&](T gm) {
+      if (gm > M) {
+        if (M != ce_neg_inf<T>()) { S *= ce_exp<T>(M - gm); T1 += (M - gm) * T2; }
+        M = gm;
+      }
+    };
+    auto add = [&](T xv, T pv, T wv) {
+      const T shv = xv - M;
+      S += ce_exp<T>(shv);
+      if (need_sums) {
+        T q = wv;
+        if (pr) q *= pv * (T(1) - eps) + unif;
+        T1 += q * shv;
+        T2 += q;
+      }
+    };
+    int64_t scalar_from = 0;
+    if (vec_ok) {
+      const int64_t n_vec = a.C / VEC;
+      scalar_from = n_vec * VEC;
+      for (int64_t v0 = threadIdx.x; v0 < n_vec; v0 += (int64_t)blockDim.x * kGroup) {
+        T v[kGroup][VEC], pv[kGroup][VEC], wv[kGroup][VEC];
+        T gm = ce_neg_inf<T>();
+#pragma unroll
+        for (int k = 0; k < kGroup; ++k) {
+          const int64_t vi = v0 + (int64_t)k * blockDim.x;
+          const bool live = vi < n_vec;
+          ce_load_vec<T, VEC>(x + (live ? vi : 0) * VEC, v[k]);
+          if (pr) ce_load_vec<T, VEC>(pr + (live ? vi : 0) * VEC, pv[k]);
+          if (use_w) ce_load_vec<T, VEC>(a.weight + (live ? vi : 0) * VEC, wv[k]);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            if (!live) v[k][e] = ce_neg_inf<T>();        // exp(-inf - M) = 0; the sums skip dead vectors below
+            gm = v[k][e] > gm ? v[k][e] : gm;
+          }
+        }
+        raise(gm);
+#pragma unroll
+        for (int k = 0; k < kGroup; ++k) {
+          if (v0 + (int64_t)k * blockDim.x >= n_vec) continue;
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) add(v[k][e], pr ? pv[k][e] : T(0), use_w ? wv[k][e] : T(1));
+        }
+      }
+    }
+    for (int64_t c = scalar_from + threadIdx.x; c < a.C; c += blockDim.x) {
+      const T xv = x[c];
+      raise(xv);
+      add(xv, pr ? pr[c] : T(0), use_w ? a.weight[c] : T(1));
+    }
+    // combine within the warp, then across warps: (M, S, T1, T2) pairs merge by rescaling the smaller maximum's side
+    auto merge = [&](T m2, T s2, T t12, T t22) {
+      const T mm = m2 > M ? m2 : M;
+      if (mm == ce_neg_inf<T>()) return;
+      const T f1 = M == ce_neg_inf<T>() ? T(0) : ce_exp<T>(M - mm), f2 = m2 == ce_neg_inf<T>() ? T(0) : ce_exp<T>(m2 - mm);
+      const T d1 = M == ce_neg_inf<T>() ? T(0) : (M - mm) * T2, d2 = m2 == ce_neg_inf<T>() ? T(0) : (m2 - mm) * t22;
+      S = S * f1 + s2 * f2;
+      T1 = (T1 + d1) + (t12 + d2);
+      T2 += t22;
+      M = mm;
+    };
+    for (int o = 16; o > 0; o >>= 1)
+      merge(__shfl_xor_sync(0xffffffffu, M, o), __shfl_xor_sync(0xffffffffu, S, o), __shfl_xor_sync(0xffffffffu, T1, o),
+            __shfl_xor_sync(0xffffffffu, T2, o));
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  if (lane == 0) { sh_m[warp] = M; sh_s[warp] = S; sh_t1[warp] = T1; sh_t2[warp] = T2; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (skip) { ce_finish<T>(a, row, T(0), T(1), T(0), T(0), false); return; }
+    T m = sh_m[0], s = sh_s[0], t1 = sh_t1[0], t2 = sh_t2[0];
+    for (int w = 1; w < n_warps; ++w) {
+      const T m2 = sh_m[w], mm = m2 > m ? m2 : m;
+      if (mm == ce_neg_inf<T>()) continue;
+      const T f1 = m == ce_neg_inf<T>() ? T(0) : ce_exp<T>(m - mm), f2 = m2 == ce_neg_inf<T>() ? T(0) : ce_exp<T>(m2 - mm);
+      const T d1 = m == ce_neg_inf<T>() ? T(0) : (m - mm) * t2, d2 = m2 == ce_neg_inf<T>() ? T(0) : (m2 - mm) * sh_t2[w];
+      s = s * f1 + sh_s[w] * f2;
+      t1 = (t1 + d1) + (sh_t1[w] + d2);
+      t2 += sh_t2[w];
+      m = mm;
+    }
+    ce_finish<T>(a, row, m, s, t1, t2, need_sums);
+  }
+}
+
+// Deterministic reduction of the per-position losses: sum, or mean over the valid targets (their count, their summed
+// class weights when weights are given, or `fixed_count` positions for probability targets).  256 partial sums in
+// double, combined in a fixed order.
 template <typename T>
-__global__ void ce_reduce_kernel(const T* per_pos, const int64_t* targets, T* out, int64_t n, int reduction,
-                                 int64_t ignore_index) {
+__global__ void ce_reduce_kernel(const T* per_pos, const int64_t* targets, const T* sel_w, T* out, int64_t n, int reduction,
+                                 int64_t ignore_index, double fixed_count) {
   __shared__ double ssum[256];
-  __shared__ long long scnt[256];
-  double s = 0.0;
-  long long c = 0;
+  __shared__ double sden[256];
+  double s = 0.0, c = 0.0;
   for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
     s += (double)per_pos[i];
-    c += targets[i] != ignore_index;
+    if (sel_w) c += (double)sel_w[i];
+    else if (targets) c += targets[i] != ignore_index ? 1.0 : 0.0;
   }
   ssum[threadIdx.x] = s;
-  scnt[threadIdx.x] = c;
+  sden[threadIdx.x] = c;
   __syncthreads();
   for (int o = 128; o > 0; o >>= 1) {
-    if ((int)threadIdx.x < o) { ssum[threadIdx.x] += ssum[threadIdx.x + o]; scnt[threadIdx.x] += scnt[threadIdx.x + o]; }
+    if ((int)threadIdx.x < o) { ssum[threadIdx.x] += ssum[threadIdx.x + o]; sden[threadIdx.x] += sden[threadIdx.x + o]; }
     __syncthreads();
   }
   if (threadIdx.x == 0) {
-    T num = (T)ssum[0];
-    out[0] = reduction == 2 ? num : (T)(num / (T)scnt[0]);
+    const T num = (T)ssum[0];
+    const T den = (sel_w || targets) ? (T)sden[0] : (T)fixed_count;
+    out[0] = reduction == 2 ? num : (T)(num / den);
   }
 }
 
@@ -353,20 +534,47 @@ cudaError_t launch_gather(const void* x, const int64_t* idx, void* out, int esiz
   return cudaGetLastError();
 }
 
-cudaError_t launch_ce_rows(const void* logits, const int64_t* targets, void* per_pos, int dtype, int64_t outer,
-                           int64_t C, int64_t inner, int64_t ignore_index, int* status, cudaStream_t s) {
-  const int64_t n = outer * inner;
-  if (n == 0) return cudaSuccess;
-  const unsigned g = grid_for(n, 128);
-  if (dtype == BG_F64) ce_rows_kernel<double><<<g, 128, 0, s>>>((const double*)logits, targets, (double*)per_pos, outer, C, inner, ignore_index, status);
-  else ce_rows_kernel<float><<<g, 128, 0, s>>>((const float*)logits, targets, (float*)per_pos, outer, C, inner, ignore_index, status);
+namespace {
+template <typename T>
+cudaError_t ce_rows_typed(const CeProblem& c, cudaStream_t s) {
+  CeRowArgs<T> a{};
+  a.logits = reinterpret_cast<const T*>(c.logits);
+  a.idx = c.prob_targets ? nullptr : reinterpret_cast<const int64_t*>(c.targets);
+  a.prob = c.prob_targets ? reinterpret_cast<const T*>(c.targets) : nullptr;
+  a.weight = reinterpret_cast<const T*>(c.weight);
+  a.per_pos = reinterpret_cast<T*>(c.per_pos);
+  a.sel_w = reinterpret_cast<T*>(c.sel_w);
+  a.outer = c.outer; a.C = c.C; a.inner = c.inner; a.ignore_index = c.ignore_index;
+  a.smoothing = (T)c.label_smoothing;
+  a.status = c.status;
+  const int64_t n = c.outer * c.inner;
+  if (c.inner == 1 && c.C >= 512 && n <= 0x7fffffff) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const bool aligned = (reinterpret_cast<uintptr_t>(c.logits) & 15) == 0 && c.C % VEC == 0 &&
+                         (!c.prob_targets || (reinterpret_cast<uintptr_t>(c.targets) & 15) == 0) &&
+                         (!c.weight || (reinterpret_cast<uintptr_t>(c.weight) & 15) == 0);
+    const int threads = c.C >= 4096 ? 256 : 128;
+    ce_row_kernel<T, VEC><<<(unsigned)n, threads, 0, s>>>(a, aligned ? 1 : 0);
+  } else {
+    ce_pos_kernel<T><<<grid_for(n, 128), 128, 0, s>>>(a);
+  }
   return cudaGetLastError();
 }
+}  // namespace
 
-cudaError_t launch_ce_reduce(const void* per_pos, const int64_t* targets, void* out, int dtype, int64_t n,
-                             int reduction, int64_t ignore_index, cudaStream_t s) {
-  if (dtype == BG_F64) ce_reduce_kernel<double><<<1, 256, 0, s>>>((const double*)per_pos, targets, (double*)out, n, reduction, ignore_index);
-  else ce_reduce_kernel<float><<<1, 256, 0, s>>>((const float*)per_pos, targets, (float*)out, n, reduction, ignore_index);
+cudaError_t launch_ce_rows(const CeProblem& c, cudaStream_t s) {
+  if (c.outer * c.inner == 0) return cudaSuccess;
+  return c.dtype == BG_F64 ? ce_rows_typed<double>(c, s) : ce_rows_typed<float>(c, s);
+}
+
+cudaError_t launch_ce_reduce(const void* per_pos, const int64_t* targets, const void* sel_w, void* out, int dtype, int64_t n,
+                             int reduction, int64_t ignore_index, double fixed_count, cudaStream_t s) {
+  if (dtype == BG_F64)
+    ce_reduce_kernel<double><<<1, 256, 0, s>>>((const double*)per_pos, targets, (const double*)sel_w, (double*)out, n, reduction,
+                                                ignore_index, fixed_count);
+  else
+    ce_reduce_kernel<float><<<1, 256, 0, s>>>((const float*)per_pos, targets, (const float*)sel_w, (float*)out, n, reduction,
+                                               ignore_index, fixed_count);
   return cudaGetLastError();
 }
 

@@ -8,6 +8,8 @@
 
 #include <string.h>
 
+#include <atomic>
+
 namespace bg {
 namespace {
 
@@ -18,8 +20,9 @@ constexpr size_t kHeaderBytes = 256;                 // status word, kept apart 
 static __device__ __align__(256) unsigned char g_ce_scratch[kHeaderBytes + kNoAllocMaxPositions * sizeof(float)];
 
 // The array's name is a host-side stand-in, not a device address: the address each device uses is
-// looked up once per device with that device current.
-void* g_scratch_ptr[64] = {nullptr};
+// looked up once per device with that device current.  Host threads may race to fill a slot; they all store the
+// same address, atomically.
+std::atomic<void*> g_scratch_ptr[64];
 
 void set_err(char* err, size_t cap, const char* msg) {
   if (err && cap) {
@@ -38,18 +41,20 @@ extern "C" int bg_cross_entropy_noalloc(const float* logits, const int64_t* targ
   if (!logits || !targets || !out) { set_err(err, err_capacity, "CUDA bridge: cross_entropy_noalloc: null pointer"); return BG_ERR_INVALID; }
   if (rows < 0 || classes <= 0 || inner <= 0) { set_err(err, err_capacity, "CUDA bridge: cross_entropy_noalloc: bad shape"); return BG_ERR_INVALID; }
   if (reduction != 1 && reduction != 2) { set_err(err, err_capacity, "CUDA bridge: cross_entropy_noalloc: reduction must be 1 (mean) or 2 (sum)"); return BG_ERR_INVALID; }
-  const int64_t positions = rows * inner;
+  // rows * inner is compared without being formed: two huge extents must not wrap to a small product
+  const int64_t positions = rows > kNoAllocMaxPositions / inner ? kNoAllocMaxPositions + 1 : rows * inner;
   if (positions > kNoAllocMaxPositions) {
     char msg[200];
-    snprintf(msg, sizeof(msg), "CUDA bridge: cross_entropy_noalloc: %lld positions exceed the static scratch of %lld; use run_tensor_plan",
-             (long long)positions, (long long)kNoAllocMaxPositions);
+    snprintf(msg, sizeof(msg), "CUDA bridge: cross_entropy_noalloc: %lld x %lld positions exceed the static scratch of %lld; use run_tensor_plan",
+             (long long)rows, (long long)inner, (long long)kNoAllocMaxPositions);
     set_err(err, err_capacity, msg);
     return BG_ERR_UNSUPPORTED;
   }
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= 64) { set_err(err, err_capacity, "CUDA bridge: cross_entropy_noalloc: no current device"); return BG_ERR_CUDA; }
-  if (!g_scratch_ptr[dev]) {
+  void* scratch = g_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (!scratch) {
     // first call on this device: resolve the device address of the static array
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_ce_scratch);
@@ -58,18 +63,25 @@ extern "C" int bg_cross_entropy_noalloc(const float* logits, const int64_t* targ
       set_err(err, err_capacity, "CUDA bridge: cross_entropy_noalloc: cudaGetSymbolAddress failed");
       return BG_ERR_CUDA;
     }
-    g_scratch_ptr[dev] = p;
+    g_scratch_ptr[dev].store(p, std::memory_order_release);
+    scratch = p;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  unsigned char* base = reinterpret_cast<unsigned char*>(g_scratch_ptr[dev]);
+  unsigned char* base = reinterpret_cast<unsigned char*>(scratch);
   int* status = reinterpret_cast<int*>(base);
   float* per_pos = reinterpret_cast<float*>(base + kHeaderBytes);
   // the array keeps the previous call's contents: the status word must start at zero, the
   // per-position values are all rewritten before they are read
   e = cudaMemsetAsync(status, 0, sizeof(int), st);
-  if (e == cudaSuccess && positions > 0)
-    e = launch_ce_rows(logits, targets, per_pos, BG_F32, rows, classes, inner, ignore_index, status, st);
-  if (e == cudaSuccess) e = launch_ce_reduce(per_pos, targets, out, BG_F32, positions, reduction, ignore_index, st);
+  if (e == cudaSuccess && positions > 0) {
+    CeProblem c{};
+    c.logits = logits; c.targets = targets; c.per_pos = per_pos;
+    c.dtype = BG_F32;
+    c.outer = rows; c.C = classes; c.inner = inner; c.ignore_index = ignore_index;
+    c.status = status;
+    e = launch_ce_rows(c, st);
+  }
+  if (e == cudaSuccess) e = launch_ce_reduce(per_pos, targets, nullptr, out, BG_F32, positions, reduction, ignore_index, 0.0, st);
   int host_status = 0;
   if (e == cudaSuccess) e = cudaMemcpyAsync(&host_status, status, sizeof(int), cudaMemcpyDeviceToHost, st);
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);

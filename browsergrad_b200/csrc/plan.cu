@@ -613,6 +613,18 @@ void Compiler::build_views() {
         need_inputs(1);
         kind_[i] = K_VIEW;
         break;
+      case BG_OP_SLICE: {
+        need_inputs(1);
+        const Node& sn = nodes_[resolve(n.in[0])];
+        if (sn.rank != n.rank) err(BG_ERR_INVALID, "SLICE: rank changes");
+        for (int d = 0; d < n.rank; ++d) {
+          const int64_t start = n.iarg[d] & (((int64_t)1 << 40) - 1), step = n.iarg[d] >> 40;
+          if (step < 1 || n.shape[d] < 0 || (n.shape[d] > 0 && start + (n.shape[d] - 1) * step >= sn.shape[d]))
+            err(BG_ERR_INVALID, "SLICE: range exceeds the input's extent");
+        }
+        kind_[i] = K_VIEW;
+        break;
+      }
       case BG_OP_REDUCE: case BG_OP_FUSED_SOFTMAX: case BG_OP_LAYER_NORM:
         kind_[i] = K_ROW;
         v.set_dense(n.shape, n.rank);
@@ -678,6 +690,18 @@ void Compiler::analyse() {
         else err(BG_ERR_INVALID, "BROADCAST_TO: shapes are not broadcastable");
       }
       leaflike_[i] = leaflike_[src];
+    } else if (n.op == BG_OP_SLICE) {
+      if (sv.is_const) { v = sv; v.set_dense(n.shape, n.rank); leaflike_[i] = 1; }
+      else {
+        v = sv;
+        for (int d = 0; d < n.rank; ++d) {
+          const int64_t start = n.iarg[d] & (((int64_t)1 << 40) - 1), step = n.iarg[d] >> 40;
+          v.off += start * sv.stride[d];
+          v.stride[d] = sv.stride[d] * step;
+          v.shape[d] = n.shape[d];
+        }
+        leaflike_[i] = leaflike_[src];
+      }
     } else {  // RESHAPE
       if (nodes_[src].numel() != n.numel()) err(BG_ERR_INVALID, "RESHAPE: element count changes");
       if (sv.is_const) { v = sv; v.set_dense(n.shape, n.rank); leaflike_[i] = 1; }
@@ -2723,40 +2747,68 @@ void Compiler::emit_scatter(int n, int key) {
 }
 
 void Compiler::emit_ce(int n, int key) {
+  // iarg: [0] reduction (0 none, 1 mean, 2 sum), [1] ignore_index, [2] batch_rank, [3] bit 0 probability targets,
+  // bit 1 class weights as a third input; farg[0] label smoothing
   const Node& t = nodes_[n];
-  if (t.in.size() != 2) err(BG_ERR_UNSUPPORTED, "CROSS_ENTROPY: class weights are not supported");
-  const int x = resolve(t.in[0]), tg = resolve(t.in[1]);
+  const bool prob = (t.iarg[3] & 1) != 0, has_w = (t.iarg[3] & 2) != 0;
+  if (t.in.size() != (has_w ? 3u : 2u)) err(BG_ERR_INVALID, "CROSS_ENTROPY: inputs are (logits, targets[, class weights])");
+  const int x = resolve(t.in[0]), tg = resolve(t.in[1]), wn = has_w ? resolve(t.in[2]) : -1;
   const View xv = view_[x], tv = view_[tg];
-  if (tv.dtype != BG_I64) err(BG_ERR_UNSUPPORTED, "CROSS_ENTROPY: class-index (int64) targets only");
   if (xv.dtype != BG_F32 && xv.dtype != BG_F64) err(BG_ERR_UNSUPPORTED, "CROSS_ENTROPY: float32/float64 logits only");
+  if (!prob && tv.dtype != BG_I64) err(BG_ERR_UNSUPPORTED, "CROSS_ENTROPY: class-index targets must be int64");
+  if (prob && tv.dtype != xv.dtype) err(BG_ERR_UNSUPPORTED, "CROSS_ENTROPY: probability targets must have the logits' dtype");
   if (t.dtype != xv.dtype) err(BG_ERR_INVALID, "CROSS_ENTROPY: output dtype must equal the logits dtype");
   if (!xv.contiguous() || !tv.contiguous() || xv.is_const || tv.is_const) err(BG_ERR_UNSUPPORTED, "CROSS_ENTROPY: operands must be dense tensors");
   if (t.iarg[2] != 0) err(BG_ERR_UNSUPPORTED, "CROSS_ENTROPY: batch_rank must be 0");
   const int reduction = (int)t.iarg[0];
   const int64_t ignore = t.iarg[1];
+  const double smoothing = t.farg[0];
+  if (!(smoothing >= 0.0 && smoothing <= 1.0)) err(BG_ERR_INVALID, "CROSS_ENTROPY: label smoothing outside [0, 1]");
   int64_t outer, C, inner = 1;
   if (xv.rank == 1) { outer = 1; C = xv.shape[0]; }
   else { outer = xv.shape[0]; C = xv.shape[1]; for (int d = 2; d < xv.rank; ++d) inner *= xv.shape[d]; }
-  if (tv.numel() != outer * inner) err(BG_ERR_INVALID, "CROSS_ENTROPY: target shape does not match the logits");
+  if (tv.numel() != (prob ? outer * C * inner : outer * inner)) err(BG_ERR_INVALID, "CROSS_ENTROPY: target shape does not match the logits");
   if (C == 0) err(BG_ERR_INVALID, "CROSS_ENTROPY: empty class axis");
+  View wv;
+  if (has_w) {
+    wv = view_[wn];
+    if (wv.dtype != xv.dtype) err(BG_ERR_UNSUPPORTED, "CROSS_ENTROPY: class weights must have the logits' dtype");
+    if (wv.numel() != C || !wv.contiguous() || wv.is_const) err(BG_ERR_INVALID, "CROSS_ENTROPY: class weights must be a dense [C] tensor");
+  }
   own_slot(n);
   const int es = dtype_size(xv.dtype);
-  const int npos_slot = reduction == 0 ? view_[n].slot : new_slot(outer * inner * es, false, -1);
-  const int sx = xv.slot, st = tv.slot, so = view_[n].slot, dt = xv.dtype;
-  const int64_t offx = xv.off * es, offt = tv.off * 8, npos = outer * inner;
+  const int64_t npos = outer * inner;
+  const int npos_slot = reduction == 0 ? view_[n].slot : new_slot(npos * es, false, -1);
+  // the weighted mean divides by the summed weights of the valid targets: one more value per position
+  const int selw_slot = (has_w && !prob && reduction == 1) ? new_slot(npos * es, false, -1) : -1;
+  const int sx = xv.slot, st = tv.slot, sw = has_w ? wv.slot : -1, so = view_[n].slot, dt = xv.dtype;
+  const int64_t offx = xv.off * es, offt = tv.off * dtype_size(tv.dtype), offw = has_w ? wv.off * es : 0;
   cp_->uses_status = true;
   PUnit pu;
   pu.order_key = key;
   pu.dep_nodes = {x, tg};
+  if (has_w) pu.dep_nodes.push_back(wn);
   pu.out_nodes = {n};
-  pu.u.name = "cross_entropy";
+  pu.u.name = std::string("cross_entropy") + (prob ? "+prob" : "") + (has_w ? "+weight" : "") + (smoothing != 0.0 ? "+smooth" : "");
   pu.u.launches = reduction == 0 ? 1 : 2;
   if (npos_slot != so) pu.u.writes.push_back(npos_slot);
+  if (selw_slot >= 0) pu.u.writes.push_back(selw_slot);
   pu.u.fn = [=](Run& r) {
-    const int64_t* tp = reinterpret_cast<const int64_t*>(reinterpret_cast<char*>(r.ptr[st]) + offt);
-    cudaError_t e = launch_ce_rows(reinterpret_cast<char*>(r.ptr[sx]) + offx, tp, r.ptr[npos_slot], dt, outer, C, inner, ignore,
-                                   r.ctx->d_status, r.ctx->stream);
-    if (e == cudaSuccess && reduction != 0) e = launch_ce_reduce(r.ptr[npos_slot], tp, r.ptr[so], dt, npos, reduction, ignore, r.ctx->stream);
+    CeProblem c{};
+    c.logits = reinterpret_cast<char*>(r.ptr[sx]) + offx;
+    c.targets = reinterpret_cast<char*>(r.ptr[st]) + offt;
+    c.weight = sw >= 0 ? reinterpret_cast<char*>(r.ptr[sw]) + offw : nullptr;
+    c.per_pos = r.ptr[npos_slot];
+    c.sel_w = selw_slot >= 0 ? r.ptr[selw_slot] : nullptr;
+    c.dtype = dt;
+    c.prob_targets = prob ? 1 : 0;
+    c.outer = outer; c.C = C; c.inner = inner; c.ignore_index = ignore;
+    c.label_smoothing = smoothing;
+    c.status = r.ctx->d_status;
+    cudaError_t e = launch_ce_rows(c, r.ctx->stream);
+    if (e == cudaSuccess && reduction != 0)
+      e = launch_ce_reduce(c.per_pos, prob ? nullptr : reinterpret_cast<const int64_t*>(c.targets), c.sel_w, r.ptr[so], dt, npos, reduction,
+                           ignore, (double)npos, r.ctx->stream);
     return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "cross entropy launch");
   };
   add_unit(std::move(pu));

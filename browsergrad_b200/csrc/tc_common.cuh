@@ -171,6 +171,16 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 
+// True in exactly one lane of a converged warp.  The MMA-issuing warps run their loops with all 32 lanes (addresses,
+// descriptors and loop counters are then warp-uniform values the compiler can keep in uniform registers) and let
+// the elected lane issue the tcgen05 / barrier instructions; a loop that only one lane runs pays a transfer into the
+// uniform register file for every operand of every tcgen05.mma.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }

@@ -456,6 +456,27 @@ class Tensor:
                                {"dim": axis}))
 
 
+    def narrow(self, axis: int, start: int, length: int) -> "Tensor":
+        """``NARROW`` node as the reference's derivative rules emit it (_vjp.py:383, :426; contract
+        _framework_contracts.py:5345-5383): ``length`` consecutive positions of ``axis`` from ``start``."""
+        axis = int(axis)
+        if self.ndim == 0 or axis < 0 or axis >= self.ndim:
+            raise ValueError("narrow: axis out of range")
+        start, length = int(start), int(length)
+        if start < 0 or length < 0 or start + length > self.shape[axis]:
+            raise ValueError("narrow: range exceeds the axis extent")
+        shape = self.shape[:axis] + (length,) + self.shape[axis + 1:]
+        return self._wrap(Node("NARROW", (self._uop,), shape, self.dtype, {"axis": axis, "start": start, "length": length}))
+
+    def slice(self, slices: Sequence[slice]) -> "Tensor":
+        """``SLICE`` node (_ir.py:131, emitted by the PAD derivative rule, _vjp.py:455-472): NumPy basic slicing with
+        one ``slice`` per leading axis."""
+        slices = tuple(slices)
+        if len(slices) > self.ndim or any(not isinstance(sl, slice) for sl in slices):
+            raise ValueError("slice: one slice object per leading axis")
+        shape = tuple(len(range(*sl.indices(d))) for sl, d in zip(slices, self.shape)) + self.shape[len(slices):]
+        return self._wrap(Node("SLICE", (self._uop,), shape, self.dtype, {"slices": slices}))
+
     def scatter(self, dim: int, index: "Tensor", src: Any) -> "Tensor":
         """``SCATTER`` node (_tensor_proxy.py:2703-2751): a copy of ``self`` with ``src`` stored at the places
         ``index`` names along ``dim``.  ``src`` is a tensor of the index's shape and the target's dtype, or a
@@ -562,25 +583,38 @@ def layer_norm(x: Tensor, normalized_shape: Sequence[int], weight: Optional[Tens
     return Tensor(Node("LAYER_NORM", (x._uop, w._uop, b._uop), x.shape, x.dtype, arg), x._store)
 
 
-def cross_entropy(logits: Tensor, target: Tensor, reduction: str = "mean",
-                  ignore_index: int = -100) -> Tensor:
-    """Class-index cross entropy over axis 1 of ``[N, C, ...]`` logits.
+def cross_entropy(logits: Tensor, target: Tensor, weight: Optional[Tensor] = None, reduction: str = "mean",
+                  ignore_index: int = -100, label_smoothing: float = 0.0) -> Tensor:
+    """Cross entropy over axis 1 of ``[N, C, ...]`` logits (axis 0 of ``[C]``), for int64 class-index targets or
+    probability targets of the logits' shape, with optional class weights ``[C]`` and label smoothing.
 
-    Mirrors the node the reference emits for index targets without class weights or label
-    smoothing (_functional.py:178-262; contract inference in _framework_contracts.py).
+    Mirrors the node the reference emits (_functional.py:178-262; contract inference
+    _framework_contracts.py:3470-3610): a target whose shape equals the logits' selects the
+    probability mode; the weights travel as a third input.
     """
     if reduction not in ("mean", "sum", "none"):
         raise ValueError(f"cross_entropy: reduction {reduction!r}")
-    if target.dtype != "int64" or logits.ndim < 2:
-        raise ValueError("cross_entropy: int64 class-index targets and [N, C, ...] logits")
-    if target.shape != logits.shape[:1] + logits.shape[2:]:
-        raise ValueError("cross_entropy: target shape does not match logits")
-    out_shape = target.shape if reduction == "none" else ()
-    out_dtype = logits.dtype
+    if logits.ndim < 1:
+        raise ValueError("cross_entropy: logits need a class axis")
+    mode = "probabilities" if target.shape == logits.shape else "indices"
+    positions = logits.shape[:1] + logits.shape[2:] if logits.ndim > 1 else ()
+    if mode == "indices":
+        if target.dtype != "int64":
+            raise ValueError("cross_entropy: class-index targets must be int64")
+        if target.shape != positions:
+            raise ValueError("cross_entropy: target shape does not match logits")
+    elif target.dtype != logits.dtype:
+        raise ValueError("cross_entropy: probability targets must have the logits' dtype")
+    n_class = logits.shape[1] if logits.ndim > 1 else logits.shape[0]
+    if weight is not None and (weight.shape != (n_class,) or weight.dtype != logits.dtype):
+        raise ValueError("cross_entropy: weight must be a [C] tensor of the logits' dtype")
+    if not 0.0 <= float(label_smoothing) <= 1.0:
+        raise ValueError("cross_entropy: label_smoothing must be in [0, 1]")
+    out_shape = positions if reduction == "none" else ()
     arg = {"reduction": reduction, "batch_rank": 0, "ignore_index": int(ignore_index),
-           "has_weight": False, "label_smoothing": 0.0, "target_mode": "indices"}
-    return Tensor(Node("CROSS_ENTROPY", (logits._uop, target._uop), out_shape, out_dtype, arg),
-                  logits._store)
+           "has_weight": weight is not None, "label_smoothing": float(label_smoothing), "target_mode": mode}
+    inputs = (logits._uop, target._uop) + ((weight._uop,) if weight is not None else ())
+    return Tensor(Node("CROSS_ENTROPY", inputs, out_shape, logits.dtype, arg), logits._store)
 
 
 def scaled_dot_product_attention(q: Tensor, k: Tensor, v: Tensor, attn_mask: Any = None,
@@ -719,3 +753,11 @@ def toposort(root: Node) -> list:
         order.append(node)
         stack.pop()
     return order
+
+
+def narrow(t: Tensor, axis: int, start: int, length: int) -> Tensor:
+    return t.narrow(axis, start, length)
+
+
+def take_slice(t: Tensor, slices: Sequence[Any]) -> Tensor:
+    return t.slice(slices)

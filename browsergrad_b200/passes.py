@@ -256,7 +256,9 @@ def lower_composites(root: Any) -> Any:
     * ``SORT_VALUES`` / ``TOPK_VALUES`` -> ``INDEX`` along the ordering axis (_realize.py:1149-1176);
     * ``PROD`` -> ``REDUCE`` with the product combiner (``np.prod(dtype=...)``, _realize.py:335-343);
     * ``PAD`` -> one ``CONCAT`` per padded axis whose outer inputs are the broadcast fill constant
-      (``np.pad(mode="constant")``, _realize.py:1131-1140).
+      (``np.pad(mode="constant")``, _realize.py:1131-1140);
+    * ``NARROW(x; axis, start, length)`` -> ``SLICE`` with one slice per axis (_realize.py:309-314): a strided
+      view on the device, where the reference copies.
     """
     def make(like: Any, op: str, inputs: tuple, shape: tuple, dtype: str, arg: Any) -> Any:
         return type(like)(op=op, inputs=inputs, shape=tuple(shape), dtype=dtype, arg=arg)
@@ -318,6 +320,11 @@ def lower_composites(root: Any) -> Any:
                 shape[axis] += int(lo) + int(hi)
                 out = make(node, "CONCAT", tuple(parts), tuple(shape), node.dtype, {"axis": axis})
             return out
+        if node.op == "NARROW":
+            (x,) = ins
+            axis, start, length = int(node.arg["axis"]) % max(len(x.shape), 1), int(node.arg["start"]), int(node.arg["length"])
+            slices = tuple(slice(start, start + length) if d == axis else slice(None) for d in range(len(x.shape)))
+            return make(node, "SLICE", (x,), node.shape, node.dtype, {"slices": slices})
         if node.op == "STACK":
             axis = int(node.arg["axis"])
             parts = []
@@ -343,7 +350,7 @@ def lower_composites(root: Any) -> Any:
             a = make(node, "RESHAPE", (x,), split, node.dtype, {"new_shape": split})
             b = make(node, "BROADCAST_TO", (a,), wide, node.dtype, {"shape": wide})
             return make(node, "RESHAPE", (b,), node.shape, node.dtype, {"new_shape": tuple(node.shape)})
-        if node.op in ("PERMUTE", "RESHAPE", "BROADCAST_TO", "LOAD") and len(ins) == 1 and ins[0].dtype != node.dtype:
+        if node.op in ("PERMUTE", "RESHAPE", "BROADCAST_TO", "LOAD", "SLICE") and len(ins) == 1 and ins[0].dtype != node.dtype:
             # A view built outside the autocast block keeps the dtype its input had before the cast pass
             # narrowed it; the reference's realizer hands the narrow array through unchanged
             # (_realize.py:1114-1121), so the view carries its input's real dtype here.

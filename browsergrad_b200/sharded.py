@@ -79,27 +79,35 @@ def gather_rows(local: np.ndarray, total_rows: int, group: Any = None, device: O
 
 
 def combine_mean(local_mean: np.ndarray, local_count: int, group: Any = None, device: Optional[str] = None) -> np.ndarray:
-    """Global mean from per-rank means over ``local_count`` valid positions (one all-reduce of
-    (sum, count)).  The summation order differs from a single-device reduction: tolerance, not bit-exact."""
+    """Global mean from per-rank means over ``local_count`` contributing positions (one all-reduce of
+    (sum, count)).  A rank with no contributing position (its local mean is 0/0 = NaN) adds (0, 0); the
+    result is NaN only when no rank contributes, as a single-device mean over nothing is.  The summation
+    order differs from a single-device reduction: tolerance, not bit-exact."""
     import torch
     dist = _dist()
-    pair = torch.tensor([float(local_mean) * local_count, float(local_count)], dtype=torch.float64)
+    local_sum = float(local_mean) * local_count if local_count > 0 else 0.0
+    pair = torch.tensor([local_sum, float(local_count)], dtype=torch.float64)
     if device is not None:
         pair = pair.to(device)
     dist.all_reduce(pair, op=dist.ReduceOp.SUM, group=group)
     pair = pair.cpu()
-    return np.asarray(pair[0].item() / pair[1].item(), dtype=np.asarray(local_mean).dtype)
+    total, count = pair[0].item(), pair[1].item()
+    return np.asarray(total / count if count > 0 else float("nan"), dtype=np.asarray(local_mean).dtype)
 
 
 def realize_sharded(build: Callable[[Dict[str, Any]], Any], arrays: Dict[str, np.ndarray], sharded_keys: Sequence[str],
                     realize: Callable[[Any], np.ndarray], make_tensor: Callable[[np.ndarray], Any], *,
                     gather: bool = True, reduce: str = "rows", group: Any = None,
-                    device: Optional[str] = None) -> np.ndarray:
+                    device: Optional[str] = None,
+                    valid_count: Optional[Callable[[Dict[str, np.ndarray]], int]] = None) -> np.ndarray:
     """Run ``build`` on this rank's shard and combine the results.
 
     ``realize`` maps a graph tensor to an ndarray (``realize_cuda`` in production), ``make_tensor``
     wraps an ndarray as a leaf.  ``reduce`` = "rows" concatenates row blocks (``gather=False`` keeps
-    the local block), "mean" combines a mean-reduced scalar.
+    the local block), "mean" combines a mean-reduced scalar from per-rank (sum, count) pairs.  The count
+    is what the local mean divided by: ``valid_count(local_arrays)`` when given -- for cross entropy the
+    number of targets that differ from ``ignore_index`` (packages/browsergrad-jit/src/python/
+    _framework_contracts.py:3725-3753 divides by exactly that) -- else the shard's row count.
     """
     dist = _dist()
     world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -113,7 +121,8 @@ def realize_sharded(build: Callable[[Dict[str, Any]], Any], arrays: Dict[str, np
         return out
     if reduce == "mean":
         lo, hi = shard_bounds(total, world, rank)
-        return combine_mean(out, hi - lo, group, device)
+        count = int(valid_count(local)) if valid_count is not None else hi - lo
+        return combine_mean(out, count, group, device)
     if not gather:
         return out
     return gather_rows(out, total, group, device)

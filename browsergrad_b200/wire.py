@@ -184,14 +184,34 @@ def encode_plan(plan: Dict[str, Any], permute_axes: Optional[Dict[int, Tuple[int
             st.iarg[1] = int(arg["k"])
             st.iarg[2] = 1 if arg.get("largest", True) else 0
             st.iarg[3] = 1 if arg.get("sorted", True) else 0
+        elif op == "SLICE":
+            src_shape = tuple(int(d) for d in steps_in[ins[0]]["shape"])
+            slices = tuple(arg["slices"])
+            if len(slices) > len(src_shape) or any(not isinstance(sl, slice) for sl in slices):
+                raise JitNotImplementedError("CUDA bridge: SLICE takes one slice object per leading axis (no integers, "
+                                             "ellipsis or new axes). Fall back to bg.realize() (NumPy).")
+            slices = slices + (slice(None),) * (len(src_shape) - len(slices))
+            for d, (sl, extent) in enumerate(zip(slices, src_shape)):
+                start, stop, step = sl.indices(extent)
+                if step < 1:
+                    raise JitNotImplementedError("CUDA bridge: SLICE with a negative step is not supported. "
+                                                 "Fall back to bg.realize() (NumPy).")
+                length = max(0, (stop - start + step - 1) // step)
+                if d >= len(shape) or shape[d] != length:
+                    raise KernelError(f"CUDA bridge: SLICE: declared shape {shape} does not match the slices", 1)
+                st.iarg[d] = (start if length else 0) + (step << 40)
         elif op == "CROSS_ENTROPY":
-            if arg.get("target_mode", "indices") != "indices" or arg.get("has_weight") or arg.get("label_smoothing"):
-                raise JitNotImplementedError(
-                    "CUDA bridge: CROSS_ENTROPY with class weights, label smoothing or probability targets "
-                    "is not supported. Fall back to bg.realize() (NumPy).")
+            mode = arg.get("target_mode", "indices")
+            if mode not in ("indices", "probabilities"):
+                raise KernelError(f"CUDA bridge: CROSS_ENTROPY: unknown target_mode {mode!r}", 1)
+            has_weight = bool(arg.get("has_weight"))
+            if len(ins) != (3 if has_weight else 2):
+                raise KernelError("CUDA bridge: CROSS_ENTROPY: inputs are (logits, targets[, class weights])", 1)
             st.iarg[0] = {"none": 0, "mean": 1, "sum": 2}[arg["reduction"]]
             st.iarg[1] = int(arg["ignore_index"])
             st.iarg[2] = int(arg.get("batch_rank", 0))
+            st.iarg[3] = (1 if mode == "probabilities" else 0) | (2 if has_weight else 0)
+            st.farg[0] = float(arg.get("label_smoothing", 0.0) or 0.0)
         elif op == "ATTENTION_FORWARD":
             st.farg[0] = float(arg["scale"])
         elif op == "FUSED_ELEMENTWISE":

@@ -78,7 +78,11 @@ typedef enum bg_opcode {
      of the target with source values stored at the indexed places.  An index outside the axis or two
      index entries naming one destination end the plan with BG_ERR_INDEX_RANGE, as the reference raises. */
   BG_OP_SCATTER = 35,
-  BG_OP_COUNT = 36
+  /* Basic slicing x[start:stop:step, ...] (_realize.py:1124-1128; NARROW, _realize.py:309-314, arrives as the same
+     opcode): a strided view of the input, iarg[d] = start_d + (step_d << 40) per input axis (start >= 0,
+     step >= 1, the declared shape gives the extents).  Never a copy unless the view is the plan's root. */
+  BG_OP_SLICE = 36,
+  BG_OP_COUNT = 37
 } bg_opcode;
 
 typedef enum bg_cmp { BG_CMP_EQ = 0, BG_CMP_NE = 1, BG_CMP_LT = 2, BG_CMP_LE = 3,
@@ -101,8 +105,9 @@ typedef enum bg_reduce { BG_RED_SUM = 0, BG_RED_MAX = 1, BG_RED_MIN = 2, BG_RED_
  *   FUSED_SOFTMAX    iarg[0] = axis (non-negative)
  *   LAYER_NORM       iarg[0] = rows, iarg[1] = cols, farg[0] = eps
  *   INDEX            iarg[0] = gather dimension
- *   CROSS_ENTROPY    iarg[0] = 0 none / 1 mean / 2 sum; iarg[1] = ignore_index;
- *                    iarg[2] = batch_rank (class-index targets, no weights, no smoothing)
+ *   CROSS_ENTROPY    iarg[0] = 0 none / 1 mean / 2 sum; iarg[1] = ignore_index; iarg[2] = batch_rank (0);
+ *                    iarg[3] = bit 0 probability targets (else int64 class indices), bit 1 class weights
+ *                    as a third input; farg[0] = label smoothing
  *   ATTENTION_FORWARD farg[0] = scale
  *   FUSED_ELEMENTWISE ext[ext_offset .. +3*ext_count) = (bg_opcode, lhs_ref, rhs_ref) triples;
  *                    refs < 0 name input -ref-1, refs >= 0 an earlier triple

@@ -180,6 +180,17 @@ def _h_stack(node, vt, store):  # _realize.py:299-306
     return np.array(np.stack(arrays, axis=int(node.arg["axis"])), dtype=np.dtype(node.dtype), copy=True)
 
 
+def _h_narrow(node, vt, store):  # _realize.py:309-314
+    a = node.arg
+    index = [slice(None)] * len(node.shape)
+    index[a["axis"]] = slice(a["start"], a["start"] + a["length"])
+    return np.array(vt[id(node.inputs[0])][tuple(index)], dtype=np.dtype(node.dtype), copy=True)
+
+
+def _h_slice(node, vt, store):  # _realize.py:1124-1128
+    return vt[id(node.inputs[0])][tuple(node.arg["slices"])]
+
+
 def _h_tril(node, vt, store):  # _realize.py:317-320
     return np.array(np.tril(_in(node, vt, 0), k=int(node.arg["diagonal"])), dtype=np.dtype(node.dtype), copy=True)
 
@@ -329,17 +340,19 @@ def _h_fused_softmax(node, vt, store):  # _realize.py:1603-1614
 
 
 def _h_cross_entropy(node, vt, store):
-    """Index-target branch of ``execute_cross_entropy_arrays``
-    (_framework_contracts.py:3644-3664 log-probabilities, :3667-3702 selection,
-    :3725-3753 reduction, :3756-3835 driver), without class weights or label smoothing."""
+    """``execute_cross_entropy_arrays`` (_framework_contracts.py:3756-3835): log-probabilities (:3644-3664),
+    class-index selection with optional class weights (:3667-3702), probability targets and label smoothing
+    (:3776-3824), reduction (:3725-3753)."""
     arg = node.arg
-    if arg.get("target_mode") != "indices" or arg.get("has_weight") or arg.get("label_smoothing"):
-        raise OracleError("cross_entropy: only unweighted class-index targets are restated")
+    mode = arg.get("target_mode", "indices")
+    has_weight = bool(arg.get("has_weight"))
+    eps = float(arg.get("label_smoothing", 0.0) or 0.0)
     logits_in, targets = _in(node, vt, 0), _in(node, vt, 1)
     batch_rank = int(arg.get("batch_rank", 0))
     class_axis = batch_rank + 1 if logits_in.ndim > batch_rank + 1 else batch_rank
     dtype = np.dtype("float32" if node.dtype == "float16" else node.dtype)  # :3613-3616
     logits = logits_in.astype(dtype, copy=False)
+    n_class = logits.shape[class_axis]
     maximum = np.max(logits, axis=class_axis, keepdims=True)
     shifted = np.empty(logits.shape, dtype=dtype)
     np.subtract(logits, maximum, out=shifted)
@@ -349,21 +362,50 @@ def _h_cross_entropy(node, vt, store):
     norm = exps.sum(axis=class_axis, keepdims=True, dtype=dtype)
     with np.errstate(divide="ignore", invalid="ignore"):
         np.log(norm, out=norm)
-    np.subtract(shifted, norm, out=shifted)
-    ignore = int(arg["ignore_index"])
-    valid = targets != ignore
-    n_class = logits.shape[class_axis]
-    if bool(valid.any()):
-        lo = int(np.min(targets, where=valid, initial=0))
-        hi = int(np.max(targets, where=valid, initial=0))
-        if lo < 0 or hi >= n_class:
-            raise OracleError(f"cross_entropy: target values must be in [0, {n_class})")
-    safe = np.where(valid, targets, 0)
-    sel_w = valid.astype(dtype, copy=False)
-    class_last = np.moveaxis(shifted, class_axis, -1)
-    per = np.take_along_axis(class_last, safe[..., None], axis=-1)[..., 0]
-    np.negative(per, out=per)
-    np.copyto(per, 0.0, where=~valid)
+    np.subtract(shifted, norm, out=shifted)          # log-probabilities
+    weight_view = None
+    if has_weight:                                   # class weights broadcast along the class axis
+        w = _in(node, vt, 2).astype(dtype, copy=False)
+        shape = [1] * logits.ndim
+        shape[class_axis] = n_class
+        weight_view = w.reshape(shape)
+    valid = sel_w = None
+    if mode == "probabilities":
+        coef = targets.astype(dtype, copy=False)
+        if eps != 0.0:
+            coef = np.array(coef, dtype=dtype, copy=True)
+            np.multiply(coef, 1.0 - eps, out=coef)
+            np.add(coef, eps / n_class, out=coef)
+        if weight_view is not None:
+            coef = np.multiply(coef, weight_view)
+        per = np.multiply(shifted, coef).sum(axis=class_axis, dtype=dtype)
+        np.negative(per, out=per)
+    else:
+        ignore = int(arg["ignore_index"])
+        valid = targets != ignore
+        if bool(valid.any()):
+            lo = int(np.min(targets, where=valid, initial=0))
+            hi = int(np.max(targets, where=valid, initial=0))
+            if lo < 0 or hi >= n_class:
+                raise OracleError(f"cross_entropy: target values must be in [0, {n_class})")
+        safe = np.where(valid, targets, 0)
+        if has_weight:
+            sel_w = np.where(valid, _in(node, vt, 2).astype(dtype, copy=False)[safe], 0.0)
+        else:
+            sel_w = valid.astype(dtype, copy=False)
+        class_last = np.moveaxis(shifted, class_axis, -1)
+        per = np.take_along_axis(class_last, safe[..., None], axis=-1)[..., 0]
+        np.negative(per, out=per)
+        if has_weight:
+            np.multiply(per, sel_w, out=per)
+        if eps != 0.0:
+            src = shifted if weight_view is None else np.multiply(shifted, weight_view)
+            smooth = src.sum(axis=class_axis, dtype=dtype)
+            np.negative(smooth, out=smooth)
+            np.multiply(per, 1.0 - eps, out=per)
+            np.multiply(smooth, eps / n_class, out=smooth)
+            np.add(per, smooth, out=per)
+        np.copyto(per, 0.0, where=~valid)
     red = arg["reduction"]
     if red == "none":
         result = per
@@ -373,7 +415,13 @@ def _h_cross_entropy(node, vt, store):
         if red == "sum":
             result = num
         else:
-            den = valid.sum(axis=axes) if axes else np.asarray(valid)
+            if mode == "indices":
+                src = sel_w if has_weight else valid
+                den = src.sum(axis=axes) if axes else np.asarray(src)
+            else:
+                den = 1
+                for d in per.shape[batch_rank:]:
+                    den *= d
             with np.errstate(divide="ignore", invalid="ignore"):
                 result = np.divide(num, den)
     return np.array(result, dtype=np.dtype(node.dtype), copy=True)
@@ -423,7 +471,7 @@ _DISPATCH: Dict[str, Callable] = {
     "PERMUTE": lambda n, vt, s: np.transpose(_in(n, vt, 0), axes=n.arg["axes"]),   # :1119-1121
     "WHERE": _h_where,
     "CLAMP": _h_clamp, "FLIP": _h_flip, "CUMSUM": _h_cumsum, "CONCAT": _h_concat, "STACK": _h_stack,
-    "TRIL": _h_tril, "TRIU": _h_triu, "VAR": _h_var, "PROD": _h_prod, "PAD": _h_pad, "SCATTER": _h_scatter, "REPEAT": _h_repeat, "REPEAT_INTERLEAVE": _h_repeat_interleave,
+    "NARROW": _h_narrow, "SLICE": _h_slice, "TRIL": _h_tril, "TRIU": _h_triu, "VAR": _h_var, "PROD": _h_prod, "PAD": _h_pad, "SCATTER": _h_scatter, "REPEAT": _h_repeat, "REPEAT_INTERLEAVE": _h_repeat_interleave,
     "SORT_INDICES": _h_sort_indices, "SORT_VALUES": _h_take_along, "TOPK_INDICES": _h_topk_indices, "TOPK_VALUES": _h_take_along,
     "INDEX": _h_index,
     "BROADCAST_TO": _h_broadcast_to,

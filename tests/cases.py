@@ -30,6 +30,22 @@ class RefApi:
         self.cat, self.stack, self.cumsum = bg.cat, bg.stack, bg.cumsum
         self.sort, self.topk = bg.sort, bg.topk
         self.pad = F.pad
+        self._bg = bg
+
+    def _raw(self, t: Any, op: str, shape: tuple, arg: Any) -> Any:
+        """A node no public builder of the reference emits (its derivative rules do, _vjp.py:383-472), built with the
+        reference's own ``UOp`` constructor and wrapped like any other recorded value."""
+        node = self._bg._ir.UOp(op=op, inputs=(t._uop,), shape=tuple(shape), dtype=t._uop.dtype, arg=arg)
+        return type(t)(node, t._session)
+
+    def narrow(self, t: Any, axis: int, start: int, length: int) -> Any:
+        shape = t.shape[:axis] + (length,) + t.shape[axis + 1:]
+        return self._raw(t, "NARROW", shape, {"axis": axis, "start": start, "length": length})
+
+    def take_slice(self, t: Any, slices: Any) -> Any:
+        slices = tuple(slices)
+        shape = tuple(len(range(*sl.indices(d))) for sl, d in zip(slices, t.shape)) + tuple(t.shape[len(slices):])
+        return self._raw(t, "SLICE", shape, {"slices": slices})
 
 
 def canonical_arg(op: str, arg: Any) -> Any:
@@ -39,6 +55,8 @@ def canonical_arg(op: str, arg: Any) -> Any:
         return {k: canonical_arg("", v) for k, v in sorted(arg.items()) if k != "vjp_of"}
     if isinstance(arg, (tuple, list)):
         return [canonical_arg("", v) for v in arg]
+    if isinstance(arg, slice):
+        return ["slice", arg.start, arg.stop, arg.step]
     if isinstance(arg, float):
         return repr(arg)
     if isinstance(arg, (np.integer,)):
@@ -61,6 +79,7 @@ class Case:
     kind: str = "float"          # "float" (tolerance) or "exact" (bit-exact)
     rtol: float = 1e-5
     reference_has_it: bool = True
+    floor_bits: Any = None       # overrides the k of the element-wise gate (tests/util.py); None = from the graph
 
 
 def _rng(seed: int) -> np.random.Generator:
@@ -97,7 +116,25 @@ def _misc_inputs() -> Dict[str, np.ndarray]:
         "src_part": r.standard_normal((6, 3, 33), dtype=np.float32),
         "logits3": r.standard_normal((4, 7, 5), dtype=np.float32),
         "tgt3": r.integers(0, 7, (4, 5), dtype=np.int64),
+        "cw": np.linspace(0.25, 2.0, 7, dtype=np.float32),
+        "probs": _softmax_rows(r.standard_normal((12, 7), dtype=np.float32)),
     }
+
+
+def _softmax_rows(a: np.ndarray) -> np.ndarray:
+    e = np.exp(a - a.max(axis=1, keepdims=True))
+    return (e / e.sum(axis=1, keepdims=True)).astype(a.dtype)
+
+
+def _long_ce_inputs(rows: int, classes: int, dtype: Any = np.float32) -> Callable[[], Dict[str, np.ndarray]]:
+    def make() -> Dict[str, np.ndarray]:
+        r = _rng(700 + classes)
+        tgt = r.integers(0, classes, (rows,), dtype=np.int64)
+        tgt[rows // 2] = -100
+        return {"logits": (r.standard_normal((rows, classes)) * 4).astype(dtype), "tgt": tgt,
+                "cw": r.uniform(0.5, 1.5, (classes,)).astype(dtype),
+                "probs": _softmax_rows(r.standard_normal((rows, classes)).astype(dtype))}
+    return make
 
 
 def _attn_small(b: int, h: int, s: int, d: int) -> Callable[[], Dict[str, np.ndarray]]:
@@ -399,7 +436,27 @@ CASES: Dict[str, Case] = {
     "ce_none": Case(_misc_inputs,
                     lambda api, t, raw: api.cross_entropy(t["logits"], t["tgt"], reduction="none")),
     "ce_spatial": Case(_misc_inputs, lambda api, t, raw: api.cross_entropy(t["logits3"], t["tgt3"])),
-    "tanh": Case(_misc_inputs, lambda api, t, raw: api.tanh(t["x"])),
+    # (e^x - e^-x) / (e^x + e^-x): the numerator cancels near zero, so small outputs carry the absolute error of exp
+    # class weights, label smoothing, probability targets (_framework_contracts.py:3756-3835)
+    "ce_weight_mean": Case(_misc_inputs, lambda api, t, raw: api.cross_entropy(t["logits"], t["tgt"], weight=t["cw"])),
+    "ce_weight_sum": Case(_misc_inputs, lambda api, t, raw: api.cross_entropy(t["logits"], t["tgt"], weight=t["cw"], reduction="sum")),
+    "ce_weight_none": Case(_misc_inputs, lambda api, t, raw: api.cross_entropy(t["logits"], t["tgt"], weight=t["cw"], reduction="none")),
+    "ce_smooth": Case(_misc_inputs, lambda api, t, raw: api.cross_entropy(t["logits"], t["tgt"], label_smoothing=0.1)),
+    "ce_weight_smooth": Case(_misc_inputs, lambda api, t, raw: api.cross_entropy(t["logits"], t["tgt"], weight=t["cw"], reduction="sum",
+                                                                                 label_smoothing=0.25)),
+    "ce_prob": Case(_misc_inputs, lambda api, t, raw: api.cross_entropy(t["logits"], t["probs"])),
+    "ce_prob_smooth_weight": Case(_misc_inputs, lambda api, t, raw: api.cross_entropy(t["logits"], t["probs"], weight=t["cw"],
+                                                                                      reduction="none", label_smoothing=0.2)),
+    "ce_spatial_weight": Case(_misc_inputs, lambda api, t, raw: api.cross_entropy(t["logits3"], t["tgt3"], weight=t["cw"])),
+    # long contiguous class axes: one CTA per position (vector loads; a class count that is no multiple of four;
+    # float64; every optional term at once)
+    "ce_long_row": Case(_long_ce_inputs(6, 4100), lambda api, t, raw: api.cross_entropy(t["logits"], t["tgt"], reduction="none")),
+    "ce_long_row_odd": Case(_long_ce_inputs(5, 1030), lambda api, t, raw: api.cross_entropy(t["logits"], t["tgt"], label_smoothing=0.1)),
+    "ce_long_row_f64": Case(_long_ce_inputs(3, 2050, np.float64),
+                            lambda api, t, raw: api.cross_entropy(t["logits"], t["tgt"], weight=t["cw"], label_smoothing=0.3)),
+    "ce_long_prob": Case(_long_ce_inputs(4, 4096), lambda api, t, raw: api.cross_entropy(t["logits"], t["probs"], weight=t["cw"],
+                                                                                        label_smoothing=0.05)),
+    "tanh": Case(_misc_inputs, lambda api, t, raw: api.tanh(t["x"]), floor_bits=0),
     "scalar_only": Case(_misc_inputs, lambda api, t, raw: t["row"].sum() * 2.0 + 1.0),
     "empty_rows": Case(lambda: {"a": np.zeros((0, 8), np.float32), "b": np.ones((0, 8), np.float32)},
                        lambda api, t, raw: api.relu(t["a"] * t["b"])),
@@ -410,6 +467,21 @@ CASES: Dict[str, Case] = {
     "scatter_empty_index": Case(lambda: {"a": np.arange(12, dtype=np.float32).reshape(3, 4), "i": np.zeros((0, 4), np.int64),
                                          "s": np.zeros((0, 4), np.float32)},
                                 lambda api, t, raw: t["a"].scatter(0, t["i"], t["s"]), kind="exact"),
+    # NARROW / SLICE: strided views on the device, built through the node constructor (no public builder emits them)
+    "narrow_rows_chain": Case(_misc_inputs, lambda api, t, raw: api.relu(api.narrow(t["x"], 0, 2, 3) * 2.0)),
+    "narrow_last_softmax": Case(_misc_inputs, lambda api, t, raw: api.softmax(api.narrow(t["x"], 2, 1, 32), dim=-1)),
+    "narrow_root_copy": Case(_misc_inputs, lambda api, t, raw: api.narrow(t["x"], 1, 1, 3), kind="exact"),
+    "narrow_int": Case(_misc_inputs, lambda api, t, raw: api.narrow(t["i"], 2, 5, 20),
+                       kind="exact"),
+    "narrow_empty": Case(_misc_inputs, lambda api, t, raw: api.narrow(t["x"], 1, 2, 0), kind="exact"),
+    "slice_steps_root": Case(_misc_inputs, lambda api, t, raw: api.take_slice(t["x"], (slice(1, 6, 2), slice(None), slice(3, 33, 3))),
+                             kind="exact"),
+    "slice_rows_matmul": Case(_misc_inputs, lambda api, t, raw: api.take_slice(t["m79"], (slice(2, 7),)) @ t["bn"]),
+    "slice_mid_rowsum": Case(_misc_inputs, lambda api, t, raw: api.take_slice(t["x"], (slice(None), slice(1, 4))).sum(-1)),
+    "slice_then_reshape": Case(_misc_inputs, lambda api, t, raw: api.take_slice(t["x"], (slice(None), slice(0, 5, 2))).reshape(6, 99) + 1.0),
+    "slice_undoes_pad": Case(_misc_inputs, lambda api, t, raw: api.take_slice(api.pad(t["x"], (1, 2), value=0.5),
+                                                                          (slice(None), slice(None), slice(1, 34))), kind="exact"),
+    "slice_of_permuted": Case(_misc_inputs, lambda api, t, raw: api.exp(api.take_slice(t["x"].permute(2, 0, 1), (slice(4, 20, 5), slice(1, 5))) * 0.5)),
     "single_element": Case(lambda: {"a": np.array([[2.5]], np.float32)},
                            lambda api, t, raw: api.softmax(t["a"] * t["a"], dim=-1)),
 }

@@ -30,4 +30,5 @@ def pytest_sessionfinish(session, exitstatus):
         return
     import numpy as np
     with open(path, "w") as fh:
-        json.dump({"numpy": np.__version__, "floor_bits": util.FLOOR_BITS, "comparisons": util.ERROR_LOG}, fh, indent=1)
+        json.dump({"numpy": np.__version__, "floor_bits": {"pointwise": util.FLOOR_BITS_POINTWISE, "contraction": util.FLOOR_BITS_CONTRACTION},
+                   "comparisons": util.ERROR_LOG}, fh, indent=1)

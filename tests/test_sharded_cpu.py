@@ -37,6 +37,13 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
         mlp = configs.mlp_inputs(batch=10)
         loss = sharded.realize_sharded(lambda t: configs.mlp_loss(graph, t), mlp, ["x", "y"], realize, make, reduce="mean")
         np.save(os.path.join(out_dir, f"loss_{rank}.npy"), loss)
+        # the same with ignored targets: rank 1's shard (rows 5..9) is all ignore_index, rank 0 holds two of them
+        ign = configs.mlp_inputs(batch=10)
+        ign["y"] = ign["y"].copy()
+        ign["y"][[1, 3, 5, 6, 7, 8, 9]] = -100
+        loss_ign = sharded.realize_sharded(lambda t: configs.mlp_loss(graph, t), ign, ["x", "y"], realize, make, reduce="mean",
+                                           valid_count=lambda local: int((local["y"] != -100).sum()))
+        np.save(os.path.join(out_dir, f"loss_ign_{rank}.npy"), loss_ign)
         # bool output travels as bytes
         got_b = sharded.realize_sharded(lambda t: t["a"] > t["b"], arrays, list("abcd"), realize, make)
         np.save(os.path.join(out_dir, f"bool_{rank}.npy"), got_b)
@@ -69,7 +76,15 @@ def test_two_rank_gloo_matches_single_process(tmp_path):
     mlp = configs.mlp_inputs(batch=10)
     tm = {k: graph.from_numpy(v, store) for k, v in mlp.items()}
     want_loss = oracle.realize(passes.prepare(configs.mlp_loss(graph, tm)._uop), store)
+    ign = configs.mlp_inputs(batch=10)
+    ign["y"] = ign["y"].copy()
+    ign["y"][[1, 3, 5, 6, 7, 8, 9]] = -100
+    ti = {k: graph.from_numpy(v, store) for k, v in ign.items()}
+    want_ign = oracle.realize(passes.prepare(configs.mlp_loss(graph, ti)._uop), store)
+    assert np.isfinite(want_ign)
     for r in range(world):
+        loss_ign = np.load(tmp_path / f"loss_ign_{r}.npy")
+        assert abs(float(loss_ign) - float(want_ign)) <= 1e-5 * abs(float(want_ign)), (loss_ign, want_ign)
         got = np.load(tmp_path / f"rows_{r}.npy")
         assert got.tobytes() == want.tobytes()      # row-wise ops shard bit-exactly
         assert np.load(tmp_path / f"bool_{r}.npy").tobytes() == want_b.tobytes()
