@@ -241,9 +241,14 @@ def time_plan(bridge, torch, stream, graph_root, store, front, steps: int, warmu
     return ms, prof, trace
 
 
-EXTRA_NAMES = ("mlp", "gemm_bf16_1024", "gemm_fp32_1024", "gemm_bf16_4096", "gemm_fp32_4096", "gemm_bf16_8192", "gemm_fp32_8192",
-               "attn_fp32", "attn_bf16", "gpt")
+EXTRA_NAMES = ("mlp", "interp", "gemm_bf16_1024", "gemm_fp32_1024", "gemm_bf16_4096", "gemm_fp32_4096", "gemm_bf16_8192",
+               "gemm_fp32_8192", "attn_fp32", "attn_bf16", "gpt")
 NOMINAL = {"hbm_gbs": 7700.0, "bf16_tflops": 2250.0}   # B200 data-sheet figures, printed beside the measured peaks
+
+
+def rows_for_interp(attn_batch: int) -> int:
+    """Rows of the interpreter extras: the full 16384 of config 2, scaled down with --attn-batch for profiler captures."""
+    return ROWS if attn_batch >= 16 else max(1024, ROWS * attn_batch // 16)
 
 
 def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn_batch: int = 16) -> dict:
@@ -252,7 +257,36 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn
     when a single kernel is captured under a profiler)."""
     from browsergrad_b200 import configs, front, graph
     want = set(only) if only else set(EXTRA_NAMES)
-    out = {"mlp": [], "gemm": [], "attention": [], "gpt": []}
+    out = {"mlp": [], "interpreter": [], "gemm": [], "attention": [], "gpt": []}
+    if "interp" in want:
+        # The generic interpreter, which every fusion group without a specialised kernel gets: the three config-2
+        # plans with the pattern kernels switched off, and two chains no pattern matches (an fp32 select chain and the
+        # float64 GELU tail the reference's F.gelu produces under NumPy 2).  Algorithmic bytes = operands read once,
+        # result written once.
+        rows_i = rows_for_interp(attn_batch)
+        arrays = configs.chain_inputs(rows_i, COLS)
+        store = graph.BufferStore()
+        t = {k: graph.from_numpy(v, store) for k, v in arrays.items()}
+        rc = rows_i * COLS
+        plans = [("y = relu(a*b+c)*exp(-d), pattern kernels off", configs.chain_y(graph, t), 20 * rc, 0),
+                 ("row-sum of y, pattern kernels off", configs.chain_rowsum(graph, t), 16 * rc + 4 * rows_i, 0),
+                 ("row-softmax of y, pattern kernels off", configs.chain_rowsoftmax(graph, t), 20 * rc, 0),
+                 ("where(a > b, a*c, d) * exp(-b) + c (fp32, no pattern)",
+                  graph.where(t["a"] > t["b"], t["a"] * t["c"], t["d"]) * graph.exp(-t["b"]) + t["c"], 20 * rc, 1),
+                 ("gelu(a*b+c) (float64 tail, no pattern)", graph.gelu(t["a"] * t["b"] + t["c"]), (12 + 8) * rc, 1)]
+        for name, root, nbytes, keep_patterns in plans:
+            bridge.set_option("static_patterns", keep_patterns)
+            try:
+                ms, prof, trace = time_plan(bridge, torch, stream, root, store, front, steps)
+            finally:
+                bridge.set_option("static_patterns", 1)
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            out["interpreter"].append({"workload": f"{name}, fp32 [{rows_i},{COLS}]", "plan_ms": ms, "kernels": trace,
+                                       "algorithmic_bytes": nbytes,
+                                       "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                                    "frac": gbs / peaks["hbm_gbs"], "frac_of_nominal": gbs / NOMINAL["hbm_gbs"],
+                                                    "nominal_peak": NOMINAL["hbm_gbs"], "basis": "plan time"}})
+        del arrays, store, t
     if "mlp" in want:
         # configuration 1 is latency-bound (13 MFLOP): report microseconds per forward, no roofline fraction
         arrays = configs.mlp_inputs()

@@ -90,6 +90,13 @@ class CudaBridge:
         del keep
         return int(h.value)
 
+    def alloc(self, shape: Sequence[int], dtype: str) -> int:
+        """A device buffer the caller fills itself through ``device_pointer`` on ``stream()`` (the destination of a
+        device-side collective); released like any other handle."""
+        h = C.c_int64()
+        self._check(self._lib.bg_alloc(self._ctx, _shape_arr(shape), len(shape), self._dt(dtype), C.byref(h)))
+        return int(h.value)
+
     def materialize(self, handle: int, shape: Sequence[int], dtype: str) -> bytes:
         n = C.c_int64()
         self._check(self._lib.bg_handle_nbytes(self._ctx, int(handle), C.byref(n)))

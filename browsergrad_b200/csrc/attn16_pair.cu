@@ -45,16 +45,26 @@ struct PairCfg {
   static constexpr int ColS = 0;                       // S of tile A, S of tile B: 2 x 128 columns
   static constexpr int ColO = 256;                     // O of tile A, of tile B: 2 x 64
   static constexpr int ColP = 384;                     // P of tile A, of tile B (16-bit pairs): 2 x 64
-  static constexpr int smem_bytes(bool p_in_tmem) { return 2 * QBytes + NK * KBytes + NV * VBytes + (p_in_tmem ? 0 : 2 * PBytes); }
+  static constexpr int StageBytes = BKV * 256;         // one fp32 tile of 128 rows x 64 values, as two 128-byte-wide boxes
+  static constexpr int smem_bytes(bool p_in_tmem, bool kv32) {
+    return 2 * QBytes + NK * KBytes + NV * VBytes + (kv32 ? 2 * StageBytes : 0) + (p_in_tmem ? 0 : 2 * PBytes);
+  }
 };
 constexpr float kLazyRescaleLog2 = 8.0f;
-constexpr int kPairThreads = 384;        // three warpgroups: producer + MMA, softmax A, softmax B
-// The register pool of a CTA is what it was launched with (168 per thread for 384 threads); the first warpgroup
-// shrinks to kRegsLight so that the softmax warpgroups can grow to kRegsSoftmax.  A request beyond the pool would wait
-// for ever, hence the assertion.
-constexpr int kRegsLaunch = 168, kRegsLight = 72, kRegsSoftmax = 216;
-static_assert(128 * kRegsLight + 256 * kRegsSoftmax <= kRegsLaunch * kPairThreads, "setmaxnreg requests exceed the CTA's register pool");
-static_assert(kRegsLight % 8 == 0 && kRegsSoftmax % 8 == 0, "setmaxnreg takes multiples of 8");
+// Threads and registers.  Without in-kernel conversion: three warpgroups (producer + MMA issuers, softmax A, softmax
+// B); with it a fourth one converts fp32 K / V tiles to the operand type.
+// The register pool of a CTA is what it was launched with (Launch registers per thread); the light warpgroups
+// shrink to Light so that the softmax warpgroups can grow to Softmax.  A request beyond the pool would wait for ever,
+// hence the assertions (and the check of the compiled register count at launch).
+template <bool KV32>
+struct PairRegs {
+  static constexpr int Threads = KV32 ? 512 : 384;
+  static constexpr int Launch = KV32 ? 128 : 168;
+  static constexpr int Light = 72;
+  static constexpr int Softmax = KV32 ? 184 : 216;
+  static_assert((Threads - 256) * Light + 256 * Softmax <= Launch * Threads, "setmaxnreg requests exceed the CTA's register pool");
+  static_assert(Light % 8 == 0 && Softmax % 8 == 0, "setmaxnreg takes multiples of 8");
+};
 
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack16(float a0, float a1) {
@@ -67,36 +77,53 @@ __device__ __forceinline__ uint32_t pack16(float a0, float a1) {
 // the common case: a taken branch over a long cold block costs an instruction fetch the loop cannot afford.
 
 // Puts a score tile into the form the main path expects (see the kernel): masked and out-of-range scores become
-// -inf; with `by_element` the scores become scale * s (+ mask), element by element.  32 scores per step.
-__device__ __noinline__ void fixup_scores(const AttnParams& p, uint32_t t_s, int k0, bool by_element, int tclass, uint4 w4, float scale,
+// -inf; with `by_element` the scores become scale * s (+ mask), element by element.  32 scores per step.  Returns a
+// bit per 32-key piece of the row that is masked out entirely (bit-word masks only).
+__device__ __noinline__ uint32_t fixup_scores(const AttnParams& p, uint32_t t_s, int k0, bool by_element, int tclass, uint4 w4, float scale,
                                           bool per_elem_scale, size_t score_row, size_t mask_row) {
+  if (!by_element) {
+    // bit words: the whole row at once (the caller holds no scores yet, so the registers are free)
+    uint32_t r[128];
+    tmem_ld32_issue(t_s, r);
+    tmem_ld32_issue(t_s + 32, r + 32);
+    tmem_ld32_issue(t_s + 64, r + 64);
+    tmem_ld32_issue(t_s + 96, r + 96);
+    uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int left = p.Sk - (k0 + c * 32);            // keys of this piece that exist
+      if (left < 32) w[c] |= left <= 0 ? 0xffffffffu : (0xffffffffu << left);
+    }
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 128; ++i)
+      if ((w[i >> 5] >> (i & 31)) & 1u) r[i] = __float_as_uint(-CUDART_INF_F);
+    tmem_st32_issue(t_s, r);
+    tmem_st32_issue(t_s + 32, r + 32);
+    tmem_st32_issue(t_s + 64, r + 64);
+    tmem_st32_issue(t_s + 96, r + 96);
+    tmem_st_wait();
+    return (w[0] == 0xffffffffu ? 1u : 0u) | (w[1] == 0xffffffffu ? 2u : 0u) | (w[2] == 0xffffffffu ? 4u : 0u) | (w[3] == 0xffffffffu ? 8u : 0u);
+  }
+  const bool with_mask = p.mask && tclass >= 2;
 #pragma unroll 1
   for (int c = 0; c < 4; ++c) {
     uint32_t r[32];
     tmem_ld32(t_s + (uint32_t)(c * 32), r);
-    if (by_element) {
-      const bool with_mask = p.mask && tclass >= 2;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int key = k0 + c * 32 + i;
-        const bool in_range = key < p.Sk;
-        float v = __fmul_rn(__uint_as_float(r[i]), per_elem_scale ? (in_range ? p.scale_buf[score_row + key] : 0.f) : scale);
-        if (with_mask && in_range) {
-          if (p.mask_is_bool) { if (reinterpret_cast<const unsigned char*>(p.mask)[mask_row + key]) v = -CUDART_INF_F; }
-          else v = __fadd_rn(v, reinterpret_cast<const float*>(p.mask)[mask_row + key]);
-        }
-        r[i] = __float_as_uint(in_range ? v : -CUDART_INF_F);
+    for (int i = 0; i < 32; ++i) {
+      const int key = k0 + c * 32 + i;
+      const bool in_range = key < p.Sk;
+      float v = __fmul_rn(__uint_as_float(r[i]), per_elem_scale ? (in_range ? p.scale_buf[score_row + key] : 0.f) : scale);
+      if (with_mask && in_range) {
+        if (p.mask_is_bool) { if (reinterpret_cast<const unsigned char*>(p.mask)[mask_row + key]) v = -CUDART_INF_F; }
+        else v = __fadd_rn(v, reinterpret_cast<const float*>(p.mask)[mask_row + key]);
       }
-    } else {
-      uint32_t word = c == 0 ? w4.x : (c == 1 ? w4.y : (c == 2 ? w4.z : w4.w));
-      const int left = p.Sk - (k0 + c * 32);          // keys of this piece that exist
-      if (left < 32) word |= left <= 0 ? 0xffffffffu : (0xffffffffu << left);
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if ((word >> i) & 1u) r[i] = __float_as_uint(-CUDART_INF_F);
+      r[i] = __float_as_uint(in_range ? v : -CUDART_INF_F);
     }
     tmem_st32(t_s + (uint32_t)(c * 32), r);
   }
+  return 0u;
 }
 
 // O[row, 0..63] *= alpha in tensor memory (tcgen05.ld / st are warp-wide: every lane of the warp calls this).
@@ -112,8 +139,10 @@ __device__ __noinline__ void rescale_o(uint32_t t_o, float alpha) {
 }
 
 // VMN: V tiles are rows of V (MN-major B operand), else V^T tiles (K-major).  PT: P lives in tensor memory.
-template <bool BF16, bool VMN, bool PT>
-__global__ void __launch_bounds__(kPairThreads, 1)
+// KV32: K and V are fp32 in global memory; their tiles land in a staging buffer (TMA) and a converter warpgroup
+// rounds them to the operand type into the operand rings, as the graph's CAST nodes would (needs VMN and PT).
+template <bool BF16, bool VMN, bool PT, bool KV32>
+__global__ void __launch_bounds__(PairRegs<KV32>::Threads, 1)
 attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const __grid_constant__ AttnParams p) {
   using C = PairCfg;
   constexpr int BKV = C::BKV;
@@ -122,7 +151,8 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   unsigned char* sQ = smem;                                   // [2][QBytes]
   unsigned char* sK = sQ + 2 * C::QBytes;                     // [NK][KBytes]
   unsigned char* sV = sK + C::NK * C::KBytes;                 // [NV][VBytes]
-  unsigned char* sP = sV + C::NV * C::VBytes;                 // [2][PBytes] unless PT
+  unsigned char* sStage = sV + C::NV * C::VBytes;             // [2][StageBytes] fp32 K tile, fp32 V tile (KV32)
+  unsigned char* sP = sStage + (KV32 ? 2 * C::StageBytes : 0); // [2][PBytes] unless PT
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + (PT ? 0 : 2 * C::PBytes));
   uint64_t* q_full = bars;                // [2] query rows of a tile are in shared memory (4 arrivals)
   uint64_t* k_full = q_full + 2;          // [NK]
@@ -133,7 +163,9 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   uint64_t* s_empty = s_full + 2;         // [2] its softmax warps hold the scores in registers (4 arrivals)
   uint64_t* p_full = s_empty + 2;         // [2] P is published (4 arrivals)
   uint64_t* pv_full = p_full + 2;         // [2] P V has completed
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_full + 2);
+  uint64_t* stage_full = pv_full + 2;     // [2] an fp32 K (0) / V (1) tile has landed in its staging buffer
+  uint64_t* stage_empty = stage_full + 2; // [2] the converter warps have read it (4 arrivals)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(stage_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   unsigned char* s_cls = reinterpret_cast<unsigned char*>(tmem_holder + 4);   // [2][n_kv] tile classes of the two query tiles
 
@@ -154,7 +186,7 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     const unsigned char* cls_a = p.tile_class ? p.tile_class + (size_t)(2 * pair) * n_kv : nullptr;
     const unsigned char* cls_b = p.tile_class && has_b ? p.tile_class + (size_t)(2 * pair + 1) * n_kv : nullptr;
     const unsigned char dflt = p.mask ? 3 : 1;
-    for (int j = threadIdx.x; j < n_kv; j += kPairThreads) {
+    for (int j = threadIdx.x; j < n_kv; j += PairRegs<KV32>::Threads) {
       s_cls[j] = cls_a ? cls_a[j] : dflt;
       s_cls[n_kv + j] = has_b ? (cls_b ? cls_b[j] : dflt) : (unsigned char)0;
     }
@@ -170,8 +202,10 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       mbar_init(&p_full[g], 4); mbar_init(&pv_full[g], 1);
     }
     // a K or V slot is free once both issuers are done with it
-    for (int s = 0; s < C::NK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 2); }
-    for (int s = 0; s < C::NV; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 2); }
+    // an operand tile is complete when its TMA bytes have landed, or (KV32) when the four converter warps have written it
+    for (int s = 0; s < C::NK; ++s) { mbar_init(&k_full[s], KV32 ? 4 : 1); mbar_init(&k_empty[s], 2); }
+    for (int s = 0; s < C::NV; ++s) { mbar_init(&v_full[s], KV32 ? 4 : 1); mbar_init(&v_empty[s], 2); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&stage_full[i], 1); mbar_init(&stage_empty[i], 4); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -185,9 +219,22 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLight));
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PairRegs<KV32>::Light));
     if (warp == 0) {
-      if (lane == 0) {
+      if (KV32) {
+        // fp32 tiles into the staging buffers: lane 0 K, lane 1 V; two boxes of 32 values (128 bytes) per row
+        if (lane < 2) {
+          const CUtensorMap* tm = lane == 0 ? &tmK : &tmV;
+          unsigned char* st = sStage + lane * C::StageBytes;
+          int u = 0;
+          for (int j = next_union(0); j < n_kv; j = next_union(j + 1), ++u) {
+            if (!mbar_wait(&stage_empty[lane], ((uint32_t)u & 1u) ^ 1u, abort_flag)) break;
+            mbar_expect_tx(&stage_full[lane], C::StageBytes);
+            tma_load_4d(tm, st, &stage_full[lane], 0, j * BKV, h, b);
+            tma_load_4d(tm, st + C::StageBytes / 2, &stage_full[lane], 32, j * BKV, h, b);
+          }
+        }
+      } else if (lane == 0) {
         int u = 0;
         for (int j = next_union(0); j < n_kv; j = next_union(j + 1), ++u) {
           const int s = u % C::NK;
@@ -292,8 +339,39 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         u = un;
       }
     }
+  } else if (KV32 && warp >= 12) {
+    // ---- converter warpgroup: staging buffer (fp32, two 128-byte-swizzled boxes per tile) -> operand ring (16 bit,
+    //      128-byte swizzle); thread r owns row r of the tile.  K tiles and V tiles alternate.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PairRegs<KV32>::Light));
+    const int r = threadIdx.x & 127, sw = r & 7;
+    bool ok = true;
+    int u = 0;
+    for (int j = next_union(0); j < n_kv && ok; j = next_union(j + 1), ++u) {
+#pragma unroll 1
+      for (int which = 0; which < 2 && ok; ++which) {       // 0: K, 1: V
+        const int slot = u % (which == 0 ? C::NK : C::NV);
+        uint64_t* full = which == 0 ? &k_full[slot] : &v_full[slot];
+        uint64_t* empty = which == 0 ? &k_empty[slot] : &v_empty[slot];
+        unsigned char* dst = (which == 0 ? sK + slot * C::KBytes : sV + slot * C::VBytes) + r * 128;
+        const unsigned char* src = sStage + which * C::StageBytes + r * 128;
+        ok = __all_sync(0xffffffffu, mbar_wait(&stage_full[which], (uint32_t)u & 1u, abort_flag) &&
+                                         mbar_wait(empty, ((uint32_t)(u / (which == 0 ? C::NK : C::NV)) & 1u) ^ 1u, abort_flag));
+        if (!ok) break;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {                         // eight output chunks of eight values
+          const unsigned char* box = src + (c >> 2) * (C::StageBytes / 2);
+          const float4 lo = *reinterpret_cast<const float4*>(box + ((((2 * c) & 7) ^ sw) << 4));
+          const float4 hi = *reinterpret_cast<const float4*>(box + ((((2 * c + 1) & 7) ^ sw) << 4));
+          *reinterpret_cast<uint4*>(dst + ((c ^ sw) << 4)) =
+              make_uint4(pack16<BF16>(lo.x, lo.y), pack16<BF16>(lo.z, lo.w), pack16<BF16>(hi.x, hi.y), pack16<BF16>(hi.z, hi.w));
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(full); mbar_arrive(&stage_empty[which]); }
+      }
+    }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(PairRegs<KV32>::Softmax));
     const int g = (warp - 4) >> 2;                  // query tile of this warp
     const int quarter = warp & 3;                   // tensor-memory lane quarter this warp may access
     const int r_in_tile = quarter * 32 + lane;
@@ -364,7 +442,10 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         ok = __all_sync(0xffffffffu, mbar_wait(&s_full[g], (uint32_t)t & 1u, abort_flag));
         if (!ok) break;
         tc_fence_after();
-        if (fixup) fixup_scores(p, t_s, k0, by_element, tclass, w4, scale, per_elem_scale, score_row, mask_row);
+        // 32-key pieces that are masked for every row of this warp (the far side of a causal diagonal) need no
+        // exponentials: their probabilities are zero
+        uint32_t dead = 0u;
+        if (fixup) dead = __reduce_and_sync(0xffffffffu, fixup_scores(p, t_s, k0, by_element, tclass, w4, scale, per_elem_scale, score_row, mask_row));
         const bool fast = !by_element;      // scale still to be applied (folded into the exponent)
         float x[BKV];
         {
@@ -408,9 +489,17 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         {
           float ps[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int i = 0; i < BKV; ++i) {
-            x[i] = ex2_approx(fmaf(x[i], cc, -ml));
-            ps[i & 3] += x[i];
+          for (int c = 0; c < BKV / 32; ++c) {
+            if ((dead >> c) & 1u) {
+#pragma unroll
+              for (int i = c * 32; i < c * 32 + 32; ++i) x[i] = 0.f;
+            } else {
+#pragma unroll
+              for (int i = c * 32; i < c * 32 + 32; ++i) {
+                x[i] = ex2_approx(fmaf(x[i], cc, -ml));
+                ps[i & 3] += x[i];
+              }
+            }
           }
           l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
         }
@@ -495,18 +584,20 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 }
 
 template <bool BF16>
-cudaError_t launch_variant(bool vmn, bool pt, dim3 grid, size_t smem, cudaStream_t s, const CUtensorMap& k, const CUtensorMap& v, const AttnParams& p) {
+cudaError_t launch_variant(bool vmn, bool pt, bool kv32, dim3 grid, size_t smem, cudaStream_t s, const CUtensorMap& k, const CUtensorMap& v,
+                           const AttnParams& p) {
   void (*kern)(const CUtensorMap, const CUtensorMap, const AttnParams) =
-      vmn ? (pt ? attn16_pair_kernel<BF16, true, true> : attn16_pair_kernel<BF16, true, false>)
-          : (pt ? attn16_pair_kernel<BF16, false, true> : attn16_pair_kernel<BF16, false, false>);
-  // the register hand-over in the kernel assumes the pool of a launch at kRegsLaunch registers per thread
+      kv32 ? attn16_pair_kernel<BF16, true, true, true>
+           : vmn ? (pt ? attn16_pair_kernel<BF16, true, true, false> : attn16_pair_kernel<BF16, true, false, false>)
+                 : (pt ? attn16_pair_kernel<BF16, false, true, false> : attn16_pair_kernel<BF16, false, false, false>);
+  // the register hand-over in the kernel assumes the pool of a launch at PairRegs::Launch registers per thread
   cudaFuncAttributes fa;
   cudaError_t e = cudaFuncGetAttributes(&fa, kern);
   if (e != cudaSuccess) return e;
-  if (fa.numRegs < kRegsLaunch) return cudaErrorLaunchOutOfResources;
+  if (fa.numRegs < (kv32 ? PairRegs<true>::Launch : PairRegs<false>::Launch)) return cudaErrorLaunchOutOfResources;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  kern<<<grid, kPairThreads, smem, s>>>(k, v, p);
+  kern<<<grid, kv32 ? PairRegs<true>::Threads : PairRegs<false>::Threads, smem, s>>>(k, v, p);
   return cudaGetLastError();
 }
 
@@ -515,24 +606,25 @@ cudaError_t launch_variant(bool vmn, bool pt, dim3 grid, size_t smem, cudaStream
 bool attn16_pair_usable(int Sk, int out_dtype, const void* out, long long out_sb, long long out_sh, long long out_ss) {
   // the tile classes of both query tiles are kept in shared memory beside the operand tiles
   const int n_kv = (Sk + PairCfg::BKV - 1) / PairCfg::BKV;
-  if ((size_t)PairCfg::smem_bytes(false) + 256 + 1024 + 2 * (size_t)n_kv > 227 * 1024) return false;
+  if ((size_t)PairCfg::smem_bytes(false, false) + 256 + 1024 + 2 * (size_t)n_kv > 227 * 1024) return false;
   // output rows are written in 16-byte pieces
   const int es = dtype_size(out_dtype);
   const long long per16 = 16 / es;
   return (reinterpret_cast<uintptr_t>(out) & 15) == 0 && out_sb % per16 == 0 && out_sh % per16 == 0 && out_ss % per16 == 0;
 }
 
-cudaError_t launch_attn16_pair(const attn::AttnParams& p, bool bf16, bool v_mn, bool p_in_tmem, const CUtensorMap& tm_k,
+cudaError_t launch_attn16_pair(const attn::AttnParams& p, bool bf16, bool v_mn, bool p_in_tmem, bool kv_fp32, const CUtensorMap& tm_k,
                                const CUtensorMap& tm_v, cudaStream_t s) {
+  if (kv_fp32 && !(v_mn && p_in_tmem)) return cudaErrorInvalidValue;
   const int n_qt = (p.Sq + kQRows - 1) / kQRows;
   const long long n_cta = (long long)((n_qt + 1) / 2) * p.B * p.H;
   if (n_cta <= 0 || n_cta > 0x7fffffffll) return cudaErrorInvalidValue;
   const int n_kv = (p.Sk + PairCfg::BKV - 1) / PairCfg::BKV;
-  const size_t smem = (size_t)PairCfg::smem_bytes(p_in_tmem) + 256 + 1024 + 2 * (size_t)n_kv;
+  const size_t smem = (size_t)PairCfg::smem_bytes(p_in_tmem, kv_fp32) + 256 + 1024 + 2 * (size_t)n_kv;
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
   dim3 grid((unsigned)n_cta);
-  return bf16 ? launch_variant<true>(v_mn, p_in_tmem, grid, smem, s, tm_k, tm_v, p)
-              : launch_variant<false>(v_mn, p_in_tmem, grid, smem, s, tm_k, tm_v, p);
+  return bf16 ? launch_variant<true>(v_mn, p_in_tmem, kv_fp32, grid, smem, s, tm_k, tm_v, p)
+              : launch_variant<false>(v_mn, p_in_tmem, kv_fp32, grid, smem, s, tm_k, tm_v, p);
 }
 
 }  // namespace bg

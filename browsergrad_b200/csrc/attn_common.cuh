@@ -64,9 +64,16 @@ struct AttnParams {
 }  // namespace attn
 
 // Two-query-tile 16-bit kernel (attn16_pair.cu).  `p` carries the query rows' address and strides; K tiles are
-// [128 keys, 64] boxes of tm_k; tm_v gives [128 keys, 64] boxes of V (v_mn) or [64, 64 keys] boxes of V^T.
+// [128 keys, 64] boxes of tm_k; tm_v gives [128 keys, 64] boxes of V (v_mn) or [64, 64 keys] boxes of V^T.  With
+// kv_fp32 (needs v_mn and p_in_tmem) both maps describe fp32 tensors in boxes of [128 keys, 32 values] and the kernel
+// rounds the tiles to the operand type itself.
 bool attn16_pair_usable(int Sk, int out_dtype, const void* out, long long out_sb, long long out_sh, long long out_ss);
-cudaError_t launch_attn16_pair(const attn::AttnParams& p, bool bf16, bool v_mn, bool p_in_tmem, const CUtensorMap& tm_k,
+cudaError_t launch_attn16_pair(const attn::AttnParams& p, bool bf16, bool v_mn, bool p_in_tmem, bool kv_fp32, const CUtensorMap& tm_k,
                                const CUtensorMap& tm_v, cudaStream_t s);
+
+// 3xTF32 kernel with one thread per query row and P / O in tensor memory (attn_tf32_row.cu).  maps: Q hi, Q lo
+// ([128 rows, 32] boxes), K hi, K lo ([64 keys, 32] boxes), V^T hi, V^T lo ([64 rows, 32 keys] boxes).
+bool attn_tf32_row_usable(int Sk, int out_dtype, const void* out, long long out_sb, long long out_sh, long long out_ss);
+cudaError_t launch_attn_tf32_row(const attn::AttnParams& p, const CUtensorMap maps[6], cudaStream_t s);
 
 }  // namespace bg

@@ -953,6 +953,24 @@ bool make_map4(CUtensorMap* map, const void* ptr, int dtype, int B, int H, long 
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// [B, H, rows, cols] tensor with element strides sb / sh / ss over batch, head and row (rows of `cols` contiguous
+// values), box = box_cols x box_rows, 128-byte swizzle.
+bool make_map4_strided(CUtensorMap* map, const void* ptr, int dtype, int B, int H, long long rows, long long cols, long long sb,
+                       long long sh, long long ss, int box_cols, int box_rows) {
+  EncodeTiledFn fn = attn_encode_fn();
+  if (!fn) return false;
+  const int es = dtype_size(dtype);
+  CUtensorMapDataType dt = dtype == BG_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                           : dtype == BG_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)H, (cuuint64_t)B};
+  // a broadcast batch or head axis (stride 0) is described with extent 1: the kernel then always asks for index 0
+  cuuint64_t strides[3] = {(cuuint64_t)ss * es, (cuuint64_t)(sh ? sh : rows * ss) * es, (cuuint64_t)(sb ? sb : rows * ss * H) * es};
+  cuuint32_t box[4] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(map, dt, 4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 unsigned prep_grid(long long n) {
   long long g = (n + 255) / 256;
   if (g > 148 * 16) g = 148 * 16;
@@ -990,6 +1008,8 @@ void attn_scratch_sizes(const AttnProblem& a, int64_t bytes[8]) {
 // 16-bit kernel choice: bit 0 the two-tile (pair) kernel, bit 1 V as an MN-major operand (no transposing pass),
 // bit 2 P in tensor memory.  0 selects the single-tile kernel.
 int g_attn16_variant = kAttn16DefaultVariant;
+// 3xTF32 kernel choice: 0 two threads per row with P in shared memory, 1 one thread per row with P and O in tensor memory.
+int g_attn32_variant = kAttn32DefaultVariant;
 
 cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bool check_uniform, bool classify_mask, int* status,
                                 cudaStream_t s) {
@@ -999,6 +1019,12 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
   const bool pair = !tf32 && (g_attn16_variant & 1) && attn16_pair_usable(a.Sk, a.out_dtype, a.out, a.out_sb, a.out_sh, a.out_ss);
   const bool v_mn = pair && (g_attn16_variant & 2);
   const bool p_tmem = pair && (g_attn16_variant & 4);
+  // fp32 K and V converted inside the kernel: rows of 64 contiguous values, every stride a positive multiple of 16 bytes
+  auto fp32_rows = [&](const AttnOperand& o) {
+    return o.dtype == BG_F32 && o.stride[3] == 1 && (reinterpret_cast<uintptr_t>(o.ptr) & 15) == 0 && o.stride[0] > 0 && o.stride[1] > 0 &&
+           o.stride[2] >= a.D && o.stride[0] % 4 == 0 && o.stride[1] % 4 == 0 && o.stride[2] % 4 == 0;
+  };
+  const bool kv32 = v_mn && p_tmem && (g_attn16_variant & 8) && fp32_rows(a.k) && fp32_rows(a.v);
   // operand staging: dense Q, K, V^T (or V) in the kernel's encoding
   const int kind = tf32 ? PREP_TF32 : (a.ab_dtype == BG_F16 ? PREP_F16 : PREP_BF16);
   const AttnOperand* ops[3] = {&a.q, &a.k, &a.v};
@@ -1019,6 +1045,7 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
         continue;
       }
     }
+    if (kv32 && i > 0) continue;
     // 16-bit operands that are already dense [B,H,S,D] feed the TMA maps directly
     if (!tf32 && as_rows && dense && ops[i]->dtype == a.ab_dtype && aligned) {
       staged[i] = ops[i]->ptr;
@@ -1070,8 +1097,13 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
   }
   CUtensorMap q0, q1, k0, k1, v0, v1;
   if (!pair && !make_map4(&q0, staged[0], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
-  if (!make_map4(&k0, staged[1], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
-  if (v_mn) {
+  if (kv32) {
+    if (!make_map4_strided(&k0, a.k.ptr, BG_F32, a.B, a.H, a.Sk, a.D, a.k.stride[0], a.k.stride[1], a.k.stride[2], 32, bkv) ||
+        !make_map4_strided(&v0, a.v.ptr, BG_F32, a.B, a.H, a.Sk, a.D, a.v.stride[0], a.v.stride[1], a.v.stride[2], 32, bkv))
+      return cudaErrorInvalidValue;
+  } else if (!make_map4(&k0, staged[1], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
+  if (kv32) {
+  } else if (v_mn) {
     if (!make_map4(&v0, staged[2], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
   } else if (!make_map4(&v0, staged[2], sdt, a.B, a.H, a.D, a.Sk, kHeadDim)) return cudaErrorInvalidValue;
   q1 = q0; k1 = k0; v1 = v0;
@@ -1109,10 +1141,14 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
       p.q_ptr = staged[0]; p.q_sb = (long long)a.H * a.Sq * a.D; p.q_sh = (long long)a.Sq * a.D; p.q_ss = a.D;
       p.q_f32 = 0;
     }
-    return launch_attn16_pair(p, a.ab_dtype == BG_BF16, v_mn, p_tmem, k0, v0, s);
+    return launch_attn16_pair(p, a.ab_dtype == BG_BF16, v_mn, p_tmem, kv32, k0, v0, s);
   }
   dim3 grid((a.Sq + kQRows - 1) / kQRows, a.H, a.B);
   cudaError_t e;
+  if (tf32 && g_attn32_variant == 1 && attn_tf32_row_usable(a.Sk, a.out_dtype, a.out, a.out_sb, a.out_sh, a.out_ss)) {
+    const CUtensorMap maps[6] = {q0, q1, k0, k1, v0, v1};
+    return launch_attn_tf32_row(p, maps, s);
+  }
   if (tf32) {
     const size_t smem = AttnCfg::SmemBytes + 256 + 2048 + 1024;
     e = cudaFuncSetAttribute(attn_tf32_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -296,8 +296,12 @@ void attn_scratch_sizes(const AttnProblem& a, int64_t bytes[8]);
 // scratch[7] is the device flag "scale_buf is uniform"; it is (re)computed when check_uniform is set.
 cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bool check_uniform, bool classify_mask, int* status, cudaStream_t s);
 // Which 16-bit attention kernel runs (attn_tc.cu): bit 0 the two-query-tile kernel, bit 1 V as an MN-major operand,
-// bit 2 P kept in tensor memory; 0 is the single-tile kernel.
+// bit 2 P kept in tensor memory, bit 3 (with bits 1 and 2) fp32 K / V converted inside the kernel; 0 is the single-tile kernel.
 extern int g_attn16_variant;
 constexpr int kAttn16DefaultVariant = 1;
+// Which 3xTF32 attention kernel runs: 0 two threads per row, P through shared memory; 1 one thread per row, P and O in
+// tensor memory.
+extern int g_attn32_variant;
+constexpr int kAttn32DefaultVariant = 0;
 
 }  // namespace bg

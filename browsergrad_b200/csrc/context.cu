@@ -112,13 +112,14 @@ static bool is_pinned(const void* p) {
 
 int h2d(bg_context* ctx, void* dst, const void* src, size_t n) {
   if (n == 0) return BG_OK;
-  if (n <= (64u << 10)) {
+  const bool pinned = is_pinned(src);
+  if (n <= (64u << 10) && !pinned) {
     cudaError_t e = cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, ctx->stream);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "upload copy");
-    // pageable source: the runtime has staged it before returning
+    // pageable source: the runtime has staged it before returning, the caller may reuse its buffer
     return BG_OK;
   }
-  if (is_pinned(src)) {
+  if (pinned) {
     // page-locked caller memory: one DMA straight from the caller's buffer
     cudaError_t e = cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, ctx->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
@@ -384,8 +385,12 @@ int bg_set_option(bg_context* ctx, const char* key, int64_t value) {
     g_tc_pair_width = (int)value;
   }
   else if (k == "attention16_kernel") {
-    if (value < -1 || value > 7) return fail(ctx, BG_ERR_INVALID, "set_option: attention16_kernel is a bit set in 0..7, or -1 for the default");
+    if (value < -1 || value > 15) return fail(ctx, BG_ERR_INVALID, "set_option: attention16_kernel is a bit set in 0..15, or -1 for the default");
     g_attn16_variant = value < 0 ? kAttn16DefaultVariant : (int)value;     // process-wide: a launch policy, not plan state
+  }
+  else if (k == "attention32_kernel") {
+    if (value < -1 || value > 1) return fail(ctx, BG_ERR_INVALID, "set_option: attention32_kernel is 0, 1, or -1 for the default");
+    g_attn32_variant = value < 0 ? kAttn32DefaultVariant : (int)value;
   }
   else if (k == "static_patterns") { ctx->static_patterns = value != 0; ctx->plan_cache.clear(); }
   else if (k == "gemm_groups") { ctx->gemm_groups = value != 0; ctx->plan_cache.clear(); }
@@ -418,6 +423,21 @@ int bg_upload(bg_context* ctx, const void* data, size_t nbytes, const int64_t* s
   return BG_OK;
 }
 
+int bg_alloc(bg_context* ctx, const int64_t* shape, int rank, int dtype, bg_handle* out) {
+  if (!ctx || !out) return BG_ERR_INVALID;
+  if (rank < 0 || rank > BG_MAX_RANK || (rank > 0 && !shape)) return fail(ctx, BG_ERR_INVALID, "alloc: bad rank");
+  const int es = dtype_size(dtype);
+  if (es == 0) return fail(ctx, BG_ERR_INVALID, "alloc: unknown dtype");
+  for (int i = 0; i < rank; ++i)
+    if (shape[i] < 0) return fail(ctx, BG_ERR_INVALID, "alloc: negative extent");
+  const int64_t bytes = numel_of(shape, rank) * es;
+  cudaSetDevice(ctx->device);
+  void* p = nullptr;
+  if (int rc = dev_alloc(ctx, bytes, &p)) return rc;
+  *out = mint_handle(ctx, p, bytes, dtype, shape, rank);
+  return BG_OK;
+}
+
 int bg_materialize(bg_context* ctx, bg_handle h, void* out, size_t nbytes) {
   if (!ctx) return BG_ERR_INVALID;
   auto it = ctx->handles.find(h);
@@ -427,7 +447,13 @@ int bg_materialize(bg_context* ctx, bg_handle h, void* out, size_t nbytes) {
                                          std::to_string(it->second.bytes));
   if (nbytes > 0 && !out) return fail(ctx, BG_ERR_INVALID, "materialize: null destination");
   cudaSetDevice(ctx->device);
-  return d2h(ctx, out, it->second.ptr, nbytes);
+  const int rc = d2h(ctx, out, it->second.ptr, nbytes);
+  if (rc == BG_OK && ctx->status_pending) {
+    // d2h synchronised the stream: the status copy behind the producing plan has landed
+    const int st = take_device_status(ctx);
+    if (st != 0) return fail(ctx, st, device_status_message(st) + " (in the plan that produced this buffer or an earlier one)");
+  }
+  return rc;
 }
 
 int bg_release(bg_context* ctx, bg_handle h) {
@@ -487,6 +513,10 @@ int bg_flush_profiles(bg_context* ctx, bg_profile_entry* out, int capacity, int*
   cudaSetDevice(ctx->device);
   cudaError_t e = cudaStreamSynchronize(ctx->stream);
   if (e != cudaSuccess) return cuda_fail(ctx, e, "flush_profiles synchronize");
+  if (ctx->status_pending) {
+    const int st = take_device_status(ctx);
+    if (st != 0) return fail(ctx, st, device_status_message(st) + " (in an earlier plan)");
+  }
   for (auto& pe : ctx->pending_events) {
     float ms = 0.f;
     if (cudaEventElapsedTime(&ms, pe.second.first, pe.second.second) == cudaSuccess) {

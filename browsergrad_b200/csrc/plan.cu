@@ -104,7 +104,13 @@ struct CompiledPlan {
   int root_rank = 0;
   int64_t root_shape[kMaxRank] = {0};
   int64_t root_bytes = 0;
+  // The device status word: `uses_status` marks kernels that can refuse their data (an index outside its axis) --
+  // the plan then ends with a synchronising check, as the reference raises at the call; `uses_wait_status` marks
+  // kernels whose bounded device waits can give up (tensor-core pipelines).  That is a fault of the device, not of
+  // the data, so a plan that keeps its root on the device does not wait for it: the word is copied to the host
+  // behind the plan and examined by the next call that synchronises anyway or starts another plan.
   bool uses_status = false;
+  bool uses_wait_status = false;
   int64_t plan_peak = 0;
   std::string trace;
 };
@@ -2186,7 +2192,7 @@ void Compiler::emit_attention(int n, int key) {
   pu.u.name = std::string(ap.mode == 1 ? "attention_tc_3xtf32" : "attention_tc") + (ap.mask >= 0 ? (ap.mask_is_bool ? "+boolmask" : "+mask") : "") +
               (ap.out_node >= 0 ? "+merge" : "") + "[" + dtype_name(fin.dtype) + "]";
   pu.u.launches = 4 + (ap.mask >= 0) + (ap.scale_node >= 0);
-  cp_->uses_status = true;
+  cp_->uses_wait_status = true;
   pu.u.fn = [=](Run& r) {
     AttnProblem a = tmpl;
     a.q.ptr = reinterpret_cast<char*>(r.ptr[sq]) + offq;
@@ -2421,7 +2427,7 @@ void Compiler::emit_matmul(int n, int key) {
           }
         }
       }
-      cp_->uses_status = true;
+      cp_->uses_wait_status = true;
       const int sc_slot = sc;
       pu.u.fn = [=](Run& r) {
         cudaStream_t st = r.ctx->stream;
@@ -3081,11 +3087,34 @@ std::shared_ptr<CompiledPlan> Compiler::compile() {
 
 }  // namespace
 
+// Reads (and clears) the status word as last copied to the host; call after a synchronisation of the stream, or
+// without one to pick up what an earlier copy already delivered.
+int take_device_status(bg_context* ctx) {
+  ctx->status_pending = false;
+  const int st = *ctx->h_status;
+  if (st != 0) {
+    *ctx->h_status = 0;
+    cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
+  }
+  return st;
+}
+
+std::string device_status_message(int status_rc) {
+  return status_rc == BG_ERR_INDEX_RANGE ? "run_tensor_plan: gather / scatter / cross_entropy index outside its axis, or scatter indices naming one destination twice"
+         : status_rc == BG_ERR_DEVICE_TIMEOUT ? "run_tensor_plan: a device-side wait of a tensor-core kernel gave up (status 6)"
+                                              : "run_tensor_plan: device-side status " + std::to_string(status_rc);
+}
+
 int run_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs, int n_inputs, void* out_host,
              size_t out_nbytes, bg_handle* out_handle) {
   if (!plan->steps || plan->n_steps <= 0) return fail(ctx, BG_ERR_INVALID, "run_tensor_plan: empty plan");
   if (n_inputs > 0 && !inputs) return fail(ctx, BG_ERR_INVALID, "run_tensor_plan: null inputs");
   cudaSetDevice(ctx->device);
+  // a device-side wait that gave up in an earlier plan whose root stayed on the device is reported here at the latest
+  if (ctx->status_pending && *ctx->h_status != 0) {
+    const int st = take_device_status(ctx);
+    return fail(ctx, st, device_status_message(st) + " (in an earlier plan)");
+  }
   uint64_t h = 1469598103934665603ull;
   h = fnv1a(plan->steps, sizeof(bg_plan_step) * (size_t)plan->n_steps, h);
   if (plan->n_ext > 0) h = fnv1a(plan->ext, sizeof(int32_t) * (size_t)plan->n_ext, h);
@@ -3185,19 +3214,18 @@ int run_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs, 
   if (cp->plan_peak > ctx->plan_peak) ctx->plan_peak = cp->plan_peak;
   if (!run.ptr[cp->root_slot]) { cleanup(false); return fail(ctx, BG_ERR_INVALID, "run_tensor_plan: root was not produced"); }
   int status_rc = BG_OK;
-  if (cp->uses_status) {
+  if (cp->uses_status || cp->uses_wait_status)
     cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream);
+  if (cp->uses_status || (cp->uses_wait_status && out_host)) {
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) { cleanup(false); return cuda_fail(ctx, e, "plan execution"); }
-    if (*ctx->h_status != 0) {
-      status_rc = *ctx->h_status;
-      cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
-    }
+    status_rc = take_device_status(ctx);
+  } else if (cp->uses_wait_status) {
+    ctx->status_pending = true;
   }
   if (status_rc) {
     cleanup(false);
-    return fail(ctx, status_rc, status_rc == BG_ERR_INDEX_RANGE ? "run_tensor_plan: gather / scatter / cross_entropy index outside its axis, or scatter indices naming one destination twice"
-                                                               : "run_tensor_plan: device-side status " + std::to_string(status_rc));
+    return fail(ctx, status_rc, device_status_message(status_rc));
   }
   if (out_host) {
     int rc = d2h(ctx, out_host, run.ptr[cp->root_slot], (size_t)cp->root_bytes);

@@ -42,6 +42,7 @@ struct bg_context {
   // device status word written by kernels that can refuse (index range, bounded waits)
   int* d_status = nullptr;
   int* h_status = nullptr;  // pinned
+  bool status_pending = false;   // a plan that may have set the word ended without a synchronising check
   // pinned staging for host <-> device copies
   void* stage = nullptr;
   size_t stage_bytes = 0;
@@ -103,6 +104,8 @@ void split_planes_drop(bg_context* ctx, const void* ptr);
 void* cast_copy_for(bg_context* ctx, const void* ptr, int64_t bytes, int dtype, bool* fresh);
 void cast_copy_drop(bg_context* ctx, const void* ptr);
 
+int take_device_status(bg_context* ctx);
+std::string device_status_message(int status_rc);
 int run_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs, int n_inputs, void* out_host,
              size_t out_nbytes, bg_handle* out_handle);
 

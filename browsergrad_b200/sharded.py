@@ -78,6 +78,70 @@ def gather_rows(local: np.ndarray, total_rows: int, group: Any = None, device: O
     return np.concatenate(rows, axis=0) if rows else buf[:0]
 
 
+class _DeviceView:
+    """Exposes the device buffer behind a bridge handle through ``__cuda_array_interface__`` so that
+    ``torch.as_tensor`` wraps it without a copy (raw bytes; the caller reinterprets)."""
+
+    def __init__(self, ptr: int, nbytes: int) -> None:
+        self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False), "version": 3}
+
+
+def device_bytes(bridge: Any, handle: int, nbytes: int, device: int) -> Any:
+    """The bytes behind ``handle`` as a uint8 CUDA tensor sharing the bridge's memory (no copy).  The tensor is only
+    valid while the handle lives, and work on it must be ordered on the bridge's stream."""
+    import torch
+    return torch.as_tensor(_DeviceView(bridge.device_pointer(handle), nbytes), device=torch.device("cuda", device))
+
+
+def gather_rows_device(bridge: Any, handle: int, local_shape: Sequence[int], dtype: str, total_rows: int, *,
+                       group: Any = None, device: int = 0) -> int:
+    """All-gather the row blocks the ranks hold on their devices into the full array on every rank's device and
+    return a bridge handle to it: ``torch.distributed.all_gather_into_tensor`` (NCCL over NVLink) reads the bridge's
+    own buffer and writes straight into a buffer the bridge allocated (``bridge.alloc``) -- nothing passes through
+    host memory, and no kernel is handed a peer's pointer (NCCL moves the bytes).  Blocks of unequal height are padded
+    to the tallest inside the exchange.  The collective is ordered on the bridge's stream."""
+    import torch
+    from . import _lib
+    dist = _dist()
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    itemsize = _lib.DTYPE_SIZE[dtype]
+    row_bytes = itemsize
+    for d in local_shape[1:]:
+        row_bytes *= int(d)
+    spans = [shard_bounds(total_rows, world, r) for r in range(world)]
+    heights = [hi - lo for lo, hi in spans]
+    if int(local_shape[0]) != heights[rank]:
+        raise ValueError(f"gather_rows_device: rank {rank} holds {local_shape[0]} rows, its share of {total_rows} is {heights[rank]}")
+    max_h = max(heights)
+    dev = torch.device("cuda", device)
+    stream = torch.cuda.ExternalStream(bridge.stream(), device=dev)
+    out_shape = (total_rows,) + tuple(int(d) for d in local_shape[1:])
+    out = bridge.alloc(out_shape, dtype)
+    try:
+        with torch.cuda.stream(stream):
+            mine = device_bytes(bridge, handle, heights[rank] * row_bytes, device) if heights[rank] * row_bytes else \
+                torch.empty(0, dtype=torch.uint8, device=dev)
+            full = device_bytes(bridge, out, total_rows * row_bytes, device) if total_rows * row_bytes else \
+                torch.empty(0, dtype=torch.uint8, device=dev)
+            if min(heights) == max_h:
+                dist.all_gather_into_tensor(full, mine, group=group)
+            else:
+                padded = torch.zeros(max_h * row_bytes, dtype=torch.uint8, device=dev)
+                padded[: mine.numel()] = mine
+                parts = torch.empty(world * max_h * row_bytes, dtype=torch.uint8, device=dev)
+                dist.all_gather_into_tensor(parts, padded, group=group)
+                for r, (lo, hi) in enumerate(spans):
+                    full[lo * row_bytes: hi * row_bytes] = parts[r * max_h * row_bytes: r * max_h * row_bytes + (hi - lo) * row_bytes]
+                # torch frees the temporaries once this returns; they were used on the bridge's stream
+                padded.record_stream(stream)
+                parts.record_stream(stream)
+    except BaseException:
+        bridge.release(out)
+        raise
+    return out
+
+
 def combine_mean(local_mean: np.ndarray, local_count: int, group: Any = None, device: Optional[str] = None) -> np.ndarray:
     """Global mean from per-rank means over ``local_count`` contributing positions (one all-reduce of
     (sum, count)).  A rank with no contributing position (its local mean is 0/0 = NaN) adds (0, 0); the

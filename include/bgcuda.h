@@ -174,14 +174,21 @@ int bg_abi_version(void);
 /* options: "profiling" (0/1), "f64_contraction" (0 = exact fp64 FMA, 1 = fp32-faithful tensor
  * path, 2 = automatic: tensor path when no fp64 leaf enters the plan), "fusion" (0/1), "tensor_cores" (0/1),
  * "static_patterns" (0/1), "gemm_groups" (0/1), "gemm_cta_pairs" (0/1/2), "gemm_pair_tile_width" (0/256/192/128),
- * "attention16_kernel" (bit set: 1 two query tiles per CTA, 2 V as an MN-major operand, 4 P in tensor memory;
- * 0 one query tile per CTA; -1 restores the default). */
+ * "attention16_kernel" (bit set: 1 two query tiles per CTA, 2 V as an MN-major operand, 4 P in tensor memory,
+ * 8 fp32 K / V converted inside the kernel; 0 one query tile per CTA; -1 restores the default),
+ * "attention32_kernel" (3xTF32 attention: 0 two threads per row, 1 one thread per row with P and O in tensor
+ * memory; -1 restores the default). */
 int bg_set_option(bg_context* ctx, const char* key, int64_t value);
 
 /* -- buffers: upload / materialize / release (_bridge.py:65-71; realizer.ts:1006-1041) ----- */
 int bg_upload(bg_context* ctx, const void* data, size_t nbytes, const int64_t* shape, int rank,
               int dtype, bg_handle* out);
 int bg_materialize(bg_context* ctx, bg_handle h, void* out, size_t nbytes);
+/* A buffer of the given shape and dtype whose contents the caller writes itself, on the context's stream (bg_stream),
+ * through bg_device_pointer: the destination of a device-side collective (the all-gather of row shards or of the
+ * column blocks of a wide Linear across GPUs).  No counterpart in the reference bridge, which has one device
+ * (the only "collective" there is a single-device simulation, semantic_host_graph_wgsl.ts:143-160). */
+int bg_alloc(bg_context* ctx, const int64_t* shape, int rank, int dtype, bg_handle* out);
 int bg_release(bg_context* ctx, bg_handle h);     /* idempotent; unknown handle is a no-op */
 int bg_handle_nbytes(bg_context* ctx, bg_handle h, int64_t* out);
 

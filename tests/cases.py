@@ -318,6 +318,8 @@ CASES: Dict[str, Case] = {
                                        lambda api, t, raw: configs.attention(api, t, "mask", "float16"), rtol=2e-2),
     "c4_attn_growing_f32": Case(_attn_growing(1, 2, 640, 64),
                                 lambda api, t, raw: configs.attention(api, t, "mask")),
+    # 1280 keys = 20 key tiles of 64: crosses two folds of the tensor-memory accumulator into registers
+    "c4_attn_long_f32": Case(_attn_growing(1, 1, 1280, 64), lambda api, t, raw: configs.attention(api, t, "mask")),
     "typed_attention_d64": Case(_attn_small(2, 2, 136, 64),
                                 lambda api, t, raw: api.attention_forward(t["q"], t["k"], t["v"])),
     "c4_attn_full": Case(_attn_small(1, 2, 96, 32),

@@ -120,11 +120,12 @@ ATTN16_CASES = ["c4_attn_mask_f16", "c4_attn_causal_f16", "c4_attn_mask_bf16", "
                 "c4_attn_merge_heads_bf16"]
 
 
-@pytest.mark.parametrize("variant", [0, 1, 3, 5, 7])
+@pytest.mark.parametrize("variant", [0, 1, 3, 5, 7, 15])
 @pytest.mark.parametrize("name", ATTN16_CASES)
 def test_every_16bit_attention_kernel_matches_oracle(bridge, name, variant):
     """Option attention16_kernel: 0 = one query tile per CTA; bit 0 = two query tiles per CTA, bit 1 = V consumed as an
-    MN-major operand (no transposing pass), bit 2 = P kept in tensor memory."""
+    MN-major operand (no transposing pass), bit 2 = P kept in tensor memory, bit 3 = fp32 K / V rounded to the operand
+    type inside the kernel (no staging pass at all for autocast graphs)."""
     case = CASES[name]
     t, store, _ = build_case(case)
     want = oracle_value(t, store)
@@ -135,6 +136,27 @@ def test_every_16bit_attention_kernel_matches_oracle(bridge, name, variant):
         bridge.set_option("attention16_kernel", -1)       # back to the library's default
     assert any(ln.startswith("attention_tc") for ln in bridge.last_plan_trace())
     check(case, got, want, f"{name} (attention16_kernel={variant})")
+
+
+ATTN32_CASES = ["c4_attn_mask_d64", "c4_attn_causal_d64", "c4_attn_causal_tiles", "c4_attn_mask_tiles", "c4_attn_nomask_d64",
+                "typed_attention_d64", "c4_attn_merge_heads", "c4_attn_growing_f32", "c4_attn_long_f32"]
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("name", ATTN32_CASES)
+def test_every_3xtf32_attention_kernel_matches_oracle(bridge, name, variant):
+    """Option attention32_kernel: 0 = two threads per query row, P through shared memory, P.V folded into registers
+    every tile; 1 = one thread per row, P and O in tensor memory, O folded into registers every eighth tile."""
+    case = CASES[name]
+    t, store, _ = build_case(case)
+    want = oracle_value(t, store)
+    bridge.set_option("attention32_kernel", variant)
+    try:
+        got = realize_cuda(t, bridge)
+    finally:
+        bridge.set_option("attention32_kernel", -1)
+    assert any(ln.startswith("attention_tc_3xtf32") for ln in bridge.last_plan_trace())
+    check(case, got, want, f"{name} (attention32_kernel={variant})")
 
 
 @pytest.mark.parametrize("name", ["c3_tc_f32", "c3_tc_f16", "c3_tc_bf16", "c3_tc_ragged", "c3_tc_relu", "c3_tc_rowmajor_b",
