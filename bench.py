@@ -32,6 +32,8 @@ if ROOT not in sys.path:
 
 ROWS, COLS = 16384, 4096
 METRIC = "fused-eltwise HBM GB/s, GEMM TFLOP/s, attention tok/s at 1/2/4/8 B200 vs roofline"
+# the same string in both arms; how many of the rows one step covers is a key of its own (rows_per_step)
+WORKLOAD = f"config 2: fused elementwise/reduce chains y, row-sum, row-softmax over fp32 [{ROWS},{COLS}]"
 
 
 def algorithmic_bytes(rows: int, cols: int) -> dict:
@@ -129,7 +131,7 @@ def cpu_reference_realize():
         sys.path.insert(0, ref_dir)
         try:
             import browsergrad_jit as bg
-            from tests.cases import RefApi
+            from oracle.ref_api import RefApi
             api = RefApi(bg)
 
             def run(arrays):
@@ -386,6 +388,95 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn
     return out
 
 
+def collective_extras(bridge, torch, dist, world: int, rank: int, local: int, reps: int = 5) -> dict:
+    """The data-path collectives of configuration 5 (GPT decoder, batch 64 split 8 per GPU) at N > 1, wall-clock
+    between two barriers, slowest of the ranks: (i) the hidden states of every rank's shard all-gathered on the devices
+    ([8192, 768] fp32 per rank) and (ii) the LM head ([32000, 768]) split along its output columns, each rank
+    multiplying the gathered hidden states by its own block, the logits blocks all-gathered and laid side by side.
+    Hidden states and weights are seeded synthetic values of the configuration's shapes (the cost of the exchange does
+    not depend on them).  `nccl_all_gather` is a plain all_gather_into_tensor of the same bytes between torch buffers,
+    measured in the same run, as the yardstick."""
+    from browsergrad_b200 import front, graph, sharded
+
+    def timed(fn) -> float:
+        best = None
+        for i in range(reps + 1):       # pass 0 warms up (communicator set-up, plan compilation) and is not counted
+            dist.barrier()
+            bridge.synchronize()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            fn()
+            bridge.synchronize()
+            torch.cuda.synchronize()
+            dist.barrier()
+            dt = time.perf_counter() - t0
+            if i > 0:
+                best = dt if best is None else min(best, dt)
+        t = torch.tensor([best], device=f"cuda:{local}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    rows, d_model, vocab = 8 * 1024, 768, 32000
+    rng = np.random.default_rng(400 + rank)
+    hidden = rng.standard_normal((rows, d_model), dtype=np.float32)
+    h_local = bridge.upload(hidden, hidden.shape, "float32")
+    out = {}
+    # (i) hidden states
+    gathered = []
+
+    def gather_hidden():
+        while gathered:
+            bridge.release(gathered.pop())
+        gathered.append(sharded.gather_rows_device(bridge, h_local, (rows, d_model), "float32", world * rows, device=local))
+    t_gather = timed(gather_hidden)
+    nbytes = world * rows * d_model * 4
+    recv = (world - 1) * rows * d_model * 4
+    a = torch.empty(rows * d_model, dtype=torch.float32, device=f"cuda:{local}")
+    full = torch.empty(world * rows * d_model, dtype=torch.float32, device=f"cuda:{local}")
+    t_nccl = timed(lambda: dist.all_gather_into_tensor(full, a))
+    out["hidden_gather"] = {"workload": f"all-gather of [{rows},{d_model}] fp32 hidden states per rank into [{world * rows},{d_model}] on every rank",
+                            "ms": 1e3 * t_gather, "bytes_received_per_rank": recv, "gbs_per_rank": recv / t_gather / 1e9,
+                            "bus_gbs": nbytes * (world - 1) / world / t_gather / 1e9,
+                            "nccl_all_gather": {"ms": 1e3 * t_nccl, "gbs_per_rank": recv / t_nccl / 1e9},
+                            "frac_of_nccl": t_nccl / t_gather}
+    # (ii) column-split LM head on the gathered hidden states
+    w = np.random.default_rng(401).standard_normal((vocab, d_model), dtype=np.float32) * np.float32(0.02)
+    store = graph.BufferStore()
+    table = front.resident_table(bridge) or front.DeviceBufferTable(bridge)
+    bridge._front_table = table
+    bid = "gathered_hidden"
+    table.register(bid, gathered.pop())
+    buf = graph.Node("BUFFER", (), (world * rows, d_model), "float32", bid)
+    x = graph.Tensor(graph.Node("LOAD", (buf,), buf.shape, buf.dtype, None), front._ResidentStore(store, table, bridge))
+    results = []
+
+    def lm_head():
+        while results:
+            t_out = results.pop()
+            table.release(t_out._uop.inputs[0].arg)
+        results.append(sharded.column_split_linear(bridge, x, w, None, device=local))
+    t_head = timed(lm_head)
+    m = world * rows
+    logits_bytes = m * vocab * 4
+    recv_head = logits_bytes * (world - 1) // world
+    a2 = torch.empty(m * (vocab // world), dtype=torch.float32, device=f"cuda:{local}")
+    full2 = torch.empty(m * vocab, dtype=torch.float32, device=f"cuda:{local}")
+    t_nccl2 = timed(lambda: dist.all_gather_into_tensor(full2, a2))
+    del a2, full2
+    out["lm_head_column_split"] = {"workload": f"logits [{m},{vocab}] fp32 = hidden [{m},{d_model}] . W^T, W split {vocab // world} columns per rank "
+                                               "(3xTF32), blocks all-gathered on the devices and laid side by side",
+                                   "ms": 1e3 * t_head, "bytes_received_per_rank": recv_head, "gbs_per_rank": recv_head / t_head / 1e9,
+                                   "tflops_per_rank": 2.0 * m * (vocab // world) * d_model / t_head / 1e12,
+                                   "nccl_all_gather": {"ms": 1e3 * t_nccl2, "gbs_per_rank": recv_head / t_nccl2 / 1e9},
+                                   "all_gather_share_of_time": t_nccl2 / t_head}
+    while results:
+        t_out = results.pop()
+        table.release(t_out._uop.inputs[0].arg)
+    table.release(bid)
+    bridge.release(h_local)
+    return out
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -403,8 +494,7 @@ def run_reference(args) -> None:
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"config 2: fused elementwise/reduce chains y, row-sum, row-softmax over fp32 [{ROWS},{COLS}]",
-                   "sample": sample},
+        "config": {"workload": WORKLOAD, "rows_per_step": workers * sample_rows, "sample": sample},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": workers, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -443,7 +533,9 @@ def main() -> None:
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+        # a rank that fails must not leave the others waiting for the default ten minutes
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=240))
     rows = args.rows
     bytes_step = algorithmic_bytes(rows, COLS)
     total_bytes = sum(bytes_step.values())
@@ -524,13 +616,20 @@ def main() -> None:
     if per_kernel:
         top = max(per_kernel, key=lambda k: per_kernel[k]["ms"])
         achieved = bytes_step[top] / (per_kernel[top]["ms"] * 1e-3) / 1e9
-        # DRAM read+write per launch from the ncu capture summarised in profiles/config2_pattern_kernels_rows4096.md
-        # (fp32 [4096, 4096]), scaled by the row count: traffic grows in proportion to the rows processed
-        ncu_traffic_4096_rows = {"y": 309.9e6, "rowsum": 275.3e6, "rowsoftmax": 307.8e6}
+        # DRAM read+write per launch: one ncu capture of a smaller case, kept as a tracked file that names the capture,
+        # scaled by the rows processed (traffic grows in proportion); the capture understates the write side (see its
+        # note), so the figure is floored at the algorithmic bytes
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "config2_pattern_kernels_traffic.json")
+        if os.path.exists(tpath):
+            with open(tpath) as fh:
+                cap = json.load(fh)
+            traffic = max(float(cap["bytes_per_launch"][top]) * rows / float(cap["rows"]), float(bytes_step[top]))
         roofline = {"bound": "hbm", "kernel": per_kernel[top]["name"], "achieved": achieved, "peak": peaks["hbm_gbs"],
                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                     "frac_of_nominal": achieved / NOMINAL["hbm_gbs"], "nominal_peak": NOMINAL["hbm_gbs"],
-                    "traffic": ncu_traffic_4096_rows[top] * rows / 4096.0, "algorithmic_bytes": bytes_step[top],
+                    "traffic": traffic, "traffic_source": "profiles/config2_pattern_kernels_traffic.json (scaled by rows, floored at the algorithmic bytes)",
+                    "algorithmic_bytes": bytes_step[top],
                     "per_kernel": {k: {"name": v["name"], "ms_per_launch": v["ms"],
                                        "achieved_gbs": bytes_step[k] / (v["ms"] * 1e-3) / 1e9,
                                        "frac": bytes_step[k] / (v["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"]}
@@ -623,13 +722,20 @@ def main() -> None:
                                     "tokens_per_s": world * args.attn_batch * 2048 / (attn16_ms * 1e-3)}],
                      "gemm": {"workload": mine["gemm"][0]["workload"], "plan_ms": gemm_ms,
                               "tflops": world * 2.0 * 8192 ** 3 / (gemm_ms * 1e-3) / 1e12}}
+        try:
+            coll = collective_extras(bridge, torch, dist, world, rank, local)
+            if isinstance(extra, dict):
+                extra["collectives"] = coll
+        except Exception as exc:       # every rank runs the same calls; a failure is reported, not hidden
+            if isinstance(extra, dict):
+                extra["collectives"] = {"error": repr(exc)}
 
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"config 2: fused elementwise/reduce chains y, row-sum, row-softmax over fp32 [{rows},{COLS}] per GPU",
+            "config": {"workload": WORKLOAD, "rows_per_step": world * rows, "rows_per_gpu": rows,
                        "algorithmic_bytes_per_step": total_bytes, "l2": "inputs (4 x 268 MB) exceed the 126 MB L2",
                        "parallelism": f"row-sharded x{world}, no collective"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,

@@ -91,6 +91,7 @@ SIGNATURES = {
     "bg_compile_plan_dry": (C.c_int, [C.POINTER(Plan), C.c_int, C.c_char_p, C.c_size_t]),
     "bg_cross_entropy_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int,
                                            C.c_int64, C.c_void_p, C.c_char_p, C.c_size_t]),
+    "bg_selftest_wait_timeout": (C.c_int, [C.c_void_p, C.c_int64]),
     "bg_alloc": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.c_int, C.c_int, C.POINTER(C.c_int64)]),
     "bg_stream": (C.c_void_p, [C.c_void_p]),
     "bg_device_pointer": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p)]),

@@ -90,6 +90,11 @@ class CudaBridge:
         del keep
         return int(h.value)
 
+    def selftest_wait_timeout(self, limit_cycles: int = 2_000_000) -> None:
+        """Runs the bounded device wait until it gives up; raises ``KernelError`` with status 6 (device-side wait timed
+        out).  The bridge stays usable."""
+        self._check(self._lib.bg_selftest_wait_timeout(self._ctx, int(limit_cycles)))
+
     def alloc(self, shape: Sequence[int], dtype: str) -> int:
         """A device buffer the caller fills itself through ``device_pointer`` on ``stream()`` (the destination of a
         device-side collective); released like any other handle."""

@@ -195,6 +195,26 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   auto need_b = [&](int j) { return s_cls[n_kv + j] != 0; };
   auto next_union = [&](int j) { while (j < n_kv && !need_a(j) && !need_b(j)) ++j; return j; };
 
+  // The softmax threads fetch their query rows now: the loads are in flight while the barriers are set up and tensor
+  // memory is allocated (64 fp32 values, or 64 16-bit values, per thread).
+  uint4 qraw[16];
+  bool q_row_ok = false;
+  if (warp >= 4 && warp < 12) {
+    const int g = (warp - 4) >> 2;
+    const int row = (2 * pair + g) * kQRows + (warp & 3) * 32 + lane;
+    q_row_ok = (g == 0 || has_b) && row < p.Sq;
+    const long long qoff = (long long)b * p.q_sb + (long long)h * p.q_sh + (long long)(q_row_ok ? row : 0) * p.q_ss;
+    if (p.q_f32) {
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(p.q_ptr) + qoff);
+#pragma unroll
+      for (int c = 0; c < 16; ++c) qraw[c] = q_row_ok ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
+    } else {
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q_ptr) + qoff);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) qraw[c] = q_row_ok ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+
   if (threadIdx.x == 0) {
     for (int g = 0; g < 2; ++g) {
       mbar_init(&q_full[g], 4);
@@ -385,26 +405,19 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     const unsigned char* cls = s_cls + g * n_kv;
 
     if (active) {
-      // ---- this thread's query row -> shared memory in the operand layout ---------------------------------------
+      // ---- this thread's query row (fetched at the top of the kernel) -> shared memory in the operand layout ----
       unsigned char* qrow = sQ + g * C::QBytes + r_in_tile * 128;
-      const long long qoff = (long long)b * p.q_sb + (long long)h * p.q_sh + (long long)(row_ok ? row : 0) * p.q_ss;
       if (p.q_f32) {
-        const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q_ptr) + qoff);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
-          if (row_ok) { lo = __ldg(src + 2 * c); hi = __ldg(src + 2 * c + 1); }
+          const uint4 lo = qraw[2 * c], hi = qraw[2 * c + 1];
           *reinterpret_cast<uint4*>(qrow + ((c ^ sw) << 4)) =
-              make_uint4(pack16<BF16>(lo.x, lo.y), pack16<BF16>(lo.z, lo.w), pack16<BF16>(hi.x, hi.y), pack16<BF16>(hi.z, hi.w));
+              make_uint4(pack16<BF16>(__uint_as_float(lo.x), __uint_as_float(lo.y)), pack16<BF16>(__uint_as_float(lo.z), __uint_as_float(lo.w)),
+                         pack16<BF16>(__uint_as_float(hi.x), __uint_as_float(hi.y)), pack16<BF16>(__uint_as_float(hi.z), __uint_as_float(hi.w)));
         }
       } else {
-        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q_ptr) + qoff);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint4 v = make_uint4(0u, 0u, 0u, 0u);
-          if (row_ok) v = __ldg(src + c);
-          *reinterpret_cast<uint4*>(qrow + ((c ^ sw) << 4)) = v;
-        }
+        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(qrow + ((c ^ sw) << 4)) = qraw[c];
       }
       fence_async_smem();
       __syncwarp();

@@ -266,6 +266,8 @@ bool tc_gemm_supported(int64_t M, int64_t N, int64_t K, int ab_dtype);
 cudaError_t launch_gemm_tc(const TcGemm& g, int* status, cudaStream_t s);
 // 1 to 3 problems that share A, M, N, K, dtypes and the epilogue kind and differ in B, bias and C, as one launch.
 cudaError_t launch_gemm_tc_group(const TcGemm* gs, int n_prob, int* status, cudaStream_t s);
+// Self test of the bounded device wait: a wait of `limit_cycles` on a barrier nothing arrives on; sets *status.
+cudaError_t launch_wait_timeout_selftest(long long limit_cycles, int* status, cudaStream_t s);
 // hi = tf32(x) (round to nearest), lo = x - hi, for fp32 or fp64 input; optional transpose is not done here.
 cudaError_t launch_tf32_split(const void* src, int src_dtype, float* hi, float* lo, int64_t n, cudaStream_t s);
 // dst (f16 / bf16) = round-to-nearest-even(src fp32), dense, eight elements per thread step.

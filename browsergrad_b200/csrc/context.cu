@@ -42,6 +42,9 @@ static void flush_block_cache(bg_context* ctx) {
 
 int dev_alloc(bg_context* ctx, int64_t logical_bytes, void** out) {
   const size_t padded = padded_size(logical_bytes);
+  // test hook (option "fail_allocation_after"): the n-th allocation from now reports what an exhausted device would
+  if (ctx->fail_alloc_countdown > 0 && --ctx->fail_alloc_countdown == 0)
+    return cuda_fail(ctx, cudaErrorMemoryAllocation, "device allocation");
   auto hit = ctx->block_cache.find(padded);
   if (hit != ctx->block_cache.end()) {
     *out = hit->second;
@@ -392,6 +395,10 @@ int bg_set_option(bg_context* ctx, const char* key, int64_t value) {
     if (value < -1 || value > 1) return fail(ctx, BG_ERR_INVALID, "set_option: attention32_kernel is 0, 1, or -1 for the default");
     g_attn32_variant = value < 0 ? kAttn32DefaultVariant : (int)value;
   }
+  else if (k == "fail_allocation_after") {
+    if (value < 0) return fail(ctx, BG_ERR_INVALID, "set_option: fail_allocation_after takes a count (0 = off)");
+    ctx->fail_alloc_countdown = value;
+  }
   else if (k == "static_patterns") { ctx->static_patterns = value != 0; ctx->plan_cache.clear(); }
   else if (k == "gemm_groups") { ctx->gemm_groups = value != 0; ctx->plan_cache.clear(); }
   else return fail(ctx, BG_ERR_INVALID, "set_option: unknown option '" + k + "'");
@@ -420,6 +427,19 @@ int bg_upload(bg_context* ctx, const void* data, size_t nbytes, const int64_t* s
     return rc;
   }
   *out = mint_handle(ctx, p, bytes, dtype, shape, rank);
+  return BG_OK;
+}
+
+int bg_selftest_wait_timeout(bg_context* ctx, int64_t limit_cycles) {
+  if (!ctx) return BG_ERR_INVALID;
+  if (limit_cycles < 1000 || limit_cycles > 2000000000ll) return fail(ctx, BG_ERR_INVALID, "selftest_wait_timeout: limit outside [1e3, 2e9] cycles");
+  cudaSetDevice(ctx->device);
+  cudaError_t e = launch_wait_timeout_selftest(limit_cycles, ctx->d_status, ctx->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "selftest_wait_timeout");
+  const int st = take_device_status(ctx);
+  if (st != 0) return fail(ctx, st, device_status_message(st));
   return BG_OK;
 }
 

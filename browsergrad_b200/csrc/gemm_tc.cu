@@ -895,4 +895,26 @@ cudaError_t launch_tf32_split(const void* src, int src_dtype, float* hi, float* 
   return cudaGetLastError();
 }
 
+// One CTA waits, with the bounded wait every tensor-core kernel uses, on a barrier that nothing ever arrives on, and
+// reports the give-up through the status word exactly as those kernels do: the host-visible half of the protocol
+// (status word -> BG_ERR_DEVICE_TIMEOUT, context usable afterwards) can be exercised without a fault.
+__global__ void wait_timeout_selftest_kernel(long long limit_cycles, int* status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    tc::mbar_init(&bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) tc::mbar_wait(&bar, 0, &abort_flag, limit_cycles);
+  __syncthreads();
+  if (abort_flag && threadIdx.x == 0) atomicExch(status, BG_ERR_DEVICE_TIMEOUT);
+}
+
+cudaError_t launch_wait_timeout_selftest(long long limit_cycles, int* status, cudaStream_t s) {
+  wait_timeout_selftest_kernel<<<1, 32, 0, s>>>(limit_cycles, status);
+  return cudaGetLastError();
+}
+
 }  // namespace bg

@@ -72,6 +72,8 @@ struct bg_context {
   std::unordered_multimap<size_t, void*> block_cache;
   size_t block_cache_bytes = 0;
   size_t block_cache_cap = (size_t)16 << 30;
+  // fault injection on the host (tests): the n-th device allocation from now fails as an exhausted device would
+  int64_t fail_alloc_countdown = 0;
 };
 
 namespace bg {

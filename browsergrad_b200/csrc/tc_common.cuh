@@ -29,12 +29,12 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: false when the deadline passes (the caller then abandons its role).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long limit = kWaitCycles) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try(bar, parity)) {
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > limit) {
       *abort_flag = 1;
       return false;
     }

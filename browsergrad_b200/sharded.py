@@ -142,6 +142,50 @@ def gather_rows_device(bridge: Any, handle: int, local_shape: Sequence[int], dty
     return out
 
 
+def resident_handle(tensor: Any) -> int:
+    """Bridge handle behind a tensor returned by ``front.realize_cuda_resident``."""
+    buf = tensor._uop.inputs[0] if tensor._uop.op == "LOAD" else tensor._uop
+    h = tensor._store._table.get(buf.arg)
+    if h is None:
+        raise ValueError(f"buffer {buf.arg!r} is not resident on the device")
+    return h
+
+
+def column_split_linear(bridge: Any, x: Any, weight: np.ndarray, bias: Optional[np.ndarray], *, group: Any = None,
+                        device: int = 0) -> Any:
+    """``x @ weight.T + bias`` for a very wide ``weight`` [N, K] (an LM head), split along N over the ranks: every rank
+    multiplies the same ``x`` [M, K] (a graph tensor; device-resident or not) by its own block of ``N / world`` rows of
+    ``weight`` held in its own HBM, the [M, N / world] blocks are all-gathered on the devices (NCCL; no kernel reads a
+    peer's memory) and one strided copy per rank lays them side by side.  Returns a device-resident graph tensor
+    [M, N] on every rank (``front.materialize_resident`` fetches it).  The per-element products and their order are
+    those of the unsplit Linear, so the result is bit-identical to it."""
+    from . import front, graph
+    dist = _dist()
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    n_total, k = int(weight.shape[0]), int(weight.shape[1])
+    if n_total % world:
+        raise ValueError(f"column_split_linear: {n_total} output columns do not divide over {world} ranks")
+    n_r = n_total // world
+    m = int(x.shape[0])
+    store = x._store
+    w_r = graph.from_numpy(np.ascontiguousarray(weight[rank * n_r:(rank + 1) * n_r]), store)
+    b_r = graph.from_numpy(np.ascontiguousarray(bias[rank * n_r:(rank + 1) * n_r]), store) if bias is not None else None
+    local = front.realize_cuda_resident(graph.linear(x, w_r, b_r), bridge)          # [M, n_r] on this rank's device
+    h_local = resident_handle(local)
+    # all-gather as row blocks of a [world * M, n_r] array, then [world, M, n_r] -> [M, world, n_r] = [M, N]
+    h_all = gather_rows_device(bridge, h_local, (m, n_r), local.dtype, world * m, group=group, device=device)
+    local._store._table.release(local._uop.inputs[0].arg)
+    table = local._store._table
+    bid = f"resident_{h_all}"
+    table.register(bid, h_all)
+    buf = graph.Node("BUFFER", (), (world, m, n_r), local.dtype, bid)
+    blocks = graph.Tensor(graph.Node("LOAD", (buf,), buf.shape, buf.dtype, None), local._store)
+    out = front.realize_cuda_resident(blocks.permute(1, 0, 2).reshape(m, n_total), bridge)
+    table.release(bid)
+    return out
+
+
 def combine_mean(local_mean: np.ndarray, local_count: int, group: Any = None, device: Optional[str] = None) -> np.ndarray:
     """Global mean from per-rank means over ``local_count`` contributing positions (one all-reduce of
     (sum, count)).  A rank with no contributing position (its local mean is 0/0 = NaN) adds (0, 0); the

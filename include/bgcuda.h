@@ -243,6 +243,11 @@ int bg_cross_entropy_noalloc(const float* logits, const int64_t* targets, float*
  * kernels selectable).  Used to test the plan compiler
  * on machines without a GPU. */
 int bg_compile_plan_dry(const bg_plan* plan, int fusion, char* out, size_t capacity);
+/* Diagnostics of the failure paths.  One small kernel waits `limit_cycles` SM cycles, with the bounded wait of the
+ * tensor-core kernels, on a barrier nothing arrives on and gives up: the call returns BG_ERR_DEVICE_TIMEOUT through the
+ * same status word those kernels use, and the context stays usable.  (Option "fail_allocation_after" = n makes the
+ * n-th device allocation from now fail with BG_ERR_OOM.)  No counterpart in the reference bridge. */
+int bg_selftest_wait_timeout(bg_context* ctx, int64_t limit_cycles);
 /* The CUDA stream all work of this context is ordered on (a cudaStream_t). */
 void* bg_stream(bg_context* ctx);
 /* Raw device pointer behind a handle, for callers that time kernels themselves. */
