@@ -214,13 +214,16 @@ def cpu_baseline(sample_rows: int, repeats: int = 1) -> dict:
             "seconds": best, "single_process_value": nbytes / single / 1e9}
 
 
-def time_plan(bridge, torch, stream, graph_root, store, front, steps: int, warmup: int = 3):
+EXTRA_WARMUP = 3   # untimed realizations before each extra workload; a profiler capture lowers it (--extra-warmup)
+
+
+def time_plan(bridge, torch, stream, graph_root, store, front, steps: int, warmup: int = -1):
     """Average device time (ms) of one realization with resident leaves, plus the per-kernel profile.
     The plan is timed without per-unit events; the profile comes from a second pass of the same length."""
     prepared, plan = front.plan_for(graph_root._uop)
     table = front.DeviceBufferTable(bridge)
     inputs = front._bind_inputs(plan, store, table, True)
-    for _ in range(warmup):
+    for _ in range(EXTRA_WARMUP if warmup < 0 else warmup):
         bridge.release(bridge.run_tensor_plan_resident(plan, inputs, prepared.dtype))
     bridge.synchronize()
     bridge.flushProfiles()
@@ -379,7 +382,7 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn
         t = {k: graph.from_numpy(v, store) for k, v in arrays.items()}
         root = configs.gpt_forward(graph, t, meta)
         gpt_steps = max(3, steps // 2)
-        ms, prof, trace = time_plan(bridge, torch, stream, root, store, front, gpt_steps, warmup=3)
+        ms, prof, trace = time_plan(bridge, torch, stream, root, store, front, gpt_steps)
         top = sorted(prof, key=lambda p: -p["ms"])[:6]
         out["gpt"].append({"workload": "GPT decoder forward 12L d768 h12 mlp3072 V32000 seq1024, batch 8 (one GPU's shard of 64), fp32 graph (3xTF32)",
                            "tokens_per_s": 8 * 1024 / (ms * 1e-3), "plan_ms": ms, "units": len(trace),
@@ -514,6 +517,7 @@ def main() -> None:
     ap.add_argument("--only", default="", help="comma-separated extra workloads to run instead of the main benchmark: "
                     + ", ".join(EXTRA_NAMES))
     ap.add_argument("--attn-batch", type=int, default=16)
+    ap.add_argument("--extra-warmup", type=int, default=3, help="untimed realizations before each --only workload")
     ap.add_argument("--e2e-chunks", type=int, default=16)
     ap.add_argument("--e2e-lanes", type=int, default=4)
     ap.add_argument("--option", action="append", default=[], metavar="KEY=VALUE",
@@ -546,6 +550,8 @@ def main() -> None:
         bridge.set_option(key, int(val))
     stream = torch.cuda.ExternalStream(bridge.stream(), device=local)
     if args.only:
+        global EXTRA_WARMUP
+        EXTRA_WARMUP = max(0, args.extra_warmup)
         names = [n for n in args.only.split(",") if n]
         bad = [n for n in names if n not in EXTRA_NAMES + ("gemm_widths",)]
         if bad:

@@ -53,14 +53,20 @@ enum EwOp : uint8_t {
   E_SUB,        // dst <- a - b            (ADD of a NEG)
   E_RELU,       // dst <- a > 0 ? a : +0   (CONST 0, CMP gt, WHERE)
   E_EXPNEG,     // dst <- exp(-a)          (NEG, EXP)
+  E_COPY,       // dst <- a                (a dense fp32 LOAD or STORE after operand folding)
   E_OPCOUNT
 };
 
-// Register fields of fp32 instructions may name global memory directly instead of a shared-memory
-// register: a source 0x80|k reads input k (dense fp32, vector-aligned) at the element's own linear
-// index, a destination 0x80|k writes output k.  The compiler folds single-use LOADs and final
-// STOREs this way, so a value that is consumed once never round-trips through shared memory.
+// Register fields of fp32 instructions may name something else than a shared-memory register:
+//   0x80|k   source: input k (dense fp32, vector-aligned) read at the element's own linear index;
+//            destination: output k written there.  The compiler folds single-use LOADs and final
+//            STOREs this way, so a value that is consumed once never round-trips through shared memory;
+//   0xC0|k   source: consts[k] as an fp32 splat;
+//   kEwAcc   the accumulator: the value the previous instruction left in real registers.  A result
+//            whose only reader is the next instruction goes there and nowhere else.
 constexpr uint8_t kEwDirect = 0x80;
+constexpr uint8_t kEwConst = 0xC0;
+constexpr uint8_t kEwAcc = 0x7e;
 
 struct EwInstr {
   uint8_t op, type, dst, a, b, c;
@@ -300,10 +306,10 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
 // Which 16-bit attention kernel runs (attn_tc.cu): bit 0 the two-query-tile kernel, bit 1 V as an MN-major operand,
 // bit 2 P kept in tensor memory, bit 3 (with bits 1 and 2) fp32 K / V converted inside the kernel; 0 is the single-tile kernel.
 extern int g_attn16_variant;
-constexpr int kAttn16DefaultVariant = 1;
+constexpr int kAttn16DefaultVariant = 15;
 // Which 3xTF32 attention kernel runs: 0 two threads per row, P through shared memory; 1 one thread per row, P and O in
 // tensor memory.
 extern int g_attn32_variant;
-constexpr int kAttn32DefaultVariant = 0;
+constexpr int kAttn32DefaultVariant = 1;
 
 }  // namespace bg

@@ -21,7 +21,16 @@
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
+#include <map>
+#include <mutex>
+#include <tuple>
+
 namespace bg {
+
+// CTAs per SM the flat kernel is compiled for (caps its registers per thread at 65536 / (256 * this)).
+#ifndef BG_EW_MIN_CTAS
+#define BG_EW_MIN_CTAS 3
+#endif
 
 constexpr int kBlock = 256;
 constexpr int kVec = 4;
@@ -38,6 +47,13 @@ struct RegFile {
   __device__ __forceinline__ RegFile(char* base, int U_, int planes)
       : tbase(base + threadIdx.x * 16), U(U_), rstride((uint32_t)U_ * planes * (kBlock * 16)),
         ustride((uint32_t)planes * (kBlock * 16)) {}
+  // The same register file seen from chunk u0 on, n chunks long.
+  __device__ __forceinline__ RegFile group(int u0, int n) const {
+    RegFile g = *this;
+    g.tbase += (uint32_t)u0 * ustride;
+    g.U = n;
+    return g;
+  }
   __device__ __forceinline__ char* slot(int r, int u, int h) const {
     return tbase + (uint32_t)r * rstride + (uint32_t)u * ustride + (uint32_t)h * (kBlock * 16);
   }
@@ -355,7 +371,7 @@ __device__ __forceinline__ double fdiv(double a, double b) { return __ddiv_rn(a,
 
 // The opcode switch sits outside the chunk loop: one decode per instruction per pass, then the
 // same operation over all U chunks (unrolled when UT > 0).
-#define BG_FOR_U _Pragma("unroll") for (int u = 0; u < nU; ++u)
+#define BG_FOR_U _Pragma("unroll 4") for (int u = 0; u < nU; ++u)
 #define BG_UNARY(T, EXPR)                                   \
   BG_FOR_U {                                                \
     V4<T> a = rget<T>(rf, ins.a, u), r;                     \
@@ -369,130 +385,171 @@ __device__ __forceinline__ double fdiv(double a, double b) { return __ddiv_rn(a,
     rput<T>(rf, ins.dst, u, r);                             \
   }
 
-// fp32 operand fetch / result store with the direct-global encoding (kEwDirect).
-__device__ __forceinline__ V4<float> getf(const EwProgram& p, const RegFile& rf, const Pos& pos, int r, int u) {
+// ------------------------------------------------------------------------------------
+// fp32 fast path
+// ------------------------------------------------------------------------------------
+// fp32 arithmetic, compares, selects and dense copies work on the UT chunks of a pass at once, with
+// their operands in real registers.  An operand field names a shared-memory register, input k of the
+// program (read straight from global memory), a constant, or the accumulator: the registers the
+// previous instruction left its result in.  A result field names a shared-memory register, output k
+// (written straight to global memory) or the accumulator alone.  Lanes beyond the end of the tensor
+// or row read zero and are not stored; what is computed on them is never seen.
+template <int UT>
+__device__ __forceinline__ void fast_fetch(const EwProgram& p, const RegFile& rf, const Pos& pos, bool full, int r,
+                                           float4 (&x)[UT]) {
   if (r & kEwDirect) {
-    const float* src = reinterpret_cast<const float*>(p.inputs[r & 0x7f].ptr) + pos.idx(u);
-    const int nv = pos.nvalid(u);
-    if (nv == 4) {
-      float4 t = __ldg(reinterpret_cast<const float4*>(src));
-      return {{t.x, t.y, t.z, t.w}};
-    }
-    V4<float> x;
+    if ((r & kEwConst) == kEwConst) {
+      const float f = (float)__longlong_as_double(p.consts[r & 0x3f]);
 #pragma unroll
-    for (int e = 0; e < 4; ++e) x.v[e] = e < nv ? src[e] : 0.f;
-    return x;
-  }
-  return rget<float>(rf, r, u);
-}
-__device__ __forceinline__ void putf(const EwProgram& p, const RegFile& rf, const Pos& pos, int r, int u, const V4<float>& x) {
-  if (r & kEwDirect) {
-    float* dst = reinterpret_cast<float*>(p.outputs[r & 0x7f].ptr) + pos.idx(u);
-    const int nv = pos.nvalid(u);
-    if (nv == 4) {
-      *reinterpret_cast<float4*>(dst) = make_float4(x.v[0], x.v[1], x.v[2], x.v[3]);
+      for (int u = 0; u < UT; ++u) x[u] = make_float4(f, f, f, f);
+      return;
+    }
+    const float* src = reinterpret_cast<const float*>(p.inputs[r & 0x3f].ptr) + pos.idx0;
+    if (full) {
+#pragma unroll
+      for (int u = 0; u < UT; ++u) x[u] = __ldg(reinterpret_cast<const float4*>(src) + u * (kChunk / 4));
     } else {
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
-        if (e < nv) dst[e] = x.v[e];
+      for (int u = 0; u < UT; ++u) {
+        const int nv = pos.nvalid(u);
+        const float* q = src + u * kChunk;
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (nv == 4) {
+          t = __ldg(reinterpret_cast<const float4*>(q));
+        } else if (nv > 0) {
+          t.x = q[0];
+          if (nv > 1) t.y = q[1];
+          if (nv > 2) t.z = q[2];
+        }
+        x[u] = t;
+      }
     }
     return;
   }
-  rput<float>(rf, r, u, x);
+  const char* s = rf.tbase + (uint32_t)r * rf.rstride;
+#pragma unroll
+  for (int u = 0; u < UT; ++u) x[u] = *reinterpret_cast<const float4*>(s + u * rf.ustride);
 }
+
+template <int UT>
+__device__ __forceinline__ void fast_put(const EwProgram& p, const RegFile& rf, const Pos& pos, bool full, int r,
+                                         const float4 (&x)[UT]) {
+  if (r == kEwAcc) return;
+  if (r & kEwDirect) {
+    float* dst = reinterpret_cast<float*>(p.outputs[r & 0x3f].ptr) + pos.idx0;
+    if (full) {
+#pragma unroll
+      for (int u = 0; u < UT; ++u) reinterpret_cast<float4*>(dst)[u * (kChunk / 4)] = x[u];
+    } else {
+#pragma unroll
+      for (int u = 0; u < UT; ++u) {
+        const int nv = pos.nvalid(u);
+        float* q = dst + u * kChunk;
+        if (nv == 4) {
+          *reinterpret_cast<float4*>(q) = x[u];
+        } else if (nv > 0) {
+          q[0] = x[u].x;
+          if (nv > 1) q[1] = x[u].y;
+          if (nv > 2) q[2] = x[u].z;
+        }
+      }
+    }
+    return;
+  }
+  char* d = rf.tbase + (uint32_t)r * rf.rstride;
+#pragma unroll
+  for (int u = 0; u < UT; ++u) *reinterpret_cast<float4*>(d + u * rf.ustride) = x[u];
+}
+
+// f over every element of the pass.
+template <int UT, typename F>
+__device__ __forceinline__ void map1(float4 (&a)[UT], F f) {
+#pragma unroll
+  for (int u = 0; u < UT; ++u) a[u] = make_float4(f(a[u].x), f(a[u].y), f(a[u].z), f(a[u].w));
+}
+template <int UT, typename F>
+__device__ __forceinline__ void map2(float4 (&a)[UT], const float4 (&b)[UT], F f) {
+#pragma unroll
+  for (int u = 0; u < UT; ++u) a[u] = make_float4(f(a[u].x, b[u].x), f(a[u].y, b[u].y), f(a[u].z, b[u].z), f(a[u].w, b[u].w));
+}
+// Bulky bodies exist once, out of line, and are called per chunk.
+__device__ __noinline__ float4 div4(float4 a, float4 b) { return make_float4(fdiv(a.x, b.x), fdiv(a.y, b.y), fdiv(a.z, b.z), fdiv(a.w, b.w)); }
+__device__ __noinline__ float4 log4(float4 a) { return make_float4(logf(a.x), logf(a.y), logf(a.z), logf(a.w)); }
+__device__ __noinline__ float4 sin4(float4 a) { return make_float4(sinf(a.x), sinf(a.y), sinf(a.z), sinf(a.w)); }
+__device__ __noinline__ float4 cos4(float4 a) { return make_float4(cosf(a.x), cosf(a.y), cosf(a.z), cosf(a.w)); }
+__device__ __forceinline__ float sign1(float x) { return x != x ? x : (float)((x > 0) - (x < 0)); }
+__device__ __noinline__ float4 sign4(float4 a) { return make_float4(sign1(a.x), sign1(a.y), sign1(a.z), sign1(a.w)); }
 
 template <int UT, typename F>
-__device__ __forceinline__ void f32_unary(const EwProgram& p, const EwInstr ins, const RegFile& rf, const Pos& pos, F f) {
-  constexpr int N = UT > 0 ? UT : 1;
-  if (UT > 0) {
-    // fetch every chunk first: independent global / shared loads are in flight together
-    V4<float> a[N];
+__device__ __forceinline__ void cmp_put(const RegFile& rf, int dst, const float4 (&a)[UT], const float4 (&b)[UT], F f) {
+  char* d = rf.tbase + (uint32_t)dst * rf.rstride;
 #pragma unroll
-    for (int u = 0; u < N; ++u) a[u] = getf(p, rf, pos, ins.a, u);
-#pragma unroll
-    for (int u = 0; u < N; ++u) {
-      V4<float> r;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = f(a[u].v[e]);
-      putf(p, rf, pos, ins.dst, u, r);
-    }
+  for (int u = 0; u < UT; ++u)
+    *reinterpret_cast<uint4*>(d + u * rf.ustride) =
+        make_uint4(f(a[u].x, b[u].x), f(a[u].y, b[u].y), f(a[u].z, b[u].z), f(a[u].w, b[u].w));
+}
+
+// Opcodes the fast path executes when the instruction's class is fp32.
+constexpr uint32_t kFastOps = (1u << E_ADD) | (1u << E_MUL) | (1u << E_DIV) | (1u << E_NEG) | (1u << E_EXP) | (1u << E_LOG) |
+                              (1u << E_ABS) | (1u << E_SIGN) | (1u << E_SIN) | (1u << E_COS) | (1u << E_CMP) | (1u << E_WHERE) |
+                              (1u << E_SUB) | (1u << E_RELU) | (1u << E_EXPNEG) | (1u << E_COPY);
+constexpr uint32_t kTwoOperandOps = (1u << E_ADD) | (1u << E_MUL) | (1u << E_DIV) | (1u << E_SUB) | (1u << E_CMP) | (1u << E_WHERE);
+static_assert(E_OPCOUNT <= 32, "opcode masks are 32 bits wide");
+
+template <int UT>
+__device__ __forceinline__ void fast_instr(const EwProgram& p, const EwInstr ins, const RegFile& rf, const Pos& pos, bool full,
+                                           float4 (&acc)[UT]) {
+  const int op = ins.op;
+  const int ra = op == E_WHERE ? ins.b : ins.a;
+  if (ra != kEwAcc) fast_fetch<UT>(p, rf, pos, full, ra, acc);
+  float4 b[UT];
+  if ((kTwoOperandOps >> op) & 1u) {
+    fast_fetch<UT>(p, rf, pos, full, op == E_WHERE ? ins.c : ins.b, b);
   } else {
-#pragma unroll 1
-    for (int u = 0; u < rf.U; ++u) {
-      V4<float> a = getf(p, rf, pos, ins.a, u), r;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = f(a.v[e]);
-      putf(p, rf, pos, ins.dst, u, r);
+    for (int u = 0; u < UT; ++u) b[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  switch (op) {
+#define BG_CALL4(FN) _Pragma("unroll") for (int u = 0; u < UT; ++u) acc[u] = FN
+    case E_ADD: map2<UT>(acc, b, [](float x, float y) { return fadd(x, y); }); break;
+    case E_SUB: map2<UT>(acc, b, [](float x, float y) { return fadd(x, -y); }); break;
+    case E_MUL: map2<UT>(acc, b, [](float x, float y) { return fmul(x, y); }); break;
+    case E_DIV: BG_CALL4(div4(acc[u], b[u])); break;
+    case E_NEG: map1<UT>(acc, [](float x) { return -x; }); break;
+    case E_RELU: map1<UT>(acc, [](float x) { return x > 0.f ? x : 0.f; }); break;
+    case E_EXPNEG:
+      map1<UT>(acc, [](float x) { return -x; });
+      // fall through
+    case E_EXP: map1<UT>(acc, [](float x) { return expf(x); }); break;
+    case E_LOG: BG_CALL4(log4(acc[u])); break;
+    case E_ABS: map1<UT>(acc, [](float x) { return x < 0 ? -x : (x == 0 ? 0.f : x); }); break;
+    case E_SIGN: BG_CALL4(sign4(acc[u])); break;
+    case E_SIN: BG_CALL4(sin4(acc[u])); break;
+    case E_COS: BG_CALL4(cos4(acc[u])); break;
+#undef BG_CALL4
+    case E_WHERE: {
+      const char* c = rf.tbase + (uint32_t)ins.a * rf.rstride;
+#pragma unroll
+      for (int u = 0; u < UT; ++u) {
+        const uint4 m = *reinterpret_cast<const uint4*>(c + u * rf.ustride);
+        acc[u] = make_float4(m.x ? acc[u].x : b[u].x, m.y ? acc[u].y : b[u].y, m.z ? acc[u].z : b[u].z, m.w ? acc[u].w : b[u].w);
+      }
+      break;
     }
+    case E_CMP:
+      // the result is a predicate register in shared memory; the accumulator keeps operand a
+      switch (ins.aux) {
+        case BG_CMP_EQ: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x == y); }); break;
+        case BG_CMP_NE: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x != y); }); break;
+        case BG_CMP_LT: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x < y); }); break;
+        case BG_CMP_LE: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x <= y); }); break;
+        case BG_CMP_GT: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x > y); }); break;
+        default: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x >= y); }); break;
+      }
+      return;
+    default: break;   // E_COPY
   }
-}
-
-template <int UT, typename F>
-__device__ __forceinline__ void f32_binary(const EwProgram& p, const EwInstr ins, const RegFile& rf, const Pos& pos, F f) {
-  constexpr int N = UT > 0 ? UT : 1;
-  if (UT > 0) {
-    V4<float> a[N], b[N];
-#pragma unroll
-    for (int u = 0; u < N; ++u) { a[u] = getf(p, rf, pos, ins.a, u); b[u] = getf(p, rf, pos, ins.b, u); }
-#pragma unroll
-    for (int u = 0; u < N; ++u) {
-      V4<float> r;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = f(a[u].v[e], b[u].v[e]);
-      putf(p, rf, pos, ins.dst, u, r);
-    }
-  } else {
-#pragma unroll 1
-    for (int u = 0; u < rf.U; ++u) {
-      V4<float> a = getf(p, rf, pos, ins.a, u), b = getf(p, rf, pos, ins.b, u), r;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) r.v[e] = f(a.v[e], b.v[e]);
-      putf(p, rf, pos, ins.dst, u, r);
-    }
-  }
-}
-
-template <int UT>
-__device__ __forceinline__ void f32_instr(const EwProgram& p, const EwInstr ins, const RegFile& rf, const Pos& pos) {
-  switch (ins.op) {
-    case E_ADD: f32_binary<UT>(p, ins, rf, pos, [](float x, float y) { return fadd(x, y); }); break;
-    case E_SUB: f32_binary<UT>(p, ins, rf, pos, [](float x, float y) { return fadd(x, -y); }); break;
-    case E_MUL: f32_binary<UT>(p, ins, rf, pos, [](float x, float y) { return fmul(x, y); }); break;
-    case E_DIV: f32_binary<UT>(p, ins, rf, pos, [](float x, float y) { return fdiv(x, y); }); break;
-    case E_NEG: f32_unary<UT>(p, ins, rf, pos, [](float x) { return -x; }); break;
-    case E_RELU: f32_unary<UT>(p, ins, rf, pos, [](float x) { return x > 0.f ? x : 0.f; }); break;
-    case E_EXP: f32_unary<UT>(p, ins, rf, pos, [](float x) { return expf(x); }); break;
-    case E_EXPNEG: f32_unary<UT>(p, ins, rf, pos, [](float x) { return expf(-x); }); break;
-    case E_LOG: f32_unary<UT>(p, ins, rf, pos, [](float x) { return logf(x); }); break;
-    case E_ABS: f32_unary<UT>(p, ins, rf, pos, [](float x) { return x < 0 ? -x : (x == 0 ? 0.f : x); }); break;
-    case E_SIGN: f32_unary<UT>(p, ins, rf, pos, [](float x) { return x != x ? x : (float)((x > 0) - (x < 0)); }); break;
-    case E_SIN: f32_unary<UT>(p, ins, rf, pos, [](float x) { return sinf(x); }); break;
-    default: f32_unary<UT>(p, ins, rf, pos, [](float x) { return cosf(x); }); break;
-  }
-}
-
-template <int UT>
-__device__ __forceinline__ void f32_where(const EwProgram& p, const EwInstr ins, const RegFile& rf, const Pos& pos) {
-  const int nU = UT > 0 ? UT : rf.U;
-  BG_FOR_U {
-    V4<uint32_t> c = rget<uint32_t>(rf, ins.a, u);
-    V4<float> x = getf(p, rf, pos, ins.b, u), y = getf(p, rf, pos, ins.c, u), r;
-#pragma unroll
-    for (int e = 0; e < 4; ++e) r.v[e] = c.v[e] ? x.v[e] : y.v[e];
-    putf(p, rf, pos, ins.dst, u, r);
-  }
-}
-
-template <int UT>
-__device__ __forceinline__ void f32_cmp(const EwProgram& p, const EwInstr ins, const RegFile& rf, const Pos& pos) {
-  const int nU = UT > 0 ? UT : rf.U;
-  BG_FOR_U {
-    V4<float> a = getf(p, rf, pos, ins.a, u), b = getf(p, rf, pos, ins.b, u);
-    V4<uint32_t> r;
-#pragma unroll
-    for (int e = 0; e < 4; ++e) r.v[e] = cmp_op<float>(a.v[e], b.v[e], ins.aux);
-    rput<uint32_t>(rf, ins.dst, u, r);
-  }
+  fast_put<UT>(p, rf, pos, full, ins.dst, acc);
 }
 
 template <int UT, typename T>
@@ -583,10 +640,19 @@ template <typename S> __device__ __forceinline__ void cvt_from(const EwInstr ins
   }
 }
 
-// Less common instructions, kept out of line so the hot switch stays small.
-__device__ __noinline__ void misc_instr(const EwProgram& p, const EwInstr ins, const RegFile rf) {
+// Everything outside the fp32 fast path, out of line and shared by every kernel: loads and stores of any
+// dtype and addressing mode, constants, conversions, 64-bit and boolean arithmetic.
+__device__ __noinline__ void slow_instr(const EwProgram& p, const EwInstr ins, const RegFile rf, const Pos pos) {
   const int nU = rf.U;
   switch (ins.op) {
+    case E_LOAD:
+#pragma unroll 1
+      for (int u = 0; u < nU; ++u) load_chunk(p, ins, rf, u, ChunkPos{pos.idx(u), pos.nvalid(u)});
+      break;
+    case E_STORE:
+#pragma unroll 1
+      for (int u = 0; u < nU; ++u) store_chunk(p, ins, rf, u, ChunkPos{pos.idx(u), pos.nvalid(u)});
+      break;
     case E_CONST: {
       const int64_t bits = p.consts[ins.aux];
 #pragma unroll 1
@@ -674,70 +740,26 @@ __device__ __noinline__ void misc_instr(const EwProgram& p, const EwInstr ins, c
   }
 }
 
-// One instruction over all chunks of a pass.
-template <int UT>
-__device__ __forceinline__ void exec_instr(const EwProgram& p, const EwInstr ins, const RegFile& rf, const Pos& pos) {
-  const int nU = UT > 0 ? UT : rf.U;
-  switch (ins.op) {
-    case E_LOAD: {
-      const EwOperand& o = p.inputs[ins.aux];
-      // hot path: dense fp32 operand, every chunk of this thread fully inside the tensor / row
-      if (UT > 0 && o.mode == A_CONTIG && o.vec_ok && o.dtype == BG_F32 && pos.end - pos.idx(UT - 1) >= 4) {
-        const float* src = reinterpret_cast<const float*>(o.ptr) + pos.idx0;
-        float4 t[UT > 0 ? UT : 1];
-#pragma unroll
-        for (int u = 0; u < nU; ++u) t[u] = __ldg(reinterpret_cast<const float4*>(src + (int64_t)u * kChunk));
-#pragma unroll
-        for (int u = 0; u < nU; ++u) *reinterpret_cast<float4*>(rf.slot(ins.dst, u, 0)) = t[u];
-      } else {
-#pragma unroll 1
-        for (int u = 0; u < nU; ++u) load_chunk(p, ins, rf, u, ChunkPos{pos.idx(u), pos.nvalid(u)});
-      }
-      break;
-    }
-    case E_STORE: {
-      const EwOutput& o = p.outputs[ins.aux];
-      if (UT > 0 && ins.type == T_F32 && o.vec_ok && o.dtype == BG_F32 && pos.end - pos.idx(UT - 1) >= 4) {
-        float* dst = reinterpret_cast<float*>(o.ptr) + pos.idx0;
-#pragma unroll
-        for (int u = 0; u < nU; ++u)
-          *reinterpret_cast<float4*>(dst + (int64_t)u * kChunk) = *reinterpret_cast<const float4*>(rf.slot(ins.a, u, 0));
-      } else {
-#pragma unroll 1
-        for (int u = 0; u < nU; ++u) store_chunk(p, ins, rf, u, ChunkPos{pos.idx(u), pos.nvalid(u)});
-      }
-      break;
-    }
-    case E_ADD: case E_MUL: case E_DIV: case E_NEG: case E_EXP: case E_LOG: case E_ABS: case E_SIGN: case E_SIN: case E_COS:
-    case E_SUB: case E_RELU: case E_EXPNEG:
-      if (ins.type == T_F32) f32_instr<UT>(p, ins, rf, pos);
-      else misc_instr(p, ins, rf);
-      break;
-    case E_CMP:
-      if (ins.type == T_F32) f32_cmp<UT>(p, ins, rf, pos);
-      else misc_instr(p, ins, rf);
-      break;
-    case E_WHERE:
-      if (ins.type == T_F32) f32_where<UT>(p, ins, rf, pos);
-      else misc_instr(p, ins, rf);
-      break;
-    default:
-      misc_instr(p, ins, rf);
-      break;
-  }
-}
-
+// The program over the UT chunks of one pass.
 template <int UT>
 __device__ __forceinline__ void run_program(const EwProgram& p, const RegFile& rf, const Pos& pos) {
+  float4 acc[UT];
+#pragma unroll
+  for (int u = 0; u < UT; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool full = pos.end - pos.idx(UT - 1) >= 4;   // every chunk of this thread is complete
 #pragma unroll 1
-  for (int i = 0; i < p.n_instr; ++i) exec_instr<UT>(p, p.instr[i], rf, pos);
+  for (int i = 0; i < p.n_instr; ++i) {
+    const EwInstr ins = p.instr[i];
+    if (ins.type == T_F32 && ((kFastOps >> ins.op) & 1u)) fast_instr<UT>(p, ins, rf, pos, full, acc);
+    else slow_instr(p, ins, rf, pos);
+  }
 }
 
 // ------------------------------------------------------------------------------------
 // Flat elementwise kernel
 // ------------------------------------------------------------------------------------
 template <int UT>
-__global__ void __launch_bounds__(kBlock) ew_kernel(const __grid_constant__ EwProgram p, int U, int64_t n_tiles) {
+__global__ void __launch_bounds__(kBlock, BG_EW_MIN_CTAS) ew_kernel(const __grid_constant__ EwProgram p, int U, int64_t n_tiles) {
   extern __shared__ __align__(16) char smem[];
   const RegFile rf(smem, U, p.wide ? 2 : 1);
   const int64_t tile_elems = (int64_t)U * kChunk;
@@ -745,6 +767,31 @@ __global__ void __launch_bounds__(kBlock) ew_kernel(const __grid_constant__ EwPr
     const Pos pos{tile * tile_elems + (int64_t)threadIdx.x * kVec, p.numel};
     run_program<UT>(p, rf, pos);
   }
+}
+
+// Shared-memory opt-in and carve-out for a launch with `smem` dynamic bytes; *ctas_per_sm receives how many
+// CTAs of it one SM holds, which sizes the grid of the persistent loops.
+static cudaError_t prepare_kernel(const void* kern, size_t smem, int* ctas_per_sm) {
+  // remembered per (device, kernel, size): the attribute and occupancy calls cost microseconds each
+  static std::mutex mu;
+  static std::map<std::tuple<int, const void*, size_t>, int> known;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const auto key = std::make_tuple(dev, kern, smem);
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = known.find(key);
+  if (it != known.end()) { *ctas_per_sm = it->second; return cudaSuccess; }
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+  if (e != cudaSuccess) return e;
+  int n = 0;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kBlock, smem);
+  if (e != cudaSuccess) return e;
+  *ctas_per_sm = n < 1 ? 1 : n;
+  known[key] = *ctas_per_sm;
+  return cudaSuccess;
 }
 
 cudaError_t launch_elementwise(const EwProgram& p, cudaStream_t s, int sm_count) {
@@ -756,15 +803,11 @@ cudaError_t launch_elementwise(const EwProgram& p, cudaStream_t s, int sm_count)
   const size_t smem = per_chunk * U;
   if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
   auto kern = U == 4 ? ew_kernel<4> : (U == 2 ? ew_kernel<2> : ew_kernel<1>);
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
-    if (e != cudaSuccess) return e;
-  }
   const int64_t tile_elems = (int64_t)U * kChunk;
   const int64_t n_tiles = (p.numel + tile_elems - 1) / tile_elems;
-  int ctas_per_sm = (int)(200 * 1024 / (smem ? smem : 1));
-  if (ctas_per_sm > 8) ctas_per_sm = 8;
-  if (ctas_per_sm < 1) ctas_per_sm = 1;
+  int ctas_per_sm = 1;
+  cudaError_t e = prepare_kernel(reinterpret_cast<const void*>(kern), smem, &ctas_per_sm);
+  if (e != cudaSuccess) return e;
   int64_t grid = (int64_t)sm_count * ctas_per_sm;
   if (grid > n_tiles) grid = n_tiles;
   kern<<<(unsigned)grid, kBlock, smem, s>>>(p, U, n_tiles);
@@ -854,11 +897,26 @@ __device__ __forceinline__ void store_scalar(void* ptr, int dt, int64_t i, doubl
   }
 }
 
-// Reduction over one row with values of class T arriving pass by pass (U chunks per pass).
-template <int UT, typename T>
+// The program over chunks [c_begin, c_end) of a row that starts at linear index row_base and ends before
+// row_end: groups of four chunks, then single chunks.  With `resident` chunk c uses slot c of the register
+// file (the whole row stays on chip); otherwise chunk c uses slot c - c_begin.
+__device__ __forceinline__ void run_row_chunks(const EwProgram& p, const RegFile& rf, int64_t row_base, int64_t row_end, int c_begin,
+                                               int c_end, bool resident) {
+  int c = c_begin;
+  for (; c + 4 <= c_end; c += 4) {
+    const Pos pos{row_base + (int64_t)c * kChunk + (int64_t)threadIdx.x * kVec, row_end};
+    run_program<4>(p, rf.group(resident ? c : c - c_begin, 4), pos);
+  }
+  for (; c < c_end; ++c) {
+    const Pos pos{row_base + (int64_t)c * kChunk + (int64_t)threadIdx.x * kVec, row_end};
+    run_program<1>(p, rf.group(resident ? c : c - c_begin, 1), pos);
+  }
+}
+
+// Reduction over one row with values of class T arriving pass by pass (up to four chunks per pass).
+template <typename T>
 __device__ __forceinline__ void row_reduce(const EwProgram& p, const RegFile& rf, int64_t row, int64_t n_chunks,
                                            char* scratch) {
-  const int nU = UT > 0 ? UT : rf.U;
   const int op = p.tail_arg;
   const bool is_arg = op == BG_RED_ARGMAX || op == BG_RED_ARGMIN;
   T acc = T(0);
@@ -867,43 +925,40 @@ __device__ __forceinline__ void row_reduce(const EwProgram& p, const RegFile& rf
   if (op == BG_RED_MIN) acc = highest<T>();
   if (op == BG_RED_PROD) acc = T(1);
   bool any_nan = false;
-  const int64_t row_end = (row + 1) * p.cols;
-  for (int64_t c0 = 0; c0 < n_chunks; c0 += nU) {
+  const int64_t row_base = row * p.cols;
+  const int64_t row_end = row_base + p.cols;
+  const int step = rf.U >= 4 ? 4 : 1;
+  for (int64_t c0 = 0; c0 < n_chunks; c0 += step) {
+    const int nU = n_chunks - c0 >= step ? step : (int)(n_chunks - c0);
     const int64_t col0 = c0 * kChunk + (int64_t)threadIdx.x * kVec;
-    const Pos pos{row * p.cols + col0, row_end};
-    run_program<UT>(p, rf, pos);
+    const Pos pos{row_base + col0, row_end};
+    run_row_chunks(p, rf, row_base, row_end, (int)c0, (int)c0 + nU, false);
     if (op == BG_RED_SUM || op == BG_RED_MEAN) {
-      if (pos.end - pos.idx(nU - 1) >= 4) {
+      if (nU == 4 && pos.end - pos.idx(3) >= 4) {
 #pragma unroll
-        for (int u = 0; u < nU; ++u) {
+        for (int u = 0; u < 4; ++u) {
           V4<T> x = rget<T>(rf, p.tail_reg, u);
           acc += (x.v[0] + x.v[1]) + (x.v[2] + x.v[3]);
         }
-      } else {
-#pragma unroll 1
-        for (int u = 0; u < nU; ++u) {
-          const int nv = pos.nvalid(u);
-          V4<T> x = rget<T>(rf, p.tail_reg, u);
-          for (int e = 0; e < nv; ++e) acc += x.v[e];
-        }
+        continue;
       }
-    } else {
+    }
 #pragma unroll 1
-      for (int u = 0; u < nU; ++u) {
-        const int nv = pos.nvalid(u);
-        if (nv == 0) continue;
-        const int64_t col = col0 + (int64_t)u * kChunk;
-        V4<T> x = rget<T>(rf, p.tail_reg, u);
-        for (int e = 0; e < nv; ++e) {
-          const T v = x.v[e];
-          if (op == BG_RED_PROD) { acc *= v; continue; }
-          if (is_arg) {
-            if (arg_better<T>(v, col + e, acc, best_i, op == BG_RED_ARGMAX)) { acc = v; best_i = col + e; }
-          } else {
-            if (v != v) any_nan = true;
-            if (op == BG_RED_MAX) acc = v > acc ? v : acc;
-            else acc = v < acc ? v : acc;
-          }
+    for (int u = 0; u < nU; ++u) {
+      const int nv = pos.nvalid(u);
+      if (nv == 0) continue;
+      const int64_t col = col0 + (int64_t)u * kChunk;
+      V4<T> x = rget<T>(rf, p.tail_reg, u);
+      for (int e = 0; e < nv; ++e) {
+        const T v = x.v[e];
+        if (op == BG_RED_SUM || op == BG_RED_MEAN) { acc += v; continue; }
+        if (op == BG_RED_PROD) { acc *= v; continue; }
+        if (is_arg) {
+          if (arg_better<T>(v, col + e, acc, best_i, op == BG_RED_ARGMAX)) { acc = v; best_i = col + e; }
+        } else {
+          if (v != v) any_nan = true;
+          if (op == BG_RED_MAX) acc = v > acc ? v : acc;
+          else acc = v < acc ? v : acc;
         }
       }
     }
@@ -941,14 +996,16 @@ __device__ __forceinline__ void row_reduce(const EwProgram& p, const RegFile& rf
   }
 }
 
-__device__ __noinline__ void row_reduce_bool(const EwProgram& p, const RegFile rf, int64_t row, int64_t n_chunks) {
-  const int nU = rf.U;
+__device__ __forceinline__ void row_reduce_bool(const EwProgram& p, const RegFile& rf, int64_t row, int64_t n_chunks) {
+  const int step = rf.U >= 4 ? 4 : 1;
   const bool is_any = p.tail_arg == BG_RED_ANY;
   int local = is_any ? 0 : 1;
-  const int64_t row_end = (row + 1) * p.cols;
-  for (int64_t c0 = 0; c0 < n_chunks; c0 += nU) {
-    const Pos pos{row * p.cols + c0 * kChunk + (int64_t)threadIdx.x * kVec, row_end};
-    run_program<0>(p, rf, pos);
+  const int64_t row_base = row * p.cols;
+  const int64_t row_end = row_base + p.cols;
+  for (int64_t c0 = 0; c0 < n_chunks; c0 += step) {
+    const int nU = n_chunks - c0 >= step ? step : (int)(n_chunks - c0);
+    const Pos pos{row_base + c0 * kChunk + (int64_t)threadIdx.x * kVec, row_end};
+    run_row_chunks(p, rf, row_base, row_end, (int)c0, (int)c0 + nU, false);
 #pragma unroll 1
     for (int u = 0; u < nU; ++u) {
       const int nv = pos.nvalid(u);
@@ -964,16 +1021,16 @@ __device__ __noinline__ void row_reduce_bool(const EwProgram& p, const RegFile r
 }
 
 // softmax / layer norm: the whole row stays in the register file (n_chunks <= U).
-template <int UT, typename T>
+template <typename T, bool SOFTMAX>
 __device__ __forceinline__ void row_resident_tail(const EwProgram& p, const RegFile& rf, int64_t row, char* scratch) {
-  const int nU = UT > 0 ? UT : rf.U;
+  const int nU = rf.U;
   const int64_t col0 = (int64_t)threadIdx.x * kVec;
   const Pos pos{row * p.cols + col0, (row + 1) * p.cols};
-  run_program<UT>(p, rf, pos);
+  run_row_chunks(p, rf, row * p.cols, (row + 1) * p.cols, 0, nU, true);
   const int r = p.tail_reg;
   const EwOutput& out = p.outputs[p.tail_out];
   const bool full = pos.end - pos.idx(nU - 1) >= 4;   // every chunk of this thread is complete
-  if (p.tail == TAIL_SOFTMAX) {
+  if (SOFTMAX) {
     T m = lowest<T>();
     bool nan = false;
     BG_FOR_U {
@@ -1074,22 +1131,27 @@ __device__ __forceinline__ void row_resident_tail(const EwProgram& p, const RegF
   }
 }
 
-template <int UT>
-__global__ void __launch_bounds__(kBlock) row_kernel(const __grid_constant__ EwProgram p, int U, int64_t n_chunks) {
+// One kernel per kind of tail, so that each carries only its own tail's registers.
+enum RowKind {
+  ROW_REDUCE_F32 = 0, ROW_REDUCE_F64, ROW_REDUCE_I64, ROW_REDUCE_BOOL,
+  ROW_SOFTMAX_F32, ROW_SOFTMAX_F64, ROW_LAYERNORM_F32, ROW_LAYERNORM_F64
+};
+
+template <int KIND>
+__global__ void __launch_bounds__(kBlock, BG_EW_MIN_CTAS) row_kernel(const __grid_constant__ EwProgram p, int U, int64_t n_chunks) {
   extern __shared__ __align__(16) char smem[];
   const int planes = p.wide ? 2 : 1;
   const RegFile rf(smem, U, planes);
   char* scratch = smem + (size_t)p.n_regs * U * planes * kBlock * 16;
   for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
-    if (p.tail == TAIL_REDUCE) {
-      if (p.tail_type == T_F32) row_reduce<UT, float>(p, rf, row, n_chunks, scratch);
-      else if (p.tail_type == T_F64) row_reduce<0, double>(p, rf, row, n_chunks, scratch);
-      else if (p.tail_type == T_I64) row_reduce<0, long long>(p, rf, row, n_chunks, scratch);
-      else row_reduce_bool(p, rf, row, n_chunks);
-    } else {
-      if (p.tail_type == T_F64) row_resident_tail<0, double>(p, rf, row, scratch);
-      else row_resident_tail<UT, float>(p, rf, row, scratch);
-    }
+    if (KIND == ROW_REDUCE_F32) row_reduce<float>(p, rf, row, n_chunks, scratch);
+    else if (KIND == ROW_REDUCE_F64) row_reduce<double>(p, rf, row, n_chunks, scratch);
+    else if (KIND == ROW_REDUCE_I64) row_reduce<long long>(p, rf, row, n_chunks, scratch);
+    else if (KIND == ROW_REDUCE_BOOL) row_reduce_bool(p, rf, row, n_chunks);
+    else if (KIND == ROW_SOFTMAX_F32) row_resident_tail<float, true>(p, rf, row, scratch);
+    else if (KIND == ROW_SOFTMAX_F64) row_resident_tail<double, true>(p, rf, row, scratch);
+    else if (KIND == ROW_LAYERNORM_F32) row_resident_tail<float, false>(p, rf, row, scratch);
+    else row_resident_tail<double, false>(p, rf, row, scratch);
   }
 }
 
@@ -1105,22 +1167,27 @@ cudaError_t launch_rowwise(const EwProgram& p, cudaStream_t s, int sm_count, int
   const int64_t n_chunks = (p.cols + kChunk - 1) / kChunk;
   int U;
   if (p.tail == TAIL_REDUCE) {
-    U = n_chunks >= 4 ? 4 : (n_chunks >= 2 ? 2 : 1);
-    while (U > 1 && per_chunk * U > 64 * 1024) U >>= 1;
+    // passes of four chunks where the row and the register file allow, else of one
+    U = (n_chunks >= 4 && per_chunk * 4 <= 64 * 1024) ? 4 : 1;
   } else {
     U = (int)n_chunks;
   }
   if (U < 1) U = 1;
   const size_t smem = per_chunk * U + 512;
   if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
-  auto kern = U == 4 ? row_kernel<4> : (U == 2 ? row_kernel<2> : (U == 1 ? row_kernel<1> : row_kernel<0>));
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
-    if (e != cudaSuccess) return e;
+  void (*kern)(EwProgram, int, int64_t);
+  if (p.tail == TAIL_REDUCE) {
+    kern = p.tail_type == T_F32 ? row_kernel<ROW_REDUCE_F32>
+         : p.tail_type == T_F64 ? row_kernel<ROW_REDUCE_F64>
+         : p.tail_type == T_I64 ? row_kernel<ROW_REDUCE_I64> : row_kernel<ROW_REDUCE_BOOL>;
+  } else {
+    const bool wide_row = p.tail_type == T_F64;
+    if (p.tail == TAIL_SOFTMAX) kern = wide_row ? row_kernel<ROW_SOFTMAX_F64> : row_kernel<ROW_SOFTMAX_F32>;
+    else kern = wide_row ? row_kernel<ROW_LAYERNORM_F64> : row_kernel<ROW_LAYERNORM_F32>;
   }
-  int ctas_per_sm = (int)(200 * 1024 / smem);
-  if (ctas_per_sm > 8) ctas_per_sm = 8;
-  if (ctas_per_sm < 1) ctas_per_sm = 1;
+  int ctas_per_sm = 1;
+  cudaError_t e = prepare_kernel(reinterpret_cast<const void*>(kern), smem, &ctas_per_sm);
+  if (e != cudaSuccess) return e;
   int64_t grid = (int64_t)sm_count * ctas_per_sm;
   if (grid > p.rows) grid = p.rows;
   kern<<<(unsigned)grid, kBlock, smem, s>>>(p, U, n_chunks);

@@ -1159,7 +1159,7 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
   {
     auto is_unary = [](uint8_t op) {
       return op == E_NEG || op == E_EXP || op == E_LOG || op == E_ABS || op == E_SIGN || op == E_SIN || op == E_COS ||
-             op == E_ISNAN || op == E_CVT || op == E_NARROW || op == E_STORE || op == E_RELU || op == E_EXPNEG;
+             op == E_ISNAN || op == E_CVT || op == E_NARROW || op == E_STORE || op == E_RELU || op == E_EXPNEG || op == E_COPY;
     };
     auto n_src = [&](const VInstr& I) { return (I.op == E_LOAD || I.op == E_CONST) ? 0 : (is_unary(I.op) ? 1 : (I.op == E_WHERE ? 3 : 2)); };
     auto src = [](VInstr& I, int k) -> int& { return k == 0 ? I.a : (k == 1 ? I.b : I.c); };
@@ -1218,13 +1218,15 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
         }
       }
     }
-    // constants nobody reads any more
-    for (size_t i = 0; i < code.size(); ++i)
-      if (!dead[i] && code[i].op == E_CONST && uses[code[i].dst] == 0) dead[i] = 1;
-    // single-use dense fp32 LOADs become direct operands of their consumer
+    // fp32 constants become operands of the fp32 instructions that read them; single-use dense fp32
+    // LOADs become direct operands of their consumer
     auto f32_value_op = [](uint8_t op) {
       return op == E_ADD || op == E_SUB || op == E_MUL || op == E_DIV || op == E_NEG || op == E_EXP || op == E_LOG ||
              op == E_ABS || op == E_SIGN || op == E_SIN || op == E_COS || op == E_RELU || op == E_EXPNEG;
+    };
+    auto dense_f32_in = [&](int k) {
+      const EwOperand& o = P.inputs[k];
+      return o.mode == A_CONTIG && o.dtype == BG_F32 && o.vec_ok;
     };
     for (size_t i = 0; i < code.size(); ++i) {
       if (dead[i]) continue;
@@ -1234,15 +1236,21 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
       if (!arith && I.op != E_CMP && I.op != E_WHERE) continue;
       for (int k = (I.op == E_WHERE ? 1 : 0); k < n_src(I); ++k) {
         int v = src(I, k);
-        if (v < 0 || def[v] < 0 || uses[v] != 1) continue;
+        if (v < 0 || def[v] < 0) continue;
         VInstr& L = code[def[v]];
-        if (L.op != E_LOAD || L.type != T_F32) continue;
-        const EwOperand& o = P.inputs[L.aux];
-        if (o.mode != A_CONTIG || o.dtype != BG_F32 || !o.vec_ok) continue;
+        if (L.op == E_CONST && L.type == T_F32) {
+          src(I, k) = -3000 - (int)L.aux;
+          continue;
+        }
+        if (uses[v] != 1 || L.op != E_LOAD || L.type != T_F32 || !dense_f32_in(L.aux)) continue;
         dead[def[v]] = 1;
         src(I, k) = -1000 - (int)L.aux;
       }
     }
+    recount(uses, def);
+    // constants nobody reads any more
+    for (size_t i = 0; i < code.size(); ++i)
+      if (!dead[i] && code[i].op == E_CONST && uses[code[i].dst] == 0) dead[i] = 1;
     // a final STORE of a value produced by fp32 arithmetic becomes that instruction's destination
     for (size_t i = 0; i < code.size(); ++i) {
       if (dead[i]) continue;
@@ -1256,10 +1264,51 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
       D.dst = -2000 - (int)S.aux;
       dead[i] = 1;
     }
+    // what is left of the dense fp32 LOADs and STOREs runs as a copy on the fast path
+    for (size_t i = 0; i < code.size(); ++i) {
+      if (dead[i]) continue;
+      VInstr& I = code[i];
+      if (I.type != T_F32) continue;
+      if (I.op == E_LOAD && dense_f32_in(I.aux)) {
+        I.op = E_COPY;
+        I.a = -1000 - (int)I.aux;
+        I.aux = 0;
+      } else if (I.op == E_STORE && P.outputs[I.aux].dtype == BG_F32 && P.outputs[I.aux].vec_ok) {
+        I.op = E_COPY;
+        I.dst = -2000 - (int)I.aux;
+        I.aux = 0;
+      }
+    }
     std::vector<VInstr> kept;
     for (size_t i = 0; i < code.size(); ++i)
       if (!dead[i]) kept.push_back(code[i]);
     code.swap(kept);
+    dead.assign(code.size(), 0);
+    recount(uses, def);
+    // a value whose only reader is the next instruction stays in the accumulator (-4000)
+    for (size_t i = 0; i + 1 < code.size(); ++i) {
+      VInstr& Pd = code[i];
+      VInstr& C = code[i + 1];
+      if (Pd.type != T_F32 || C.type != T_F32 || Pd.dst < 0 || uses[Pd.dst] != 1) continue;
+      if (!(f32_value_op(Pd.op) || Pd.op == E_WHERE)) continue;
+      const int v = Pd.dst;
+      bool ok = false;
+      if (C.op == E_ADD || C.op == E_MUL) {
+        // c = 1 records the exchange for readers that want the operands in graph order
+        if (C.b == v && C.a != v) { std::swap(C.a, C.b); C.c = 1; }
+        ok = C.a == v;
+      } else if (C.op == E_SUB || C.op == E_DIV || C.op == E_CMP) {
+        ok = C.a == v && C.b != v;
+      } else if (C.op == E_WHERE) {
+        ok = C.b == v && C.a != v && C.c != v;
+      } else if (C.op == E_COPY || (f32_value_op(C.op) && is_unary(C.op))) {
+        ok = C.a == v;
+      }
+      if (!ok) continue;
+      Pd.dst = -4000;
+      if (C.op == E_WHERE) C.b = -4000;
+      else C.a = -4000;
+    }
   }
   if ((int)code.size() > kEwMaxInstr) { why = "too many instructions"; return false; }
   // register allocation (linear scan; a destination may take over a source that dies here)
@@ -1269,7 +1318,7 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
     auto use = [&](int v) { if (v >= 0) last[v] = (int)i; };
     const bool unary = I.op == E_NEG || I.op == E_EXP || I.op == E_LOG || I.op == E_ABS || I.op == E_SIGN || I.op == E_SIN ||
                        I.op == E_COS || I.op == E_ISNAN || I.op == E_CVT || I.op == E_NARROW || I.op == E_STORE ||
-                       I.op == E_RELU || I.op == E_EXPNEG;
+                       I.op == E_RELU || I.op == E_EXPNEG || I.op == E_COPY;
     if (I.op == E_LOAD || I.op == E_CONST) continue;
     use(I.a);
     if (!unary) use(I.b);
@@ -1294,16 +1343,19 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
     O.aux = I.aux;
     const bool unary = I.op == E_NEG || I.op == E_EXP || I.op == E_LOG || I.op == E_ABS || I.op == E_SIGN || I.op == E_SIN ||
                        I.op == E_COS || I.op == E_ISNAN || I.op == E_CVT || I.op == E_NARROW || I.op == E_STORE ||
-                       I.op == E_RELU || I.op == E_EXPNEG;
+                       I.op == E_RELU || I.op == E_EXPNEG || I.op == E_COPY;
     const bool leaf = I.op == E_LOAD || I.op == E_CONST;
     int srcs[3] = {leaf ? -1 : I.a, (leaf || unary) ? -1 : I.b, I.op == E_WHERE ? I.c : -1};
     auto enc = [&](int v) -> uint8_t {
+      if (v == -4000) return kEwAcc;
+      if (v <= -3000) return (uint8_t)(kEwConst | (-3000 - v));                 // constant operand
       if (v <= -1000 && v > -2000) return (uint8_t)(kEwDirect | (-1000 - v));   // direct global input
       return v >= 0 ? (uint8_t)phys[v] : 0;
     };
     O.a = enc(srcs[0]);
     O.b = enc(srcs[1]);
     O.c = enc(srcs[2]);
+    if ((I.op == E_ADD || I.op == E_MUL) && I.type == T_F32 && I.c == 1) O.c = 1;   // operands were exchanged
     for (int k = 0; k < 3; ++k)
       if (srcs[k] >= 0 && last[srcs[k]] == (int)i && phys[srcs[k]] >= 0) {
         bool dup = false;
@@ -1312,7 +1364,8 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
       }
     if (I.type == T_F64 || I.type == T_I64) wide = true;
     if (I.op == E_CVT && ((I.aux & 0xF) == T_F64 || (I.aux & 0xF) == T_I64)) wide = true;
-    if (I.dst <= -2000) O.dst = (uint8_t)(kEwDirect | (-2000 - I.dst));   // direct global output
+    if (I.dst == -4000) O.dst = kEwAcc;
+    else if (I.dst <= -2000) O.dst = (uint8_t)(kEwDirect | (-2000 - I.dst));   // direct global output
     if (I.dst >= 0) {
       phys[I.dst] = alloc_reg();
       O.dst = (uint8_t)phys[I.dst];
@@ -1354,8 +1407,8 @@ static std::string program_signature(const EwProgram& P, int* kind, int* arg) {
   bool ok = true;
   auto operand = [&](uint8_t r) -> std::string {
     if (r & kEwDirect) {
-      if (!dense(r & 0x7f)) ok = false;
-      return "i" + std::to_string(r & 0x7f);
+      if ((r & kEwConst) == kEwConst || !dense(r & 0x3f)) { ok = false; return "?"; }
+      return "i" + std::to_string(r & 0x3f);
     }
     auto it = reg.find(r);
     if (it == reg.end()) { ok = false; return "?"; }
@@ -1373,11 +1426,14 @@ static std::string program_signature(const EwProgram& P, int* kind, int* arg) {
       result = operand(I.a);
       ++n_results;
       continue;
+    } else if (I.op == E_COPY) {
+      v = operand(I.a);
     } else {
       const char* nm = opname(I.op);
       if (!nm) return "";
       const bool binary = I.op == E_ADD || I.op == E_SUB || I.op == E_MUL || I.op == E_DIV;
-      v = std::string(nm) + "(" + operand(I.a) + (binary ? "," + operand(I.b) : "") + ")";
+      const bool exchanged = (I.op == E_ADD || I.op == E_MUL) && I.c == 1;
+      v = std::string(nm) + "(" + operand(exchanged ? I.b : I.a) + (binary ? "," + operand(exchanged ? I.a : I.b) : "") + ")";
     }
     if (I.dst & kEwDirect) {
       if (P.outputs[I.dst & 0x7f].dtype != BG_F32 || !P.outputs[I.dst & 0x7f].vec_ok) return "";
@@ -1431,7 +1487,8 @@ static bool match_static_ln(ProgramSpec& ps) {
   std::map<int, std::vector<int>> reg;   // register -> operands whose left-to-right sum it holds
   int sum_out = -1;
   auto source = [&](uint8_t r, std::vector<int>& out) -> bool {
-    if (r & kEwDirect) { out.assign(1, r & 0x7f); return true; }
+    if ((r & kEwConst) == kEwConst) return false;
+    if (r & kEwDirect) { out.assign(1, r & 0x3f); return true; }
     auto it = reg.find(r);
     if (it == reg.end()) return false;
     out = it->second;
@@ -1442,6 +1499,14 @@ static bool match_static_ln(ProgramSpec& ps) {
     std::vector<int> a, b;
     if (I.op == E_LOAD) {
       reg[I.dst] = {(int)I.aux};
+    } else if (I.op == E_COPY && (I.dst & kEwDirect)) {
+      // the fp32 row sum written out as it is
+      const int o = I.dst & 0x3f;
+      if (I.a != (uint8_t)P.tail_reg || sum_out >= 0 || P.outputs[o].dtype != sum_dtype) return false;
+      sum_out = o;
+    } else if (I.op == E_COPY) {
+      if (!source(I.a, a) || a.size() != 1) return false;
+      reg[I.dst] = a;
     } else if (I.op == E_CVT) {
       // widening a loaded fp32 operand before it joins an fp64 sum
       if (I.type != T_F64 || !source(I.a, a) || a.size() != 1 || P.inputs[a[0]].dtype != BG_F32) return false;
