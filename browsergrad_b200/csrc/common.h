@@ -121,6 +121,8 @@ struct EwProgram {
   int32_t tail_w, tail_b;       // operand indices (layer norm weight/bias, CE target)
   int32_t tail_out_dtype;
   float tail_eps;
+  int32_t tail_acc;             // the last instruction is an fp32 one that produces tail_reg: its accumulator holds the row values
+  int32_t pad0;
   int64_t rows, cols;           // row mode: numel = rows * cols
   int64_t tail_aux;             // CE: ignore_index
   EwInstr instr[kEwMaxInstr];

@@ -502,52 +502,54 @@ __device__ __forceinline__ void fast_instr(const EwProgram& p, const EwInstr ins
   const int op = ins.op;
   const int ra = op == E_WHERE ? ins.b : ins.a;
   if (ra != kEwAcc) fast_fetch<UT>(p, rf, pos, full, ra, acc);
-  float4 b[UT];
   if ((kTwoOperandOps >> op) & 1u) {
+    float4 b[UT];
     fast_fetch<UT>(p, rf, pos, full, op == E_WHERE ? ins.c : ins.b, b);
-  } else {
+    switch (op) {
+      case E_ADD: map2<UT>(acc, b, [](float x, float y) { return fadd(x, y); }); break;
+      case E_SUB: map2<UT>(acc, b, [](float x, float y) { return fadd(x, -y); }); break;
+      case E_MUL: map2<UT>(acc, b, [](float x, float y) { return fmul(x, y); }); break;
+      case E_DIV:
 #pragma unroll
-    for (int u = 0; u < UT; ++u) b[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-  }
-  switch (op) {
-#define BG_CALL4(FN) _Pragma("unroll") for (int u = 0; u < UT; ++u) acc[u] = FN
-    case E_ADD: map2<UT>(acc, b, [](float x, float y) { return fadd(x, y); }); break;
-    case E_SUB: map2<UT>(acc, b, [](float x, float y) { return fadd(x, -y); }); break;
-    case E_MUL: map2<UT>(acc, b, [](float x, float y) { return fmul(x, y); }); break;
-    case E_DIV: BG_CALL4(div4(acc[u], b[u])); break;
-    case E_NEG: map1<UT>(acc, [](float x) { return -x; }); break;
-    case E_RELU: map1<UT>(acc, [](float x) { return x > 0.f ? x : 0.f; }); break;
-    case E_EXPNEG:
-      map1<UT>(acc, [](float x) { return -x; });
-      // fall through
-    case E_EXP: map1<UT>(acc, [](float x) { return expf(x); }); break;
-    case E_LOG: BG_CALL4(log4(acc[u])); break;
-    case E_ABS: map1<UT>(acc, [](float x) { return x < 0 ? -x : (x == 0 ? 0.f : x); }); break;
-    case E_SIGN: BG_CALL4(sign4(acc[u])); break;
-    case E_SIN: BG_CALL4(sin4(acc[u])); break;
-    case E_COS: BG_CALL4(cos4(acc[u])); break;
-#undef BG_CALL4
-    case E_WHERE: {
-      const char* c = rf.tbase + (uint32_t)ins.a * rf.rstride;
+        for (int u = 0; u < UT; ++u) acc[u] = div4(acc[u], b[u]);
+        break;
+      case E_WHERE: {
+        const char* c = rf.tbase + (uint32_t)ins.a * rf.rstride;
 #pragma unroll
-      for (int u = 0; u < UT; ++u) {
-        const uint4 m = *reinterpret_cast<const uint4*>(c + u * rf.ustride);
-        acc[u] = make_float4(m.x ? acc[u].x : b[u].x, m.y ? acc[u].y : b[u].y, m.z ? acc[u].z : b[u].z, m.w ? acc[u].w : b[u].w);
+        for (int u = 0; u < UT; ++u) {
+          const uint4 m = *reinterpret_cast<const uint4*>(c + u * rf.ustride);
+          acc[u] = make_float4(m.x ? acc[u].x : b[u].x, m.y ? acc[u].y : b[u].y, m.z ? acc[u].z : b[u].z, m.w ? acc[u].w : b[u].w);
+        }
+        break;
       }
-      break;
+      default:   // E_CMP: the result is a predicate register in shared memory; the accumulator keeps operand a
+        switch (ins.aux) {
+          case BG_CMP_EQ: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x == y); }); break;
+          case BG_CMP_NE: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x != y); }); break;
+          case BG_CMP_LT: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x < y); }); break;
+          case BG_CMP_LE: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x <= y); }); break;
+          case BG_CMP_GT: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x > y); }); break;
+          default: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x >= y); }); break;
+        }
+        return;
     }
-    case E_CMP:
-      // the result is a predicate register in shared memory; the accumulator keeps operand a
-      switch (ins.aux) {
-        case BG_CMP_EQ: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x == y); }); break;
-        case BG_CMP_NE: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x != y); }); break;
-        case BG_CMP_LT: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x < y); }); break;
-        case BG_CMP_LE: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x <= y); }); break;
-        case BG_CMP_GT: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x > y); }); break;
-        default: cmp_put<UT>(rf, ins.dst, acc, b, [](float x, float y) { return (uint32_t)(x >= y); }); break;
-      }
-      return;
-    default: break;   // E_COPY
+  } else {
+#define BG_CALL4(FN) _Pragma("unroll") for (int u = 0; u < UT; ++u) acc[u] = FN(acc[u])
+    switch (op) {
+      case E_NEG: map1<UT>(acc, [](float x) { return -x; }); break;
+      case E_RELU: map1<UT>(acc, [](float x) { return x > 0.f ? x : 0.f; }); break;
+      case E_EXPNEG:
+        map1<UT>(acc, [](float x) { return -x; });
+        // fall through
+      case E_EXP: map1<UT>(acc, [](float x) { return expf(x); }); break;
+      case E_LOG: BG_CALL4(log4); break;
+      case E_ABS: map1<UT>(acc, [](float x) { return x < 0 ? -x : (x == 0 ? 0.f : x); }); break;
+      case E_SIGN: BG_CALL4(sign4); break;
+      case E_SIN: BG_CALL4(sin4); break;
+      case E_COS: BG_CALL4(cos4); break;
+      default: break;   // E_COPY
+    }
+#undef BG_CALL4
   }
   fast_put<UT>(p, rf, pos, full, ins.dst, acc);
 }
@@ -741,9 +743,9 @@ __device__ __noinline__ void slow_instr(const EwProgram& p, const EwInstr ins, c
 }
 
 // The program over the UT chunks of one pass.
+// `acc` is the accumulator; the caller may read the last instruction's result from it.
 template <int UT>
-__device__ __forceinline__ void run_program(const EwProgram& p, const RegFile& rf, const Pos& pos) {
-  float4 acc[UT];
+__device__ __forceinline__ void run_program(const EwProgram& p, const RegFile& rf, const Pos& pos, float4 (&acc)[UT]) {
 #pragma unroll
   for (int u = 0; u < UT; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
   const bool full = pos.end - pos.idx(UT - 1) >= 4;   // every chunk of this thread is complete
@@ -765,7 +767,8 @@ __global__ void __launch_bounds__(kBlock, BG_EW_MIN_CTAS) ew_kernel(const __grid
   const int64_t tile_elems = (int64_t)U * kChunk;
   for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
     const Pos pos{tile * tile_elems + (int64_t)threadIdx.x * kVec, p.numel};
-    run_program<UT>(p, rf, pos);
+    float4 acc[UT];
+    run_program<UT>(p, rf, pos, acc);
   }
 }
 
@@ -900,16 +903,19 @@ __device__ __forceinline__ void store_scalar(void* ptr, int dt, int64_t i, doubl
 // The program over chunks [c_begin, c_end) of a row that starts at linear index row_base and ends before
 // row_end: groups of four chunks, then single chunks.  With `resident` chunk c uses slot c of the register
 // file (the whole row stays on chip); otherwise chunk c uses slot c - c_begin.
+// `last` receives the accumulator of the last group (all four entries after a group of four, entry 0 after a single chunk).
 __device__ __forceinline__ void run_row_chunks(const EwProgram& p, const RegFile& rf, int64_t row_base, int64_t row_end, int c_begin,
-                                               int c_end, bool resident) {
+                                               int c_end, bool resident, float4 (&last)[4]) {
   int c = c_begin;
   for (; c + 4 <= c_end; c += 4) {
     const Pos pos{row_base + (int64_t)c * kChunk + (int64_t)threadIdx.x * kVec, row_end};
-    run_program<4>(p, rf.group(resident ? c : c - c_begin, 4), pos);
+    run_program<4>(p, rf.group(resident ? c : c - c_begin, 4), pos, last);
   }
   for (; c < c_end; ++c) {
     const Pos pos{row_base + (int64_t)c * kChunk + (int64_t)threadIdx.x * kVec, row_end};
-    run_program<1>(p, rf.group(resident ? c : c - c_begin, 1), pos);
+    float4 one[1];
+    run_program<1>(p, rf.group(resident ? c : c - c_begin, 1), pos, one);
+    last[0] = one[0];
   }
 }
 
@@ -932,13 +938,19 @@ __device__ __forceinline__ void row_reduce(const EwProgram& p, const RegFile& rf
     const int nU = n_chunks - c0 >= step ? step : (int)(n_chunks - c0);
     const int64_t col0 = c0 * kChunk + (int64_t)threadIdx.x * kVec;
     const Pos pos{row_base + col0, row_end};
-    run_row_chunks(p, rf, row_base, row_end, (int)c0, (int)c0 + nU, false);
+    float4 last[4];
+    run_row_chunks(p, rf, row_base, row_end, (int)c0, (int)c0 + nU, false, last);
     if (op == BG_RED_SUM || op == BG_RED_MEAN) {
       if (nU == 4 && pos.end - pos.idx(3) >= 4) {
+        if (sizeof(T) == 4 && p.tail_acc) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          V4<T> x = rget<T>(rf, p.tail_reg, u);
-          acc += (x.v[0] + x.v[1]) + (x.v[2] + x.v[3]);
+          for (int u = 0; u < 4; ++u) acc += (T)((last[u].x + last[u].y) + (last[u].z + last[u].w));
+        } else {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            V4<T> x = rget<T>(rf, p.tail_reg, u);
+            acc += (x.v[0] + x.v[1]) + (x.v[2] + x.v[3]);
+          }
         }
         continue;
       }
@@ -1005,7 +1017,8 @@ __device__ __forceinline__ void row_reduce_bool(const EwProgram& p, const RegFil
   for (int64_t c0 = 0; c0 < n_chunks; c0 += step) {
     const int nU = n_chunks - c0 >= step ? step : (int)(n_chunks - c0);
     const Pos pos{row_base + c0 * kChunk + (int64_t)threadIdx.x * kVec, row_end};
-    run_row_chunks(p, rf, row_base, row_end, (int)c0, (int)c0 + nU, false);
+    float4 last[4];
+    run_row_chunks(p, rf, row_base, row_end, (int)c0, (int)c0 + nU, false, last);
 #pragma unroll 1
     for (int u = 0; u < nU; ++u) {
       const int nv = pos.nvalid(u);
@@ -1020,16 +1033,65 @@ __device__ __forceinline__ void row_reduce_bool(const EwProgram& p, const RegFil
   if (threadIdx.x == 0) store_scalar(p.outputs[p.tail_out].ptr, p.tail_out_dtype, row, 0.0, r != 0, true);
 }
 
+// Softmax of a row of N complete fp32 chunks with the row in real registers: same operations in the same order as
+// the general tail below.  A NaN in the row needs no test of its own: the maximum skips it, its exponential is NaN,
+// so is the sum, and every quotient by that sum.
+template <int N>
+__device__ __forceinline__ void softmax_in_registers(const RegFile& rf, int r, bool in_acc, const float4 (&last)[4], float* dst,
+                                                     char* scratch) {
+  float4 x[N];
+  if (in_acc) {
+#pragma unroll
+    for (int u = 0; u < N; ++u) x[u] = last[u];
+  } else {
+#pragma unroll
+    for (int u = 0; u < N; ++u) x[u] = *reinterpret_cast<const float4*>(rf.slot(r, u, 0));
+  }
+  float m = -CUDART_INF_F;
+#pragma unroll
+  for (int u = 0; u < N; ++u) {
+    m = x[u].x > m ? x[u].x : m;
+    m = x[u].y > m ? x[u].y : m;
+    m = x[u].z > m ? x[u].z : m;
+    m = x[u].w > m ? x[u].w : m;
+  }
+  m = block_reduce<float>(m, [](float a, float b) { return a > b ? a : b; }, m, scratch);
+  float sum = 0.f;
+#pragma unroll
+  for (int u = 0; u < N; ++u) {
+    x[u] = make_float4(expf(fadd(x[u].x, -m)), expf(fadd(x[u].y, -m)), expf(fadd(x[u].z, -m)), expf(fadd(x[u].w, -m)));
+    sum += x[u].x;
+    sum += x[u].y;
+    sum += x[u].z;
+    sum += x[u].w;
+  }
+  sum = block_reduce<float>(sum, [](float a, float b) { return a + b; }, 0.f, scratch);
+#pragma unroll
+  for (int u = 0; u < N; ++u)
+    reinterpret_cast<float4*>(dst)[u * (kChunk / 4)] = make_float4(fdiv(x[u].x, sum), fdiv(x[u].y, sum), fdiv(x[u].z, sum), fdiv(x[u].w, sum));
+}
+
 // softmax / layer norm: the whole row stays in the register file (n_chunks <= U).
 template <typename T, bool SOFTMAX>
 __device__ __forceinline__ void row_resident_tail(const EwProgram& p, const RegFile& rf, int64_t row, char* scratch) {
   const int nU = rf.U;
   const int64_t col0 = (int64_t)threadIdx.x * kVec;
   const Pos pos{row * p.cols + col0, (row + 1) * p.cols};
-  run_row_chunks(p, rf, row * p.cols, (row + 1) * p.cols, 0, nU, true);
+  float4 last[4];
+  run_row_chunks(p, rf, row * p.cols, (row + 1) * p.cols, 0, nU, true, last);
   const int r = p.tail_reg;
   const EwOutput& out = p.outputs[p.tail_out];
   const bool full = pos.end - pos.idx(nU - 1) >= 4;   // every chunk of this thread is complete
+  // (the test is the same for every thread of the CTA: the branch holds barriers)
+  if (SOFTMAX && sizeof(T) == 4 && p.cols == (int64_t)nU * kChunk && out.vec_ok && out.dtype == BG_F32 &&
+      (nU == 4 || nU == 2 || nU == 1)) {
+    const bool in_acc = p.tail_acc && nU != 2;
+    float* dst = reinterpret_cast<float*>(out.ptr) + pos.idx0;
+    if (nU == 4) softmax_in_registers<4>(rf, r, in_acc, last, dst, scratch);
+    else if (nU == 2) softmax_in_registers<2>(rf, r, in_acc, last, dst, scratch);
+    else softmax_in_registers<1>(rf, r, in_acc, last, dst, scratch);
+    return;
+  }
   if (SOFTMAX) {
     T m = lowest<T>();
     bool nan = false;

@@ -1376,6 +1376,14 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
   P.n_regs = std::max<int>(1, (int)busy.size());
   P.wide = wide ? 1 : 0;
   if (tail_reg_v >= 0) P.tail_reg = phys[tail_reg_v];
+  P.tail_acc = 0;
+  if (tail_reg_v >= 0 && !code.empty()) {
+    const VInstr& L = code.back();
+    const bool value_op = L.op == E_ADD || L.op == E_SUB || L.op == E_MUL || L.op == E_DIV || L.op == E_NEG || L.op == E_EXP ||
+                          L.op == E_LOG || L.op == E_ABS || L.op == E_SIGN || L.op == E_SIN || L.op == E_COS || L.op == E_RELU ||
+                          L.op == E_EXPNEG || L.op == E_WHERE || L.op == E_COPY;
+    if (L.type == T_F32 && value_op && L.dst == tail_reg_v) P.tail_acc = 1;
+  }
   const int64_t per_chunk = (int64_t)P.n_regs * (wide ? 2 : 1) * 4096;
   if (per_chunk > 190 * 1024) { why = "register file does not fit shared memory"; return false; }
   ps.row = tail_node >= 0;
