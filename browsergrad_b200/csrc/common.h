@@ -53,7 +53,9 @@ enum EwOp : uint8_t {
   E_SUB,        // dst <- a - b            (ADD of a NEG)
   E_RELU,       // dst <- a > 0 ? a : +0   (CONST 0, CMP gt, WHERE)
   E_EXPNEG,     // dst <- exp(-a)          (NEG, EXP)
-  E_COPY,       // dst <- a                (a dense fp32 LOAD or STORE after operand folding)
+  E_COPY,       // dst <- a                (a dense fp32 LOAD or STORE after operand folding; a float64 output widens)
+  E_GELU,       // dst <- a / (1 + exp(-2 k (a + 0.044715 a^3))), k = sqrt(2/pi): the tanh GELU of an fp32 value, which
+                // replaces its float64 evaluation 0.5 a (1 + tanh(k (a + 0.044715 a^3))) in plans without a float64 leaf
   E_OPCOUNT
 };
 

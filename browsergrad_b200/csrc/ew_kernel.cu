@@ -436,6 +436,24 @@ __device__ __forceinline__ void fast_put(const EwProgram& p, const RegFile& rf, 
                                          const float4 (&x)[UT]) {
   if (r == kEwAcc) return;
   if (r & kEwDirect) {
+    if (p.outputs[r & 0x3f].dtype == BG_F64) {
+      // an fp32 value stored into a float64 output
+      double* dst = reinterpret_cast<double*>(p.outputs[r & 0x3f].ptr) + pos.idx0;
+#pragma unroll
+      for (int u = 0; u < UT; ++u) {
+        const int nv = full ? 4 : pos.nvalid(u);
+        double* q = dst + u * kChunk;
+        if (nv == 4) {
+          reinterpret_cast<double2*>(q)[0] = make_double2((double)x[u].x, (double)x[u].y);
+          reinterpret_cast<double2*>(q)[1] = make_double2((double)x[u].z, (double)x[u].w);
+        } else if (nv > 0) {
+          q[0] = (double)x[u].x;
+          if (nv > 1) q[1] = (double)x[u].y;
+          if (nv > 2) q[2] = (double)x[u].z;
+        }
+      }
+      return;
+    }
     float* dst = reinterpret_cast<float*>(p.outputs[r & 0x3f].ptr) + pos.idx0;
     if (full) {
 #pragma unroll
@@ -477,6 +495,18 @@ __device__ __noinline__ float4 div4(float4 a, float4 b) { return make_float4(fdi
 __device__ __noinline__ float4 log4(float4 a) { return make_float4(logf(a.x), logf(a.y), logf(a.z), logf(a.w)); }
 __device__ __noinline__ float4 sin4(float4 a) { return make_float4(sinf(a.x), sinf(a.y), sinf(a.z), sinf(a.w)); }
 __device__ __noinline__ float4 cos4(float4 a) { return make_float4(cosf(a.x), cosf(a.y), cosf(a.z), cosf(a.w)); }
+// tanh GELU of an fp32 value: with u = k (x + 0.044715 x^3), 0.5 x (1 + tanh u) = x / (1 + e^(-2u)).  One
+// exponential and no cancellation for negative x.  Where the float64 form overflows (|u| beyond the largest argument
+// of exp, 709.78) it yields inf / inf = NaN, and so does this.
+__device__ __forceinline__ float gelu1(float x) {
+  float t = fmul(0.044715f, x);
+  t = fmul(t, x);
+  t = fmul(t, x);
+  const float u = fmul(0.7978845608028654f, fadd(x, t));
+  const float e = expf(fmul(-2.0f, u));
+  const float g = __fdividef(x, fadd(1.0f, e));
+  return fabsf(u) > 709.782712893384f ? CUDART_NAN_F : g;
+}
 __device__ __forceinline__ float sign1(float x) { return x != x ? x : (float)((x > 0) - (x < 0)); }
 __device__ __noinline__ float4 sign4(float4 a) { return make_float4(sign1(a.x), sign1(a.y), sign1(a.z), sign1(a.w)); }
 
@@ -492,7 +522,7 @@ __device__ __forceinline__ void cmp_put(const RegFile& rf, int dst, const float4
 // Opcodes the fast path executes when the instruction's class is fp32.
 constexpr uint32_t kFastOps = (1u << E_ADD) | (1u << E_MUL) | (1u << E_DIV) | (1u << E_NEG) | (1u << E_EXP) | (1u << E_LOG) |
                               (1u << E_ABS) | (1u << E_SIGN) | (1u << E_SIN) | (1u << E_COS) | (1u << E_CMP) | (1u << E_WHERE) |
-                              (1u << E_SUB) | (1u << E_RELU) | (1u << E_EXPNEG) | (1u << E_COPY);
+                              (1u << E_SUB) | (1u << E_RELU) | (1u << E_EXPNEG) | (1u << E_COPY) | (1u << E_GELU);
 constexpr uint32_t kTwoOperandOps = (1u << E_ADD) | (1u << E_MUL) | (1u << E_DIV) | (1u << E_SUB) | (1u << E_CMP) | (1u << E_WHERE);
 static_assert(E_OPCOUNT <= 32, "opcode masks are 32 bits wide");
 
@@ -542,6 +572,7 @@ __device__ __forceinline__ void fast_instr(const EwProgram& p, const EwInstr ins
         map1<UT>(acc, [](float x) { return -x; });
         // fall through
       case E_EXP: map1<UT>(acc, [](float x) { return expf(x); }); break;
+      case E_GELU: map1<UT>(acc, [](float x) { return gelu1(x); }); break;
       case E_LOG: BG_CALL4(log4); break;
       case E_ABS: map1<UT>(acc, [](float x) { return x < 0 ? -x : (x == 0 ? 0.f : x); }); break;
       case E_SIGN: BG_CALL4(sign4); break;
@@ -752,8 +783,14 @@ __device__ __forceinline__ void run_program(const EwProgram& p, const RegFile& r
 #pragma unroll 1
   for (int i = 0; i < p.n_instr; ++i) {
     const EwInstr ins = p.instr[i];
-    if (ins.type == T_F32 && ((kFastOps >> ins.op) & 1u)) fast_instr<UT>(p, ins, rf, pos, full, acc);
-    else slow_instr(p, ins, rf, pos);
+    if (ins.type == T_F32 && ((kFastOps >> ins.op) & 1u)) {
+      fast_instr<UT>(p, ins, rf, pos, full, acc);
+    } else {
+      slow_instr(p, ins, rf, pos);
+      // nothing reads the accumulator across an instruction of the slow path: it need not survive the call
+#pragma unroll
+      for (int u = 0; u < UT; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
 }
 
@@ -820,25 +857,28 @@ cudaError_t launch_elementwise(const EwProgram& p, cudaStream_t s, int sm_count)
 // ------------------------------------------------------------------------------------
 // Row kernel: program + on-chip tail over the last axis
 // ------------------------------------------------------------------------------------
+// Reduction over the CTA with one barrier.  Warp results go to one of two scratch buffers, `flip` says which and
+// alternates from call to call: a buffer is written again only after the barrier of the call in between, which
+// every thread passes after it has read the buffer.  Lane l of every warp combines buffer entries l & 7 by the same
+// butterfly, so all threads hold the same bits.
 template <typename T, typename F>
-__device__ __forceinline__ T block_reduce(T v, F f, T ident, char* scratch) {
+__device__ __forceinline__ T block_reduce(T v, F f, char* scratch, int& flip) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     T other = __shfl_xor_sync(0xffffffffu, v, o);
     v = f(v, other);
   }
-  T* s = reinterpret_cast<T*>(scratch);
+  T* s = reinterpret_cast<T*>(scratch + 256 + flip * 64);
+  flip ^= 1;
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
-  __syncthreads();
   if (l == 0) s[w] = v;
   __syncthreads();
-  T r = l < (kBlock / 32) ? s[l] : ident;
+  T r = s[l & (kBlock / 32 - 1)];
 #pragma unroll
   for (int o = 4; o > 0; o >>= 1) {
     T other = __shfl_xor_sync(0xffffffffu, r, o);
     r = f(r, other);
   }
-  r = __shfl_sync(0xffffffffu, r, 0);
   return r;
 }
 
@@ -922,7 +962,7 @@ __device__ __forceinline__ void run_row_chunks(const EwProgram& p, const RegFile
 // Reduction over one row with values of class T arriving pass by pass (up to four chunks per pass).
 template <typename T>
 __device__ __forceinline__ void row_reduce(const EwProgram& p, const RegFile& rf, int64_t row, int64_t n_chunks,
-                                           char* scratch) {
+                                           char* scratch, int& flip) {
   const int op = p.tail_arg;
   const bool is_arg = op == BG_RED_ARGMAX || op == BG_RED_ARGMIN;
   T acc = T(0);
@@ -982,7 +1022,7 @@ __device__ __forceinline__ void row_reduce(const EwProgram& p, const RegFile& rf
     return;
   }
   if (op == BG_RED_SUM || op == BG_RED_MEAN) {
-    acc = block_reduce<T>(acc, [](T a, T b) { return a + b; }, T(0), scratch);
+    acc = block_reduce<T>(acc, [](T a, T b) { return a + b; }, scratch, flip);
     if (threadIdx.x == 0) {
       if (op == BG_RED_MEAN) {
         if (kIsInt) store_scalar(p.outputs[p.tail_out].ptr, p.tail_out_dtype, row, (double)acc / (double)p.cols, 0, false);
@@ -994,12 +1034,12 @@ __device__ __forceinline__ void row_reduce(const EwProgram& p, const RegFile& rf
     return;
   }
   if (op == BG_RED_PROD) {
-    acc = block_reduce<T>(acc, [](T a, T b) { return a * b; }, T(1), scratch);
+    acc = block_reduce<T>(acc, [](T a, T b) { return a * b; }, scratch, flip);
     if (threadIdx.x == 0) store_scalar(p.outputs[p.tail_out].ptr, p.tail_out_dtype, row, (double)acc, (long long)acc, kIsInt);
     return;
   }
   const bool want_max = op == BG_RED_MAX;
-  acc = block_reduce<T>(acc, [want_max](T a, T b) { return want_max ? (a > b ? a : b) : (a < b ? a : b); }, acc, scratch);
+  acc = block_reduce<T>(acc, [want_max](T a, T b) { return want_max ? (a > b ? a : b) : (a < b ? a : b); }, scratch, flip);
   int nan_any = __syncthreads_or(any_nan ? 1 : 0);
   if (threadIdx.x == 0) {
     double fv = (double)acc;
@@ -1033,12 +1073,30 @@ __device__ __forceinline__ void row_reduce_bool(const EwProgram& p, const RegFil
   if (threadIdx.x == 0) store_scalar(p.outputs[p.tail_out].ptr, p.tail_out_dtype, row, 0.0, r != 0, true);
 }
 
+// exp(x - m) and the division by the row sum of the fp32 softmax tails, as the specialised softmax kernel does them:
+// 2^((x - m) * log2 e) on the hardware exp2 unit (x - m <= 0 is bounded by the row's range, so the rounding of the
+// argument stays near 1e-6 relative), one IEEE reciprocal per row and one multiply per element.  fp64 rows keep
+// exp() and a true division.
+template <typename T> __device__ __forceinline__ T softmax_exp(T x, T m);
+template <> __device__ __forceinline__ float softmax_exp<float>(float x, float m) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(fmul(fadd(x, -m), 1.4426950408889634f)));
+  return y;
+}
+template <> __device__ __forceinline__ double softmax_exp<double>(double x, double m) { return exp(fadd(x, -m)); }
+template <typename T> __device__ __forceinline__ T softmax_scale(T sum);
+template <> __device__ __forceinline__ float softmax_scale<float>(float sum) { return __fdiv_rn(1.0f, sum); }
+template <> __device__ __forceinline__ double softmax_scale<double>(double sum) { return sum; }
+template <typename T> __device__ __forceinline__ T softmax_norm(T e, T scale);
+template <> __device__ __forceinline__ float softmax_norm<float>(float e, float scale) { return fmul(e, scale); }
+template <> __device__ __forceinline__ double softmax_norm<double>(double e, double scale) { return fdiv(e, scale); }
+
 // Softmax of a row of N complete fp32 chunks with the row in real registers: same operations in the same order as
 // the general tail below.  A NaN in the row needs no test of its own: the maximum skips it, its exponential is NaN,
 // so is the sum, and every quotient by that sum.
 template <int N>
 __device__ __forceinline__ void softmax_in_registers(const RegFile& rf, int r, bool in_acc, const float4 (&last)[4], float* dst,
-                                                     char* scratch) {
+                                                     char* scratch, int& flip) {
   float4 x[N];
   if (in_acc) {
 #pragma unroll
@@ -1055,25 +1113,27 @@ __device__ __forceinline__ void softmax_in_registers(const RegFile& rf, int r, b
     m = x[u].z > m ? x[u].z : m;
     m = x[u].w > m ? x[u].w : m;
   }
-  m = block_reduce<float>(m, [](float a, float b) { return a > b ? a : b; }, m, scratch);
+  m = block_reduce<float>(m, [](float a, float b) { return a > b ? a : b; }, scratch, flip);
   float sum = 0.f;
 #pragma unroll
   for (int u = 0; u < N; ++u) {
-    x[u] = make_float4(expf(fadd(x[u].x, -m)), expf(fadd(x[u].y, -m)), expf(fadd(x[u].z, -m)), expf(fadd(x[u].w, -m)));
+    x[u] = make_float4(softmax_exp<float>(x[u].x, m), softmax_exp<float>(x[u].y, m), softmax_exp<float>(x[u].z, m),
+                       softmax_exp<float>(x[u].w, m));
     sum += x[u].x;
     sum += x[u].y;
     sum += x[u].z;
     sum += x[u].w;
   }
-  sum = block_reduce<float>(sum, [](float a, float b) { return a + b; }, 0.f, scratch);
+  sum = block_reduce<float>(sum, [](float a, float b) { return a + b; }, scratch, flip);
+  const float inv = softmax_scale<float>(sum);
 #pragma unroll
   for (int u = 0; u < N; ++u)
-    reinterpret_cast<float4*>(dst)[u * (kChunk / 4)] = make_float4(fdiv(x[u].x, sum), fdiv(x[u].y, sum), fdiv(x[u].z, sum), fdiv(x[u].w, sum));
+    reinterpret_cast<float4*>(dst)[u * (kChunk / 4)] = make_float4(fmul(x[u].x, inv), fmul(x[u].y, inv), fmul(x[u].z, inv), fmul(x[u].w, inv));
 }
 
 // softmax / layer norm: the whole row stays in the register file (n_chunks <= U).
 template <typename T, bool SOFTMAX>
-__device__ __forceinline__ void row_resident_tail(const EwProgram& p, const RegFile& rf, int64_t row, char* scratch) {
+__device__ __forceinline__ void row_resident_tail(const EwProgram& p, const RegFile& rf, int64_t row, char* scratch, int& flip) {
   const int nU = rf.U;
   const int64_t col0 = (int64_t)threadIdx.x * kVec;
   const Pos pos{row * p.cols + col0, (row + 1) * p.cols};
@@ -1087,9 +1147,9 @@ __device__ __forceinline__ void row_resident_tail(const EwProgram& p, const RegF
       (nU == 4 || nU == 2 || nU == 1)) {
     const bool in_acc = p.tail_acc && nU != 2;
     float* dst = reinterpret_cast<float*>(out.ptr) + pos.idx0;
-    if (nU == 4) softmax_in_registers<4>(rf, r, in_acc, last, dst, scratch);
-    else if (nU == 2) softmax_in_registers<2>(rf, r, in_acc, last, dst, scratch);
-    else softmax_in_registers<1>(rf, r, in_acc, last, dst, scratch);
+    if (nU == 4) softmax_in_registers<4>(rf, r, in_acc, last, dst, scratch, flip);
+    else if (nU == 2) softmax_in_registers<2>(rf, r, in_acc, last, dst, scratch, flip);
+    else softmax_in_registers<1>(rf, r, in_acc, last, dst, scratch, flip);
     return;
   }
   if (SOFTMAX) {
@@ -1105,7 +1165,7 @@ __device__ __forceinline__ void row_resident_tail(const EwProgram& p, const RegF
           m = x.v[e] > m ? x.v[e] : m;
         }
     }
-    m = block_reduce<T>(m, [](T a, T b) { return a > b ? a : b; }, m, scratch);
+    m = block_reduce<T>(m, [](T a, T b) { return a > b ? a : b; }, scratch, flip);
     if (__syncthreads_or(nan ? 1 : 0)) m = (T)CUDART_NAN;
     T sum = T(0);
     BG_FOR_U {
@@ -1114,20 +1174,21 @@ __device__ __forceinline__ void row_resident_tail(const EwProgram& p, const RegF
         V4<T> x = rget<T>(rf, r, u);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          x.v[e] = f_exp<T>(fadd(x.v[e], -m));
+          x.v[e] = softmax_exp<T>(x.v[e], m);
           if (e < nv) sum += x.v[e];
         }
         rput<T>(rf, r, u, x);
       }
     }
-    sum = block_reduce<T>(sum, [](T a, T b) { return a + b; }, T(0), scratch);
+    sum = block_reduce<T>(sum, [](T a, T b) { return a + b; }, scratch, flip);
+    const T scale = softmax_scale<T>(sum);
     const EwInstr st{E_STORE, (uint8_t)p.tail_type, 0, (uint8_t)r, 0, 0, (uint16_t)p.tail_out};
     BG_FOR_U {
       const int nv = full ? 4 : pos.nvalid(u);
       if (nv > 0) {
         V4<T> x = rget<T>(rf, r, u);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) x.v[e] = fdiv(x.v[e], sum);
+        for (int e = 0; e < 4; ++e) x.v[e] = softmax_norm<T>(x.v[e], scale);
         if (sizeof(T) == 4 && nv == 4 && out.vec_ok && out.dtype == BG_F32) {
           *reinterpret_cast<float4*>(reinterpret_cast<float*>(out.ptr) + pos.idx(u)) =
               make_float4((float)x.v[0], (float)x.v[1], (float)x.v[2], (float)x.v[3]);
@@ -1146,7 +1207,7 @@ __device__ __forceinline__ void row_resident_tail(const EwProgram& p, const RegF
       for (int e = 0; e < 4; ++e)
         if (e < nv) sum += (float)x.v[e];
     }
-    sum = block_reduce<float>(sum, [](float a, float b) { return a + b; }, 0.f, scratch);
+    sum = block_reduce<float>(sum, [](float a, float b) { return a + b; }, scratch, flip);
     const float mean = sum / (float)p.cols;
     float sq = 0.f;
     BG_FOR_U {
@@ -1159,7 +1220,7 @@ __device__ __forceinline__ void row_resident_tail(const EwProgram& p, const RegF
           sq += __fmul_rn(c, c);
         }
     }
-    sq = block_reduce<float>(sq, [](float a, float b) { return a + b; }, 0.f, scratch);
+    sq = block_reduce<float>(sq, [](float a, float b) { return a + b; }, scratch, flip);
     const float var = sq / (float)p.cols;
     const float inv = 1.0f / sqrtf(var + p.tail_eps);
     const EwOperand& w = p.inputs[p.tail_w];
@@ -1205,15 +1266,16 @@ __global__ void __launch_bounds__(kBlock, BG_EW_MIN_CTAS) row_kernel(const __gri
   const int planes = p.wide ? 2 : 1;
   const RegFile rf(smem, U, planes);
   char* scratch = smem + (size_t)p.n_regs * U * planes * kBlock * 16;
+  int flip = 0;   // which scratch buffer the next block reduction uses
   for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
-    if (KIND == ROW_REDUCE_F32) row_reduce<float>(p, rf, row, n_chunks, scratch);
-    else if (KIND == ROW_REDUCE_F64) row_reduce<double>(p, rf, row, n_chunks, scratch);
-    else if (KIND == ROW_REDUCE_I64) row_reduce<long long>(p, rf, row, n_chunks, scratch);
+    if (KIND == ROW_REDUCE_F32) row_reduce<float>(p, rf, row, n_chunks, scratch, flip);
+    else if (KIND == ROW_REDUCE_F64) row_reduce<double>(p, rf, row, n_chunks, scratch, flip);
+    else if (KIND == ROW_REDUCE_I64) row_reduce<long long>(p, rf, row, n_chunks, scratch, flip);
     else if (KIND == ROW_REDUCE_BOOL) row_reduce_bool(p, rf, row, n_chunks);
-    else if (KIND == ROW_SOFTMAX_F32) row_resident_tail<float, true>(p, rf, row, scratch);
-    else if (KIND == ROW_SOFTMAX_F64) row_resident_tail<double, true>(p, rf, row, scratch);
-    else if (KIND == ROW_LAYERNORM_F32) row_resident_tail<float, false>(p, rf, row, scratch);
-    else row_resident_tail<double, false>(p, rf, row, scratch);
+    else if (KIND == ROW_SOFTMAX_F32) row_resident_tail<float, true>(p, rf, row, scratch, flip);
+    else if (KIND == ROW_SOFTMAX_F64) row_resident_tail<double, true>(p, rf, row, scratch, flip);
+    else if (KIND == ROW_LAYERNORM_F32) row_resident_tail<float, false>(p, rf, row, scratch, flip);
+    else row_resident_tail<double, false>(p, rf, row, scratch, flip);
   }
 }
 

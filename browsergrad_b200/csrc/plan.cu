@@ -845,6 +845,8 @@ struct VInstr {
   uint16_t aux;
 };
 
+static std::string gelu_expr_text();
+
 bool Compiler::build_program(const std::vector<int>& members, int tail_node, ProgramSpec& ps, std::vector<int>& dep_nodes,
                              std::vector<int>& out_nodes, std::string& why) {
   std::vector<VInstr> code;
@@ -942,6 +944,28 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
     auto need = [&](size_t k) {
       if (n.in.size() != k) err(BG_ERR_INVALID, std::string(op_name(n.op)) + ": expected " + std::to_string(k) + " inputs");
     };
+    // The float64 tanh GELU of an fp32 value, in a plan whose leaves hold no float64 data, is evaluated in fp32 and
+    // widened (the same rule sends such contractions to the 3xTF32 path).  The float64 instructions already emitted
+    // for its inner nodes die below unless something else reads them.
+    if (n.op == BG_OP_MUL && n.dtype == BG_F64 && n.in.size() == 2 && ctx_->fusion &&
+        (ctx_->f64_mode == 1 || (ctx_->f64_mode == 2 && !has_f64_leaf_))) {
+      int x = -1;
+      for (int k = 0; k < 2 && x < 0; ++k) {
+        const int h = resolve(n.in[k]);
+        if (kind_[h] != K_EW || nodes_[h].op != BG_OP_MUL || nodes_[h].in.size() != 2) continue;
+        for (int j = 0; j < 2; ++j) {
+          const int c = resolve(nodes_[h].in[j]);
+          if (kind_[c] == K_CONST && view_[c].is_const && dtype_is_float(nodes_[c].dtype) && view_[c].cf == 0.5) x = resolve(nodes_[h].in[1 - j]);
+        }
+      }
+      if (x >= 0 && nodes_[x].dtype == BG_F32 && act_expr(m, x, find(m), 0) == gelu_expr_text()) {
+        const int xv = operand(x, T_F32);
+        if (failed) return false;
+        const int y = emit(E_GELU, T_F32, xv, 0, 0, 0);
+        vreg[m] = emit(E_CVT, T_F64, y, 0, 0, (uint16_t)T_F32);
+        continue;
+      }
+    }
     switch (n.op) {
       case BG_OP_ADD: case BG_OP_MUL: case BG_OP_DIV: {
         need(2);
@@ -1159,7 +1183,8 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
   {
     auto is_unary = [](uint8_t op) {
       return op == E_NEG || op == E_EXP || op == E_LOG || op == E_ABS || op == E_SIGN || op == E_SIN || op == E_COS ||
-             op == E_ISNAN || op == E_CVT || op == E_NARROW || op == E_STORE || op == E_RELU || op == E_EXPNEG || op == E_COPY;
+             op == E_ISNAN || op == E_CVT || op == E_NARROW || op == E_STORE || op == E_RELU || op == E_EXPNEG || op == E_COPY ||
+             op == E_GELU;
     };
     auto n_src = [&](const VInstr& I) { return (I.op == E_LOAD || I.op == E_CONST) ? 0 : (is_unary(I.op) ? 1 : (I.op == E_WHERE ? 3 : 2)); };
     auto src = [](VInstr& I, int k) -> int& { return k == 0 ? I.a : (k == 1 ? I.b : I.c); };
@@ -1178,6 +1203,30 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
     };
     std::vector<int> uses, def;
     recount(uses, def);
+    // values nothing reads (the inner nodes of an expression that was replaced as a whole)
+    for (bool again = true; again;) {
+      again = false;
+      for (size_t i = code.size(); i-- > 0;) {
+        if (dead[i] || code[i].op == E_STORE || code[i].dst < 0 || uses[code[i].dst] != 0) continue;
+        dead[i] = 1;
+        again = true;
+      }
+      if (again) recount(uses, def);
+    }
+    // an fp32 value widened only to be stored into a float64 output is stored by the fp32 instruction itself
+    for (size_t i = 0; i < code.size(); ++i) {
+      if (dead[i]) continue;
+      VInstr& S = code[i];
+      if (S.op != E_STORE || S.type != T_F64 || S.a < 0 || def[S.a] < 0 || uses[S.a] != 1 || S.a == tail_reg_v) continue;
+      const int wi = def[S.a];
+      const VInstr& W = code[wi];
+      if (W.op != E_CVT || W.type != T_F64 || (W.aux & 0xF) != T_F32) continue;
+      if (P.outputs[S.aux].dtype != BG_F64 || !P.outputs[S.aux].vec_ok) continue;
+      S.type = T_F32;
+      S.a = W.a;
+      dead[wi] = 1;
+      recount(uses, def);
+    }
     for (size_t i = 0; i < code.size(); ++i) {
       if (dead[i]) continue;
       VInstr& I = code[i];
@@ -1222,7 +1271,7 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
     // LOADs become direct operands of their consumer
     auto f32_value_op = [](uint8_t op) {
       return op == E_ADD || op == E_SUB || op == E_MUL || op == E_DIV || op == E_NEG || op == E_EXP || op == E_LOG ||
-             op == E_ABS || op == E_SIGN || op == E_SIN || op == E_COS || op == E_RELU || op == E_EXPNEG;
+             op == E_ABS || op == E_SIGN || op == E_SIN || op == E_COS || op == E_RELU || op == E_EXPNEG || op == E_GELU;
     };
     auto dense_f32_in = [&](int k) {
       const EwOperand& o = P.inputs[k];
@@ -1258,7 +1307,7 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
       if (S.op != E_STORE || S.type != T_F32 || S.a < 0 || def[S.a] < 0) continue;
       if (uses[S.a] != 1 || S.a == tail_reg_v) continue;
       const EwOutput& o = P.outputs[S.aux];
-      if (o.dtype != BG_F32 || !o.vec_ok) continue;
+      if ((o.dtype != BG_F32 && o.dtype != BG_F64) || !o.vec_ok) continue;   // float64: the store widens
       VInstr& D = code[def[S.a]];
       if (D.type != T_F32 || !(f32_value_op(D.op) || D.op == E_WHERE)) continue;
       D.dst = -2000 - (int)S.aux;
@@ -1273,7 +1322,7 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
         I.op = E_COPY;
         I.a = -1000 - (int)I.aux;
         I.aux = 0;
-      } else if (I.op == E_STORE && P.outputs[I.aux].dtype == BG_F32 && P.outputs[I.aux].vec_ok) {
+      } else if (I.op == E_STORE && (P.outputs[I.aux].dtype == BG_F32 || P.outputs[I.aux].dtype == BG_F64) && P.outputs[I.aux].vec_ok) {
         I.op = E_COPY;
         I.dst = -2000 - (int)I.aux;
         I.aux = 0;
@@ -1318,7 +1367,7 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
     auto use = [&](int v) { if (v >= 0) last[v] = (int)i; };
     const bool unary = I.op == E_NEG || I.op == E_EXP || I.op == E_LOG || I.op == E_ABS || I.op == E_SIGN || I.op == E_SIN ||
                        I.op == E_COS || I.op == E_ISNAN || I.op == E_CVT || I.op == E_NARROW || I.op == E_STORE ||
-                       I.op == E_RELU || I.op == E_EXPNEG || I.op == E_COPY;
+                       I.op == E_RELU || I.op == E_EXPNEG || I.op == E_COPY || I.op == E_GELU;
     if (I.op == E_LOAD || I.op == E_CONST) continue;
     use(I.a);
     if (!unary) use(I.b);
@@ -1343,7 +1392,7 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
     O.aux = I.aux;
     const bool unary = I.op == E_NEG || I.op == E_EXP || I.op == E_LOG || I.op == E_ABS || I.op == E_SIGN || I.op == E_SIN ||
                        I.op == E_COS || I.op == E_ISNAN || I.op == E_CVT || I.op == E_NARROW || I.op == E_STORE ||
-                       I.op == E_RELU || I.op == E_EXPNEG || I.op == E_COPY;
+                       I.op == E_RELU || I.op == E_EXPNEG || I.op == E_COPY || I.op == E_GELU;
     const bool leaf = I.op == E_LOAD || I.op == E_CONST;
     int srcs[3] = {leaf ? -1 : I.a, (leaf || unary) ? -1 : I.b, I.op == E_WHERE ? I.c : -1};
     auto enc = [&](int v) -> uint8_t {
@@ -1381,7 +1430,7 @@ bool Compiler::build_program(const std::vector<int>& members, int tail_node, Pro
     const VInstr& L = code.back();
     const bool value_op = L.op == E_ADD || L.op == E_SUB || L.op == E_MUL || L.op == E_DIV || L.op == E_NEG || L.op == E_EXP ||
                           L.op == E_LOG || L.op == E_ABS || L.op == E_SIGN || L.op == E_SIN || L.op == E_COS || L.op == E_RELU ||
-                          L.op == E_EXPNEG || L.op == E_WHERE || L.op == E_COPY;
+                          L.op == E_EXPNEG || L.op == E_WHERE || L.op == E_COPY || L.op == E_GELU;
     if (L.type == T_F32 && value_op && L.dst == tail_reg_v) P.tail_acc = 1;
   }
   const int64_t per_chunk = (int64_t)P.n_regs * (wide ? 2 : 1) * 4096;
@@ -1779,6 +1828,12 @@ int Compiler::tc_mode(int n) {
   return mode;
 }
 
+// act_expr() of the reference's tanh GELU of x: 0.5 x (1 + tanh(k (x + 0.044715 x^3))) with tanh written out in exponentials.
+static std::string gelu_expr_text() {
+  const std::string Z = "mul(c0.797885,add(x,mul(mul(mul(c0.044715,x),x),x)))";
+  return "mul(mul(c0.5,x),add(c1,div(add(exp(" + Z + "),neg(exp(neg(" + Z + ")))),add(exp(" + Z + "),exp(neg(" + Z + "))))))";
+}
+
 // Expression of `node` in terms of the value `x`, constants, and elementwise members of group g.
 std::string Compiler::act_expr(int node, int x, int g, int depth) {
   node = resolve(node);
@@ -1919,8 +1974,7 @@ void Compiler::plan_tc_epilogues(const std::map<int, std::vector<int>>& groups) 
   epi_plan_.clear();
   absorbed_groups_.clear();
   if (!ctx_->fusion) return;
-  const std::string Z = "mul(c0.797885,add(x,mul(mul(mul(c0.044715,x),x),x)))";
-  const std::string gelu = "mul(mul(c0.5,x),add(c1,div(add(exp(" + Z + "),neg(exp(neg(" + Z + ")))),add(exp(" + Z + "),exp(neg(" + Z + "))))))";
+  const std::string gelu = gelu_expr_text();
   const std::string relu = "where(cmp" + std::to_string((int)BG_CMP_GT) + "(x,c0),x,c0)";
   for (int n = 0; n < (int)nodes_.size(); ++n) {
     if (kind_[n] != K_OTHER || nodes_[n].op != BG_OP_MATMUL) continue;

@@ -381,6 +381,12 @@ CASES: Dict[str, Case] = {
                             lambda api, t, raw: (t["x"] * t["row"] + t["col"]) / t["p"]),
     "log_exp": Case(_misc_inputs, lambda api, t, raw: (t["p"].log() * 0.5).exp()),
     "f64_chain": Case(_misc_inputs, lambda api, t, raw: (t["d"] * t["d"] + t["x"]).exp() / 3.0),
+    # F.gelu of an fp32 value: Python scalars make its tail float64 under NumPy 2.  Without a float64 leaf in the plan
+    # the tail is evaluated in fp32 and widened (inputs span the saturated ends: 9 * x); with one it stays float64.
+    "gelu_f64_tail": Case(_misc_inputs, lambda api, t, raw: api.gelu(t["x"] * t["p"] + t["row"])),
+    "gelu_f64_tail_wide": Case(_misc_inputs, lambda api, t, raw: api.gelu(t["x"] * 9.0)),
+    "gelu_f64_tail_rows": Case(_misc_inputs, lambda api, t, raw: api.gelu(t["x"] * t["p"]).sum(axis=-1)),
+    "gelu_f64_leaf": Case(_misc_inputs, lambda api, t, raw: api.gelu(t["x"] * t["p"]) + t["d"], rtol=1e-12),
     "f16_chain": Case(_misc_inputs, lambda api, t, raw: t["h"] * t["h"] + t["h"], rtol=2e-3),
     "cast_chain": Case(_misc_inputs,
                        lambda api, t, raw: (t["x"] * 100.0).cast("int32").cast("float32") + t["row"]),
