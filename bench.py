@@ -246,7 +246,7 @@ def time_plan(bridge, torch, stream, graph_root, store, front, steps: int, warmu
     return ms, prof, trace
 
 
-EXTRA_NAMES = ("mlp", "interp", "gemm_bf16_1024", "gemm_fp32_1024", "gemm_bf16_4096", "gemm_fp32_4096", "gemm_bf16_8192",
+EXTRA_NAMES = ("mlp", "interp", "ce", "gemm_bf16_1024", "gemm_fp32_1024", "gemm_bf16_4096", "gemm_fp32_4096", "gemm_bf16_8192",
                "gemm_fp32_8192", "attn_fp32", "attn_bf16", "gpt")
 NOMINAL = {"hbm_gbs": 7700.0, "bf16_tflops": 2250.0}   # B200 data-sheet figures, printed beside the measured peaks
 
@@ -262,7 +262,7 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn
     when a single kernel is captured under a profiler)."""
     from browsergrad_b200 import configs, front, graph
     want = set(only) if only else set(EXTRA_NAMES)
-    out = {"mlp": [], "interpreter": [], "gemm": [], "attention": [], "gpt": []}
+    out = {"mlp": [], "interpreter": [], "cross_entropy": [], "gemm": [], "attention": [], "gpt": []}
     if "interp" in want:
         # The generic interpreter, which every fusion group without a specialised kernel gets: the three config-2
         # plans with the pattern kernels switched off, and two chains no pattern matches (an fp32 select chain and the
@@ -299,9 +299,33 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn
         t = {k: graph.from_numpy(v, store) for k, v in arrays.items()}
         root = configs.mlp_loss(graph, t)
         ms, prof, trace = time_plan(bridge, torch, stream, root, store, front, max(steps, 20))
+        n_prof = max(steps, 20)
         out["mlp"].append({"workload": "MLP 784-128(ReLU)-10 + cross entropy, batch 64, fp32", "us_per_forward": ms * 1e3,
-                           "kernels": trace})
+                           "kernels": trace,
+                           "kernel_us": {p["name"]: 1e3 * p["ms"] / n_prof for p in prof},
+                           "note": "us_per_forward is the time between back-to-back forwards on the stream (host submission "
+                                   "included when it is the slower side); kernel_us are the units' own device times"})
         del arrays, store, t
+    if "ce" in want:
+        # cross entropy over the vocabulary of configuration 5: [8192, 32000] fp32 logits, int64 targets, mean
+        # reduction.  Algorithmic bytes = the logits read once plus the targets.
+        import numpy as np
+        ce_rows, ce_classes = 8192 * attn_batch // 16 if attn_batch < 16 else 8192, 32000
+        rng = np.random.default_rng(5)
+        store = graph.BufferStore()
+        logits = graph.from_numpy(rng.standard_normal((ce_rows, ce_classes), dtype=np.float32), store)
+        target = graph.from_numpy(rng.integers(0, ce_classes, (ce_rows,), dtype=np.int64), store)
+        for name, root in (("mean", graph.cross_entropy(logits, target)),
+                           ("mean, label smoothing 0.1", graph.cross_entropy(logits, target, label_smoothing=0.1))):
+            ms, prof, trace = time_plan(bridge, torch, stream, root, store, front, steps)
+            nbytes = ce_rows * ce_classes * 4 + ce_rows * 8
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            out["cross_entropy"].append({"workload": f"cross entropy ({name}), fp32 logits [{ce_rows},{ce_classes}], int64 targets",
+                                         "plan_ms": ms, "kernels": trace, "algorithmic_bytes": nbytes,
+                                         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                                      "frac": gbs / peaks["hbm_gbs"], "frac_of_nominal": gbs / NOMINAL["hbm_gbs"],
+                                                      "nominal_peak": NOMINAL["hbm_gbs"], "basis": "plan time"}})
+        del store, logits, target
     for n in (1024, 4096, 8192):
         for amp in ("bfloat16", ""):
             if f"gemm_{'bf16' if amp else 'fp32'}_{n}" not in want:
@@ -380,13 +404,16 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn
         meta = arrays.pop("_meta")
         store = graph.BufferStore()
         t = {k: graph.from_numpy(v, store) for k, v in arrays.items()}
-        root = configs.gpt_forward(graph, t, meta)
         gpt_steps = max(3, steps // 2)
-        ms, prof, trace = time_plan(bridge, torch, stream, root, store, front, gpt_steps)
-        top = sorted(prof, key=lambda p: -p["ms"])[:6]
-        out["gpt"].append({"workload": "GPT decoder forward 12L d768 h12 mlp3072 V32000 seq1024, batch 8 (one GPU's shard of 64), fp32 graph (3xTF32)",
-                           "tokens_per_s": 8 * 1024 / (ms * 1e-3), "plan_ms": ms, "units": len(trace),
-                           "top_kernels": [{"name": p["name"], "ms_per_forward": p["ms"] / gpt_steps} for p in top]})
+        # the fp32 graph (contractions on the 3xTF32 path), then the same decoder built under autocast: float16 is the
+        # dtype the reference's AMP pass pins, bfloat16 follows the same cast rule
+        for amp, label in (("", "fp32 graph (3xTF32)"), ("float16", "float16 autocast"), ("bfloat16", "bfloat16 autocast")):
+            root = configs.gpt_forward(graph, t, meta, amp=amp)
+            ms, prof, trace = time_plan(bridge, torch, stream, root, store, front, gpt_steps)
+            top = sorted(prof, key=lambda p: -p["ms"])[:6]
+            out["gpt"].append({"workload": f"GPT decoder forward 12L d768 h12 mlp3072 V32000 seq1024, batch 8 (one GPU's shard of 64), {label}",
+                               "tokens_per_s": 8 * 1024 / (ms * 1e-3), "plan_ms": ms, "units": len(trace),
+                               "top_kernels": [{"name": p["name"], "ms_per_forward": p["ms"] / gpt_steps} for p in top]})
         del arrays, store, t
     return out
 
@@ -452,12 +479,13 @@ def collective_extras(bridge, torch, dist, world: int, rank: int, local: int, re
     buf = graph.Node("BUFFER", (), (world * rows, d_model), "float32", bid)
     x = graph.Tensor(graph.Node("LOAD", (buf,), buf.shape, buf.dtype, None), front._ResidentStore(store, table, bridge))
     results = []
+    w_block = sharded.weight_block(w, x._store)       # this rank's [vocab / world, d_model] rows: uploaded by the first call, resident after
 
     def lm_head():
         while results:
             t_out = results.pop()
             table.release(t_out._uop.inputs[0].arg)
-        results.append(sharded.column_split_linear(bridge, x, w, None, device=local))
+        results.append(sharded.column_split_linear(bridge, x, w_block, None, device=local))
     t_head = timed(lm_head)
     m = world * rows
     logits_bytes = m * vocab * 4

@@ -122,9 +122,13 @@ def gpt_inputs(layers: int = 12, d_model: int = 768, heads: int = 12, d_mlp: int
     return t
 
 
-def gpt_forward(api: Any, t: Dict[str, Any], meta: Tuple[int, ...], logits: bool = True) -> Any:
+def gpt_forward(api: Any, t: Dict[str, Any], meta: Tuple[int, ...], logits: bool = True, amp: str = "") -> Any:
     """Config 5: pre-LayerNorm GPT decoder forward built from gather, layer_norm, linear,
-    scaled_dot_product_attention, gelu and residual adds; the LM head shares ``wte``."""
+    scaled_dot_product_attention, gelu and residual adds; the LM head shares ``wte``.  ``amp`` = "", "float16" or
+    "bfloat16" builds it under autocast."""
+    if amp:
+        with api.autocast(dtype=amp):
+            return gpt_forward(api, t, meta, logits)
     layers, d_model, heads, d_mlp, vocab, seq, batch = (int(v) for v in meta)
     dh = d_model // heads
     x = t["wte"].gather(0, t["tok_index"]) + t["wpe"].gather(0, t["pos_index"])

@@ -250,6 +250,12 @@ struct GemmProblem {
 // Reference-order SIMT GEMM for every dtype (fp32 FMA, fp64 FMA, exact int64).
 cudaError_t launch_gemm_simt(const GemmProblem& p, cudaStream_t s);
 
+// Split-K kernel for small 2-D fp32 problems (gemm_simt.cu), with an fp32 bias row and ReLU folded.  gemm_small_plan
+// says whether the problem qualifies, into how many K slices it is cut and how many bytes of partial tiles it needs;
+// `counters` are 1024 device ints that are zero between launches.
+bool gemm_small_plan(const GemmProblem& p, int sm_count, int* splits, int64_t* partial_bytes);
+cudaError_t launch_gemm_small(const GemmProblem& p, const void* bias, int act, void* partials, int* counters, int splits, cudaStream_t s);
+
 // Tensor-core GEMM (gemm_tc.cu): C[M,N] = epilogue(A[M,K] . B[N,K]^T), operands dense row-major.
 enum TcAct { TC_ACT_NONE = 0, TC_ACT_RELU = 1, TC_ACT_GELU = 2 };
 struct TcGemm {

@@ -341,6 +341,13 @@ int bg_create(int device_ordinal, bg_context** out) {
     return BG_ERR_CUDA;
   }
   cudaMemsetAsync(ctx->d_status, 0, 256, ctx->stream);
+  if (cudaMalloc(&ctx->gemm_counters, 1024 * sizeof(int)) != cudaSuccess) {
+    cudaFree(ctx->d_status);
+    cudaFreeHost(ctx->h_status);
+    delete ctx;
+    return BG_ERR_CUDA;
+  }
+  cudaMemsetAsync(ctx->gemm_counters, 0, 1024 * sizeof(int), ctx->stream);
   *out = ctx;
   return BG_OK;
 }
@@ -366,6 +373,7 @@ int bg_destroy(bg_context* ctx) {
   cudaStreamSynchronize(ctx->stream);
   if (ctx->uniform_pool) cudaFree(ctx->uniform_pool);
   if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->gemm_counters) cudaFree(ctx->gemm_counters);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   if (ctx->stage) cudaFreeHost(ctx->stage);
   cudaStreamDestroy(ctx->stream);

@@ -234,6 +234,15 @@ struct CeRowArgs {
 template <typename T> __device__ __forceinline__ T ce_exp(T x);
 template <> __device__ __forceinline__ float ce_exp<float>(float x) { return expf(x); }
 template <> __device__ __forceinline__ double ce_exp<double>(double x) { return exp(x); }
+// exp of a non-positive shifted logit inside the long-row sum: fp32 rows use the hardware exp2 unit (the argument is
+// bounded below by the row's range, so its rounding stays near 1e-6 relative on terms that matter); fp64 rows keep exp().
+template <typename T> __device__ __forceinline__ T ce_exp_term(T x);
+template <> __device__ __forceinline__ float ce_exp_term<float>(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+  return y;
+}
+template <> __device__ __forceinline__ double ce_exp_term<double>(double x) { return exp(x); }
 template <typename T> __device__ __forceinline__ T ce_log(T x);
 template <> __device__ __forceinline__ float ce_log<float>(float x) { return logf(x); }
 template <> __device__ __forceinline__ double ce_log<double>(double x) { return log(x); }
@@ -313,13 +322,13 @@ __global__ void ce_pos_kernel(const CeRowArgs<T> a) {
 // 16-byte vectors (coalesced), keeping a running maximum that is raised once per group of vectors, and the partial
 // (M, S, T1, T2) of all threads are combined through shared memory.  The row is read from DRAM once; the statistics
 // are rescaled, never the data.
-template <typename T, int VEC>
+template <typename T, int VEC, bool SUMS>
 __global__ void __launch_bounds__(256) ce_row_kernel(const CeRowArgs<T> a, int vec_ok) {
-  constexpr int kGroup = 4;                       // vectors per thread between maximum updates
+  constexpr int kGroup = (sizeof(T) == 4 && !SUMS) ? 8 : 4;   // vectors per thread in flight between maximum updates
   const int64_t row = blockIdx.x;
   const T* x = a.logits + row * a.C;
   const T* pr = a.prob ? a.prob + row * a.C : nullptr;
-  const bool need_sums = a.prob != nullptr || a.smoothing != T(0);
+  constexpr bool need_sums = SUMS;                // probability targets or label smoothing: the weighted sums T1, T2
   const T eps = a.smoothing, unif = a.smoothing / (T)a.C;
   __shared__ T sh_m[8], sh_s[8], sh_t1[8], sh_t2[8];
   const bool skip = !a.prob && a.idx[row] == a.ignore_index;      // the whole CTA agrees
@@ -335,7 +344,7 @@ __global__ void __launch_bounds__(256) ce_row_kernel(const CeRowArgs<T> a, int v
     };
     auto add = [&](T xv, T pv, T wv) {
       const T shv = xv - M;
-      S += ce_exp<T>(shv);
+      S += ce_exp_term<T>(shv);
       if (need_sums) {
         T q = wv;
         if (pr) q *= pv * (T(1) - eps) + unif;
@@ -554,7 +563,8 @@ cudaError_t ce_rows_typed(const CeProblem& c, cudaStream_t s) {
                          (!c.prob_targets || (reinterpret_cast<uintptr_t>(c.targets) & 15) == 0) &&
                          (!c.weight || (reinterpret_cast<uintptr_t>(c.weight) & 15) == 0);
     const int threads = c.C >= 4096 ? 256 : 128;
-    ce_row_kernel<T, VEC><<<(unsigned)n, threads, 0, s>>>(a, aligned ? 1 : 0);
+    if (a.prob != nullptr || a.smoothing != T(0)) ce_row_kernel<T, VEC, true><<<(unsigned)n, threads, 0, s>>>(a, aligned ? 1 : 0);
+    else ce_row_kernel<T, VEC, false><<<(unsigned)n, threads, 0, s>>>(a, aligned ? 1 : 0);
   } else {
     ce_pos_kernel<T><<<grid_for(n, 128), 128, 0, s>>>(a);
   }

@@ -104,11 +104,12 @@ struct CompiledPlan {
   int root_rank = 0;
   int64_t root_shape[kMaxRank] = {0};
   int64_t root_bytes = 0;
-  // The device status word: `uses_status` marks kernels that can refuse their data (an index outside its axis) --
-  // the plan then ends with a synchronising check, as the reference raises at the call; `uses_wait_status` marks
-  // kernels whose bounded device waits can give up (tensor-core pipelines).  That is a fault of the device, not of
-  // the data, so a plan that keeps its root on the device does not wait for it: the word is copied to the host
-  // behind the plan and examined by the next call that synchronises anyway or starts another plan.
+  // The device status word: `uses_status` marks kernels that can refuse their data (an index outside its axis),
+  // `uses_wait_status` kernels whose bounded device waits can give up (tensor-core pipelines).  A plan that returns
+  // its root to the host synchronises anyway and examines the word before it hands anything back, so the refusal is
+  // raised at the call, as the reference raises it.  A plan that keeps its root on the device does not wait: the word
+  // is copied to the host behind the plan and examined by the next call that synchronises or starts another plan --
+  // always before any byte computed from the refused data can reach the host.
   bool uses_status = false;
   bool uses_wait_status = false;
   int64_t plan_peak = 0;
@@ -280,6 +281,7 @@ class Compiler {
   std::map<std::tuple<int, int64_t, int64_t, int>, std::pair<int, int>> conv_memo_;   // fp32 A operand -> (16-bit slot, converting unit)
   std::set<int> absorbed_groups_;
   int tc_mode(int n);                      // -1: SIMT; 0: 16-bit operands; 1: 3xTF32
+  bool small_gemm(int n, int* splits, int64_t* partial_bytes);   // a 2-D fp32 MATMUL the split-K small kernel takes
   std::string act_expr(int node, int x, int g, int depth);
   void plan_tc_epilogues(const std::map<int, std::vector<int>>& groups);
   std::shared_ptr<CompiledPlan> cp_;
@@ -1834,6 +1836,22 @@ static std::string gelu_expr_text() {
   return "mul(mul(c0.5,x),add(c1,div(add(exp(" + Z + "),neg(exp(neg(" + Z + ")))),add(exp(" + Z + "),exp(neg(" + Z + "))))))";
 }
 
+// A small 2-D fp32 MATMUL (below the tensor-core threshold) runs on the split-K kernel of gemm_simt.cu.
+bool Compiler::small_gemm(int n, int* splits, int64_t* partial_bytes) {
+  const Node& t = nodes_[n];
+  if (!ctx_->fusion || t.in.size() != 2 || t.rank != 2 || t.dtype != BG_F32 || tc_mode(n) >= 0) return false;
+  const View& av = view_[resolve(t.in[0])];
+  const View& bv = view_[resolve(t.in[1])];
+  if (av.is_const || bv.is_const || av.rank != 2 || bv.rank != 2 || av.dtype != BG_F32 || bv.dtype != BG_F32) return false;
+  GemmProblem gp{};
+  gp.m = av.shape[0];
+  gp.k = av.shape[1];
+  gp.n = bv.shape[1];
+  if (bv.shape[0] != gp.k) return false;
+  gp.a.dtype = gp.b.dtype = gp.c_dtype = BG_F32;
+  return gemm_small_plan(gp, ctx_->sm_count, splits, partial_bytes);
+}
+
 // Expression of `node` in terms of the value `x`, constants, and elementwise members of group g.
 std::string Compiler::act_expr(int node, int x, int g, int depth) {
   node = resolve(node);
@@ -1979,7 +1997,10 @@ void Compiler::plan_tc_epilogues(const std::map<int, std::vector<int>>& groups) 
   for (int n = 0; n < (int)nodes_.size(); ++n) {
     if (kind_[n] != K_OTHER || nodes_[n].op != BG_OP_MATMUL) continue;
     if (attn_plan_.count(n) || attn_absorbed_.count(n)) continue;
-    if (tc_mode(n) < 0) continue;
+    int small_splits = 0;
+    int64_t small_bytes = 0;
+    const bool small = tc_mode(n) < 0 && small_gemm(n, &small_splits, &small_bytes);   // fp32 bias row and ReLU only
+    if (tc_mode(n) < 0 && !small) continue;
     const int64_t N = nodes_[n].shape[1];
     EpiPlan ep;
     std::set<int> absorbed;
@@ -2009,7 +2030,8 @@ void Compiler::plan_tc_epilogues(const std::map<int, std::vector<int>>& groups) 
         const View& bv = view_[other];
         const bool row = !bv.is_const && bv.numel() == N && bv.contiguous() && bv.rank >= 1 && bv.shape[bv.rank - 1] == N &&
                          leaflike_[other] && (bv.dtype == BG_F32 || bv.dtype == BG_F64 || bv.dtype == BG_F16);
-        if (row && (nodes_[nx].dtype == BG_F32 || nodes_[nx].dtype == BG_F64)) {
+        if (row && (nodes_[nx].dtype == BG_F32 || nodes_[nx].dtype == BG_F64) &&
+            (!small || (bv.dtype == BG_F32 && nodes_[nx].dtype == BG_F32))) {
           ep.bias_node = other;
           absorbed.insert(nx);
           cur = nx;
@@ -2059,6 +2081,7 @@ void Compiler::plan_tc_epilogues(const std::map<int, std::vector<int>>& groups) 
     }
     const int fdt = nodes_[final_node].dtype;
     if (fdt != BG_F32 && fdt != BG_F64) continue;
+    if (small && (fdt != BG_F32 || ep.act == TC_ACT_GELU)) continue;
     ep.wide = fdt == BG_F64 && ep.act == TC_ACT_GELU && nodes_[cur].dtype != BG_F64 ? 1 : (fdt == BG_F64 ? 1 : 0);
     ep.final_node = final_node;
     ep.group = g;
@@ -2652,6 +2675,49 @@ void Compiler::emit_matmul(int n, int key) {
         return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "tensor-core gemm launch");
       };
       tc_unit_of_[n] = (int)punits_.size();
+      add_unit(std::move(pu));
+      return;
+    }
+  }
+  {
+    int splits = 0;
+    int64_t partial_bytes = 0;
+    if (!a_vec && !b_vec && small_gemm(n, &splits, &partial_bytes) && gemm_small_plan(gp, ctx_->sm_count, &splits, &partial_bytes)) {
+      PUnit pu;
+      pu.order_key = key;
+      pu.dep_nodes = {a, b};
+      pu.out_nodes = {n};
+      int out_slot = sc, bias_slot = -1, act = TC_ACT_NONE;
+      int64_t bias_off = 0;
+      std::string epi_name;
+      auto ep_it = epi_plan_.find(n);
+      if (ep_it != epi_plan_.end()) {
+        const EpiPlan& ep = ep_it->second;
+        out_slot = view_[ep.final_node].slot;
+        act = ep.act;
+        if (ep.bias_node >= 0) {
+          const View& bvw = view_[ep.bias_node];
+          bias_slot = bvw.slot;
+          bias_off = bvw.off * 4;
+          pu.dep_nodes.push_back(ep.bias_node);
+          epi_name += "+bias";
+        }
+        if (act == TC_ACT_RELU) epi_name += "+relu";
+        pu.out_nodes = {ep.final_node};
+      }
+      const int part_slot = partial_bytes > 0 ? new_slot(partial_bytes, false, -1) : -1;
+      if (part_slot >= 0) pu.u.writes.push_back(part_slot);
+      pu.u.name = std::string("gemm_small") + epi_name + "[float32]";
+      pu.u.fn = [=](Run& r) {
+        GemmProblem p = gp;
+        p.a.ptr = reinterpret_cast<char*>(r.ptr[sa]) + offa;
+        p.b.ptr = reinterpret_cast<char*>(r.ptr[sb]) + offb;
+        p.c = r.ptr[out_slot];
+        const void* bias = bias_slot >= 0 ? reinterpret_cast<char*>(r.ptr[bias_slot]) + bias_off : nullptr;
+        cudaError_t e = launch_gemm_small(p, bias, act, part_slot >= 0 ? r.ptr[part_slot] : nullptr, r.ctx->gemm_counters, splits,
+                                          r.ctx->stream);
+        return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "small gemm launch");
+      };
       add_unit(std::move(pu));
       return;
     }
@@ -3343,11 +3409,11 @@ int run_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs, 
   int status_rc = BG_OK;
   if (cp->uses_status || cp->uses_wait_status)
     cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream);
-  if (cp->uses_status || (cp->uses_wait_status && out_host)) {
+  if ((cp->uses_status || cp->uses_wait_status) && out_host) {
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) { cleanup(false); return cuda_fail(ctx, e, "plan execution"); }
     status_rc = take_device_status(ctx);
-  } else if (cp->uses_wait_status) {
+  } else if (cp->uses_status || cp->uses_wait_status) {
     ctx->status_pending = true;
   }
   if (status_rc) {

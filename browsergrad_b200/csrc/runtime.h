@@ -43,6 +43,7 @@ struct bg_context {
   int* d_status = nullptr;
   int* h_status = nullptr;  // pinned
   bool status_pending = false;   // a plan that may have set the word ended without a synchronising check
+  int* gemm_counters = nullptr;  // 1024 device ints, zero between launches: tile arrival counters of the split-K small GEMM
   // pinned staging for host <-> device copies
   void* stage = nullptr;
   size_t stage_bytes = 0;

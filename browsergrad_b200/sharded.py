@@ -151,26 +151,38 @@ def resident_handle(tensor: Any) -> int:
     return h
 
 
-def column_split_linear(bridge: Any, x: Any, weight: np.ndarray, bias: Optional[np.ndarray], *, group: Any = None,
-                        device: int = 0) -> Any:
-    """``x @ weight.T + bias`` for a very wide ``weight`` [N, K] (an LM head), split along N over the ranks: every rank
-    multiplies the same ``x`` [M, K] (a graph tensor; device-resident or not) by its own block of ``N / world`` rows of
-    ``weight`` held in its own HBM, the [M, N / world] blocks are all-gathered on the devices (NCCL; no kernel reads a
-    peer's memory) and one strided copy per rank lays them side by side.  Returns a device-resident graph tensor
-    [M, N] on every rank (``front.materialize_resident`` fetches it).  The per-element products and their order are
-    those of the unsplit Linear, so the result is bit-identical to it."""
-    from . import front, graph
+def weight_block(weight: np.ndarray, store: Any, group: Any = None) -> Any:
+    """This rank's block of ``N / world`` rows of ``weight`` [N, ...] as a graph leaf of ``store``.  Made once and
+    passed to ``column_split_linear`` call after call, it is uploaded once and then stays in this rank's HBM."""
+    from . import graph
     dist = _dist()
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
-    n_total, k = int(weight.shape[0]), int(weight.shape[1])
+    n_total = int(weight.shape[0])
     if n_total % world:
-        raise ValueError(f"column_split_linear: {n_total} output columns do not divide over {world} ranks")
+        raise ValueError(f"weight_block: {n_total} rows do not divide over {world} ranks")
     n_r = n_total // world
+    return graph.from_numpy(np.ascontiguousarray(weight[rank * n_r:(rank + 1) * n_r]), store)
+
+
+def column_split_linear(bridge: Any, x: Any, weight: Any, bias: Any, *, group: Any = None, device: int = 0) -> Any:
+    """``x @ weight.T + bias`` for a very wide ``weight`` [N, K] (an LM head), split along N over the ranks: every rank
+    multiplies the same ``x`` [M, K] (a graph tensor; device-resident or not) by its own block of ``N / world`` rows of
+    ``weight`` held in its own HBM, the [M, N / world] blocks are all-gathered on the devices (NCCL; no kernel reads a
+    peer's memory) and one strided copy per rank lays them side by side.  ``weight`` / ``bias`` are either the whole
+    arrays (this rank's block is cut out and uploaded by this call) or the leaves ``weight_block`` made from them (the
+    block is uploaded once and reused).  Returns a device-resident graph tensor [M, N] on every rank
+    (``front.materialize_resident`` fetches it).  The per-element products and their order are those of the unsplit
+    Linear, so the result is bit-identical to it."""
+    from . import front, graph
+    dist = _dist()
+    world = dist.get_world_size(group)
     m = int(x.shape[0])
     store = x._store
-    w_r = graph.from_numpy(np.ascontiguousarray(weight[rank * n_r:(rank + 1) * n_r]), store)
-    b_r = graph.from_numpy(np.ascontiguousarray(bias[rank * n_r:(rank + 1) * n_r]), store) if bias is not None else None
+    w_r = weight if isinstance(weight, graph.Tensor) else weight_block(weight, store, group)
+    b_r = bias if bias is None or isinstance(bias, graph.Tensor) else weight_block(bias, store, group)
+    n_r = int(w_r.shape[0])
+    n_total = n_r * world
     local = front.realize_cuda_resident(graph.linear(x, w_r, b_r), bridge)          # [M, n_r] on this rank's device
     h_local = resident_handle(local)
     # all-gather as row blocks of a [world * M, n_r] array, then [world, M, n_r] -> [M, world, n_r] = [M, N]

@@ -295,6 +295,10 @@ CASES: Dict[str, Case] = {
                          lambda api, t, raw: configs.attention(api, t, "none")),
     "c5_gpt_tiny": Case(_gpt_tiny, lambda api, t, raw: configs.gpt_forward(api, t, raw["_meta"]),
                         rtol=1e-4),
+    "c5_gpt_tiny_f16": Case(_gpt_tiny, lambda api, t, raw: configs.gpt_forward(api, t, raw["_meta"], amp="float16"),
+                            rtol=2e-2),
+    "c5_gpt_tiny_bf16": Case(_gpt_tiny, lambda api, t, raw: configs.gpt_forward(api, t, raw["_meta"], amp="bfloat16"),
+                             rtol=2e-2, reference_has_it=False),
     # -- single ops and edge cases -----------------------------------------------------
     "typed_attention": Case(_attn_small(2, 2, 40, 24),
                             lambda api, t, raw: api.attention_forward(t["q"], t["k"], t["v"])),

@@ -53,6 +53,22 @@ def test_cross_entropy_target_out_of_range_is_refused(bridge, classes):
     _still_works(bridge)
 
 
+def test_refusal_in_a_plan_whose_root_stays_on_the_device_is_raised_before_any_byte_reaches_the_host(bridge):
+    """A plan that keeps its root on the device does not wait for the device: the refusal is raised by the call
+    that fetches the buffer (or by the next plan), never later than the first byte read back."""
+    from browsergrad_b200.front import materialize_resident, realize_cuda_resident, release_resident_leaves
+    store = graph.BufferStore()
+    x = graph.from_numpy(np.arange(12, dtype=np.float32).reshape(3, 4), store)
+    idx = np.zeros((2, 4), np.int64)
+    idx[0, 1] = 5
+    kept = realize_cuda_resident(x.gather(0, graph.from_numpy(idx, store)) * 2.0, bridge)
+    with pytest.raises(KernelError) as exc:
+        materialize_resident(kept)
+    assert exc.value.status == 7
+    release_resident_leaves(bridge)
+    _still_works(bridge)
+
+
 def test_exhausted_device_memory_is_reported_as_out_of_memory(bridge):
     case = CASES["c2_rowsoftmax"]
     t, _, _ = build_case(case)

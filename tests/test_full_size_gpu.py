@@ -131,3 +131,25 @@ def test_config5_full_depth_sequences_are_independent_and_match_the_oracle(bridg
     assert logits.shape == (seq, vocab)
     want_tail = want[-64:].astype(np.float64) @ one["wte"].astype(np.float64).T
     assert rel_err(logits[-64:], want_tail.astype(logits.dtype)) <= 1e-5
+
+
+@pytest.mark.parametrize("amp", ["float16", "bfloat16"])
+def test_config5_full_depth_under_autocast_matches_the_oracle(bridge, amp):
+    """The 12-layer decoder built under autocast (float16 is the dtype the reference's AMP pass pins,
+    packages/browsergrad-jit/src/python/_amp.py:183-261; bfloat16 follows the same cast rule): one sequence, hidden
+    states and the logits of the last 64 positions against the oracle, at the 2e-2 of the 16-bit path."""
+    one = configs.gpt_inputs(batch=1)
+    meta = one.pop("_meta")
+    layers, d_model, heads, d_mlp, vocab, seq, batch = (int(v) for v in meta)
+    store = graph.BufferStore()
+    t = _tensors(one, store)
+    hidden = realize_cuda(configs.gpt_forward(graph, t, meta, logits=False, amp=amp), bridge)
+    trace = bridge.last_plan_trace()
+    assert any(ln.startswith("gemm_tc") and "3xtf32" not in ln for ln in trace), trace      # the 16-bit tensor-core path ran
+    want = _oracle(configs.gpt_forward(graph, t, meta, logits=False, amp=amp), store)
+    assert hidden.shape == want.shape == (seq, d_model)
+    assert rel_err(hidden, want) <= 2e-2
+    logits = realize_cuda(configs.gpt_forward(graph, t, meta, amp=amp), bridge)
+    assert logits.shape == (seq, vocab)
+    want_logits = _oracle(configs.gpt_forward(graph, t, meta, amp=amp), store)
+    assert rel_err(logits[-64:], want_logits[-64:]) <= 2e-2
