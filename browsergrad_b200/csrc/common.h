@@ -285,7 +285,7 @@ cudaError_t launch_gemm_tc_group(const TcGemm* gs, int n_prob, int* status, cuda
 // Self test of the bounded device wait: a wait of `limit_cycles` on a barrier nothing arrives on; sets *status.
 cudaError_t launch_wait_timeout_selftest(long long limit_cycles, int* status, cudaStream_t s);
 // hi = tf32(x) (round to nearest), lo = x - hi, for fp32 or fp64 input; optional transpose is not done here.
-cudaError_t launch_tf32_split(const void* src, int src_dtype, float* hi, float* lo, int64_t n, cudaStream_t s);
+cudaError_t launch_tf32_split(const void* src, int src_dtype, float* hi, float* lo, int64_t n, int64_t k, cudaStream_t s);
 // dst (f16 / bf16) = round-to-nearest-even(src fp32), dense, eight elements per thread step.
 cudaError_t launch_convert16(const float* src, void* dst, int64_t n, int dtype16, cudaStream_t s);
 

@@ -12,8 +12,9 @@
 //              vector stores of the result rows.
 // Loads carry no cluster multicast.  Two operand encodings share the kernel:
 //   * 16-bit (f16 / bf16) operands, fp32 accumulate;
-//   * 3xTF32 for fp32-faithful results: A and B are pre-split into hi = tf32(x) and lo = x - hi;
-//     the K loop runs three passes (lo.hi, hi.lo, hi.hi - small terms first) into one accumulator.
+//   * a split product for fp32-faithful results ("3xTF32" in kernel names): A and B are pre-split into hi = tf32(x),
+//     bf16(x) and bf16(x - hi); hi.hi runs on the tf32 path, the two correction products on the bf16 path;
+//     the K loop runs three passes (residual.bf16, bf16.residual, hi.hi - small terms first) into one accumulator.
 // Every wait is bounded by a clock deadline; on expiry the kernel records
 // BG_ERR_DEVICE_TIMEOUT in the status word, lets copies in flight land, frees its tensor memory
 // and returns.
@@ -49,6 +50,9 @@ struct TcParams {
   int round_acc;        // 0: none, BG_F16 + 1 / BG_BF16 + 1: round the accumulator through that dtype first
   int wide;             // activation arithmetic in fp64
   uint32_t idesc;
+  uint32_t idesc16;     // split product: the instruction descriptor of its two bf16 passes
+  int mixed;            // split product: 1 = correction passes on bf16 planes; 0 = on the fp32 residual plane (tf32), for row
+                        // lengths whose bf16 rows would not start on 16-byte boundaries
   int group_m;
   int* status;
   // grouped launch of the CTA-pair kernel: n_prob problems that share A, M, N, K and the epilogue kind and
@@ -58,7 +62,7 @@ struct TcParams {
   const void* biasg[3];
 };
 constexpr int kMaxGroup = 3;
-struct PairBMaps { CUtensorMap m[2 * kMaxGroup]; };   // per problem: B (or its hi plane), then its lo plane
+struct PairBMaps { CUtensorMap m[3 * kMaxGroup]; };   // per problem: B (or its tf32 plane), then its bf16 plane and its bf16 residual plane
 
 // gelu(x) with the op order of the reference graph: 0.5*x*(1 + tanh(c*(x + 0.044715*x*x*x))),
 // tanh(u) = (e^u - e^-u) / (e^u + e^-u)
@@ -241,8 +245,8 @@ __device__ __forceinline__ bool drain_chunks(const TcParams& p, uint64_t* acc_fu
 // double-buffered in tensor memory, so the epilogue of tile t overlaps the MMAs of tile t + 1.
 template <int BN, bool TF32>
 __global__ void __launch_bounds__(kTcThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
-               const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
+               const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2,
                const __grid_constant__ TcParams p) {
   constexpr int kABytes = BM * kStageRowBytes;
   constexpr int kBBytes = BN * kStageRowBytes;
@@ -298,17 +302,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         for (int ch = 0; ch < n_chunks && ok; ++ch) {
           const int kb0 = ch * p.chunk_blocks, kb1 = min(kb0 + p.chunk_blocks, p.num_k_blocks);
           for (int pass = 0; pass < p.passes && ok; ++pass) {
-            // passes of the split product: lo.hi, hi.lo, hi.hi (a single pass uses map 0 of each operand)
-            const CUtensorMap* ma = (p.passes == 3 && pass == 0) ? &tmA1 : &tmA0;
-            const CUtensorMap* mb = (p.passes == 3 && pass == 1) ? &tmB1 : &tmB0;
-            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+            // passes of the split product: residual(A).B and A.residual(B) on bf16 planes (64 k per block), then
+            // tf32(A).tf32(B) (32 k per block); a single pass uses map 0 of each operand
+            const bool p16 = p.passes == 3 && p.mixed && pass < 2;
+            const bool legacy = p.passes == 3 && !p.mixed;      // maps 1 hold the fp32 residual planes
+            const CUtensorMap* ma = p16 ? (pass == 0 ? &tmA2 : &tmA1) : ((legacy && pass == 0) ? &tmA1 : &tmA0);
+            const CUtensorMap* mb = p16 ? (pass == 0 ? &tmB1 : &tmB2) : ((legacy && pass == 1) ? &tmB1 : &tmB0);
+            const int b0 = p16 ? kb0 >> 1 : kb0, b1 = p16 ? (kb1 + 1) >> 1 : kb1, per = p16 ? 64 : p.elems_per_block;
+            for (int kb = b0; kb < b1; ++kb, ++it) {
               const int s = it % kStages;
               const uint32_t ph = (uint32_t)(it / kStages) & 1u;
               if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
               unsigned char* sa = smem + s * kStageBytes;
               mbar_expect_tx(&full_bar[s], kStageBytes);
-              tma_load_2d(ma, sa, &full_bar[s], kb * p.elems_per_block, m0);
-              tma_load_2d(mb, sa + kABytes, &full_bar[s], kb * p.elems_per_block, n0);
+              tma_load_2d(ma, sa, &full_bar[s], kb * per, m0);
+              tma_load_2d(mb, sa + kABytes, &full_bar[s], kb * per, n0);
             }
           }
         }
@@ -326,17 +334,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
           const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN);
           const int kb0 = ch * p.chunk_blocks, kb1 = min(kb0 + p.chunk_blocks, p.num_k_blocks);
           uint32_t accumulate = 0;
-          for (int k = 0; k < (kb1 - kb0) * p.passes; ++k, ++it) {
+          // stages of this chunk: two bf16 passes of ceil(blocks / 2) stages, then the tf32 pass (one pass otherwise)
+          const int n16 = (p.passes == 3 && p.mixed) ? ((kb1 + 1) >> 1) - (kb0 >> 1) : 0;
+          const int n_stage = p.passes == 3 ? (p.mixed ? 2 * n16 + (kb1 - kb0) : 3 * (kb1 - kb0)) : kb1 - kb0;
+          for (int k = 0; k < n_stage; ++k, ++it) {
             const int s = it % kStages;
             const uint32_t ph = (uint32_t)(it / kStages) & 1u;
             if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t sa = smem_u32(smem + s * kStageBytes);
             const uint64_t da = make_kmajor_sw128_desc(sa), db = make_kmajor_sw128_desc(sa + kABytes);
+            const bool tf32 = TF32 && k >= 2 * n16;
 #pragma unroll
             for (int kk = 0; kk < kStageRowBytes / 32; ++kk) {
               // each instruction consumes 32 bytes of K; the start address advances inside the swizzle row
-              umma<TF32>(tmem_acc, da + (uint64_t)(kk * 32 >> 4), db + (uint64_t)(kk * 32 >> 4), p.idesc, accumulate);
+              if (TF32) umma_sel(tmem_acc, da + (uint64_t)(kk * 32 >> 4), db + (uint64_t)(kk * 32 >> 4), tf32 ? p.idesc : p.idesc16, accumulate, tf32);
+              else umma<false>(tmem_acc, da + (uint64_t)(kk * 32 >> 4), db + (uint64_t)(kk * 32 >> 4), p.idesc, accumulate);
               accumulate = 1;
             }
             umma_commit(&empty_bar[s]);
@@ -423,7 +436,7 @@ constexpr int kPairStages = 6;
 
 template <bool TF32, int TN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
                     const __grid_constant__ PairBMaps tmB, const __grid_constant__ TcParams p) {
   constexpr int kHalf = 128;                           // rows of A each CTA stages
   constexpr int kBHalf = TN / 2;                       // rows of B each CTA stages
@@ -486,17 +499,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         for (int ch = 0; ch < n_chunks && ok; ++ch) {
           const int kb0 = ch * p.chunk_blocks, kb1 = min(kb0 + p.chunk_blocks, p.num_k_blocks);
           for (int pass = 0; pass < p.passes && ok; ++pass) {
-            const CUtensorMap* ma = (p.passes == 3 && pass == 0) ? &tmA1 : &tmA0;
-            const CUtensorMap* mb = &tmB.m[2 * prob + ((p.passes == 3 && pass == 1) ? 1 : 0)];
-            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+            // residual(A).B and A.residual(B) on bf16 planes (64 k per block), then tf32(A).tf32(B) (32 k per block)
+            const bool p16 = p.passes == 3 && p.mixed && pass < 2;
+            const bool legacy = p.passes == 3 && !p.mixed;      // maps 1 hold the fp32 residual planes
+            const CUtensorMap* ma = p16 ? (pass == 0 ? &tmA2 : &tmA1) : ((legacy && pass == 0) ? &tmA1 : &tmA0);
+            const CUtensorMap* mb = &tmB.m[3 * prob + (p16 ? (pass == 0 ? 1 : 2) : ((legacy && pass == 1) ? 1 : 0))];
+            const int b0 = p16 ? kb0 >> 1 : kb0, b1 = p16 ? (kb1 + 1) >> 1 : kb1, per = p16 ? 64 : p.elems_per_block;
+            for (int kb = b0; kb < b1; ++kb, ++it) {
               const int s = it % kPairStages;
               const uint32_t ph = (uint32_t)(it / kPairStages) & 1u;
               if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
               unsigned char* sa = smem + s * kStageBytes;
               const uint32_t full0 = map_to_cta(smem_u32(&full_bar[s]), 0);
               mbar_expect_tx_at(full0, kStageBytes);
-              tma_load_2d_pair(ma, sa, full0, kb * p.elems_per_block, m0 + (int)rank * kHalf);
-              tma_load_2d_pair(mb, sa + kABytes, full0, kb * p.elems_per_block, n0 + (int)rank * kBHalf);
+              tma_load_2d_pair(ma, sa, full0, kb * per, m0 + (int)rank * kHalf);
+              tma_load_2d_pair(mb, sa + kABytes, full0, kb * per, n0 + (int)rank * kBHalf);
             }
           }
         }
@@ -514,16 +531,20 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
           const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * TN);
           const int kb0 = ch * p.chunk_blocks, kb1 = min(kb0 + p.chunk_blocks, p.num_k_blocks);
           uint32_t accumulate = 0;
-          for (int k = 0; k < (kb1 - kb0) * p.passes; ++k, ++it) {
+          const int n16 = (p.passes == 3 && p.mixed) ? ((kb1 + 1) >> 1) - (kb0 >> 1) : 0;
+          const int n_stage = p.passes == 3 ? (p.mixed ? 2 * n16 + (kb1 - kb0) : 3 * (kb1 - kb0)) : kb1 - kb0;
+          for (int k = 0; k < n_stage; ++k, ++it) {
             const int s = it % kPairStages;
             const uint32_t ph = (uint32_t)(it / kPairStages) & 1u;
             if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t sa = smem_u32(smem + s * kStageBytes);
             const uint64_t da = make_kmajor_sw128_desc(sa), db = make_kmajor_sw128_desc(sa + kABytes);
+            const bool tf32 = TF32 && k >= 2 * n16;
 #pragma unroll
             for (int kk = 0; kk < kStageRowBytes / 32; ++kk) {
-              umma_pair<TF32>(tmem_acc, da + (uint64_t)(kk * 32 >> 4), db + (uint64_t)(kk * 32 >> 4), p.idesc, accumulate);
+              if (TF32) umma_pair_sel(tmem_acc, da + (uint64_t)(kk * 32 >> 4), db + (uint64_t)(kk * 32 >> 4), tf32 ? p.idesc : p.idesc16, accumulate, tf32);
+              else umma_pair<false>(tmem_acc, da + (uint64_t)(kk * 32 >> 4), db + (uint64_t)(kk * 32 >> 4), p.idesc, accumulate);
               accumulate = 1;
             }
             const uint32_t e = smem_u32(&empty_bar[s]);
@@ -601,7 +622,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
   }
 }
 
-__global__ void tf32_split_kernel(const void* src, int src_dtype, float* hi, float* lo, int64_t n) {
+// Rows of k elements can travel as bf16 planes when they start on 16-byte boundaries.
+__host__ __device__ inline bool split_is_mixed(int64_t k) { return (k * 2) % 16 == 0; }
+
+// The fp32 residual plane (lo = x - tf32(x)) for row lengths that cannot use bf16 planes: three tf32 passes.
+__global__ void tf32_split_legacy_kernel(const void* src, int src_dtype, float* hi, float* lo, int64_t n) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     float x;
     double xd = 0.0;
@@ -611,8 +636,50 @@ __global__ void tf32_split_kernel(const void* src, int src_dtype, float* hi, flo
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
     const float fh = __uint_as_float(h);
     hi[i] = fh;
-    // the residual is exact in fp32; for fp64 sources it also carries the bits fp32 dropped
     lo[i] = src_dtype == BG_F64 ? (float)(xd - (double)fh) : __fadd_rn(x, -fh);
+  }
+}
+
+// Planes of an operand of the split product, n elements each: hi = tf32(x) as fp32, then (in the 16-bit area)
+// bf16(x) and bf16(x - hi).  x.y is computed as hi_x.hi_y on the tf32 path plus residual(x).bf16(y) and
+// bf16(x).residual(y) on the bf16 path: the residual is below 2^-11 |x|, so the 2^-9 relative rounding of the bf16
+// factors leaves about 2^-20 |x.y| per product -- the error level of an fp32 accumulation -- at two thirds of the
+// tensor-pipe time of three tf32 passes (a bf16 instruction covers twice the k of a tf32 one).
+__global__ void tf32_split_kernel(const void* src, int src_dtype, float* hi, __nv_bfloat16* x16, __nv_bfloat16* lo16, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float x;
+    double xd = 0.0;
+    if (src_dtype == BG_F64) { xd = reinterpret_cast<const double*>(src)[i]; x = (float)xd; }
+    else x = reinterpret_cast<const float*>(src)[i];
+    uint32_t h;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+    const float fh = __uint_as_float(h);
+    hi[i] = fh;
+    x16[i] = __float2bfloat16_rn(x);
+    // the residual is exact in fp32; for fp64 sources it also carries the bits fp32 dropped
+    lo16[i] = __float2bfloat16_rn(src_dtype == BG_F64 ? (float)(xd - (double)fh) : __fadd_rn(x, -fh));
+  }
+}
+
+// The same for a dense fp32 source whose length is a multiple of 4: 16-byte loads and stores.
+__global__ void tf32_split4_kernel(const float4* __restrict__ src, float4* __restrict__ hi, uint2* __restrict__ x16, uint2* __restrict__ lo16,
+                                   int64_t n4) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    const float4 x = __ldcs(src + i);
+    const float xs[4] = {x.x, x.y, x.z, x.w};
+    float hs[4], ls[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      uint32_t h;
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(xs[e]));
+      hs[e] = __uint_as_float(h);
+      ls[e] = __fadd_rn(xs[e], -hs[e]);
+    }
+    hi[i] = make_float4(hs[0], hs[1], hs[2], hs[3]);
+    __nv_bfloat162 a0 = __floats2bfloat162_rn(xs[0], xs[1]), a1 = __floats2bfloat162_rn(xs[2], xs[3]);
+    __nv_bfloat162 l0 = __floats2bfloat162_rn(ls[0], ls[1]), l1 = __floats2bfloat162_rn(ls[2], ls[3]);
+    x16[i] = make_uint2(*reinterpret_cast<uint32_t*>(&a0), *reinterpret_cast<uint32_t*>(&a1));
+    lo16[i] = make_uint2(*reinterpret_cast<uint32_t*>(&l0), *reinterpret_cast<uint32_t*>(&l1));
   }
 }
 
@@ -680,12 +747,21 @@ bool make_operand_map(CUtensorMap* map, const void* ptr, int dtype, int64_t rows
 
 template <int BN, bool TF32>
 cudaError_t launch_variant(const TcGemm& g, int* status, cudaStream_t s) {
-  CUtensorMap a0, a1, b0, b1;
+  CUtensorMap a0, a1, a2, b0, b1, b2;
   if (!make_operand_map(&a0, g.A, g.ab_dtype, g.M, g.K, BM)) return cudaErrorInvalidValue;
   if (!make_operand_map(&b0, g.B, g.ab_dtype, g.N, g.K, BN)) return cudaErrorInvalidValue;
-  a1 = a0;
-  b1 = b0;
-  if (TF32) {
+  a1 = a2 = a0;
+  b1 = b2 = b0;
+  const bool mixed = TF32 && split_is_mixed(g.K);
+  if (mixed) {
+    // the 16-bit area of a split operand: the bf16 plane, then the bf16 residual plane
+    const char* a16 = reinterpret_cast<const char*>(g.A_lo);
+    const char* b16 = reinterpret_cast<const char*>(g.B_lo);
+    if (!make_operand_map(&a1, a16, BG_BF16, g.M, g.K, BM)) return cudaErrorInvalidValue;
+    if (!make_operand_map(&a2, a16 + g.M * g.K * 2, BG_BF16, g.M, g.K, BM)) return cudaErrorInvalidValue;
+    if (!make_operand_map(&b1, b16, BG_BF16, g.N, g.K, BN)) return cudaErrorInvalidValue;
+    if (!make_operand_map(&b2, b16 + g.N * g.K * 2, BG_BF16, g.N, g.K, BN)) return cudaErrorInvalidValue;
+  } else if (TF32) {
     if (!make_operand_map(&a1, g.A_lo, g.ab_dtype, g.M, g.K, BM)) return cudaErrorInvalidValue;
     if (!make_operand_map(&b1, g.B_lo, g.ab_dtype, g.N, g.K, BN)) return cudaErrorInvalidValue;
   }
@@ -708,6 +784,8 @@ cudaError_t launch_variant(const TcGemm& g, int* status, cudaStream_t s) {
   p.group_m = 8;
   const uint32_t fmt = TF32 ? 2u : (g.ab_dtype == BG_BF16 ? 1u : 0u);
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  p.idesc16 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  p.mixed = mixed ? 1 : 0;
   constexpr int kStages = (BN == 256) ? 4 : 6;
   const size_t smem = (size_t)kStages * (BM + BN) * kStageRowBytes + 256 + 1024;
   auto kern = gemm_tc_kernel<BN, TF32>;
@@ -718,7 +796,7 @@ cudaError_t launch_variant(const TcGemm& g, int* status, cudaStream_t s) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int64_t grid = tiles < sms ? tiles : sms;
-  kern<<<(unsigned)grid, kTcThreads, smem, s>>>(a0, a1, b0, b1, p);
+  kern<<<(unsigned)grid, kTcThreads, smem, s>>>(a0, a1, a2, b0, b1, b2, p);
   return cudaGetLastError();
 }
 
@@ -726,16 +804,29 @@ template <bool TF32, int TN>
 cudaError_t launch_pair(const TcGemm* gs, int n_prob, int* status, cudaStream_t s, bool* launched) {
   *launched = false;
   const TcGemm& g = gs[0];
-  CUtensorMap a0, a1;
+  CUtensorMap a0, a1, a2;
   PairBMaps bm;
   if (!make_operand_map(&a0, g.A, g.ab_dtype, g.M, g.K, 128)) return cudaErrorInvalidValue;
-  a1 = a0;
-  if (TF32 && !make_operand_map(&a1, g.A_lo, g.ab_dtype, g.M, g.K, 128)) return cudaErrorInvalidValue;
+  a1 = a2 = a0;
+  const bool mixed = TF32 && split_is_mixed(g.K);
+  if (mixed) {
+    const char* a16 = reinterpret_cast<const char*>(g.A_lo);     // bf16 plane, then bf16 residual plane
+    if (!make_operand_map(&a1, a16, BG_BF16, g.M, g.K, 128)) return cudaErrorInvalidValue;
+    if (!make_operand_map(&a2, a16 + g.M * g.K * 2, BG_BF16, g.M, g.K, 128)) return cudaErrorInvalidValue;
+  } else if (TF32) {
+    if (!make_operand_map(&a1, g.A_lo, g.ab_dtype, g.M, g.K, 128)) return cudaErrorInvalidValue;
+  }
   for (int i = 0; i < kMaxGroup; ++i) {
     const TcGemm& gi = gs[i < n_prob ? i : 0];
-    if (!make_operand_map(&bm.m[2 * i], gi.B, gi.ab_dtype, gi.N, gi.K, TN / 2)) return cudaErrorInvalidValue;
-    bm.m[2 * i + 1] = bm.m[2 * i];
-    if (TF32 && !make_operand_map(&bm.m[2 * i + 1], gi.B_lo, gi.ab_dtype, gi.N, gi.K, TN / 2)) return cudaErrorInvalidValue;
+    if (!make_operand_map(&bm.m[3 * i], gi.B, gi.ab_dtype, gi.N, gi.K, TN / 2)) return cudaErrorInvalidValue;
+    bm.m[3 * i + 1] = bm.m[3 * i + 2] = bm.m[3 * i];
+    if (mixed) {
+      const char* b16 = reinterpret_cast<const char*>(gi.B_lo);
+      if (!make_operand_map(&bm.m[3 * i + 1], b16, BG_BF16, gi.N, gi.K, TN / 2)) return cudaErrorInvalidValue;
+      if (!make_operand_map(&bm.m[3 * i + 2], b16 + gi.N * gi.K * 2, BG_BF16, gi.N, gi.K, TN / 2)) return cudaErrorInvalidValue;
+    } else if (TF32) {
+      if (!make_operand_map(&bm.m[3 * i + 1], gi.B_lo, gi.ab_dtype, gi.N, gi.K, TN / 2)) return cudaErrorInvalidValue;
+    }
   }
   TcParams p{};
   p.M = (int)g.M;
@@ -758,6 +849,8 @@ cudaError_t launch_pair(const TcGemm* gs, int n_prob, int* status, cudaStream_t 
   for (int i = 0; i < kMaxGroup; ++i) { p.Cg[i] = gs[i < n_prob ? i : 0].C; p.biasg[i] = gs[i < n_prob ? i : 0].bias; }
   const uint32_t fmt = TF32 ? 2u : (g.ab_dtype == BG_BF16 ? 1u : 0u);
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+  p.idesc16 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+  p.mixed = mixed ? 1 : 0;
   const size_t smem = (size_t)kPairStages * (128 + TN / 2) * kStageRowBytes + 256 + 1024;
   auto kern = gemm_tc_pair_kernel<TF32, TN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -783,7 +876,7 @@ cudaError_t launch_pair(const TcGemm* gs, int n_prob, int* status, cudaStream_t 
   if (max_pairs <= 0) return cudaSuccess;   // not launched: the caller falls back to single CTAs
   const int64_t tiles = ((g.M + 255) / 256) * ((g.N + TN - 1) / TN) * n_prob;
   const int64_t pairs = tiles < max_pairs ? tiles : max_pairs;
-  kern<<<(unsigned)(2 * pairs), kTcThreads, smem, s>>>(a0, a1, bm, p);
+  kern<<<(unsigned)(2 * pairs), kTcThreads, smem, s>>>(a0, a1, a2, bm, p);
   *launched = true;
   return cudaGetLastError();
 }
@@ -887,11 +980,30 @@ cudaError_t launch_convert16(const float* src, void* dst, int64_t n, int dtype16
   return cudaGetLastError();
 }
 
-cudaError_t launch_tf32_split(const void* src, int src_dtype, float* hi, float* lo, int64_t n, cudaStream_t s) {
+// `lo` (n fp32 slots) receives, for rows of k elements that can travel as bf16, the bf16 plane and then the bf16 residual
+// plane; otherwise the fp32 residual plane.
+cudaError_t launch_tf32_split(const void* src, int src_dtype, float* hi, float* lo, int64_t n, int64_t k, cudaStream_t s) {
   if (n == 0) return cudaSuccess;
+  if (!split_is_mixed(k)) {
+    int64_t grid = (n + 255) / 256;
+    if (grid > 148 * 16) grid = 148 * 16;
+    tf32_split_legacy_kernel<<<(unsigned)grid, 256, 0, s>>>(src, src_dtype, hi, lo, n);
+    return cudaGetLastError();
+  }
+  __nv_bfloat16* x16 = reinterpret_cast<__nv_bfloat16*>(lo);
+  __nv_bfloat16* lo16 = x16 + n;
+  const bool vec = src_dtype == BG_F32 && n % 4 == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(hi)) & 15) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(x16) | reinterpret_cast<uintptr_t>(lo16)) & 7) == 0;
+  if (vec) {
+    int64_t grid = (n / 4 + 255) / 256;
+    if (grid > 148 * 16) grid = 148 * 16;
+    tf32_split4_kernel<<<(unsigned)grid, 256, 0, s>>>(reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(hi),
+                                                      reinterpret_cast<uint2*>(x16), reinterpret_cast<uint2*>(lo16), n / 4);
+    return cudaGetLastError();
+  }
   int64_t grid = (n + 255) / 256;
   if (grid > 148 * 16) grid = 148 * 16;
-  tf32_split_kernel<<<(unsigned)grid, 256, 0, s>>>(src, src_dtype, hi, lo, n);
+  tf32_split_kernel<<<(unsigned)grid, 256, 0, s>>>(src, src_dtype, hi, x16, lo16, n);
   return cudaGetLastError();
 }
 

@@ -2601,7 +2601,7 @@ void Compiler::emit_matmul(int n, int key) {
         g.ab_dtype = ab;
         void* tmp_planes = nullptr;     // hi / lo planes of a B operand that is neither a slot nor kept with a handle
         if (mode == 1) {
-          if (!a_shared) e = launch_tf32_split(pa, a_dt, (float*)r.ptr[a_hi], (float*)r.ptr[a_lo], M * K, st);
+          if (!a_shared) e = launch_tf32_split(pa, a_dt, (float*)r.ptr[a_hi], (float*)r.ptr[a_lo], M * K, K, st);
           float* bh = b_leaf ? nullptr : (float*)r.ptr[b_hi];
           float* bl = b_leaf ? nullptr : (float*)r.ptr[b_lo];
           bool split_b = true;
@@ -2614,7 +2614,7 @@ void Compiler::emit_matmul(int n, int key) {
               bh = reinterpret_cast<float*>(tmp_planes); bl = bh + N * K;
             }
           }
-          if (e == cudaSuccess && split_b) e = launch_tf32_split(pb, b_dt, bh, bl, N * K, st);
+          if (e == cudaSuccess && split_b) e = launch_tf32_split(pb, b_dt, bh, bl, N * K, K, st);
           if (e != cudaSuccess) { if (tmp_planes) dev_free(r.ctx, tmp_planes, 2 * N * K * 4); return cuda_fail(r.ctx, e, "tf32 split launch"); }
           g.A = r.ptr[a_hi]; g.A_lo = r.ptr[a_lo]; g.B = bh; g.B_lo = bl;
         } else {

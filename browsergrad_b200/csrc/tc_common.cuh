@@ -243,6 +243,15 @@ __device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t da, uint64_t
         : "memory");
   }
 }
+// The instruction kind chosen at run time (the passes of a split product differ in it).
+__device__ __forceinline__ void umma_sel(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate, bool tf32) {
+  if (tf32) umma<true>(tmem_d, da, db, idesc, accumulate);
+  else umma<false>(tmem_d, da, db, idesc, accumulate);
+}
+__device__ __forceinline__ void umma_pair_sel(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate, bool tf32) {
+  if (tf32) umma_pair<true>(tmem_d, da, db, idesc, accumulate);
+  else umma_pair<false>(tmem_d, da, db, idesc, accumulate);
+}
 // Arrives on one barrier (given by its shared::cluster address) once every MMA issued so far has completed.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
