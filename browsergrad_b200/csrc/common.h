@@ -287,7 +287,7 @@ cudaError_t launch_wait_timeout_selftest(long long limit_cycles, int* status, cu
 // hi = tf32(x) (round to nearest), lo = x - hi, for fp32 or fp64 input; optional transpose is not done here.
 cudaError_t launch_tf32_split(const void* src, int src_dtype, float* hi, float* lo, int64_t n, int64_t k, cudaStream_t s);
 // dst (f16 / bf16) = round-to-nearest-even(src fp32), dense, eight elements per thread step.
-cudaError_t launch_convert16(const float* src, void* dst, int64_t n, int dtype16, cudaStream_t s);
+cudaError_t launch_convert16(const void* src, int src_dtype, void* dst, int64_t n, int dtype16, cudaStream_t s);
 
 // Fused attention (attn_tc.cu).  Operands are [B,H,S,D] views with element strides; D = 64.
 struct AttnOperand {

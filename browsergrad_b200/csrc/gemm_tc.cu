@@ -683,10 +683,21 @@ __global__ void tf32_split4_kernel(const float4* __restrict__ src, float4* __res
   }
 }
 
-__global__ void convert16_kernel(const float* __restrict__ src, void* dst, int64_t n, int bf16) {
+template <typename S>
+__global__ void convert16_kernel(const S* __restrict__ src, void* dst, int64_t n, int bf16) {
   const int64_t n8 = n >> 3;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
-    const float4 a = __ldcs(reinterpret_cast<const float4*>(src) + 2 * i), b = __ldcs(reinterpret_cast<const float4*>(src) + 2 * i + 1);
+    float4 a, b;
+    if (sizeof(S) == 8) {
+      // float64 source: rounded to fp32 first and then to the 16-bit type, as the interpreter's CAST does
+      const double2* q = reinterpret_cast<const double2*>(src) + 4 * i;
+      const double2 d0 = __ldcs(q), d1 = __ldcs(q + 1), d2 = __ldcs(q + 2), d3 = __ldcs(q + 3);
+      a = make_float4((float)d0.x, (float)d0.y, (float)d1.x, (float)d1.y);
+      b = make_float4((float)d2.x, (float)d2.y, (float)d3.x, (float)d3.y);
+    } else {
+      a = __ldcs(reinterpret_cast<const float4*>(src) + 2 * i);
+      b = __ldcs(reinterpret_cast<const float4*>(src) + 2 * i + 1);
+    }
     uint32_t w[4];
     if (bf16) {
       __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
@@ -704,8 +715,8 @@ __global__ void convert16_kernel(const float* __restrict__ src, void* dst, int64
   // ragged end
   if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
     const int64_t i = (n8 << 3) + threadIdx.x;
-    if (bf16) reinterpret_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn(src[i]);
-    else reinterpret_cast<__half*>(dst)[i] = __float2half_rn(src[i]);
+    if (bf16) reinterpret_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn((float)src[i]);
+    else reinterpret_cast<__half*>(dst)[i] = __float2half_rn((float)src[i]);
   }
 }
 
@@ -968,7 +979,7 @@ cudaError_t launch_gemm_tc(const TcGemm& g, int* status, cudaStream_t s) {
   return wide_tile ? launch_variant<256, false>(g, status, s) : launch_variant<128, false>(g, status, s);
 }
 
-cudaError_t launch_convert16(const float* src, void* dst, int64_t n, int dtype16, cudaStream_t s) {
+cudaError_t launch_convert16(const void* src, int src_dtype, void* dst, int64_t n, int dtype16, cudaStream_t s) {
   if (n == 0) return cudaSuccess;
   // vector path needs 32-byte aligned source and 16-byte aligned destination; slots and handles are 256-byte aligned,
   // view offsets inside them need not be
@@ -976,7 +987,10 @@ cudaError_t launch_convert16(const float* src, void* dst, int64_t n, int dtype16
   int64_t grid = (n / 8 + 255) / 256;
   if (grid > 148 * 16) grid = 148 * 16;
   if (grid < 1) grid = 1;
-  convert16_kernel<<<(unsigned)grid, 256, 0, s>>>(src, dst, n, dtype16 == BG_BF16 ? 1 : 0);
+  if (src_dtype == BG_F64)
+    convert16_kernel<double><<<(unsigned)grid, 256, 0, s>>>(reinterpret_cast<const double*>(src), dst, n, dtype16 == BG_BF16 ? 1 : 0);
+  else
+    convert16_kernel<float><<<(unsigned)grid, 256, 0, s>>>(reinterpret_cast<const float*>(src), dst, n, dtype16 == BG_BF16 ? 1 : 0);
   return cudaGetLastError();
 }
 

@@ -5,7 +5,8 @@
 //   out[r, :] = (f32(h) - mean) / sqrt(var + eps) * w + b
 //
 // h is optionally stored (it is the residual stream the next block adds to).  The terms are fp32 or
-// fp64 and are added in the sum type T, left to right, exactly as the generic interpreter does;
+// fp64 -- in an fp32 sum also f16 / bf16, widened exactly (the 16-bit output of an autocast Linear) -- and are
+// added in the sum type T, left to right, exactly as the generic interpreter does;
 // the statistics are fp32 over f32(h), the reference's rule for LAYER_NORM
 // (packages/browsergrad-jit/src/python/_realize.py:1384-1402 casts the row to float32 first).
 //
@@ -13,6 +14,9 @@
 // and written once, the two reductions are shuffles, and no block-wide barrier is needed.  All
 // loads of one term's row share are independent, so many are in flight per lane.
 #include "common.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 namespace bg {
 namespace {
@@ -28,6 +32,14 @@ __device__ __forceinline__ Vec4<T> load4(const void* base, int dtype, int64_t el
     const double2 a = __ldg(reinterpret_cast<const double2*>(reinterpret_cast<const double*>(base) + elem));
     const double2 b = __ldg(reinterpret_cast<const double2*>(reinterpret_cast<const double*>(base) + elem) + 1);
     r.v[0] = (T)a.x; r.v[1] = (T)a.y; r.v[2] = (T)b.x; r.v[3] = (T)b.y;
+  } else if (dtype == BG_F16) {
+    const uint2 a = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(base) + elem));
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&a.x)), hi = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
+    r.v[0] = (T)lo.x; r.v[1] = (T)lo.y; r.v[2] = (T)hi.x; r.v[3] = (T)hi.y;
+  } else if (dtype == BG_BF16) {
+    const uint2 a = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(base) + elem));
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x)), hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+    r.v[0] = (T)lo.x; r.v[1] = (T)lo.y; r.v[2] = (T)hi.x; r.v[3] = (T)hi.y;
   } else {
     const float4 a = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + elem));
     r.v[0] = (T)a.x; r.v[1] = (T)a.y; r.v[2] = (T)a.z; r.v[3] = (T)a.w;

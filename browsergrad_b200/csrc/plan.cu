@@ -104,6 +104,8 @@ struct CompiledPlan {
   int root_rank = 0;
   int64_t root_shape[kMaxRank] = {0};
   int64_t root_bytes = 0;
+  // the bytes the plan was compiled from: a cache hit is a hit only when they are equal, not merely their hash
+  std::vector<unsigned char> key_bytes;
   // The device status word: `uses_status` marks kernels that can refuse their data (an index outside its axis),
   // `uses_wait_status` kernels whose bounded device waits can give up (tensor-core pipelines).  A plan that returns
   // its root to the host synchronises anyway and examines the word before it hands anything back, so the refusal is
@@ -257,7 +259,7 @@ class Compiler {
   std::map<int, EpiPlan> epi_plan_;       // MATMUL node -> folded epilogue
   // MATMUL node -> fp32 nodes behind absorbed fp32 -> 16-bit CASTs of its A / B operand (-1: operand used as is)
   std::map<int, std::pair<int, int>> gemm_cast_src_;
-  int absorbable_cast(int node, int dtype16, int& cast_node);
+  int absorbable_cast(int node, int dtype16, int& cast_node, bool allow_f64 = false);
   void plan_gemm_casts();
   // Tensor-core GEMMs of one plan that read the same A and differ only in their leaf B / bias (the q / k / v
   // projections of one activation) run as one launch: every member prepares its operands in a unit of its own,
@@ -478,9 +480,17 @@ void Compiler::simplify() {
       n = f;
     }
   }
+  // A CAST to the dtype its input already has changes nothing: it becomes a view (the AMP pass narrows the 16-bit
+  // output of an attention block once more in front of the next Linear).
+  for (int i = 0; i < nn; ++i) {
+    Node& c = nodes_[i];
+    if (c.op == BG_OP_CAST && c.in.size() == 1 && nodes_[c.in[0]].dtype == c.dtype && nodes_[c.in[0]].rank == c.rank) c.op = BG_OP_RESHAPE;
+  }
   // CAST(PERMUTE(x)) -> PERMUTE(CAST(x)): the conversion then reads x densely and the permutation stays
-  // a view (the AMP pass casts the transposed weight of every Linear, _amp.py:215-226).
-  {
+  // a view (the AMP pass casts the transposed weight of every Linear, _amp.py:215-226).  Repeated until nothing
+  // moves, so a cast sinks below a chain of permutations (the transposed keys of an attention block).
+  for (bool moved = true; moved;) {
+    moved = false;
     std::vector<int> n_uses(nn, 0);
     for (int i = 0; i < nn; ++i)
       for (int in : nodes_[i].in) n_uses[in]++;
@@ -501,6 +511,34 @@ void Compiler::simplify() {
       perm.step = c.step;
       nodes_[pi] = cast;
       nodes_[i] = perm;
+      moved = true;
+    }
+  }
+  // CAST to a 16-bit type of (views of) a CAST from that same type: both casts are exact inverses on these values
+  // (the AMP pass widens an attention output to fp32 and narrows it again in front of the next Linear,
+  // _amp.py:183-261).  Both become views, so the 16-bit tensor is read in place.
+  {
+    std::vector<int> n_uses(nn, 0);
+    for (int i = 0; i < nn; ++i)
+      for (int in : nodes_[i].in) n_uses[in]++;
+    for (int i = 0; i < nn; ++i) {
+      Node& c = nodes_[i];
+      if (c.op != BG_OP_CAST || c.in.size() != 1 || (c.dtype != BG_F16 && c.dtype != BG_BF16)) continue;
+      std::vector<int> chain;
+      int v = c.in[0];
+      while ((nodes_[v].op == BG_OP_PERMUTE || nodes_[v].op == BG_OP_RESHAPE) && nodes_[v].in.size() == 1 && n_uses[v] == 1 && v != root_) {
+        chain.push_back(v);
+        v = nodes_[v].in[0];
+      }
+      Node& w = nodes_[v];
+      if (w.op != BG_OP_CAST || w.in.size() != 1 || n_uses[v] != 1 || v == root_) continue;
+      if ((w.dtype != BG_F32 && w.dtype != BG_F64) || nodes_[w.in[0]].dtype != c.dtype) continue;
+      const int rank_w = w.rank;
+      w.op = BG_OP_RESHAPE;          // same shape: a view of its 16-bit input
+      w.dtype = c.dtype;
+      (void)rank_w;
+      for (int u : chain) nodes_[u].dtype = c.dtype;
+      c.op = BG_OP_RESHAPE;
     }
   }
   auto compute_live = [&]() {
@@ -1536,8 +1574,13 @@ static bool match_static_ln(ProgramSpec& ps) {
   };
   if (!float_vec(P.tail_w) || !float_vec(P.tail_b)) return false;
   // 1 = dense rows, 2 = one vector for every row, 0 = neither
+  auto half_vec = [&](int k) {
+    const EwOperand& o = P.inputs[k];
+    return (o.dtype == BG_F16 || o.dtype == BG_BF16) && ps.in_off_bytes[k] % 8 == 0;
+  };
   auto term_kind = [&](int k) -> int {
     const EwOperand& o = P.inputs[k];
+    if (!wide && half_vec(k)) return o.mode == A_CONTIG ? 1 : 0;     // a dense 16-bit term of an fp32 sum, widened exactly
     if (!float_vec(k) || (!wide && o.dtype != BG_F32)) return 0;
     if (o.mode == A_CONTIG) return 1;
     if (o.mode == A_STRIDED && P.ndim == 2 && P.shape[1] == P.cols && o.stride[0] == 0 && o.stride[1] == 1) return 2;
@@ -1590,7 +1633,7 @@ static bool match_static_ln(ProgramSpec& ps) {
   if (it == reg.end()) return false;
   if ((sum_out >= 0) != (P.n_outputs == 2) || sum_out == P.tail_out) return false;
   const std::vector<int>& terms = it->second;
-  // a lone fp32 operand feeding an fp64 row, or mixed widths in an fp32 sum, stay on the interpreter
+  // a lone operand of another width than the row's stays on the interpreter
   if (terms.size() == 1 && P.inputs[terms[0]].dtype != sum_dtype) return false;
   for (size_t k = 0; k < terms.size(); ++k) {
     const int kind = term_kind(terms[k]);
@@ -1884,7 +1927,7 @@ std::string Compiler::act_expr(int node, int x, int g, int depth) {
 // whole group is [CAST to fp32] -> [+ bias row] -> [relu | gelu] of that product.
 // The fp32 node whose CAST to `dtype16` is all that stands between it and `node` (through views only), when that
 // cast exists for this one consumer chain, is an elementwise group of its own and reads a dense fp32 tensor; -1 else.
-int Compiler::absorbable_cast(int node, int dtype16, int& cast_node) {
+int Compiler::absorbable_cast(int node, int dtype16, int& cast_node, bool allow_f64) {
   auto single = [&](int v) {
     std::set<int> c(cons_[v].begin(), cons_[v].end());
     return c.size() == 1 && v != root_;
@@ -1900,7 +1943,9 @@ int Compiler::absorbable_cast(int node, int dtype16, int& cast_node) {
     if (i != pnode && kind_[i] == K_EW && find(i) == g) return -1;    // fused with other elementwise work
   const int src = resolve(nodes_[pnode].in[0]);
   const View& sv = view_[src];
-  if (sv.is_const || sv.slot < 0 || sv.dtype != BG_F32 || !sv.contiguous() || sv.rank != nodes_[pnode].rank) return -1;
+  if (sv.is_const || sv.slot < 0 || !(sv.dtype == BG_F32 || (allow_f64 && sv.dtype == BG_F64)) || !sv.contiguous() ||
+      sv.rank != nodes_[pnode].rank)
+    return -1;
   for (int d = 0; d < sv.rank; ++d)
     if (sv.shape[d] != nodes_[pnode].shape[d]) return -1;
   cast_node = pnode;
@@ -1975,7 +2020,8 @@ void Compiler::plan_gemm_casts() {
     const bool a_dense = av.stride[1] == 1 && av.stride[0] == K;
     const bool b_kmajor = bv.stride[0] == 1 && bv.stride[1] == K;
     int ca = -1, cb = -1;
-    int sa = a_dense ? absorbable_cast(a, av.dtype, ca) : -1;
+    // an activation may also be a float64 tensor (LayerNorm outputs of autocast graphs are): the conversion pass reads it
+    int sa = a_dense ? absorbable_cast(a, av.dtype, ca, true) : -1;
     int sb = b_kmajor ? absorbable_cast(b, bv.dtype, cb) : -1;
     if (sa >= 0 && sb >= 0 && ca == cb) sb = -1;
     // the conversion pass moves eight elements per step: the operand must start on a 32-byte boundary of its slot
@@ -2045,10 +2091,17 @@ void Compiler::plan_tc_epilogues(const std::map<int, std::vector<int>>& groups) 
     for (int m : mem)
       if (need_mat_[m]) mats.push_back(m);
     int final_node = -1;
+    bool out16 = false;       // the group ends in the CAST back to the product's 16-bit type: the epilogue stores that type
     if (mats.size() == 1) {
-      if (mats[0] == cur) final_node = cur;
+      int target = mats[0];
+      const Node& mn = nodes_[target];
+      if (!small && ep.round_acc && mn.op == BG_OP_CAST && mn.in.size() == 1 && mn.dtype == nodes_[n].dtype) {
+        const int inner = resolve(mn.in[0]);
+        if (kind_[inner] == K_EW && find(inner) == g && nodes_[inner].dtype == BG_F32) { target = inner; out16 = true; }
+      }
+      if (target == cur) final_node = mats[0];
       else {
-        const std::string e = act_expr(mats[0], cur, g, 0);
+        const std::string e = act_expr(target, cur, g, 0);
         if (e == relu) { ep.act = TC_ACT_RELU; final_node = mats[0]; }
         else if (e == gelu) { ep.act = TC_ACT_GELU; final_node = mats[0]; }
       }
@@ -2080,9 +2133,9 @@ void Compiler::plan_tc_epilogues(const std::map<int, std::vector<int>>& groups) 
       if (!all) continue;
     }
     const int fdt = nodes_[final_node].dtype;
-    if (fdt != BG_F32 && fdt != BG_F64) continue;
+    if (fdt != BG_F32 && fdt != BG_F64 && !out16) continue;
     if (small && (fdt != BG_F32 || ep.act == TC_ACT_GELU)) continue;
-    ep.wide = fdt == BG_F64 && ep.act == TC_ACT_GELU && nodes_[cur].dtype != BG_F64 ? 1 : (fdt == BG_F64 ? 1 : 0);
+    ep.wide = out16 ? 0 : fdt == BG_F64 && ep.act == TC_ACT_GELU && nodes_[cur].dtype != BG_F64 ? 1 : (fdt == BG_F64 ? 1 : 0);
     ep.final_node = final_node;
     ep.group = g;
     epi_plan_[n] = ep;
@@ -2449,7 +2502,8 @@ void Compiler::emit_matmul(int n, int key) {
         // the activation is converted by a unit of its own (its time shows up beside the GEMM's, not inside it)
         const View& sv = view_[a_f32];
         const int f32_slot = sv.slot;
-        const int64_t f32_off = (sv.off + av.off) * 4;
+        const int src_dt = sv.dtype;                         // fp32, or float64
+        const int64_t f32_off = (sv.off + av.off) * dtype_size(src_dt);
         const auto ckey = std::make_tuple(f32_slot, f32_off, M * K, ab);
         auto chit = conv_memo_.find(ckey);
         if (chit != conv_memo_.end()) {
@@ -2469,8 +2523,8 @@ void Compiler::emit_matmul(int n, int key) {
         cu.u.name = std::string("convert16[") + dtype_name(ab) + "]";
         const int conv_slot = a_conv;
         cu.u.fn = [=](Run& r) {
-          cudaError_t e = launch_convert16(reinterpret_cast<const float*>(reinterpret_cast<char*>(r.ptr[f32_slot]) + f32_off),
-                                           r.ptr[conv_slot], M * K, ab, r.ctx->stream);
+          cudaError_t e = launch_convert16(reinterpret_cast<char*>(r.ptr[f32_slot]) + f32_off, src_dt, r.ptr[conv_slot], M * K, ab,
+                                           r.ctx->stream);
           return e == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e, "operand conversion launch");
         };
         pu.dep_punits.push_back((int)punits_.size());
@@ -2633,7 +2687,7 @@ void Compiler::emit_matmul(int n, int key) {
             } else {
               dst = r.ptr[b_conv];
             }
-            if (convert) e = launch_convert16(reinterpret_cast<const float*>(pb), dst, N * K, ab, st);
+            if (convert) e = launch_convert16(pb, BG_F32, dst, N * K, ab, st);
             pb = dst;
           }
           if (e != cudaSuccess) { if (tmp_planes) dev_free(r.ctx, tmp_planes, N * K * 2); return cuda_fail(r.ctx, e, "operand conversion launch"); }
@@ -3312,9 +3366,17 @@ int run_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs, 
   h = fnv1a(plan->steps, sizeof(bg_plan_step) * (size_t)plan->n_steps, h);
   if (plan->n_ext > 0) h = fnv1a(plan->ext, sizeof(int32_t) * (size_t)plan->n_ext, h);
   h = fnv1a(&plan->root_id, sizeof(int32_t), h);
+  const size_t step_bytes = sizeof(bg_plan_step) * (size_t)plan->n_steps;
+  const size_t ext_bytes = plan->n_ext > 0 ? sizeof(int32_t) * (size_t)plan->n_ext : 0;
+  auto same_bytes = [&](const CompiledPlan& c) {
+    if (c.key_bytes.size() != step_bytes + ext_bytes + sizeof(int32_t)) return false;
+    const unsigned char* k = c.key_bytes.data();
+    return memcmp(k, plan->steps, step_bytes) == 0 && (ext_bytes == 0 || memcmp(k + step_bytes, plan->ext, ext_bytes) == 0) &&
+           memcmp(k + step_bytes + ext_bytes, &plan->root_id, sizeof(int32_t)) == 0;
+  };
   std::shared_ptr<CompiledPlan> cp;
   auto it = ctx->plan_cache.find(h);
-  if (it != ctx->plan_cache.end()) {
+  if (it != ctx->plan_cache.end() && same_bytes(*it->second)) {
     cp = it->second;
     ctx->cache_hits++;
   } else {
@@ -3324,8 +3386,12 @@ int run_plan(bg_context* ctx, const bg_plan* plan, const bg_plan_input* inputs, 
     } catch (CompileError& ce) {
       return fail(ctx, ce.code > 0 ? ce.code : BG_ERR_UNSUPPORTED, "run_tensor_plan: " + ce.msg);
     }
+    cp->key_bytes.resize(step_bytes + ext_bytes + sizeof(int32_t));
+    memcpy(cp->key_bytes.data(), plan->steps, step_bytes);
+    if (ext_bytes) memcpy(cp->key_bytes.data() + step_bytes, plan->ext, ext_bytes);
+    memcpy(cp->key_bytes.data() + step_bytes + ext_bytes, &plan->root_id, sizeof(int32_t));
     if (ctx->plan_cache.size() > 256) ctx->plan_cache.clear();
-    ctx->plan_cache[h] = cp;
+    ctx->plan_cache[h] = cp;     // a different plan with the same hash replaces the old entry
     ctx->cache_misses++;
   }
   ctx->last_trace = cp->trace;

@@ -133,14 +133,15 @@ def _unwrap(tensor: Any) -> Tuple[Any, Any]:
     return node, store
 
 
-_PLAN_MEMO: Dict[int, Tuple[Any, Any, Dict[str, Any]]] = {}
+_PLAN_MEMO: Dict[Tuple[int, bool], Tuple[Any, Any, Dict[str, Any]]] = {}
 
 
 def plan_for(node: Any, fusion: bool = True) -> Tuple[Any, Dict[str, Any]]:
     """Prepared root and plan for a graph, memoised on the root object so that repeated
     realizations of one graph skip the passes (the reference memoises whole traces,
     packages/browsergrad-jit/src/python/_trace_cache.py:183-265)."""
-    hit = _PLAN_MEMO.get(id(node))
+    key = (id(node), bool(fusion))
+    hit = _PLAN_MEMO.get(key)
     if hit is not None and hit[0] is node:
         return hit[1], hit[2]
     prepared = passes.lower_composites(passes.prepare(node, fusion=fusion))
@@ -152,7 +153,7 @@ def plan_for(node: Any, fusion: bool = True) -> Tuple[Any, Dict[str, Any]]:
                 "Fall back to bg.realize() (NumPy).")
     if len(_PLAN_MEMO) > 128:
         _PLAN_MEMO.clear()
-    _PLAN_MEMO[id(node)] = (node, prepared, plan)
+    _PLAN_MEMO[key] = (node, prepared, plan)
     return prepared, plan
 
 
