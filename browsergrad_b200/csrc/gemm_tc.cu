@@ -661,19 +661,29 @@ __global__ void tf32_split_kernel(const void* src, int src_dtype, float* hi, __n
   }
 }
 
-// The same for a dense fp32 source whose length is a multiple of 4: 16-byte loads and stores.
-__global__ void tf32_split4_kernel(const float4* __restrict__ src, float4* __restrict__ hi, uint2* __restrict__ x16, uint2* __restrict__ lo16,
+// The same for a dense fp32 or float64 source whose length is a multiple of 4: 16-byte loads and stores.
+template <typename S>
+__global__ void tf32_split4_kernel(const S* __restrict__ src, float4* __restrict__ hi, uint2* __restrict__ x16, uint2* __restrict__ lo16,
                                    int64_t n4) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
-    const float4 x = __ldcs(src + i);
-    const float xs[4] = {x.x, x.y, x.z, x.w};
+    double xd[4];
+    float xs[4];
+    if (sizeof(S) == 8) {
+      const double2 a = __ldcs(reinterpret_cast<const double2*>(src) + 2 * i), b = __ldcs(reinterpret_cast<const double2*>(src) + 2 * i + 1);
+      xd[0] = a.x; xd[1] = a.y; xd[2] = b.x; xd[3] = b.y;
+    } else {
+      const float4 x = __ldcs(reinterpret_cast<const float4*>(src) + i);
+      xd[0] = x.x; xd[1] = x.y; xd[2] = x.z; xd[3] = x.w;
+    }
     float hs[4], ls[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
+      xs[e] = (float)xd[e];
       uint32_t h;
       asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(xs[e]));
       hs[e] = __uint_as_float(h);
-      ls[e] = __fadd_rn(xs[e], -hs[e]);
+      // for float64 sources the residual also carries the bits fp32 dropped
+      ls[e] = sizeof(S) == 8 ? (float)(xd[e] - (double)hs[e]) : __fadd_rn(xs[e], -hs[e]);
     }
     hi[i] = make_float4(hs[0], hs[1], hs[2], hs[3]);
     __nv_bfloat162 a0 = __floats2bfloat162_rn(xs[0], xs[1]), a1 = __floats2bfloat162_rn(xs[2], xs[3]);
@@ -1006,13 +1016,18 @@ cudaError_t launch_tf32_split(const void* src, int src_dtype, float* hi, float* 
   }
   __nv_bfloat16* x16 = reinterpret_cast<__nv_bfloat16*>(lo);
   __nv_bfloat16* lo16 = x16 + n;
-  const bool vec = src_dtype == BG_F32 && n % 4 == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(hi)) & 15) == 0 &&
+  const bool vec = (src_dtype == BG_F32 || src_dtype == BG_F64) && n % 4 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(hi)) & 15) == 0 &&
                    ((reinterpret_cast<uintptr_t>(x16) | reinterpret_cast<uintptr_t>(lo16)) & 7) == 0;
   if (vec) {
     int64_t grid = (n / 4 + 255) / 256;
     if (grid > 148 * 16) grid = 148 * 16;
-    tf32_split4_kernel<<<(unsigned)grid, 256, 0, s>>>(reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(hi),
-                                                      reinterpret_cast<uint2*>(x16), reinterpret_cast<uint2*>(lo16), n / 4);
+    if (src_dtype == BG_F64)
+      tf32_split4_kernel<double><<<(unsigned)grid, 256, 0, s>>>(reinterpret_cast<const double*>(src), reinterpret_cast<float4*>(hi),
+                                                                reinterpret_cast<uint2*>(x16), reinterpret_cast<uint2*>(lo16), n / 4);
+    else
+      tf32_split4_kernel<float><<<(unsigned)grid, 256, 0, s>>>(reinterpret_cast<const float*>(src), reinterpret_cast<float4*>(hi),
+                                                               reinterpret_cast<uint2*>(x16), reinterpret_cast<uint2*>(lo16), n / 4);
     return cudaGetLastError();
   }
   int64_t grid = (n + 255) / 256;
