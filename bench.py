@@ -341,8 +341,10 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn
             # graph asks for); the GEMM unit alone, from the profiled pass, is kept beside it
             tf = 2.0 * n ** 3 / (ms * 1e-3) / 1e12
             tf_kernel = 2.0 * n ** 3 / (k_ms * 1e-3) / 1e12
-            peak = peaks["bf16_tflops"] if amp else peaks["bf16_tflops"] / 2.0 / 3.0
-            nominal = NOMINAL["bf16_tflops"] if amp else NOMINAL["bf16_tflops"] / 2.0 / 3.0
+            # fp32 operands: one product on the tf32 path (half the bf16 rate) plus two correction products on the
+            # bf16 path = four bf16-product times per result
+            peak = peaks["bf16_tflops"] if amp else peaks["bf16_tflops"] / 4.0
+            nominal = NOMINAL["bf16_tflops"] if amp else NOMINAL["bf16_tflops"] / 4.0
             out["gemm"].append({"workload": f"Linear+bias+GELU M=N=K={n} {'bf16 autocast' if amp else 'fp32 (3xTF32)'}",
                                 "tflops": tf, "plan_ms": ms, "kernel_ms": k_ms, "kernel_tflops": tf_kernel, "kernels": trace,
                                 "timing": "plan_ms: CUDA events around back-to-back plans; kernel_ms: events around the GEMM "
@@ -351,7 +353,8 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn
                                              "frac_of_nominal": tf / nominal, "nominal_peak": nominal, "basis": "plan time",
                                              "kernel_only_frac": tf_kernel / peak, "kernel_only_frac_of_nominal": tf_kernel / nominal,
                                              "peak_note": "measured cuBLAS bf16 burst" if amp else
-                                             "measured bf16 burst / 2 (tf32) / 3 (three products per result)"}})
+                                             "measured bf16 burst / 4 (split product: tf32(x).tf32(y) at half the bf16 rate "
+                                             "plus two bf16 correction products); the three-tf32-pass scheme it replaces had burst / 6"}})
             del arrays, store, t
     b, h, s, d = attn_batch, 12, 2048, 64
     for amp in ("", "bfloat16"):
