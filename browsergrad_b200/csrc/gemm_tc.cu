@@ -64,40 +64,35 @@ struct TcParams {
 constexpr int kMaxGroup = 3;
 struct PairBMaps { CUtensorMap m[3 * kMaxGroup]; };   // per problem: B (or its tf32 plane), then its bf16 plane and its bf16 residual plane
 
-// gelu(x) with the op order of the reference graph: 0.5*x*(1 + tanh(c*(x + 0.044715*x*x*x))),
-// tanh(u) = (e^u - e^-u) / (e^u + e^-u)
-template <typename T>
-__device__ __forceinline__ T gelu_graph(T x) {
-  const T c = (T)0.7978845608028654;
-  T t = (T)0.044715 * x;
-  t = t * x;
-  t = t * x;
-  T u = c * (x + t);
-  if (sizeof(T) == 4) {
-    // fp32 graphs reach this epilogue only through the 16-bit autocast path (tolerance 2e-2):
-    // hardware exp2-based exp and approximate divide, same expression
-    const float ep = __expf((float)u), en = __expf(-(float)u);
-    const float th = __fdividef(ep - en, ep + en);
-    return (T)((0.5f * (float)x) * (1.0f + th));
-  }
-  T ep = (T)exp((double)u);
-  T en = (T)exp((double)-u);
-  T th = (ep + (-en)) / (ep + en);
-  return ((T)0.5 * x) * ((T)1.0 + th);
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_fast(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
-// gelu for results that are stored as fp64: the product is fp32-accurate (3xTF32), so the activation
-// is evaluated in fp32 and widened.  With u = c*(x + 0.044715 x^3), the graph's
-// 0.5*x*(1 + (e^u - e^-u)/(e^u + e^-u)) equals x / (1 + e^(-2u)); this form needs one exponential,
-// has no cancellation for negative x and does not overflow to inf/inf for |u| > 88 (~1e-7 relative).
-__device__ __forceinline__ float gelu_accurate(float x) {
-  const float c2 = 2.0f * 0.7978845608028654f;
-  float t = 0.044715f * x;
-  t = t * x;
-  t = t * x;
-  const float e = expf(-c2 * (x + t));
-  return __fdividef(x, 1.0f + e) ;
+// gelu(x) = 0.5 x (1 + tanh(u)), u = k (x + 0.044715 x^3), of the reference graph, evaluated as x / (1 + e^(-2u)):
+// one exponential on the exp2 unit, no cancellation for negative x.  The graph writes tanh as
+// (e^u - e^-u) / (e^u + e^-u), which is inf / inf = NaN once e^|u| overflows the graph's arithmetic type; `u_max` is
+// that type's largest exponent argument (88.72 for fp32 graphs, 709.78 for float64 tails) and the result is NaN
+// beyond it, as the reference's is.
+__device__ __forceinline__ float gelu_one_exp(float x, float u_max) {
+  const float x2 = x * x;
+  const float u = x * fmaf(0.7978845608028654f * 0.044715f, x2, 0.7978845608028654f);
+  const float e = ex2_fast(u * (-2.0f * 1.4426950408889634f));
+  const float g = x * rcp_fast(1.0f + e);
+  return fabsf(u) > u_max ? __int_as_float(0x7fc00000) : g;
 }
+// fp32 graphs reach the epilogue through the 16-bit autocast path (tolerance 2e-2)
+template <typename T>
+__device__ __forceinline__ T gelu_graph(T x) { return (T)gelu_one_exp((float)x, 88.72f); }
+// results stored as float64: the product is fp32-accurate (split product), so the activation is evaluated in fp32
+// (about 1e-6 relative) and widened
+__device__ __forceinline__ float gelu_accurate(float x) { return gelu_one_exp(x, 709.78f); }
 
 __device__ __forceinline__ float load_bias(const void* b, int dt, int col) {
   switch (dt) {
