@@ -35,6 +35,13 @@ constexpr int BM = 128;
 constexpr int kStageRowBytes = 128;          // one swizzle row: 64 x 16-bit or 32 x tf32
 constexpr int kTf32ChunkBlocks = 16;         // 3xTF32: K blocks (of 32 floats) summed in tensor memory before a register add
 constexpr int kTcThreads = 320;          // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per TMEM lane quarter)
+// The 16-bit kernels run sixteen epilogue warps (four per TMEM lane quarter): with short K loops the epilogue's
+// instruction issue, not the tensor pipe, sets the pace, and their 100 registers per thread leave room for it.  The
+// split-product kernels keep eight (their epilogue warps hold the accumulation chunks in registers).
+template <bool TF32> struct EpiCfg {
+  static constexpr int kWarps = TF32 ? 8 : 16;
+  static constexpr int kThreads = 64 + 32 * kWarps;
+};
 
 struct TcParams {
   int M, N;
@@ -239,7 +246,7 @@ __device__ __forceinline__ bool drain_chunks(const TcParams& p, uint64_t* acc_fu
 // Persistent kernel: each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The accumulator is
 // double-buffered in tensor memory, so the epilogue of tile t overlaps the MMAs of tile t + 1.
 template <int BN, bool TF32>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(EpiCfg<TF32>::kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
                const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2,
                const __grid_constant__ TcParams p) {
@@ -273,7 +280,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], EpiCfg<TF32>::kWarps); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -381,7 +388,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         tc_fence_after();
         const uint32_t tmem_acc = lane_base + (uint32_t)(buf * BN);
 #pragma unroll 1
-        for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
+        for (int c = half; c < BN / 32; c += EpiCfg<TF32>::kWarps / 4) {      // the warps of a lane quarter take the 32-column chunks in turn
           uint32_t r[32];
           if (n_chunks > 0) tmem_ld32(tmem_acc + (uint32_t)(c * 32), r);
           else {
@@ -430,7 +437,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 constexpr int kPairStages = 6;
 
 template <bool TF32, int TN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(EpiCfg<TF32>::kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
                     const __grid_constant__ PairBMaps tmB, const __grid_constant__ TcParams p) {
   constexpr int kHalf = 128;                           // rows of A each CTA stages
@@ -468,7 +475,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) { mbar_init(&full_bar[s], 2); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 16); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 2 * EpiCfg<TF32>::kWarps); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -584,7 +591,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         tc_fence_after();
         const uint32_t tmem_acc = lane_base + (uint32_t)(buf * TN);
 #pragma unroll 1
-        for (int c = half * (TN / 64); c < (half + 1) * (TN / 64); ++c) {
+        for (int c = half; c < TN / 32; c += EpiCfg<TF32>::kWarps / 4) {
           uint32_t r[32];
           if (n_chunks > 0) tmem_ld32(tmem_acc + (uint32_t)(c * 32), r);
           else {
@@ -812,7 +819,7 @@ cudaError_t launch_variant(const TcGemm& g, int* status, cudaStream_t s) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int64_t grid = tiles < sms ? tiles : sms;
-  kern<<<(unsigned)grid, kTcThreads, smem, s>>>(a0, a1, a2, b0, b1, b2, p);
+  kern<<<(unsigned)grid, EpiCfg<TF32>::kThreads, smem, s>>>(a0, a1, a2, b0, b1, b2, p);
   return cudaGetLastError();
 }
 
@@ -876,7 +883,7 @@ cudaError_t launch_pair(const TcGemm* gs, int n_prob, int* status, cudaStream_t 
   if (max_pairs < 0) {
     cudaLaunchConfig_t qc{};
     qc.gridDim = dim3(2, 1, 1);
-    qc.blockDim = dim3(kTcThreads, 1, 1);
+    qc.blockDim = dim3(EpiCfg<TF32>::kThreads, 1, 1);
     qc.dynamicSmemBytes = smem;
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -892,7 +899,7 @@ cudaError_t launch_pair(const TcGemm* gs, int n_prob, int* status, cudaStream_t 
   if (max_pairs <= 0) return cudaSuccess;   // not launched: the caller falls back to single CTAs
   const int64_t tiles = ((g.M + 255) / 256) * ((g.N + TN - 1) / TN) * n_prob;
   const int64_t pairs = tiles < max_pairs ? tiles : max_pairs;
-  kern<<<(unsigned)(2 * pairs), kTcThreads, smem, s>>>(a0, a1, a2, bm, p);
+  kern<<<(unsigned)(2 * pairs), EpiCfg<TF32>::kThreads, smem, s>>>(a0, a1, a2, bm, p);
   *launched = true;
   return cudaGetLastError();
 }
