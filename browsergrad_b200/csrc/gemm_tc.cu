@@ -34,7 +34,6 @@ using namespace tc;
 constexpr int BM = 128;
 constexpr int kStageRowBytes = 128;          // one swizzle row: 64 x 16-bit or 32 x tf32
 constexpr int kTf32ChunkBlocks = 16;         // 3xTF32: K blocks (of 32 floats) summed in tensor memory before a register add
-constexpr int kTcThreads = 320;          // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per TMEM lane quarter)
 // The 16-bit kernels run sixteen epilogue warps (four per TMEM lane quarter): with short K loops the epilogue's
 // instruction issue, not the tensor pipe, sets the pace, and their 100 registers per thread leave room for it.  The
 // split-product kernels keep eight (their epilogue warps hold the accumulation chunks in registers).
@@ -101,6 +100,14 @@ __device__ __forceinline__ T gelu_graph(T x) { return (T)gelu_one_exp((float)x, 
 // (about 1e-6 relative) and widened
 __device__ __forceinline__ float gelu_accurate(float x) { return gelu_one_exp(x, 709.78f); }
 
+// One 32-byte store per lane: an epilogue thread owns a row of the tile, so a 16-byte store fills half a sector per
+// lane; the 256-bit form (sm_100) writes whole sectors with half the instructions.  `p` is 32-byte aligned.
+__device__ __forceinline__ void st_global_256(void* p, const uint32_t (&w)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+               "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+
 __device__ __forceinline__ float load_bias(const void* b, int dt, int col) {
   switch (dt) {
     case BG_F32: return reinterpret_cast<const float*>(b)[col];
@@ -139,6 +146,25 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
   }
   const bool full = col0 + 32 <= p.N;
   const size_t base = (size_t)row * p.N + col0;
+  const bool al32 = (reinterpret_cast<uintptr_t>(C) & 31) == 0;      // 32-byte stores need the tensor to start on a sector
+  if (p.c_dtype == BG_F64 && full && al32 && (p.N & 3) == 0) {
+    double* out = reinterpret_cast<double*>(C) + base;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      uint32_t w[8];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        double x = (double)v[j + t];
+        if (p.act == TC_ACT_RELU) x = x > 0.0 ? x : 0.0;
+        else if (p.act == TC_ACT_GELU) x = (double)gelu_accurate(v[j + t]);
+        const unsigned long long b = (unsigned long long)__double_as_longlong(x);
+        w[2 * t] = (uint32_t)b;
+        w[2 * t + 1] = (uint32_t)(b >> 32);
+      }
+      st_global_256(out + j, w);
+    }
+    return;
+  }
   if (p.c_dtype == BG_F64) {
     double* out = reinterpret_cast<double*>(C) + base;
 #pragma unroll
@@ -168,7 +194,15 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
   }
   if (p.c_dtype == BG_F32) {
     float* out = reinterpret_cast<float*>(C) + base;
-    if (full && (p.N & 3) == 0) {
+    if (full && al32 && (p.N & 7) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint32_t w[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) w[t] = __float_as_uint(v[j + t]);
+        st_global_256(out + j, w);
+      }
+    } else if (full && (p.N & 3) == 0) {
 #pragma unroll
       for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
     } else {
@@ -178,7 +212,18 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
     }
   } else if (p.c_dtype == BG_F16) {
     __half* out = reinterpret_cast<__half*>(C) + base;
-    if (full && (p.N & 7) == 0) {
+    if (full && al32 && (p.N & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 16) {
+        uint32_t w[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          __half2 h = __floats2half2_rn(v[j + 2 * t], v[j + 2 * t + 1]);
+          w[t] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        st_global_256(out + j, w);
+      }
+    } else if (full && (p.N & 7) == 0) {
 #pragma unroll
       for (int j = 0; j < 32; j += 8) {
         __half2 h[4];
@@ -193,7 +238,18 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
     }
   } else {
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(C) + base;
-    if (full && (p.N & 7) == 0) {
+    if (full && al32 && (p.N & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 16) {
+        uint32_t w[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(v[j + 2 * t], v[j + 2 * t + 1]);
+          w[t] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        st_global_256(out + j, w);
+      }
+    } else if (full && (p.N & 7) == 0) {
 #pragma unroll
       for (int j = 0; j < 32; j += 8) {
         __nv_bfloat162 h[4];
