@@ -34,11 +34,12 @@ using namespace tc;
 constexpr int BM = 128;
 constexpr int kStageRowBytes = 128;          // one swizzle row: 64 x 16-bit or 32 x tf32
 constexpr int kTf32ChunkBlocks = 16;         // 3xTF32: K blocks (of 32 floats) summed in tensor memory before a register add
-// The 16-bit kernels run sixteen epilogue warps (four per TMEM lane quarter): with short K loops the epilogue's
-// instruction issue, not the tensor pipe, sets the pace, and their 100 registers per thread leave room for it.  The
-// split-product kernels keep eight (their epilogue warps hold the accumulation chunks in registers).
+// Sixteen epilogue warps in the 16-bit kernels, twelve in the split-product kernels (four / three per TMEM lane
+// quarter, taking the 32-column chunks of a tile in turn): with short K loops the epilogue's instruction issue, not
+// the tensor pipe, sets the pace.  A split-product warp holds up to three chunks of partial sums in registers, which
+// is what limits its count.
 template <bool TF32> struct EpiCfg {
-  static constexpr int kWarps = TF32 ? 8 : 16;
+  static constexpr int kWarps = TF32 ? 12 : 16;
   static constexpr int kThreads = 64 + 32 * kWarps;
 };
 
@@ -270,10 +271,12 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
 // 3xTF32 kernels therefore accumulate at most `chunk_blocks` K blocks in tensor memory; the epilogue warps
 // add each partial sum into registers with round-to-nearest fp32 adds (one warp owns NC x 32 columns of 32
 // rows) and apply the epilogue to the total.  `use` counts accumulator buffers consumed by this CTA.
+// This warp owns the 32-column chunks first_chunk_col, first_chunk_col + chunk_stride, ... below n_cols_chunks.
 template <int NC>
 __device__ __forceinline__ bool drain_chunks(const TcParams& p, uint64_t* acc_full, uint32_t tmem_lane_base, int buf_cols, int first_chunk_col,
-                                             int n_chunks, int& use, volatile int* abort_flag, float (&acc)[NC][32], int lane,
-                                             uint32_t acc_empty_addr0, bool remote_arrive, uint64_t* acc_empty_local) {
+                                             int chunk_stride, int n_cols_chunks, int n_chunks, int& use, volatile int* abort_flag,
+                                             float (&acc)[NC][32], int lane, uint32_t acc_empty_addr0, bool remote_arrive,
+                                             uint64_t* acc_empty_local) {
 #pragma unroll
   for (int c = 0; c < NC; ++c)
 #pragma unroll
@@ -284,10 +287,13 @@ __device__ __forceinline__ bool drain_chunks(const TcParams& p, uint64_t* acc_fu
     tc_fence_after();
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
-      uint32_t r[32];
-      tmem_ld32(tmem_lane_base + (uint32_t)(buf * buf_cols + (first_chunk_col + c) * 32), r);
+      const int cc = first_chunk_col + c * chunk_stride;
+      if (cc < n_cols_chunks) {          // the same for every lane of the warp
+        uint32_t r[32];
+        tmem_ld32(tmem_lane_base + (uint32_t)(buf * buf_cols + cc * 32), r);
 #pragma unroll
-      for (int j = 0; j < 32; ++j) acc[c][j] = __fadd_rn(acc[c][j], __uint_as_float(r[j]));
+        for (int j = 0; j < 32; ++j) acc[c][j] = __fadd_rn(acc[c][j], __uint_as_float(r[j]));
+      }
     }
     tc_fence_before();
     __syncwarp();
@@ -428,14 +434,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
       const int row = m0 + q * 32 + lane;
       const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
       if (TF32) {
-        constexpr int NC = BN / 64;
+        constexpr int kParts = EpiCfg<TF32>::kWarps / 4;
+        constexpr int NC = (BN / 32 + kParts - 1) / kParts;
         float acc[NC][32];
-        ok = drain_chunks<NC>(p, acc_full, lane_base, BN, half * NC, n_chunks, use, abort_flag, acc, lane, 0u, false, acc_empty);
+        ok = drain_chunks<NC>(p, acc_full, lane_base, BN, half, kParts, BN / 32, n_chunks, use, abort_flag, acc, lane, 0u, false, acc_empty);
         if (!ok) break;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
-          const int col0 = n0 + (half * NC + c) * 32;
-          if (row < p.M && col0 < p.N) epilogue_chunk(p, reinterpret_cast<const uint32_t*>(acc[c]), row, col0, p.C, p.bias);
+          const int cc = half + c * kParts;
+          const int col0 = n0 + cc * 32;
+          if (cc < BN / 32 && row < p.M && col0 < p.N) epilogue_chunk(p, reinterpret_cast<const uint32_t*>(acc[c]), row, col0, p.C, p.bias);
         }
       } else {
         const int buf = use & 1;
@@ -631,14 +639,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
       const int row = m0 + (int)rank * kHalf + q * 32 + lane;
       const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
       if (TF32) {
-        constexpr int NC = TN / 64;
+        constexpr int kParts = EpiCfg<TF32>::kWarps / 4;
+        constexpr int NC = (TN / 32 + kParts - 1) / kParts;
         float acc[NC][32];
-        ok = drain_chunks<NC>(p, acc_full, lane_base, TN, half * NC, n_chunks, use, abort_flag, acc, lane, acc_empty0, true, nullptr);
+        ok = drain_chunks<NC>(p, acc_full, lane_base, TN, half, kParts, TN / 32, n_chunks, use, abort_flag, acc, lane, acc_empty0, true, nullptr);
         if (!ok) break;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
-          const int col0 = n0 + (half * NC + c) * 32;
-          if (row < p.M && col0 < p.N) epilogue_chunk(p, reinterpret_cast<const uint32_t*>(acc[c]), row, col0, Cp, biasp);
+          const int cc = half + c * kParts;
+          const int col0 = n0 + cc * 32;
+          if (cc < TN / 32 && row < p.M && col0 < p.N) epilogue_chunk(p, reinterpret_cast<const uint32_t*>(acc[c]), row, col0, Cp, biasp);
         }
       } else {
         const int buf = use & 1;
