@@ -205,6 +205,8 @@ class CudaBridge:
 
     # -- whole-plan methods (_bridge.py:262-289) ---------------------------------------------
     def _encode(self, plan: Dict[str, Any], requests_json: Optional[str]) -> wire.EncodedPlan:
+        """The flat encoding of ``plan``, remembered per plan object: a plan dict must not be edited in place after
+        its first run (build a new dict instead), or the remembered encoding goes stale."""
         key = id(plan)
         hit = self._plan_cache.get(key)
         if hit is not None and hit[0] is plan and requests_json is None:
