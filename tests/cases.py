@@ -141,6 +141,14 @@ def _mlp2_inputs() -> Dict[str, np.ndarray]:
             "w2": r.standard_normal((272, 300), dtype=np.float32) / np.float32(17), "b2": r.standard_normal((272,), dtype=np.float32) * np.float32(0.1)}
 
 
+def _small_gemm_inputs(m: int, n: int, k: int) -> Callable[[], Dict[str, np.ndarray]]:
+    def make() -> Dict[str, np.ndarray]:
+        r = _rng(79 + m + n + k)
+        return {"x": r.standard_normal((m, k), dtype=np.float32), "w": r.standard_normal((n, k), dtype=np.float32) / np.float32(k ** 0.5),
+                "wt": r.standard_normal((k, n), dtype=np.float32) / np.float32(k ** 0.5), "bias": r.standard_normal((n,), dtype=np.float32)}
+    return make
+
+
 def _ln_inputs(rows: int, cols: int) -> Callable[[], Dict[str, np.ndarray]]:
     def make() -> Dict[str, np.ndarray]:
         r = _rng(300 + cols)
@@ -401,6 +409,14 @@ CASES: Dict[str, Case] = {
     "permute_copy": Case(_misc_inputs, lambda api, t, raw: t["x"].permute(2, 0, 1), kind="exact"),
     "permute_add": Case(_misc_inputs, lambda api, t, raw: t["x"].permute(1, 0, 2) + t["row"]),
     "reshape_reduce": Case(_misc_inputs, lambda api, t, raw: t["x"].reshape(30, 33).sum(axis=0)),
+    # 2-D fp32 products below the tensor-core threshold: the split-K kernel (32 x 32 tiles, ragged edges, one to many
+    # K slices, a K that leaves a short last slice), with and without its folded bias / ReLU, row-major and transposed B
+    "small_gemm_relu": Case(_small_gemm_inputs(70, 100, 300), lambda api, t, raw: api.relu(api.linear(t["x"], t["w"], t["bias"]))),
+    "small_gemm_bias": Case(_small_gemm_inputs(33, 65, 1000), lambda api, t, raw: api.linear(t["x"], t["w"], t["bias"])),
+    "small_gemm_plain": Case(_small_gemm_inputs(64, 10, 128), lambda api, t, raw: t["x"] @ t["wt"]),
+    "small_gemm_one_slice": Case(_small_gemm_inputs(500, 300, 32), lambda api, t, raw: api.relu(t["x"] @ t["wt"] + t["bias"])),
+    "small_gemm_kept_product": Case(_small_gemm_inputs(48, 40, 96),
+                                    lambda api, t, raw: (lambda p: api.cat([api.relu(p + t["bias"]), p], 1))(t["x"] @ t["wt"])),
     "matmul_batched_bcast": Case(_misc_inputs, lambda api, t, raw: t["bm"] @ t["bn"]),
     "matmul_vec_rhs": Case(_misc_inputs, lambda api, t, raw: t["m79"] @ t["v9"]),
     "matmul_vec_lhs": Case(_misc_inputs, lambda api, t, raw: t["v9"] @ t["bn"]),

@@ -75,6 +75,39 @@ def test_full_size_config2_takes_the_pattern_kernels():
         assert rc == 0 and len(lines) == 1 and lines[0].startswith("static_"), lines
 
 
+def test_autocast_decoder_block_leaves_nothing_on_the_interpreter():
+    """The casts the AMP pass inserts around every MATMUL are removed or absorbed by the plan compiler: a decoder block
+    built under autocast lowers to tensor-core GEMMs (bias + GELU + narrowing cast in the epilogue, q / k / v as one
+    grid), the fused attention, the specialised LayerNorm kernel and one conversion per activation."""
+    import collections
+    from browsergrad_b200 import configs, graph
+    arrays = configs.gpt_inputs(layers=2, batch=8)
+    meta = arrays.pop("_meta")
+    store = graph.BufferStore()
+    t = {k: graph.from_numpy(v, store) for k, v in arrays.items()}
+    for amp in ("float16", "bfloat16"):
+        _, plan = front.plan_for(configs.gpt_forward(graph, t, meta, amp=amp)._uop)
+        rc, lines = dry(plan, fusion=3)
+        assert rc == 0, lines
+        units = collections.Counter(lines)
+        assert not any(ln.startswith(("ew[", "row[")) for ln in lines), units
+        assert units[f"gemm_tc+bias+gelu[{amp}]"] == 2 and units[f"gemm_tc+bias[{amp}] x3"] == 2, units
+        assert units[f"attention_tc+mask+merge[{amp}]"] == 2 and units["static_row[CAST,ADD,ADD|LAYER_NORM]"] == 4, units
+
+
+def test_small_fp32_products_take_the_split_k_kernel_with_their_epilogue():
+    for name, expect in (("small_gemm_relu", ["gemm_small+bias+relu[float32]"]), ("small_gemm_bias", ["gemm_small+bias[float32]"]),
+                         ("small_gemm_plain", ["gemm_small[float32]"]), ("c1_mlp_ce", None)):
+        t, _, _ = build_case(CASES[name])
+        _, plan = front.plan_for(t._uop)
+        rc, lines = dry(plan, fusion=3)
+        assert rc == 0, lines
+        if expect is not None:
+            assert lines == expect, lines
+        else:
+            assert lines == ["gemm_small+bias+relu[float32]", "gemm_small+bias[float32]", "cross_entropy"], lines
+
+
 def test_unsupported_opcode_mentions_numpy_fallback():
     plan = {"step_count": 1, "root_id": 0, "steps": [
         {"step": 0, "value_id": 0, "op": "CONV2D", "input_ids": [], "shape": [1], "dtype": "float32", "arg": None}]}
