@@ -322,19 +322,21 @@ __global__ void ce_pos_kernel(const CeRowArgs<T> a) {
 // 16-byte vectors (coalesced), keeping a running maximum that is raised once per group of vectors, and the partial
 // (M, S, T1, T2) of all threads are combined through shared memory.  The row is read from DRAM once; the statistics
 // are rescaled, never the data.
-template <typename T, int VEC, bool SUMS>
+// SUMS: 0 none (index targets, no smoothing); 1 label smoothing with neither probability targets nor class weights (the
+// per-class factor is one: no second or third operand stream); 2 the general weighted sums.
+template <typename T, int VEC, int SUMS>
 __global__ void __launch_bounds__(256) ce_row_kernel(const CeRowArgs<T> a, int vec_ok) {
-  constexpr int kGroup = (sizeof(T) == 4 && !SUMS) ? 8 : 4;   // vectors per thread in flight between maximum updates
+  constexpr int kGroup = (sizeof(T) == 4 && SUMS < 2) ? 8 : 4;   // vectors per thread in flight between maximum updates
   const int64_t row = blockIdx.x;
   const T* x = a.logits + row * a.C;
-  const T* pr = a.prob ? a.prob + row * a.C : nullptr;
-  constexpr bool need_sums = SUMS;                // probability targets or label smoothing: the weighted sums T1, T2
+  const T* pr = (SUMS == 2 && a.prob) ? a.prob + row * a.C : nullptr;
+  constexpr bool need_sums = SUMS != 0;           // probability targets or label smoothing: the weighted sums T1, T2
   const T eps = a.smoothing, unif = a.smoothing / (T)a.C;
   __shared__ T sh_m[8], sh_s[8], sh_t1[8], sh_t2[8];
   const bool skip = !a.prob && a.idx[row] == a.ignore_index;      // the whole CTA agrees
   T M = ce_neg_inf<T>(), S = T(0), T1 = T(0), T2 = T(0);           // T1 is kept relative to the running M
   if (!skip) {
-    const bool use_w = a.weight != nullptr && need_sums;
+    const bool use_w = SUMS == 2 && a.weight != nullptr;
     // raise the reference maximum to gm: S scales by exp(M - gm), T1 (kept relative to M) shifts by (M - gm) * T2
     auto raise = [&](T gm) {
       if (gm > M) {
@@ -563,8 +565,9 @@ cudaError_t ce_rows_typed(const CeProblem& c, cudaStream_t s) {
                          (!c.prob_targets || (reinterpret_cast<uintptr_t>(c.targets) & 15) == 0) &&
                          (!c.weight || (reinterpret_cast<uintptr_t>(c.weight) & 15) == 0);
     const int threads = c.C >= 4096 ? 256 : 128;
-    if (a.prob != nullptr || a.smoothing != T(0)) ce_row_kernel<T, VEC, true><<<(unsigned)n, threads, 0, s>>>(a, aligned ? 1 : 0);
-    else ce_row_kernel<T, VEC, false><<<(unsigned)n, threads, 0, s>>>(a, aligned ? 1 : 0);
+    if (a.prob != nullptr || (a.smoothing != T(0) && a.weight != nullptr)) ce_row_kernel<T, VEC, 2><<<(unsigned)n, threads, 0, s>>>(a, aligned ? 1 : 0);
+    else if (a.smoothing != T(0)) ce_row_kernel<T, VEC, 1><<<(unsigned)n, threads, 0, s>>>(a, aligned ? 1 : 0);
+    else ce_row_kernel<T, VEC, 0><<<(unsigned)n, threads, 0, s>>>(a, aligned ? 1 : 0);
   } else {
     ce_pos_kernel<T><<<grid_for(n, 128), 128, 0, s>>>(a);
   }
