@@ -72,8 +72,10 @@ cudaError_t launch_attn16_pair(const attn::AttnParams& p, bool bf16, bool v_mn, 
                                const CUtensorMap& tm_v, cudaStream_t s);
 
 // 3xTF32 kernel with one thread per query row and P / O in tensor memory (attn_tf32_row.cu).  maps: Q hi, Q lo
-// ([128 rows, 32] boxes), K hi, K lo ([64 keys, 32] boxes), V^T hi, V^T lo ([64 rows, 32 keys] boxes).
-bool attn_tf32_row_usable(int Sk, int out_dtype, const void* out, long long out_sb, long long out_sh, long long out_ss);
-cudaError_t launch_attn_tf32_row(const attn::AttnParams& p, const CUtensorMap maps[6], cudaStream_t s);
+// ([128 rows, 32] boxes), K hi, K lo ([64 keys, 32] boxes), V^T hi, V^T lo ([64 rows, 32 keys] boxes).  With `raw`
+// the Q hi and K hi maps describe the caller's own fp32 rows (same boxes), the lo maps of Q and K are not used and the
+// kernel splits the values itself (one more K stage in shared memory, hence the flag in the usability check).
+bool attn_tf32_row_usable(int Sk, int out_dtype, const void* out, long long out_sb, long long out_sh, long long out_ss, bool raw);
+cudaError_t launch_attn_tf32_row(const attn::AttnParams& p, const CUtensorMap maps[6], bool raw, cudaStream_t s);
 
 }  // namespace bg

@@ -1008,7 +1008,8 @@ void attn_scratch_sizes(const AttnProblem& a, int64_t bytes[8]) {
 // 16-bit kernel choice: bit 0 the two-tile (pair) kernel, bit 1 V as an MN-major operand (no transposing pass),
 // bit 2 P in tensor memory.  0 selects the single-tile kernel.
 int g_attn16_variant = kAttn16DefaultVariant;
-// 3xTF32 kernel choice: 0 two threads per row with P in shared memory, 1 one thread per row with P and O in tensor memory.
+// 3xTF32 kernel choice: 0 two threads per row with P in shared memory, 1 one thread per row with P and O in tensor
+// memory, 3 the same with fp32 Q and K rows split into planes inside the kernel.
 int g_attn32_variant = kAttn32DefaultVariant;
 
 cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bool check_uniform, bool classify_mask, int* status,
@@ -1025,6 +1026,10 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
            o.stride[2] >= a.D && o.stride[0] % 4 == 0 && o.stride[1] % 4 == 0 && o.stride[2] % 4 == 0;
   };
   const bool kv32 = v_mn && p_tmem && (g_attn16_variant & 8) && fp32_rows(a.k) && fp32_rows(a.v);
+  // 3xTF32, one thread per row: fp32 Q and K rows are split into hi / lo planes inside the kernel
+  const bool row32 = tf32 && (g_attn32_variant & 1);
+  const bool raw_qk = row32 && (g_attn32_variant & 2) && fp32_rows(a.q) && fp32_rows(a.k) &&
+                      attn_tf32_row_usable(a.Sk, a.out_dtype, a.out, a.out_sb, a.out_sh, a.out_ss, true);
   // operand staging: dense Q, K, V^T (or V) in the kernel's encoding
   const int kind = tf32 ? PREP_TF32 : (a.ab_dtype == BG_F16 ? PREP_F16 : PREP_BF16);
   const AttnOperand* ops[3] = {&a.q, &a.k, &a.v};
@@ -1046,6 +1051,7 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
       }
     }
     if (kv32 && i > 0) continue;
+    if (raw_qk && i < 2) continue;
     // 16-bit operands that are already dense [B,H,S,D] feed the TMA maps directly
     if (!tf32 && as_rows && dense && ops[i]->dtype == a.ab_dtype && aligned) {
       staged[i] = ops[i]->ptr;
@@ -1096,8 +1102,13 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
     }
   }
   CUtensorMap q0, q1, k0, k1, v0, v1;
-  if (!pair && !make_map4(&q0, staged[0], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
-  if (kv32) {
+  if (raw_qk) {
+    if (!make_map4_strided(&q0, a.q.ptr, BG_F32, a.B, a.H, a.Sq, a.D, a.q.stride[0], a.q.stride[1], a.q.stride[2], 32, kQRows) ||
+        !make_map4_strided(&k0, a.k.ptr, BG_F32, a.B, a.H, a.Sk, a.D, a.k.stride[0], a.k.stride[1], a.k.stride[2], 32, bkv))
+      return cudaErrorInvalidValue;
+  } else if (!pair && !make_map4(&q0, staged[0], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
+  if (raw_qk) {
+  } else if (kv32) {
     if (!make_map4_strided(&k0, a.k.ptr, BG_F32, a.B, a.H, a.Sk, a.D, a.k.stride[0], a.k.stride[1], a.k.stride[2], 32, bkv) ||
         !make_map4_strided(&v0, a.v.ptr, BG_F32, a.B, a.H, a.Sk, a.D, a.v.stride[0], a.v.stride[1], a.v.stride[2], 32, bkv))
       return cudaErrorInvalidValue;
@@ -1108,8 +1119,8 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
   } else if (!make_map4(&v0, staged[2], sdt, a.B, a.H, a.D, a.Sk, kHeadDim)) return cudaErrorInvalidValue;
   q1 = q0; k1 = k0; v1 = v0;
   if (tf32) {
-    if (!make_map4(&q1, scratch[1], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
-    if (!make_map4(&k1, scratch[3], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
+    if (!raw_qk && !make_map4(&q1, scratch[1], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
+    if (!raw_qk && !make_map4(&k1, scratch[3], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
     if (!make_map4(&v1, scratch[5], sdt, a.B, a.H, a.D, a.Sk, kHeadDim)) return cudaErrorInvalidValue;
   }
   AttnParams p{};
@@ -1145,9 +1156,9 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
   }
   dim3 grid((a.Sq + kQRows - 1) / kQRows, a.H, a.B);
   cudaError_t e;
-  if (tf32 && g_attn32_variant == 1 && attn_tf32_row_usable(a.Sk, a.out_dtype, a.out, a.out_sb, a.out_sh, a.out_ss)) {
+  if (row32 && (raw_qk || attn_tf32_row_usable(a.Sk, a.out_dtype, a.out, a.out_sb, a.out_sh, a.out_ss, false))) {
     const CUtensorMap maps[6] = {q0, q1, k0, k1, v0, v1};
-    return launch_attn_tf32_row(p, maps, s);
+    return launch_attn_tf32_row(p, maps, raw_qk, s);
   }
   if (tf32) {
     const size_t smem = AttnCfg::SmemBytes + 256 + 2048 + 1024;

@@ -2,11 +2,13 @@
 // one thread per query row, probabilities and output kept in tensor memory.
 //
 // One CTA owns 128 query rows of one (batch, head) and walks the key tiles (64 keys) that its mask classes keep:
-//   warp 0      producer: lane 0 Q once and the K tiles, lane 1 the V^T tiles (TMA, two-stage rings of their own);
-//               every operand arrives pre-split into hi = tf32(x) and lo = x - hi planes
+//   warp 0      producer: lane 0 Q once and the K tiles, lane 1 the V^T tiles (TMA, rings of their own); an operand
+//               arrives pre-split into hi = tf32(x) and lo = x - hi planes, or (RAW) Q and K arrive as the caller's
+//               fp32 rows in the hi planes' places and four converter warps round them in place and write the lo planes
 //   warp 1      MMA issuer (all lanes run the loop, an elected lane issues): S = Q K^T as the three products
 //               lo.hi, hi.lo, hi.hi into a double-buffered S; O += P V likewise, with P read from tensor memory
-//   warps 2-5   softmax: one thread per query row.  A thread reads its 64 scores of a tile once (tcgen05.ld), frees
+//   4 warps     softmax (warps 2-5; 4-7 under RAW, where warps 2, 3 idle and 8-11 convert, so that whole warpgroups
+//               trade registers with setmaxnreg): one thread per query row.  A thread reads its 64 scores of a tile once (tcgen05.ld), frees
 //               S at once, takes the row maximum, the exponentials against a lazily raised reference maximum and the
 //               row sum with no exchange between threads, splits the probabilities into hi / lo and stores both
 //               planes to tensor memory (double-buffered: tile t+1's probabilities are written while P.V of tile t
@@ -33,15 +35,24 @@ namespace {
 using namespace tc;
 using namespace attn;
 
+template <bool RAW>
 struct RowCfg {
   static constexpr int BKV = 64;
-  static constexpr int NK = 2, NV = 2;
+  // RAW halves what a K tile asks of the TMA unit but puts the converters between the load and the product: a
+  // third K stage covers that hop
+  static constexpr int NK = RAW ? 3 : 2, NV = 2;
   // planes of a tile: hi k-block 0, hi k-block 1, lo k-block 0, lo k-block 1 (a k-block is 32 floats = 128 bytes)
   static constexpr int QBytes = 4 * kQRows * 128;
   static constexpr int KBytes = 4 * BKV * 128;
   static constexpr int VBytes = 4 * kHeadDim * 128;            // V^T: 64 rows x (2 x 32) keys, hi and lo
-  static constexpr int SmemBytes = QBytes + NK * KBytes + NV * VBytes;   // 192 KB
-  static constexpr int Threads = 192;
+  static constexpr int SmemBytes = QBytes + NK * KBytes + NV * VBytes;   // 192 KB (224 KB under RAW)
+  static constexpr int Threads = RAW ? 384 : 192;
+  static constexpr int SoftmaxWarp0 = RAW ? 4 : 2;
+  // setmaxnreg (RAW): the CTA's register pool is Launch per thread; two warpgroups shrink to Light, the softmax
+  // warpgroup grows to Softmax.  A request beyond the pool would wait for ever, hence the assertion and the check of
+  // the compiled register count at launch.
+  static constexpr int Launch = 168, Light = 72, Softmax = 248;
+  static_assert(256 * Light + 128 * Softmax <= Launch * 384, "setmaxnreg requests exceed the CTA's register pool");
   static constexpr int TmemCols = 512;
   static constexpr int ColS = 0;                               // 2 x 64
   static constexpr int ColP = 128;                             // 2 x (hi 64 | lo 64)
@@ -71,12 +82,32 @@ __device__ __forceinline__ void umma_ts_tf32(uint32_t tmem_d, uint32_t tmem_a, u
       : "memory");
 }
 
-__global__ void __launch_bounds__(RowCfg::Threads, 1)
+// RAW: split the fp32 values that the TMA unit left in a tile's hi planes (`bytes` of them) into hi = tf32(x), in
+// place, and lo = x - hi in the lo planes that follow.  Same offsets in both, so the swizzle does not matter.
+__device__ __forceinline__ void split_planes(unsigned char* hi_planes, int bytes, int tid) {
+  float4* h = reinterpret_cast<float4*>(hi_planes);
+  float4* l = reinterpret_cast<float4*>(hi_planes + bytes);
+#pragma unroll 4
+  for (int c = tid; c < bytes / 16; c += 128) {
+    const float4 x = h[c];
+    uint32_t a, b, cc, d;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(a) : "f"(x.x));
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(b) : "f"(x.y));
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(cc) : "f"(x.z));
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(d) : "f"(x.w));
+    const float4 hi = make_float4(__uint_as_float(a), __uint_as_float(b), __uint_as_float(cc), __uint_as_float(d));
+    h[c] = hi;
+    l[c] = make_float4(x.x - hi.x, x.y - hi.y, x.z - hi.z, x.w - hi.w);
+  }
+}
+
+template <bool RAW>
+__global__ void __launch_bounds__(RowCfg<RAW>::Threads, 1)
 attn_tf32_row_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant__ CUtensorMap tmQ1,
                      const __grid_constant__ CUtensorMap tmK0, const __grid_constant__ CUtensorMap tmK1,
                      const __grid_constant__ CUtensorMap tmV0, const __grid_constant__ CUtensorMap tmV1,
                      const __grid_constant__ AttnParams p) {
-  using C = RowCfg;
+  using C = RowCfg<RAW>;
   constexpr int BKV = C::BKV;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -93,7 +124,9 @@ attn_tf32_row_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_cons
   uint64_t* s_empty = s_full + 2;         // [2] the softmax warps hold its scores in registers (4 arrivals)
   uint64_t* p_full = s_empty + 2;         // [2] its probabilities are in tensor memory (4 arrivals)
   uint64_t* pv_full = p_full + 2;         // [2] its P V has completed
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_full + 2);
+  uint64_t* q_raw = pv_full + 2;          // RAW: the fp32 rows of Q have landed
+  uint64_t* k_raw = q_raw + 1;            // [NK] RAW: the fp32 rows of a K tile have landed
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(k_raw + C::NK);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   unsigned char* s_cls = reinterpret_cast<unsigned char*>(tmem_holder + 4);   // [n_kv] tile classes of this query tile
 
@@ -115,8 +148,9 @@ attn_tf32_row_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_cons
   auto next_tile = [&](int j) { while (j < n_kv && s_cls[j] == 0) ++j; return j; };
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    for (int s = 0; s < C::NK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    mbar_init(q_full, RAW ? 4 : 1);       // RAW: the four converter warps publish an operand
+    mbar_init(q_raw, 1);
+    for (int s = 0; s < C::NK; ++s) { mbar_init(&k_full[s], RAW ? 4 : 1); mbar_init(&k_empty[s], 1); mbar_init(&k_raw[s], 1); }
     for (int s = 0; s < C::NV; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
@@ -134,22 +168,35 @@ attn_tf32_row_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
+  const bool softmax_warp = warp >= C::SoftmaxWarp0 && warp < C::SoftmaxWarp0 + 4;
+  if (!softmax_warp) {
+  if constexpr (RAW) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::Light));
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(q_full, C::QBytes);
-      for (int kb = 0; kb < 2; ++kb) {
-        tma_load_4d(&tmQ0, sQ + kb * (kQRows * 128), q_full, kb * 32, q0, h, b);
-        tma_load_4d(&tmQ1, sQ + (2 + kb) * (kQRows * 128), q_full, kb * 32, q0, h, b);
+      if constexpr (RAW) {
+        mbar_expect_tx(q_raw, C::QBytes / 2);
+        for (int kb = 0; kb < 2; ++kb) tma_load_4d(&tmQ0, sQ + kb * (kQRows * 128), q_raw, kb * 32, q0, h, b);
+      } else {
+        mbar_expect_tx(q_full, C::QBytes);
+        for (int kb = 0; kb < 2; ++kb) {
+          tma_load_4d(&tmQ0, sQ + kb * (kQRows * 128), q_full, kb * 32, q0, h, b);
+          tma_load_4d(&tmQ1, sQ + (2 + kb) * (kQRows * 128), q_full, kb * 32, q0, h, b);
+        }
       }
       int t = 0;
       for (int j = next_tile(0); j < n_kv; j = next_tile(j + 1), ++t) {
         const int s = t % C::NK;
         if (!mbar_wait(&k_empty[s], ((uint32_t)(t / C::NK) & 1u) ^ 1u, abort_flag)) break;
         unsigned char* st = sK + s * C::KBytes;
-        mbar_expect_tx(&k_full[s], C::KBytes);
-        for (int kb = 0; kb < 2; ++kb) {
-          tma_load_4d(&tmK0, st + kb * (BKV * 128), &k_full[s], kb * 32, j * BKV, h, b);
-          tma_load_4d(&tmK1, st + (2 + kb) * (BKV * 128), &k_full[s], kb * 32, j * BKV, h, b);
+        if constexpr (RAW) {
+          mbar_expect_tx(&k_raw[s], C::KBytes / 2);
+          for (int kb = 0; kb < 2; ++kb) tma_load_4d(&tmK0, st + kb * (BKV * 128), &k_raw[s], kb * 32, j * BKV, h, b);
+        } else {
+          mbar_expect_tx(&k_full[s], C::KBytes);
+          for (int kb = 0; kb < 2; ++kb) {
+            tma_load_4d(&tmK0, st + kb * (BKV * 128), &k_full[s], kb * 32, j * BKV, h, b);
+            tma_load_4d(&tmK1, st + (2 + kb) * (BKV * 128), &k_full[s], kb * 32, j * BKV, h, b);
+          }
         }
       }
     } else if (lane == 1) {
@@ -237,7 +284,30 @@ attn_tf32_row_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_cons
       if (t + 2 < n_proc) ok = issue_qk(t + 2);
       if (ok) ok = issue_pv(t);
     }
+  } else if (RAW && warp >= 8) {
+    // converters: Q once, then every K tile in the producer's order
+    const int ctid = (int)threadIdx.x - 256;
+    auto publish = [&](uint64_t* bar) {
+      fence_async_smem();                           // the planes are read by the tensor core (async proxy)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar);
+    };
+    bool ok = __all_sync(0xffffffffu, mbar_wait(q_raw, 0, abort_flag)) != 0;
+    if (ok) {
+      split_planes(sQ, C::QBytes / 2, ctid);
+      publish(q_full);
+    }
+    int t = 0;
+    for (int j = next_tile(0); j < n_kv && ok; j = next_tile(j + 1), ++t) {
+      const int s = t % C::NK;
+      ok = __all_sync(0xffffffffu, mbar_wait(&k_raw[s], (uint32_t)(t / C::NK) & 1u, abort_flag)) != 0;
+      if (!ok) break;
+      split_planes(sK + s * C::KBytes, C::KBytes / 2, ctid);
+      publish(&k_full[s]);
+    }
+  }
   } else {
+    if constexpr (RAW) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::Softmax));
     const int quarter = warp & 3;                   // tensor-memory lane quarter this warp may access
     const int r_in_tile = quarter * 32 + lane;
     const int row = q0 + r_in_tile;
@@ -428,24 +498,37 @@ attn_tf32_row_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_cons
 
 }  // namespace
 
-bool attn_tf32_row_usable(int Sk, int out_dtype, const void* out, long long out_sb, long long out_sh, long long out_ss) {
+bool attn_tf32_row_usable(int Sk, int out_dtype, const void* out, long long out_sb, long long out_sh, long long out_ss, bool raw) {
   if (out_dtype != BG_F32 && out_dtype != BG_F64) return false;
-  const int n_kv = (Sk + RowCfg::BKV - 1) / RowCfg::BKV;
-  if ((size_t)RowCfg::SmemBytes + 256 + 1024 + (size_t)n_kv > 227 * 1024) return false;
+  const int n_kv = (Sk + 63) / 64;
+  if ((size_t)(raw ? RowCfg<true>::SmemBytes : RowCfg<false>::SmemBytes) + 256 + 1024 + (size_t)n_kv > 227 * 1024) return false;
   const long long per16 = 16 / dtype_size(out_dtype);
   return (reinterpret_cast<uintptr_t>(out) & 15) == 0 && out_sb % per16 == 0 && out_sh % per16 == 0 && out_ss % per16 == 0;
 }
 
-cudaError_t launch_attn_tf32_row(const attn::AttnParams& p, const CUtensorMap maps[6], cudaStream_t s) {
+template <bool RAW>
+static cudaError_t launch_row(const attn::AttnParams& p, const CUtensorMap maps[6], unsigned n_cta, size_t n_kv, cudaStream_t s) {
+  using C = RowCfg<RAW>;
+  const size_t smem = (size_t)C::SmemBytes + 256 + 1024 + n_kv;
+  auto kern = attn_tf32_row_kernel<RAW>;
+  if (RAW) {
+    cudaFuncAttributes fa;
+    cudaError_t e = cudaFuncGetAttributes(&fa, kern);
+    if (e != cudaSuccess) return e;
+    if (fa.numRegs < C::Launch) return cudaErrorLaunchOutOfResources;   // the pool that setmaxnreg draws on
+  }
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  kern<<<dim3(n_cta), C::Threads, smem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_attn_tf32_row(const attn::AttnParams& p, const CUtensorMap maps[6], bool raw, cudaStream_t s) {
   const int n_qt = (p.Sq + kQRows - 1) / kQRows;
   const long long n_cta = (long long)n_qt * p.B * p.H;
   if (n_cta <= 0 || n_cta > 0x7fffffffll) return cudaErrorInvalidValue;
-  const int n_kv = (p.Sk + RowCfg::BKV - 1) / RowCfg::BKV;
-  const size_t smem = (size_t)RowCfg::SmemBytes + 256 + 1024 + (size_t)n_kv;
-  cudaError_t e = cudaFuncSetAttribute(attn_tf32_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return e;
-  attn_tf32_row_kernel<<<dim3((unsigned)n_cta), RowCfg::Threads, smem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
-  return cudaGetLastError();
+  const size_t n_kv = (size_t)((p.Sk + 63) / 64);
+  return raw ? launch_row<true>(p, maps, (unsigned)n_cta, n_kv, s) : launch_row<false>(p, maps, (unsigned)n_cta, n_kv, s);
 }
 
 }  // namespace bg

@@ -318,8 +318,8 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
 extern int g_attn16_variant;
 constexpr int kAttn16DefaultVariant = 15;
 // Which 3xTF32 attention kernel runs: 0 two threads per row, P through shared memory; 1 one thread per row, P and O in
-// tensor memory.
+// tensor memory; 3 as 1, and fp32 Q / K rows are split into their hi / lo planes inside the kernel.
 extern int g_attn32_variant;
-constexpr int kAttn32DefaultVariant = 1;
+constexpr int kAttn32DefaultVariant = 3;
 
 }  // namespace bg

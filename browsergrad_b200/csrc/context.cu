@@ -400,7 +400,7 @@ int bg_set_option(bg_context* ctx, const char* key, int64_t value) {
     g_attn16_variant = value < 0 ? kAttn16DefaultVariant : (int)value;     // process-wide: a launch policy, not plan state
   }
   else if (k == "attention32_kernel") {
-    if (value < -1 || value > 1) return fail(ctx, BG_ERR_INVALID, "set_option: attention32_kernel is 0, 1, or -1 for the default");
+    if (value < -1 || value > 3 || value == 2) return fail(ctx, BG_ERR_INVALID, "set_option: attention32_kernel is 0, 1, 3, or -1 for the default");
     g_attn32_variant = value < 0 ? kAttn32DefaultVariant : (int)value;
   }
   else if (k == "fail_allocation_after") {

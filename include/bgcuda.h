@@ -177,7 +177,7 @@ int bg_abi_version(void);
  * "attention16_kernel" (bit set: 1 two query tiles per CTA, 2 V as an MN-major operand, 4 P in tensor memory,
  * 8 fp32 K / V converted inside the kernel; 0 one query tile per CTA; -1 restores the default),
  * "attention32_kernel" (3xTF32 attention: 0 two threads per row, 1 one thread per row with P and O in tensor
- * memory; -1 restores the default). */
+ * memory, 3 the same with fp32 Q / K rows split into planes inside the kernel; -1 restores the default). */
 int bg_set_option(bg_context* ctx, const char* key, int64_t value);
 
 /* -- buffers: upload / materialize / release (_bridge.py:65-71; realizer.ts:1006-1041) ----- */

@@ -142,11 +142,12 @@ ATTN32_CASES = ["c4_attn_mask_d64", "c4_attn_causal_d64", "c4_attn_causal_tiles"
                 "typed_attention_d64", "c4_attn_merge_heads", "c4_attn_growing_f32", "c4_attn_long_f32"]
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 3])
 @pytest.mark.parametrize("name", ATTN32_CASES)
 def test_every_3xtf32_attention_kernel_matches_oracle(bridge, name, variant):
     """Option attention32_kernel: 0 = two threads per query row, P through shared memory, P.V folded into registers
-    every tile; 1 = one thread per row, P and O in tensor memory, O folded into registers every eighth tile."""
+    every tile; 1 = one thread per row, P and O in tensor memory, O folded into registers every eighth tile; 3 = as 1, with
+    fp32 Q and K rows split into hi / lo planes by converter warps of the kernel instead of a staging pass."""
     case = CASES[name]
     t, store, _ = build_case(case)
     want = oracle_value(t, store)
