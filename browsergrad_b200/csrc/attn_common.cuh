@@ -1,6 +1,7 @@
 // Declarations shared by the fused attention kernels (attn_tc.cu, attn16_pair.cu): kernel parameters and
 // the small PTX helpers both files use.
 #pragma once
+#include <cuda_bf16.h>
 
 #include <cuda.h>
 #include <stdint.h>
@@ -53,6 +54,9 @@ struct AttnParams {
   int out_dtype;
   int round_scores;            // dtype + 1: round S through f16 / bf16 before the softmax (autocast graphs)
   uint32_t idesc_qk, idesc_pv;
+  float* planes_hi;            // 3xTF32 row kernel: store the result as split-product operand planes instead of `out`
+  __nv_bfloat16* planes_16;    // bf16(x) plane; the bf16(x - tf32(x)) plane follows after planes_n elements
+  long long planes_n;
   int* status;
   // query rows read by the kernel itself (pair kernel): 64 contiguous values per row, fp32 (rounded to the operand
   // type as the graph's CAST would) or already of the operand type, at b * q_sb + h * q_sh + row * q_ss elements

@@ -1156,7 +1156,14 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
   }
   dim3 grid((a.Sq + kQRows - 1) / kQRows, a.H, a.B);
   cudaError_t e;
+  const long long n_out = (long long)a.B * a.H * a.Sq * a.D;
   if (row32 && (raw_qk || attn_tf32_row_usable(a.Sk, a.out_dtype, a.out, a.out_sb, a.out_sh, a.out_ss, false))) {
+    // (row offsets that keep `out` 16-byte aligned keep the planes' fp32 rows 16- and bf16 rows 8-byte aligned)
+    if (a.planes_hi) {
+      p.planes_hi = reinterpret_cast<float*>(a.planes_hi);
+      p.planes_16 = reinterpret_cast<__nv_bfloat16*>(a.planes_lo);
+      p.planes_n = n_out;
+    }
     const CUtensorMap maps[6] = {q0, q1, k0, k1, v0, v1};
     return launch_attn_tf32_row(p, maps, raw_qk, s);
   }
@@ -1165,6 +1172,12 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
     e = cudaFuncSetAttribute(attn_tf32_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     attn_tf32_fwd_kernel<<<grid, kAttnThreads, smem, s>>>(q0, q1, k0, k1, v0, v1, p);
+    // this kernel stores `out` only: the planes a consumer was promised are made from it
+    {
+      const cudaError_t le = cudaGetLastError();
+      if (le != cudaSuccess || !a.planes_hi) return le;
+      return launch_tf32_split(a.out, a.out_dtype, reinterpret_cast<float*>(a.planes_hi), reinterpret_cast<float*>(a.planes_lo), n_out, 8, s);
+    }
   } else {
     const size_t smem = Attn16::SmemBytes + 256 + 2048 + 1024;
     auto kern = a.ab_dtype == BG_BF16 ? attn16_fwd_kernel<true> : attn16_fwd_kernel<false>;

@@ -469,7 +469,27 @@ attn_tf32_row_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_cons
       if (row_ok) {
         const float inv = 1.0f / l;   // l = 0 for a fully masked row: 0 * inf = NaN, as the reference's softmax gives
         const size_t base = (size_t)((long long)b * p.out_sb + (long long)h * p.out_sh + (long long)row * p.out_ss);
-        if (p.out_dtype == BG_F32) {
+        if (p.planes_hi) {
+          float* hi = p.planes_hi + base;
+          __nv_bfloat16* x16 = p.planes_16 + base;
+          __nv_bfloat16* lo16 = x16 + p.planes_n;
+#pragma unroll
+          for (int d = 0; d < kHeadDim; d += 4) {
+            uint32_t hw[4];
+            float y[4], lw[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              y[e] = o[d + e] * inv;
+              asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hw[e]) : "f"(y[e]));
+              lw[e] = __fadd_rn(y[e], -__uint_as_float(hw[e]));
+            }
+            *reinterpret_cast<uint4*>(hi + d) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+            __nv_bfloat162 a0 = __floats2bfloat162_rn(y[0], y[1]), a1 = __floats2bfloat162_rn(y[2], y[3]);
+            __nv_bfloat162 l0 = __floats2bfloat162_rn(lw[0], lw[1]), l1 = __floats2bfloat162_rn(lw[2], lw[3]);
+            *reinterpret_cast<uint2*>(x16 + d) = make_uint2(*reinterpret_cast<uint32_t*>(&a0), *reinterpret_cast<uint32_t*>(&a1));
+            *reinterpret_cast<uint2*>(lo16 + d) = make_uint2(*reinterpret_cast<uint32_t*>(&l0), *reinterpret_cast<uint32_t*>(&l1));
+          }
+        } else if (p.out_dtype == BG_F32) {
           float* out = reinterpret_cast<float*>(p.out) + base;
 #pragma unroll
           for (int d = 0; d < kHeadDim; d += 4)

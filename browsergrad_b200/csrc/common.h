@@ -165,6 +165,9 @@ struct LnArgs {
   const void* w;
   const void* b;
   int64_t rows, cols;
+  // non-null: `out` is not written; the rows are stored as the planes launch_tf32_split(out, ...) would have made
+  void* planes_hi;
+  void* planes_lo;
 };
 bool static_ln_shape_ok(int64_t rows, int64_t cols);
 cudaError_t launch_static_ln(const LnArgs& a, cudaStream_t s, int sm_count);
@@ -272,6 +275,10 @@ struct TcGemm {
   int act;              // TcAct
   int round_acc;        // 0, or dtype + 1: round the accumulator through f16 / bf16 before the epilogue
   int wide;             // activation arithmetic in fp64 (for fp64 results)
+  // Non-null (single problems, N a multiple of 8, pointers 32-byte aligned): C is not written; the epilogue stores
+  // the result as the planes launch_tf32_split(C, c_dtype, planes_hi, planes_lo, M*N, N) would have made of it.
+  void* planes_hi;
+  void* planes_lo;
 };
 // Set by the host-only dry compile so that plans can be lowered as they would be on a B200.
 extern bool g_tc_assume_available;
@@ -308,6 +315,11 @@ struct AttnProblem {
   int out_dtype;
   int mode;                 // 0: 16-bit operands (ab_dtype), 1: 3xTF32
   int ab_dtype;
+  // 3xTF32 only, non-null when the result only feeds split products as their A operand: the planes
+  // launch_tf32_split would make of the B*H*Sq*D result values (same element offsets as `out`, which must then
+  // cover its elements densely).  `out` is written only when the kernel in use cannot store planes.
+  void* planes_hi;
+  void* planes_lo;
 };
 bool attn_tc_supported(const AttnProblem& a);
 void attn_scratch_sizes(const AttnProblem& a, int64_t bytes[8]);

@@ -67,6 +67,10 @@ struct TcParams {
   int n_prob;
   void* Cg[3];
   const void* biasg[3];
+  // The result is the A operand of split products only: instead of C the epilogue stores its planes (tf32(x) as
+  // fp32; then, in the 16-bit area, bf16(x) and bf16(x - tf32(x)), M*N elements each).  N is a multiple of 8.
+  float* planes_hi;
+  __nv_bfloat16* planes_16;
 };
 constexpr int kMaxGroup = 3;
 struct PairBMaps { CUtensorMap m[3 * kMaxGroup]; };   // per problem: B (or its tf32 plane), then its bf16 plane and its bf16 residual plane
@@ -147,6 +151,37 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
   }
   const bool full = col0 + 32 <= p.N;
   const size_t base = (size_t)row * p.N + col0;
+  if (p.planes_hi) {
+    // the value the C store would have held (an fp32 value also when C is fp64), split as launch_tf32_split does
+    float* hi = p.planes_hi + base;
+    __nv_bfloat16* x16 = p.planes_16 + base;
+    __nv_bfloat16* lo16 = x16 + (size_t)p.M * p.N;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      if (col0 + j + 8 > p.N) break;
+      uint32_t wh[8], wx[4], wl[4];
+      float xs[8], ls[8];
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        float x = v[j + t];
+        if (p.act == TC_ACT_RELU) x = x > 0.f ? x : 0.f;
+        else if (p.act == TC_ACT_GELU) x = p.c_dtype == BG_F64 ? gelu_accurate(x) : gelu_graph<float>(x);
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(wh[t]) : "f"(x));
+        xs[t] = x;
+        ls[t] = __fadd_rn(x, -__uint_as_float(wh[t]));
+      }
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(xs[2 * t], xs[2 * t + 1]), l = __floats2bfloat162_rn(ls[2 * t], ls[2 * t + 1]);
+        wx[t] = *reinterpret_cast<uint32_t*>(&a);
+        wl[t] = *reinterpret_cast<uint32_t*>(&l);
+      }
+      st_global_256(hi + j, wh);
+      *reinterpret_cast<uint4*>(x16 + j) = make_uint4(wx[0], wx[1], wx[2], wx[3]);
+      *reinterpret_cast<uint4*>(lo16 + j) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+    }
+    return;
+  }
   const bool al32 = (reinterpret_cast<uintptr_t>(C) & 31) == 0;      // 32-byte stores need the tensor to start on a sector
   if (p.c_dtype == BG_F64 && full && al32 && (p.N & 3) == 0) {
     double* out = reinterpret_cast<double*>(C) + base;
@@ -870,6 +905,8 @@ cudaError_t launch_variant(const TcGemm& g, int* status, cudaStream_t s) {
   p.round_acc = g.round_acc;
   p.wide = g.wide;
   p.status = status;
+  p.planes_hi = reinterpret_cast<float*>(g.planes_hi);
+  p.planes_16 = reinterpret_cast<__nv_bfloat16*>(g.planes_lo);
   p.group_m = 8;
   const uint32_t fmt = TF32 ? 2u : (g.ab_dtype == BG_BF16 ? 1u : 0u);
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -933,6 +970,8 @@ cudaError_t launch_pair(const TcGemm* gs, int n_prob, int* status, cudaStream_t 
   p.round_acc = g.round_acc;
   p.wide = g.wide;
   p.status = status;
+  p.planes_hi = reinterpret_cast<float*>(g.planes_hi);
+  p.planes_16 = reinterpret_cast<__nv_bfloat16*>(g.planes_lo);
   p.group_m = 4;
   p.n_prob = n_prob;
   for (int i = 0; i < kMaxGroup; ++i) { p.Cg[i] = gs[i < n_prob ? i : 0].C; p.biasg[i] = gs[i < n_prob ? i : 0].bias; }

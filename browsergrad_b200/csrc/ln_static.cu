@@ -57,6 +57,23 @@ __device__ __forceinline__ void store4(void* base, int dtype, int64_t elem, cons
   }
 }
 
+// The planes launch_tf32_split makes of the row (tf32(y); bf16(y); bf16(y - tf32(y))), for an output that only feeds
+// split products as their A operand.
+__device__ __forceinline__ void store4_planes(float* hi, __nv_bfloat16* x16, __nv_bfloat16* lo16, int64_t elem, const float* y) {
+  uint32_t h[4];
+  float l[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h[e]) : "f"(y[e]));
+    l[e] = __fadd_rn(y[e], -__uint_as_float(h[e]));
+  }
+  *reinterpret_cast<uint4*>(hi + elem) = make_uint4(h[0], h[1], h[2], h[3]);
+  __nv_bfloat162 a0 = __floats2bfloat162_rn(y[0], y[1]), a1 = __floats2bfloat162_rn(y[2], y[3]);
+  __nv_bfloat162 l0 = __floats2bfloat162_rn(l[0], l[1]), l1 = __floats2bfloat162_rn(l[2], l[3]);
+  *reinterpret_cast<uint2*>(x16 + elem) = make_uint2(*reinterpret_cast<uint32_t*>(&a0), *reinterpret_cast<uint32_t*>(&a1));
+  *reinterpret_cast<uint2*>(lo16 + elem) = make_uint2(*reinterpret_cast<uint32_t*>(&l0), *reinterpret_cast<uint32_t*>(&l1));
+}
+
 __device__ __forceinline__ void store4_sum(float* base, int64_t elem, const float* h) {
   *reinterpret_cast<float4*>(base + elem) = make_float4(h[0], h[1], h[2], h[3]);
 }
@@ -73,7 +90,7 @@ __device__ __forceinline__ float warp_sum(float x) {
 }
 
 // G = float4 groups a lane may hold (cols <= 128 * G)
-template <typename T, int G>
+template <typename T, int G, bool PLANES>
 __global__ void __launch_bounds__(kLnThreads) static_ln_kernel(const __grid_constant__ LnArgs a) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * kLnThreads + threadIdx.x) >> 5;
@@ -145,13 +162,18 @@ __global__ void __launch_bounds__(kLnThreads) static_ln_kernel(const __grid_cons
           const float xh = __fmul_rn(__fadd_rn(x[g][e], -mean), inv);
           y[e] = __fadd_rn(__fmul_rn(xh, w.v[e]), b.v[e]);
         }
-        store4(a.out, a.out_dtype, rbase + (int64_t)grp * 4, y);
+        if constexpr (PLANES) {
+          __nv_bfloat16* x16 = reinterpret_cast<__nv_bfloat16*>(a.planes_lo);
+          store4_planes(reinterpret_cast<float*>(a.planes_hi), x16, x16 + a.rows * a.cols, rbase + (int64_t)grp * 4, y);
+        } else {
+          store4(a.out, a.out_dtype, rbase + (int64_t)grp * 4, y);
+        }
       }
     }
   }
 }
 
-template <typename T>
+template <typename T, bool PLANES>
 cudaError_t launch_t(const LnArgs& a, cudaStream_t s, int sm_count) {
   const int c4 = (int)(a.cols >> 2);
   const int groups = (c4 + 31) / 32;
@@ -159,10 +181,10 @@ cudaError_t launch_t(const LnArgs& a, cudaStream_t s, int sm_count) {
   int64_t grid = (a.rows + warps_per_cta - 1) / warps_per_cta;
   const int64_t cap = (int64_t)sm_count * 8;
   if (grid > cap) grid = cap;
-  if (groups <= 2) static_ln_kernel<T, 2><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
-  else if (groups <= 4) static_ln_kernel<T, 4><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
-  else if (groups <= 6) static_ln_kernel<T, 6><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
-  else static_ln_kernel<T, 8><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
+  if (groups <= 2) static_ln_kernel<T, 2, PLANES><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
+  else if (groups <= 4) static_ln_kernel<T, 4, PLANES><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
+  else if (groups <= 6) static_ln_kernel<T, 6, PLANES><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
+  else static_ln_kernel<T, 8, PLANES><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
   return cudaGetLastError();
 }
 
@@ -172,7 +194,8 @@ bool static_ln_shape_ok(int64_t rows, int64_t cols) { return rows > 0 && cols >=
 
 cudaError_t launch_static_ln(const LnArgs& a, cudaStream_t s, int sm_count) {
   if (!static_ln_shape_ok(a.rows, a.cols) || a.n_terms < 1 || a.n_terms > 4) return cudaErrorInvalidValue;
-  return a.wide ? launch_t<double>(a, s, sm_count) : launch_t<float>(a, s, sm_count);
+  if (a.planes_hi) return a.wide ? launch_t<double, true>(a, s, sm_count) : launch_t<float, true>(a, s, sm_count);
+  return a.wide ? launch_t<double, false>(a, s, sm_count) : launch_t<float, false>(a, s, sm_count);
 }
 
 }  // namespace bg

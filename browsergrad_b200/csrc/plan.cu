@@ -207,6 +207,7 @@ struct ProgramSpec {
   int ln_term[4] = {0, 0, 0, 0};
   int ln_rowvec[4] = {0, 0, 0, 0};
   int ln_sum_out = -1;
+  int ln_planes_hi = -1, ln_planes_lo = -1;   // slots of the normalised rows stored as split-product operand planes
 };
 
 class Compiler {
@@ -284,6 +285,8 @@ class Compiler {
   std::set<int> absorbed_groups_;
   int tc_mode(int n);                      // -1: SIMT; 0: 16-bit operands; 1: 3xTF32
   bool small_gemm(int n, int* splits, int64_t* partial_bytes);   // a 2-D fp32 MATMUL the split-K small kernel takes
+  bool feeds_only_split_gemms(int f);      // every reader of f is the dense A operand of a bf16-plane split product
+  void publish_planes(int f, int hi, int lo, int punit);
   std::string act_expr(int node, int x, int g, int depth);
   void plan_tc_epilogues(const std::map<int, std::vector<int>>& groups);
   std::shared_ptr<CompiledPlan> cp_;
@@ -1667,6 +1670,7 @@ static int run_static_ln(Run& r, const ProgramSpec& ps) {
   a.eps = P.tail_eps;
   a.rows = P.rows;
   a.cols = P.cols;
+  if (ps.ln_planes_hi >= 0) { a.planes_hi = r.ptr[ps.ln_planes_hi]; a.planes_lo = r.ptr[ps.ln_planes_lo]; }
   cudaError_t e = launch_static_ln(a, r.ctx->stream, r.ctx->sm_count);
   if (e != cudaSuccess) return cuda_fail(r.ctx, e, "layer norm kernel launch");
   return BG_OK;
@@ -1714,6 +1718,13 @@ void Compiler::emit_group(const std::vector<int>& members, int tail_node, int ke
       ps->static_arg = arg;
     }
     if (ps->static_pattern < 0) match_static_ln(*ps);
+    if (ps->ln_terms > 0 && tail_node >= 0 && ps->prog.cols % 8 == 0 && feeds_only_split_gemms(tail_node)) {
+      const int64_t n = ps->prog.rows * ps->prog.cols;
+      ps->ln_planes_hi = new_slot(n * 4, false, -1);
+      ps->ln_planes_lo = new_slot(n * 4, false, -1);
+      pu.u.writes.push_back(ps->ln_planes_hi); pu.u.writes.push_back(ps->ln_planes_lo);
+      publish_planes(tail_node, ps->ln_planes_hi, ps->ln_planes_lo, (int)punits_.size());
+    }
   }
   std::ostringstream nm;
   if (ps->static_pattern >= 0 || ps->ln_terms > 0) nm << "static_";
@@ -1722,6 +1733,7 @@ void Compiler::emit_group(const std::vector<int>& members, int tail_node, int ke
   if (members.size() > 6) nm << ",+" << members.size() - 6;
   if (tail_node >= 0) nm << (members.empty() ? "" : "|") << op_name(nodes_[tail_node].op);
   nm << "]";
+  if (ps->ln_planes_hi >= 0) nm << "+split";
   pu.u.name = nm.str();
   pu.u.fn = [ps](Run& r) { return run_program(r, *ps); };
   add_unit(std::move(pu));
@@ -1877,6 +1889,49 @@ int Compiler::tc_mode(int n) {
 static std::string gelu_expr_text() {
   const std::string Z = "mul(c0.797885,add(x,mul(mul(mul(c0.044715,x),x),x)))";
   return "mul(mul(c0.5,x),add(c1,div(add(exp(" + Z + "),neg(exp(neg(" + Z + ")))),add(exp(" + Z + "),exp(neg(" + Z + "))))))";
+}
+
+// True when the value of node f is read by nothing but tensor-core split products that take all of it as their dense
+// [M, K] A operand (through reshapes), K a multiple of 8: the unit that computes f can then store the operand planes
+// of those products (tf32(x); bf16(x); bf16(x - tf32(x))) in place of f itself, and no pass of its own splits f.
+bool Compiler::feeds_only_split_gemms(int f) {
+  if (!ctx_->fusion || !ctx_->static_patterns || f == root_) return false;
+  const View& fv = view_[f];
+  if (fv.is_const || fv.off != 0 || !fv.contiguous() || (fv.dtype != BG_F32 && fv.dtype != BG_F64)) return false;
+  const int64_t numel = fv.numel();
+  bool any = false;
+  std::vector<int> stack{f};
+  std::set<int> seen;
+  while (!stack.empty()) {
+    const int v = stack.back();
+    stack.pop_back();
+    if (!seen.insert(v).second) continue;
+    if (v == root_) return false;
+    for (int c : cons_[v]) {
+      if (kind_[c] == K_DEAD) continue;
+      if (kind_[c] == K_VIEW || kind_[c] == K_ALIAS) {
+        if (view_[c].slot != fv.slot) return false;          // a reshape that became a copy reads f itself
+        stack.push_back(c);
+        continue;
+      }
+      const Node& m = nodes_[c];
+      if (m.op != BG_OP_MATMUL || kind_[c] != K_OTHER || attn_plan_.count(c) || attn_absorbed_.count(c) || tc_mode(c) != 1) return false;
+      const View& av = view_[resolve(m.in[0])];
+      const View& bv = view_[resolve(m.in[1])];
+      if (av.slot != fv.slot || bv.slot == fv.slot) return false;
+      if (av.off != 0 || av.rank != 2 || av.stride[1] != 1 || av.stride[0] != av.shape[1] || av.shape[0] * av.shape[1] != numel ||
+          av.shape[1] % 8 != 0)
+        return false;
+      any = true;
+    }
+  }
+  return any;
+}
+
+// The unit `punit` (being built: the next one added) stores the planes of f: the products that read f find them
+// where they would have looked for a split made by an earlier product of the plan.
+void Compiler::publish_planes(int f, int hi, int lo, int punit) {
+  split_memo_[std::make_tuple(view_[f].slot, (int64_t)0, view_[f].numel())] = {hi, lo, punit};
 }
 
 // A small 2-D fp32 MATMUL (below the tensor-core threshold) runs on the split-K kernel of gemm_simt.cu.
@@ -2395,9 +2450,19 @@ void Compiler::emit_attention(int n, int key) {
   pu.u.name = std::string(ap.mode == 1 ? "attention_tc_3xtf32" : "attention_tc") + (ap.mask >= 0 ? (ap.mask_is_bool ? "+boolmask" : "+mask") : "") +
               (ap.out_node >= 0 ? "+merge" : "") + "[" + dtype_name(fin.dtype) + "]";
   pu.u.launches = 4 + (ap.mask >= 0) + (ap.scale_node >= 0);
+  // a 3xTF32 result that only feeds split products (the output projection) leaves the kernel as their operand planes
+  int planes_hi = -1, planes_lo = -1;
+  if (ap.mode == 1 && feeds_only_split_gemms(out_node)) {
+    const int64_t n_out = nodes_[out_node].numel();
+    planes_hi = new_slot(n_out * 4, false, -1); planes_lo = new_slot(n_out * 4, false, -1);
+    pu.u.writes.push_back(planes_hi); pu.u.writes.push_back(planes_lo);
+    publish_planes(out_node, planes_hi, planes_lo, (int)punits_.size());
+    pu.u.name += "+split";
+  }
   cp_->uses_wait_status = true;
   pu.u.fn = [=](Run& r) {
     AttnProblem a = tmpl;
+    if (planes_hi >= 0) { a.planes_hi = r.ptr[planes_hi]; a.planes_lo = r.ptr[planes_lo]; }
     a.q.ptr = reinterpret_cast<char*>(r.ptr[sq]) + offq;
     a.k.ptr = reinterpret_cast<char*>(r.ptr[sk]) + offk;
     a.v.ptr = reinterpret_cast<char*>(r.ptr[sv]) + offv;
@@ -2600,6 +2665,14 @@ void Compiler::emit_matmul(int n, int key) {
         if (ep.act == TC_ACT_GELU) epi_name += "+gelu";
         pu.out_nodes = {ep.final_node};
       }
+      // a result that only feeds split products leaves this unit as their operand planes
+      int out_hi = -1, out_lo = -1;
+      if (mode == 1 && !gemm_group_of_.count(n) && feeds_only_split_gemms(pu.out_nodes[0])) {
+        out_hi = new_slot(M * N * 4, false, -1); out_lo = new_slot(M * N * 4, false, -1);
+        pu.u.writes.push_back(out_hi); pu.u.writes.push_back(out_lo);
+        publish_planes(pu.out_nodes[0], out_hi, out_lo, (int)punits_.size());
+        epi_name += "+split";
+      }
       pu.u.launches = 1 + (a_copy >= 0) + (b_copy >= 0) + (mode == 1 ? (a_shared ? 0 : 1) + 1 : 0) + (b_f32 >= 0);
       pu.u.name = std::string(mode == 0 ? "gemm_tc" : "gemm_tc_3xtf32") + epi_name + "[" + dtype_name(t.dtype) + "]";
       // member of a joint launch: every member but the last only prepares; the last one launches and produces all results
@@ -2702,6 +2775,7 @@ void Compiler::emit_matmul(int n, int key) {
         g.act = epi->act;
         g.round_acc = epi->round_acc;
         g.wide = epi->wide;
+        if (out_hi >= 0) { g.planes_hi = r.ptr[out_hi]; g.planes_lo = r.ptr[out_lo]; }
         const size_t tmp_bytes = mode == 1 ? 2 * N * K * 4 : N * K * 2;
         if (grun) {
           // a run that stopped between the members leaves their temporary planes behind: the next run's

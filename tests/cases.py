@@ -141,6 +141,24 @@ def _mlp2_inputs() -> Dict[str, np.ndarray]:
             "w2": r.standard_normal((272, 300), dtype=np.float32) / np.float32(17), "b2": r.standard_normal((272,), dtype=np.float32) * np.float32(0.1)}
 
 
+def _split_chain_inputs() -> Dict[str, np.ndarray]:
+    """Two Linears whose hidden width (304) lets the second product take the first one's result as operand planes
+    stored by the producing kernel; rows for a LayerNorm and heads for an attention in front of a projection."""
+    r = _rng(91)
+    out = {"x": r.standard_normal((264, 272), dtype=np.float32), "y": r.standard_normal((264, 272), dtype=np.float32),
+           "w1": r.standard_normal((304, 272), dtype=np.float32) / np.float32(16), "b1": r.standard_normal((304,), dtype=np.float32) * np.float32(0.1),
+           "w2": r.standard_normal((272, 304), dtype=np.float32) / np.float32(17), "b2": r.standard_normal((272,), dtype=np.float32) * np.float32(0.1),
+           "w1t": r.standard_normal((272, 304), dtype=np.float32) / np.float32(16), "w2t": r.standard_normal((304, 280), dtype=np.float32) / np.float32(17),
+           "g": np.linspace(0.5, 1.5, 272, dtype=np.float32), "be": np.linspace(-0.2, 0.2, 272, dtype=np.float32),
+           "wp": r.standard_normal((264, 256), dtype=np.float32) / np.float32(16), "bp": r.standard_normal((264,), dtype=np.float32) * np.float32(0.1)}
+    for name in "qkv":
+        out["w" + name] = r.standard_normal((320, 272), dtype=np.float32) / np.float32(16)
+        out["b" + name] = r.standard_normal((320,), dtype=np.float32) * np.float32(0.1)
+    out.update(configs.attention_inputs(2, 4, 192, 64))
+    out["mask"] = configs.causal_mask(192)
+    return out
+
+
 def _small_gemm_inputs(m: int, n: int, k: int) -> Callable[[], Dict[str, np.ndarray]]:
     def make() -> Dict[str, np.ndarray]:
         r = _rng(79 + m + n + k)
@@ -261,6 +279,19 @@ CASES: Dict[str, Case] = {
                                reference_has_it=False),
     "c3_chain_relu_f32": Case(_mlp2_inputs, lambda api, t, raw: api.linear(api.relu(api.linear(t["x"], t["w1"], t["b1"])), t["w2"], t["b2"])),
     "c3_chain_gelu_f64": Case(_mlp2_inputs, lambda api, t, raw: api.linear(api.gelu(api.linear(t["x"], t["w1"], t["b1"])), t["w2"], t["b2"])),
+    # the hidden value only feeds the next product: the first kernel's epilogue stores its operand planes (tf32(x),
+    # bf16(x), bf16(x - tf32(x))) instead of the value; likewise a LayerNorm and an attention in front of products
+    "c3_chain_relu_planes": Case(_split_chain_inputs, lambda api, t, raw: api.linear(api.relu(api.linear(t["x"], t["w1"], t["b1"])), t["w2"], t["b2"])),
+    "c3_chain_gelu_planes": Case(_split_chain_inputs, lambda api, t, raw: api.linear(api.gelu(api.linear(t["x"], t["w1"], t["b1"])), t["w2"], t["b2"])),
+    "c3_chain_plain_planes": Case(_split_chain_inputs, lambda api, t, raw: (t["x"] @ t["w1t"]) @ t["w2t"]),
+    "c3_chain_two_readers_planes": Case(_split_chain_inputs, lambda api, t, raw: (lambda h: api.cat(
+        [api.linear(h, t["w2"], t["b2"]), h.reshape(2, 132, 304).reshape(264, 304) @ t["w2t"]], 1))(api.gelu(api.linear(t["x"], t["w1"], t["b1"])))),
+    "ln_then_linear_planes": Case(_split_chain_inputs, lambda api, t, raw: api.linear(
+        api.layer_norm(t["x"] + t["y"], (272,), t["g"], t["be"]), t["w1"], t["b1"])),
+    "ln_then_qkv_planes": Case(_split_chain_inputs, lambda api, t, raw: (lambda h: api.cat(
+        [api.linear(h, t["w" + c], t["b" + c]) for c in "qkv"], 1))(api.layer_norm(t["x"] + t["y"], (272,), t["g"], t["be"]))),
+    "c4_attn_proj_planes": Case(_split_chain_inputs, lambda api, t, raw: api.linear(
+        configs.attention(api, t, "mask").permute(0, 2, 1, 3).reshape(2 * 192, 4 * 64), t["wp"], t["bp"])),
     "c3_chain_kept_hidden": Case(_mlp2_inputs, lambda api, t, raw: (lambda h: api.cat([api.linear(h, t["w2"], t["b2"]), h], 1))(
         api.gelu(api.linear(t["x"], t["w1"], t["b1"])))),
     "c4_attn_mask": Case(_attn_small(2, 3, 64, 16),
