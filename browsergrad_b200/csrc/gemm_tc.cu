@@ -123,6 +123,8 @@ __device__ __forceinline__ float load_bias(const void* b, int dt, int col) {
 }
 
 // Epilogue of one 32-column chunk of one accumulator row: rounding, bias, activation, store.
+// SPLIT: the kernel computes split products, whose results may leave as operand planes (p.planes_hi).
+template <bool SPLIT>
 __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t* r, int row, int col0, void* C, const void* bias) {
   float v[32];
 #pragma unroll
@@ -151,7 +153,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
   }
   const bool full = col0 + 32 <= p.N;
   const size_t base = (size_t)row * p.N + col0;
-  if (p.planes_hi) {
+  if (SPLIT && p.planes_hi) {
     // the value the C store would have held (an fp32 value also when C is fp64), split as launch_tf32_split does
     float* hi = p.planes_hi + base;
     __nv_bfloat16* x16 = p.planes_16 + base;
@@ -478,7 +480,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         for (int c = 0; c < NC; ++c) {
           const int cc = half + c * kParts;
           const int col0 = n0 + cc * 32;
-          if (cc < BN / 32 && row < p.M && col0 < p.N) epilogue_chunk(p, reinterpret_cast<const uint32_t*>(acc[c]), row, col0, p.C, p.bias);
+          if (cc < BN / 32 && row < p.M && col0 < p.N) epilogue_chunk<TF32>(p, reinterpret_cast<const uint32_t*>(acc[c]), row, col0, p.C, p.bias);
         }
       } else {
         const int buf = use & 1;
@@ -495,7 +497,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             for (int j = 0; j < 32; ++j) r[j] = 0;
           }
           const int col0 = n0 + c * 32;
-          if (row < p.M && col0 < p.N) epilogue_chunk(p, r, row, col0, p.C, p.bias);
+          if (row < p.M && col0 < p.N) epilogue_chunk<TF32>(p, r, row, col0, p.C, p.bias);
         }
         // the buffer's values are in registers / memory: hand it back to the MMA warp
         tc_fence_before();
@@ -683,7 +685,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         for (int c = 0; c < NC; ++c) {
           const int cc = half + c * kParts;
           const int col0 = n0 + cc * 32;
-          if (cc < TN / 32 && row < p.M && col0 < p.N) epilogue_chunk(p, reinterpret_cast<const uint32_t*>(acc[c]), row, col0, Cp, biasp);
+          if (cc < TN / 32 && row < p.M && col0 < p.N) epilogue_chunk<TF32>(p, reinterpret_cast<const uint32_t*>(acc[c]), row, col0, Cp, biasp);
         }
       } else {
         const int buf = use & 1;
@@ -700,7 +702,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             for (int j = 0; j < 32; ++j) r[j] = 0;
           }
           const int col0 = n0 + c * 32;
-          if (row < p.M && col0 < p.N) epilogue_chunk(p, r, row, col0, Cp, biasp);
+          if (row < p.M && col0 < p.N) epilogue_chunk<TF32>(p, r, row, col0, Cp, biasp);
         }
         tc_fence_before();
         __syncwarp();

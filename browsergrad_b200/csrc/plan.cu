@@ -287,6 +287,9 @@ class Compiler {
   bool small_gemm(int n, int* splits, int64_t* partial_bytes);   // a 2-D fp32 MATMUL the split-K small kernel takes
   bool feeds_only_split_gemms(int f);      // every reader of f is the dense A operand of a bf16-plane split product
   void publish_planes(int f, int hi, int lo, int punit);
+  bool feeds_only_attention32(int f);      // every reader of the fp64 value f is a fused 3xTF32 attention
+  bool narrow_store(int n);                // the fp64 result of tensor-core MATMUL n is stored as the fp32 values it holds
+  std::set<int> narrow32_slots_;           // slots of fp64 nodes that hold fp32 data (read only by the attention kernels)
   std::string act_expr(int node, int x, int g, int depth);
   void plan_tc_epilogues(const std::map<int, std::vector<int>>& groups);
   std::shared_ptr<CompiledPlan> cp_;
@@ -1928,6 +1931,66 @@ bool Compiler::feeds_only_split_gemms(int f) {
   return any;
 }
 
+// True when the fp64 value of node f -- the result of a 3xTF32 product, so every element is an fp32 number -- is read
+// by nothing but fused 3xTF32 attentions (as Q, K or V, through views).  Those kernels compute on fp32: the product
+// then stores fp32 into f's storage and the attention reads fp32 rows, half the bytes on either side and no pass
+// that narrows Q and K.
+bool Compiler::feeds_only_attention32(int f) {
+  if (!ctx_->fusion || !ctx_->static_patterns || f == root_) return false;
+  const View& fv = view_[f];
+  if (fv.is_const || fv.dtype != BG_F64 || fv.off != 0 || !fv.contiguous()) return false;
+  std::vector<int> stack{f};
+  std::set<int> seen;
+  while (!stack.empty()) {
+    const int v = stack.back();
+    stack.pop_back();
+    if (!seen.insert(v).second) continue;
+    if (v == root_) return false;
+    for (int c : cons_[v]) {
+      if (kind_[c] == K_DEAD) continue;
+      if (kind_[c] == K_VIEW || kind_[c] == K_ALIAS) {
+        if (view_[c].slot != fv.slot) return false;
+        stack.push_back(c);
+        continue;
+      }
+      // the Q K^T product inside a fused attention, or its final product (absorbed casts of other kernels are not)
+      const bool inner_product = attn_absorbed_.count(c) && nodes_[c].op == BG_OP_MATMUL;
+      if (!attn_plan_.count(c) && !inner_product) return false;
+    }
+  }
+  bool any = false;
+  for (const auto& kv : attn_plan_) {
+    const AttnPlan& ap = kv.second;
+    const int ops[3] = {ap.q, ap.kt, ap.v};
+    const int srcs[3] = {ap.q_src, ap.kt_src, ap.v_src};
+    for (int i = 0; i < 3; ++i) {
+      if (view_[ops[i]].slot != fv.slot) continue;
+      if (ap.mode != 1 || srcs[i] >= 0) return false;
+      any = true;
+    }
+    if (ap.mask >= 0 && view_[ap.mask].slot == fv.slot) return false;
+    if (ap.scale_node >= 0 && view_[ap.scale_node].slot == fv.slot) return false;
+  }
+  return any;
+}
+
+bool Compiler::narrow_store(int n) {
+  auto final_of = [&](int m) {
+    auto it = epi_plan_.find(m);
+    return it != epi_plan_.end() ? it->second.final_node : m;
+  };
+  auto one = [&](int m) {
+    auto it = epi_plan_.find(m);
+    if (it != epi_plan_.end() && it->second.act != TC_ACT_NONE) return false;
+    return tc_mode(m) == 1 && nodes_[final_of(m)].dtype == BG_F64 && feeds_only_attention32(final_of(m));
+  };
+  auto gi = gemm_group_of_.find(n);
+  if (gi == gemm_group_of_.end()) return one(n);
+  for (int m : gemm_groups_[gi->second].members)     // one store type per joint launch
+    if (!one(m)) return false;
+  return true;
+}
+
 // The unit `punit` (being built: the next one added) stores the planes of f: the products that read f find them
 // where they would have looked for a split made by an earlier product of the plan.
 void Compiler::publish_planes(int f, int hi, int lo, int punit) {
@@ -2393,7 +2456,7 @@ void Compiler::emit_attention(int n, int key) {
   tmpl.mask_is_bool = ap.mask_is_bool;
   auto operand = [&](const View& v, bool swap_last) {
     AttnOperand o{};
-    o.dtype = v.dtype;
+    o.dtype = narrow32_slots_.count(v.slot) ? (int)BG_F32 : v.dtype;   // an fp64 product stored as its fp32 values
     for (int d = 0; d < 4; ++d) o.stride[d] = v.stride[d];
     if (swap_last) std::swap(o.stride[2], o.stride[3]);   // the [B,H,D,Sk] view read as [B,H,Sk,D]
     for (int d = 0; d < 4; ++d)
@@ -2436,6 +2499,7 @@ void Compiler::emit_attention(int n, int key) {
   // an operand whose cast was absorbed is read from the fp32 tensor behind it: same index map, the source's storage
   auto slot_of = [&](const View& v, int src) { return src >= 0 ? view_[src].slot : v.slot; };
   auto off_of = [&](const View& v, int src) {
+    if (src < 0 && narrow32_slots_.count(v.slot)) return v.off * (int64_t)4;
     return src >= 0 ? (view_[src].off + v.off) * (int64_t)4 : v.off * (int64_t)dtype_size(v.dtype);
   };
   const int out_node = ap.out_node >= 0 ? ap.out_node : n;
@@ -2641,7 +2705,8 @@ void Compiler::emit_matmul(int n, int key) {
           pu.u.writes.push_back(b_hi); pu.u.writes.push_back(b_lo);
         }
       }
-      const int a_dt = av.dtype, b_dt = bv.dtype, c_dt = t.dtype;
+      const bool narrow = mode == 1 && narrow_store(n);
+      const int a_dt = av.dtype, b_dt = bv.dtype, c_dt = narrow ? BG_F32 : t.dtype;
       auto epi = std::make_shared<TcEpilogue>();
       tc_epilogues_[n] = epi;
       std::string epi_name;
@@ -2664,6 +2729,11 @@ void Compiler::emit_matmul(int n, int key) {
         if (ep.act == TC_ACT_RELU) epi_name += "+relu";
         if (ep.act == TC_ACT_GELU) epi_name += "+gelu";
         pu.out_nodes = {ep.final_node};
+      }
+      if (narrow) {
+        if (epi->out_slot >= 0) epi->out_dtype = BG_F32;
+        narrow32_slots_.insert(view_[pu.out_nodes[0]].slot);
+        epi_name += "+f32store";
       }
       // a result that only feeds split products leaves this unit as their operand planes
       int out_hi = -1, out_lo = -1;
@@ -3148,6 +3218,7 @@ bool Compiler::try_lower() {
   copy_src_.clear();
   tc_epilogues_.clear();
   split_memo_.clear();
+  narrow32_slots_.clear();
   conv_memo_.clear();
   tc_unit_of_.clear();
   attn_plan_.clear();

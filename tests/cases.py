@@ -159,6 +159,26 @@ def _split_chain_inputs() -> Dict[str, np.ndarray]:
     return out
 
 
+def _f64_block_inputs() -> Dict[str, np.ndarray]:
+    r = _rng(93)
+    out = {"x": r.standard_normal((384, 256), dtype=np.float32), "mask": configs.causal_mask(192),
+           "wp": r.standard_normal((264, 256), dtype=np.float32) / np.float32(16), "bp": r.standard_normal((264,), dtype=np.float32) * np.float32(0.1)}
+    for name in "qkv":
+        out["w" + name] = r.standard_normal((256, 256), dtype=np.float32) / np.float32(16)
+        out["b" + name] = r.standard_normal((256,), dtype=np.float32) * np.float32(0.1)
+    return out
+
+
+def _f64_attention_block(api: Any, t: Dict[str, Any], keep_q: bool = False) -> Any:
+    """q / k / v projections of a float64 activation (the GELU of an fp32 tensor, as after the first MLP of a decoder),
+    heads split by views, attention, heads merged, output projection."""
+    h = api.gelu(t["x"])
+    q, k, v = (api.linear(h, t["w" + c], t["b" + c]).reshape(2, 192, 4, 64).permute(0, 2, 1, 3) for c in "qkv")
+    o = api.scaled_dot_product_attention(q, k, v, attn_mask=t["mask"]).permute(0, 2, 1, 3).reshape(384, 256)
+    out = api.linear(o, t["wp"], t["bp"])
+    return api.cat([out, q.permute(0, 2, 1, 3).reshape(384, 256)], 1) if keep_q else out
+
+
 def _small_gemm_inputs(m: int, n: int, k: int) -> Callable[[], Dict[str, np.ndarray]]:
     def make() -> Dict[str, np.ndarray]:
         r = _rng(79 + m + n + k)
@@ -292,6 +312,10 @@ CASES: Dict[str, Case] = {
         [api.linear(h, t["w" + c], t["b" + c]) for c in "qkv"], 1))(api.layer_norm(t["x"] + t["y"], (272,), t["g"], t["be"]))),
     "c4_attn_proj_planes": Case(_split_chain_inputs, lambda api, t, raw: api.linear(
         configs.attention(api, t, "mask").permute(0, 2, 1, 3).reshape(2 * 192, 4 * 64), t["wp"], t["bp"])),
+    # fp64-typed q / k / v products read by nothing but the attention are stored as the fp32 values they hold; a
+    # projection that something else reads too keeps its fp64 store
+    "c4_attn_block_f64": Case(_f64_block_inputs, lambda api, t, raw: _f64_attention_block(api, t)),
+    "c4_attn_block_f64_kept_q": Case(_f64_block_inputs, lambda api, t, raw: _f64_attention_block(api, t, True)),
     "c3_chain_kept_hidden": Case(_mlp2_inputs, lambda api, t, raw: (lambda h: api.cat([api.linear(h, t["w2"], t["b2"]), h], 1))(
         api.gelu(api.linear(t["x"], t["w1"], t["b1"])))),
     "c4_attn_mask": Case(_attn_small(2, 3, 64, 16),
