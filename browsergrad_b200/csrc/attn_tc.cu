@@ -956,7 +956,7 @@ bool make_map4(CUtensorMap* map, const void* ptr, int dtype, int B, int H, long 
 // [B, H, rows, cols] tensor with element strides sb / sh / ss over batch, head and row (rows of `cols` contiguous
 // values), box = box_cols x box_rows, 128-byte swizzle.
 bool make_map4_strided(CUtensorMap* map, const void* ptr, int dtype, int B, int H, long long rows, long long cols, long long sb,
-                       long long sh, long long ss, int box_cols, int box_rows) {
+                       long long sh, long long ss, int box_cols, int box_rows, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = attn_encode_fn();
   if (!fn) return false;
   const int es = dtype_size(dtype);
@@ -967,7 +967,7 @@ bool make_map4_strided(CUtensorMap* map, const void* ptr, int dtype, int B, int 
   cuuint64_t strides[3] = {(cuuint64_t)ss * es, (cuuint64_t)(sh ? sh : rows * ss) * es, (cuuint64_t)(sb ? sb : rows * ss * H) * es};
   cuuint32_t box[4] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  return fn(map, dt, 4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  return fn(map, dt, 4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -1026,9 +1026,9 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
            o.stride[2] >= a.D && o.stride[0] % 4 == 0 && o.stride[1] % 4 == 0 && o.stride[2] % 4 == 0;
   };
   const bool kv32 = v_mn && p_tmem && (g_attn16_variant & 8) && fp32_rows(a.k) && fp32_rows(a.v);
-  // 3xTF32, one thread per row: fp32 Q and K rows are split into hi / lo planes inside the kernel
+  // 3xTF32, one thread per row: fp32 Q, K and V rows are split into hi / lo planes inside the kernel
   const bool row32 = tf32 && (g_attn32_variant & 1);
-  const bool raw_qk = row32 && (g_attn32_variant & 2) && fp32_rows(a.q) && fp32_rows(a.k) &&
+  const bool raw_qk = row32 && (g_attn32_variant & 2) && fp32_rows(a.q) && fp32_rows(a.k) && fp32_rows(a.v) &&
                       attn_tf32_row_usable(a.Sk, a.out_dtype, a.out, a.out_sb, a.out_sh, a.out_ss, true);
   // operand staging: dense Q, K, V^T (or V) in the kernel's encoding
   const int kind = tf32 ? PREP_TF32 : (a.ab_dtype == BG_F16 ? PREP_F16 : PREP_BF16);
@@ -1051,7 +1051,7 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
       }
     }
     if (kv32 && i > 0) continue;
-    if (raw_qk && i < 2) continue;
+    if (raw_qk) continue;
     // 16-bit operands that are already dense [B,H,S,D] feed the TMA maps directly
     if (!tf32 && as_rows && dense && ops[i]->dtype == a.ab_dtype && aligned) {
       staged[i] = ops[i]->ptr;
@@ -1104,7 +1104,10 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
   CUtensorMap q0, q1, k0, k1, v0, v1;
   if (raw_qk) {
     if (!make_map4_strided(&q0, a.q.ptr, BG_F32, a.B, a.H, a.Sq, a.D, a.q.stride[0], a.q.stride[1], a.q.stride[2], 32, kQRows) ||
-        !make_map4_strided(&k0, a.k.ptr, BG_F32, a.B, a.H, a.Sk, a.D, a.k.stride[0], a.k.stride[1], a.k.stride[2], 32, bkv))
+        !make_map4_strided(&k0, a.k.ptr, BG_F32, a.B, a.H, a.Sk, a.D, a.k.stride[0], a.k.stride[1], a.k.stride[2], 32, bkv) ||
+        // rows of V feed the tensor core as an MN-major operand of 32-bit values: that takes the swizzle of 32-byte pieces
+        !make_map4_strided(&v0, a.v.ptr, BG_F32, a.B, a.H, a.Sk, a.D, a.v.stride[0], a.v.stride[1], a.v.stride[2], 32, bkv,
+                           CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
       return cudaErrorInvalidValue;
   } else if (!pair && !make_map4(&q0, staged[0], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
   if (raw_qk) {
@@ -1113,7 +1116,7 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
         !make_map4_strided(&v0, a.v.ptr, BG_F32, a.B, a.H, a.Sk, a.D, a.v.stride[0], a.v.stride[1], a.v.stride[2], 32, bkv))
       return cudaErrorInvalidValue;
   } else if (!make_map4(&k0, staged[1], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
-  if (kv32) {
+  if (kv32 || raw_qk) {
   } else if (v_mn) {
     if (!make_map4(&v0, staged[2], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
   } else if (!make_map4(&v0, staged[2], sdt, a.B, a.H, a.D, a.Sk, kHeadDim)) return cudaErrorInvalidValue;
@@ -1121,7 +1124,7 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
   if (tf32) {
     if (!raw_qk && !make_map4(&q1, scratch[1], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
     if (!raw_qk && !make_map4(&k1, scratch[3], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
-    if (!make_map4(&v1, scratch[5], sdt, a.B, a.H, a.D, a.Sk, kHeadDim)) return cudaErrorInvalidValue;
+    if (!raw_qk && !make_map4(&v1, scratch[5], sdt, a.B, a.H, a.D, a.Sk, kHeadDim)) return cudaErrorInvalidValue;
   }
   AttnParams p{};
   p.B = a.B; p.H = a.H; p.Sq = a.Sq; p.Sk = a.Sk;

@@ -2,13 +2,14 @@
 // one thread per query row, probabilities and output kept in tensor memory.
 //
 // One CTA owns 128 query rows of one (batch, head) and walks the key tiles (64 keys) that its mask classes keep:
-//   warp 0      producer: lane 0 Q once and the K tiles, lane 1 the V^T tiles (TMA, rings of their own); an operand
-//               arrives pre-split into hi = tf32(x) and lo = x - hi planes, or (RAW) Q and K arrive as the caller's
-//               fp32 rows in the hi planes' places and four converter warps round them in place and write the lo planes
+//   warp 0      producer: lane 0 Q once and the K tiles, lane 1 the V tiles (TMA, rings of their own); an operand
+//               arrives pre-split into hi = tf32(x) and lo = x - hi planes (V transposed: a K-major operand), or (RAW)
+//               Q, K and V arrive as the caller's fp32 rows in the hi planes' places and converter warps round them in
+//               place and write the lo planes (V then stays as rows: an MN-major operand)
 //   warp 1      MMA issuer (all lanes run the loop, an elected lane issues): S = Q K^T as the three products
 //               lo.hi, hi.lo, hi.hi into a double-buffered S; O += P V likewise, with P read from tensor memory
-//   4 warps     softmax (warps 2-5; 4-7 under RAW, where warps 2, 3 idle and 8-11 convert, so that whole warpgroups
-//               trade registers with setmaxnreg): one thread per query row.  A thread reads its 64 scores of a tile once (tcgen05.ld), frees
+//   4 warps     softmax (warps 2-5; 4-7 under RAW, where warps 2, 3 convert V and 8-11 convert Q and K, so that whole
+//               warpgroups trade registers with setmaxnreg): one thread per query row.  A thread reads its 64 scores of a tile once (tcgen05.ld), frees
 //               S at once, takes the row maximum, the exponentials against a lazily raised reference maximum and the
 //               row sum with no exchange between threads, splits the probabilities into hi / lo and stores both
 //               planes to tensor memory (double-buffered: tile t+1's probabilities are written while P.V of tile t
@@ -84,11 +85,12 @@ __device__ __forceinline__ void umma_ts_tf32(uint32_t tmem_d, uint32_t tmem_a, u
 
 // RAW: split the fp32 values that the TMA unit left in a tile's hi planes (`bytes` of them) into hi = tf32(x), in
 // place, and lo = x - hi in the lo planes that follow.  Same offsets in both, so the swizzle does not matter.
+template <int THREADS>
 __device__ __forceinline__ void split_planes(unsigned char* hi_planes, int bytes, int tid) {
   float4* h = reinterpret_cast<float4*>(hi_planes);
   float4* l = reinterpret_cast<float4*>(hi_planes + bytes);
 #pragma unroll 4
-  for (int c = tid; c < bytes / 16; c += 128) {
+  for (int c = tid; c < bytes / 16; c += THREADS) {
     const float4 x = h[c];
     uint32_t a, b, cc, d;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(a) : "f"(x.x));
@@ -99,6 +101,22 @@ __device__ __forceinline__ void split_planes(unsigned char* hi_planes, int bytes
     h[c] = hi;
     l[c] = make_float4(x.x - hi.x, x.y - hi.y, x.z - hi.z, x.w - hi.w);
   }
+}
+
+// RAW: rows of V as an MN-major operand of 32-bit values: a key (K index) is a 128-byte row of 32 head-dimension
+// values, stored with the 128-byte swizzle of 32-byte pieces (the TMA map's SWIZZLE_128B_ATOM_32B, the descriptor's
+// layout type 1), whose pattern repeats every 4 keys = 512 bytes (the stride byte offset); the second half of the head
+// dimension is a tile of its own `kRawVHalf` bytes on (the leading byte offset).  One tf32 instruction (K = 8) reads
+// 8 keys = 1024 bytes from its start address.
+constexpr uint32_t kRawVHalf = 64 * 128;
+__device__ __forceinline__ uint64_t make_v_rows_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(kRawVHalf >> 4) << 16;
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)1 << 61;
+  return d;
 }
 
 template <bool RAW>
@@ -126,7 +144,8 @@ attn_tf32_row_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_cons
   uint64_t* pv_full = p_full + 2;         // [2] its P V has completed
   uint64_t* q_raw = pv_full + 2;          // RAW: the fp32 rows of Q have landed
   uint64_t* k_raw = q_raw + 1;            // [NK] RAW: the fp32 rows of a K tile have landed
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(k_raw + C::NK);
+  uint64_t* v_raw = k_raw + C::NK;        // [NV] RAW: likewise of a V tile
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(v_raw + C::NV);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   unsigned char* s_cls = reinterpret_cast<unsigned char*>(tmem_holder + 4);   // [n_kv] tile classes of this query tile
 
@@ -151,7 +170,7 @@ attn_tf32_row_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_cons
     mbar_init(q_full, RAW ? 4 : 1);       // RAW: the four converter warps publish an operand
     mbar_init(q_raw, 1);
     for (int s = 0; s < C::NK; ++s) { mbar_init(&k_full[s], RAW ? 4 : 1); mbar_init(&k_empty[s], 1); mbar_init(&k_raw[s], 1); }
-    for (int s = 0; s < C::NV; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int s = 0; s < C::NV; ++s) { mbar_init(&v_full[s], RAW ? 2 : 1); mbar_init(&v_empty[s], 1); mbar_init(&v_raw[s], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
       mbar_init(&p_full[i], 4); mbar_init(&pv_full[i], 1);
@@ -205,10 +224,16 @@ attn_tf32_row_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_cons
         const int s = t % C::NV;
         if (!mbar_wait(&v_empty[s], ((uint32_t)(t / C::NV) & 1u) ^ 1u, abort_flag)) break;
         unsigned char* st = sV + s * C::VBytes;
-        mbar_expect_tx(&v_full[s], C::VBytes);
-        for (int kb = 0; kb < 2; ++kb) {
-          tma_load_4d(&tmV0, st + kb * (kHeadDim * 128), &v_full[s], j * BKV + kb * 32, 0, h, b);
-          tma_load_4d(&tmV1, st + (2 + kb) * (kHeadDim * 128), &v_full[s], j * BKV + kb * 32, 0, h, b);
+        if constexpr (RAW) {
+          // rows of V: the two halves of the head dimension as tiles of [64 keys, 32 values]
+          mbar_expect_tx(&v_raw[s], C::VBytes / 2);
+          for (int half = 0; half < 2; ++half) tma_load_4d(&tmV0, st + half * kRawVHalf, &v_raw[s], half * 32, j * BKV, h, b);
+        } else {
+          mbar_expect_tx(&v_full[s], C::VBytes);
+          for (int kb = 0; kb < 2; ++kb) {
+            tma_load_4d(&tmV0, st + kb * (kHeadDim * 128), &v_full[s], j * BKV + kb * 32, 0, h, b);
+            tma_load_4d(&tmV1, st + (2 + kb) * (kHeadDim * 128), &v_full[s], j * BKV + kb * 32, 0, h, b);
+          }
         }
       }
     }
@@ -262,12 +287,18 @@ attn_tf32_row_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_cons
         for (int pass = 0; pass < 3; ++pass) {
           const uint32_t pa = t_p + (pass == 0 ? (uint32_t)BKV : 0u);
           const uint32_t va = v_addr + (pass == 1 ? 2 * (kHeadDim * 128) : 0);
+          if constexpr (RAW) {
 #pragma unroll
-          for (int kb = 0; kb < 2; ++kb) {
-            const uint64_t db = make_kmajor_sw128_desc(va + kb * (kHeadDim * 128));
+            for (int g = 0; g < 8; ++g)      // groups of 8 keys
+              umma_ts_tf32(d_o, pa + (uint32_t)(g * 8), make_v_rows_desc(va + (uint32_t)(g * 1024)), idesc_pv, (pass | g) ? 1u : fresh);
+          } else {
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              umma_ts_tf32(d_o, pa + (uint32_t)(kb * 32 + k * 8), db + (uint64_t)(k * 2), idesc_pv, (pass | kb | k) ? 1u : fresh);
+            for (int kb = 0; kb < 2; ++kb) {
+              const uint64_t db = make_kmajor_sw128_desc(va + kb * (kHeadDim * 128));
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                umma_ts_tf32(d_o, pa + (uint32_t)(kb * 32 + k * 8), db + (uint64_t)(k * 2), idesc_pv, (pass | kb | k) ? 1u : fresh);
+            }
           }
         }
         umma_commit(&pv_full[pbuf]);
@@ -294,7 +325,7 @@ attn_tf32_row_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_cons
     };
     bool ok = __all_sync(0xffffffffu, mbar_wait(q_raw, 0, abort_flag)) != 0;
     if (ok) {
-      split_planes(sQ, C::QBytes / 2, ctid);
+      split_planes<128>(sQ, C::QBytes / 2, ctid);
       publish(q_full);
     }
     int t = 0;
@@ -302,8 +333,22 @@ attn_tf32_row_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_cons
       const int s = t % C::NK;
       ok = __all_sync(0xffffffffu, mbar_wait(&k_raw[s], (uint32_t)(t / C::NK) & 1u, abort_flag)) != 0;
       if (!ok) break;
-      split_planes(sK + s * C::KBytes, C::KBytes / 2, ctid);
+      split_planes<128>(sK + s * C::KBytes, C::KBytes / 2, ctid);
       publish(&k_full[s]);
+    }
+  } else if (RAW && warp >= 2 && warp < 4) {
+    // converters of the V tiles
+    const int ctid = (int)threadIdx.x - 64;
+    bool ok = true;
+    int t = 0;
+    for (int j = next_tile(0); j < n_kv && ok; j = next_tile(j + 1), ++t) {
+      const int s = t % C::NV;
+      ok = __all_sync(0xffffffffu, mbar_wait(&v_raw[s], (uint32_t)(t / C::NV) & 1u, abort_flag)) != 0;
+      if (!ok) break;
+      split_planes<64>(sV + s * C::VBytes, C::VBytes / 2, ctid);
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&v_full[s]);
     }
   }
   } else {
@@ -531,6 +576,8 @@ static cudaError_t launch_row(const attn::AttnParams& p, const CUtensorMap maps[
   using C = RowCfg<RAW>;
   const size_t smem = (size_t)C::SmemBytes + 256 + 1024 + n_kv;
   auto kern = attn_tf32_row_kernel<RAW>;
+  attn::AttnParams pr = p;
+  if (RAW) pr.idesc_pv |= 1u << 16;         // V rows: the B operand of P V is MN-major
   if (RAW) {
     cudaFuncAttributes fa;
     cudaError_t e = cudaFuncGetAttributes(&fa, kern);
@@ -539,7 +586,7 @@ static cudaError_t launch_row(const attn::AttnParams& p, const CUtensorMap maps[
   }
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  kern<<<dim3(n_cta), C::Threads, smem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
+  kern<<<dim3(n_cta), C::Threads, smem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], pr);
   return cudaGetLastError();
 }
 
