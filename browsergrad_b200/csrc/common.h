@@ -168,6 +168,10 @@ struct LnArgs {
   // non-null: `out` is not written; the rows are stored as the planes launch_tf32_split(out, ...) would have made
   void* planes_hi;
   void* planes_lo;
+  // non-null: `out` is not written; the rows are stored rounded to out16_dtype (BG_F16 / BG_BF16), as a CAST of `out`
+  // would have given
+  void* out16;
+  int32_t out16_dtype;
 };
 bool static_ln_shape_ok(int64_t rows, int64_t cols);
 cudaError_t launch_static_ln(const LnArgs& a, cudaStream_t s, int sm_count);

@@ -90,7 +90,8 @@ __device__ __forceinline__ float warp_sum(float x) {
 }
 
 // G = float4 groups a lane may hold (cols <= 128 * G)
-template <typename T, int G, bool PLANES>
+// OUT: 0 the rows in out_dtype, 1 split-product operand planes, 2 the rows rounded to f16 / bf16 (out16_dtype)
+template <typename T, int G, int OUT>
 __global__ void __launch_bounds__(kLnThreads) static_ln_kernel(const __grid_constant__ LnArgs a) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * kLnThreads + threadIdx.x) >> 5;
@@ -162,9 +163,20 @@ __global__ void __launch_bounds__(kLnThreads) static_ln_kernel(const __grid_cons
           const float xh = __fmul_rn(__fadd_rn(x[g][e], -mean), inv);
           y[e] = __fadd_rn(__fmul_rn(xh, w.v[e]), b.v[e]);
         }
-        if constexpr (PLANES) {
+        if constexpr (OUT == 1) {
           __nv_bfloat16* x16 = reinterpret_cast<__nv_bfloat16*>(a.planes_lo);
           store4_planes(reinterpret_cast<float*>(a.planes_hi), x16, x16 + a.rows * a.cols, rbase + (int64_t)grp * 4, y);
+        } else if constexpr (OUT == 2) {
+          // the value an fp32 / fp64 store followed by a CAST to the 16-bit type would give: y is an fp32 number
+          uint2 w;
+          if (a.out16_dtype == BG_BF16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
+            w = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+          } else {
+            __half2 lo = __floats2half2_rn(y[0], y[1]), hi = __floats2half2_rn(y[2], y[3]);
+            w = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+          }
+          *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.out16) + rbase + (int64_t)grp * 4) = w;
         } else {
           store4(a.out, a.out_dtype, rbase + (int64_t)grp * 4, y);
         }
@@ -173,7 +185,7 @@ __global__ void __launch_bounds__(kLnThreads) static_ln_kernel(const __grid_cons
   }
 }
 
-template <typename T, bool PLANES>
+template <typename T, int OUT>
 cudaError_t launch_t(const LnArgs& a, cudaStream_t s, int sm_count) {
   const int c4 = (int)(a.cols >> 2);
   const int groups = (c4 + 31) / 32;
@@ -181,10 +193,10 @@ cudaError_t launch_t(const LnArgs& a, cudaStream_t s, int sm_count) {
   int64_t grid = (a.rows + warps_per_cta - 1) / warps_per_cta;
   const int64_t cap = (int64_t)sm_count * 8;
   if (grid > cap) grid = cap;
-  if (groups <= 2) static_ln_kernel<T, 2, PLANES><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
-  else if (groups <= 4) static_ln_kernel<T, 4, PLANES><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
-  else if (groups <= 6) static_ln_kernel<T, 6, PLANES><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
-  else static_ln_kernel<T, 8, PLANES><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
+  if (groups <= 2) static_ln_kernel<T, 2, OUT><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
+  else if (groups <= 4) static_ln_kernel<T, 4, OUT><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
+  else if (groups <= 6) static_ln_kernel<T, 6, OUT><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
+  else static_ln_kernel<T, 8, OUT><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
   return cudaGetLastError();
 }
 
@@ -194,8 +206,9 @@ bool static_ln_shape_ok(int64_t rows, int64_t cols) { return rows > 0 && cols >=
 
 cudaError_t launch_static_ln(const LnArgs& a, cudaStream_t s, int sm_count) {
   if (!static_ln_shape_ok(a.rows, a.cols) || a.n_terms < 1 || a.n_terms > 4) return cudaErrorInvalidValue;
-  if (a.planes_hi) return a.wide ? launch_t<double, true>(a, s, sm_count) : launch_t<float, true>(a, s, sm_count);
-  return a.wide ? launch_t<double, false>(a, s, sm_count) : launch_t<float, false>(a, s, sm_count);
+  if (a.planes_hi) return a.wide ? launch_t<double, 1>(a, s, sm_count) : launch_t<float, 1>(a, s, sm_count);
+  if (a.out16) return a.wide ? launch_t<double, 2>(a, s, sm_count) : launch_t<float, 2>(a, s, sm_count);
+  return a.wide ? launch_t<double, 0>(a, s, sm_count) : launch_t<float, 0>(a, s, sm_count);
 }
 
 }  // namespace bg

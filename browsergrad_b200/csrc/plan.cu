@@ -208,6 +208,7 @@ struct ProgramSpec {
   int ln_rowvec[4] = {0, 0, 0, 0};
   int ln_sum_out = -1;
   int ln_planes_hi = -1, ln_planes_lo = -1;   // slots of the normalised rows stored as split-product operand planes
+  int ln_out16 = -1, ln_out16_dtype = 0;      // slot of the normalised rows stored in the 16-bit type of the GEMMs that read them
 };
 
 class Compiler {
@@ -287,6 +288,7 @@ class Compiler {
   bool small_gemm(int n, int* splits, int64_t* partial_bytes);   // a 2-D fp32 MATMUL the split-K small kernel takes
   bool feeds_only_split_gemms(int f);      // every reader of f is the dense A operand of a bf16-plane split product
   void publish_planes(int f, int hi, int lo, int punit);
+  bool feeds_only_convert16(int f, int* dtype16);   // every reader of f is the absorbed 16-bit CAST of a GEMM's A operand
   bool feeds_only_attention32(int f);      // every reader of the fp64 value f is a fused 3xTF32 attention
   bool narrow_store(int n);                // the fp64 result of tensor-core MATMUL n is stored as the fp32 values it holds
   std::set<int> narrow32_slots_;           // slots of fp64 nodes that hold fp32 data (read only by the attention kernels)
@@ -1674,6 +1676,7 @@ static int run_static_ln(Run& r, const ProgramSpec& ps) {
   a.rows = P.rows;
   a.cols = P.cols;
   if (ps.ln_planes_hi >= 0) { a.planes_hi = r.ptr[ps.ln_planes_hi]; a.planes_lo = r.ptr[ps.ln_planes_lo]; }
+  if (ps.ln_out16 >= 0) { a.out16 = r.ptr[ps.ln_out16]; a.out16_dtype = ps.ln_out16_dtype; }
   cudaError_t e = launch_static_ln(a, r.ctx->stream, r.ctx->sm_count);
   if (e != cudaSuccess) return cuda_fail(r.ctx, e, "layer norm kernel launch");
   return BG_OK;
@@ -1728,6 +1731,14 @@ void Compiler::emit_group(const std::vector<int>& members, int tail_node, int ke
       pu.u.writes.push_back(ps->ln_planes_hi); pu.u.writes.push_back(ps->ln_planes_lo);
       publish_planes(tail_node, ps->ln_planes_hi, ps->ln_planes_lo, (int)punits_.size());
     }
+    int dt16 = 0;
+    if (ps->ln_terms > 0 && tail_node >= 0 && ps->ln_planes_hi < 0 && feeds_only_convert16(tail_node, &dt16)) {
+      const int64_t n = ps->prog.rows * ps->prog.cols;
+      ps->ln_out16 = new_slot(n * 2, false, -1);
+      ps->ln_out16_dtype = dt16;
+      pu.u.writes.push_back(ps->ln_out16);
+      conv_memo_[std::make_tuple(view_[tail_node].slot, (int64_t)0, n, dt16)] = {ps->ln_out16, (int)punits_.size()};
+    }
   }
   std::ostringstream nm;
   if (ps->static_pattern >= 0 || ps->ln_terms > 0) nm << "static_";
@@ -1737,6 +1748,7 @@ void Compiler::emit_group(const std::vector<int>& members, int tail_node, int ke
   if (tail_node >= 0) nm << (members.empty() ? "" : "|") << op_name(nodes_[tail_node].op);
   nm << "]";
   if (ps->ln_planes_hi >= 0) nm << "+split";
+  if (ps->ln_out16 >= 0) nm << "+cast16";
   pu.u.name = nm.str();
   pu.u.fn = [ps](Run& r) { return run_program(r, *ps); };
   add_unit(std::move(pu));
@@ -1929,6 +1941,51 @@ bool Compiler::feeds_only_split_gemms(int f) {
     }
   }
   return any;
+}
+
+// True when the fp32 / fp64 value of node f is read by nothing but CASTs to one 16-bit type that tensor-core GEMMs
+// absorbed as the conversion of their dense A operand (autocast Linears after a LayerNorm): the unit that computes f
+// can then store the 16-bit rows itself, registered where those GEMMs look for an activation already converted.
+bool Compiler::feeds_only_convert16(int f, int* dtype16) {
+  if (!ctx_->fusion || !ctx_->static_patterns || f == root_) return false;
+  const View& fv = view_[f];
+  if (fv.is_const || fv.off != 0 || !fv.contiguous() || (fv.dtype != BG_F32 && fv.dtype != BG_F64)) return false;
+  const int64_t numel = fv.numel();
+  // the casts that GEMMs of this plan absorbed as conversions of all of f
+  std::set<int> a_casts;
+  int dt = -1;
+  for (const auto& kv : gemm_cast_src_) {
+    const int n = kv.first, sa = kv.second.first;
+    if (sa < 0 || view_[sa].slot != fv.slot) continue;
+    const int a = resolve(nodes_[n].in[0]);
+    const View& av = view_[a];
+    int ca = -1;
+    if (absorbable_cast(a, av.dtype, ca, true) != sa || ca < 0) return false;
+    if (view_[sa].off + av.off != 0 || av.rank != 2 || av.shape[0] * av.shape[1] != numel || numel % 8 != 0) return false;
+    if (dt >= 0 && dt != av.dtype) return false;
+    dt = av.dtype;
+    a_casts.insert(ca);
+  }
+  if (a_casts.empty()) return false;
+  std::vector<int> stack{f};
+  std::set<int> seen;
+  while (!stack.empty()) {
+    const int v = stack.back();
+    stack.pop_back();
+    if (!seen.insert(v).second) continue;
+    if (v == root_) return false;
+    for (int c : cons_[v]) {
+      if (kind_[c] == K_DEAD) continue;
+      if (kind_[c] == K_VIEW || kind_[c] == K_ALIAS) {
+        if (view_[c].slot != fv.slot) return false;
+        stack.push_back(c);
+        continue;
+      }
+      if (!a_casts.count(c)) return false;
+    }
+  }
+  *dtype16 = dt;
+  return true;
 }
 
 // True when the fp64 value of node f -- the result of a 3xTF32 product, so every element is an fp32 number -- is read

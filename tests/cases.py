@@ -179,6 +179,13 @@ def _f64_attention_block(api: Any, t: Dict[str, Any], keep_q: bool = False) -> A
     return api.cat([out, q.permute(0, 2, 1, 3).reshape(384, 256)], 1) if keep_q else out
 
 
+def _ln_qkv_amp(api: Any, t: Dict[str, Any], amp: str, keep: bool) -> Any:
+    with api.autocast(dtype=amp):
+        h = api.layer_norm(t["x"] + t["y"], (272,), t["g"], t["be"])
+        out = api.cat([api.linear(h, t["w" + c], t["b" + c]) for c in "qkv"], 1)
+        return api.cat([out, h], 1) if keep else out
+
+
 def _small_gemm_inputs(m: int, n: int, k: int) -> Callable[[], Dict[str, np.ndarray]]:
     def make() -> Dict[str, np.ndarray]:
         r = _rng(79 + m + n + k)
@@ -312,6 +319,12 @@ CASES: Dict[str, Case] = {
         [api.linear(h, t["w" + c], t["b" + c]) for c in "qkv"], 1))(api.layer_norm(t["x"] + t["y"], (272,), t["g"], t["be"]))),
     "c4_attn_proj_planes": Case(_split_chain_inputs, lambda api, t, raw: api.linear(
         configs.attention(api, t, "mask").permute(0, 2, 1, 3).reshape(2 * 192, 4 * 64), t["wp"], t["bp"])),
+    # autocast: a LayerNorm whose rows only feed Linears stores them in the 16-bit type itself; one that something else
+    # reads too keeps its fp32 store and the conversion pass
+    "ln_then_qkv_f16": Case(_split_chain_inputs, lambda api, t, raw: _ln_qkv_amp(api, t, "float16", False), rtol=2e-2),
+    "ln_then_qkv_bf16": Case(_split_chain_inputs, lambda api, t, raw: _ln_qkv_amp(api, t, "bfloat16", False), rtol=2e-2,
+                             reference_has_it=False),
+    "ln_then_qkv_f16_kept": Case(_split_chain_inputs, lambda api, t, raw: _ln_qkv_amp(api, t, "float16", True), rtol=2e-2),
     # fp64-typed q / k / v products read by nothing but the attention are stored as the fp32 values they hold; a
     # projection that something else reads too keeps its fp64 store
     "c4_attn_block_f64": Case(_f64_block_inputs, lambda api, t, raw: _f64_attention_block(api, t)),

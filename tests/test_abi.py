@@ -78,7 +78,8 @@ def test_full_size_config2_takes_the_pattern_kernels():
 def test_autocast_decoder_block_leaves_nothing_on_the_interpreter():
     """The casts the AMP pass inserts around every MATMUL are removed or absorbed by the plan compiler: a decoder block
     built under autocast lowers to tensor-core GEMMs (bias + GELU + narrowing cast in the epilogue, q / k / v as one
-    grid), the fused attention, the specialised LayerNorm kernel and one conversion per activation."""
+    grid), the fused attention and the specialised LayerNorm kernel, which stores its rows in the 16-bit type the next
+    Linears read (no conversion pass of its own)."""
     import collections
     from browsergrad_b200 import configs, graph
     arrays = configs.gpt_inputs(layers=2, batch=8)
@@ -92,7 +93,8 @@ def test_autocast_decoder_block_leaves_nothing_on_the_interpreter():
         units = collections.Counter(lines)
         assert not any(ln.startswith(("ew[", "row[")) for ln in lines), units
         assert units[f"gemm_tc+bias+gelu[{amp}]"] == 2 and units[f"gemm_tc+bias[{amp}] x3"] == 2, units
-        assert units[f"attention_tc+mask+merge[{amp}]"] == 2 and units["static_row[CAST,ADD,ADD|LAYER_NORM]"] == 4, units
+        assert units[f"attention_tc+mask+merge[{amp}]"] == 2 and units["static_row[CAST,ADD,ADD|LAYER_NORM]+cast16"] == 4, units
+        assert not any(ln.startswith("convert16") for ln in lines), units
 
 
 def test_small_fp32_products_take_the_split_k_kernel_with_their_epilogue():
