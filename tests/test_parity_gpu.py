@@ -139,7 +139,9 @@ def test_every_16bit_attention_kernel_matches_oracle(bridge, name, variant):
 
 
 ATTN32_CASES = ["c4_attn_mask_d64", "c4_attn_causal_d64", "c4_attn_causal_tiles", "c4_attn_mask_tiles", "c4_attn_nomask_d64",
-                "typed_attention_d64", "c4_attn_merge_heads", "c4_attn_growing_f32", "c4_attn_long_f32"]
+                "typed_attention_d64", "c4_attn_merge_heads", "c4_attn_growing_f32", "c4_attn_long_f32",
+                # results stored as operand planes of the projection behind them; fp64-typed q / k / v stored as fp32
+                "c4_attn_proj_planes", "c4_attn_block_f64"]
 
 
 @pytest.mark.parametrize("variant", [0, 1, 3])
