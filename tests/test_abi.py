@@ -110,6 +110,36 @@ def test_small_fp32_products_take_the_split_k_kernel_with_their_epilogue():
             assert lines == ["gemm_small+bias+relu[float32]", "gemm_small+bias[float32]", "cross_entropy"], lines
 
 
+def test_values_read_only_by_products_leave_their_producer_in_the_operand_format():
+    """A value that nothing but split products read (as their dense A operand, K a multiple of 8) is stored by its
+    producer as those products' operand planes (+split); LayerNorm rows that only autocast Linears read are stored in
+    their 16-bit type (+cast16, no convert16 unit); fp64-typed products that only a fused fp32 attention reads are
+    stored as the fp32 numbers they hold (+f32store).  A second reader of another kind keeps the plain store."""
+    expect = {
+        "c3_chain_relu_planes": ["gemm_tc_3xtf32+bias+relu+split[float32]", "gemm_tc_3xtf32+bias[float32]"],
+        "c3_chain_gelu_planes": ["gemm_tc_3xtf32+bias+gelu+split[float32]", "gemm_tc_3xtf32+bias[float64]"],
+        "c3_chain_plain_planes": ["gemm_tc_3xtf32+split[float32]", "gemm_tc_3xtf32[float32]"],
+        "c3_chain_gelu_f64": ["gemm_tc_3xtf32+bias+gelu[float32]", "gemm_tc_3xtf32+bias[float64]"],     # K = 300: fp32 residual planes
+        "c3_chain_kept_hidden": ["gemm_tc_3xtf32+bias+gelu[float32]", "gemm_tc_3xtf32+bias[float64]", "place[CONCAT]"],
+        "ln_then_linear_planes": ["static_row[ADD|LAYER_NORM]+split", "gemm_tc_3xtf32+bias[float32]"],
+        "c4_attn_proj_planes": ["attention_tc_3xtf32+mask+merge[float32]+split", "gemm_tc_3xtf32+bias[float32]"],
+    }
+    for name, want in expect.items():
+        t, _, _ = build_case(CASES[name])
+        _, plan = front.plan_for(t._uop)
+        rc, lines = dry(plan, fusion=3)
+        assert rc == 0 and lines == want, (name, lines)
+    for name, has, has_not in (("ln_then_qkv_planes", "static_row[ADD|LAYER_NORM]+split", "split["),
+                               ("ln_then_qkv_f16", "static_row[ADD|LAYER_NORM]+cast16", "convert16"),
+                               ("ln_then_qkv_f16_kept", "convert16[float16]", "+cast16"),
+                               ("c4_attn_block_f64", "gemm_tc_3xtf32+bias+f32store[float64]", "convert16"),
+                               ("c4_attn_block_f64_kept_q", "gemm_tc_3xtf32+bias[float64] x2", "convert16")):
+        t, _, _ = build_case(CASES[name])
+        _, plan = front.plan_for(t._uop)
+        rc, lines = dry(plan, fusion=3)
+        assert rc == 0 and has in lines and not any(has_not in ln for ln in lines), (name, lines)
+
+
 def test_unsupported_opcode_mentions_numpy_fallback():
     plan = {"step_count": 1, "root_id": 0, "steps": [
         {"step": 0, "value_id": 0, "op": "CONV2D", "input_ids": [], "shape": [1], "dtype": "float32", "arg": None}]}
