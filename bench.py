@@ -219,7 +219,9 @@ EXTRA_WARMUP = 3   # untimed realizations before each extra workload; a profiler
 
 def time_plan(bridge, torch, stream, graph_root, store, front, steps: int, warmup: int = -1):
     """Average device time (ms) of one realization with resident leaves, plus the per-kernel profile.
-    The plan is timed without per-unit events; the profile comes from a second pass of the same length."""
+    The plan is timed without per-unit events; the profile comes from runs with them.  Blocks of timed runs
+    alternate with single profiled runs, so that both see the same clocks (a long run of GEMMs settles from its burst clock
+    to the sustained one: a profile taken only after the timed steps reported units slower than their whole plan)."""
     prepared, plan = front.plan_for(graph_root._uop)
     table = front.DeviceBufferTable(bridge)
     inputs = front._bind_inputs(plan, store, table, True)
@@ -227,20 +229,25 @@ def time_plan(bridge, torch, stream, graph_root, store, front, steps: int, warmu
         bridge.release(bridge.run_tensor_plan_resident(plan, inputs, prepared.dtype))
     bridge.synchronize()
     bridge.flushProfiles()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(steps):
+    n_blocks = max(1, min(steps, 5))
+    per = (steps + n_blocks - 1) // n_blocks
+    pairs = []
+    for _ in range(n_blocks):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(per):
+            bridge.release(bridge.run_tensor_plan_resident(plan, inputs, prepared.dtype))
+        e1.record(stream)
+        pairs.append((e0, e1))
+        bridge.set_option("profiling", 1)      # one profiled run per block
         bridge.release(bridge.run_tensor_plan_resident(plan, inputs, prepared.dtype))
-    e1.record(stream)
+        bridge.set_option("profiling", 0)
     bridge.synchronize()
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / steps
-    bridge.set_option("profiling", 1)
-    for _ in range(steps):
-        bridge.release(bridge.run_tensor_plan_resident(plan, inputs, prepared.dtype))
-    bridge.synchronize()
+    ms = sum(a.elapsed_time(b) for a, b in pairs) / (n_blocks * per)
     prof = bridge.flushProfiles()
-    bridge.set_option("profiling", 0)
+    for p in prof:
+        p["runs"] = n_blocks                # forwards the profile covers
     trace = bridge.last_plan_trace()
     table.release_all()
     return ms, prof, trace
@@ -299,10 +306,9 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn
         t = {k: graph.from_numpy(v, store) for k, v in arrays.items()}
         root = configs.mlp_loss(graph, t)
         ms, prof, trace = time_plan(bridge, torch, stream, root, store, front, max(steps, 20))
-        n_prof = max(steps, 20)
         out["mlp"].append({"workload": "MLP 784-128(ReLU)-10 + cross entropy, batch 64, fp32", "us_per_forward": ms * 1e3,
                            "kernels": trace,
-                           "kernel_us": {p["name"]: 1e3 * p["ms"] / n_prof for p in prof},
+                           "kernel_us": {p["name"]: 1e3 * p["ms"] / p["runs"] for p in prof},
                            "note": "us_per_forward is the time between back-to-back forwards on the stream (host submission "
                                    "included when it is the slower side); kernel_us are the units' own device times"})
         del arrays, store, t
@@ -416,7 +422,7 @@ def extra_measurements(bridge, torch, stream, peaks, steps: int, only=None, attn
             top = sorted(prof, key=lambda p: -p["ms"])[:6]
             out["gpt"].append({"workload": f"GPT decoder forward 12L d768 h12 mlp3072 V32000 seq1024, batch 8 (one GPU's shard of 64), {label}",
                                "tokens_per_s": 8 * 1024 / (ms * 1e-3), "plan_ms": ms, "units": len(trace),
-                               "top_kernels": [{"name": p["name"], "ms_per_forward": p["ms"] / gpt_steps} for p in top]})
+                               "top_kernels": [{"name": p["name"], "ms_per_forward": p["ms"] / p["runs"]} for p in top]})
         del arrays, store, t
     return out
 

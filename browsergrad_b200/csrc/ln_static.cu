@@ -10,9 +10,10 @@
 // the statistics are fp32 over f32(h), the reference's rule for LAYER_NORM
 // (packages/browsergrad-jit/src/python/_realize.py:1384-1402 casts the row to float32 first).
 //
-// One warp owns one row: a lane keeps cols/32 values in registers, so a row is read from HBM once
-// and written once, the two reductions are shuffles, and no block-wide barrier is needed.  All
-// loads of one term's row share are independent, so many are in flight per lane.
+// One CTA owns one row at a time and a thread four of its values, so a row is read from HBM once and written once.
+// (A warp per row, each lane holding cols / 32 values, ran at 0.6 of the copy bandwidth: each load sits behind the
+// type switch of its term, so a lane waited out some thirty memory round trips one after another, with too few warps
+// resident to hide them.)
 #include "common.h"
 
 #include <cuda_bf16.h>
@@ -21,7 +22,6 @@
 namespace bg {
 namespace {
 
-constexpr int kLnThreads = 256;
 
 template <typename T> struct Vec4 { T v[4]; };
 
@@ -74,6 +74,47 @@ __device__ __forceinline__ void store4_planes(float* hi, __nv_bfloat16* x16, __n
   *reinterpret_cast<uint2*>(lo16 + elem) = make_uint2(*reinterpret_cast<uint32_t*>(&l0), *reinterpret_cast<uint32_t*>(&l1));
 }
 
+// Four fp32 or 16-bit values of a term as raw bytes: the type switch holds nothing but the loads themselves
+// (predicated loads, no use of the data), so the loads of several terms are in flight together; load4 converts inside
+// the switch, which makes a thread wait for each load before it issues the next.
+__device__ __forceinline__ uint4 load_raw4(const void* base, int dtype, int64_t elem) {
+  uint4 r = make_uint4(0u, 0u, 0u, 0u);
+  if (dtype == BG_F32) {
+    r = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(base) + elem));
+  } else {
+    const uint2 h = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(base) + elem));
+    r.x = h.x;
+    r.y = h.y;
+  }
+  return r;
+}
+__device__ __forceinline__ Vec4<float> convert_raw4(const uint4& r, int dtype) {
+  Vec4<float> o;
+  if (dtype == BG_F32) {
+    o.v[0] = __uint_as_float(r.x); o.v[1] = __uint_as_float(r.y); o.v[2] = __uint_as_float(r.z); o.v[3] = __uint_as_float(r.w);
+  } else if (dtype == BG_F16) {
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&r.x)), hi = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+    o.v[0] = lo.x; o.v[1] = lo.y; o.v[2] = hi.x; o.v[3] = hi.y;
+  } else {
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x)), hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    o.v[0] = lo.x; o.v[1] = lo.y; o.v[2] = hi.x; o.v[3] = hi.y;
+  }
+  return o;
+}
+
+// The value an fp32 / fp64 store followed by a CAST to the 16-bit type would give: y is an fp32 number.
+__device__ __forceinline__ void store4_16(void* base, int dtype16, int64_t elem, const float* y) {
+  uint2 w;
+  if (dtype16 == BG_BF16) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
+    w = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+  } else {
+    __half2 lo = __floats2half2_rn(y[0], y[1]), hi = __floats2half2_rn(y[2], y[3]);
+    w = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+  }
+  *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(base) + elem) = w;
+}
+
 __device__ __forceinline__ void store4_sum(float* base, int64_t elem, const float* h) {
   *reinterpret_cast<float4*>(base + elem) = make_float4(h[0], h[1], h[2], h[3]);
 }
@@ -91,95 +132,96 @@ __device__ __forceinline__ float warp_sum(float x) {
 
 // G = float4 groups a lane may hold (cols <= 128 * G)
 // OUT: 0 the rows in out_dtype, 1 split-product operand planes, 2 the rows rounded to f16 / bf16 (out16_dtype)
-template <typename T, int G, int OUT>
-__global__ void __launch_bounds__(kLnThreads) static_ln_kernel(const __grid_constant__ LnArgs a) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warp = ((int64_t)blockIdx.x * kLnThreads + threadIdx.x) >> 5;
-  const int64_t n_warps = ((int64_t)gridDim.x * kLnThreads) >> 5;
+// One CTA per row, one float4 group per thread (cols / 4 threads, rounded up to whole warps): a thread holds four
+// values, so some sixty warps are resident per SM and the loads of a row -- each behind the type switch of its term --
+// overlap across warps instead of queueing up in one lane.  The two statistics are reduced by shuffles inside a warp
+// and through shared memory across the warps (every thread adds the warps' partial sums in the same order, so all agree
+// on the bits); two scratch rows alternate, so a row costs two barriers.  gamma and beta are read once per CTA.
+template <typename T, int OUT>
+__global__ void __launch_bounds__(256) static_ln_cta_kernel(const __grid_constant__ LnArgs a) {
+  __shared__ float red_sum[2][8], red_sq[2][8];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int c4 = (int)(a.cols >> 2);
-  for (int64_t row = warp; row < a.rows; row += n_warps) {
-    const int64_t rbase = row * a.cols;
-    T h[G][4];
+  const int grp = threadIdx.x;
+  const bool on = grp < c4;
+  Vec4<float> w, b;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const int grp = g * 32 + lane;
-      if (grp < c4) {
-        const Vec4<T> t = load4<T>(a.term[0], a.term_dtype[0], (a.term_rowvec[0] ? 0 : rbase) + (int64_t)grp * 4);
+  for (int e = 0; e < 4; ++e) { w.v[e] = 0.f; b.v[e] = 0.f; }
+  if (on) {
+    w = load4<float>(a.w, a.w_dtype, (int64_t)grp * 4);
+    b = load4<float>(a.b, a.b_dtype, (int64_t)grp * 4);
+  }
+  int flip = 0;
+  for (int64_t row = blockIdx.x; row < a.rows; row += gridDim.x, flip ^= 1) {
+    const int64_t at = row * a.cols + (int64_t)grp * 4;
+    float x[4] = {0.f, 0.f, 0.f, 0.f};
+    if (on) {
+      T h[4];
+      if constexpr (sizeof(T) == 4) {
+        // fp32 sums move few bytes per load (a 16-bit or fp32 term): all terms' loads are issued before the first use
+        uint4 raw[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) h[g][e] = t.v[e];
-      }
-    }
+        for (int k = 0; k < 4; ++k)
+          if (k < a.n_terms) raw[k] = load_raw4(a.term[k], a.term_dtype[k], a.term_rowvec[k] ? (int64_t)grp * 4 : at);
+        {
+          const Vec4<float> t = convert_raw4(raw[0], a.term_dtype[0]);
 #pragma unroll
-    for (int k = 1; k < 4; ++k) {
-      if (k < a.n_terms) {
+          for (int e = 0; e < 4; ++e) h[e] = t.v[e];
+        }
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-          const int grp = g * 32 + lane;
-          if (grp < c4) {
-            const Vec4<T> t = load4<T>(a.term[k], a.term_dtype[k], (a.term_rowvec[k] ? 0 : rbase) + (int64_t)grp * 4);
+        for (int k = 1; k < 4; ++k)
+          if (k < a.n_terms) {
+            const Vec4<float> t = convert_raw4(raw[k], a.term_dtype[k]);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) h[g][e] = h[g][e] + t.v[e];
+            for (int e = 0; e < 4; ++e) h[e] = h[e] + t.v[e];
           }
+      } else {
+        // fp64 sums: one term at a time keeps the thread at 40 registers (48 warps per SM), which is what fills HBM here
+        {
+          const Vec4<T> t = load4<T>(a.term[0], a.term_dtype[0], a.term_rowvec[0] ? (int64_t)grp * 4 : at);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) h[e] = t.v[e];
+        }
+#pragma unroll 1
+        for (int k = 1; k < a.n_terms; ++k) {
+          const Vec4<T> t = load4<T>(a.term[k], a.term_dtype[k], a.term_rowvec[k] ? (int64_t)grp * 4 : at);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) h[e] = h[e] + t.v[e];
         }
       }
+      if (a.sum_out) store4_sum(reinterpret_cast<T*>(a.sum_out), at, h);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) x[e] = (float)h[e];
     }
-    float x[G][4];
-    float sum = 0.f;
+    float s = warp_sum((x[0] + x[1]) + (x[2] + x[3]));
+    if (lane == 0) red_sum[flip][wid] = s;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < nw; ++i) tot += red_sum[flip][i];
+    const float mean = tot / (float)a.cols;
+    float c[4], sq = 0.f;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const int grp = g * 32 + lane;
-      if (grp < c4) {
-        if (a.sum_out) store4_sum(reinterpret_cast<T*>(a.sum_out), rbase + (int64_t)grp * 4, h[g]);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          x[g][e] = (float)h[g][e];
-          sum += x[g][e];
-        }
-      }
+    for (int e = 0; e < 4; ++e) {
+      c[e] = on ? __fadd_rn(x[e], -mean) : 0.f;
+      sq += __fmul_rn(c[e], c[e]);
     }
-    const float mean = warp_sum(sum) / (float)a.cols;
-    float sq = 0.f;
+    sq = warp_sum(sq);
+    if (lane == 0) red_sq[flip][wid] = sq;
+    __syncthreads();
+    float tsq = 0.f;
+    for (int i = 0; i < nw; ++i) tsq += red_sq[flip][i];
+    const float inv = 1.0f / sqrtf(tsq / (float)a.cols + a.eps);
+    if (on) {
+      float y[4];
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      if (g * 32 + lane < c4) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float c = __fadd_rn(x[g][e], -mean);
-          sq += __fmul_rn(c, c);
-        }
-      }
-    }
-    const float var = warp_sum(sq) / (float)a.cols;
-    const float inv = 1.0f / sqrtf(var + a.eps);
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const int grp = g * 32 + lane;
-      if (grp < c4) {
-        const Vec4<float> w = load4<float>(a.w, a.w_dtype, (int64_t)grp * 4);
-        const Vec4<float> b = load4<float>(a.b, a.b_dtype, (int64_t)grp * 4);
-        float y[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float xh = __fmul_rn(__fadd_rn(x[g][e], -mean), inv);
-          y[e] = __fadd_rn(__fmul_rn(xh, w.v[e]), b.v[e]);
-        }
-        if constexpr (OUT == 1) {
-          __nv_bfloat16* x16 = reinterpret_cast<__nv_bfloat16*>(a.planes_lo);
-          store4_planes(reinterpret_cast<float*>(a.planes_hi), x16, x16 + a.rows * a.cols, rbase + (int64_t)grp * 4, y);
-        } else if constexpr (OUT == 2) {
-          // the value an fp32 / fp64 store followed by a CAST to the 16-bit type would give: y is an fp32 number
-          uint2 w;
-          if (a.out16_dtype == BG_BF16) {
-            __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
-            w = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-          } else {
-            __half2 lo = __floats2half2_rn(y[0], y[1]), hi = __floats2half2_rn(y[2], y[3]);
-            w = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-          }
-          *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.out16) + rbase + (int64_t)grp * 4) = w;
-        } else {
-          store4(a.out, a.out_dtype, rbase + (int64_t)grp * 4, y);
-        }
+      for (int e = 0; e < 4; ++e) y[e] = __fadd_rn(__fmul_rn(__fmul_rn(c[e], inv), w.v[e]), b.v[e]);
+      if constexpr (OUT == 1) {
+        __nv_bfloat16* x16 = reinterpret_cast<__nv_bfloat16*>(a.planes_lo);
+        store4_planes(reinterpret_cast<float*>(a.planes_hi), x16, x16 + a.rows * a.cols, at, y);
+      } else if constexpr (OUT == 2) {
+        store4_16(a.out16, a.out16_dtype, at, y);
+      } else {
+        store4(a.out, a.out_dtype, at, y);
       }
     }
   }
@@ -188,15 +230,14 @@ __global__ void __launch_bounds__(kLnThreads) static_ln_kernel(const __grid_cons
 template <typename T, int OUT>
 cudaError_t launch_t(const LnArgs& a, cudaStream_t s, int sm_count) {
   const int c4 = (int)(a.cols >> 2);
-  const int groups = (c4 + 31) / 32;
-  const int64_t warps_per_cta = kLnThreads / 32;
-  int64_t grid = (a.rows + warps_per_cta - 1) / warps_per_cta;
-  const int64_t cap = (int64_t)sm_count * 8;
-  if (grid > cap) grid = cap;
-  if (groups <= 2) static_ln_kernel<T, 2, OUT><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
-  else if (groups <= 4) static_ln_kernel<T, 4, OUT><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
-  else if (groups <= 6) static_ln_kernel<T, 6, OUT><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
-  else static_ln_kernel<T, 8, OUT><<<(unsigned)grid, kLnThreads, 0, s>>>(a);
+  const int threads = ((c4 + 31) / 32) * 32;
+  // persistent CTAs, as many as are resident by their registers (40 per thread for fp64 sums, 56 for fp32 sums)
+  int per_sm = (sizeof(T) == 8 ? 1536 : 1152) / threads;
+  if (per_sm < 1) per_sm = 1;
+  if (per_sm > 16) per_sm = 16;
+  int64_t grid = (int64_t)sm_count * per_sm;
+  if (grid > a.rows) grid = a.rows;
+  static_ln_cta_kernel<T, OUT><<<(unsigned)grid, threads, 0, s>>>(a);
   return cudaGetLastError();
 }
 
@@ -206,6 +247,8 @@ bool static_ln_shape_ok(int64_t rows, int64_t cols) { return rows > 0 && cols >=
 
 cudaError_t launch_static_ln(const LnArgs& a, cudaStream_t s, int sm_count) {
   if (!static_ln_shape_ok(a.rows, a.cols) || a.n_terms < 1 || a.n_terms > 4) return cudaErrorInvalidValue;
+  for (int k = 0; k < a.n_terms; ++k)
+    if (!a.wide && a.term_dtype[k] == BG_F64) return cudaErrorInvalidValue;      // an fp32 sum has no fp64 term
   if (a.planes_hi) return a.wide ? launch_t<double, 1>(a, s, sm_count) : launch_t<float, 1>(a, s, sm_count);
   if (a.out16) return a.wide ? launch_t<double, 2>(a, s, sm_count) : launch_t<float, 2>(a, s, sm_count);
   return a.wide ? launch_t<double, 0>(a, s, sm_count) : launch_t<float, 0>(a, s, sm_count);
