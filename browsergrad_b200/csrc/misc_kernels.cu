@@ -210,6 +210,38 @@ __global__ void gather_kernel(const __grid_constant__ GatherParams p) {
   }
 }
 
+// Rows of a table picked by an index of the output's full shape (an embedding lookup as the graph states it: x[R, C],
+// idx[N, C], dim 0, 4-byte elements, C a multiple of 4): a thread takes four neighbouring elements of one output row,
+// reads their four indices with two 16-byte loads and, when they name the same table row (they do when every output
+// row repeats its token id), moves the values with one 16-byte load and store; otherwise element by element.
+__global__ void gather_rows4_kernel(const uint32_t* __restrict__ x, const int64_t* __restrict__ idx, uint32_t* __restrict__ out,
+                                    long long n4, int cols, long long x_rows, int* status) {
+  const int c4 = cols >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const int col = (int)(i % c4) * 4;
+    const longlong2 a = __ldg(reinterpret_cast<const longlong2*>(idx) + 2 * i), b = __ldg(reinterpret_cast<const longlong2*>(idx) + 2 * i + 1);
+    const long long g[4] = {a.x, a.y, b.x, b.y};
+    bool bad = false;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) bad |= g[e] < 0 || g[e] >= x_rows;
+    if (bad) {
+      // as the element-wise kernel: elements with a bad index are left unwritten and the status word says so
+      atomicExch(status, BG_ERR_INDEX_RANGE);
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (g[e] >= 0 && g[e] < x_rows) out[4 * i + e] = x[g[e] * cols + col + e];
+      continue;
+    }
+    if (g[0] == g[1] && g[0] == g[2] && g[0] == g[3]) {
+      reinterpret_cast<uint4*>(out)[i] = __ldg(reinterpret_cast<const uint4*>(x + g[0] * cols + col));
+    } else {
+      uint4 v;
+      v.x = x[g[0] * cols + col]; v.y = x[g[1] * cols + col + 1]; v.z = x[g[2] * cols + col + 2]; v.w = x[g[3] * cols + col + 3];
+      reinterpret_cast<uint4*>(out)[i] = v;
+    }
+  }
+}
+
 // ---- cross entropy (execute_cross_entropy_arrays, _framework_contracts.py:3756-3835) ---------------------------
 // Per position, over the class axis of logits [outer, C, inner], in the logits' own float type T:
 //   M = max_c x_c, S = sum_c exp(x_c - M), lse = log S, logp_c = (x_c - M) - lse                      (:3644-3664)
@@ -535,6 +567,13 @@ cudaError_t launch_gather(const void* x, const int64_t* idx, void* out, int esiz
   p.numel = 1;
   for (int d = 0; d < rank; ++d) { p.x_shape[d] = x_shape[d]; p.idx_shape[d] = idx_shape[d]; p.numel *= idx_shape[d]; }
   if (p.numel == 0) return cudaSuccess;
+  if (esize == 4 && rank == 2 && dim == 0 && idx_shape[1] == x_shape[1] && x_shape[1] % 4 == 0 &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(idx) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+    const long long n4 = p.numel / 4;
+    gather_rows4_kernel<<<grid_for(n4, 256), 256, 0, s>>>(reinterpret_cast<const uint32_t*>(x), idx, reinterpret_cast<uint32_t*>(out), n4,
+                                                         (int)x_shape[1], (long long)x_shape[0], status);
+    return cudaGetLastError();
+  }
   const unsigned g = grid_for(p.numel, 256);
   switch (esize) {
     case 1: gather_kernel<uint8_t><<<g, 256, 0, s>>>(p); break;

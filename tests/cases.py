@@ -73,6 +73,11 @@ def _misc_inputs() -> Dict[str, np.ndarray]:
         "table": r.standard_normal((17, 33), dtype=np.float32),
         "tidx": np.ascontiguousarray(np.broadcast_to(r.integers(0, 17, (9, 1), dtype=np.int64), (9, 33))),
         "cidx": r.integers(0, 33, (17, 4), dtype=np.int64),
+        # rows of 36 four-byte values: the lookup kernel that moves four neighbours of a row at a time, with every
+        # output row repeating one table row (an embedding lookup) and with a different table row per element
+        "table36": r.standard_normal((17, 36), dtype=np.float32),
+        "tidx36": np.ascontiguousarray(np.broadcast_to(r.integers(0, 17, (9, 1), dtype=np.int64), (9, 36))),
+        "tidx36_mixed": r.integers(0, 17, (9, 36), dtype=np.int64),
         "bm": r.standard_normal((2, 1, 7, 9), dtype=np.float32),
         "bn": r.standard_normal((3, 9, 4), dtype=np.float32),
         "v9": r.standard_normal((9,), dtype=np.float32),
@@ -437,6 +442,8 @@ CASES: Dict[str, Case] = {
     "repeat_interleave_mid": Case(_misc_inputs, lambda api, t, raw: t["i"].repeat_interleave(3, 1), kind="exact"),
     "repeat_interleave_fused": Case(_misc_inputs, lambda api, t, raw: (t["x"] * t["p"]).repeat_interleave(2, 2) + 1.0),
     "gather_rows": Case(_misc_inputs, lambda api, t, raw: t["table"].gather(0, t["tidx"]), kind="exact"),
+    "gather_rows_by4": Case(_misc_inputs, lambda api, t, raw: t["table36"].gather(0, t["tidx36"]), kind="exact"),
+    "gather_rows_by4_mixed": Case(_misc_inputs, lambda api, t, raw: t["table36"].gather(0, t["tidx36_mixed"]), kind="exact"),
     "gather_cols": Case(_misc_inputs, lambda api, t, raw: t["table"].gather(1, t["cidx"]), kind="exact"),
     "int_arith": Case(_misc_inputs, lambda api, t, raw: (t["i"] * t["j"] + t["i"]) * 3 + (-t["j"]),
                       kind="exact"),
