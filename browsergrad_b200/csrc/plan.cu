@@ -2794,7 +2794,7 @@ void Compiler::emit_matmul(int n, int key) {
       }
       // a result that only feeds split products leaves this unit as their operand planes
       int out_hi = -1, out_lo = -1;
-      if (mode == 1 && !gemm_group_of_.count(n) && feeds_only_split_gemms(pu.out_nodes[0])) {
+      if (mode == 1 && N % 8 == 0 && !gemm_group_of_.count(n) && feeds_only_split_gemms(pu.out_nodes[0])) {   // rows of N: whole 32-byte stores
         out_hi = new_slot(M * N * 4, false, -1); out_lo = new_slot(M * N * 4, false, -1);
         pu.u.writes.push_back(out_hi); pu.u.writes.push_back(out_lo);
         publish_planes(pu.out_nodes[0], out_hi, out_lo, (int)punits_.size());

@@ -318,6 +318,9 @@ CASES: Dict[str, Case] = {
     "c3_chain_plain_planes": Case(_split_chain_inputs, lambda api, t, raw: (t["x"] @ t["w1t"]) @ t["w2t"]),
     "c3_chain_two_readers_planes": Case(_split_chain_inputs, lambda api, t, raw: (lambda h: api.cat(
         [api.linear(h, t["w2"], t["b2"]), h.reshape(2, 132, 304).reshape(264, 304) @ t["w2t"]], 1))(api.gelu(api.linear(t["x"], t["w1"], t["b1"])))),
+    # the reader's rows (240) are a multiple of 8, the producer's (300) are not: the value keeps its plain store
+    "c3_chain_reshaped_reader": Case(_mlp2_inputs, lambda api, t, raw: api.relu(api.linear(t["x"], t["w1"], t["b1"])).reshape(330, 240)
+                                     @ t["w2"].reshape(340, 240).permute(1, 0)),
     "ln_then_linear_planes": Case(_split_chain_inputs, lambda api, t, raw: api.linear(
         api.layer_norm(t["x"] + t["y"], (272,), t["g"], t["be"]), t["w1"], t["b1"])),
     "ln_then_qkv_planes": Case(_split_chain_inputs, lambda api, t, raw: (lambda h: api.cat(
