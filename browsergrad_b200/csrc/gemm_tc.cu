@@ -126,13 +126,24 @@ __device__ __forceinline__ float load_bias(const void* b, int dt, int col) {
 // SPLIT: the kernel computes split products, whose results may leave as operand planes (p.planes_hi).
 template <bool SPLIT>
 __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t* r, int row, int col0, void* C, const void* bias) {
+  // (the choices that are the same for every element -- rounding, activation, store type -- are taken outside the
+  // element loops: inside them the compiler predicates, and every element then issues the instructions of all branches)
   float v[32];
+  if (p.round_acc == BG_F16 + 1) {
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    float x = __uint_as_float(r[j]);
-    if (p.round_acc == BG_F16 + 1) x = __half2float(__float2half_rn(x));
-    else if (p.round_acc == BG_BF16 + 1) x = __bfloat162float(__float2bfloat16_rn(x));
-    v[j] = x;
+    for (int j = 0; j < 32; j += 2) {
+      const float2 f = __half22float2(__floats2half2_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1])));
+      v[j] = f.x; v[j + 1] = f.y;
+    }
+  } else if (p.round_acc == BG_BF16 + 1) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      const float2 f = __bfloat1622float2(__floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1])));
+      v[j] = f.x; v[j + 1] = f.y;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
   }
   if (bias) {
     if (p.bias_dtype == BG_F32 && col0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(bias) & 15) == 0 && (col0 & 3) == 0) {
@@ -153,6 +164,21 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
   }
   const bool full = col0 + 32 <= p.N;
   const size_t base = (size_t)row * p.N + col0;
+  if ((SPLIT && p.planes_hi) || p.c_dtype == BG_F64) {
+    // fp64 results and operand planes hold the fp32 value of the activation
+    if (p.act == TC_ACT_RELU) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+    } else if (p.act == TC_ACT_GELU) {
+      if (p.c_dtype == BG_F64) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = gelu_accurate(v[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = gelu_graph<float>(v[j]);
+      }
+    }
+  }
   if (SPLIT && p.planes_hi) {
     // the value the C store would have held (an fp32 value also when C is fp64), split as launch_tf32_split does
     float* hi = p.planes_hi + base;
@@ -165,9 +191,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
       float xs[8], ls[8];
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
-        float x = v[j + t];
-        if (p.act == TC_ACT_RELU) x = x > 0.f ? x : 0.f;
-        else if (p.act == TC_ACT_GELU) x = p.c_dtype == BG_F64 ? gelu_accurate(x) : gelu_graph<float>(x);
+        const float x = v[j + t];
         asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(wh[t]) : "f"(x));
         xs[t] = x;
         ls[t] = __fadd_rn(x, -__uint_as_float(wh[t]));
@@ -192,9 +216,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
       uint32_t w[8];
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
-        double x = (double)v[j + t];
-        if (p.act == TC_ACT_RELU) x = x > 0.0 ? x : 0.0;
-        else if (p.act == TC_ACT_GELU) x = (double)gelu_accurate(v[j + t]);
+        const double x = (double)v[j + t];
         const unsigned long long b = (unsigned long long)__double_as_longlong(x);
         w[2 * t] = (uint32_t)b;
         w[2 * t + 1] = (uint32_t)(b >> 32);
@@ -210,10 +232,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
       double w[2];
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
-        double x = (double)v[j + t];
-        if (p.act == TC_ACT_RELU) x = x > 0.0 ? x : 0.0;
-        else if (p.act == TC_ACT_GELU) x = (double)gelu_accurate(v[j + t]);
-        w[t] = x;
+        w[t] = (double)v[j + t];
       }
       if (full && (p.N & 1) == 0) *reinterpret_cast<double2*>(out + j) = make_double2(w[0], w[1]);
       else {
@@ -223,12 +242,12 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
     }
     return;
   }
+  if (p.act == TC_ACT_RELU) {
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    float x = v[j];
-    if (p.act == TC_ACT_RELU) x = x > 0.f ? x : 0.f;
-    else if (p.act == TC_ACT_GELU) x = gelu_graph<float>(x);
-    v[j] = x;
+    for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+  } else if (p.act == TC_ACT_GELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = gelu_graph<float>(v[j]);
   }
   if (p.c_dtype == BG_F32) {
     float* out = reinterpret_cast<float*>(C) + base;
