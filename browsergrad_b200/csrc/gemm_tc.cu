@@ -1049,15 +1049,18 @@ int g_tc_pair_mode = 1;   // 0: never, 1: when the problem fills the device with
 // Width of the CTA-pair tile (256 rows x TN columns).  A pair works through ceil(tiles / pairs) tiles one
 // after the other; a tile costs about TN + 64 (the A half of every stage does not shrink with TN), so a
 // narrower tile wins when it removes a mostly idle last round: M = 8192, N = 768 is 96 tiles of 256 columns
-// (two rounds on 74 pairs, the second a third full) but 128 tiles of 192 columns (two shorter rounds).
-static int pair_tile_width(int64_t M, int64_t N, int pairs, int n_prob = 1) {
+// (two rounds on 74 pairs, the second a third full) but 128 tiles of 192 columns (two shorter rounds).  A tile of
+// the split product carries a larger cost that does not shrink with its width (the folds of its accumulation chunks
+// and its final epilogue by the same warps): TN + 256 reproduces the measured order of the widths on the decoder's
+// shapes ([8192, 768] x 768 / 2304 / 3072 and 4096^3), where TN + 64 chose 192 columns for N = 3072 (202 us against 192).
+static int pair_tile_width(int64_t M, int64_t N, int pairs, bool split, int n_prob = 1) {
   int best = 256;
   int64_t best_cost = -1;
   const int widths[3] = {256, 192, 128};
   for (int w : widths) {
     const int64_t tiles = ((M + 255) / 256) * ((N + w - 1) / w) * n_prob;
     const int64_t rounds = (tiles + pairs - 1) / pairs;
-    const int64_t cost = rounds * (w + 64);
+    const int64_t cost = rounds * (w + (split ? 256 : 64));
     if (best_cost < 0 || cost < best_cost) { best = w; best_cost = cost; }
   }
   return best;
@@ -1084,7 +1087,7 @@ cudaError_t launch_gemm_tc_group(const TcGemm* gs, int n_prob, int* status, cuda
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (n_prob > 1 && g.M > 128 && g.N > 128 && g_tc_pair_mode != 0) {
     bool launched = false;
-    const int tn = g_tc_pair_width ? g_tc_pair_width : pair_tile_width(g.M, g.N, sms / 2, n_prob);
+    const int tn = g_tc_pair_width ? g_tc_pair_width : pair_tile_width(g.M, g.N, sms / 2, tf32, n_prob);
     {
       cudaError_t e = tf32 ? launch_pair_width<true>(tn, gs, n_prob, status, s, &launched) : launch_pair_width<false>(tn, gs, n_prob, status, s, &launched);
       if (e != cudaSuccess || launched) return e;
@@ -1106,7 +1109,7 @@ cudaError_t launch_gemm_tc(const TcGemm& g, int* status, cudaStream_t s) {
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (pair_ok && (g_tc_pair_mode == 2 || (g_tc_pair_mode == 1 && tiles256 >= 64))) {
     bool launched = false;
-    const int tn = g_tc_pair_width ? g_tc_pair_width : pair_tile_width(g.M, g.N, sms / 2);
+    const int tn = g_tc_pair_width ? g_tc_pair_width : pair_tile_width(g.M, g.N, sms / 2, tf32);
     cudaError_t e = tf32 ? launch_pair_width<true>(tn, &g, 1, status, s, &launched) : launch_pair_width<false>(tn, &g, 1, status, s, &launched);
     if (e != cudaSuccess || launched) return e;
   }
