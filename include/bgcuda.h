@@ -220,7 +220,10 @@ int bg_run_tensor_plan_resident(bg_context* ctx, const bg_plan* plan,
 int bg_alive_handle_count(bg_context* ctx, int64_t* out);
 int bg_resource_snapshot(bg_context* ctx, bg_resource_stats* out);
 int bg_flush_profiles(bg_context* ctx, bg_profile_entry* out, int capacity, int* n_out);
-/* Text listing of the kernels the most recent plan compiled to, one per line. */
+/* Text listing of the kernels the most recent plan compiled to, one per line: the unit's kind, what was folded into
+ * it ("+bias", "+gelu", "+mask", "+merge"), the operand format it stores for its readers ("+split": operand planes of
+ * the split products that read it; "+cast16": the 16-bit type of the autocast Linears that read it; "+f32store": the
+ * fp32 values of an fp64-typed product that only the fused attention reads), and the dtype of the graph node. */
 int bg_last_plan_trace(bg_context* ctx, char* out, size_t capacity);
 /*
  * Cross entropy over class-index targets with no allocation of any kind (no counterpart in the
