@@ -37,6 +37,22 @@ __global__ void strided_copy_kernel(const __grid_constant__ CopyParams p) {
   }
 }
 
+// Strided copy whose innermost axis has unit stride: whole 16-byte vectors of the rows move (a permutation of the
+// leading axes, e.g. [ranks, M, n] -> [M, ranks, n]).  shape / stride describe the view in units of vectors for the last
+// axis and of bytes for the strides; one index decomposition per vector instead of one per element.
+__global__ void strided_copy_vec_kernel(const __grid_constant__ CopyParams p) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < p.numel; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t rem = i, off = 0;
+#pragma unroll 1
+    for (int d = p.rank - 1; d >= 0; --d) {
+      int64_t q = rem / p.shape[d];
+      off += (rem - q * p.shape[d]) * p.stride[d];
+      rem = q;
+    }
+    reinterpret_cast<uint4*>(p.out)[i] = __ldcs(reinterpret_cast<const uint4*>(p.in + off));
+  }
+}
+
 // Tiled transpose of the two fastest-varying axes when the innermost output axis reads with a
 // large stride: [batch.., A, B] view whose input has unit stride along A.
 template <typename T>
@@ -512,6 +528,25 @@ cudaError_t launch_strided_copy(const StridedView& in, void* out, int64_t numel,
         case 4: transpose_tile_kernel<uint32_t><<<grid, block, 0, s>>>((const uint32_t*)in.ptr, (uint32_t*)out, A, B, in.stride[in.rank - 1], 0, 0, batch); break;
         default: transpose_tile_kernel<uint64_t><<<grid, block, 0, s>>>((const uint64_t*)in.ptr, (uint64_t*)out, A, B, in.stride[in.rank - 1], 0, 0, batch); break;
       }
+      return cudaGetLastError();
+    }
+  }
+  // rows of whole 16-byte vectors, every row starting on a 16-byte boundary
+  if (in.rank >= 2 && in.stride[in.rank - 1] == 1 && (in.shape[in.rank - 1] * es) % 16 == 0 &&
+      ((reinterpret_cast<uintptr_t>(in.ptr) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+    bool ok = true;
+    for (int d = 0; d + 1 < in.rank; ++d) ok = ok && in.stride[d] >= 0 && (in.stride[d] * es) % 16 == 0;
+    if (ok) {
+      CopyParams v{};
+      v.in = reinterpret_cast<const char*>(in.ptr);
+      v.out = reinterpret_cast<char*>(out);
+      v.esize = 16;
+      v.rank = in.rank;
+      v.numel = numel * es / 16;
+      for (int d = 0; d + 1 < in.rank; ++d) { v.shape[d] = in.shape[d]; v.stride[d] = in.stride[d] * es; }
+      v.shape[in.rank - 1] = in.shape[in.rank - 1] * es / 16;
+      v.stride[in.rank - 1] = 16;
+      strided_copy_vec_kernel<<<grid_for(v.numel, 256), 256, 0, s>>>(v);
       return cudaGetLastError();
     }
   }
