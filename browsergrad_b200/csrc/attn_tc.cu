@@ -1028,7 +1028,7 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
   const bool kv32 = v_mn && p_tmem && (g_attn16_variant & 8) && fp32_rows(a.k) && fp32_rows(a.v);
   // 3xTF32, one thread per row: fp32 Q, K and V rows are split into hi / lo planes inside the kernel
   const bool row32 = tf32 && (g_attn32_variant & 1);
-  const bool raw_qk = row32 && (g_attn32_variant & 2) && fp32_rows(a.q) && fp32_rows(a.k) && fp32_rows(a.v) &&
+  const bool raw_rows = row32 && (g_attn32_variant & 2) && fp32_rows(a.q) && fp32_rows(a.k) && fp32_rows(a.v) &&
                       attn_tf32_row_usable(a.Sk, a.out_dtype, a.out, a.out_sb, a.out_sh, a.out_ss, true);
   // operand staging: dense Q, K, V^T (or V) in the kernel's encoding
   const int kind = tf32 ? PREP_TF32 : (a.ab_dtype == BG_F16 ? PREP_F16 : PREP_BF16);
@@ -1051,7 +1051,7 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
       }
     }
     if (kv32 && i > 0) continue;
-    if (raw_qk) continue;
+    if (raw_rows) continue;
     // 16-bit operands that are already dense [B,H,S,D] feed the TMA maps directly
     if (!tf32 && as_rows && dense && ops[i]->dtype == a.ab_dtype && aligned) {
       staged[i] = ops[i]->ptr;
@@ -1102,7 +1102,7 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
     }
   }
   CUtensorMap q0, q1, k0, k1, v0, v1;
-  if (raw_qk) {
+  if (raw_rows) {
     if (!make_map4_strided(&q0, a.q.ptr, BG_F32, a.B, a.H, a.Sq, a.D, a.q.stride[0], a.q.stride[1], a.q.stride[2], 32, kQRows) ||
         !make_map4_strided(&k0, a.k.ptr, BG_F32, a.B, a.H, a.Sk, a.D, a.k.stride[0], a.k.stride[1], a.k.stride[2], 32, bkv) ||
         // rows of V feed the tensor core as an MN-major operand of 32-bit values: that takes the swizzle of 32-byte pieces
@@ -1110,21 +1110,21 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
                            CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
       return cudaErrorInvalidValue;
   } else if (!pair && !make_map4(&q0, staged[0], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
-  if (raw_qk) {
+  if (raw_rows) {
   } else if (kv32) {
     if (!make_map4_strided(&k0, a.k.ptr, BG_F32, a.B, a.H, a.Sk, a.D, a.k.stride[0], a.k.stride[1], a.k.stride[2], 32, bkv) ||
         !make_map4_strided(&v0, a.v.ptr, BG_F32, a.B, a.H, a.Sk, a.D, a.v.stride[0], a.v.stride[1], a.v.stride[2], 32, bkv))
       return cudaErrorInvalidValue;
   } else if (!make_map4(&k0, staged[1], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
-  if (kv32 || raw_qk) {
+  if (kv32 || raw_rows) {
   } else if (v_mn) {
     if (!make_map4(&v0, staged[2], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
   } else if (!make_map4(&v0, staged[2], sdt, a.B, a.H, a.D, a.Sk, kHeadDim)) return cudaErrorInvalidValue;
   q1 = q0; k1 = k0; v1 = v0;
   if (tf32) {
-    if (!raw_qk && !make_map4(&q1, scratch[1], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
-    if (!raw_qk && !make_map4(&k1, scratch[3], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
-    if (!raw_qk && !make_map4(&v1, scratch[5], sdt, a.B, a.H, a.D, a.Sk, kHeadDim)) return cudaErrorInvalidValue;
+    if (!raw_rows && !make_map4(&q1, scratch[1], sdt, a.B, a.H, a.Sq, a.D, kQRows)) return cudaErrorInvalidValue;
+    if (!raw_rows && !make_map4(&k1, scratch[3], sdt, a.B, a.H, a.Sk, a.D, bkv)) return cudaErrorInvalidValue;
+    if (!raw_rows && !make_map4(&v1, scratch[5], sdt, a.B, a.H, a.D, a.Sk, kHeadDim)) return cudaErrorInvalidValue;
   }
   AttnParams p{};
   p.B = a.B; p.H = a.H; p.Sq = a.Sq; p.Sk = a.Sk;
@@ -1160,7 +1160,7 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
   dim3 grid((a.Sq + kQRows - 1) / kQRows, a.H, a.B);
   cudaError_t e;
   const long long n_out = (long long)a.B * a.H * a.Sq * a.D;
-  if (row32 && (raw_qk || attn_tf32_row_usable(a.Sk, a.out_dtype, a.out, a.out_sb, a.out_sh, a.out_ss, false))) {
+  if (row32 && (raw_rows || attn_tf32_row_usable(a.Sk, a.out_dtype, a.out, a.out_sb, a.out_sh, a.out_ss, false))) {
     // (row offsets that keep `out` 16-byte aligned keep the planes' fp32 rows 16- and bf16 rows 8-byte aligned)
     if (a.planes_hi) {
       p.planes_hi = reinterpret_cast<float*>(a.planes_hi);
@@ -1168,7 +1168,7 @@ cudaError_t launch_attention_tc(const AttnProblem& a, void* const scratch[8], bo
       p.planes_n = n_out;
     }
     const CUtensorMap maps[6] = {q0, q1, k0, k1, v0, v1};
-    return launch_attn_tf32_row(p, maps, raw_qk, s);
+    return launch_attn_tf32_row(p, maps, raw_rows, s);
   }
   if (tf32) {
     const size_t smem = AttnCfg::SmemBytes + 256 + 2048 + 1024;

@@ -286,6 +286,7 @@ class Compiler {
   std::set<int> absorbed_groups_;
   int tc_mode(int n);                      // -1: SIMT; 0: 16-bit operands; 1: 3xTF32
   bool small_gemm(int n, int* splits, int64_t* partial_bytes);   // a 2-D fp32 MATMUL the split-K small kernel takes
+  bool storage_readers(int f, std::vector<int>& readers);   // who reads f's storage; false if it must hold f as typed
   bool feeds_only_split_gemms(int f);      // every reader of f is the dense A operand of a bf16-plane split product
   void publish_planes(int f, int hi, int lo, int punit);
   bool feeds_only_convert16(int f, int* dtype16);   // every reader of f is the absorbed 16-bit CAST of a GEMM's A operand
@@ -1906,15 +1907,13 @@ static std::string gelu_expr_text() {
   return "mul(mul(c0.5,x),add(c1,div(add(exp(" + Z + "),neg(exp(neg(" + Z + ")))),add(exp(" + Z + "),exp(neg(" + Z + "))))))";
 }
 
-// True when the value of node f is read by nothing but tensor-core split products that take all of it as their dense
-// [M, K] A operand (through reshapes), K a multiple of 8: the unit that computes f can then store the operand planes
-// of those products (tf32(x); bf16(x); bf16(x - tf32(x))) in place of f itself, and no pass of its own splits f.
-bool Compiler::feeds_only_split_gemms(int f) {
+// The nodes that read the storage of f: its consumers, followed through the views that alias it.  False when the
+// storage has to hold f as the graph types it -- f (or a view of it) is the plan's root, f is not a dense buffer of
+// its own, or a reshape of it became a copy.
+bool Compiler::storage_readers(int f, std::vector<int>& readers) {
   if (!ctx_->fusion || !ctx_->static_patterns || f == root_) return false;
   const View& fv = view_[f];
-  if (fv.is_const || fv.off != 0 || !fv.contiguous() || (fv.dtype != BG_F32 && fv.dtype != BG_F64)) return false;
-  const int64_t numel = fv.numel();
-  bool any = false;
+  if (fv.is_const || fv.off != 0 || !fv.contiguous()) return false;
   std::vector<int> stack{f};
   std::set<int> seen;
   while (!stack.empty()) {
@@ -1925,31 +1924,44 @@ bool Compiler::feeds_only_split_gemms(int f) {
     for (int c : cons_[v]) {
       if (kind_[c] == K_DEAD) continue;
       if (kind_[c] == K_VIEW || kind_[c] == K_ALIAS) {
-        if (view_[c].slot != fv.slot) return false;          // a reshape that became a copy reads f itself
+        if (view_[c].slot != fv.slot) return false;
         stack.push_back(c);
-        continue;
+      } else {
+        readers.push_back(c);
       }
-      const Node& m = nodes_[c];
-      if (m.op != BG_OP_MATMUL || kind_[c] != K_OTHER || attn_plan_.count(c) || attn_absorbed_.count(c) || tc_mode(c) != 1) return false;
-      const View& av = view_[resolve(m.in[0])];
-      const View& bv = view_[resolve(m.in[1])];
-      if (av.slot != fv.slot || bv.slot == fv.slot) return false;
-      if (av.off != 0 || av.rank != 2 || av.stride[1] != 1 || av.stride[0] != av.shape[1] || av.shape[0] * av.shape[1] != numel ||
-          av.shape[1] % 8 != 0)
-        return false;
-      any = true;
     }
   }
-  return any;
+  return true;
+}
+
+// True when the value of node f is read by nothing but tensor-core split products that take all of it as their dense
+// [M, K] A operand (through reshapes), K a multiple of 8: the unit that computes f can then store the operand planes
+// of those products (tf32(x); bf16(x); bf16(x - tf32(x))) in place of f itself, and no pass of its own splits f.
+bool Compiler::feeds_only_split_gemms(int f) {
+  std::vector<int> readers;
+  const View& fv = view_[f];
+  if ((fv.dtype != BG_F32 && fv.dtype != BG_F64) || !storage_readers(f, readers)) return false;
+  const int64_t numel = fv.numel();
+  for (int c : readers) {
+    const Node& m = nodes_[c];
+    if (m.op != BG_OP_MATMUL || kind_[c] != K_OTHER || attn_plan_.count(c) || attn_absorbed_.count(c) || tc_mode(c) != 1) return false;
+    const View& av = view_[resolve(m.in[0])];
+    const View& bv = view_[resolve(m.in[1])];
+    if (av.slot != fv.slot || bv.slot == fv.slot) return false;
+    if (av.off != 0 || av.rank != 2 || av.stride[1] != 1 || av.stride[0] != av.shape[1] || av.shape[0] * av.shape[1] != numel ||
+        av.shape[1] % 8 != 0)
+      return false;
+  }
+  return !readers.empty();
 }
 
 // True when the fp32 / fp64 value of node f is read by nothing but CASTs to one 16-bit type that tensor-core GEMMs
 // absorbed as the conversion of their dense A operand (autocast Linears after a LayerNorm): the unit that computes f
 // can then store the 16-bit rows itself, registered where those GEMMs look for an activation already converted.
 bool Compiler::feeds_only_convert16(int f, int* dtype16) {
-  if (!ctx_->fusion || !ctx_->static_patterns || f == root_) return false;
+  std::vector<int> readers;
   const View& fv = view_[f];
-  if (fv.is_const || fv.off != 0 || !fv.contiguous() || (fv.dtype != BG_F32 && fv.dtype != BG_F64)) return false;
+  if ((fv.dtype != BG_F32 && fv.dtype != BG_F64) || !storage_readers(f, readers)) return false;
   const int64_t numel = fv.numel();
   // the casts that GEMMs of this plan absorbed as conversions of all of f
   std::set<int> a_casts;
@@ -1967,23 +1979,8 @@ bool Compiler::feeds_only_convert16(int f, int* dtype16) {
     a_casts.insert(ca);
   }
   if (a_casts.empty()) return false;
-  std::vector<int> stack{f};
-  std::set<int> seen;
-  while (!stack.empty()) {
-    const int v = stack.back();
-    stack.pop_back();
-    if (!seen.insert(v).second) continue;
-    if (v == root_) return false;
-    for (int c : cons_[v]) {
-      if (kind_[c] == K_DEAD) continue;
-      if (kind_[c] == K_VIEW || kind_[c] == K_ALIAS) {
-        if (view_[c].slot != fv.slot) return false;
-        stack.push_back(c);
-        continue;
-      }
-      if (!a_casts.count(c)) return false;
-    }
-  }
+  for (int c : readers)
+    if (!a_casts.count(c)) return false;
   *dtype16 = dt;
   return true;
 }
@@ -1993,27 +1990,13 @@ bool Compiler::feeds_only_convert16(int f, int* dtype16) {
 // then stores fp32 into f's storage and the attention reads fp32 rows, half the bytes on either side and no pass
 // that narrows Q and K.
 bool Compiler::feeds_only_attention32(int f) {
-  if (!ctx_->fusion || !ctx_->static_patterns || f == root_) return false;
+  std::vector<int> readers;
+  if (view_[f].dtype != BG_F64 || !storage_readers(f, readers)) return false;
   const View& fv = view_[f];
-  if (fv.is_const || fv.dtype != BG_F64 || fv.off != 0 || !fv.contiguous()) return false;
-  std::vector<int> stack{f};
-  std::set<int> seen;
-  while (!stack.empty()) {
-    const int v = stack.back();
-    stack.pop_back();
-    if (!seen.insert(v).second) continue;
-    if (v == root_) return false;
-    for (int c : cons_[v]) {
-      if (kind_[c] == K_DEAD) continue;
-      if (kind_[c] == K_VIEW || kind_[c] == K_ALIAS) {
-        if (view_[c].slot != fv.slot) return false;
-        stack.push_back(c);
-        continue;
-      }
-      // the Q K^T product inside a fused attention, or its final product (absorbed casts of other kernels are not)
-      const bool inner_product = attn_absorbed_.count(c) && nodes_[c].op == BG_OP_MATMUL;
-      if (!attn_plan_.count(c) && !inner_product) return false;
-    }
+  for (int c : readers) {
+    // the Q K^T product inside a fused attention, or its final product (absorbed casts of other kernels are not)
+    const bool inner_product = attn_absorbed_.count(c) && nodes_[c].op == BG_OP_MATMUL;
+    if (!attn_plan_.count(c) && !inner_product) return false;
   }
   bool any = false;
   for (const auto& kv : attn_plan_) {
