@@ -1,6 +1,7 @@
 """Error types of the CUDA bridge, named after the reference's
 (packages/browsergrad-kernels/src/types.ts:86-91 ``KernelError``;
-packages/browsergrad-jit/src/python/_errors.py ``RealizationError`` / ``JitNotImplementedError``)."""
+packages/browsergrad-jit/src/python/_errors.py ``RealizationError`` / ``JitNotImplementedError`` /
+``BufferTableError``)."""
 
 
 class KernelError(RuntimeError):
@@ -17,3 +18,7 @@ class RealizationError(RuntimeError):
 
 class JitNotImplementedError(NotImplementedError):
     """Raised for opcodes outside the forward path."""
+
+
+class BufferTableError(RuntimeError):
+    """Raised by the device buffer table for a buffer id that is registered twice or not at all."""

@@ -18,15 +18,16 @@ import numpy as np
 
 from . import _lib, graph, passes
 from .bridge import CudaBridge
-from .errors import JitNotImplementedError, RealizationError
+from .errors import BufferTableError, JitNotImplementedError, RealizationError
 
 _DTYPE_BYTES = _lib.DTYPE_SIZE
 
 
 class DeviceBufferTable:
-    """``buffer id -> device handle`` (the role of ``GpuBufferTable``,
-    packages/browsergrad-jit/src/python/_gpu_buffer_table.py:35-131): uploads are idempotent per
-    id and live until ``release_all``."""
+    """``buffer id -> device handle`` with the methods of ``GpuBufferTable``
+    (packages/browsergrad-jit/src/python/_gpu_buffer_table.py:35-131): ``register`` / ``get`` / ``has`` / ``detach`` /
+    ``replace`` / ``release`` / ``release_all``, plus ``upload``, which is idempotent per id.  Handles live until they
+    are released or detached."""
 
     def __init__(self, bridge: CudaBridge) -> None:
         self.bridge = bridge
@@ -35,6 +36,9 @@ class DeviceBufferTable:
 
     def get(self, buffer_id: str) -> Optional[int]:
         return self._handles.get(buffer_id)
+
+    def has(self, buffer_id: str) -> bool:
+        return buffer_id in self._handles
 
     def upload(self, buffer_id: str, array: np.ndarray) -> int:
         h = self._handles.get(buffer_id)
@@ -45,7 +49,23 @@ class DeviceBufferTable:
         return h
 
     def register(self, buffer_id: str, handle: int) -> None:
-        old = self._handles.get(buffer_id)
+        """Bind ``buffer_id`` to ``handle``; an id that is already bound raises (_gpu_buffer_table.py:63-74:
+        registering twice would hide a double upload).  ``replace`` rebinds."""
+        if buffer_id in self._handles:
+            raise BufferTableError(f"DeviceBufferTable: buffer_id {buffer_id!r} is already registered with a handle; "
+                                   "consult get() before uploading again, or use replace()")
+        self._handles[buffer_id] = handle
+
+    def detach(self, buffer_id: str) -> int:
+        """Remove a handle without releasing it: the caller owns it from here (_gpu_buffer_table.py:82-90)."""
+        if buffer_id not in self._handles:
+            raise BufferTableError(f"DeviceBufferTable: cannot detach unknown buffer_id {buffer_id!r}")
+        return self._handles.pop(buffer_id)
+
+    def replace(self, buffer_id: str, handle: int) -> None:
+        """Bind ``buffer_id`` to ``handle`` and release the handle it had (_gpu_buffer_table.py:92-99): the next
+        realization that names the id reads the new buffer, e.g. a key / value cache that grew."""
+        old = self._handles.pop(buffer_id, None)
         if old is not None and old != handle:
             self.bridge.release(old)
         self._handles[buffer_id] = handle

@@ -68,3 +68,31 @@ def test_resident_root_feeds_a_contraction_and_a_view(bridge):
         out._store.get(out._uop.inputs[0].arg)
     release_resident_leaves(bridge)
     assert bridge.aliveHandleCount() == 0
+
+
+def test_replace_rebinds_a_buffer_id_for_the_next_realization(bridge):
+    """``replace`` (_gpu_buffer_table.py:92-99): a graph that names a buffer id reads whatever the table binds to it
+    at realization time, and the handle it had is released."""
+    from browsergrad_b200 import front
+    rng = np.random.default_rng(9)
+    first = rng.standard_normal((40, 24), dtype=np.float32)
+    second = rng.standard_normal((40, 24), dtype=np.float32)
+    store = graph.BufferStore()
+    table = front.DeviceBufferTable(bridge)
+    bridge._front_table = table
+    table.register("state", bridge.upload(first, first.shape, "float32"))
+    buf = graph.Node("BUFFER", (), first.shape, "float32", "state")
+    x = graph.Tensor(graph.Node("LOAD", (buf,), buf.shape, buf.dtype, None), front._ResidentStore(store, table, bridge))
+    out = front.materialize_resident(front.realize_cuda_resident(x * 2.0, bridge))
+    np.testing.assert_array_equal(out, first * np.float32(2.0))
+    alive = bridge.aliveHandleCount()
+    table.replace("state", bridge.upload(second, second.shape, "float32"))
+    assert bridge.aliveHandleCount() == alive                      # one uploaded, the old one released
+    out = front.materialize_resident(front.realize_cuda_resident(x * 2.0, bridge))
+    np.testing.assert_array_equal(out, second * np.float32(2.0))
+    kept = table.detach("state")                                   # ours now: the table no longer releases it
+    release_resident_leaves(bridge)
+    table.release_all()
+    assert bridge.aliveHandleCount() == 1
+    bridge.release(kept)
+    assert bridge.aliveHandleCount() == 0
