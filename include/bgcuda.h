@@ -173,7 +173,9 @@ const char* bg_last_error(bg_context* ctx);
 int bg_abi_version(void);
 /* options: "profiling" (0/1), "f64_contraction" (0 = exact fp64 FMA, 1 = fp32-faithful tensor
  * path, 2 = automatic: tensor path when no fp64 leaf enters the plan), "fusion" (0/1), "tensor_cores" (0/1),
- * "static_patterns" (0/1), "gemm_groups" (0/1), "gemm_cta_pairs" (0/1/2), "gemm_pair_tile_width" (0/256/192/128),
+ * "static_patterns" (0/1: the kernels specialised for whole expressions -- the dominant chains, residual + LayerNorm
+ * rows -- and the producer-side operand formats that go with them; 0 leaves every elementwise / row group to the
+ * generic interpreter and every value in the type the graph gives it), "gemm_groups" (0/1), "gemm_cta_pairs" (0/1/2), "gemm_pair_tile_width" (0/256/192/128),
  * "attention16_kernel" (bit set: 1 two query tiles per CTA, 2 V as an MN-major operand, 4 P in tensor memory,
  * 8 fp32 K / V converted inside the kernel; 0 one query tile per CTA; -1 restores the default),
  * "attention32_kernel" (3xTF32 attention: 0 two threads per row, 1 one thread per row with P and O in tensor
