@@ -237,6 +237,10 @@ struct CeProblem {
 cudaError_t launch_ce_rows(const CeProblem& c, cudaStream_t s);
 // Per-position losses -> sum (reduction 2) or mean (1): the mean divides by the summed `sel_w` when given, else by the
 // number of `targets` that differ from ignore_index when given, else by `fixed_count`.
+// Losses and their mean / sum in one launch of one CTA, for at most 256 positions with a short class axis; the bits
+// launch_ce_rows + launch_ce_reduce give.
+bool ce_small_usable(const CeProblem& c);
+cudaError_t launch_ce_small(const CeProblem& c, void* out, int reduction, double fixed_count, cudaStream_t s);
 cudaError_t launch_ce_reduce(const void* per_pos, const int64_t* targets, const void* sel_w, void* out, int dtype, int64_t n,
                              int reduction, int64_t ignore_index, double fixed_count, cudaStream_t s);
 

@@ -342,28 +342,32 @@ template <> __device__ __forceinline__ void ce_load_vec<double, 2>(const double*
 // One thread per position; the class axis is `inner` elements apart, so neighbouring threads read neighbouring
 // addresses when inner > 1.  Used for spatial logits and for short class axes.
 template <typename T>
+__device__ __forceinline__ void ce_one_position(const CeRowArgs<T>& a, int64_t t, bool need_sums) {
+  const int64_t o = t / a.inner, i = t - o * a.inner;
+  const int64_t base = o * a.C * a.inner + i;
+  if (!a.prob && a.idx[t] == a.ignore_index) { ce_finish<T>(a, t, T(0), T(1), T(0), T(0), false); return; }
+  T M = a.logits[base];
+  for (int64_t c = 1; c < a.C; ++c) { const T v = a.logits[base + c * a.inner]; M = v > M ? v : M; }
+  T S = T(0), T1 = T(0), T2 = T(0);
+  for (int64_t c = 0; c < a.C; ++c) {
+    const T sh = a.logits[base + c * a.inner] - M;
+    S += ce_exp<T>(sh);
+    if (need_sums) {
+      T q = a.weight ? a.weight[c] : T(1);
+      if (a.prob) q *= a.prob[base + c * a.inner] * (T(1) - a.smoothing) + a.smoothing / (T)a.C;
+      T1 += q * sh;
+      T2 += q;
+    }
+  }
+  ce_finish<T>(a, t, M, S, T1, T2, need_sums);
+}
+
+template <typename T>
 __global__ void ce_pos_kernel(const CeRowArgs<T> a) {
   const int64_t n = a.outer * a.inner;
   const bool need_sums = a.prob != nullptr || a.smoothing != T(0);
-  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t o = t / a.inner, i = t - o * a.inner;
-    const int64_t base = o * a.C * a.inner + i;
-    if (!a.prob && a.idx[t] == a.ignore_index) { ce_finish<T>(a, t, T(0), T(1), T(0), T(0), false); continue; }
-    T M = a.logits[base];
-    for (int64_t c = 1; c < a.C; ++c) { const T v = a.logits[base + c * a.inner]; M = v > M ? v : M; }
-    T S = T(0), T1 = T(0), T2 = T(0);
-    for (int64_t c = 0; c < a.C; ++c) {
-      const T sh = a.logits[base + c * a.inner] - M;
-      S += ce_exp<T>(sh);
-      if (need_sums) {
-        T q = a.weight ? a.weight[c] : T(1);
-        if (a.prob) q *= a.prob[base + c * a.inner] * (T(1) - a.smoothing) + a.smoothing / (T)a.C;
-        T1 += q * sh;
-        T2 += q;
-      }
-    }
-    ce_finish<T>(a, t, M, S, T1, T2, need_sums);
-  }
+  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x)
+    ce_one_position<T>(a, t, need_sums);
 }
 
 // One CTA per position for class axes that are contiguous (inner == 1) and long: every thread walks the row in
@@ -499,6 +503,37 @@ __global__ void ce_reduce_kernel(const T* per_pos, const int64_t* targets, const
   }
 }
 
+// Up to 256 positions with a short class axis (a classifier head on one small batch): the per-position losses and
+// their reduction in one launch of one CTA -- thread t takes position t, then the CTA reduces exactly as
+// ce_reduce_kernel does (each of its 256 partial sums holds at most one position here), so the bits are the same.
+template <typename T>
+__global__ void __launch_bounds__(256) ce_small_kernel(const CeRowArgs<T> a, const int64_t* targets, T* out, int reduction, double fixed_count) {
+  __shared__ double ssum[256];
+  __shared__ double sden[256];
+  const int64_t n = a.outer * a.inner;
+  const bool need_sums = a.prob != nullptr || a.smoothing != T(0);
+  double s = 0.0, c = 0.0;
+  if ((int64_t)threadIdx.x < n) {
+    ce_one_position<T>(a, threadIdx.x, need_sums);
+    // the thread reads back what it has just written itself
+    s = (double)a.per_pos[threadIdx.x];
+    if (a.sel_w) c = (double)a.sel_w[threadIdx.x];
+    else if (targets) c = targets[threadIdx.x] != a.ignore_index ? 1.0 : 0.0;
+  }
+  ssum[threadIdx.x] = s;
+  sden[threadIdx.x] = c;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o) { ssum[threadIdx.x] += ssum[threadIdx.x + o]; sden[threadIdx.x] += sden[threadIdx.x + o]; }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const T num = (T)ssum[0];
+    const T den = (a.sel_w || targets) ? (T)sden[0] : (T)fixed_count;
+    out[0] = reduction == 2 ? num : (T)(num / den);
+  }
+}
+
 inline unsigned grid_for(int64_t n, int block) {
   int64_t g = (n + block - 1) / block;
   if (g < 1) g = 1;
@@ -621,7 +656,7 @@ cudaError_t launch_gather(const void* x, const int64_t* idx, void* out, int esiz
 
 namespace {
 template <typename T>
-cudaError_t ce_rows_typed(const CeProblem& c, cudaStream_t s) {
+CeRowArgs<T> ce_args(const CeProblem& c) {
   CeRowArgs<T> a{};
   a.logits = reinterpret_cast<const T*>(c.logits);
   a.idx = c.prob_targets ? nullptr : reinterpret_cast<const int64_t*>(c.targets);
@@ -632,8 +667,16 @@ cudaError_t ce_rows_typed(const CeProblem& c, cudaStream_t s) {
   a.outer = c.outer; a.C = c.C; a.inner = c.inner; a.ignore_index = c.ignore_index;
   a.smoothing = (T)c.label_smoothing;
   a.status = c.status;
+  return a;
+}
+// long contiguous class axes take the CTA-per-row kernel, everything else a thread per position
+bool ce_row_path(const CeProblem& c) { return c.inner == 1 && c.C >= 512 && c.outer * c.inner <= 0x7fffffff; }
+
+template <typename T>
+cudaError_t ce_rows_typed(const CeProblem& c, cudaStream_t s) {
+  CeRowArgs<T> a = ce_args<T>(c);
   const int64_t n = c.outer * c.inner;
-  if (c.inner == 1 && c.C >= 512 && n <= 0x7fffffff) {
+  if (ce_row_path(c)) {
     constexpr int VEC = 16 / (int)sizeof(T);
     const bool aligned = (reinterpret_cast<uintptr_t>(c.logits) & 15) == 0 && c.C % VEC == 0 &&
                          (!c.prob_targets || (reinterpret_cast<uintptr_t>(c.targets) & 15) == 0) &&
@@ -652,6 +695,15 @@ cudaError_t ce_rows_typed(const CeProblem& c, cudaStream_t s) {
 cudaError_t launch_ce_rows(const CeProblem& c, cudaStream_t s) {
   if (c.outer * c.inner == 0) return cudaSuccess;
   return c.dtype == BG_F64 ? ce_rows_typed<double>(c, s) : ce_rows_typed<float>(c, s);
+}
+
+bool ce_small_usable(const CeProblem& c) { const int64_t n = c.outer * c.inner; return n > 0 && n <= 256 && !ce_row_path(c); }
+
+cudaError_t launch_ce_small(const CeProblem& c, void* out, int reduction, double fixed_count, cudaStream_t s) {
+  const int64_t* targets = c.prob_targets ? nullptr : reinterpret_cast<const int64_t*>(c.targets);
+  if (c.dtype == BG_F64) ce_small_kernel<double><<<1, 256, 0, s>>>(ce_args<double>(c), targets, reinterpret_cast<double*>(out), reduction, fixed_count);
+  else ce_small_kernel<float><<<1, 256, 0, s>>>(ce_args<float>(c), targets, reinterpret_cast<float*>(out), reduction, fixed_count);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_ce_reduce(const void* per_pos, const int64_t* targets, const void* sel_w, void* out, int dtype, int64_t n,

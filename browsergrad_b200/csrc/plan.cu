@@ -3242,6 +3242,10 @@ void Compiler::emit_ce(int n, int key) {
     c.outer = outer; c.C = C; c.inner = inner; c.ignore_index = ignore;
     c.label_smoothing = smoothing;
     c.status = r.ctx->d_status;
+    if (reduction != 0 && ce_small_usable(c)) {
+      cudaError_t e1 = launch_ce_small(c, r.ptr[so], reduction, (double)npos, r.ctx->stream);
+      return e1 == cudaSuccess ? (int)BG_OK : cuda_fail(r.ctx, e1, "cross entropy launch");
+    }
     cudaError_t e = launch_ce_rows(c, r.ctx->stream);
     if (e == cudaSuccess && reduction != 0)
       e = launch_ce_reduce(c.per_pos, prob ? nullptr : reinterpret_cast<const int64_t*>(c.targets), c.sel_w, r.ptr[so], dt, npos, reduction,
