@@ -182,6 +182,8 @@ attn16_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   // key tile, and a global load in the MMA thread's loop delays every product behind it.  Without a class table
   // every key tile is processed (class 3 with a mask, else 1); a tile B that does not exist has class 0 throughout.
   const bool has_b = 2 * pair + 1 < n_qt;
+  grid_dependency_wait();       // the tile classes below may come from a kernel of the same plan
+  grid_launch_dependents();
   {
     const unsigned char* cls_a = p.tile_class ? p.tile_class + (size_t)(2 * pair) * n_kv : nullptr;
     const unsigned char* cls_b = p.tile_class && has_b ? p.tile_class + (size_t)(2 * pair + 1) * n_kv : nullptr;
@@ -610,8 +612,7 @@ cudaError_t launch_variant(bool vmn, bool pt, bool kv32, dim3 grid, size_t smem,
   if (fa.numRegs < (kv32 ? PairRegs<true>::Launch : PairRegs<false>::Launch)) return cudaErrorLaunchOutOfResources;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  kern<<<grid, kv32 ? PairRegs<true>::Threads : PairRegs<false>::Threads, smem, s>>>(k, v, p);
-  return cudaGetLastError();
+  return launch_dependent(kern, dim3(grid), dim3(kv32 ? PairRegs<true>::Threads : PairRegs<false>::Threads), smem, s, k, v, p);
 }
 
 }  // namespace

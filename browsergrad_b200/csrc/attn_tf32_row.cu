@@ -159,6 +159,8 @@ attn_tf32_row_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_cons
   const int b = bh / p.H, h = bh % p.H;
   const int q0 = q_tile * kQRows;
   const int n_kv = (p.Sk + BKV - 1) / BKV;
+  grid_dependency_wait();       // the tile classes below may come from a kernel of the same plan
+  grid_launch_dependents();
   {
     const unsigned char* cls = p.tile_class ? p.tile_class + (size_t)q_tile * n_kv : nullptr;
     const unsigned char dflt = p.mask ? 3 : 1;
@@ -586,8 +588,7 @@ static cudaError_t launch_row(const attn::AttnParams& p, const CUtensorMap maps[
   }
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  kern<<<dim3(n_cta), C::Threads, smem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], pr);
-  return cudaGetLastError();
+  return launch_dependent(kern, dim3(n_cta), dim3(C::Threads), smem, s, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], pr);
 }
 
 cudaError_t launch_attn_tf32_row(const attn::AttnParams& p, const CUtensorMap maps[6], bool raw, cudaStream_t s) {

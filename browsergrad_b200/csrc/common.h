@@ -293,6 +293,11 @@ extern bool g_tc_assume_available;
 // CTA-pair (cta_group::2) GEMM tiles: 0 never, 1 for problems that fill the device (default), 2 whenever legal.
 extern int g_tc_pair_mode;
 extern int g_tc_pair_width;
+// Programmatic dependent launch of the decoder's kernels (1 = on): a kernel of the chain may be set up on the SMs the
+// kernel before it has left, while that kernel's last CTAs still run; it waits for the whole grid before it (and for
+// its memory) at grid_dependency_wait(), which it reaches before its first access to global memory.  Only kernels that
+// contain that wait are ever launched this way.
+extern int g_dependent_launch;
 bool tc_gemm_supported(int64_t M, int64_t N, int64_t K, int ab_dtype);
 cudaError_t launch_gemm_tc(const TcGemm& g, int* status, cudaStream_t s);
 // 1 to 3 problems that share A, M, N, K, dtypes and the epilogue kind and differ in B, bias and C, as one launch.
@@ -341,5 +346,26 @@ constexpr int kAttn16DefaultVariant = 15;
 // tensor memory; 3 as 1, and fp32 Q / K rows are split into their hi / lo planes inside the kernel.
 extern int g_attn32_variant;
 constexpr int kAttn32DefaultVariant = 3;
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Launch of a kernel that calls grid_dependency_wait() before it touches global memory.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute at{};
+  at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &at;
+  cfg.numAttrs = g_dependent_launch ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#endif
 
 }  // namespace bg

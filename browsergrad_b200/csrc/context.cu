@@ -395,6 +395,7 @@ int bg_set_option(bg_context* ctx, const char* key, int64_t value) {
     if (value != 0 && value != 256 && value != 192 && value != 128) return fail(ctx, BG_ERR_INVALID, "set_option: gemm_pair_tile_width is 0, 256, 192 or 128");
     g_tc_pair_width = (int)value;
   }
+  else if (k == "dependent_launch") g_dependent_launch = value != 0;   // process-wide: a launch policy, not plan state
   else if (k == "attention16_kernel") {
     if (value < -1 || value > 15) return fail(ctx, BG_ERR_INVALID, "set_option: attention16_kernel is a bit set in 0..15, or -1 for the default");
     g_attn16_variant = value < 0 ? kAttn16DefaultVariant : (int)value;     // process-wide: a launch policy, not plan state

@@ -153,6 +153,8 @@ __global__ void __launch_bounds__(256) gemm_small_kernel(const __grid_constant__
   __shared__ float As[SM_KC][SM_T + 1];
   __shared__ float Bs[SM_KC][SM_T + 1];
   __shared__ int s_last;
+  grid_dependency_wait();
+  grid_launch_dependents();
   const int splits = gridDim.z;
   const int64_t m0 = (int64_t)blockIdx.y * SM_T, n0 = (int64_t)blockIdx.x * SM_T;
   const int64_t k0 = (int64_t)blockIdx.z * kc;
@@ -258,8 +260,8 @@ bool gemm_small_plan(const GemmProblem& p, int sm_count, int* splits, int64_t* p
 cudaError_t launch_gemm_small(const GemmProblem& p, const void* bias, int act, void* partials, int* counters, int splits, cudaStream_t s) {
   const int64_t kc = (p.k + splits - 1) / splits;
   dim3 grid((unsigned)((p.n + SM_T - 1) / SM_T), (unsigned)((p.m + SM_T - 1) / SM_T), (unsigned)splits);
-  gemm_small_kernel<<<grid, 256, 0, s>>>(p, reinterpret_cast<const float*>(bias), act, reinterpret_cast<float*>(partials), counters, (int)kc);
-  return cudaGetLastError();
+  return launch_dependent(gemm_small_kernel, grid, dim3(256), 0, s, p, reinterpret_cast<const float*>(bias), act,
+                          reinterpret_cast<float*>(partials), counters, (int)kc);
 }
 
 cudaError_t launch_gemm_simt(const GemmProblem& p, cudaStream_t s) {

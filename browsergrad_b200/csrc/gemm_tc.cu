@@ -411,6 +411,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   const int n_chunks = p.num_k_blocks > 0 ? (p.num_k_blocks + p.chunk_blocks - 1) / p.chunk_blocks : 0;
+  grid_dependency_wait();       // barriers and tensor memory are set up; nothing of global memory has been touched
+  grid_launch_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -610,6 +612,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   const int n_chunks = p.num_k_blocks > 0 ? (p.num_k_blocks + p.chunk_blocks - 1) / p.chunk_blocks : 0;
+  grid_dependency_wait();       // barriers and tensor memory are set up; nothing of global memory has been touched
+  grid_launch_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -943,8 +947,7 @@ cudaError_t launch_variant(const TcGemm& g, int* status, cudaStream_t s) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int64_t grid = tiles < sms ? tiles : sms;
-  kern<<<(unsigned)grid, EpiCfg<TF32>::kThreads, smem, s>>>(a0, a1, a2, b0, b1, b2, p);
-  return cudaGetLastError();
+  return launch_dependent(kern, dim3((unsigned)grid), dim3(EpiCfg<TF32>::kThreads), smem, s, a0, a1, a2, b0, b1, b2, p);
 }
 
 template <bool TF32, int TN>
@@ -1025,9 +1028,8 @@ cudaError_t launch_pair(const TcGemm* gs, int n_prob, int* status, cudaStream_t 
   if (max_pairs <= 0) return cudaSuccess;   // not launched: the caller falls back to single CTAs
   const int64_t tiles = ((g.M + 255) / 256) * ((g.N + TN - 1) / TN) * n_prob;
   const int64_t pairs = tiles < max_pairs ? tiles : max_pairs;
-  kern<<<(unsigned)(2 * pairs), EpiCfg<TF32>::kThreads, smem, s>>>(a0, a1, a2, bm, p);
   *launched = true;
-  return cudaGetLastError();
+  return launch_dependent(kern, dim3((unsigned)(2 * pairs)), dim3(EpiCfg<TF32>::kThreads), smem, s, a0, a1, a2, bm, p);
 }
 
 }  // namespace
@@ -1044,6 +1046,7 @@ bool tc_gemm_supported(int64_t M, int64_t N, int64_t K, int ab_dtype) {
   return true;
 }
 
+int g_dependent_launch = 1;
 int g_tc_pair_mode = 1;   // 0: never, 1: when the problem fills the device with 256 x 256 tiles, 2: whenever legal
 
 // Width of the CTA-pair tile (256 rows x TN columns).  A pair works through ceil(tiles / pairs) tiles one

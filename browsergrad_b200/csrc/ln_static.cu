@@ -140,6 +140,8 @@ __device__ __forceinline__ float warp_sum(float x) {
 template <typename T, int OUT>
 __global__ void __launch_bounds__(256) static_ln_cta_kernel(const __grid_constant__ LnArgs a) {
   __shared__ float red_sum[2][8], red_sq[2][8];
+  grid_dependency_wait();
+  grid_launch_dependents();
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int c4 = (int)(a.cols >> 2);
   const int grp = threadIdx.x;
@@ -237,8 +239,7 @@ cudaError_t launch_t(const LnArgs& a, cudaStream_t s, int sm_count) {
   if (per_sm > 16) per_sm = 16;
   int64_t grid = (int64_t)sm_count * per_sm;
   if (grid > a.rows) grid = a.rows;
-  static_ln_cta_kernel<T, OUT><<<(unsigned)grid, threads, 0, s>>>(a);
-  return cudaGetLastError();
+  return launch_dependent(static_ln_cta_kernel<T, OUT>, dim3((unsigned)grid), dim3((unsigned)threads), 0, s, a);
 }
 
 }  // namespace

@@ -233,6 +233,8 @@ __global__ void gather_kernel(const __grid_constant__ GatherParams p) {
 __global__ void gather_rows4_kernel(const uint32_t* __restrict__ x, const int64_t* __restrict__ idx, uint32_t* __restrict__ out,
                                     long long n4, int cols, long long x_rows, int* status) {
   const int c4 = cols >> 2;
+  grid_dependency_wait();
+  grid_launch_dependents();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
     const int col = (int)(i % c4) * 4;
     const longlong2 a = __ldg(reinterpret_cast<const longlong2*>(idx) + 2 * i), b = __ldg(reinterpret_cast<const longlong2*>(idx) + 2 * i + 1);
@@ -510,6 +512,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) ce_small_kernel(const CeRowArgs<T> a, const int64_t* targets, T* out, int reduction, double fixed_count) {
   __shared__ double ssum[256];
   __shared__ double sden[256];
+  grid_dependency_wait();
+  grid_launch_dependents();
   const int64_t n = a.outer * a.inner;
   const bool need_sums = a.prob != nullptr || a.smoothing != T(0);
   double s = 0.0, c = 0.0;
@@ -640,9 +644,8 @@ cudaError_t launch_gather(const void* x, const int64_t* idx, void* out, int esiz
   if (esize == 4 && rank == 2 && dim == 0 && idx_shape[1] == x_shape[1] && x_shape[1] % 4 == 0 &&
       ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(idx) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
     const long long n4 = p.numel / 4;
-    gather_rows4_kernel<<<grid_for(n4, 256), 256, 0, s>>>(reinterpret_cast<const uint32_t*>(x), idx, reinterpret_cast<uint32_t*>(out), n4,
-                                                         (int)x_shape[1], (long long)x_shape[0], status);
-    return cudaGetLastError();
+    return launch_dependent(gather_rows4_kernel, dim3(grid_for(n4, 256)), dim3(256), 0, s, reinterpret_cast<const uint32_t*>(x), idx,
+                            reinterpret_cast<uint32_t*>(out), n4, (int)x_shape[1], (long long)x_shape[0], status);
   }
   const unsigned g = grid_for(p.numel, 256);
   switch (esize) {
@@ -701,9 +704,11 @@ bool ce_small_usable(const CeProblem& c) { const int64_t n = c.outer * c.inner; 
 
 cudaError_t launch_ce_small(const CeProblem& c, void* out, int reduction, double fixed_count, cudaStream_t s) {
   const int64_t* targets = c.prob_targets ? nullptr : reinterpret_cast<const int64_t*>(c.targets);
-  if (c.dtype == BG_F64) ce_small_kernel<double><<<1, 256, 0, s>>>(ce_args<double>(c), targets, reinterpret_cast<double*>(out), reduction, fixed_count);
-  else ce_small_kernel<float><<<1, 256, 0, s>>>(ce_args<float>(c), targets, reinterpret_cast<float*>(out), reduction, fixed_count);
-  return cudaGetLastError();
+  if (c.dtype == BG_F64)
+    return launch_dependent(ce_small_kernel<double>, dim3(1), dim3(256), 0, s, ce_args<double>(c), targets, reinterpret_cast<double*>(out), reduction,
+                            fixed_count);
+  return launch_dependent(ce_small_kernel<float>, dim3(1), dim3(256), 0, s, ce_args<float>(c), targets, reinterpret_cast<float*>(out), reduction,
+                          fixed_count);
 }
 
 cudaError_t launch_ce_reduce(const void* per_pos, const int64_t* targets, const void* sel_w, void* out, int dtype, int64_t n,

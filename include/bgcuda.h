@@ -178,6 +178,10 @@ int bg_abi_version(void);
  * generic interpreter and every value in the type the graph gives it), "gemm_groups" (0/1), "gemm_cta_pairs" (0/1/2), "gemm_pair_tile_width" (0/256/192/128),
  * "attention16_kernel" (bit set: 1 two query tiles per CTA, 2 V as an MN-major operand, 4 P in tensor memory,
  * 8 fp32 K / V converted inside the kernel; 0 one query tile per CTA; -1 restores the default),
+ * "dependent_launch" (0/1, default 1: the tensor-core GEMMs, the fused attentions, the LayerNorm rows, the small GEMM,
+ * the one-launch cross entropy and the embedding lookup are launched with programmatic stream serialization -- each is
+ * set up on the SMs the kernel before it has left and waits for that whole kernel before its first access to global
+ * memory; 0 restores plain stream order),
  * "attention32_kernel" (3xTF32 attention: 0 two threads per row, 1 one thread per row with P and O in tensor
  * memory, 3 the same with fp32 Q / K rows split into planes inside the kernel; -1 restores the default). */
 int bg_set_option(bg_context* ctx, const char* key, int64_t value);

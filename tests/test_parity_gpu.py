@@ -63,6 +63,24 @@ def test_pattern_kernels_and_interpreter_agree(bridge, name):
         assert got_static.tobytes() == got_generic.tobytes()
 
 
+@pytest.mark.parametrize("name", ["c1_mlp_ce", "c3_chain_gelu_planes", "ln_then_qkv_f16", "c4_attn_block_f64", "c4_attn_merge_heads_bf16",
+                                  "gather_rows_by4"])
+def test_dependent_launch_changes_no_bit(bridge, name):
+    """Option dependent_launch: the decoder's kernels may be set up on the SMs while the kernel before them drains and
+    wait for it before they touch global memory; the results are those of plain stream order."""
+    case = CASES[name]
+    t, store, _ = build_case(case)
+    want = oracle_value(t, store)
+    got_on = realize_cuda(t, bridge)
+    bridge.set_option("dependent_launch", 0)
+    try:
+        got_off = realize_cuda(t, bridge)
+    finally:
+        bridge.set_option("dependent_launch", 1)
+    assert got_on.tobytes() == got_off.tobytes()
+    check(case, got_on, want, f"{name} (dependent launch)")
+
+
 @pytest.mark.parametrize("name,expect", [
     ("c3_tc_f32", "gemm_tc_3xtf32+bias+gelu[float32]"),
     ("c3_tc_f16", "gemm_tc+bias+gelu[float16]"),
